@@ -1,0 +1,288 @@
+"""ctypes binding of the CPU oracle (``liboracle.so``, built from ``rivoli_oracle.c``).
+
+Test infrastructure only: imported by ``tests/``, by the smoke check and by the
+``cpu_baseline`` / ``--impl reference`` legs of the benchmark. The product package never
+imports this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "liboracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile ``liboracle.so`` beside its source if it is missing or stale."""
+    src = os.path.join(_HERE, "rivoli_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return _SO
+
+
+class Geom(C.Structure):
+    """Mirror of ``orc_geom`` (same field order as the product's ``DsaGeom``)."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "n_heads", "kv_lora", "rope_dim", "index_heads", "index_dim", "page_tokens", "top_k",
+        "max_pages_per_seq", "n_pool_pages")] + [(n, C.c_float) for n in (
+        "softmax_scale", "index_wscale", "index_dscale")]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        L = _lib
+        L.orc_f32_to_bf16.restype = C.c_uint16
+        L.orc_f32_to_bf16.argtypes = [C.c_float]
+        L.orc_bf16_to_f32.restype = C.c_float
+        L.orc_bf16_to_f32.argtypes = [C.c_uint16]
+        L.orc_f32_to_e4m3.restype = C.c_uint8
+        L.orc_f32_to_e4m3.argtypes = [C.c_float]
+        L.orc_e4m3_to_f32.restype = C.c_float
+        L.orc_e4m3_to_f32.argtypes = [C.c_uint8]
+        L.orc_lcg_next.restype = C.c_float
+        L.orc_pool_new.restype = C.c_void_p
+        L.orc_pool_block_table.restype = C.POINTER(C.c_int32)
+        L.orc_pool_free_list.restype = C.POINTER(C.c_int32)
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    a = np.ascontiguousarray(a, dtype=dt)
+    return a
+
+
+# --- codecs -------------------------------------------------------------------------------------
+def f32_to_bf16(x) -> np.ndarray:
+    """Vectorised RNE f32 -> bf16 bits (same rule as ``orc_f32_to_bf16``)."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    nan = (b & 0x7FFFFFFF) > 0x7F800000
+    r = ((b >> 16) & 1) + 0x7FFF
+    out = ((b + r) >> 16).astype(np.uint16)
+    out[nan] = ((b[nan] >> 16) | 0x40).astype(np.uint16)
+    return out
+
+
+def bf16_to_f32(b) -> np.ndarray:
+    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_e4m3(x) -> np.ndarray:
+    x = _c(x, np.float32)
+    L = lib()
+    return np.array([L.orc_f32_to_e4m3(float(v)) for v in x.ravel()], dtype=np.uint8).reshape(x.shape)
+
+
+def e4m3_table() -> np.ndarray:
+    L = lib()
+    return np.array([L.orc_e4m3_to_f32(c) for c in range(256)], dtype=np.float32)
+
+
+class Lcg:
+    """The reference tests' deterministic input stream."""
+
+    def __init__(self, seed: int):
+        self.state = C.c_uint64(seed)
+
+    def f(self) -> float:
+        return float(lib().orc_lcg_next(C.byref(self.state)))
+
+    def draws(self, n: int) -> np.ndarray:
+        out = np.empty(n, dtype=np.float32)
+        lib().orc_lcg_fill(C.byref(self.state), _p(out), C.c_size_t(n))
+        return out
+
+
+# --- reference-layout operators -----------------------------------------------------------------
+def append_kv(latent, rope, lc8, lscale, rc, pos, kvl, ropn, n_blocks) -> int:
+    return lib().orc_append_kv(_p(_c(latent, np.float32)), _p(_c(rope, np.float32)), _p(lc8),
+                               _p(lscale), _p(rc), pos, kvl, ropn, n_blocks)
+
+
+def gather_rope(q, h, qh, nope, ropn) -> np.ndarray:
+    out = np.zeros(h * ropn, dtype=np.float32)
+    lib().orc_gather_rope(_p(_c(q, np.float32)), _p(out), h, qh, nope, ropn)
+    return out
+
+
+def index_append(k, kcache, pos, hd) -> None:
+    lib().orc_index_append(_p(_c(k, np.float32)), _p(kcache), pos, hd)
+
+
+def index_score(q, w, kcache, heads, nt, nh, nact, hd, wscale, dscale) -> np.ndarray:
+    out = np.zeros(nt, dtype=np.float32)
+    hp = None if heads is None else _c(heads, np.uint32)
+    lib().orc_index_score(_p(_c(q, np.float32)), _p(_c(w, np.float32)), _p(_c(kcache, np.uint16)),
+                          _p(hp), nt, nh, nact, hd, C.c_float(wscale), C.c_float(dscale), _p(out))
+    return out
+
+
+def index_topk(scores, k) -> np.ndarray:
+    s = _c(scores, np.float32)
+    rows = np.zeros(max(min(k, s.size), 1), dtype=np.uint32)
+    n = lib().orc_index_topk(_p(s), s.size, k, _p(rows))
+    return rows[:n]
+
+
+def topk_value_order(scores, k) -> np.ndarray:
+    s = _c(scores, np.float32)
+    rows = np.zeros(max(min(k, s.size), 1), dtype=np.uint32)
+    n = lib().orc_topk_value_order(_p(s), s.size, k, _p(rows))
+    return rows[:n]
+
+
+def softmax(v) -> np.ndarray:
+    v = _c(v, np.float32).copy()
+    lib().orc_softmax(_p(v), v.size)
+    return v
+
+
+def mla_attend(qabs, qrope, lc8, lscale, rc, rows, H, nr, kvl, rope, n_blocks, scale) -> np.ndarray:
+    out = np.zeros(H * kvl, dtype=np.float32)
+    rp = None if rows is None else _c(rows, np.uint32)
+    lib().orc_mla_attend(_p(_c(qabs, np.float32)), _p(_c(qrope, np.float32)), _p(_c(lc8, np.uint8)),
+                         _p(_c(lscale, np.float32)), _p(_c(rc, np.uint16)), _p(rp), H, nr, kvl, rope,
+                         n_blocks, C.c_float(scale), _p(out))
+    return out
+
+
+def mla_plan_splits(H, nr, have_scratch=True):
+    n, tps = C.c_int(), C.c_int()
+    lib().orc_mla_plan_splits(H, nr, int(have_scratch), C.byref(n), C.byref(tps))
+    return n.value, tps.value
+
+
+def mla_attend_partial(qabs, qrope, lc8, lscale, rc, H, r0, r1, kvl, rope, n_blocks, scale):
+    acc = np.zeros(H * kvl, dtype=np.float32)
+    ml = np.zeros(H * 2, dtype=np.float32)
+    lib().orc_mla_attend_partial(_p(_c(qabs, np.float32)), _p(_c(qrope, np.float32)),
+                                 _p(_c(lc8, np.uint8)), _p(_c(lscale, np.float32)),
+                                 _p(_c(rc, np.uint16)), H, r0, r1, kvl, rope, n_blocks,
+                                 C.c_float(scale), _p(acc), _p(ml))
+    return acc, ml
+
+
+def attend_combine(acc, ml, H, kvl, n_splits) -> np.ndarray:
+    out = np.zeros(H * kvl, dtype=np.float32)
+    lib().orc_attend_combine(_p(_c(acc, np.float32)), _p(_c(ml, np.float32)), H, kvl, n_splits, _p(out))
+    return out
+
+
+# --- paged layout ---------------------------------------------------------------------------------
+def kv_append_paged(g: Geom, latent, index_key, row_seq, row_pos, block_table, latent_pool,
+                    latent_scale, index_pool, index_scale) -> int:
+    latent = _c(latent, np.uint16)
+    index_key = _c(index_key, np.uint16)
+    row_pos = _c(row_pos, np.int32)
+    rs = None if row_seq is None else _c(row_seq, np.int32)
+    return lib().orc_kv_append_paged(C.byref(g), _p(latent), _p(index_key), _p(rs), _p(row_pos),
+                                     row_pos.size, _p(_c(block_table, np.int32)), _p(latent_pool),
+                                     _p(latent_scale), _p(index_pool), _p(index_scale))
+
+
+def index_q_quant(q_bf16, hd):
+    q = _c(q_bf16, np.uint16)
+    n = q.size // hd
+    codes = np.zeros(q.shape, dtype=np.uint8)
+    scales = np.zeros(n, dtype=np.float32)
+    lib().orc_index_q_quant(_p(q), n, hd, _p(codes), _p(scales))
+    return codes, scales
+
+
+def index_score_paged(g: Geom, qcodes, qscales, w, index_pool, index_scale, block_table, seq_len,
+                      score_stride) -> np.ndarray:
+    seq_len = _c(seq_len, np.int32)
+    B = seq_len.size
+    scores = np.zeros((B, score_stride), dtype=np.float32)
+    lib().orc_index_score_paged(C.byref(g), _p(_c(qcodes, np.uint8)), _p(_c(qscales, np.float32)),
+                                _p(_c(w, np.float32)), _p(index_pool), _p(index_scale),
+                                _p(_c(block_table, np.int32)), _p(seq_len), B, _p(scores), score_stride)
+    return scores
+
+
+def index_topk_batched(scores, seq_len, k):
+    scores = _c(scores, np.float32)
+    seq_len = _c(seq_len, np.int32)
+    B = seq_len.size
+    rows = np.full((B, k), 0xFFFFFFFF, dtype=np.uint32)
+    n_sel = np.zeros(B, dtype=np.int32)
+    lib().orc_index_topk_batched(_p(scores), scores.shape[1], _p(seq_len), B, k, _p(rows), _p(n_sel))
+    return rows, n_sel
+
+
+def mla_attend_paged(g: Geom, q, latent_pool, latent_scale, block_table, rows, n_rows,
+                     want_f32=False):
+    q = _c(q, np.uint16)
+    n_rows = _c(n_rows, np.int32)
+    B = n_rows.size
+    out = np.zeros((B, g.n_heads, g.kv_lora), dtype=np.uint16)
+    out_f32 = np.zeros((B, g.n_heads, g.kv_lora), dtype=np.float32)
+    m = np.zeros((B, g.n_heads), dtype=np.float32)
+    lse = np.zeros((B, g.n_heads), dtype=np.float32)
+    rp, stride = (None, 0) if rows is None else (_c(rows, np.uint32), rows.shape[1])
+    lib().orc_mla_attend_paged(C.byref(g), _p(q), _p(latent_pool), _p(latent_scale),
+                               _p(_c(block_table, np.int32)), _p(rp), stride, _p(n_rows), B, _p(out),
+                               _p(out_f32), _p(m), _p(lse))
+    return (out, out_f32, m, lse) if want_f32 else (out, m, lse)
+
+
+def attend_merge_partials(part_out, part_lse, kvl) -> np.ndarray:
+    part_out = _c(part_out, np.uint16)
+    part_lse = _c(part_lse, np.float32)
+    G = part_out.shape[0]
+    n = part_lse.size // G
+    out = np.zeros((n, kvl), dtype=np.uint16)
+    lib().orc_attend_merge_partials(_p(part_out), _p(part_lse), G, n, kvl, _p(out))
+    return out
+
+
+class Pool:
+    """LIFO page allocator of the oracle (see ``orc_pool_*``)."""
+
+    def __init__(self, n_pages, n_seqs, max_pages_per_seq, page_tokens):
+        self._h = C.c_void_p(lib().orc_pool_new(n_pages, n_seqs, max_pages_per_seq, page_tokens))
+        self.shape = (n_seqs, max_pages_per_seq)
+        self.n_pages = n_pages
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().orc_pool_free(self._h)
+            self._h = None
+
+    def shuffle(self, seed):
+        lib().orc_pool_shuffle(self._h, C.c_uint64(seed))
+
+    def reserve(self, seq, n_tokens) -> int:
+        return lib().orc_pool_reserve(self._h, seq, n_tokens)
+
+    def release(self, seq) -> int:
+        return lib().orc_pool_release(self._h, seq)
+
+    @property
+    def n_free(self) -> int:
+        return lib().orc_pool_n_free(self._h)
+
+    def block_table(self) -> np.ndarray:
+        p = lib().orc_pool_block_table(self._h)
+        return np.ctypeslib.as_array(p, shape=self.shape).copy()
+
+    def free_list(self) -> np.ndarray:
+        p = lib().orc_pool_free_list(self._h)
+        return np.ctypeslib.as_array(p, shape=(self.n_pages,))[: self.n_free].copy()
+
+
+def num_threads() -> int:
+    return lib().orc_num_threads()
