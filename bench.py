@@ -1,0 +1,358 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-time MLA + DSA KV-cache path (one layer-step per "step").
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1]
+
+A layer-step = append one token per sequence -> indexer q quant + score + exact top-k ->
+gather/dequant + MLA attention -> bf16 out, over the whole per-GPU batch. Default workload
+is the sparse DSA decode layer (batch 128 x context 16384, top-k 2048, 64-token pages
+scattered over a pool 1.25x the live set). With N > 1 every rank runs the same per-GPU
+batch on its own sequences (weak scaling, no collective on the data path); the value is the
+aggregate over ranks, timed on the device and reduced with MAX over ranks.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: B per GPU, context after append, heads, index heads, index dim, page, top_k, seed
+    "cfg1": dict(B=1, ctx=257, n_heads=16, index_heads=8, index_dim=64, page_tokens=16, top_k=64, seed=0),
+    "cfg2": dict(B=32, ctx=2048, n_heads=64, index_heads=32, index_dim=128, page_tokens=64, top_k=2048, seed=1),
+    "cfg3": dict(B=128, ctx=16384, n_heads=64, index_heads=32, index_dim=128, page_tokens=64, top_k=2048, seed=2),
+}
+KV_LORA, ROPE = 512, 64
+METRIC = "DSA decode layer-steps/s (batch×ctx)"
+
+
+def algorithmic_bytes(w):
+    """Per-sequence algorithmic bytes of one layer-step, by stage (append, index, attend)."""
+    nt, k, H, nh, hd = w["ctx"], w["top_k"], w["n_heads"], w["index_heads"], w["index_dim"]
+    n_sel = min(k, nt)
+    W = KV_LORA + ROPE
+    append = W * 2 + hd * 2 + 4 + W + 8 + hd + 4
+    index = nt * (hd + 4) + nh * hd * 2 + nh * 4 + n_sel * 4
+    attend = n_sel * (W + 8) + H * W * 2 + n_sel * 4 + H * KV_LORA * 2
+    return dict(append=append, index=index, attend=attend)
+
+
+def algorithmic_flops(w):
+    nt, k, H, nh, hd = w["ctx"], w["top_k"], w["n_heads"], w["index_heads"], w["index_dim"]
+    n_sel = min(k, nt)
+    return dict(index=2 * nh * hd * nt, attend=2 * H * n_sel * (KV_LORA + ROPE + KV_LORA))
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def build_layer(w, device, seed):
+    """Device state for one workload: pools filled on the GPU by the append kernel."""
+    import torch
+    from rivoli_b200 import backend as be
+    from rivoli_b200.layer import DsaDecodeLayer
+
+    B, ctx, P = w["B"], w["ctx"], w["page_tokens"]
+    pages_per_seq = (ctx + P - 1) // P
+    live = B * pages_per_seq
+    n_pool = max(int(np.ceil(live * 1.25)), live)
+    g = be.DsaGeom.make(n_heads=w["n_heads"], kv_lora=KV_LORA, rope_dim=ROPE, index_heads=w["index_heads"],
+                        index_dim=w["index_dim"], page_tokens=P, top_k=w["top_k"],
+                        max_pages_per_seq=pages_per_seq, n_pool_pages=n_pool)
+    layer = DsaDecodeLayer(g, B, device=device, max_ctx=ctx, shuffle_seed=seed * 7919 + 17)
+    for b in range(B):
+        layer.reserve(b, ctx)
+    layer.upload_block_table()
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    W = KV_LORA + ROPE
+    # history: ctx-1 tokens per sequence, appended in chunks to bound scratch memory
+    chunk = 1 << 16
+    total = B * (ctx - 1)
+    for s0 in range(0, total, chunk):
+        n = min(chunk, total - s0)
+        idx = torch.arange(s0, s0 + n, device=device, dtype=torch.int64)
+        seq = (idx // (ctx - 1)).to(torch.int32)
+        pos = (idx % (ctx - 1)).to(torch.int32)
+        lat = torch.randn((n, W), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+        key = torch.randn((n, w["index_dim"]), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+        layer.append(lat, key, pos, seq)
+    torch.cuda.synchronize(device)
+    layer.check_status()
+    return g, layer, gen
+
+
+def step_inputs(w, device, gen, pinned=False):
+    import torch
+    B, W = w["B"], KV_LORA + ROPE
+    mk = lambda *s: torch.randn(s, generator=gen, device=device, dtype=torch.float32)
+    d = dict(latent=mk(B, W).to(torch.bfloat16), index_key=mk(B, w["index_dim"]).to(torch.bfloat16),
+             index_q=mk(B, w["index_heads"], w["index_dim"]).to(torch.bfloat16),
+             index_w=mk(B, w["index_heads"]).to(torch.bfloat16).to(torch.float32),
+             q=mk(B, w["n_heads"], W).to(torch.bfloat16))
+    if pinned:
+        return {k: v.cpu().pin_memory() for k, v in d.items()}
+    return d
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from rivoli_b200 import backend as be
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    be.lib()
+    w = WORKLOADS[args.workload]
+    g, layer, gen = build_layer(w, device, w["seed"] + 1000 * rank)
+    B, ctx = w["B"], w["ctx"]
+    x = step_inputs(w, device, gen)
+    row_pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=device)
+    seq_len = torch.full((B,), ctx, dtype=torch.int32, device=device)
+
+    def step(inp, timed=None):
+        ev = timed
+        if ev: ev[0].record()
+        layer.append(inp["latent"], inp["index_key"], row_pos)
+        if ev: ev[1].record()
+        layer.select(inp["index_q"], inp["index_w"], seq_len)
+        if ev: ev[2].record()
+        layer.attend(inp["q"])
+        if ev: ev[3].record()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        step(x)
+    barrier()
+    layer.check_status()
+
+    # ---- device-resident timing --------------------------------------------------------------------
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for i in range(args.steps):
+        step(x, evs[i])
+    t1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = t0.elapsed_time(t1)
+    stage_ms = [float(np.mean([e[i].elapsed_time(e[i + 1]) for e in evs])) for i in range(3)]
+
+    # ---- end to end through the host-facing call: pinned host inputs, device->host result ------------
+    xh = step_inputs(w, device, gen, pinned=True)
+    xd = {k: torch.empty_like(v, device=device) for k, v in xh.items()}
+    out_h = torch.empty((B, w["n_heads"], KV_LORA), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        for k in xh:
+            xd[k].copy_(xh[k], non_blocking=True)
+        step(xd)
+        out_h.copy_(layer.out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    h2d = int(sum(v.numel() * v.element_size() for v in xh.values()))
+    d2h = int(out_h.numel() * out_h.element_size())
+
+    if world > 1:
+        t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        ab, af = algorithmic_bytes(w), algorithmic_flops(w)
+        peaks = {}
+        pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(pk):
+            peaks = json.load(open(pk))
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+        # dominant kernel: the indexer (score + top-k), HBM bound
+        idx_ms = stage_ms[1]
+        achieved = ab["index"] * B / (idx_ms * 1e-3) / 1e9
+        value = world * args.steps / (ms_total * 1e-3)
+        line = {
+            "metric": METRIC, "value": value, "unit": "layer-steps/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}: batch {B}/GPU x ctx {ctx}, top-k {w['top_k']}, "
+                                   f"{w['page_tokens']}-token pages scattered in a 1.25x pool, seed {w['seed']}",
+                       "l2": "inputs larger than L2 (index keys + latents >> 126 MB)" if B * ctx * 132 > 2e8
+                             else "working set fits L2: latency-bound config",
+                       "sequences_per_step": B * world},
+            "e2e": {"value": world * args.steps / (ms_e2e * 1e-3), "unit": "layer-steps/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * 6,
+            "stage_ms": {"append": stage_ms[0], "index_select": stage_ms[1], "attend": stage_ms[2]},
+            "roofline": {"bound": "hbm", "kernel": "index_select (q quant + score + top-k)",
+                         "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "peak_source": peak_src, "traffic": None,
+                         "layer_step_bytes": sum(ab.values()) * B,
+                         "layer_step_gbs": sum(ab.values()) * B / (ms_total / args.steps * 1e-3) / 1e9,
+                         "attend_tflops": af["attend"] * B / (stage_ms[2] * 1e-3) / 1e12},
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(w, seconds=12.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_sample_state(w, n_seq, seed):
+    """A bounded sample of the workload for the CPU arm: n_seq sequences of the same shape."""
+    from oracle.workload import State
+    return State(seed, n_seq, [w["ctx"]] * n_seq, n_heads=w["n_heads"], index_heads=w["index_heads"],
+                 index_dim=w["index_dim"], page_tokens=w["page_tokens"], top_k=w["top_k"], pool_factor=1.25)
+
+
+def cpu_baseline(w, seconds=12.0, n_seq=None):
+    """Times the oracle (C restatement of the reference's host arithmetic, OpenMP) on a bounded
+    sample of the same workload and scales to whole-batch layer-steps/s."""
+    from oracle import oracle as orc
+    n_seq = n_seq or max(1, min(w["B"], 8))
+    st = cpu_sample_state(w, n_seq, w["seed"])
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        st.oracle_step()
+        reps += 1
+        if time.perf_counter() - t0 > seconds or reps >= 50:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    per_seq = dt / n_seq
+    return {"value": 1.0 / (per_seq * w["B"]), "unit": "layer-steps/s", "cores": orc.num_threads(),
+            "kind": "port", "nproc": os.cpu_count(),
+            "sample": f"{n_seq} of {w['B']} sequences of the same shape (ctx {w['ctx']}), {reps} repetitions, "
+                      f"{dt:.3f} s per sample step; scaled by {w['B']}/{n_seq}"}
+
+
+def run_reference(args):
+    """The reference's own CPU arithmetic for this path (the oracle port: the reference is a
+    Rust + HIP tree that cannot be compiled on this image), all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = WORKLOADS[args.workload]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    from oracle import oracle as orc
+    n_seq = max(1, min(w["B"], 8))
+    st = cpu_sample_state(w, n_seq, w["seed"])
+    for _ in range(min(args.warmup, 1)):
+        st.oracle_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        st.oracle_step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = 1.0 / (dt / n_seq * w["B"])
+    sample = (f"each step = {n_seq} of {w['B']} sequences of the same shape (ctx {w['ctx']}); value scaled by "
+              f"{w['B']}/{n_seq}; one host, all threads")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "layer-steps/s", "n_gpus": world,
+            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / n_seq * w["B"] * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU)",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}: batch {w['B']} x ctx {w['ctx']}, top-k {w['top_k']}"},
+            "cpu_baseline": {"value": value, "unit": "layer-steps/s", "cores": orc.num_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": value, "unit": "layer-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg3", choices=list(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,198 @@
+/*
+ * C ABI of librivolikernels (CUDA, sm_100a): the decode-time MLA + DSA KV-cache operators.
+ *
+ * This is the FFI wall the reference's `crates/backend` binds: launch-only entry points
+ * `extern "C" int rivoli_<op>(...)` over caller-owned DEVICE pointers. None of them
+ * allocates, copies to the host or synchronises unless its comment says so.
+ *
+ * Return code convention (reference: crates/backend/kernels/mla.hip:7-8,
+ * crates/backend/src/hip.rs:328-336):
+ *      0           launched
+ *      > 0         argument guard, decided on the host BEFORE anything is dereferenced
+ *                  1001 argument <= 0 / out of range      1002 size bound
+ *                  1003 grouping / power of two           1004 divisibility / unsupported width
+ *                  1005 geometry                          1006 shared-memory / scalar range
+ *                  1007 page pool exhausted               1008 library state (no device, ...)
+ *      < 0         -(cudaError_t) of the launch
+ *
+ * Part 1 keeps the reference's signatures symbol for symbol (single sequence, f32
+ * activations, contiguous slabs, null stream). Part 2 is the batched / paged / bf16
+ * surface the reference does not have; every such entry point takes one `const DsaGeom*`
+ * and a trailing `void* stream` (a cudaStream_t; NULL = the legacy default stream), the
+ * convention of crates/backend/kernels/mla.hip:508-525.
+ */
+#ifndef RIVOLI_KERNELS_H
+#define RIVOLI_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------------------------------
+ * Part 1 - reference-compatible symbols
+ * ------------------------------------------------------------------------------------- */
+
+/* Replaces crates/backend/kernels/fwd.hip:224-235 (Rust: launch_append_kv,
+ * crates/backend/src/hip_attn.rs:130-147). One token: per-128 block absmax scale + e4m3
+ * codes into row `pos` of lc8/lscale, roped key as bf16 into row `pos` of rc.
+ * Guards: 1001 pos<0 or any size <=0; 1002 kvl not a multiple of 128 in [128,1024] or ropn>kvl. */
+int rivoli_append_kv(const float* latent, const float* rope, unsigned char* lc8, float* lscale,
+                     unsigned short* rc, int pos, int kvl, int ropn, int n_blocks);
+
+/* Replaces crates/backend/kernels/fwd.hip:237-245 (launch_gather_rope). */
+int rivoli_gather_rope(const float* q, float* qrope, int h, int qh, int nope, int ropn);
+
+/* Replaces crates/backend/kernels/indexer.hip:268-276 (launch_index_append,
+ * crates/backend/src/hip_attn.rs:445-455): one bf16 indexer key row at `pos`. */
+int rivoli_index_append(const float* k, unsigned short* kcache, int pos, int hd);
+
+/* Replaces crates/backend/kernels/indexer.hip:278-295 (launch_index_score,
+ * hip_attn.rs:457-476): scores[t] = sum over active heads of w[h]*wscale*ReLU((q_h.k_t)*dscale).
+ * heads NULL = all nh heads. Guards: 1001 sizes / nact>nh; 1002 nact>1024 or staging > 64 KiB. */
+int rivoli_index_score(const float* q, const float* w, const unsigned short* kcache,
+                       const unsigned int* heads, int nt, int nh, int nact, int hd, float wscale,
+                       float dscale, float* scores);
+
+/* Replaces crates/backend/kernels/indexer.hip:327-335 (launch_index_topk,
+ * hip_attn.rs:478-495): rows[0..min(k,nt)) = the top-k set (score descending, index
+ * ascending on ties, -0.0 == +0.0) emitted ASCENDING by index. Writes nothing past
+ * min(k,nt). Guards: 1001 nt<=0 or k<=0. */
+int rivoli_index_topk(const float* scores, int nt, int k, unsigned int* rows);
+
+/* Replaces crates/backend/kernels/attn.hip:279-308 (launch_attend, hip_attn.rs:101-128):
+ * clat[h] = sum_t softmax_t((qabs_h.L_t + qrope_h.R_t)*scale) * L_t over the fp8 latent cache
+ * (per-128 block scales) and bf16 roped keys; rows NULL = dense over 0..nr, else the nr
+ * listed tokens. partial = scratch of rivoli_mla_attend_scratch_floats() floats, or NULL
+ * (single split). Guards: 1001 sizes; 1002 16*(kvl+rope)*4 > 65536; 1004 kvl>512 or kvl%128. */
+int rivoli_mla_attend(const float* qabs, const float* qrope, const unsigned char* Lc8,
+                      const float* Lscale, const unsigned short* Rc, const unsigned int* rows, int H,
+                      int nr, int kvl, int rope, int n_blocks, float scale, float* clat,
+                      float* partial);
+
+/* Replaces crates/backend/kernels/attn.hip:100-103 (crates/backend/src/hip.rs:425-430). */
+size_t rivoli_mla_attend_scratch_floats(int H, int kvl);
+
+/* Replaces crates/backend/kernels/linalg.hip:403 (hip.rs device_sync): blocks until every
+ * launched kernel has retired. Returns 0 or -(cudaError_t). */
+int rivoli_device_sync(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Part 2 - batched, paged, bf16 surface
+ *
+ * Pool row r = page * page_tokens + slot:
+ *   latent_pool  u8  [n_pool_pages * page_tokens][kv_lora + rope_dim]  e4m3 c_kv then k_rope
+ *   latent_scale f32 [n_pool_pages * page_tokens][2]                   s_c, s_r (absmax/448, 1 if 0)
+ *   index_pool   u8  [n_pool_pages * page_tokens][index_dim]           e4m3 indexer key
+ *   index_scale  f32 [n_pool_pages * page_tokens]
+ *   block_table  i32 [B][max_pages_per_seq]    page id of logical page j of sequence b
+ * Token t of sequence b lives at page block_table[b][t / page_tokens], slot t % page_tokens.
+ * ------------------------------------------------------------------------------------- */
+
+/* Geometry of one MLA + DSA decode layer. Plain 32-bit fields, 48 bytes, align 4; the
+ * Rust mirror is #[repr(C)] and asserts the same size (cf. CompGeom,
+ * crates/backend/src/abi.rs:24-45). */
+typedef struct DsaGeom {
+    int32_t n_heads;            /* attention query heads (64) */
+    int32_t kv_lora;            /* latent width (512); multiple of 128, <= 512 */
+    int32_t rope_dim;           /* roped key width (64); multiple of 16 */
+    int32_t index_heads;        /* lightning-indexer heads (32) */
+    int32_t index_dim;          /* indexer head dim (128); multiple of 16, <= 512 */
+    int32_t page_tokens;        /* tokens per page (64); power of two */
+    int32_t top_k;              /* rows attended per sequence (2048) */
+    int32_t max_pages_per_seq;  /* block_table row pitch */
+    int32_t n_pool_pages;       /* pages in the pool (bounds check of block_table entries) */
+    float softmax_scale;        /* multiplies q.k before softmax */
+    float index_wscale;         /* index_heads^-0.5 */
+    float index_dscale;         /* index_dim^-0.5 */
+} DsaGeom;
+
+/* Batched form of rivoli_append_kv + rivoli_index_append (fwd.hip:51-71, indexer.hip:54-58)
+ * on the paged fp8 pool. Row i (of n_rows) belongs to sequence row_seq[i] (NULL = i) and
+ * is written at token position row_pos[i]. latent bf16 [n_rows][kv_lora+rope_dim],
+ * index_key bf16 [n_rows][index_dim]. Three per-token absmax scales (c_kv, k_rope, key).
+ * Guards: 1001 n_rows<=0 / NULL; 1004/1005 geometry. A block_table entry outside the pool
+ * makes the kernel skip that row and raise bit 0 of *status (device i32, may be NULL). */
+int rivoli_kv_append_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,
+                           const int32_t* row_seq, const int32_t* row_pos, int n_rows,
+                           const int32_t* block_table, uint8_t* latent_pool, float* latent_scale,
+                           uint8_t* index_pool, float* index_scale, int32_t* status, void* stream);
+
+/* Indexer query -> e4m3 codes + one absmax scale per (sequence, head) vector.
+ * q bf16 [n_vec][hd]. No reference counterpart (the reference scores f32 q against bf16
+ * keys); same codec and scale rule as append. */
+int rivoli_index_q_quant(const uint16_t* q, int n_vec, int hd, uint8_t* codes, float* scales,
+                         void* stream);
+
+/* Batched, paged form of rivoli_index_score (indexer.hip:60-93): for t < seq_len[b]
+ *   cd = left fold over d of qcode[b][h][d]*kcode[t][d];  dot = (cd*s_q[b][h])*s_k[t]
+ *   scores[b][t] = fold over h ascending of acc + (w[b][h]*wscale)*max(dot*dscale, 0)
+ * in IEEE f32 with that exact order, so it is bit-reproducible. scores f32 [B][score_stride]. */
+int rivoli_index_score_paged(const DsaGeom* g, const uint8_t* qcodes, const float* qscales,
+                             const float* w, const uint8_t* index_pool, const float* index_scale,
+                             const int32_t* block_table, const int32_t* seq_len, int B, float* scores,
+                             int score_stride, void* stream);
+
+/* Batched form of rivoli_index_topk (indexer.hip:146-257): rows u32 [B][k], the first
+ * n_sel[b] = min(k, seq_len[b]) entries ascending; later entries untouched. */
+int rivoli_index_topk_batched(const float* scores, int score_stride, const int32_t* seq_len, int B,
+                              int k, uint32_t* rows, int32_t* n_sel, void* stream);
+
+/* Bytes of scratch rivoli_mla_attend_paged_bf16 needs for B sequences (split partials). */
+size_t rivoli_mla_attend_paged_scratch_bytes(const DsaGeom* g, int B);
+
+/* Batched, paged form of rivoli_mla_attend (attn.hip:119-232 + combine :241-273).
+ * q bf16 [B][n_heads][kv_lora+rope_dim] (absorbed q then roped q); rows u32 [B][row_stride]
+ * or NULL (dense: row j = token j); n_rows i32 [B]. out bf16 [B][n_heads][kv_lora].
+ * out_m / out_lse f32 [B][n_heads] (may be NULL): max score and log-sum-exp, the partial a
+ * page-range shard hands to rivoli_attend_merge_partials. scratch = the bytes above. */
+int rivoli_mla_attend_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
+                                 const float* latent_scale, const int32_t* block_table,
+                                 const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
+                                 uint16_t* out, float* out_m, float* out_lse, void* scratch,
+                                 void* stream);
+
+/* Merge G shards' normalised partials (attn.hip:241-273 with (m_s, l_s) = (lse_g, 1)):
+ * weight_g = exp(lse_g - max lse), ascending g. part_out bf16 [G][n_vec][kvl],
+ * part_lse f32 [G][n_vec], out bf16 [n_vec][kvl]. */
+int rivoli_attend_merge_partials(const uint16_t* part_out, const float* part_lse, int G, int n_vec,
+                                 int kvl, uint16_t* out, void* stream);
+
+/* CUDA-core (f32 accumulate) implementation of rivoli_mla_attend_paged_bf16, same contract.
+ * No reference counterpart beyond attn.hip:119-232 itself: it is the cross-check of the
+ * tensor-core kernel and serves geometries that kernel does not cover. */
+size_t rivoli_attend_simt_scratch_bytes(const DsaGeom* g, int B);
+int rivoli_attend_simt_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
+                                  const float* latent_scale, const int32_t* block_table,
+                                  const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
+                                  uint16_t* out, float* out_m, float* out_lse, void* scratch,
+                                  void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Part 3 - host-side page allocator (no device work)
+ *
+ * The reference keeps contiguous KV slabs (crates/engine/src/glm/engine.rs:77-83) and has
+ * no pager; the nearest idiom is its expert arena's LIFO free list
+ * (crates/core/src/arena.rs:131-149). alloc pops the tail of the free list, release pushes
+ * a sequence's pages logical page 0 first, so page tables are a pure function of the call
+ * history. reserve: 0 ok, 1001 bad sequence, 1002 block-table row full, 1007 pool exhausted.
+ * ------------------------------------------------------------------------------------- */
+void* rivoli_pagepool_create(int n_pages, int n_seqs, int max_pages_per_seq, int page_tokens);
+void rivoli_pagepool_destroy(void* pool);
+void rivoli_pagepool_shuffle(void* pool, uint64_t seed);
+int rivoli_pagepool_reserve(void* pool, int seq, int n_tokens);
+int rivoli_pagepool_release(void* pool, int seq);
+int rivoli_pagepool_n_free(const void* pool);
+int rivoli_pagepool_seq_pages(const void* pool, int seq);
+const int32_t* rivoli_pagepool_block_table(const void* pool);   /* [n_seqs][max_pages_per_seq], -1 unmapped */
+const int32_t* rivoli_pagepool_free_list(const void* pool);     /* [n_free] */
+
+/* Library build tag, e.g. "sm_100a". */
+const char* rivoli_kernels_arch(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RIVOLI_KERNELS_H */

@@ -121,13 +121,14 @@ ORC_API void orc_lcg_fill(uint64_t* state, float* out, size_t n) {
 
 /* Block absmax -> scale -> e4m3 codes; roped key -> bf16; row `pos` of three slabs.
  * Host statement: crates/engine/tests/fwd_kernel.rs:159-175; kernel
- * crates/backend/kernels/fwd.hip:51-71. Block size = kvl / n_blocks (the reference
- * fixes it at 128, crates/core/src/num.rs:186). */
+ * crates/backend/kernels/fwd.hip:51-71. The block is always 128 wide
+ * (crates/core/src/num.rs:186); n_blocks is only the row pitch of the scale slab. */
 ORC_API int orc_append_kv(const float* latent, const float* rope, uint8_t* lc8, float* lscale,
                           uint16_t* rc, int pos, int kvl, int ropn, int n_blocks) {
-    if (pos < 0 || kvl <= 0 || ropn <= 0 || n_blocks <= 0 || kvl % n_blocks) return 1001;
-    int blk = kvl / n_blocks;
-    for (int b = 0; b < n_blocks; ++b) {
+    if (pos < 0 || kvl <= 0 || ropn <= 0 || n_blocks <= 0) return 1001;
+    if (kvl > 1024 || kvl < 128 || (kvl % 128) != 0 || ropn > kvl) return 1002;  /* fwd.hip:227-229 */
+    const int blk = 128;                               /* E4M3_BLOCK; n_blocks is the scale row pitch */
+    for (int b = 0; b < kvl / blk; ++b) {
         float amax = 0.0f;
         for (int i = 0; i < blk; ++i) amax = fmaxf(amax, fabsf(latent[b * blk + i]));
         float scl = amax > 0.0f ? amax / 448.0f : 1.0f;
@@ -308,7 +309,7 @@ ORC_API void orc_mla_attend_partial(const float* qabs, const float* qrope, const
                                     const float* lscale, const uint16_t* rc, int H, int r0, int r1,
                                     int kvl, int rope, int n_blocks, float scale, float* acc,
                                     float* ml) {
-    int blk = kvl / n_blocks;
+    const int blk = 128;
     for (int head = 0; head < H; ++head) {
         const float* qa = qabs + (size_t)head * kvl;
         const float* qr = qrope + (size_t)head * rope;

@@ -1,0 +1,266 @@
+"""Host-side mirror of the reference's ``crates/backend`` operator surface for the decode
+KV-cache path, bound to ``librivolikernels.so`` through its C ABI.
+
+Names, argument order and error behaviour follow the reference's Rust launchers
+(``launch_append_kv``, ``launch_index_append``, ``launch_index_score``,
+``launch_index_topk``, ``launch_attend``, ``launch_gather_rope``, ``device_sync``,
+``attend_scratch_floats``: crates/backend/src/hip_attn.rs:101-147,443-495 and
+crates/backend/src/hip.rs:328-336,425-430): every launcher returns ``None`` on success and
+raises :class:`BackendError` whose text is ``"<name>: argument guard rejected (<code>)"``
+for a positive return and ``"<name>: CUDA error <n>"`` for a negative one, so a test can
+assert the guard code exactly as the reference's ``assert_guard`` does.
+
+Pointer arguments accept a ``torch.Tensor`` (its ``data_ptr()`` is passed), an ``int``
+device address, or ``None`` for NULL. There is NO fallback: if the CUDA library is not
+built, importing a launcher fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "librivolikernels.so")
+
+
+class BackendError(RuntimeError):
+    """A launcher refused its arguments (``code`` > 0) or the launch failed (``code`` < 0)."""
+
+    def __init__(self, name: str, code: int):
+        self.name, self.code = name, code
+        if code > 0:
+            msg = f"{name}: argument guard rejected ({code})"
+        else:
+            msg = f"{name}: CUDA error {-code}"
+        super().__init__(msg)
+
+
+class DsaGeom(C.Structure):
+    """``DsaGeom`` of include/rivoli_kernels.h (48 bytes, align 4)."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "n_heads", "kv_lora", "rope_dim", "index_heads", "index_dim", "page_tokens", "top_k",
+        "max_pages_per_seq", "n_pool_pages")] + [(n, C.c_float) for n in (
+        "softmax_scale", "index_wscale", "index_dscale")]
+
+    @classmethod
+    def make(cls, *, n_heads=64, kv_lora=512, rope_dim=64, index_heads=32, index_dim=128,
+             page_tokens=64, top_k=2048, max_pages_per_seq, n_pool_pages, softmax_scale=None,
+             index_wscale=None, index_dscale=None) -> "DsaGeom":
+        import numpy as np
+        f32 = np.float32
+        return cls(n_heads, kv_lora, rope_dim, index_heads, index_dim, page_tokens, top_k,
+                   max_pages_per_seq, n_pool_pages,
+                   float(f32(1.0) / np.sqrt(f32(kv_lora + rope_dim))) if softmax_scale is None else softmax_scale,
+                   float(f32(index_heads) ** f32(-0.5)) if index_wscale is None else index_wscale,
+                   float(f32(index_dim) ** f32(-0.5)) if index_dscale is None else index_dscale)
+
+
+assert C.sizeof(DsaGeom) == 48 and C.alignment(DsaGeom) == 4
+
+_lib = None
+
+
+def library_path() -> str:
+    return _SO
+
+
+def lib() -> C.CDLL:
+    """The loaded CUDA library. Raises if it has not been built: there is no CPU path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            raise RuntimeError(
+                f"{_SO} is missing: build it with `python -m rivoli_b200.build` "
+                "(nvcc, sm_100a). rivoli_b200 has no CPU fallback.")
+        L = C.CDLL(_SO)
+        L.rivoli_mla_attend_scratch_floats.restype = C.c_size_t
+        L.rivoli_mla_attend_paged_scratch_bytes.restype = C.c_size_t
+        L.rivoli_attend_simt_scratch_bytes.restype = C.c_size_t
+        L.rivoli_kernels_arch.restype = C.c_char_p
+        L.rivoli_pagepool_create.restype = C.c_void_p
+        L.rivoli_pagepool_block_table.restype = C.POINTER(C.c_int32)
+        L.rivoli_pagepool_free_list.restype = C.POINTER(C.c_int32)
+        for n in ("destroy", "shuffle", "reserve", "release", "n_free", "seq_pages", "block_table", "free_list"):
+            getattr(L, f"rivoli_pagepool_{n}").argtypes = None
+        _lib = L
+    return _lib
+
+
+def _ptr(x):
+    if x is None:
+        return C.c_void_p(0)
+    if isinstance(x, int):
+        return C.c_void_p(x)
+    return C.c_void_p(x.data_ptr())
+
+
+def _stream(s):
+    if s is None:
+        return C.c_void_p(0)
+    if isinstance(s, int):
+        return C.c_void_p(s)
+    return C.c_void_p(s.cuda_stream)
+
+
+def ensure_status(r: int, name: str) -> None:
+    """0 = ok, positive = argument guard, negative = -(cudaError_t) (hip.rs:328-336)."""
+    if r != 0:
+        raise BackendError(name, int(r))
+
+
+# --- Part 1: the reference's launchers ------------------------------------------------------------
+def launch_append_kv(latent, rope, lc8, lscale, rc, pos: int, kvl: int, ropn: int, n_blocks: int) -> None:
+    ensure_status(lib().rivoli_append_kv(_ptr(latent), _ptr(rope), _ptr(lc8), _ptr(lscale), _ptr(rc),
+                                         C.c_int(pos), C.c_int(kvl), C.c_int(ropn), C.c_int(n_blocks)),
+                  "append_kv")
+
+
+def launch_gather_rope(q, qrope, h: int, qh: int, nope: int, ropn: int) -> None:
+    ensure_status(lib().rivoli_gather_rope(_ptr(q), _ptr(qrope), C.c_int(h), C.c_int(qh), C.c_int(nope),
+                                           C.c_int(ropn)), "gather_rope")
+
+
+def launch_index_append(k, kcache, pos: int, hd: int) -> None:
+    ensure_status(lib().rivoli_index_append(_ptr(k), _ptr(kcache), C.c_int(pos), C.c_int(hd)), "index_append")
+
+
+def launch_index_score(q, w, kcache, heads, nt: int, nh: int, nact: int, hd: int, wscale: float,
+                       dscale: float, scores) -> None:
+    ensure_status(lib().rivoli_index_score(_ptr(q), _ptr(w), _ptr(kcache), _ptr(heads), C.c_int(nt),
+                                           C.c_int(nh), C.c_int(nact), C.c_int(hd), C.c_float(wscale),
+                                           C.c_float(dscale), _ptr(scores)), "index_score")
+
+
+def launch_index_topk(scores, nt: int, k: int, rows) -> None:
+    ensure_status(lib().rivoli_index_topk(_ptr(scores), C.c_int(nt), C.c_int(k), _ptr(rows)), "index_topk")
+
+
+def launch_attend(qabs, qrope, lc8, lscale, rc, rows, h: int, nr: int, kvl: int, rope: int, n_blocks: int,
+                  scale: float, clat, partial) -> None:
+    ensure_status(lib().rivoli_mla_attend(_ptr(qabs), _ptr(qrope), _ptr(lc8), _ptr(lscale), _ptr(rc),
+                                          _ptr(rows), C.c_int(h), C.c_int(nr), C.c_int(kvl), C.c_int(rope),
+                                          C.c_int(n_blocks), C.c_float(scale), _ptr(clat), _ptr(partial)),
+                  "mla_attend")
+
+
+def attend_scratch_floats(h: int, kvl: int) -> int:
+    return int(lib().rivoli_mla_attend_scratch_floats(C.c_int(h), C.c_int(kvl)))
+
+
+def device_sync() -> None:
+    ensure_status(lib().rivoli_device_sync(), "device_sync")
+
+
+# --- Part 2: batched / paged / bf16 -----------------------------------------------------------------
+def launch_kv_append_paged(g: DsaGeom, latent, index_key, row_seq, row_pos, n_rows: int, block_table,
+                           latent_pool, latent_scale, index_pool, index_scale, status=None, stream=None) -> None:
+    ensure_status(lib().rivoli_kv_append_paged(C.byref(g), _ptr(latent), _ptr(index_key), _ptr(row_seq),
+                                               _ptr(row_pos), C.c_int(n_rows), _ptr(block_table),
+                                               _ptr(latent_pool), _ptr(latent_scale), _ptr(index_pool),
+                                               _ptr(index_scale), _ptr(status), _stream(stream)),
+                  "kv_append_paged")
+
+
+def launch_index_q_quant(q, n_vec: int, hd: int, codes, scales, stream=None) -> None:
+    ensure_status(lib().rivoli_index_q_quant(_ptr(q), C.c_int(n_vec), C.c_int(hd), _ptr(codes), _ptr(scales),
+                                             _stream(stream)), "index_q_quant")
+
+
+def launch_index_score_paged(g: DsaGeom, qcodes, qscales, w, index_pool, index_scale, block_table, seq_len,
+                             B: int, scores, score_stride: int, stream=None) -> None:
+    ensure_status(lib().rivoli_index_score_paged(C.byref(g), _ptr(qcodes), _ptr(qscales), _ptr(w),
+                                                 _ptr(index_pool), _ptr(index_scale), _ptr(block_table),
+                                                 _ptr(seq_len), C.c_int(B), _ptr(scores),
+                                                 C.c_int(score_stride), _stream(stream)), "index_score_paged")
+
+
+def launch_index_topk_batched(scores, score_stride: int, seq_len, B: int, k: int, rows, n_sel,
+                              stream=None) -> None:
+    ensure_status(lib().rivoli_index_topk_batched(_ptr(scores), C.c_int(score_stride), _ptr(seq_len),
+                                                  C.c_int(B), C.c_int(k), _ptr(rows), _ptr(n_sel),
+                                                  _stream(stream)), "index_topk_batched")
+
+
+def attend_paged_scratch_bytes(g: DsaGeom, B: int) -> int:
+    return int(lib().rivoli_mla_attend_paged_scratch_bytes(C.byref(g), C.c_int(B)))
+
+
+def attend_simt_scratch_bytes(g: DsaGeom, B: int) -> int:
+    return int(lib().rivoli_attend_simt_scratch_bytes(C.byref(g), C.c_int(B)))
+
+
+def _attend_paged(fn, name, g, q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows, B, out,
+                  out_m, out_lse, scratch, stream):
+    ensure_status(fn(C.byref(g), _ptr(q), _ptr(latent_pool), _ptr(latent_scale), _ptr(block_table),
+                     _ptr(rows), C.c_int(row_stride), _ptr(n_rows), C.c_int(B), _ptr(out), _ptr(out_m),
+                     _ptr(out_lse), _ptr(scratch), _stream(stream)), name)
+
+
+def launch_attend_paged_bf16(g: DsaGeom, q, latent_pool, latent_scale, block_table, rows, row_stride: int,
+                             n_rows, B: int, out, out_m=None, out_lse=None, scratch=None, stream=None) -> None:
+    _attend_paged(lib().rivoli_mla_attend_paged_bf16, "mla_attend_paged_bf16", g, q, latent_pool,
+                  latent_scale, block_table, rows, row_stride, n_rows, B, out, out_m, out_lse, scratch, stream)
+
+
+def launch_attend_simt_paged_bf16(g: DsaGeom, q, latent_pool, latent_scale, block_table, rows,
+                                  row_stride: int, n_rows, B: int, out, out_m=None, out_lse=None,
+                                  scratch=None, stream=None) -> None:
+    _attend_paged(lib().rivoli_attend_simt_paged_bf16, "attend_simt_paged_bf16", g, q, latent_pool,
+                  latent_scale, block_table, rows, row_stride, n_rows, B, out, out_m, out_lse, scratch, stream)
+
+
+def launch_attend_merge_partials(part_out, part_lse, G: int, n_vec: int, kvl: int, out, stream=None) -> None:
+    ensure_status(lib().rivoli_attend_merge_partials(_ptr(part_out), _ptr(part_lse), C.c_int(G),
+                                                     C.c_int(n_vec), C.c_int(kvl), _ptr(out),
+                                                     _stream(stream)), "attend_merge_partials")
+
+
+# --- Part 3: host page allocator ----------------------------------------------------------------------
+class PagePool:
+    """LIFO page allocator + per-sequence block tables (host memory; C++ ``rivoli::PagePool``)."""
+
+    def __init__(self, n_pages: int, n_seqs: int, max_pages_per_seq: int, page_tokens: int):
+        self._h = C.c_void_p(lib().rivoli_pagepool_create(C.c_int(n_pages), C.c_int(n_seqs),
+                                                          C.c_int(max_pages_per_seq), C.c_int(page_tokens)))
+        if not self._h:
+            raise BackendError("pagepool_create", 1001)
+        self.n_pages, self.n_seqs = n_pages, n_seqs
+        self.max_pages_per_seq, self.page_tokens = max_pages_per_seq, page_tokens
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().rivoli_pagepool_destroy(self._h)
+            self._h = None
+
+    def shuffle(self, seed: int) -> None:
+        lib().rivoli_pagepool_shuffle(self._h, C.c_uint64(seed))
+
+    def reserve(self, seq: int, n_tokens: int) -> None:
+        ensure_status(lib().rivoli_pagepool_reserve(self._h, C.c_int(seq), C.c_int(n_tokens)), "pagepool_reserve")
+
+    def release(self, seq: int) -> None:
+        ensure_status(lib().rivoli_pagepool_release(self._h, C.c_int(seq)), "pagepool_release")
+
+    @property
+    def n_free(self) -> int:
+        return int(lib().rivoli_pagepool_n_free(self._h))
+
+    def seq_pages(self, seq: int) -> int:
+        return int(lib().rivoli_pagepool_seq_pages(self._h, C.c_int(seq)))
+
+    def block_table(self):
+        import numpy as np
+        p = lib().rivoli_pagepool_block_table(self._h)
+        return np.ctypeslib.as_array(p, shape=(self.n_seqs, self.max_pages_per_seq)).copy()
+
+    def free_list(self):
+        import numpy as np
+        n = self.n_free
+        if n == 0:
+            return np.zeros(0, dtype=np.int32)
+        p = lib().rivoli_pagepool_free_list(self._h)
+        return np.ctypeslib.as_array(p, shape=(n,)).copy()
+
+
+def kernels_arch() -> str:
+    return lib().rivoli_kernels_arch().decode()

@@ -1,0 +1,46 @@
+// Shared host/device helpers for librivolikernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/rivoli_kernels.h"
+
+#define RIVOLI_API extern "C" __attribute__((visibility("default")))
+
+// Launch epilogue of every entry point: 0 or -(cudaError_t), after draining any stale
+// error before the launch so the code read back belongs to this launch.
+static inline void rv_drain_error() { (void)cudaGetLastError(); }
+static inline int rv_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : -(int)e;
+}
+
+static inline bool rv_is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+
+// Geometry guard shared by every paged entry point. Decided on the host; nothing is
+// dereferenced on the device when it fails.
+static inline int rv_check_geom(const DsaGeom* g) {
+    if (!g) return 1001;
+    if (g->n_heads <= 0 || g->kv_lora <= 0 || g->rope_dim <= 0 || g->index_heads <= 0 ||
+        g->index_dim <= 0 || g->page_tokens <= 0 || g->top_k <= 0 || g->max_pages_per_seq <= 0 ||
+        g->n_pool_pages <= 0)
+        return 1001;
+    if (g->kv_lora > 512 || (g->kv_lora % 128) != 0) return 1004;
+    if ((g->rope_dim % 16) != 0 || g->rope_dim > 128) return 1004;
+    if ((g->index_dim % 16) != 0 || g->index_dim > 512) return 1004;
+    if (!rv_is_pow2(g->page_tokens)) return 1003;
+    if (g->n_heads > 128 || g->index_heads > 64) return 1002;
+    return 0;
+}
+
+__device__ __forceinline__ float rv_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float rv_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}

@@ -1,0 +1,118 @@
+"""One MLA + DSA decode layer's KV-cache path on one GPU: the caller side of the operator
+surface, i.e. what ``crates/engine/src/glm/attn.rs:119-222`` does for this path (append the
+new token, select rows with the lightning indexer, attend), batched over sequences and
+paged.
+
+The layer owns the device pools and the per-step scratch; every buffer is allocated once
+in ``__init__`` (the reference allocates all KV slabs and scratch once in
+``GlmEngine::new``, crates/engine/src/glm/engine.rs:139-260) and a step allocates nothing.
+torch is used for device memory and streams only; all arithmetic is in the CUDA library.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import backend as be
+
+
+class DsaDecodeLayer:
+    """Device state of one layer for a batch of ``n_seqs`` sequences.
+
+    Call order per layer-step (the operator order the reference documents for a full
+    indexer layer, docs/investigations/rewrite.md:135-137): ``append`` -> ``select`` ->
+    ``attend``; ``step`` does the three in order on the current stream.
+    """
+
+    def __init__(self, geom: be.DsaGeom, n_seqs: int, device="cuda:0", max_ctx: int | None = None,
+                 shuffle_seed: int | None = None):
+        be.lib()  # fail loudly if the CUDA library is missing
+        self.g = geom
+        self.B = n_seqs
+        self.dev = torch.device(device)
+        P = geom.page_tokens
+        self.max_ctx = max_ctx if max_ctx is not None else geom.max_pages_per_seq * P
+        rows = geom.n_pool_pages * P
+        W = geom.kv_lora + geom.rope_dim
+        u8, f32, i32 = torch.uint8, torch.float32, torch.int32
+        d = self.dev
+        self.latent_pool = torch.zeros(rows * W, dtype=u8, device=d)
+        self.latent_scale = torch.zeros(rows * 2, dtype=f32, device=d)
+        self.index_pool = torch.zeros(rows * geom.index_dim, dtype=u8, device=d)
+        self.index_scale = torch.zeros(rows, dtype=f32, device=d)
+        self.block_table = torch.full((n_seqs, geom.max_pages_per_seq), -1, dtype=i32, device=d)
+        self.pool = be.PagePool(geom.n_pool_pages, n_seqs, geom.max_pages_per_seq, P)
+        if shuffle_seed is not None:
+            self.pool.shuffle(shuffle_seed)
+        # per-step scratch
+        self.score_stride = self.max_ctx
+        self.scores = torch.zeros((n_seqs, self.score_stride), dtype=f32, device=d)
+        self.qcodes = torch.zeros(n_seqs * geom.index_heads * geom.index_dim, dtype=u8, device=d)
+        self.qscales = torch.zeros(n_seqs * geom.index_heads, dtype=f32, device=d)
+        self.rows = torch.zeros((n_seqs, geom.top_k), dtype=torch.int32, device=d)  # u32 payload
+        self.n_sel = torch.zeros(n_seqs, dtype=i32, device=d)
+        self.status = torch.zeros(1, dtype=i32, device=d)
+        self.out = torch.zeros((n_seqs, geom.n_heads, geom.kv_lora), dtype=torch.bfloat16, device=d)
+        self.out_m = torch.zeros((n_seqs, geom.n_heads), dtype=f32, device=d)
+        self.out_lse = torch.zeros((n_seqs, geom.n_heads), dtype=f32, device=d)
+        nbytes = max(be.attend_paged_scratch_bytes(geom, n_seqs), 16)
+        self.scratch = torch.zeros(nbytes, dtype=u8, device=d)
+
+    # --- paging -------------------------------------------------------------------------------------
+    def reserve(self, seq: int, n_tokens: int) -> None:
+        self.pool.reserve(seq, n_tokens)
+
+    def release(self, seq: int) -> None:
+        self.pool.release(seq)
+
+    def upload_block_table(self) -> None:
+        bt = torch.from_numpy(self.pool.block_table())
+        self.block_table.copy_(bt, non_blocking=False)
+
+    # --- operators ----------------------------------------------------------------------------------
+    def append(self, latent: torch.Tensor, index_key: torch.Tensor, row_pos: torch.Tensor,
+               row_seq: torch.Tensor | None = None, stream=None) -> None:
+        """Quantise and store ``n`` new tokens (bf16 ``[n, kv_lora+rope]`` and ``[n, index_dim]``)."""
+        n = latent.shape[0]
+        be.launch_kv_append_paged(self.g, latent, index_key, row_seq, row_pos, n, self.block_table,
+                                  self.latent_pool, self.latent_scale, self.index_pool, self.index_scale,
+                                  self.status, stream)
+
+    def select(self, index_q: torch.Tensor, index_w: torch.Tensor, seq_len: torch.Tensor, stream=None) -> None:
+        """Indexer: quantise q, score every cached key, exact top-k -> ``rows``/``n_sel``."""
+        g = self.g
+        be.launch_index_q_quant(index_q, self.B * g.index_heads, g.index_dim, self.qcodes, self.qscales, stream)
+        be.launch_index_score_paged(g, self.qcodes, self.qscales, index_w, self.index_pool, self.index_scale,
+                                    self.block_table, seq_len, self.B, self.scores, self.score_stride, stream)
+        be.launch_index_topk_batched(self.scores, self.score_stride, seq_len, self.B, g.top_k, self.rows,
+                                     self.n_sel, stream)
+
+    def attend(self, q: torch.Tensor, stream=None, dense_len: torch.Tensor | None = None) -> torch.Tensor:
+        """Attention over the selected rows (or, with ``dense_len``, over the whole prefix)."""
+        if dense_len is not None:
+            be.launch_attend_paged_bf16(self.g, q, self.latent_pool, self.latent_scale, self.block_table,
+                                        None, 0, dense_len, self.B, self.out, self.out_m, self.out_lse,
+                                        self.scratch, stream)
+        else:
+            be.launch_attend_paged_bf16(self.g, q, self.latent_pool, self.latent_scale, self.block_table,
+                                        self.rows, self.g.top_k, self.n_sel, self.B, self.out, self.out_m,
+                                        self.out_lse, self.scratch, stream)
+        return self.out
+
+    def step(self, latent, index_key, index_q, index_w, q, row_pos, seq_len, stream=None) -> torch.Tensor:
+        """One layer-step: append one token per sequence, select, attend."""
+        self.append(latent, index_key, row_pos, None, stream)
+        self.select(index_q, index_w, seq_len, stream)
+        return self.attend(q, stream)
+
+    def check_status(self) -> None:
+        """Raise if a kernel flagged a bad block-table entry since the last check (syncs)."""
+        s = int(self.status.item())
+        if s:
+            self.status.zero_()
+            raise be.BackendError("kv_append_paged(status)", 1005)
+
+
+def bf16_bits(t: torch.Tensor) -> np.ndarray:
+    """bf16 tensor -> numpy uint16 bit patterns (host)."""
+    return t.detach().cpu().view(torch.int16).numpy().view(np.uint16)

@@ -1,0 +1,181 @@
+"""The batched / paged / bf16 operators against the oracle on seeded decode states."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests.helpers import State, attend_close, make_geom
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def be():
+    from rivoli_b200 import backend
+    backend.lib()
+    return backend
+
+
+def dev(a):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.uint16:
+        a = a.view(np.int16)
+    if a.dtype == np.uint32:
+        a = a.view(np.int32)
+    return torch.from_numpy(a).cuda()
+
+
+def u16(t):
+    return t.cpu().view(torch.int16).numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy().view(np.uint16)
+
+
+CASES = {
+    # BASELINE config 1: 1 sequence, 256 cached + 1 appended, H=16, indexer 8x64, k=64, 16-token pages
+    "cfg1": dict(seed=0, B=1, ctx=[257], n_heads=16, index_heads=8, index_dim=64, page_tokens=16, top_k=64,
+                 pool_factor=1.0),
+    # ragged batch, model dims, top-k smaller / larger than the contexts
+    "ragged": dict(seed=11, B=5, ctx=[1, 63, 64, 65, 700], top_k=256),
+    "dense-equivalent": dict(seed=12, B=3, ctx=[300, 257, 512], top_k=2048),
+}
+
+
+def build(be, case):
+    c = dict(CASES[case])
+    st = State(c.pop("seed"), c.pop("B"), c.pop("ctx"), **c)
+    g = make_geom(be.DsaGeom, **st.geom_kw)
+    d = dict(latent_pool=dev(st.latent_pool), latent_scale=dev(st.latent_scale), index_pool=dev(st.index_pool),
+             index_scale=dev(st.index_scale), block_table=dev(st.block_table), seq_len=dev(st.seq_len),
+             row_pos=dev(st.row_pos))
+    return st, g, d
+
+
+@pytest.mark.parametrize("case", list(CASES))
+def test_layer_step_matches_oracle(be, case):
+    st, g, d = build(be, case)
+    want = st.oracle_step()
+    B = st.B
+    # 1. append: bit-exact codes and scales, and nothing else in the pool moves
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    be.launch_kv_append_paged(g, dev(st.new_latent), dev(st.new_key), None, d["row_pos"], B, d["block_table"],
+                              d["latent_pool"], d["latent_scale"], d["index_pool"], d["index_scale"], status)
+    be.device_sync()
+    assert int(status.item()) == 0
+    np.testing.assert_array_equal(d["latent_pool"].cpu().numpy(), want["latent_pool"])
+    np.testing.assert_array_equal(d["latent_scale"].cpu().numpy().view(np.uint32), want["latent_scale"].view(np.uint32))
+    np.testing.assert_array_equal(d["index_pool"].cpu().numpy(), want["index_pool"])
+    np.testing.assert_array_equal(d["index_scale"].cpu().numpy().view(np.uint32), want["index_scale"].view(np.uint32))
+    # 2. q quantisation: bit-exact
+    qc = torch.zeros(st.index_q.size, dtype=torch.uint8, device="cuda")
+    qs = torch.zeros(B * g.index_heads, dtype=torch.float32, device="cuda")
+    be.launch_index_q_quant(dev(st.index_q), B * g.index_heads, g.index_dim, qc, qs)
+    be.device_sync()
+    np.testing.assert_array_equal(qc.cpu().numpy(), want["qcodes"].ravel())
+    np.testing.assert_array_equal(qs.cpu().numpy().view(np.uint32), want["qscales"].view(np.uint32))
+    # 3. scores: BIT-exact (fixed fold order), only t < seq_len is defined
+    stride = int(st.seq_len.max())
+    sc = torch.full((B, stride), float("nan"), dtype=torch.float32, device="cuda")
+    be.launch_index_score_paged(g, qc, qs, dev(st.index_w), d["index_pool"], d["index_scale"], d["block_table"],
+                                d["seq_len"], B, sc, stride)
+    be.device_sync()
+    got = sc.cpu().numpy()
+    for b in range(B):
+        n = st.seq_len[b]
+        np.testing.assert_array_equal(got[b, :n].view(np.uint32), want["scores"][b, :n].view(np.uint32))
+        assert np.isnan(got[b, n:]).all()
+    # 4. top-k: bit-exact indices, sentinel tail
+    rows = torch.full((B, g.top_k), -1, dtype=torch.int32, device="cuda")
+    n_sel = torch.zeros(B, dtype=torch.int32, device="cuda")
+    be.launch_index_topk_batched(sc, stride, d["seq_len"], B, g.top_k, rows, n_sel)
+    be.device_sync()
+    np.testing.assert_array_equal(n_sel.cpu().numpy(), want["n_sel"])
+    np.testing.assert_array_equal(rows.cpu().numpy().view(np.uint32), want["rows"])
+    # 5. attention (both implementations) within 2e-2 rel / 1e-3 abs of the oracle's f32 result
+    for fn, nbytes in ((be.launch_attend_paged_bf16, be.attend_paged_scratch_bytes(g, B)),
+                       (be.launch_attend_simt_paged_bf16, be.attend_simt_scratch_bytes(g, B))):
+        out = torch.zeros((B, g.n_heads, g.kv_lora), dtype=torch.bfloat16, device="cuda")
+        m = torch.zeros((B, g.n_heads), dtype=torch.float32, device="cuda")
+        lse = torch.zeros((B, g.n_heads), dtype=torch.float32, device="cuda")
+        scratch = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+        fn(g, dev(st.q), d["latent_pool"], d["latent_scale"], d["block_table"], rows, g.top_k, n_sel, B, out, m,
+           lse, scratch)
+        be.device_sync()
+        ok, worst = attend_close(u16(out), want["out_f32"])
+        assert ok, worst
+        assert np.abs(lse.cpu().numpy() - want["lse"]).max() < 2e-2
+        # no-scratch (single split) path
+        out2 = torch.zeros_like(out)
+        fn(g, dev(st.q), d["latent_pool"], d["latent_scale"], d["block_table"], rows, g.top_k, n_sel, B, out2,
+           None, None, None)
+        be.device_sync()
+        ok, worst = attend_close(u16(out2), want["out_f32"])
+        assert ok, worst
+
+
+def test_dense_attend_and_partial_merge(be):
+    """Page-range sharding: attend two halves of each context separately, merge (m, lse, out)."""
+    st, g, d = build(be, "ragged")
+    want = st.oracle_step()
+    B, H, kvl = st.B, g.n_heads, g.kv_lora
+    dlp, dls = dev(want["latent_pool"]), dev(want["latent_scale"])
+    # dense oracle over the whole prefix
+    o_dense, o_f32, _, lse_dense = orc.mla_attend_paged(st.og, st.q, want["latent_pool"], want["latent_scale"],
+                                                        st.block_table, None, st.seq_len, want_f32=True)
+    out = torch.zeros((B, H, kvl), dtype=torch.bfloat16, device="cuda")
+    lse = torch.zeros((B, H), dtype=torch.float32, device="cuda")
+    be.launch_attend_paged_bf16(g, dev(st.q), dlp, dls, d["block_table"], None, 0, d["seq_len"], B, out, None, lse,
+                                None)
+    be.device_sync()
+    ok, worst = attend_close(u16(out), o_f32)
+    assert ok, worst
+    # two shards by row range -> partials -> merge
+    parts, lses = [], []
+    stride = int(st.seq_len.max())
+    for lo_f, hi_f in ((0.0, 0.5), (0.5, 1.0)):
+        rows = np.zeros((B, stride), np.uint32); n = np.zeros(B, np.int32)
+        for b in range(B):
+            lo, hi = int(st.seq_len[b] * lo_f), int(st.seq_len[b] * hi_f)
+            n[b] = hi - lo; rows[b, :hi - lo] = np.arange(lo, hi)
+        po = torch.zeros((B, H, kvl), dtype=torch.bfloat16, device="cuda")
+        pl = torch.zeros((B, H), dtype=torch.float32, device="cuda")
+        be.launch_attend_paged_bf16(g, dev(st.q), dlp, dls, d["block_table"], dev(rows), stride, dev(n), B, po,
+                                    None, pl, None)
+        parts.append(po); lses.append(pl)
+    part_out = torch.stack(parts).contiguous(); part_lse = torch.stack(lses).contiguous()
+    merged = torch.zeros((B * H, kvl), dtype=torch.bfloat16, device="cuda")
+    be.launch_attend_merge_partials(part_out, part_lse, 2, B * H, kvl, merged)
+    be.device_sync()
+    # GPU merge == oracle merge of the same partials, bit for bit up to bf16 rounding of f32 sums
+    want_m = orc.attend_merge_partials(u16(part_out).reshape(2, B * H, kvl), part_lse.cpu().numpy(), kvl)
+    diff = np.abs(orc.bf16_to_f32(u16(merged)).reshape(-1) - orc.bf16_to_f32(want_m).reshape(-1))
+    assert diff.max() <= 1e-2 * np.abs(orc.bf16_to_f32(want_m)).max()
+    # and the merged result is the dense answer (an empty shard for the 1-token sequence included)
+    ok, worst = attend_close(u16(merged).reshape(B, H, kvl), o_f32, rel=3e-2, abs_=2e-3)
+    assert ok, worst
+
+
+def test_paged_guards(be):
+    g = make_geom(be.DsaGeom, max_pages_per_seq=4, n_pool_pages=8)
+    b = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    bad = make_geom(be.DsaGeom, kv_lora=640, max_pages_per_seq=4, n_pool_pages=8)
+    for fn, code in ((lambda: be.launch_kv_append_paged(bad, b, b, None, b, 1, b, b, b, b, b), 1004),
+                     (lambda: be.launch_kv_append_paged(g, b, b, None, b, 0, b, b, b, b, b), 1001),
+                     (lambda: be.launch_index_q_quant(b, 4, 100, b, b), 1004),
+                     (lambda: be.launch_index_topk_batched(b, 64, b, 0, 4, b, b), 1001),
+                     (lambda: be.launch_attend_merge_partials(b, b, 0, 4, 512, b), 1001)):
+        with pytest.raises(be.BackendError) as e:
+            fn()
+        assert e.value.code == code
+    be.device_sync()
+
+
+def test_append_flags_unmapped_page(be):
+    """A block-table entry outside the pool is skipped and reported, never written through."""
+    st, g, d = build(be, "cfg1")
+    bt = d["block_table"].clone(); bt[0, st.row_pos[0] // g.page_tokens] = g.n_pool_pages + 5
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    before = d["latent_pool"].clone()
+    be.launch_kv_append_paged(g, dev(st.new_latent), dev(st.new_key), None, d["row_pos"], 1, bt, d["latent_pool"],
+                              d["latent_scale"], d["index_pool"], d["index_scale"], status)
+    be.device_sync()
+    assert int(status.item()) == 1
+    assert torch.equal(before, d["latent_pool"])
