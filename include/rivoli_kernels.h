@@ -140,6 +140,30 @@ int rivoli_index_score_paged(const DsaGeom* g, const uint8_t* qcodes, const floa
 int rivoli_index_topk_batched(const float* scores, int score_stride, const int32_t* seq_len, int B,
                               int k, uint32_t* rows, int32_t* n_sel, void* stream);
 
+/* Fused indexer: q quantisation + scores + exact top-k in one call, on the tensor cores
+ * where the geometry allows (index_dim 128, index_heads <= 32, 16 <= page_tokens <= 128,
+ * score_stride <= 40960), otherwise through the three operators above. Replaces the chain
+ * launch_index_score -> launch_index_topk (crates/backend/src/hip_attn.rs:457-495) for a
+ * batch. The tensor-core scores are approximate; every token within a proven error band
+ * of the k-th score is re-scored in the exact order of rivoli_index_score_paged before the
+ * final cut, so rows/n_sel are IDENTICAL to rivoli_index_score_paged +
+ * rivoli_index_topk_batched. index_q bf16 [B][index_heads][index_dim], w f32
+ * [B][index_heads]; rows u32 [B][top_k]; scratch = rivoli_index_select_scratch_bytes(). */
+size_t rivoli_index_select_scratch_bytes(const DsaGeom* g, int B, int score_stride);
+int rivoli_index_select_uses_mma(const DsaGeom* g, int score_stride);
+int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index_q, const float* w,
+                              const uint8_t* index_pool, const float* index_scale,
+                              const int32_t* block_table, const int32_t* seq_len, int B,
+                              int score_stride, uint32_t* rows, int32_t* n_sel, void* scratch,
+                              void* stream);
+/* Synchronises `stream` and returns 1008 if a bounded device-side wait of the last
+ * rivoli_index_select_paged call gave up (results are then undefined), else 0. */
+int rivoli_index_select_status(const DsaGeom* g, int B, int score_stride, void* scratch, void* stream);
+/* Diagnostics: per-sequence count of tokens the last call re-scored exactly, to HOST memory
+ * host_band[B]. Synchronises `stream`. */
+int rivoli_index_select_band_stats(const DsaGeom* g, int B, int score_stride, void* scratch,
+                                   uint32_t* host_band, void* stream);
+
 /* Bytes of scratch rivoli_mla_attend_paged_bf16 needs for B sequences (split partials). */
 size_t rivoli_mla_attend_paged_scratch_bytes(const DsaGeom* g, int B);
 

@@ -76,6 +76,7 @@ def lib() -> C.CDLL:
         L.rivoli_mla_attend_scratch_floats.restype = C.c_size_t
         L.rivoli_mla_attend_paged_scratch_bytes.restype = C.c_size_t
         L.rivoli_attend_simt_scratch_bytes.restype = C.c_size_t
+        L.rivoli_index_select_scratch_bytes.restype = C.c_size_t
         L.rivoli_kernels_arch.restype = C.c_char_p
         L.rivoli_pagepool_create.restype = C.c_void_p
         L.rivoli_pagepool_block_table.restype = C.POINTER(C.c_int32)
@@ -179,6 +180,38 @@ def launch_index_topk_batched(scores, score_stride: int, seq_len, B: int, k: int
     ensure_status(lib().rivoli_index_topk_batched(_ptr(scores), C.c_int(score_stride), _ptr(seq_len),
                                                   C.c_int(B), C.c_int(k), _ptr(rows), _ptr(n_sel),
                                                   _stream(stream)), "index_topk_batched")
+
+
+def index_select_scratch_bytes(g: DsaGeom, B: int, score_stride: int) -> int:
+    return int(lib().rivoli_index_select_scratch_bytes(C.byref(g), C.c_int(B), C.c_int(score_stride)))
+
+
+def index_select_uses_mma(g: DsaGeom, score_stride: int) -> bool:
+    return bool(lib().rivoli_index_select_uses_mma(C.byref(g), C.c_int(score_stride)))
+
+
+def launch_index_select_paged(g: DsaGeom, index_q, w, index_pool, index_scale, block_table, seq_len, B: int,
+                              score_stride: int, rows, n_sel, scratch, stream=None) -> None:
+    """Fused indexer (q quant + scores + exact top-k); rows identical to the unfused chain."""
+    ensure_status(lib().rivoli_index_select_paged(C.byref(g), _ptr(index_q), _ptr(w), _ptr(index_pool),
+                                                  _ptr(index_scale), _ptr(block_table), _ptr(seq_len),
+                                                  C.c_int(B), C.c_int(score_stride), _ptr(rows), _ptr(n_sel),
+                                                  _ptr(scratch), _stream(stream)), "index_select_paged")
+
+
+def index_select_status(g: DsaGeom, B: int, score_stride: int, scratch, stream=None) -> None:
+    """Synchronises; raises BackendError(1008) if a bounded device-side wait gave up."""
+    ensure_status(lib().rivoli_index_select_status(C.byref(g), C.c_int(B), C.c_int(score_stride), _ptr(scratch),
+                                                   _stream(stream)), "index_select_status")
+
+
+def index_select_band_stats(g: DsaGeom, B: int, score_stride: int, scratch, stream=None):
+    import numpy as np
+    out = np.zeros(B, dtype=np.uint32)
+    ensure_status(lib().rivoli_index_select_band_stats(C.byref(g), C.c_int(B), C.c_int(score_stride),
+                                                       _ptr(scratch), out.ctypes.data_as(C.c_void_p),
+                                                       _stream(stream)), "index_select_band_stats")
+    return out
 
 
 def attend_paged_scratch_bytes(g: DsaGeom, B: int) -> int:

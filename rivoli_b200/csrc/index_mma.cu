@@ -1,0 +1,537 @@
+// Lightning-indexer selection on the tensor cores, with an exactness guarantee.
+//
+// The indexer reads 132 bytes per cached token and spends 8192 FLOP on them (~62 FLOP/B),
+// so only tensor cores keep it HBM-bound. But an MMA does not accumulate in the fixed
+// order the reference's score is defined in, so its scores can differ from the exact ones
+// in the last bits, which would move top-k indices at the cut. This file therefore does:
+//
+//   1. index_q_prepare_kernel   q -> e4m3 codes + per-head scale (bit-exact codec), plus one
+//                               error-bound constant per sequence.
+//   2. index_score_mma_kernel   approximate scores a_t for every cached token: fp8 keys are
+//                               streamed page by page with cp.async straight into swizzled
+//                               shared memory and consumed by tcgen05.mma kind::f8f6f4
+//                               (tokens = M 128, heads = N 32, dims = K 128), accumulators
+//                               in TMEM, scale/ReLU/head-weight epilogue from TMEM.
+//   3. index_select_refine_kernel  per sequence: radix-select the k-th approximate score
+//                               A_k; every token with |a_t - A_k| <= 2*eps is re-scored in
+//                               the exact order (sequential f32 fold, identical to
+//                               rivoli_index_score_paged); tokens above the band are in,
+//                               below are out; the final exact top-k (ties -> lower index)
+//                               is emitted ascending.
+//
+// Why this yields the exact top-k set: with |a_t - o_t| <= eps for the exact scores o_t,
+// the k-th largest values satisfy |A_k - E_k| <= eps, so a_t > A_k + 2 eps implies
+// o_t > E_k (selected) and a_t < A_k - 2 eps implies o_t < E_k (not selected); everything
+// else is decided on exact scores. eps per sequence = max key scale * sum_h |w_h ws| ds
+// s_q[h] ||qcode_h||_2 * sqrt(hd) * 448 * 2^-15: a Cauchy-Schwarz bound on sum |q_d k_d|
+// times 2^-15 relative error. The sequential fold's own worst case is hd * 2^-24 = 2^-17
+// of sum |q_d k_d|; the tensor core measured 2^-21.9 on full-range random codes.
+#include "codec.cuh"
+#include "common.cuh"
+#include "tc_common.cuh"
+#include "topk_core.cuh"
+
+namespace {
+
+constexpr int IM_TILE = 128;       // tokens per MMA tile (M)
+constexpr int IM_HD = 128;         // index dim = one 128-byte swizzle row
+constexpr int IM_NPAD = 32;        // heads padded to N = 32
+constexpr int IM_NS = 6;           // key-tile stages in flight
+constexpr int IM_LAG = 4;          // cp.async groups kept pending
+constexpr int IM_NACC = 4;         // TMEM accumulators (32 columns each)
+constexpr int IM_TPI = 16;         // tiles per work item
+constexpr int IM_THREADS = 192;    // warps 0-3 epilogue, 4 producer, 5 MMA
+constexpr int IM_STAGE_BYTES = IM_TILE * IM_HD;   // 16 KiB
+constexpr int IM_Q_BYTES = IM_NPAD * IM_HD;       // 4 KiB
+constexpr float IM_EPS_REL = 3.0517578125e-05f;   // 2^-15
+
+struct IndexMmaArgs {
+    DsaGeom g;
+    const uint8_t* qcodes; const float* qscales; const float* w;
+    const uint8_t* index_pool; const float* index_scale; const int32_t* block_table; const int32_t* seq_len;
+    float* scores; int score_stride; int B;
+    unsigned int* skmax;   // [B] max key scale seen, float bits (>= 0)
+    int* err;              // device error word (0 = ok)
+};
+
+// ---------------------------------------------------------------------------------------------
+// 1. q quantisation + per-sequence error-bound constant. One CTA per sequence, one warp per head.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+index_q_prepare_kernel(const uint16_t* __restrict__ q, const float* __restrict__ w, int nh, int hd, float wscale,
+                       float dscale, uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
+                       unsigned int* __restrict__ skmax, int* __restrict__ err) {
+    __shared__ float term[32];
+    const int b = blockIdx.x, h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (h < nh) {
+        const size_t v = (size_t)b * nh + h;
+        // same codec path as rivoli_index_q_quant: 16 values per lane, absmax scale, e4m3 codes
+        float f[16];
+        const bool act = lane * 16 < hd;
+        if (act) {
+            const uint4* p = reinterpret_cast<const uint4*>(q + v * hd + lane * 16);
+            const uint4 p0 = p[0], p1 = p[1];
+            const uint32_t ww[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { f[2 * i] = __uint_as_float(ww[i] << 16); f[2 * i + 1] = __uint_as_float(ww[i] & 0xffff0000u); }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) f[i] = 0.0f;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+        amax = rv_warp_max(amax);
+        const float scl = rv_scale_from_amax(amax);
+        float n2 = 0.0f;
+        if (act) {
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint16_t lo = rv_f32x2_to_e4m3x2(__fdiv_rn(f[4 * i], scl), __fdiv_rn(f[4 * i + 1], scl));
+                const uint16_t hi = rv_f32x2_to_e4m3x2(__fdiv_rn(f[4 * i + 2], scl), __fdiv_rn(f[4 * i + 3], scl));
+                o[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+                const float2 a = rv_e4m3x2_to_f32x2(lo), c = rv_e4m3x2_to_f32x2(hi);
+                n2 += a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
+            }
+            *reinterpret_cast<uint4*>(codes + v * hd + lane * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        n2 = rv_warp_sum(n2);
+        if (lane == 0) {
+            scales[v] = scl;
+            term[h] = fabsf(w[v] * wscale) * dscale * scl * sqrtf(n2);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+        for (int i = 0; i < nh; ++i) s += term[i];
+        // ||kcode||_2 <= sqrt(hd) * 448; 1.01 covers the roundings of this very sum
+        cb[b] = s * sqrtf((float)hd) * 448.0f * IM_EPS_REL * 1.01f;
+        skmax[b] = 0u;
+        if (b == 0) *err = 0;   // the scorer's error word starts clean on every call
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2. approximate scores on the tensor cores (persistent CTAs, warp specialised)
+// ---------------------------------------------------------------------------------------------
+struct ImBarriers {
+    uint64_t full[IM_NS], empty[IM_NS], tfull[IM_NACC], tempty[IM_NACC], qfree[2];
+};
+
+__global__ void __launch_bounds__(IM_THREADS)
+index_score_mma_kernel(IndexMmaArgs A) {
+    extern __shared__ __align__(1024) uint8_t im_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(im_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* s_keys = smem;                                   // IM_NS x 16 KiB
+    uint8_t* s_q = smem + IM_NS * IM_STAGE_BYTES;             // 2 x 4 KiB
+    __shared__ ImBarriers bars;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_flag;
+    __shared__ float s_wh[IM_NPAD], s_sq[IM_NPAD];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const DsaGeom& g = A.g;
+    const int nh = g.index_heads, P = g.page_tokens;
+
+    if (tid == 0) {
+        for (int i = 0; i < IM_NS; ++i) { tc::mbar_init(&bars.full[i], 32); tc::mbar_init(&bars.empty[i], 1); }
+        for (int i = 0; i < IM_NACC; ++i) { tc::mbar_init(&bars.tfull[i], 1); tc::mbar_init(&bars.tempty[i], 4); }
+        tc::mbar_init(&bars.qfree[0], 1); tc::mbar_init(&bars.qfree[1], 1);
+        tc::mbar_init_fence();
+        abort_flag = 0;
+    }
+    // q tiles start zeroed: rows >= nh are never loaded and must contribute exact zeros
+    for (int i = tid; i < 2 * IM_Q_BYTES / 16; i += IM_THREADS) reinterpret_cast<uint4*>(s_q)[i] = make_uint4(0, 0, 0, 0);
+    if (warp == 5) tc::tmem_alloc<IM_NACC * 32>(&tmem_base_s);
+    tc::fence_proxy_async();
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem = tmem_base_s;
+
+    const int max_tiles = (A.score_stride + IM_TILE - 1) / IM_TILE;
+    const int chunks = (max_tiles + IM_TPI - 1) / IM_TPI;
+    const int n_items = A.B * chunks;
+
+    if (warp == 4) {
+        // ------------------------------ producer: cp.async gather of key tiles ------------------
+        int issued = 0, signalled = 0, items_done = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int b = item / chunks, c = item - b * chunks;
+            const int nt = min(A.seq_len[b], A.score_stride);
+            const int tile_end = min((c + 1) * IM_TPI, (nt + IM_TILE - 1) / IM_TILE);
+            for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
+                const int s = issued % IM_NS;
+                ok = tc::mbar_wait(&bars.empty[s], ((issued / IM_NS) & 1) ^ 1, &abort_flag, 11);
+                if (!ok) break;
+                if (tile == c * IM_TPI) {  // first tile of the item carries this sequence's q codes
+                    const int qb = items_done & 1;
+                    ok = tc::mbar_wait(&bars.qfree[qb], ((items_done >> 1) & 1) ^ 1, &abort_flag, 12);
+                    if (!ok) break;
+                    const uint32_t qdst = tc::smem_u32(s_q + qb * IM_Q_BYTES);
+#pragma unroll
+                    for (int i = 0; i < IM_NPAD / 4; ++i) {
+                        const int row = i * 4 + (lane >> 3);
+                        if (row < nh) tc::cp_async16(qdst + tc::sw128_chunk(row, lane & 7),
+                                                     A.qcodes + ((size_t)b * nh + row) * IM_HD + (lane & 7) * 16);
+                    }
+                }
+                const int t0 = tile * IM_TILE;
+                const int ppt = IM_TILE / P;  // pages per tile (P <= 128)
+                int pg = -1;
+                if (lane < ppt) {
+                    const int lp = t0 / P + lane;
+                    if (lp < g.max_pages_per_seq && lp * P < nt) pg = A.block_table[(size_t)b * g.max_pages_per_seq + lp];
+                    if (pg < 0 || pg >= g.n_pool_pages) pg = -1;
+                }
+                const uint32_t dst = tc::smem_u32(s_keys + s * IM_STAGE_BYTES);
+#pragma unroll 8
+                for (int i = 0; i < IM_TILE / 4; ++i) {
+                    const int r = i * 4 + (lane >> 3);
+                    const int rp = __shfl_sync(0xffffffffu, pg, r / P);
+                    if (t0 + r < nt && rp >= 0)
+                        tc::cp_async16(dst + tc::sw128_chunk(r, lane & 7),
+                                       A.index_pool + ((size_t)rp * P + (r & (P - 1))) * IM_HD + (lane & 7) * 16);
+                }
+                tc::cp_async_commit();
+                ++issued;
+                if (issued - signalled > IM_LAG) {
+                    tc::cp_async_wait<IM_LAG>();
+                    tc::fence_proxy_async();
+                    tc::mbar_arrive(&bars.full[signalled % IM_NS]);
+                    ++signalled;
+                }
+            }
+            if (c * IM_TPI < tile_end) ++items_done;   // only items with tiles use a q buffer
+        }
+        tc::cp_async_wait<0>();
+        tc::fence_proxy_async();
+        for (; signalled < issued; ++signalled) tc::mbar_arrive(&bars.full[signalled % IM_NS]);
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer ------------------------------------------------
+        int it = 0, items_done = 0;
+        bool ok = true;
+        const uint32_t idesc = tc::idesc_e4m3(IM_TILE, IM_NPAD, 0, 0);
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int b = item / chunks, c = item - b * chunks;
+            const int nt = min(A.seq_len[b], A.score_stride);
+            const int tile_end = min((c + 1) * IM_TPI, (nt + IM_TILE - 1) / IM_TILE);
+            const int qb = items_done & 1;
+            for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
+                const int s = it % IM_NS, a = it % IM_NACC;
+                ok = tc::mbar_wait(&bars.full[s], (it / IM_NS) & 1, &abort_flag, 21) &&
+                     tc::mbar_wait(&bars.tempty[a], ((it / IM_NACC) & 1) ^ 1, &abort_flag, 22);
+                if (!ok) break;
+                tc::tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t ka = tc::smem_u32(s_keys + s * IM_STAGE_BYTES), qa = tc::smem_u32(s_q + qb * IM_Q_BYTES);
+#pragma unroll
+                    for (int k = 0; k < IM_HD / 32; ++k)
+                        tc::mma_f8(tmem + a * 32, tc::smem_desc_sw128(ka + k * 32, 16, 1024),
+                                   tc::smem_desc_sw128(qa + k * 32, 16, 1024), idesc, k > 0);
+                    tc::mma_commit(&bars.empty[s]);
+                    tc::mma_commit(&bars.tfull[a]);
+                    if (tile == tile_end - 1) tc::mma_commit(&bars.qfree[qb]);
+                }
+                __syncwarp();
+                ++it;
+            }
+            if (c * IM_TPI < tile_end) ++items_done;      // items without tiles never touched a q buffer
+        }
+    } else {
+        // ------------------------------ epilogue: TMEM -> scores --------------------------------
+        int it = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int b = item / chunks, c = item - b * chunks;
+            const int nt = min(A.seq_len[b], A.score_stride);
+            const int tile_end = min((c + 1) * IM_TPI, (nt + IM_TILE - 1) / IM_TILE);
+            if (c * IM_TPI >= tile_end) continue;
+            tc::named_barrier(1, 128);  // previous item's constants are no longer read
+            if (tid < IM_NPAD) {
+                s_wh[tid] = tid < nh ? __fmul_rn(A.w[(size_t)b * nh + tid], g.index_wscale) : 0.0f;
+                s_sq[tid] = tid < nh ? A.qscales[(size_t)b * nh + tid] : 0.0f;
+            }
+            tc::named_barrier(1, 128);
+            float skm = 0.0f;
+            for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
+                const int a = it % IM_NACC;
+                const int t = tile * IM_TILE + tid;
+                float sk = 0.0f;
+                if (t < nt) {  // issue the scale load before waiting on the accumulator
+                    int pg = A.block_table[(size_t)b * g.max_pages_per_seq + t / P];
+                    if (pg < 0 || pg >= g.n_pool_pages) pg = 0;
+                    sk = A.index_scale[(size_t)pg * P + (t & (P - 1))];
+                }
+                ok = tc::mbar_wait(&bars.tfull[a], (it / IM_NACC) & 1, &abort_flag, 31);
+                if (!ok) break;
+                tc::tc_fence_after();
+                uint32_t r[32];
+                tc::tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + a * 32, r);
+                tc::tmem_ld_wait();
+                tc::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&bars.tempty[a]);
+                if (t < nt) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int h = 0; h < IM_NPAD; ++h) {
+                        const float dot = __fmul_rn(__fmul_rn(__uint_as_float(r[h]), s_sq[h]), sk);
+                        float rr = __fmul_rn(dot, g.index_dscale);
+                        rr = rr > 0.0f ? rr : 0.0f;
+                        acc = __fadd_rn(acc, __fmul_rn(s_wh[h], rr));
+                    }
+                    A.scores[(size_t)b * A.score_stride + t] = acc;
+                    skm = fmaxf(skm, sk);
+                }
+                ++it;
+            }
+            skm = rv_warp_max(skm);
+            if (lane == 0 && skm > 0.0f) atomicMax(&A.skmax[b], __float_as_uint(skm));
+        }
+    }
+
+    tc::tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tc::tmem_dealloc<IM_NACC * 32>(tmem);
+    if (tid == 0 && abort_flag) atomicCAS(A.err, 0, abort_flag);
+}
+
+// ---------------------------------------------------------------------------------------------
+// 3. per-sequence exact selection with band refinement
+// ---------------------------------------------------------------------------------------------
+constexpr int RF_LIST = 2048;      // band tokens re-scored per round
+
+struct RefineArgs {
+    DsaGeom g;
+    const float* scores; int score_stride; const int32_t* seq_len;
+    const uint8_t* qcodes; const float* qscales; const float* w; const float* cb; const unsigned int* skmax;
+    const uint8_t* index_pool; const float* index_scale; const int32_t* block_table;
+    uint32_t* rows; int32_t* n_sel; int k;
+    unsigned int* stats;   // [B][2]: band size, sure-in count (may be NULL)
+};
+
+__global__ void __launch_bounds__(TK_THREADS)
+index_select_refine_kernel(RefineArgs A) {
+    extern __shared__ __align__(16) uint32_t rf_smem[];
+    __shared__ TkShared sh;
+    __shared__ uint32_t list_n, n_band_total;
+    const DsaGeom& g = A.g;
+    const int nh = g.index_heads, hd = g.index_dim, P = g.page_tokens;
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nt = min(A.seq_len[b], A.score_stride);
+    const int kk = min(A.k, nt);
+    uint32_t* out = A.rows + (size_t)b * A.k;
+    if (tid == 0) A.n_sel[b] = kk > 0 ? kk : 0;
+    if (kk <= 0) return;
+    if (kk == nt) {
+        for (int i = tid; i < nt; i += TK_THREADS) out[i] = (uint32_t)i;
+        if (tid == 0 && A.stats) { A.stats[b * 2] = 0; A.stats[b * 2 + 1] = (unsigned)nt; }
+        return;
+    }
+    // dynamic shared memory: keys[nt] | qf[hd][32] | kf[32 warps][hd] | list[RF_LIST]
+    uint32_t* keys = rf_smem;
+    float* qf = reinterpret_cast<float*>(rf_smem + ((nt + 3) & ~3));
+    float* kfw = qf + hd * 32;
+    uint32_t* list = reinterpret_cast<uint32_t*>(kfw + TK_WARPS * hd);
+
+    const float* s = A.scores + (size_t)b * A.score_stride;
+    for (int i = tid; i < nt; i += TK_THREADS) keys[i] = topk_key(s[i]);
+    for (int e = tid; e < hd * 32; e += TK_THREADS) {
+        const int d = e >> 5, h = e & 31;
+        qf[e] = h < nh ? rv_e4m3_to_f32(A.qcodes[((size_t)b * nh + h) * hd + d]) : 0.0f;
+    }
+    if (tid == 0) { list_n = 0; n_band_total = 0; }
+    __syncthreads();
+    auto key_at = [&](int i) -> uint32_t { return keys[i]; };
+
+    uint32_t pivot, need;
+    tk_radix_select(key_at, nt, (uint32_t)kk, sh, pivot, need);
+    const float a_k = topk_unkey(pivot);
+    const float eps = __uint_as_float(A.skmax[b]) * A.cb[b];
+    const uint32_t k_hi = topk_key(a_k + 2.0f * eps), k_lo = topk_key(a_k - 2.0f * eps);
+
+    // this lane's head constants for the exact re-score (nh <= 32)
+    const float my_sq = lane < nh ? A.qscales[(size_t)b * nh + lane] : 0.0f;
+    const float my_wh = lane < nh ? __fmul_rn(A.w[(size_t)b * nh + lane], g.index_wscale) : 0.0f;
+
+    for (int base = 0; base < nt; base += TK_THREADS) {
+        const int i = base + tid;
+        bool band = false;
+        if (i < nt) {
+            const uint32_t u = keys[i];
+            if (u > k_hi) keys[i] = 0xffffffffu;
+            else if (u < k_lo) keys[i] = 0u;
+            else band = true;
+        }
+        const uint32_t mb = __ballot_sync(0xffffffffu, band);
+        uint32_t wbase = 0;
+        if (lane == 0 && mb) wbase = atomicAdd(&list_n, (uint32_t)__popc(mb));
+        wbase = __shfl_sync(0xffffffffu, wbase, 0);
+        if (band) list[wbase + __popc(mb & ((1u << lane) - 1u))] = (uint32_t)i;
+        __syncthreads();
+        const uint32_t ln = list_n;
+        if (ln > RF_LIST - TK_THREADS || base + TK_THREADS >= nt) {
+            // exact re-score of the listed tokens: one warp per token, lane = head
+            for (uint32_t j = warp; j < ln; j += TK_WARPS) {
+                const int t = (int)list[j];
+                int pg = A.block_table[(size_t)b * g.max_pages_per_seq + t / P];
+                if (pg < 0 || pg >= g.n_pool_pages) pg = 0;
+                const size_t r = (size_t)pg * P + (t & (P - 1));
+                float* kf = kfw + warp * hd;
+                for (int d4 = lane; d4 < hd / 4; d4 += 32) {
+                    const uint32_t cw = *reinterpret_cast<const uint32_t*>(A.index_pool + r * hd + d4 * 4);
+                    const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw >> 16));
+                    kf[d4 * 4 + 0] = x.x; kf[d4 * 4 + 1] = x.y; kf[d4 * 4 + 2] = y.x; kf[d4 * 4 + 3] = y.y;
+                }
+                const float sk = A.index_scale[r];
+                __syncwarp();
+                float cd = 0.0f;
+                for (int d = 0; d < hd; ++d) cd = fmaf(qf[d * 32 + lane], kf[d], cd);
+                const float dot = __fmul_rn(__fmul_rn(cd, my_sq), sk);
+                float rr = __fmul_rn(dot, g.index_dscale);
+                rr = rr > 0.0f ? rr : 0.0f;
+                const float cth = __fmul_rn(my_wh, rr);
+                float acc = 0.0f;
+                for (int h = 0; h < nh; ++h) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, cth, h));
+                if (lane == 0) {
+                    uint32_t ku = topk_key(acc);
+                    ku = ku == 0xffffffffu ? 0xfffffffeu : (ku == 0u ? 1u : ku);
+                    keys[t] = ku;
+                }
+                __syncwarp();
+            }
+            __syncthreads();
+            if (tid == 0) { n_band_total += ln; list_n = 0; }
+            __syncthreads();
+        }
+    }
+    // final exact selection over: sure-in = max key, band = exact keys, sure-out = 0
+    tk_radix_select(key_at, nt, (uint32_t)kk, sh, pivot, need);
+    tk_compact(key_at, nt, (uint32_t)kk, pivot, need, sh, out);
+    if (tid == 0 && A.stats) { A.stats[b * 2] = n_band_total; A.stats[b * 2 + 1] = 0; }
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct SelectScratch {
+    uint8_t* qcodes; float* qscales; float* cb; unsigned int* skmax; int* err; unsigned int* stats; float* scores;
+};
+
+SelectScratch carve(const DsaGeom* g, int B, int score_stride, void* scratch, size_t* total) {
+    uint8_t* p = static_cast<uint8_t*>(scratch);
+    size_t off = 0;
+    SelectScratch s;
+    auto take = [&](size_t n) { uint8_t* r = p ? p + off : nullptr; off += align_up(n, 256); return r; };
+    s.qcodes = take((size_t)B * g->index_heads * g->index_dim);
+    s.qscales = reinterpret_cast<float*>(take((size_t)B * g->index_heads * 4));
+    s.cb = reinterpret_cast<float*>(take((size_t)B * 4));
+    s.skmax = reinterpret_cast<unsigned int*>(take((size_t)B * 4));
+    s.err = reinterpret_cast<int*>(take(4));
+    s.stats = reinterpret_cast<unsigned int*>(take((size_t)B * 8));
+    s.scores = reinterpret_cast<float*>(take((size_t)B * score_stride * 4));
+    *total = off;
+    return s;
+}
+
+constexpr int RF_MAX_NT = 40 * 1024;   // keys + 16 KiB q + 16 KiB key rows + list within 227 KiB
+
+bool mma_geometry_ok(const DsaGeom* g, int score_stride) {
+    return g->index_dim == IM_HD && g->index_heads <= IM_NPAD && g->page_tokens >= 16 && g->page_tokens <= IM_TILE &&
+           score_stride <= RF_MAX_NT;
+}
+
+}  // namespace
+
+RIVOLI_API size_t rivoli_index_select_scratch_bytes(const DsaGeom* g, int B, int score_stride) {
+    if (!g || B <= 0 || score_stride <= 0) return 0;
+    size_t total = 0;
+    carve(g, B, score_stride, nullptr, &total);
+    return total;
+}
+
+// 1 if rivoli_index_select_paged takes the tensor-core path for this geometry, else 0.
+RIVOLI_API int rivoli_index_select_uses_mma(const DsaGeom* g, int score_stride) {
+    return (g && mma_geometry_ok(g, score_stride)) ? 1 : 0;
+}
+
+RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index_q, const float* w,
+                                         const uint8_t* index_pool, const float* index_scale,
+                                         const int32_t* block_table, const int32_t* seq_len, int B,
+                                         int score_stride, uint32_t* rows, int32_t* n_sel, void* scratch,
+                                         void* stream) {
+    if (int e = rv_check_geom(g)) return e;
+    if (B <= 0 || score_stride <= 0 || !index_q || !w || !index_pool || !index_scale || !block_table || !seq_len ||
+        !rows || !n_sel || !scratch)
+        return 1001;
+    if ((((uintptr_t)index_pool | (uintptr_t)index_q | (uintptr_t)scratch) & 15)) return 1005;
+    if ((long long)score_stride > (long long)g->max_pages_per_seq * g->page_tokens) return 1002;
+    cudaStream_t st = (cudaStream_t)stream;
+    size_t total = 0;
+    SelectScratch s = carve(g, B, score_stride, scratch, &total);
+    const int nh = g->index_heads, hd = g->index_dim;
+
+    if (!mma_geometry_ok(g, score_stride)) {
+        // geometries outside the tensor-core kernel: the exact CUDA-core scorer + exact top-k
+        int e = rivoli_index_q_quant(index_q, B * nh, hd, s.qcodes, s.qscales, stream);
+        if (e) return e;
+        e = rivoli_index_score_paged(g, s.qcodes, s.qscales, w, index_pool, index_scale, block_table, seq_len, B,
+                                     s.scores, score_stride, stream);
+        if (e) return e;
+        return rivoli_index_topk_batched(s.scores, score_stride, seq_len, B, g->top_k, rows, n_sel, stream);
+    }
+
+    rv_drain_error();
+    index_q_prepare_kernel<<<B, 32 * nh, 0, st>>>(index_q, w, nh, hd, g->index_wscale, g->index_dscale, s.qcodes,
+                                                   s.qscales, s.cb, s.skmax, s.err);
+    if (int e = rv_launch_status()) return e;
+
+    IndexMmaArgs ma{*g, s.qcodes, s.qscales, w, index_pool, index_scale, block_table, seq_len,
+                    s.scores, score_stride, B, s.skmax, s.err};
+    const size_t smem1 = (size_t)IM_NS * IM_STAGE_BYTES + 2 * IM_Q_BYTES + 1024;
+    cudaFuncSetAttribute(index_score_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int max_tiles = (score_stride + IM_TILE - 1) / IM_TILE;
+    const int n_items = B * ((max_tiles + IM_TPI - 1) / IM_TPI);
+    const int grid = n_items < 2 * sms ? n_items : 2 * sms;
+    index_score_mma_kernel<<<grid, IM_THREADS, smem1, st>>>(ma);
+    if (int e = rv_launch_status()) return e;
+
+    RefineArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb, s.skmax,
+                  index_pool, index_scale, block_table, rows, n_sel, g->top_k, s.stats};
+    const size_t smem2 = ((size_t)((score_stride + 3) & ~3) + (size_t)hd * 32 + (size_t)TK_WARPS * hd + RF_LIST) * 4;
+    cudaFuncSetAttribute(index_select_refine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    index_select_refine_kernel<<<B, TK_THREADS, smem2, st>>>(ra);
+    return rv_launch_status();
+}
+
+// Reads back the tensor-core scorer's error word (0 = no bounded wait ever gave up) and
+// clears it. Synchronises the stream.
+RIVOLI_API int rivoli_index_select_status(const DsaGeom* g, int B, int score_stride, void* scratch, void* stream) {
+    if (!g || !scratch) return 1001;
+    size_t total = 0;
+    SelectScratch s = carve(g, B, score_stride, scratch, &total);
+    int h = 0;
+    cudaError_t e = cudaMemcpyAsync(&h, s.err, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return -(int)e;
+    if (h) cudaMemsetAsync(s.err, 0, sizeof(int), (cudaStream_t)stream);
+    return h ? 1008 : 0;
+}
+
+// Diagnostics: copies the per-sequence band sizes of the last call (tokens re-scored
+// exactly) to host memory. Synchronises the stream.
+RIVOLI_API int rivoli_index_select_band_stats(const DsaGeom* g, int B, int score_stride, void* scratch,
+                                              uint32_t* host_band, void* stream) {
+    if (!g || !scratch || !host_band || B <= 0) return 1001;
+    size_t total = 0;
+    SelectScratch s = carve(g, B, score_stride, scratch, &total);
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaMemcpy2D(host_band, 4, s.stats, 8, 4, (size_t)B, cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? 0 : -(int)e;
+}

@@ -1,0 +1,112 @@
+// Block-wide exact top-k primitives over order-preserving u32 keys (1024-thread CTAs).
+// Selection order = key descending, index ascending on ties; output ascending by index.
+// Contract and tie rule: crates/backend/kernels/indexer.hip:143-257 of the reference.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+constexpr int TK_THREADS = 1024;
+constexpr int TK_WARPS = TK_THREADS / 32;
+
+// Ascending key iff ascending float; -0.0 canonicalised to +0.0 (indexer.hip:156-159).
+__device__ __forceinline__ uint32_t topk_key(float v) {
+    uint32_t b = (v == 0.0f) ? 0u : __float_as_uint(v);
+    return b ^ ((uint32_t)((int32_t)b >> 31) | 0x80000000u);
+}
+__device__ __forceinline__ float topk_unkey(uint32_t k) {
+    const uint32_t b = (k & 0x80000000u) ? (k ^ 0x80000000u) : ~k;
+    return __uint_as_float(b);
+}
+
+struct TkShared {
+    uint32_t hist[256];
+    uint32_t wcnt[TK_WARPS];
+    uint32_t pivot, need;
+};
+
+// Four 8-bit passes, MSB first: the key of the kk-th largest entry and how many of the
+// entries tied at it the selection takes. KeyAt(i) returns the key of element i.
+// Every thread of the CTA must call it. Counting is warp-aggregated so that tie-heavy
+// arrays (ReLU zeros) do not serialise on one histogram bin.
+template <class KeyAt>
+__device__ __forceinline__ void tk_radix_select(KeyAt key_at, int nt, uint32_t kk, TkShared& sh, uint32_t& pivot_out,
+                                                uint32_t& need_out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t pivot = 0u, mask = 0u, need = kk;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) sh.hist[tid] = 0u;
+        __syncthreads();
+        for (int base = 0; base < nt; base += TK_THREADS) {
+            const int i = base + tid;
+            uint32_t bin = 0xffffffffu;
+            if (i < nt) {
+                const uint32_t u = key_at(i);
+                if ((u & mask) == pivot) bin = (u >> shift) & 0xffu;
+            }
+            const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+            if (bin != 0xffffffffu && lane == __ffs(peers) - 1) atomicAdd(&sh.hist[bin], (uint32_t)__popc(peers));
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // lane owns bins 8*lane .. 8*lane+7; acc = entries in strictly higher bins
+            uint32_t h[8], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { h[j] = sh.hist[lane * 8 + j]; tot += h[j]; }
+            uint32_t incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_down_sync(0xffffffffu, incl, o);
+                if (lane + o < 32) incl += v;
+            }
+            uint32_t acc = incl - tot;
+#pragma unroll
+            for (int j = 7; j >= 0; --j) {
+                if (acc < need && need <= acc + h[j]) {
+                    sh.pivot = pivot | ((uint32_t)(lane * 8 + j) << shift);
+                    sh.need = need - acc;
+                }
+                acc += h[j];
+            }
+        }
+        __syncthreads();
+        pivot = sh.pivot;
+        need = sh.need;
+        mask |= 0xffu << shift;
+    }
+    pivot_out = pivot;
+    need_out = need;
+}
+
+// Ascending compaction: slot(i) = #(key > pivot before i) + min(#(key == pivot before i), need).
+// Ballots and a fixed scan order decide every slot; no atomics. Every thread must call it.
+template <class KeyAt>
+__device__ __forceinline__ void tk_compact(KeyAt key_at, int nt, uint32_t kk, uint32_t pivot, uint32_t need, TkShared& sh,
+                                           uint32_t* __restrict__ out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t base_gt = 0u, base_eq = 0u;
+    for (int base = 0; base < nt; base += TK_THREADS) {
+        const int i = base + tid;
+        const bool live = i < nt;
+        const uint32_t u = live ? key_at(i) : 0u;
+        const bool gt = live && u > pivot, eq = live && u == pivot;
+        const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
+        if (lane == 0) sh.wcnt[warp] = (uint32_t)__popc(mg) | ((uint32_t)__popc(me) << 16);
+        __syncthreads();
+        uint32_t pre = 0u, tot = 0u;
+#pragma unroll 8
+        for (int w2 = 0; w2 < TK_WARPS; ++w2) {
+            const uint32_t c = sh.wcnt[w2];
+            if (w2 < warp) pre += c;
+            tot += c;
+        }
+        const uint32_t lt = (1u << lane) - 1u;
+        const uint32_t g = base_gt + (pre & 0xffffu) + (uint32_t)__popc(mg & lt);
+        const uint32_t e = base_eq + (pre >> 16) + (uint32_t)__popc(me & lt);
+        if (gt || (eq && e < need)) out[g + (e < need ? e : need)] = (uint32_t)i;
+        base_gt += tot & 0xffffu;
+        base_eq += tot >> 16;
+        __syncthreads();
+        if (base_gt + min(base_eq, need) >= kk) break;  // uniform: every row is placed
+    }
+}

@@ -57,6 +57,8 @@ class DsaDecodeLayer:
         self.out_lse = torch.zeros((n_seqs, geom.n_heads), dtype=f32, device=d)
         nbytes = max(be.attend_paged_scratch_bytes(geom, n_seqs), 16)
         self.scratch = torch.zeros(nbytes, dtype=u8, device=d)
+        self.select_scratch = torch.zeros(be.index_select_scratch_bytes(geom, n_seqs, self.score_stride),
+                                          dtype=u8, device=d)
 
     # --- paging -------------------------------------------------------------------------------------
     def reserve(self, seq: int, n_tokens: int) -> None:
@@ -79,7 +81,15 @@ class DsaDecodeLayer:
                                   self.status, stream)
 
     def select(self, index_q: torch.Tensor, index_w: torch.Tensor, seq_len: torch.Tensor, stream=None) -> None:
-        """Indexer: quantise q, score every cached key, exact top-k -> ``rows``/``n_sel``."""
+        """Indexer: quantise q, score every cached key, exact top-k -> ``rows``/``n_sel``
+        (tensor-core scorer with exact refinement at the cut where the geometry allows)."""
+        be.launch_index_select_paged(self.g, index_q, index_w, self.index_pool, self.index_scale,
+                                     self.block_table, seq_len, self.B, self.score_stride, self.rows,
+                                     self.n_sel, self.select_scratch, stream)
+
+    def select_unfused(self, index_q: torch.Tensor, index_w: torch.Tensor, seq_len: torch.Tensor,
+                       stream=None) -> None:
+        """The same selection through the three separate operators on CUDA cores."""
         g = self.g
         be.launch_index_q_quant(index_q, self.B * g.index_heads, g.index_dim, self.qcodes, self.qscales, stream)
         be.launch_index_score_paged(g, self.qcodes, self.qscales, index_w, self.index_pool, self.index_scale,
@@ -107,6 +117,7 @@ class DsaDecodeLayer:
 
     def check_status(self) -> None:
         """Raise if a kernel flagged a bad block-table entry since the last check (syncs)."""
+        be.index_select_status(self.g, self.B, self.score_stride, self.select_scratch)
         s = int(self.status.item())
         if s:
             self.status.zero_()

@@ -179,3 +179,68 @@ def test_append_flags_unmapped_page(be):
     be.device_sync()
     assert int(status.item()) == 1
     assert torch.equal(before, d["latent_pool"])
+
+
+# ---- fused tensor-core indexer: rows must be IDENTICAL to the exact chain / the oracle -----------
+SELECT_CASES = {
+    "model-dims": dict(seed=21, B=4, ctx=[5000, 4097, 129, 2049], top_k=2048),
+    "short-topk": dict(seed=22, B=3, ctx=[3000, 1000, 700], top_k=64),
+    "p16": dict(seed=23, B=2, ctx=[900, 333], top_k=128, page_tokens=16),
+    "cfg1-fallback": dict(seed=0, B=1, ctx=[257], n_heads=16, index_heads=8, index_dim=64, page_tokens=16, top_k=64,
+                          pool_factor=1.0),
+}
+
+
+def _select(be, st, g, d, w):
+    B = st.B
+    stride = int(st.seq_len.max())
+    rows = torch.full((B, g.top_k), -1, dtype=torch.int32, device="cuda")
+    n_sel = torch.zeros(B, dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(be.index_select_scratch_bytes(g, B, stride), dtype=torch.uint8, device="cuda")
+    be.launch_index_select_paged(g, dev(st.index_q), dev(w), d["index_pool"], d["index_scale"], d["block_table"],
+                                 d["seq_len"], B, stride, rows, n_sel, scratch)
+    be.index_select_status(g, B, stride, scratch)
+    band = be.index_select_band_stats(g, B, stride, scratch) if be.index_select_uses_mma(g, stride) else None
+    return rows.cpu().numpy().view(np.uint32), n_sel.cpu().numpy(), band
+
+
+@pytest.mark.parametrize("case", list(SELECT_CASES))
+def test_fused_select_is_bit_identical(be, case):
+    c = dict(SELECT_CASES[case])
+    st = State(c.pop("seed"), c.pop("B"), c.pop("ctx"), **c)
+    g = make_geom(be.DsaGeom, **st.geom_kw)
+    want = st.oracle_step()
+    d = dict(index_pool=dev(want["index_pool"]), index_scale=dev(want["index_scale"]),
+             block_table=dev(st.block_table), seq_len=dev(st.seq_len))
+    rows, n_sel, band = _select(be, st, g, d, st.index_w)
+    np.testing.assert_array_equal(n_sel, want["n_sel"])
+    np.testing.assert_array_equal(rows, want["rows"])
+    if band is not None:
+        # the exact re-score touches a small fraction of the cache, not all of it
+        for b in range(st.B):
+            if st.seq_len[b] > g.top_k:
+                assert band[b] <= max(64, st.seq_len[b] // 8), (band, st.seq_len)
+
+
+def test_fused_select_tie_dominated(be):
+    """ReLU makes whole score arrays tie: all-zero head weights (every score exactly 0, the
+    index rule decides everything) and a single live head (thousands of exact zeros at the cut)."""
+    st = State(31, 2, [4000, 2600], top_k=2048)
+    g = make_geom(be.DsaGeom, **st.geom_kw)
+    base = st.oracle_step()
+    d = dict(index_pool=dev(base["index_pool"]), index_scale=dev(base["index_scale"]),
+             block_table=dev(st.block_table), seq_len=dev(st.seq_len))
+    for mode in ("zeros", "one-head"):
+        w = np.zeros_like(st.index_w)
+        if mode == "one-head":
+            w[:, 3] = 1.0
+        qc, qs = orc.index_q_quant(st.index_q, g.index_dim)
+        stride = int(st.seq_len.max())
+        sc = orc.index_score_paged(st.og, qc, qs, w, base["index_pool"], base["index_scale"], st.block_table,
+                                   st.seq_len, stride)
+        want_rows, want_n = orc.index_topk_batched(sc, st.seq_len, g.top_k)
+        rows, n_sel, band = _select(be, st, g, d, w)
+        np.testing.assert_array_equal(n_sel, want_n)
+        np.testing.assert_array_equal(rows, want_rows)
+        if mode == "zeros":
+            assert (rows[0, :2048] == np.arange(2048)).all()
