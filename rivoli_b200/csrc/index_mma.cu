@@ -8,7 +8,7 @@
 //   1. index_q_prepare_kernel   q -> e4m3 codes + per-head scale (bit-exact codec), plus one
 //                               error-bound constant per sequence.
 //   2. index_score_mma_kernel   approximate scores a_t for every cached token: fp8 keys are
-//                               streamed page by page with cp.async straight into swizzled
+//                               streamed page by page by TMA (one 2-D box per page) into swizzled
 //                               shared memory and consumed by tcgen05.mma kind::f8f6f4
 //                               (tokens = M 128, heads = N 32, dims = K 128), accumulators
 //                               in TMEM, scale/ReLU/head-weight epilogue from TMEM.
@@ -29,6 +29,7 @@
 #include "codec.cuh"
 #include "common.cuh"
 #include "tc_common.cuh"
+#include "tmap.hpp"
 #include "topk_core.cuh"
 
 namespace {
@@ -121,7 +122,8 @@ struct ImBarriers {
 };
 
 __global__ void __launch_bounds__(IM_THREADS)
-index_score_mma_kernel(IndexMmaArgs A) {
+index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_keys,
+                       const __grid_constant__ CUtensorMap tm_q) {
     extern __shared__ __align__(1024) uint8_t im_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(im_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* s_keys = smem;                                   // IM_NS x 16 KiB
@@ -129,14 +131,15 @@ index_score_mma_kernel(IndexMmaArgs A) {
     __shared__ ImBarriers bars;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
-    __shared__ float s_wh[IM_NPAD], s_sq[IM_NPAD];
+    __shared__ float s_wh[IM_NPAD];
+    __shared__ int s_pg[IM_TPI * (IM_TILE / 16)];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const DsaGeom& g = A.g;
     const int nh = g.index_heads, P = g.page_tokens;
 
     if (tid == 0) {
-        for (int i = 0; i < IM_NS; ++i) { tc::mbar_init(&bars.full[i], 32); tc::mbar_init(&bars.empty[i], 1); }
+        for (int i = 0; i < IM_NS; ++i) { tc::mbar_init(&bars.full[i], 1); tc::mbar_init(&bars.empty[i], 1); }
         for (int i = 0; i < IM_NACC; ++i) { tc::mbar_init(&bars.tfull[i], 1); tc::mbar_init(&bars.tempty[i], 4); }
         tc::mbar_init(&bars.qfree[0], 1); tc::mbar_init(&bars.qfree[1], 1);
         tc::mbar_init_fence();
@@ -156,60 +159,56 @@ index_score_mma_kernel(IndexMmaArgs A) {
     const int n_items = A.B * chunks;
 
     if (warp == 4) {
-        // ------------------------------ producer: cp.async gather of key tiles ------------------
-        int issued = 0, signalled = 0, items_done = 0;
+        // ------------------------------ producer: TMA page loads ----------------------------------
+        // A page is P rows x 128 bytes, contiguous in the pool; one 2-D TMA box per page lands it in
+        // shared memory already in the 128-byte-swizzled K-major form the MMA consumes. The whole
+        // warp fetches an item's page ids once; lane 0 then issues one instruction per page.
+        int it = 0, items_done = 0;
         bool ok = true;
+        const int ppt = IM_TILE / P;  // pages per tile (16 <= P <= 128)
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int b = item / chunks, c = item - b * chunks;
             const int nt = min(A.seq_len[b], A.score_stride);
             const int tile_end = min((c + 1) * IM_TPI, (nt + IM_TILE - 1) / IM_TILE);
+            if (c * IM_TPI >= tile_end) continue;
+            const int first_lp = c * IM_TPI * ppt;
+            __syncwarp();
+            for (int j = lane; j < IM_TPI * ppt; j += 32) {
+                const int lp = first_lp + j;
+                int pg = -1;
+                if (lp < g.max_pages_per_seq && lp * P < nt) pg = A.block_table[(size_t)b * g.max_pages_per_seq + lp];
+                s_pg[j] = (pg < 0 || pg >= g.n_pool_pages) ? -1 : pg;
+            }
+            __syncwarp();
+            const int qb = items_done & 1;
             for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
-                const int s = issued % IM_NS;
-                ok = tc::mbar_wait(&bars.empty[s], ((issued / IM_NS) & 1) ^ 1, &abort_flag, 11);
+                const int s = it % IM_NS;
+                ok = tc::mbar_wait(&bars.empty[s], ((it / IM_NS) & 1) ^ 1, &abort_flag, 11);
                 if (!ok) break;
-                if (tile == c * IM_TPI) {  // first tile of the item carries this sequence's q codes
-                    const int qb = items_done & 1;
+                const bool first = tile == c * IM_TPI;
+                if (first) {
                     ok = tc::mbar_wait(&bars.qfree[qb], ((items_done >> 1) & 1) ^ 1, &abort_flag, 12);
                     if (!ok) break;
-                    const uint32_t qdst = tc::smem_u32(s_q + qb * IM_Q_BYTES);
-#pragma unroll
-                    for (int i = 0; i < IM_NPAD / 4; ++i) {
-                        const int row = i * 4 + (lane >> 3);
-                        if (row < nh) tc::cp_async16(qdst + tc::sw128_chunk(row, lane & 7),
-                                                     A.qcodes + ((size_t)b * nh + row) * IM_HD + (lane & 7) * 16);
+                }
+                if (lane == 0) {
+                    const int pbase = (tile - c * IM_TPI) * ppt;
+                    uint32_t bytes = first ? (uint32_t)nh * IM_HD : 0u;
+                    for (int p2 = 0; p2 < ppt; ++p2) bytes += s_pg[pbase + p2] >= 0 ? (uint32_t)P * IM_HD : 0u;
+                    tc::mbar_arrive_expect_tx(&bars.full[s], bytes);
+                    if (first)  // this sequence's q codes ride the first tile's barrier
+                        tc::tma_load_2d(tc::smem_u32(s_q + qb * IM_Q_BYTES), &tm_q, 0, b * nh, &bars.full[s]);
+                    for (int p2 = 0; p2 < ppt; ++p2) {
+                        const int pg = s_pg[pbase + p2];
+                        if (pg >= 0)
+                            tc::tma_load_2d(tc::smem_u32(s_keys + s * IM_STAGE_BYTES + p2 * P * IM_HD), &tm_keys, 0,
+                                            pg * P, &bars.full[s]);
                     }
                 }
-                const int t0 = tile * IM_TILE;
-                const int ppt = IM_TILE / P;  // pages per tile (P <= 128)
-                int pg = -1;
-                if (lane < ppt) {
-                    const int lp = t0 / P + lane;
-                    if (lp < g.max_pages_per_seq && lp * P < nt) pg = A.block_table[(size_t)b * g.max_pages_per_seq + lp];
-                    if (pg < 0 || pg >= g.n_pool_pages) pg = -1;
-                }
-                const uint32_t dst = tc::smem_u32(s_keys + s * IM_STAGE_BYTES);
-#pragma unroll 8
-                for (int i = 0; i < IM_TILE / 4; ++i) {
-                    const int r = i * 4 + (lane >> 3);
-                    const int rp = __shfl_sync(0xffffffffu, pg, r / P);
-                    if (t0 + r < nt && rp >= 0)
-                        tc::cp_async16(dst + tc::sw128_chunk(r, lane & 7),
-                                       A.index_pool + ((size_t)rp * P + (r & (P - 1))) * IM_HD + (lane & 7) * 16);
-                }
-                tc::cp_async_commit();
-                ++issued;
-                if (issued - signalled > IM_LAG) {
-                    tc::cp_async_wait<IM_LAG>();
-                    tc::fence_proxy_async();
-                    tc::mbar_arrive(&bars.full[signalled % IM_NS]);
-                    ++signalled;
-                }
+                __syncwarp();
+                ++it;
             }
-            if (c * IM_TPI < tile_end) ++items_done;   // only items with tiles use a q buffer
+            ++items_done;
         }
-        tc::cp_async_wait<0>();
-        tc::fence_proxy_async();
-        for (; signalled < issued; ++signalled) tc::mbar_arrive(&bars.full[signalled % IM_NS]);
     } else if (warp == 5) {
         // ------------------------------ MMA issuer ------------------------------------------------
         int it = 0, items_done = 0;
@@ -252,20 +251,15 @@ index_score_mma_kernel(IndexMmaArgs A) {
             if (c * IM_TPI >= tile_end) continue;
             tc::named_barrier(1, 128);  // previous item's constants are no longer read
             if (tid < IM_NPAD) {
-                s_wh[tid] = tid < nh ? __fmul_rn(A.w[(size_t)b * nh + tid], g.index_wscale) : 0.0f;
-                s_sq[tid] = tid < nh ? A.qscales[(size_t)b * nh + tid] : 0.0f;
+                // a_t / s_k = sum_h (w_h ws s_q[h] ds) * max(cd_h, 0): the exact formula up to a few
+                // roundings (s_q, s_k, ds > 0 commute with the ReLU); the band covers them
+                s_wh[tid] = tid < nh ? A.w[(size_t)b * nh + tid] * g.index_wscale * A.qscales[(size_t)b * nh + tid] *
+                                           g.index_dscale : 0.0f;
             }
             tc::named_barrier(1, 128);
-            float skm = 0.0f;
             for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
                 const int a = it % IM_NACC;
                 const int t = tile * IM_TILE + tid;
-                float sk = 0.0f;
-                if (t < nt) {  // issue the scale load before waiting on the accumulator
-                    int pg = A.block_table[(size_t)b * g.max_pages_per_seq + t / P];
-                    if (pg < 0 || pg >= g.n_pool_pages) pg = 0;
-                    sk = A.index_scale[(size_t)pg * P + (t & (P - 1))];
-                }
                 ok = tc::mbar_wait(&bars.tfull[a], (it / IM_NACC) & 1, &abort_flag, 31);
                 if (!ok) break;
                 tc::tc_fence_after();
@@ -278,19 +272,11 @@ index_score_mma_kernel(IndexMmaArgs A) {
                 if (t < nt) {
                     float acc = 0.0f;
 #pragma unroll
-                    for (int h = 0; h < IM_NPAD; ++h) {
-                        const float dot = __fmul_rn(__fmul_rn(__uint_as_float(r[h]), s_sq[h]), sk);
-                        float rr = __fmul_rn(dot, g.index_dscale);
-                        rr = rr > 0.0f ? rr : 0.0f;
-                        acc = __fadd_rn(acc, __fmul_rn(s_wh[h], rr));
-                    }
-                    A.scores[(size_t)b * A.score_stride + t] = acc;
-                    skm = fmaxf(skm, sk);
+                    for (int h = 0; h < IM_NPAD; ++h) acc = fmaf(s_wh[h], fmaxf(__uint_as_float(r[h]), 0.0f), acc);
+                    A.scores[(size_t)b * A.score_stride + t] = acc;   // the key scale s_k[t] is applied by the selector
                 }
                 ++it;
             }
-            skm = rv_warp_max(skm);
-            if (lane == 0 && skm > 0.0f) atomicMax(&A.skmax[b], __float_as_uint(skm));
         }
     }
 
@@ -338,20 +324,33 @@ index_select_refine_kernel(RefineArgs A) {
     float* kfw = qf + hd * 32;
     uint32_t* list = reinterpret_cast<uint32_t*>(kfw + TK_WARPS * hd);
 
+    // approximate score = (unscaled score from the tensor-core pass) * key scale of the token
     const float* s = A.scores + (size_t)b * A.score_stride;
-    for (int i = tid; i < nt; i += TK_THREADS) keys[i] = topk_key(s[i]);
-    for (int e = tid; e < hd * 32; e += TK_THREADS) {
-        const int d = e >> 5, h = e & 31;
-        qf[e] = h < nh ? rv_e4m3_to_f32(A.qcodes[((size_t)b * nh + h) * hd + d]) : 0.0f;
+    float skm = 0.0f;
+    for (int i = tid; i < nt; i += TK_THREADS) {
+        int pg = A.block_table[(size_t)b * g.max_pages_per_seq + i / P];
+        if (pg < 0 || pg >= g.n_pool_pages) pg = 0;
+        const float sk = A.index_scale[(size_t)pg * P + (i & (P - 1))];
+        keys[i] = topk_key(s[i] * sk);
+        skm = fmaxf(skm, sk);
+    }
+    skm = rv_warp_max(skm);
+    if (lane == 0) sh.wcnt[warp] = __float_as_uint(skm);
+    for (int e = tid; e < hd * 32; e += TK_THREADS) {   // e = h * hd + d: coalesced byte reads, transposed store
+        const int h = e / hd, d = e - h * hd;
+        qf[d * 32 + h] = h < nh ? rv_e4m3_to_f32(A.qcodes[((size_t)b * nh + h) * hd + d]) : 0.0f;
     }
     if (tid == 0) { list_n = 0; n_band_total = 0; }
+    __syncthreads();
+    float sk_max = 0.0f;
+    for (int w2 = 0; w2 < TK_WARPS; ++w2) sk_max = fmaxf(sk_max, __uint_as_float(sh.wcnt[w2]));
     __syncthreads();
     auto key_at = [&](int i) -> uint32_t { return keys[i]; };
 
     uint32_t pivot, need;
     tk_radix_select(key_at, nt, (uint32_t)kk, sh, pivot, need);
     const float a_k = topk_unkey(pivot);
-    const float eps = __uint_as_float(A.skmax[b]) * A.cb[b];
+    const float eps = sk_max * A.cb[b];
     const uint32_t k_hi = topk_key(a_k + 2.0f * eps), k_lo = topk_key(a_k - 2.0f * eps);
 
     // this lane's head constants for the exact re-score (nh <= 32)
@@ -437,7 +436,7 @@ SelectScratch carve(const DsaGeom* g, int B, int score_stride, void* scratch, si
     return s;
 }
 
-constexpr int RF_MAX_NT = 40 * 1024;   // keys + 16 KiB q + 16 KiB key rows + list within 227 KiB
+constexpr int RF_MAX_NT = 32 * 1024;   // keys 128 KiB + q 16 + key rows 16 + list 8 + histograms 34 < 227 KiB
 
 bool mma_geometry_ok(const DsaGeom* g, int score_stride) {
     return g->index_dim == IM_HD && g->index_heads <= IM_NPAD && g->page_tokens >= 16 && g->page_tokens <= IM_TILE &&
@@ -499,7 +498,12 @@ RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index
     const int max_tiles = (score_stride + IM_TILE - 1) / IM_TILE;
     const int n_items = B * ((max_tiles + IM_TPI - 1) / IM_TPI);
     const int grid = n_items < 2 * sms ? n_items : 2 * sms;
-    index_score_mma_kernel<<<grid, IM_THREADS, smem1, st>>>(ma);
+    CUtensorMap tm_keys, tm_q;
+    if (int e = rivoli::make_tmap_rows_sw128(&tm_keys, index_pool, (uint64_t)g->n_pool_pages * g->page_tokens, IM_HD,
+                                             (uint32_t)g->page_tokens))
+        return e;
+    if (int e = rivoli::make_tmap_rows_sw128(&tm_q, s.qcodes, (uint64_t)B * nh, IM_HD, (uint32_t)nh)) return e;
+    index_score_mma_kernel<<<grid, IM_THREADS, smem1, st>>>(ma, tm_keys, tm_q);
     if (int e = rv_launch_status()) return e;
 
     RefineArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb, s.skmax,

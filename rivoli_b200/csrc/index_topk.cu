@@ -6,14 +6,14 @@
 // crates/core/src/routing.rs:42-61 + sort (crates/engine/tests/kernel_vector.rs:126-131).
 //
 // One CTA of 1024 threads per sequence. The order-preserving keys are staged ONCE in
-// shared memory (up to 56 Ki scores = 224 KiB; B200 has 227 KiB per CTA), so the four
+// shared memory (up to 47 Ki scores = 188 KiB; B200 has 227 KiB per CTA), so the four
 // radix passes and the compaction sweep never go back to HBM: the kernel reads each score
 // exactly once. Longer sequences fall back to re-reading global memory (L2 resident).
 // Compaction uses ballots and a fixed scan order: no atomics decide an output slot.
 #include "common.cuh"
 #include "topk_core.cuh"
 
-constexpr int TK_SMEM_KEYS = 56 * 1024;
+constexpr int TK_SMEM_KEYS = 47 * 1024;   // 188 KiB of keys + 34 KiB of per-warp histograms < 227 KiB
 
 __global__ void __launch_bounds__(TK_THREADS)
 index_topk_kernel(const float* __restrict__ scores, long long score_stride, const int32_t* __restrict__ seq_len,

@@ -20,6 +20,7 @@ __device__ __forceinline__ float topk_unkey(uint32_t k) {
 }
 
 struct TkShared {
+    uint32_t whist[TK_WARPS][256];   // one histogram per warp: no cross-warp atomic contention
     uint32_t hist[256];
     uint32_t wcnt[TK_WARPS];
     uint32_t pivot, need;
@@ -27,15 +28,15 @@ struct TkShared {
 
 // Four 8-bit passes, MSB first: the key of the kk-th largest entry and how many of the
 // entries tied at it the selection takes. KeyAt(i) returns the key of element i.
-// Every thread of the CTA must call it. Counting is warp-aggregated so that tie-heavy
-// arrays (ReLU zeros) do not serialise on one histogram bin.
+// Every thread of the CTA must call it. Each warp counts into its own histogram, so tie-heavy
+// arrays (ReLU zeros) never serialise the whole CTA on one bin.
 template <class KeyAt>
 __device__ __forceinline__ void tk_radix_select(KeyAt key_at, int nt, uint32_t kk, TkShared& sh, uint32_t& pivot_out,
                                                 uint32_t& need_out) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint32_t pivot = 0u, mask = 0u, need = kk;
     for (int shift = 24; shift >= 0; shift -= 8) {
-        if (tid < 256) sh.hist[tid] = 0u;
+        for (int i = tid; i < TK_WARPS * 256; i += TK_THREADS) (&sh.whist[0][0])[i] = 0u;
         __syncthreads();
         for (int base = 0; base < nt; base += TK_THREADS) {
             const int i = base + tid;
@@ -44,8 +45,15 @@ __device__ __forceinline__ void tk_radix_select(KeyAt key_at, int nt, uint32_t k
                 const uint32_t u = key_at(i);
                 if ((u & mask) == pivot) bin = (u >> shift) & 0xffu;
             }
-            const uint32_t peers = __match_any_sync(0xffffffffu, bin);
-            if (bin != 0xffffffffu && lane == __ffs(peers) - 1) atomicAdd(&sh.hist[bin], (uint32_t)__popc(peers));
+            // shared-memory atomic on this warp's own histogram: only lanes of one warp can collide
+            if (bin != 0xffffffffu) atomicAdd(&sh.whist[warp][bin], 1u);
+        }
+        __syncthreads();
+        if (tid < 256) {
+            uint32_t t = 0;
+#pragma unroll 8
+            for (int w2 = 0; w2 < TK_WARPS; ++w2) t += sh.whist[w2][tid];
+            sh.hist[tid] = t;
         }
         __syncthreads();
         if (warp == 0) {
