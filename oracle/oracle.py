@@ -258,9 +258,12 @@ class Pool:
         self.n_pages = n_pages
 
     def __del__(self):
-        if getattr(self, "_h", None):
-            lib().orc_pool_free(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None):
+                lib().orc_pool_free(self._h)
+                self._h = None
+        except Exception:   # interpreter shutdown: module globals may already be gone
+            pass
 
     def shuffle(self, seed):
         lib().orc_pool_shuffle(self._h, C.c_uint64(seed))

@@ -261,9 +261,12 @@ class PagePool:
         self.max_pages_per_seq, self.page_tokens = max_pages_per_seq, page_tokens
 
     def __del__(self):
-        if getattr(self, "_h", None):
-            lib().rivoli_pagepool_destroy(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None):
+                lib().rivoli_pagepool_destroy(self._h)
+                self._h = None
+        except Exception:   # interpreter shutdown: module globals may already be gone
+            pass
 
     def shuffle(self, seed: int) -> None:
         lib().rivoli_pagepool_shuffle(self._h, C.c_uint64(seed))

@@ -23,8 +23,8 @@
 // the k-th largest values satisfy |A_k - E_k| <= eps, so a_t > A_k + 2 eps implies
 // o_t > E_k (selected) and a_t < A_k - 2 eps implies o_t < E_k (not selected); everything
 // else is decided on exact scores. eps per sequence = max key scale * sum_h |w_h ws| ds
-// s_q[h] ||qcode_h||_2 * sqrt(hd) * 448 * 2^-15: a Cauchy-Schwarz bound on sum |q_d k_d|
-// times 2^-15 relative error. The sequential fold's own worst case is hd * 2^-24 = 2^-17
+// s_q[h] ||qcode_h||_2 * sqrt(hd) * 448 * 2^-16: a Cauchy-Schwarz bound on sum |q_d k_d|
+// times 2^-16 relative error. The sequential fold's own worst case is hd * 2^-24 = 2^-17
 // of sum |q_d k_d|; the tensor core measured 2^-21.9 on full-range random codes.
 #include "codec.cuh"
 #include "common.cuh"
@@ -44,7 +44,7 @@ constexpr int IM_TPI = 16;         // tiles per work item
 constexpr int IM_THREADS = 192;    // warps 0-3 epilogue, 4 producer, 5 MMA
 constexpr int IM_STAGE_BYTES = IM_TILE * IM_HD;   // 16 KiB
 constexpr int IM_Q_BYTES = IM_NPAD * IM_HD;       // 4 KiB
-constexpr float IM_EPS_REL = 3.0517578125e-05f;   // 2^-15
+constexpr float IM_EPS_REL = 1.52587890625e-05f;  // 2^-16
 
 struct IndexMmaArgs {
     DsaGeom g;
@@ -300,6 +300,7 @@ struct RefineArgs {
     unsigned int* stats;   // [B][2]: band size, sure-in count (may be NULL)
 };
 
+template <int EPT>
 __global__ void __launch_bounds__(TK_THREADS)
 index_select_refine_kernel(RefineArgs A) {
     extern __shared__ __align__(16) uint32_t rf_smem[];
@@ -318,52 +319,67 @@ index_select_refine_kernel(RefineArgs A) {
         if (tid == 0 && A.stats) { A.stats[b * 2] = 0; A.stats[b * 2 + 1] = (unsigned)nt; }
         return;
     }
-    // dynamic shared memory: keys[nt] | qf[hd][32] | kf[32 warps][hd] | list[RF_LIST]
+    // dynamic shared memory: keys[EPT*1024] | qf[hd][32] | kf[32 warps][hd] | list | bkey | pages
     uint32_t* keys = rf_smem;
-    float* qf = reinterpret_cast<float*>(rf_smem + ((nt + 3) & ~3));
+    float* qf = reinterpret_cast<float*>(rf_smem + EPT * TK_THREADS);
     float* kfw = qf + hd * 32;
     uint32_t* list = reinterpret_cast<uint32_t*>(kfw + TK_WARPS * hd);
+    uint32_t* bkey = list + RF_LIST;                      // exact keys of the listed tokens
+    int* s_pg = reinterpret_cast<int*>(bkey + RF_LIST);
 
-    // approximate score = (unscaled score from the tensor-core pass) * key scale of the token
-    const float* s = A.scores + (size_t)b * A.score_stride;
-    float skm = 0.0f;
-    for (int i = tid; i < nt; i += TK_THREADS) {
-        int pg = A.block_table[(size_t)b * g.max_pages_per_seq + i / P];
-        if (pg < 0 || pg >= g.n_pool_pages) pg = 0;
-        const float sk = A.index_scale[(size_t)pg * P + (i & (P - 1))];
-        keys[i] = topk_key(s[i] * sk);
-        skm = fmaxf(skm, sk);
+    const int n_pages = (nt + P - 1) / P;
+    for (int i = tid; i < n_pages; i += TK_THREADS) {
+        int pg = A.block_table[(size_t)b * g.max_pages_per_seq + i];
+        s_pg[i] = (pg < 0 || pg >= g.n_pool_pages) ? 0 : pg;
     }
-    skm = rv_warp_max(skm);
-    if (lane == 0) sh.wcnt[warp] = __float_as_uint(skm);
     for (int e = tid; e < hd * 32; e += TK_THREADS) {   // e = h * hd + d: coalesced byte reads, transposed store
         const int h = e / hd, d = e - h * hd;
         qf[d * 32 + h] = h < nh ? rv_e4m3_to_f32(A.qcodes[((size_t)b * nh + h) * hd + d]) : 0.0f;
     }
     if (tid == 0) { list_n = 0; n_band_total = 0; }
     __syncthreads();
-    float sk_max = 0.0f;
-    for (int w2 = 0; w2 < TK_WARPS; ++w2) sk_max = fmaxf(sk_max, __uint_as_float(sh.wcnt[w2]));
-    __syncthreads();
-    auto key_at = [&](int i) -> uint32_t { return keys[i]; };
 
-    uint32_t pivot, need;
-    tk_radix_select(key_at, nt, (uint32_t)kk, sh, pivot, need);
-    const float a_k = topk_unkey(pivot);
+    // approximate score = (unscaled score from the tensor-core pass) * key scale of the token;
+    // keys live in registers (element j of this thread is token tid + 1024 j) and in shared memory
+    const float* s = A.scores + (size_t)b * A.score_stride;
+    uint32_t key[EPT];
+    float skm = 0.0f;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const int i = tid + j * TK_THREADS;
+        uint32_t u = 0u;
+        if (i < nt) {
+            const float sk = A.index_scale[(size_t)s_pg[i / P] * P + (i & (P - 1))];
+            u = topk_key(s[i] * sk);
+            skm = fmaxf(skm, sk);
+        }
+        key[j] = u;
+        keys[i] = u;
+    }
+    int buf = 0;
+    const float sk_max = __uint_as_float(tk_block_max(__float_as_uint(skm), sh, buf));
     const float eps = sk_max * A.cb[b];
-    const uint32_t k_hi = topk_key(a_k + 2.0f * eps), k_lo = topk_key(a_k - 2.0f * eps);
+
+    // k-th largest approximate score, located to 20 key bits: A_k lies in [T, T + 0xfff]
+    const uint32_t T20 = tk_bisect<EPT>(key, (uint32_t)kk, 20, sh, buf);
+    const float lo_f = topk_unkey(T20) - 2.0f * eps, hi_f = topk_unkey(T20 | 0xfffu) + 2.0f * eps;
+    const uint32_t k_lo = lo_f == lo_f ? topk_key(lo_f) : 0u;
+    const uint32_t k_hi = hi_f == hi_f ? topk_key(hi_f) : 0xffffffffu;
 
     // this lane's head constants for the exact re-score (nh <= 32)
     const float my_sq = lane < nh ? A.qscales[(size_t)b * nh + lane] : 0.0f;
     const float my_wh = lane < nh ? __fmul_rn(A.w[(size_t)b * nh + lane], g.index_wscale) : 0.0f;
 
-    for (int base = 0; base < nt; base += TK_THREADS) {
-        const int i = base + tid;
+    uint32_t my_in = 0;       // tokens this thread classified as surely selected
+    int rounds = 0;           // re-score rounds flushed so far (0 or 1 in the common case)
+#pragma unroll 1
+    for (int j = 0; j < EPT; ++j) {
+        const int i = tid + j * TK_THREADS;
         bool band = false;
         if (i < nt) {
             const uint32_t u = keys[i];
-            if (u > k_hi) keys[i] = 0xffffffffu;
-            else if (u < k_lo) keys[i] = 0u;
+            if (u > k_hi) { keys[i] = 0xffffffffu; ++my_in; }   // surely selected
+            else if (u < k_lo) keys[i] = 0u;                      // surely not
             else band = true;
         }
         const uint32_t mb = __ballot_sync(0xffffffffu, band);
@@ -373,23 +389,29 @@ index_select_refine_kernel(RefineArgs A) {
         if (band) list[wbase + __popc(mb & ((1u << lane) - 1u))] = (uint32_t)i;
         __syncthreads();
         const uint32_t ln = list_n;
-        if (ln > RF_LIST - TK_THREADS || base + TK_THREADS >= nt) {
-            // exact re-score of the listed tokens: one warp per token, lane = head
-            for (uint32_t j = warp; j < ln; j += TK_WARPS) {
-                const int t = (int)list[j];
-                int pg = A.block_table[(size_t)b * g.max_pages_per_seq + t / P];
-                if (pg < 0 || pg >= g.n_pool_pages) pg = 0;
-                const size_t r = (size_t)pg * P + (t & (P - 1));
+        if (ln > RF_LIST - TK_THREADS || j == EPT - 1) {
+            // exact re-score of the listed tokens: one warp per token, lane = head; the code dot
+            // is the sequential f32 fold of rivoli_index_score_paged, heads fold ascending
+            for (uint32_t q2 = warp; q2 < ln; q2 += TK_WARPS) {
+                const int t = (int)list[q2];
+                const size_t r = (size_t)s_pg[t / P] * P + (t & (P - 1));
                 float* kf = kfw + warp * hd;
                 for (int d4 = lane; d4 < hd / 4; d4 += 32) {
                     const uint32_t cw = *reinterpret_cast<const uint32_t*>(A.index_pool + r * hd + d4 * 4);
                     const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw >> 16));
-                    kf[d4 * 4 + 0] = x.x; kf[d4 * 4 + 1] = x.y; kf[d4 * 4 + 2] = y.x; kf[d4 * 4 + 3] = y.y;
+                    *reinterpret_cast<float4*>(kf + d4 * 4) = make_float4(x.x, x.y, y.x, y.y);
                 }
                 const float sk = A.index_scale[r];
                 __syncwarp();
                 float cd = 0.0f;
-                for (int d = 0; d < hd; ++d) cd = fmaf(qf[d * 32 + lane], kf[d], cd);
+#pragma unroll 4
+                for (int d = 0; d < hd; d += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(kf + d);   // broadcast read
+                    cd = fmaf(qf[(d + 0) * 32 + lane], k4.x, cd);
+                    cd = fmaf(qf[(d + 1) * 32 + lane], k4.y, cd);
+                    cd = fmaf(qf[(d + 2) * 32 + lane], k4.z, cd);
+                    cd = fmaf(qf[(d + 3) * 32 + lane], k4.w, cd);
+                }
                 const float dot = __fmul_rn(__fmul_rn(cd, my_sq), sk);
                 float rr = __fmul_rn(dot, g.index_dscale);
                 rr = rr > 0.0f ? rr : 0.0f;
@@ -400,16 +422,52 @@ index_select_refine_kernel(RefineArgs A) {
                     uint32_t ku = topk_key(acc);
                     ku = ku == 0xffffffffu ? 0xfffffffeu : (ku == 0u ? 1u : ku);
                     keys[t] = ku;
+                    bkey[q2] = ku;
                 }
                 __syncwarp();
             }
             __syncthreads();
-            if (tid == 0) { n_band_total += ln; list_n = 0; }
-            __syncthreads();
+            if (j != EPT - 1) {   // an early flush: the list does not hold the whole band any more
+                ++rounds;
+                if (tid == 0) { n_band_total += ln; list_n = 0; }
+                __syncthreads();
+            }
         }
     }
-    // final exact selection over: sure-in = max key, band = exact keys, sure-out = 0
-    tk_radix_select(key_at, nt, (uint32_t)kk, sh, pivot, need);
+    const uint32_t n_band = list_n;           // tokens of the LAST round (all of them if rounds == 0)
+    if (rounds == 0) {
+        // Common case: the whole band sits in list/bkey. Rank each band token among the band by
+        // (exact key descending, index ascending); the selection takes the (kk - n_in) best.
+        const uint32_t n_in = tk_block_sum(my_in, sh, buf);
+        const uint32_t take = (uint32_t)kk - n_in;   // >= 1: at most kk - 1 tokens lie above the band
+        for (uint32_t q2 = warp; q2 < n_band; q2 += TK_WARPS) {
+            const uint32_t kq = bkey[q2], tq = list[q2];
+            uint32_t c = 0;
+            for (uint32_t j2 = lane; j2 < n_band; j2 += 32) {
+                const uint32_t kj = bkey[j2];
+                c += (kj > kq || (kj == kq && list[j2] < tq)) ? 1u : 0u;
+            }
+            c = __reduce_add_sync(0xffffffffu, c);
+            if (lane == 0) keys[tq] = c < take ? 0xffffffffu : 0u;
+        }
+        __syncthreads();
+        auto key_at = [&](int i) -> uint32_t { return keys[i]; };
+        tk_compact(key_at, nt, (uint32_t)kk, 0xfffffffeu, 0u, sh, out);
+        if (tid == 0 && A.stats) { A.stats[b * 2] = n_band; A.stats[b * 2 + 1] = n_in; }
+        return;
+    }
+    // Rare case (tie-dominated scores): the band did not fit one list. Exact selection over the
+    // whole key array: sure-in = max key, band = exact keys, sure-out = 0.
+    if (tid == 0) n_band_total += n_band;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const int i = tid + j * TK_THREADS;
+        key[j] = i < nt ? keys[i] : 0u;
+    }
+    const uint32_t pivot = tk_bisect<EPT>(key, (uint32_t)kk, 32, sh, buf);
+    const uint32_t need = (uint32_t)kk - tk_count_gt<EPT>(key, pivot, sh, buf);
+    __syncthreads();
+    auto key_at = [&](int i) -> uint32_t { return keys[i]; };
     tk_compact(key_at, nt, (uint32_t)kk, pivot, need, sh, out);
     if (tid == 0 && A.stats) { A.stats[b * 2] = n_band_total; A.stats[b * 2 + 1] = 0; }
 }
@@ -508,9 +566,19 @@ RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index
 
     RefineArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb, s.skmax,
                   index_pool, index_scale, block_table, rows, n_sel, g->top_k, s.stats};
-    const size_t smem2 = ((size_t)((score_stride + 3) & ~3) + (size_t)hd * 32 + (size_t)TK_WARPS * hd + RF_LIST) * 4;
-    cudaFuncSetAttribute(index_select_refine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-    index_select_refine_kernel<<<B, TK_THREADS, smem2, st>>>(ra);
+    const int n_pages_max = (score_stride + g->page_tokens - 1) / g->page_tokens;
+#define RV_REFINE(EPT)                                                                                            \
+    do {                                                                                                          \
+        const size_t smem2 = ((size_t)(EPT) * TK_THREADS + (size_t)hd * 32 + (size_t)TK_WARPS * hd + 2 * RF_LIST +\
+                              (size_t)n_pages_max) * 4;                                                           \
+        cudaFuncSetAttribute(index_select_refine_kernel<EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                             (int)smem2);                                                                         \
+        index_select_refine_kernel<EPT><<<B, TK_THREADS, smem2, st>>>(ra);                                        \
+    } while (0)
+    if (score_stride <= 8 * TK_THREADS) RV_REFINE(8);
+    else if (score_stride <= 16 * TK_THREADS) RV_REFINE(16);
+    else RV_REFINE(32);
+#undef RV_REFINE
     return rv_launch_status();
 }
 

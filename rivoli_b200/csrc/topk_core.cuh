@@ -23,8 +23,59 @@ struct TkShared {
     uint32_t whist[TK_WARPS][256];   // one histogram per warp: no cross-warp atomic contention
     uint32_t hist[256];
     uint32_t wcnt[TK_WARPS];
+    uint32_t red[2][TK_WARPS];       // double-buffered block reductions (tk_block_sum)
     uint32_t pivot, need;
 };
+
+// Block-wide sum with ONE barrier per call: per-warp partials go to red[buf], every warp then
+// re-reduces the 32 partials. `buf` alternates between calls, which is what makes the single
+// barrier sufficient (a warp can be at most one call ahead of the slowest one).
+__device__ __forceinline__ uint32_t tk_block_sum(uint32_t v, TkShared& sh, int& buf) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = __reduce_add_sync(0xffffffffu, v);
+    if (lane == 0) sh.red[buf][warp] = v;
+    __syncthreads();
+    const uint32_t t = __reduce_add_sync(0xffffffffu, sh.red[buf][lane]);
+    buf ^= 1;
+    return t;
+}
+
+__device__ __forceinline__ uint32_t tk_block_max(uint32_t v, TkShared& sh, int& buf) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = __reduce_max_sync(0xffffffffu, v);
+    if (lane == 0) sh.red[buf][warp] = v;
+    __syncthreads();
+    const uint32_t t = __reduce_max_sync(0xffffffffu, sh.red[buf][lane]);
+    buf ^= 1;
+    return t;
+}
+
+// k-th largest key by bisection on the key bits, MSB first, over keys held in REGISTERS
+// (element j of thread t is index t + j * 1024; slots past the end hold 0 and never count).
+// After `nbits` steps the result T has its low (32 - nbits) bits clear and satisfies
+//   #(key >= T) >= kk   and   #(key >= T + 2^(32-nbits)) < kk   (or that sum overflows),
+// so with nbits = 32 T is exactly the kk-th largest key. No atomics, no data-dependent cost:
+// tie-dominated arrays take the same time as random ones.
+template <int EPT>
+__device__ __forceinline__ uint32_t tk_bisect(const uint32_t (&key)[EPT], uint32_t kk, int nbits, TkShared& sh, int& buf) {
+    uint32_t T = 0u;
+    for (int bit = 31; bit >= 32 - nbits; --bit) {
+        const uint32_t cand = T | (1u << bit);
+        uint32_t c = 0;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) c += key[j] >= cand ? 1u : 0u;
+        if (tk_block_sum(c, sh, buf) >= kk) T = cand;
+    }
+    return T;
+}
+
+template <int EPT>
+__device__ __forceinline__ uint32_t tk_count_gt(const uint32_t (&key)[EPT], uint32_t T, TkShared& sh, int& buf) {
+    uint32_t c = 0;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) c += key[j] > T ? 1u : 0u;
+    return tk_block_sum(c, sh, buf);
+}
 
 // Four 8-bit passes, MSB first: the key of the kk-th largest entry and how many of the
 // entries tied at it the selection takes. KeyAt(i) returns the key of element i.
@@ -101,13 +152,10 @@ __device__ __forceinline__ void tk_compact(KeyAt key_at, int nt, uint32_t kk, ui
         const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
         if (lane == 0) sh.wcnt[warp] = (uint32_t)__popc(mg) | ((uint32_t)__popc(me) << 16);
         __syncthreads();
-        uint32_t pre = 0u, tot = 0u;
-#pragma unroll 8
-        for (int w2 = 0; w2 < TK_WARPS; ++w2) {
-            const uint32_t c = sh.wcnt[w2];
-            if (w2 < warp) pre += c;
-            tot += c;
-        }
+        // prefix over the 32 warp counts: lane w holds warp w's packed count
+        const uint32_t cw = sh.wcnt[lane];
+        const uint32_t pre = __reduce_add_sync(0xffffffffu, lane < warp ? cw : 0u);
+        const uint32_t tot = __reduce_add_sync(0xffffffffu, cw);
         const uint32_t lt = (1u << lane) - 1u;
         const uint32_t g = base_gt + (pre & 0xffffu) + (uint32_t)__popc(mg & lt);
         const uint32_t e = base_eq + (pre >> 16) + (uint32_t)__popc(me & lt);
