@@ -84,7 +84,7 @@ int rivoli_device_sync(void);
  *
  * Pool row r = page * page_tokens + slot:
  *   latent_pool  u8  [n_pool_pages * page_tokens][kv_lora + rope_dim]  e4m3 c_kv then k_rope
- *   latent_scale f32 [n_pool_pages * page_tokens][2]                   s_c, s_r (absmax/448, 1 if 0)
+ *   latent_scale f32 [n_pool_pages * page_tokens]                      absmax over the row / 448 (1 if 0)
  *   index_pool   u8  [n_pool_pages * page_tokens][index_dim]           e4m3 indexer key
  *   index_scale  f32 [n_pool_pages * page_tokens]
  *   block_table  i32 [B][max_pages_per_seq]    page id of logical page j of sequence b
@@ -112,7 +112,8 @@ typedef struct DsaGeom {
 /* Batched form of rivoli_append_kv + rivoli_index_append (fwd.hip:51-71, indexer.hip:54-58)
  * on the paged fp8 pool. Row i (of n_rows) belongs to sequence row_seq[i] (NULL = i) and
  * is written at token position row_pos[i]. latent bf16 [n_rows][kv_lora+rope_dim],
- * index_key bf16 [n_rows][index_dim]. Three per-token absmax scales (c_kv, k_rope, key).
+ * index_key bf16 [n_rows][index_dim]. One absmax scale per token for the latent row (c_kv and
+ * k_rope share it) and one for the indexer key.
  * Guards: 1001 n_rows<=0 / NULL; 1004/1005 geometry. A block_table entry outside the pool
  * makes the kernel skip that row and raise bit 0 of *status (device i32, may be NULL). */
 int rivoli_kv_append_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,
@@ -177,6 +178,14 @@ int rivoli_mla_attend_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint
                                  const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
                                  uint16_t* out, float* out_m, float* out_lse, void* scratch,
                                  void* stream);
+
+/* 1 when rivoli_mla_attend_paged_bf16 takes the tensor-core kernel for this geometry
+ * (n_heads 64, kv_lora 512, rope_dim 64, scratch given); it then returns in out_m a softmax
+ * reference point m <= lse rather than the exact maximum (merging needs only out and lse). */
+int rivoli_mla_attend_paged_uses_mma(const DsaGeom* g);
+/* Synchronises `stream`; 1008 if a bounded device-side wait of the last tensor-core
+ * attention call on `scratch` gave up (output undefined), else 0. */
+int rivoli_mla_attend_paged_status(const DsaGeom* g, void* scratch, void* stream);
 
 /* Merge G shards' normalised partials (attn.hip:241-273 with (m_s, l_s) = (lse_g, 1)):
  * weight_g = exp(lse_g - max lse), ascending g. part_out bf16 [G][n_vec][kvl],

@@ -345,7 +345,7 @@ ORC_API void orc_mla_attend_partial(const float* qabs, const float* qrope, const
  *
  * Pool row r = page * P + slot:
  *   latent_pool  u8  [rows][kvl + rope]   c_kv codes then k_rope codes
- *   latent_scale f32 [rows][2]            s_c, s_r
+ *   latent_scale f32 [rows]               one absmax scale over all kv_lora + rope values
  *   index_pool   u8  [rows][hd]
  *   index_scale  f32 [rows]
  *   block_table  i32 [B][max_pages]
@@ -377,9 +377,7 @@ ORC_API int orc_kv_append_paged(const orc_geom* g, const uint16_t* latent, const
         int page = block_table[(size_t)seq * g->max_pages_per_seq + pos / P];
         if (page < 0 || page >= g->n_pool_pages) return 1005;
         size_t r = (size_t)page * P + pos % P;
-        quant_row(latent + (size_t)i * w, g->kv_lora, latent_pool + r * w, latent_scale + r * 2);
-        quant_row(latent + (size_t)i * w + g->kv_lora, g->rope_dim, latent_pool + r * w + g->kv_lora,
-                  latent_scale + r * 2 + 1);
+        quant_row(latent + (size_t)i * w, w, latent_pool + r * w, latent_scale + r);
         quant_row(index_key + (size_t)i * g->index_dim, g->index_dim,
                   index_pool + r * g->index_dim, index_scale + r);
     }
@@ -456,9 +454,8 @@ ORC_API void orc_mla_attend_paged(const orc_geom* g, const uint16_t* q, const ui
             int t = rows ? (int)rows[(size_t)b * row_stride + j] : j;
             int page = block_table[(size_t)b * g->max_pages_per_seq + t / P];
             size_t r = (size_t)page * P + t % P;
-            float sc = latent_scale[r * 2], sr = latent_scale[r * 2 + 1];
-            for (int i = 0; i < kvl; ++i) lat[(size_t)j * w + i] = lut[latent_pool[r * w + i]] * sc;
-            for (int d = 0; d < rope; ++d) lat[(size_t)j * w + kvl + d] = lut[latent_pool[r * w + kvl + d]] * sr;
+            float sc = latent_scale[r];
+            for (int i = 0; i < w; ++i) lat[(size_t)j * w + i] = lut[latent_pool[r * w + i]] * sc;
         }
 #pragma omp parallel for schedule(static)
         for (int head = 0; head < H; ++head) {

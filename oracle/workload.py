@@ -53,7 +53,7 @@ class State:
         self.block_table = self.pool.block_table()
         rows = n_pool * P
         self.latent_pool = np.zeros(rows * W, np.uint8)
-        self.latent_scale = np.zeros(rows * 2, np.float32)
+        self.latent_scale = np.zeros(rows, np.float32)
         self.index_pool = np.zeros(rows * index_dim, np.uint8)
         self.index_scale = np.zeros(rows, np.float32)
         # history: every token before the one appended this step
@@ -99,3 +99,22 @@ def attend_close(got_bf16_bits, want_f32, rel=2e-2, abs_=1e-3):
     err = np.abs(got.reshape(want.shape) - want)
     tol = rel * np.abs(want) + abs_
     return bool((err <= tol).all()), float((err / tol).max())
+
+
+def attend_close_ref(got_bf16_bits, want_f32, rel=2e-2, abs_=1e-3):
+    """The reference's own tolerance form (crates/engine/tests/common/scoring.rs:191-194):
+    max|got - want| <= rel * max|want| + abs, per sequence. Returns (ok, worst err/tol,
+    worst rms(err)/rms(want))."""
+    got = orc.bf16_to_f32(np.asarray(got_bf16_bits, dtype=np.uint16)).astype(np.float64)
+    want = np.asarray(want_f32, dtype=np.float64)
+    got = got.reshape(want.shape)
+    ok, worst, worst_rms = True, 0.0, 0.0
+    for b in range(want.shape[0]):
+        err = np.abs(got[b] - want[b])
+        tol = rel * np.abs(want[b]).max() + abs_
+        ok &= bool(err.max() <= tol)
+        worst = max(worst, float(err.max() / tol))
+        r = float(np.sqrt((want[b] ** 2).mean()))
+        if r > 0:
+            worst_rms = max(worst_rms, float(np.sqrt((err ** 2).mean())) / r)
+    return ok, worst, worst_rms

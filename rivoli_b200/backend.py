@@ -218,6 +218,16 @@ def attend_paged_scratch_bytes(g: DsaGeom, B: int) -> int:
     return int(lib().rivoli_mla_attend_paged_scratch_bytes(C.byref(g), C.c_int(B)))
 
 
+def attend_paged_uses_mma(g: DsaGeom) -> bool:
+    return bool(lib().rivoli_mla_attend_paged_uses_mma(C.byref(g)))
+
+
+def attend_paged_status(g: DsaGeom, scratch, stream=None) -> None:
+    """Synchronises; raises BackendError(1008) if the tensor-core attention gave up on a wait."""
+    ensure_status(lib().rivoli_mla_attend_paged_status(C.byref(g), _ptr(scratch), _stream(stream)),
+                  "mla_attend_paged_status")
+
+
 def attend_simt_scratch_bytes(g: DsaGeom, B: int) -> int:
     return int(lib().rivoli_attend_simt_scratch_bytes(C.byref(g), C.c_int(B)))
 

@@ -11,8 +11,33 @@ extern "C" int rivoli_attend_simt_paged_bf16(const DsaGeom* g, const uint16_t* q
                                              int B, uint16_t* out, float* out_m, float* out_lse,
                                              void* scratch, void* stream);
 
+extern "C" bool rivoli_attend_mma_supported(const DsaGeom* g);
+extern "C" size_t rivoli_attend_mma_scratch_bytes(const DsaGeom* g, int B);
+extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
+                                            const float* latent_scale, const int32_t* block_table,
+                                            const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
+                                            uint16_t* out, float* out_m, float* out_lse, void* scratch,
+                                            void* stream);
+extern "C" int rivoli_attend_mma_status(void* scratch, void* stream);
+
 RIVOLI_API size_t rivoli_mla_attend_paged_scratch_bytes(const DsaGeom* g, int B) {
-    return rivoli_attend_simt_scratch_bytes(g, B);
+    if (!g || B <= 0) return 0;
+    const size_t a = rivoli_attend_simt_scratch_bytes(g, B);
+    const size_t m = rivoli_attend_mma_supported(g) ? rivoli_attend_mma_scratch_bytes(g, B) : 0;
+    return a > m ? a : m;
+}
+
+// 1 when rivoli_mla_attend_paged_bf16 runs on the tensor cores for this geometry (given scratch).
+RIVOLI_API int rivoli_mla_attend_paged_uses_mma(const DsaGeom* g) {
+    return (g && rv_check_geom(g) == 0 && rivoli_attend_mma_supported(g)) ? 1 : 0;
+}
+
+// Synchronises `stream`; 1008 if a bounded device-side wait of the last tensor-core attention
+// call on this scratch gave up (its output is then undefined), else 0.
+RIVOLI_API int rivoli_mla_attend_paged_status(const DsaGeom* g, void* scratch, void* stream) {
+    if (!g || !scratch) return 1001;
+    if (!rivoli_attend_mma_supported(g)) return 0;
+    return rivoli_attend_mma_status(scratch, stream);
 }
 
 RIVOLI_API int rivoli_mla_attend_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
@@ -20,6 +45,14 @@ RIVOLI_API int rivoli_mla_attend_paged_bf16(const DsaGeom* g, const uint16_t* q,
                                             const uint32_t* rows, int row_stride, const int32_t* n_rows,
                                             int B, uint16_t* out, float* out_m, float* out_lse,
                                             void* scratch, void* stream) {
+    if (int e = rv_check_geom(g)) return e;
+    if (B <= 0 || !q || !latent_pool || !latent_scale || !block_table || !n_rows || !out) return 1001;
+    if (rows && row_stride <= 0) return 1001;
+    // Tensor-core kernel for the model geometry (64 heads, 512 + 64 dims); it needs the scratch
+    // for its fp8 q terms. Everything else runs on the CUDA-core kernel.
+    if (scratch && rivoli_attend_mma_supported(g))
+        return rivoli_attend_mma_paged_bf16(g, q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
+                                            B, out, out_m, out_lse, scratch, stream);
     return rivoli_attend_simt_paged_bf16(g, q, latent_pool, latent_scale, block_table, rows, row_stride,
                                          n_rows, B, out, out_m, out_lse, scratch, stream);
 }

@@ -72,14 +72,11 @@ RIVOLI_API int rivoli_index_append(const float* k, unsigned short* kcache, int p
 
 // ------------------------------------------------------------------------------------------
 // Paged layout. One warp per token row; 4 rows per CTA.
-//   c_kv  (kv_lora <= 512): lane owns 16 contiguous values -> one 16-byte code store.
-//   k_rope (<= 128):        lanes own 4 contiguous values  -> one 4-byte store.
-//   key   (index_dim<=512): lane owns 16 contiguous values -> one 16-byte store.
-// A lane whose slice lies past the vector's end contributes 0 to the absmax and stores
-// nothing, so any width that is a multiple of 16 (4 for rope) works.
+//   latent row (c_kv | k_rope, <= 1024 values, one scale): lane owns two 16-value chunks.
+//   key (index_dim <= 512, one scale):                      lane owns one 16-value chunk.
+// Every store is one 16-byte vector. A lane whose chunk lies past the vector's end
+// contributes 0 to the absmax and stores nothing, so any multiple of 16 works.
 // ------------------------------------------------------------------------------------------
-struct Bf16x8 { uint4 v; };
-
 __device__ __forceinline__ void unpack8(const uint4& p, float* f) {
     const uint32_t w[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
@@ -121,23 +118,42 @@ __device__ __forceinline__ float quant_vec16(const uint16_t* __restrict__ src, i
     return scl;
 }
 
-// Same with 4 values per lane (n % 4 == 0, n <= 128).
-__device__ __forceinline__ float quant_vec4(const uint16_t* __restrict__ src, int n, uint8_t* __restrict__ dst,
-                                            int lane) {
-    float f[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool act = lane * 4 < n;
-    if (act) {
-        const uint2 p = *reinterpret_cast<const uint2*>(src + lane * 4);
-        f[0] = __uint_as_float(p.x << 16); f[1] = __uint_as_float(p.x & 0xffff0000u);
-        f[2] = __uint_as_float(p.y << 16); f[3] = __uint_as_float(p.y & 0xffff0000u);
+// A row of up to 1024 bf16 values (n % 16 == 0) under ONE scale: lane owns the 16-value chunks
+// lane and lane + 32, so each store is still a single 16-byte vector.
+__device__ __forceinline__ float quant_row_wide(const uint16_t* __restrict__ src, int n, uint8_t* __restrict__ dst,
+                                                int lane) {
+    float f[2][16];
+    bool act[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        act[c] = (lane + 32 * c) * 16 < n;
+        if (act[c]) {
+            const uint4* p = reinterpret_cast<const uint4*>(src + (lane + 32 * c) * 16);
+            unpack8(p[0], f[c]);
+            unpack8(p[1], f[c] + 8);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) f[c][i] = 0.0f;
+        }
     }
-    float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+    float amax = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[c][i]));
     amax = rv_warp_max(amax);
     const float scl = rv_scale_from_amax(amax);
-    if (act) {
-        uint32_t lo = rv_f32x2_to_e4m3x2(__fdiv_rn(f[0], scl), __fdiv_rn(f[1], scl));
-        uint32_t hi = rv_f32x2_to_e4m3x2(__fdiv_rn(f[2], scl), __fdiv_rn(f[3], scl));
-        *reinterpret_cast<uint32_t*>(dst + lane * 4) = lo | (hi << 16);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        if (!act[c]) continue;
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t lo = rv_f32x2_to_e4m3x2(__fdiv_rn(f[c][4 * i], scl), __fdiv_rn(f[c][4 * i + 1], scl));
+            uint32_t hi = rv_f32x2_to_e4m3x2(__fdiv_rn(f[c][4 * i + 2], scl), __fdiv_rn(f[c][4 * i + 3], scl));
+            w[i] = lo | (hi << 16);
+        }
+        *reinterpret_cast<uint4*>(dst + (lane + 32 * c) * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     return scl;
 }
@@ -164,12 +180,11 @@ kv_append_paged_kernel(DsaGeom g, const uint16_t* __restrict__ latent, const uin
     const size_t r = (size_t)page * g.page_tokens + (pos & (g.page_tokens - 1));
     const uint16_t* src = latent + (size_t)row * w;
     uint8_t* dst = latent_pool + r * w;
-    const float s_c = quant_vec16(src, g.kv_lora, dst, lane);
-    const float s_r = quant_vec4(src + g.kv_lora, g.rope_dim, dst + g.kv_lora, lane);
+    const float s_l = quant_row_wide(src, w, dst, lane);   // c_kv and k_rope share one scale
     const float s_i = quant_vec16(index_key + (size_t)row * g.index_dim, g.index_dim,
                                   index_pool + r * g.index_dim, lane);
     if (lane == 0) {
-        *reinterpret_cast<float2*>(latent_scale + r * 2) = make_float2(s_c, s_r);
+        latent_scale[r] = s_l;
         index_scale[r] = s_i;
     }
 }
@@ -186,7 +201,7 @@ RIVOLI_API int rivoli_kv_append_paged(const DsaGeom* g, const uint16_t* latent, 
     if ((g->rope_dim % 4) != 0 || ((g->kv_lora + g->rope_dim) % 16) != 0) return 1004;
     // 16-byte vector loads/stores: rows are multiples of 16 bytes, so only the bases matter.
     if ((((uintptr_t)latent | (uintptr_t)index_key | (uintptr_t)latent_pool | (uintptr_t)index_pool) & 15) ||
-        ((uintptr_t)latent_scale & 7))
+        ((uintptr_t)latent_scale & 3))
         return 1005;
     rv_drain_error();
     kv_append_paged_kernel<<<(n_rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(

@@ -1,0 +1,538 @@
+// Absorbed MLA decode attention on the 5th-generation tensor cores, all operands fp8.
+//
+//     out_h = sum_t softmax_t((q_h . [L_t | R_t]) * scale) * L_t        (H = 64, 512 + 64 dims)
+//
+// The cache rows are e4m3 codes with one f32 scale per token, and tcgen05 kind::f8f6f4
+// takes e4m3 operands directly, so the gathered rows are consumed AS THEY LIE in HBM: no
+// dequantisation pass and half the shared memory of a 16-bit staging. The two operands that
+// are not fp8 by nature are split into two e4m3 terms each (x ~ hi + lo, relative error
+// ~2^-8, bf16-like):
+//   * q (bf16 in)  -> q_hi | q_lo stacked along N (128 "virtual heads"), per-head scales;
+//   * P (softmax)  -> p_hi, p_lo issued as two MMAs accumulating into the same columns.
+// The per-token scale folds into the softmax: with s2 = log2(e) * scale * (q.k) and
+// s2' = s2 + log2(s_tok), P' = 2^(s2' - m) = weight * s_tok, so P' x (raw V codes) is already
+// the dequantised product and P' is bounded by 2^8 whatever the scales are.
+//
+// Orientation: tokens are the MMA M dimension (128 per tile), so every instruction is a full
+// M = 128 shape:
+//   S^T[128 tok x 128 (hi|lo heads)] = K_tile[128 x 576] . Qcat^T          18 MMAs (K = 32)
+//   O^T[512 dims x 64 heads]        += V^T (the SAME shared tile, read MN-major) . P'^T
+//                                      4 blocks x 4 K-steps x {hi, lo} = 32 MMAs (N = 64)
+// TMEM (512 columns): S double buffered (2 x 128) + O^T (4 x 64).
+//
+// One CTA per (sequence, split), 9 warps: 0-3 softmax + epilogue (TMEM lanes = tokens / dims),
+// 4 MMA issue, 5-8 gather (one thread per row, 36 x 16-byte cp.async into the swizzled tile).
+// Online softmax with a LAGGING reference max: O is rescaled only when a head's tile max
+// exceeds its reference by more than 2 (log2); P' is offset by 2^6 so that it stays <= 256 < 448
+// and typical weights keep both of their e4m3 terms in the normal range.
+// All waits are bounded (tc_common.cuh).
+#include "codec.cuh"
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int AM_TILE = 128;
+constexpr int AM_H = 64, AM_KVL = 512, AM_ROPE = 64, AM_W = AM_KVL + AM_ROPE;
+constexpr int AM_THREADS = 288;
+constexpr int AM_MAX_SPLITS = 16;
+// P'' = 2^(s2' - m_ref + AM_POFF) with m_ref lagging the true maximum by at most AM_LAG, so
+// P'' <= 2^(AM_POFF + AM_LAG) = 256 < 448 while typical weights (a few binades below the maximum)
+// land where BOTH e4m3 terms are normal numbers.
+constexpr float AM_POFF = 6.0f, AM_LAG = 2.0f;
+
+// shared memory map (bytes); every operand tile is 1024-byte aligned
+constexpr int SM_K0 = 0;                 // 2 x (4 latent chunks x [128 rows][128 B]), 128-byte swizzle
+constexpr int SM_KBUF = 65536;
+constexpr int SM_ROPE = 131072;          // [128 rows][64 B], 64-byte swizzle (single buffer)
+constexpr int SM_QL = 139264;            // 4 chunks x [128 rows: hi heads 0-63, lo heads 64-127][128 B]
+constexpr int SM_QR = 204800;            // [128 rows][64 B], 64-byte swizzle
+constexpr int SM_P = 212992;             // [128 tokens][128 B = hi 64 heads | lo 64 heads], 128-byte swizzle
+constexpr int SM_SMALL = 229376;
+constexpr int SM_TOK = SM_SMALL;         // f32 [2][128] token scales
+constexpr int SM_AHI = SM_TOK + 1024;    // f32 [64] per-head q scale * softmax scale * log2(e)
+constexpr int SM_WMAX = SM_AHI + 256;    // f32 [4][64] cross-warp exchange
+constexpr int SM_MUSE = SM_WMAX + 1024;  // f32 [64] reference max every thread uses for the current tile
+constexpr int SM_FAC = SM_MUSE + 256;    // f32 [64] rescale factor of the current tile (1 = unchanged)
+constexpr int SM_BARS = SM_FAC + 256;    // mbarriers
+constexpr int SM_MISC = SM_BARS + 128;
+constexpr int SM_TOTAL = SM_MISC + 64;   // 232,384 <= 232,448
+
+struct AmBars {
+    uint64_t k_full[2], kv_empty[2], s_full[2], s_empty[2], rope_free, p_full, p_empty, pv_done;
+};
+static_assert(sizeof(AmBars) <= 128, "barrier block");
+static_assert(SM_TOTAL <= 232448, "shared memory budget");
+
+struct AttendMmaArgs {
+    const uint8_t* qcodes;   // [B][128][576]: rows 0-63 q_hi codes, 64-127 q_lo codes
+    const float* qa;         // [B][64]: s_q[h] * softmax_scale * log2(e)
+    const uint8_t* pool; const float* pscale; const int32_t* block_table;
+    const uint32_t* rows; long long row_stride; const int32_t* n_rows;
+    int page_tokens, max_pages, n_pool_pages, n_splits;
+    uint16_t* out; float* out_m; float* out_lse; float* partial;
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t sw64_chunk(uint32_t row, uint32_t chunk) { return row * 64u + ((chunk ^ ((row >> 1) & 3u)) << 4); }
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)layout << 61;   // 2 = 128-byte swizzle, 4 = 64-byte swizzle
+    return d;
+}
+
+// ---------------------------------------------------------------------------------------------
+// q -> two e4m3 terms per head. One warp per head; 18 values per lane.
+//   hi = e4m3(q / s), s = absmax / 448;  lo = e4m3((q / s - hi) * 16)   =>  q ~ s * (hi + lo / 16)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+attend_q_prepare_kernel(const uint16_t* __restrict__ q, int n_vec, float softmax_scale, uint8_t* __restrict__ qcodes,
+                        float* __restrict__ qa, int* __restrict__ err) {
+    const int v = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *err = 0;
+    if (v >= n_vec) return;
+    const int b = v / AM_H, h = v - b * AM_H;
+    const uint16_t* src = q + (size_t)v * AM_W;
+    float f[18];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 18; ++i) { f[i] = rv_bf16_to_f32(src[lane + 32 * i]); amax = fmaxf(amax, fabsf(f[i])); }
+    amax = rv_warp_max(amax);
+    const float s = amax > 0.0f ? amax / 448.0f : 1.0f;
+    const float inv = 1.0f / s;
+    uint8_t* hi = qcodes + ((size_t)b * 128 + h) * AM_W;
+    uint8_t* lo = qcodes + ((size_t)b * 128 + 64 + h) * AM_W;
+#pragma unroll
+    for (int i = 0; i < 18; ++i) {
+        const float x = f[i] * inv;
+        uint16_t c;
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(0.0f), "f"(x));
+        const float xh = rv_e4m3x2_to_f32x2(c).x;
+        uint16_t c2;
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c2) : "f"(0.0f), "f"((x - xh) * 16.0f));
+        hi[lane + 32 * i] = (uint8_t)(c & 0xff);
+        lo[lane + 32 * i] = (uint8_t)(c2 & 0xff);
+    }
+    if (lane == 0) qa[v] = s * softmax_scale * 1.4426950408889634f;
+}
+
+// ---------------------------------------------------------------------------------------------
+// main kernel
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(AM_THREADS, 1)
+attend_mma_kernel(AttendMmaArgs A) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    AmBars& bars = *reinterpret_cast<AmBars*>(smem + SM_BARS);
+    float* s_tok = reinterpret_cast<float*>(smem + SM_TOK);
+    float* s_ahi = reinterpret_cast<float*>(smem + SM_AHI);
+    float* s_wmax = reinterpret_cast<float*>(smem + SM_WMAX);
+    float* s_muse = reinterpret_cast<float*>(smem + SM_MUSE);
+    float* s_fac = reinterpret_cast<float*>(smem + SM_FAC);
+    uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + SM_MISC);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_MISC + 4);
+    volatile int* rescale_flag = reinterpret_cast<volatile int*>(smem + SM_MISC + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x, b = blockIdx.y;
+    const int P = A.page_tokens;
+
+    int nr = A.n_rows[b];
+    {
+        const long long cap = A.rows ? A.row_stride : (long long)A.max_pages * P;
+        nr = (int)max(0LL, min((long long)nr, cap));
+    }
+    const int ntiles_all = (nr + AM_TILE - 1) / AM_TILE;
+    const int tps = (ntiles_all + A.n_splits - 1) / A.n_splits;
+    const int r_begin = split * tps * AM_TILE;
+    const int r_end = min(nr, r_begin + tps * AM_TILE);
+    const int ntiles = r_end > r_begin ? (r_end - r_begin + AM_TILE - 1) / AM_TILE : 0;
+
+    if (tid == 0) {
+        tc::mbar_init(&bars.k_full[0], 128); tc::mbar_init(&bars.k_full[1], 128);
+        tc::mbar_init(&bars.kv_empty[0], 1); tc::mbar_init(&bars.kv_empty[1], 1);
+        tc::mbar_init(&bars.s_full[0], 1); tc::mbar_init(&bars.s_full[1], 1);
+        tc::mbar_init(&bars.s_empty[0], 4); tc::mbar_init(&bars.s_empty[1], 4);
+        tc::mbar_init(&bars.rope_free, 1); tc::mbar_init(&bars.p_full, 128);
+        tc::mbar_init(&bars.p_empty, 1); tc::mbar_init(&bars.pv_done, 1);
+        tc::mbar_init_fence();
+        *abort_flag = 0;
+        *rescale_flag = 0;
+    }
+    if (warp == 4) tc::tmem_alloc<512>(tmem_base_s);
+
+    // q codes -> swizzled shared tiles (generic stores, once per CTA)
+    if (ntiles > 0) {
+        const uint8_t* qc = A.qcodes + (size_t)b * 128 * AM_W;
+        for (int c = tid; c < 128 * 36; c += AM_THREADS) {
+            const int row = c / 36, j = c - row * 36;
+            const uint4 v = *reinterpret_cast<const uint4*>(qc + (size_t)row * AM_W + j * 16);
+            uint8_t* dst = j < 32 ? smem + SM_QL + (j >> 3) * 16384 + tc::sw128_chunk(row, j & 7)
+                                  : smem + SM_QR + sw64_chunk(row, j - 32);
+            *reinterpret_cast<uint4*>(dst) = v;
+        }
+        if (tid < AM_H) s_ahi[tid] = A.qa[(size_t)b * AM_H + tid];
+    }
+    tc::fence_proxy_async();
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem = *tmem_base_s;
+    const uint32_t TM_S0 = tmem, TM_O = tmem + 256;
+
+    if (warp >= 5 && ntiles > 0) {
+        // ------------------------------ gather producers: thread = row of the tile ----------------
+        const int p = tid - 160;
+        bool ok = true;
+        const uint8_t* src = nullptr;
+        float scale = 0.0f;
+        auto locate = [&](int j) {   // row pointer + scale of this thread's row in tile j
+            src = nullptr; scale = 0.0f;
+            const int ri = r_begin + j * AM_TILE + p;
+            if (j < ntiles && ri < r_end) {
+                const uint32_t t = A.rows ? A.rows[(size_t)b * A.row_stride + ri] : (uint32_t)ri;
+                const int lp = (int)(t / (uint32_t)P);
+                int pg = lp < A.max_pages ? A.block_table[(size_t)b * A.max_pages + lp] : -1;
+                if (pg >= 0 && pg < A.n_pool_pages) {
+                    const size_t r = (size_t)pg * P + (t & (uint32_t)(P - 1));
+                    src = A.pool + r * AM_W;
+                    scale = A.pscale[r];
+                }
+            }
+        };
+        locate(0);
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int kb = j & 1;
+            ok = tc::mbar_wait(&bars.kv_empty[kb], ((j >> 1) & 1) ^ 1, abort_flag, 41) &&
+                 tc::mbar_wait(&bars.rope_free, (j & 1) ^ 1, abort_flag, 42);
+            if (!ok) break;
+            uint8_t* kbuf = smem + SM_K0 + kb * SM_KBUF;
+            if (src) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    tc::cp_async16(tc::smem_u32(kbuf + (c >> 3) * 16384 + tc::sw128_chunk(p, c & 7)), src + c * 16);
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    tc::cp_async16(tc::smem_u32(smem + SM_ROPE + sw64_chunk(p, c)), src + 512 + c * 16);
+            } else {   // rows past the end must be exact zeros: 0 x (stale NaN code) would poison O
+                const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) *reinterpret_cast<uint4*>(kbuf + (c >> 3) * 16384 + tc::sw128_chunk(p, c & 7)) = z;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(smem + SM_ROPE + sw64_chunk(p, c)) = z;
+            }
+            s_tok[kb * 128 + p] = scale;
+            tc::cp_async_commit();
+            locate(j + 1);               // next tile's address chain overlaps this tile's copies
+            tc::cp_async_wait<0>();
+            tc::fence_proxy_async();
+            tc::mbar_arrive(&bars.k_full[kb]);
+        }
+    } else if (warp == 4 && ntiles > 0) {
+        // ------------------------------ MMA issuer ------------------------------------------------
+        bool ok = true;
+        const uint32_t id_qk = tc::idesc_e4m3(128, 128, 0, 0), id_pv = tc::idesc_e4m3(128, 64, 1, 1);
+        const uint32_t a_ql = tc::smem_u32(smem + SM_QL), a_qr = tc::smem_u32(smem + SM_QR);
+        const uint32_t a_rope = tc::smem_u32(smem + SM_ROPE), a_p = tc::smem_u32(smem + SM_P);
+        for (int i = 0; i <= ntiles && ok; ++i) {
+            if (i < ntiles) {   // S^T(i) = K(i) . Qcat^T
+                const int kb = i & 1;
+                ok = tc::mbar_wait(&bars.k_full[kb], (i >> 1) & 1, abort_flag, 51) &&
+                     tc::mbar_wait(&bars.s_empty[kb], ((i >> 1) & 1) ^ 1, abort_flag, 52);
+                if (!ok) break;
+                tc::tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_k = tc::smem_u32(smem + SM_K0 + kb * SM_KBUF);
+                    const uint32_t d = TM_S0 + kb * 128;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            tc::mma_f8(d, smem_desc(a_k + c * 16384 + k * 32, 16, 1024, 2),
+                                       smem_desc(a_ql + c * 16384 + k * 32, 16, 1024, 2), id_qk, (c | k) != 0);
+#pragma unroll
+                    for (int k = 0; k < 2; ++k)
+                        tc::mma_f8(d, smem_desc(a_rope + k * 32, 16, 512, 4), smem_desc(a_qr + k * 32, 16, 512, 4), id_qk, 1);
+                    tc::mma_commit(&bars.s_full[kb]);
+                    tc::mma_commit(&bars.rope_free);
+                }
+                __syncwarp();
+            }
+            if (i >= 1) {       // O^T += V(i-1)^T . P'(i-1)^T
+                const int j = i - 1, kb = j & 1;
+                ok = tc::mbar_wait(&bars.p_full, j & 1, abort_flag, 53);
+                if (!ok) break;
+                tc::tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_k = tc::smem_u32(smem + SM_K0 + kb * SM_KBUF);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)   // p_hi
+                            tc::mma_f8(TM_O + c * 64, smem_desc(a_k + c * 16384 + k * 4096, 16384, 1024, 2),
+                                       smem_desc(a_p + k * 4096, 16384, 1024, 2), id_pv, (j | k) != 0);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)   // p_lo, same accumulator
+                            tc::mma_f8(TM_O + c * 64, smem_desc(a_k + c * 16384 + k * 4096, 16384, 1024, 2),
+                                       smem_desc(a_p + 64 + k * 4096, 16384, 1024, 2), id_pv, 1);
+                    }
+                    tc::mma_commit(&bars.kv_empty[kb]);
+                    tc::mma_commit(&bars.p_empty);
+                    tc::mma_commit(&bars.pv_done);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp < 4) {
+        // ------------------------------ softmax + epilogue: thread = token / dim lane -------------
+        const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
+        float l_part[AM_H];
+#pragma unroll
+        for (int h = 0; h < AM_H; ++h) l_part[h] = 0.0f;
+        float m_ref0 = -INFINITY, m_ref1 = -INFINITY;   // warp 0: reference max of heads lane, lane + 32
+        bool ok = ntiles > 0;
+        for (int i = 0; i < ntiles && ok; ++i) {
+            const int kb = i & 1;
+            ok = tc::mbar_wait(&bars.k_full[kb], (i >> 1) & 1, abort_flag, 61) &&
+                 tc::mbar_wait(&bars.s_full[kb], (i >> 1) & 1, abort_flag, 62);
+            if (!ok) break;
+            tc::tc_fence_after();
+            const float stok = s_tok[kb * 128 + tid];
+            const bool valid = r_begin + i * AM_TILE + tid < r_end && stok > 0.0f;
+            const float c2 = valid ? log2f(stok) + AM_POFF : 0.0f;   // P'' = weight * s_tok * 2^AM_POFF
+            float s2[AM_H];
+            {
+                uint32_t rh[32], rl[32];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + half * 32, rh);
+                    tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + 64 + half * 32, rl);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int h = 0; h < 32; ++h) {
+                        const float raw = fmaf(__uint_as_float(rl[h]), 0.0625f, __uint_as_float(rh[h]));
+                        s2[half * 32 + h] = valid ? fmaf(raw, s_ahi[half * 32 + h] * stok, c2) : -INFINITY;
+                    }
+                }
+            }
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&bars.s_empty[kb]);
+
+            // per-head tile max: warp reduce, then warp 0 folds the four warps and decides
+            {
+                float mine0 = -INFINITY, mine1 = -INFINITY;
+#pragma unroll
+                for (int h = 0; h < AM_H; ++h) {
+                    float mx;
+                    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(mx) : "f"(s2[h]));
+                    if ((h & 31) == lane) { if (h < 32) mine0 = mx; else mine1 = mx; }
+                }
+                s_wmax[warp * 64 + lane] = mine0;
+                s_wmax[warp * 64 + 32 + lane] = mine1;
+            }
+            tc::named_barrier(1, 128);
+            if (warp == 0) {
+                int need = 0;
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int h = lane + 32 * hh;
+                    const float tm = fmaxf(fmaxf(s_wmax[h], s_wmax[64 + h]), fmaxf(s_wmax[128 + h], s_wmax[192 + h]));
+                    float& mr = hh ? m_ref1 : m_ref0;
+                    float fac = 1.0f;
+                    if (mr == -INFINITY) { if (tm > -INFINITY) mr = tm; }          // first live tile of this head
+                    else if (tm > mr + AM_LAG) { fac = exp2f(mr - tm); mr = tm; need = 1; }
+                    s_muse[h] = mr;            // reference every thread uses for this tile
+                    s_fac[h] = fac;            // O / l rescale factor (1 when unchanged)
+                }
+                need = __any_sync(0xffffffffu, need);
+                if (lane == 0) *rescale_flag = need;
+            }
+            tc::named_barrier(1, 128);
+            if (*rescale_flag) {
+                // rare: bring O^T and l to the new reference. PV(i-1) must have landed first.
+                if (i >= 1) { ok = tc::mbar_wait(&bars.pv_done, (i - 1) & 1, abort_flag, 63); if (!ok) break; }
+                tc::tc_fence_after();
+                if (i >= 1) {
+                    uint32_t r[32];
+#pragma unroll 1
+                    for (int cc = 0; cc < 8; ++cc) {   // 4 blocks x 2 halves of 32 head columns
+                        tc::tmem_ld32(TM_O + lane_base + cc * 32, r);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int h = 0; h < 32; ++h) r[h] = __float_as_uint(__uint_as_float(r[h]) * s_fac[(cc & 1) * 32 + h]);
+                        tc::tmem_st32(TM_O + lane_base + cc * 32, r);
+                    }
+                    tc::tmem_st_wait();
+                }
+#pragma unroll
+                for (int h = 0; h < AM_H; ++h) l_part[h] *= s_fac[h];
+                tc::tc_fence_before();
+            }
+            // P' = 2^(s2' - m) = weight * s_tok, two e4m3 terms; l accumulates the plain weight
+            const float inv_tok = valid ? 1.0f / stok : 0.0f;
+            uint32_t hi_w[16], lo_w[16];
+#pragma unroll
+            for (int h = 0; h < AM_H; h += 2) {
+                const float p0 = valid ? exp2f(s2[h] - s_muse[h]) : 0.0f, p1 = valid ? exp2f(s2[h + 1] - s_muse[h + 1]) : 0.0f;   // s2 carries + AM_POFF
+                uint16_t ch, cl;
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(ch) : "f"(p1), "f"(p0));
+                const float2 hf = rv_e4m3x2_to_f32x2(ch);
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(cl) : "f"(p1 - hf.y), "f"(p0 - hf.x));
+                l_part[h] = fmaf(p0, inv_tok, l_part[h]);
+                l_part[h + 1] = fmaf(p1, inv_tok, l_part[h + 1]);
+                if ((h & 2) == 0) { hi_w[h >> 2] = ch; lo_w[h >> 2] = cl; }
+                else { hi_w[h >> 2] |= (uint32_t)ch << 16; lo_w[h >> 2] |= (uint32_t)cl << 16; }
+            }
+            ok = tc::mbar_wait(&bars.p_empty, (i & 1) ^ 1, abort_flag, 64);
+            if (!ok) break;
+            {
+                uint8_t* prow = smem + SM_P;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(tid, c)) =
+                        make_uint4(hi_w[4 * c], hi_w[4 * c + 1], hi_w[4 * c + 2], hi_w[4 * c + 3]);
+                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(tid, 4 + c)) =
+                        make_uint4(lo_w[4 * c], lo_w[4 * c + 1], lo_w[4 * c + 2], lo_w[4 * c + 3]);
+                }
+            }
+            tc::fence_proxy_async();
+            tc::mbar_arrive(&bars.p_full);
+        }
+
+        // ---- epilogue ----
+        if (ok && ntiles > 0) ok = tc::mbar_wait(&bars.pv_done, (ntiles - 1) & 1, abort_flag, 65);
+        tc::tc_fence_after();
+        // l per head: butterfly over the 32 token lanes, then across the 4 warps through shared memory
+        tc::named_barrier(1, 128);
+        {
+            float mine0 = 0.0f, mine1 = 0.0f;
+#pragma unroll
+            for (int h = 0; h < AM_H; ++h) {
+                const float v = rv_warp_sum(l_part[h]);
+                if ((h & 31) == lane) { if (h < 32) mine0 = v; else mine1 = v; }
+            }
+            s_wmax[warp * 64 + lane] = mine0;
+            s_wmax[warp * 64 + 32 + lane] = mine1;
+        }
+        tc::named_barrier(1, 128);
+        if (warp == 0) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int h = lane + 32 * hh;
+                const float l = s_wmax[h] + s_wmax[64 + h] + s_wmax[128 + h] + s_wmax[192 + h];
+                const float mr = hh ? m_ref1 : m_ref0;
+                const float m_nat = (mr - AM_POFF) * 0.6931471805599453f;   // reference in natural-log units (l and O carry 2^AM_POFF)
+                if (A.n_splits > 1) {
+                    float* ml = A.partial + (size_t)b * A.n_splits * AM_H * (AM_KVL + 2) +
+                                (size_t)A.n_splits * AM_H * AM_KVL + ((size_t)split * AM_H + h) * 2;
+                    ml[0] = (l > 0.0f && ok) ? m_nat : -INFINITY;
+                    ml[1] = (l > 0.0f && ok) ? l : 0.0f;
+                } else {
+                    if (A.out_m) A.out_m[(size_t)b * AM_H + h] = l > 0.0f ? m_nat : -INFINITY;
+                    if (A.out_lse) A.out_lse[(size_t)b * AM_H + h] = l > 0.0f ? m_nat + logf(l) : -INFINITY;
+                }
+                s_wmax[h] = l > 0.0f ? 1.0f / l : 0.0f;
+            }
+        }
+        tc::named_barrier(1, 128);
+        // O^T: this thread's TMEM lane is one latent dim of each 128-dim block; 64 head columns each
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            const int dim = c * 128 + tid;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                uint32_t r[32];
+                if (ntiles > 0 && ok) {
+                    tc::tmem_ld32(TM_O + lane_base + c * 64 + half * 32, r);
+                    tc::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int h = 0; h < 32; ++h) r[h] = 0u;
+                }
+#pragma unroll
+                for (int hq = 0; hq < 32; ++hq) {
+                    const int h = half * 32 + hq;
+                    const float v = __uint_as_float(r[hq]);
+                    if (A.n_splits > 1)
+                        A.partial[(size_t)b * A.n_splits * AM_H * (AM_KVL + 2) + ((size_t)split * AM_H + h) * AM_KVL + dim] = v;
+                    else
+                        A.out[((size_t)b * AM_H + h) * AM_KVL + dim] = rv_f32_to_bf16(v * s_wmax[h]);
+                }
+            }
+        }
+    }
+
+    tc::tc_fence_before();
+    __syncthreads();
+    if (warp == 4) tc::tmem_dealloc<512>(tmem);
+    if (tid == 0 && *abort_flag) atomicCAS(A.err, 0, *abort_flag);
+}
+
+int mma_splits(int B) {
+    if (B >= 100) return 1;
+    int n = (148 + B / 2) / B;
+    if (n > AM_MAX_SPLITS) n = AM_MAX_SPLITS;
+    return n < 1 ? 1 : n;
+}
+
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+}  // namespace
+
+extern "C" bool rivoli_attend_mma_supported(const DsaGeom* g) {
+    return g->n_heads == AM_H && g->kv_lora == AM_KVL && g->rope_dim == AM_ROPE;
+}
+
+// scratch layout: [err 256 B][qa B*64 f32][qcodes B*128*576][partials]
+extern "C" size_t rivoli_attend_mma_scratch_bytes(const DsaGeom* g, int B) {
+    const size_t part = mma_splits(B) > 1 ? (size_t)B * mma_splits(B) * AM_H * (AM_KVL + 2) * sizeof(float) : 0;
+    return 256 + align256((size_t)B * AM_H * 4) + align256((size_t)B * 128 * AM_W) + align256(part);
+}
+
+extern "C" void rivoli_attend_combine_paged(const float* partial, int H, int kvl, int n_splits, int B, uint16_t* out,
+                                            float* out_m, float* out_lse, cudaStream_t st);
+
+extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
+                                            const float* latent_scale, const int32_t* block_table,
+                                            const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
+                                            uint16_t* out, float* out_m, float* out_lse, void* scratch,
+                                            void* stream) {
+    if (!scratch) return 1001;
+    if (((uintptr_t)latent_pool | (uintptr_t)scratch) & 15) return 1005;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint8_t* sp = static_cast<uint8_t*>(scratch);
+    int* err = reinterpret_cast<int*>(sp);
+    float* qa = reinterpret_cast<float*>(sp + 256);
+    uint8_t* qcodes = sp + 256 + align256((size_t)B * AM_H * 4);
+    float* partial = reinterpret_cast<float*>(qcodes + align256((size_t)B * 128 * AM_W));
+    const int n_splits = mma_splits(B);
+
+    rv_drain_error();
+    attend_q_prepare_kernel<<<(B * AM_H + 7) / 8, 256, 0, st>>>(q, B * AM_H, g->softmax_scale, qcodes, qa, err);
+    if (int e = rv_launch_status()) return e;
+    AttendMmaArgs a{qcodes, qa, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
+                    g->page_tokens, g->max_pages_per_seq, g->n_pool_pages, n_splits,
+                    out, out_m, out_lse, n_splits > 1 ? partial : nullptr, err};
+    cudaFuncSetAttribute(attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
+    attend_mma_kernel<<<dim3(n_splits, B), AM_THREADS, SM_TOTAL, st>>>(a);
+    if (int e = rv_launch_status()) return e;
+    if (n_splits > 1) {
+        rivoli_attend_combine_paged(partial, AM_H, AM_KVL, n_splits, B, out, out_m, out_lse, st);
+        return rv_launch_status();
+    }
+    return 0;
+}
+
+// Synchronises `stream`; 1008 if a bounded device-side wait of the last call gave up.
+extern "C" int rivoli_attend_mma_status(void* scratch, void* stream) {
+    int h = 0;
+    cudaError_t e = cudaMemcpyAsync(&h, scratch, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return -(int)e;
+    return h ? 1008 : 0;
+}

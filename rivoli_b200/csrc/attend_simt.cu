@@ -5,7 +5,7 @@
 //                                   per-128 block scales, bf16 roped keys, one sequence;
 //                                   crates/backend/kernels/attn.hip:119-308).
 //   rivoli_attend_simt_paged_bf16 : the same arithmetic on the paged fp8 pool (bf16 q,
-//                                   per-token scales, fp8 roped keys), batched. This is the
+//                                   one scale per token, fp8 roped keys), batched. This is the
 //                                   f32 cross-check of the tensor-core kernel and the path
 //                                   used for geometries that kernel does not cover.
 //
@@ -40,7 +40,7 @@ attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int kvl, int rope, float scal
     const int W = kvl + rope;
     float* qs = smem;                      // [H][W]
     float* tile = smem + (size_t)H * W;    // [AT_TT][W]
-    __shared__ float tscale[AT_TT][2];
+    __shared__ float tscale[AT_TT];
     __shared__ const uint8_t* trow[AT_TT];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -91,15 +91,14 @@ attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int kvl, int rope, float scal
                 if (page < 0 || page >= pp.n_pool_pages) page = 0;  // guarded: never read outside the pool
                 const size_t r = (size_t)page * pp.page_tokens + (t & (uint32_t)(pp.page_tokens - 1));
                 trow[tid] = pp.pool + r * W;
-                tscale[tid][0] = pp.pscale[r * 2];
-                tscale[tid][1] = pp.pscale[r * 2 + 1];
+                tscale[tid] = pp.pscale[r];
             }
             __syncthreads();
             const int cpr = W / 16;  // 16-byte chunks per row
             for (int c = tid; c < tcount * cpr; c += AT_THREADS) {
                 const int row = c / cpr, ch = c - row * cpr;
                 const uint4 p = *reinterpret_cast<const uint4*>(trow[row] + ch * 16);
-                const float sc = tscale[row][ch * 16 < kvl ? 0 : 1];
+                const float sc = tscale[row];
                 const uint32_t wv[4] = {p.x, p.y, p.z, p.w};
                 float* dst = tile + (size_t)row * W + ch * 16;
 #pragma unroll
@@ -240,6 +239,12 @@ static int launch_attend_simt(const AttSlab& sp, const AttPaged& pp, int H, int 
     attend_combine_kernel<PAGED><<<dim3(H, B), 128, 0, st>>>(partial, H, kvl, n_splits, sp.clat, pp.out,
                                                               pp.out_m, pp.out_lse);
     return rv_launch_status();
+}
+
+// Combine launcher shared with the tensor-core kernel (same partial layout).
+extern "C" void rivoli_attend_combine_paged(const float* partial, int H, int kvl, int n_splits, int B, uint16_t* out,
+                                            float* out_m, float* out_lse, cudaStream_t st) {
+    attend_combine_kernel<true><<<dim3(H, B), 128, 0, st>>>(partial, H, kvl, n_splits, nullptr, out, out_m, out_lse);
 }
 
 RIVOLI_API size_t rivoli_mla_attend_scratch_floats(int H, int kvl) {

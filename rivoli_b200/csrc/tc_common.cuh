@@ -30,7 +30,7 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-constexpr int kMaxPolls = 4 * 1000 * 1000;  // ~0.1-0.2 s of polling, far beyond any legitimate wait
+constexpr int kMaxPolls = 1000 * 1000;  // far beyond any legitimate wait (microseconds); bounds a protocol bug
 
 // Returns false (and raises *abort_flag) if the phase never completes or another wait gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {

@@ -37,7 +37,7 @@ class DsaDecodeLayer:
         u8, f32, i32 = torch.uint8, torch.float32, torch.int32
         d = self.dev
         self.latent_pool = torch.zeros(rows * W, dtype=u8, device=d)
-        self.latent_scale = torch.zeros(rows * 2, dtype=f32, device=d)
+        self.latent_scale = torch.zeros(rows, dtype=f32, device=d)
         self.index_pool = torch.zeros(rows * geom.index_dim, dtype=u8, device=d)
         self.index_scale = torch.zeros(rows, dtype=f32, device=d)
         self.block_table = torch.full((n_seqs, geom.max_pages_per_seq), -1, dtype=i32, device=d)
@@ -118,6 +118,7 @@ class DsaDecodeLayer:
     def check_status(self) -> None:
         """Raise if a kernel flagged a bad block-table entry since the last check (syncs)."""
         be.index_select_status(self.g, self.B, self.score_stride, self.select_scratch)
+        be.attend_paged_status(self.g, self.scratch)
         s = int(self.status.item())
         if s:
             self.status.zero_()

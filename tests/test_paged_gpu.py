@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import oracle as orc
-from tests.helpers import State, attend_close, make_geom
+from tests.helpers import State, attend_close, attend_close_ref, make_geom
 
 pytestmark = pytest.mark.gpu
 
@@ -27,6 +27,19 @@ def dev(a):
 
 def u16(t):
     return t.cpu().view(torch.int16).numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy().view(np.uint16)
+
+
+def check_mma_attention(got_bits, want_f32, elementwise):
+    """Gate of the tensor-core attention (q and P each carried as two e4m3 terms, ~2^-9
+    relative, i.e. bf16-class): the reference's tolerance form with 2e-2 / 1e-3, an rms
+    bound of 0.5 % of rms(want), and - at 2048 attended rows and more, the BASELINE shapes -
+    the elementwise form |err| <= 2e-2 |want| + 1e-3 as well."""
+    ok, worst, rms = attend_close_ref(got_bits, want_f32)
+    assert ok, worst
+    assert rms <= 5e-3, rms
+    if elementwise:
+        ok, worst = attend_close(got_bits, want_f32)
+        assert ok, worst
 
 
 CASES = {
@@ -99,8 +112,12 @@ def test_layer_step_matches_oracle(be, case):
         fn(g, dev(st.q), d["latent_pool"], d["latent_scale"], d["block_table"], rows, g.top_k, n_sel, B, out, m,
            lse, scratch)
         be.device_sync()
-        ok, worst = attend_close(u16(out), want["out_f32"])
-        assert ok, worst
+        if fn is be.launch_attend_paged_bf16 and be.attend_paged_uses_mma(g):
+            be.attend_paged_status(g, scratch)
+            check_mma_attention(u16(out), want["out_f32"], st.seq_len.min() >= 2048)
+        else:
+            ok, worst = attend_close(u16(out), want["out_f32"])
+            assert ok, worst
         assert np.abs(lse.cpu().numpy() - want["lse"]).max() < 2e-2
         # no-scratch (single split) path
         out2 = torch.zeros_like(out)
@@ -244,3 +261,66 @@ def test_fused_select_tie_dominated(be):
         np.testing.assert_array_equal(rows, want_rows)
         if mode == "zeros":
             assert (rows[0, :2048] == np.arange(2048)).all()
+
+
+# ---- tensor-core attention (fp8 MMA, two-term q and P) against the oracle ---------------------------
+ATTEND_CASES = {
+    "sparse-2048-of-5000": dict(seed=41, B=3, ctx=[5000, 4097, 2500], top_k=2048),     # elementwise gate too
+    "ragged-tiles": dict(seed=42, B=6, ctx=[1, 127, 128, 129, 300, 1000], top_k=512),
+    "big-batch-one-split": dict(seed=43, B=100, ctx=[200] * 100, top_k=128),
+}
+
+
+@pytest.mark.parametrize("case", list(ATTEND_CASES))
+def test_mma_attention_matches_oracle(be, case):
+    c = dict(ATTEND_CASES[case])
+    st = State(c.pop("seed"), c.pop("B"), c.pop("ctx"), **c)
+    g = make_geom(be.DsaGeom, **st.geom_kw)
+    assert be.attend_paged_uses_mma(g)
+    want = st.oracle_step()
+    B = st.B
+    lp, ls, bt = dev(want["latent_pool"]), dev(want["latent_scale"]), dev(st.block_table)
+    rows, n_sel = dev(want["rows"]), dev(want["n_sel"])
+    out = torch.zeros((B, g.n_heads, g.kv_lora), dtype=torch.bfloat16, device="cuda")
+    m = torch.zeros((B, g.n_heads), dtype=torch.float32, device="cuda")
+    lse = torch.zeros((B, g.n_heads), dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(be.attend_paged_scratch_bytes(g, B), dtype=torch.uint8, device="cuda")
+    for _ in range(2):          # twice: barriers, TMEM and scratch must be reusable
+        be.launch_attend_paged_bf16(g, dev(st.q), lp, ls, bt, rows, g.top_k, n_sel, B, out, m, lse, scratch)
+        be.attend_paged_status(g, scratch)
+        check_mma_attention(u16(out), want["out_f32"], st.seq_len.min() >= 2048)
+        assert np.abs(lse.cpu().numpy() - want["lse"]).max() < 2e-2
+        assert (m.cpu().numpy() <= lse.cpu().numpy() + 1e-4).all()
+    # the CUDA-core kernel on the same inputs: both within tolerance of the oracle and close to each other
+    out2 = torch.zeros_like(out)
+    be.launch_attend_simt_paged_bf16(g, dev(st.q), lp, ls, bt, rows, g.top_k, n_sel, B, out2, None, None, None)
+    be.device_sync()
+    a, b2 = orc.bf16_to_f32(u16(out)).ravel(), orc.bf16_to_f32(u16(out2)).ravel()
+    assert np.abs(a - b2).max() <= 2e-2 * np.abs(b2).max() + 1e-3
+
+
+def test_mma_attention_dense_long_prefix(be):
+    """Dense (rows = NULL) attention over a few thousand tokens: many tiles per split, the
+    lagging reference max and the rare O rescale are exercised by a query aligned with one late key."""
+    st = State(44, 2, [3000, 2049], top_k=64)
+    g = make_geom(be.DsaGeom, **st.geom_kw)
+    want = st.oracle_step()
+    # make head 0 of sequence 0 attend sharply to a late token: its score towers over the rest
+    lat = want["latent_pool"].reshape(-1, 576)
+    P = g.page_tokens
+    t_late = 2900
+    r = st.block_table[0, t_late // P] * P + t_late % P
+    code = orc.e4m3_table()[lat[r]] * want["latent_scale"][r]
+    q = st.q.copy().reshape(2, 64, 576)
+    q[0, 0] = orc.f32_to_bf16((code / np.abs(code).max() * 6.0).astype(np.float32))
+    o, o_f32, _, lse_w = orc.mla_attend_paged(st.og, q, want["latent_pool"], want["latent_scale"], st.block_table,
+                                              None, st.seq_len, want_f32=True)
+    B = 2
+    out = torch.zeros((B, 64, 512), dtype=torch.bfloat16, device="cuda")
+    lse = torch.zeros((B, 64), dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(be.attend_paged_scratch_bytes(g, B), dtype=torch.uint8, device="cuda")
+    be.launch_attend_paged_bf16(g, dev(q), dev(want["latent_pool"]), dev(want["latent_scale"]), dev(st.block_table),
+                                None, 0, dev(st.seq_len), B, out, None, lse, scratch)
+    be.attend_paged_status(g, scratch)
+    check_mma_attention(u16(out), o_f32, True)
+    assert np.abs(lse.cpu().numpy() - lse_w).max() < 2e-2
