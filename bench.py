@@ -42,9 +42,9 @@ def algorithmic_bytes(w):
     nt, k, H, nh, hd = w["ctx"], w["top_k"], w["n_heads"], w["index_heads"], w["index_dim"]
     n_sel = min(k, nt)
     W = KV_LORA + ROPE
-    append = W * 2 + hd * 2 + 4 + W + 8 + hd + 4
+    append = W * 2 + hd * 2 + 4 + W + 4 + hd + 4
     index = nt * (hd + 4) + nh * hd * 2 + nh * 4 + n_sel * 4
-    attend = n_sel * (W + 8) + H * W * 2 + n_sel * 4 + H * KV_LORA * 2
+    attend = n_sel * (W + 4) + H * W * 2 + n_sel * 4 + H * KV_LORA * 2
     return dict(append=append, index=index, attend=attend)
 
 
