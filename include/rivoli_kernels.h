@@ -72,6 +72,17 @@ int rivoli_mla_attend(const float* qabs, const float* qrope, const unsigned char
                       int nr, int kvl, int rope, int n_blocks, float scale, float* clat,
                       float* partial);
 
+/* rivoli_mla_attend without the caller's `partial` scratch. No counterpart in the reference.
+ * For callers that cannot allocate device memory (everything already handed to their own
+ * arenas, a thread that must not block on the allocator, a host contract that forbids it):
+ * the split partials live in a fixed 2,105,344-byte array inside the library, sized for
+ * H <= 64 and kvl <= 512; larger shapes are refused with 1002. Calls nothing that allocates.
+ * The first call on a device looks the array's address up (do it before any stream
+ * capture). All calls on a device share the array: do not let two of them overlap on the GPU. */
+int rivoli_mla_attend_static(const float* qabs, const float* qrope, const unsigned char* Lc8,
+                             const float* Lscale, const unsigned short* Rc, const unsigned int* rows, int H,
+                             int nr, int kvl, int rope, int n_blocks, float scale, float* clat);
+
 /* Replaces crates/backend/kernels/attn.hip:100-103 (crates/backend/src/hip.rs:425-430). */
 size_t rivoli_mla_attend_scratch_floats(int H, int kvl);
 

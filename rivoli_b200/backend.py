@@ -144,6 +144,16 @@ def launch_attend(qabs, qrope, lc8, lscale, rc, rows, h: int, nr: int, kvl: int,
                   "mla_attend")
 
 
+def launch_attend_static(qabs, qrope, lc8, lscale, rc, rows, h: int, nr: int, kvl: int, rope: int, n_blocks: int,
+                         scale: float, clat) -> None:
+    """``launch_attend`` for callers that cannot lend device scratch: the split partials live in
+    an array built into the library (h <= 64, kvl <= 512). One call at a time per device."""
+    ensure_status(lib().rivoli_mla_attend_static(_ptr(qabs), _ptr(qrope), _ptr(lc8), _ptr(lscale), _ptr(rc),
+                                                 _ptr(rows), C.c_int(h), C.c_int(nr), C.c_int(kvl), C.c_int(rope),
+                                                 C.c_int(n_blocks), C.c_float(scale), _ptr(clat)),
+                  "mla_attend_static")
+
+
 def attend_scratch_floats(h: int, kvl: int) -> int:
     return int(lib().rivoli_mla_attend_scratch_floats(C.c_int(h), C.c_int(kvl)))
 

@@ -274,6 +274,60 @@ RIVOLI_API int rivoli_mla_attend(const float* qabs, const float* qrope, const un
     return launch_attend_simt<false>(sp, pp, H, kvl, rope, scale, nr, 1, n_splits, partial, 0);
 }
 
+// ------------------------------------------------------------------------------------------
+// rivoli_mla_attend_static: rivoli_mla_attend for callers that have no device memory to lend.
+//
+// Some users of this library are not in a position to call cudaMalloc at all: an engine that
+// carved up the whole device into its own arenas at start-up and treats any later driver
+// allocation as a bug, a decode thread that must never block on the allocator (cudaMalloc
+// and cudaFree serialise against the whole device), or a plugin host whose contract says
+// the plugin owns no device memory. For them the split-KV partials that rivoli_mla_attend
+// takes as the caller's `partial` scratch live here instead, in a fixed array inside the
+// library image. It is sized for the model geometry only (H <= 64 heads, kvl <= 512):
+// 16 splits x 64 x 514 floats = 2,105,344 bytes, which every GPU that loads this library
+// carries until the process exits.
+//
+// The array's name is only a host-side handle for the symbol, never a device address, so the
+// address is looked up once per device (with that device current) by cudaGetSymbolAddress
+// and that pointer is what the kernels receive. The FIRST call on a device performs that
+// look-up; make it before any stream capture begins on that device.
+//
+// All calls share the one array and it keeps whatever the last call left there. Nothing
+// in it has to start at zero (every split, an empty one included, stores its partial before
+// the combine reads it), but two calls that are in flight on the GPU at the same time (two
+// streams, or two host threads on one device) would overwrite each other's partials: keep
+// calls on one device ordered. Runs on the legacy default stream like rivoli_mla_attend.
+// ------------------------------------------------------------------------------------------
+constexpr int NA_MAX_H = 64, NA_MAX_KVL = 512, NA_MAX_DEVICES = 64;
+static __device__ __align__(256) float g_attend_static_partial[AT_MAX_SPLITS * NA_MAX_H * (NA_MAX_KVL + 2)];
+static float* g_attend_static_ptr[NA_MAX_DEVICES];   // per-device address of the array above (host side)
+
+RIVOLI_API int rivoli_mla_attend_static(const float* qabs, const float* qrope, const unsigned char* Lc8,
+                                        const float* Lscale, const unsigned short* Rc, const unsigned int* rows,
+                                        int H, int nr, int kvl, int rope, int n_blocks, float scale, float* clat) {
+    if (H <= 0 || nr <= 0 || kvl <= 0 || rope <= 0 || n_blocks <= 0) return 1001;
+    if (((size_t)16 * kvl + (size_t)16 * rope) * sizeof(float) > 65536) return 1002;
+    if (kvl > 512 || (kvl % 128) != 0) return 1004;
+    if (rope > 128) return 1002;
+    if (H > NA_MAX_H || kvl > NA_MAX_KVL) return 1002;   // beyond the built-in scratch: use rivoli_mla_attend
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return -(int)e;
+    if (dev < 0 || dev >= NA_MAX_DEVICES) return 1008;
+    if (!g_attend_static_ptr[dev]) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_attend_static_partial);
+        if (e != cudaSuccess) return -(int)e;
+        g_attend_static_ptr[dev] = p;
+    }
+    int n_splits = (nr + 255) / 256;                    // same plan as rivoli_mla_attend with scratch
+    if (n_splits > AT_MAX_SPLITS) n_splits = AT_MAX_SPLITS;
+    if (n_splits < 1) n_splits = 1;
+    AttSlab sp{qabs, qrope, Lc8, Lscale, Rc, rows, n_blocks, clat};
+    AttPaged pp{};
+    return launch_attend_simt<false>(sp, pp, H, kvl, rope, scale, nr, 1, n_splits, g_attend_static_ptr[dev], 0);
+}
+
 // Split count of the SIMT paged path: a pure function of the batch size.
 static int simt_paged_splits(int B) {
     int n = (2 * 148 + B - 1) / B;
