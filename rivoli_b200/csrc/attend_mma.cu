@@ -20,8 +20,9 @@
 //                                      4 blocks x 4 K-steps x {hi, lo} = 32 MMAs (N = 64)
 // TMEM (512 columns): S double buffered (2 x 128) + O^T (4 x 64).
 //
-// One CTA per (sequence, split), 9 warps: 0-3 softmax + epilogue (TMEM lanes = tokens / dims),
-// 4 MMA issue, 5-8 gather (one thread per row, 36 x 16-byte cp.async into the swizzled tile).
+// One CTA per (sequence, split), 13 warps: 0-7 softmax + epilogue (TMEM lane group = warp % 4 =
+// tokens / dims, warps 0-3 own heads 0-31 and warps 4-7 heads 32-63), 8 MMA issue, 9-12 gather
+// (one thread per row, 36 x 16-byte cp.async into the swizzled tile).
 // Online softmax with a LAGGING reference max: O is rescaled only when a head's tile max
 // exceeds its reference by more than 2 (log2); P' is offset by 2^6 so that it stays <= 256 < 448
 // and typical weights keep both of their e4m3 terms in the normal range.
@@ -34,7 +35,8 @@ namespace {
 
 constexpr int AM_TILE = 128;
 constexpr int AM_H = 64, AM_KVL = 512, AM_ROPE = 64, AM_W = AM_KVL + AM_ROPE;
-constexpr int AM_THREADS = 288;
+constexpr int AM_THREADS = 416;   // warps 0-7 softmax + epilogue, 8 MMA issue, 9-12 gather
+constexpr int AM_SOFTMAX_THREADS = 256;
 constexpr int AM_MAX_SPLITS = 16;
 // P'' = 2^(s2' - m_ref + AM_POFF) with m_ref lagging the true maximum by at most AM_LAG, so
 // P'' <= 2^(AM_POFF + AM_LAG) = 256 < 448 while typical weights (a few binades below the maximum)
@@ -156,14 +158,14 @@ attend_mma_kernel(AttendMmaArgs A) {
         tc::mbar_init(&bars.k_full[0], 128); tc::mbar_init(&bars.k_full[1], 128);
         tc::mbar_init(&bars.kv_empty[0], 1); tc::mbar_init(&bars.kv_empty[1], 1);
         tc::mbar_init(&bars.s_full[0], 1); tc::mbar_init(&bars.s_full[1], 1);
-        tc::mbar_init(&bars.s_empty[0], 4); tc::mbar_init(&bars.s_empty[1], 4);
-        tc::mbar_init(&bars.rope_free, 1); tc::mbar_init(&bars.p_full, 128);
+        tc::mbar_init(&bars.s_empty[0], 8); tc::mbar_init(&bars.s_empty[1], 8);
+        tc::mbar_init(&bars.rope_free, 1); tc::mbar_init(&bars.p_full, AM_SOFTMAX_THREADS);
         tc::mbar_init(&bars.p_empty, 1); tc::mbar_init(&bars.pv_done, 1);
         tc::mbar_init_fence();
         *abort_flag = 0;
         *rescale_flag = 0;
     }
-    if (warp == 4) tc::tmem_alloc<512>(tmem_base_s);
+    if (warp == 8) tc::tmem_alloc<512>(tmem_base_s);
 
     // q codes -> swizzled shared tiles (generic stores, once per CTA)
     if (ntiles > 0) {
@@ -184,9 +186,9 @@ attend_mma_kernel(AttendMmaArgs A) {
     const uint32_t tmem = *tmem_base_s;
     const uint32_t TM_S0 = tmem, TM_O = tmem + 256;
 
-    if (warp >= 5 && ntiles > 0) {
+    if (warp >= 9 && ntiles > 0) {
         // ------------------------------ gather producers: thread = row of the tile ----------------
-        const int p = tid - 160;
+        const int p = tid - 288;
         bool ok = true;
         const uint8_t* src = nullptr;
         float scale = 0.0f;
@@ -232,7 +234,7 @@ attend_mma_kernel(AttendMmaArgs A) {
             tc::fence_proxy_async();
             tc::mbar_arrive(&bars.k_full[kb]);
         }
-    } else if (warp == 4 && ntiles > 0) {
+    } else if (warp == 8 && ntiles > 0) {
         // ------------------------------ MMA issuer ------------------------------------------------
         bool ok = true;
         const uint32_t id_qk = tc::idesc_e4m3(128, 128, 0, 0), id_pv = tc::idesc_e4m3(128, 64, 1, 1);
@@ -287,13 +289,18 @@ attend_mma_kernel(AttendMmaArgs A) {
                 __syncwarp();
             }
         }
-    } else if (warp < 4) {
-        // ------------------------------ softmax + epilogue: thread = token / dim lane -------------
-        const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
-        float l_part[AM_H];
+    } else if (warp < 8) {
+        // ------------------------------ softmax + epilogue ---------------------------------------
+        // thread = (TMEM lane, head half): lane group q = warp % 4 -> token (or latent dim) 32 q + lane,
+        // hh = warp / 4 -> heads 32 hh .. 32 hh + 31.
+        const int q4 = warp & 3, hh = warp >> 2;
+        const int row = q4 * 32 + lane;                  // token of the tile / dim of a 128-dim block
+        const uint32_t lane_base = ((uint32_t)(q4 * 32)) << 16;
+        const int h0 = hh * 32;
+        float l_part[32];
 #pragma unroll
-        for (int h = 0; h < AM_H; ++h) l_part[h] = 0.0f;
-        float m_ref0 = -INFINITY, m_ref1 = -INFINITY;   // warp 0: reference max of heads lane, lane + 32
+        for (int h = 0; h < 32; ++h) l_part[h] = 0.0f;
+        float m_ref = -INFINITY;                          // threads tid < 64: reference max of head tid
         bool ok = ntiles > 0;
         for (int i = 0; i < ntiles && ok; ++i) {
             const int kb = i & 1;
@@ -301,58 +308,49 @@ attend_mma_kernel(AttendMmaArgs A) {
                  tc::mbar_wait(&bars.s_full[kb], (i >> 1) & 1, abort_flag, 62);
             if (!ok) break;
             tc::tc_fence_after();
-            const float stok = s_tok[kb * 128 + tid];
-            const bool valid = r_begin + i * AM_TILE + tid < r_end && stok > 0.0f;
+            const float stok = s_tok[kb * 128 + row];
+            const bool valid = r_begin + i * AM_TILE + row < r_end && stok > 0.0f;
             const float c2 = valid ? log2f(stok) + AM_POFF : 0.0f;   // P'' = weight * s_tok * 2^AM_POFF
-            float s2[AM_H];
+            float s2[32];
             {
                 uint32_t rh[32], rl[32];
+                tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + h0, rh);
+                tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + 64 + h0, rl);
+                tc::tmem_ld_wait();
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + half * 32, rh);
-                    tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + 64 + half * 32, rl);
-                    tc::tmem_ld_wait();
-#pragma unroll
-                    for (int h = 0; h < 32; ++h) {
-                        const float raw = fmaf(__uint_as_float(rl[h]), 0.0625f, __uint_as_float(rh[h]));
-                        s2[half * 32 + h] = valid ? fmaf(raw, s_ahi[half * 32 + h] * stok, c2) : -INFINITY;
-                    }
+                for (int h = 0; h < 32; ++h) {
+                    const float raw = fmaf(__uint_as_float(rl[h]), 0.0625f, __uint_as_float(rh[h]));
+                    s2[h] = valid ? fmaf(raw, s_ahi[h0 + h] * stok, c2) : -INFINITY;
                 }
             }
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&bars.s_empty[kb]);
 
-            // per-head tile max: warp reduce, then warp 0 folds the four warps and decides
+            // per-head tile max over the warp's 32 tokens, then across the 4 lane groups
             {
-                float mine0 = -INFINITY, mine1 = -INFINITY;
+                float mine = -INFINITY;
 #pragma unroll
-                for (int h = 0; h < AM_H; ++h) {
+                for (int h = 0; h < 32; ++h) {
                     float mx;
                     asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(mx) : "f"(s2[h]));
-                    if ((h & 31) == lane) { if (h < 32) mine0 = mx; else mine1 = mx; }
+                    if (h == lane) mine = mx;
                 }
-                s_wmax[warp * 64 + lane] = mine0;
-                s_wmax[warp * 64 + 32 + lane] = mine1;
+                s_wmax[q4 * 64 + h0 + lane] = mine;
             }
-            tc::named_barrier(1, 128);
-            if (warp == 0) {
+            tc::named_barrier(1, AM_SOFTMAX_THREADS);
+            if (tid < AM_H) {
+                const float tm = fmaxf(fmaxf(s_wmax[tid], s_wmax[64 + tid]), fmaxf(s_wmax[128 + tid], s_wmax[192 + tid]));
+                float fac = 1.0f;
                 int need = 0;
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const int h = lane + 32 * hh;
-                    const float tm = fmaxf(fmaxf(s_wmax[h], s_wmax[64 + h]), fmaxf(s_wmax[128 + h], s_wmax[192 + h]));
-                    float& mr = hh ? m_ref1 : m_ref0;
-                    float fac = 1.0f;
-                    if (mr == -INFINITY) { if (tm > -INFINITY) mr = tm; }          // first live tile of this head
-                    else if (tm > mr + AM_LAG) { fac = exp2f(mr - tm); mr = tm; need = 1; }
-                    s_muse[h] = mr;            // reference every thread uses for this tile
-                    s_fac[h] = fac;            // O / l rescale factor (1 when unchanged)
-                }
+                if (m_ref == -INFINITY) { if (tm > -INFINITY) m_ref = tm; }          // first live tile of this head
+                else if (tm > m_ref + AM_LAG) { fac = exp2f(m_ref - tm); m_ref = tm; need = 1; }
+                s_muse[tid] = m_ref;       // reference every thread uses for this tile
+                s_fac[tid] = fac;          // O / l rescale factor (1 when unchanged)
                 need = __any_sync(0xffffffffu, need);
-                if (lane == 0) *rescale_flag = need;
+                if (lane == 0 && need) *rescale_flag = 1;
             }
-            tc::named_barrier(1, 128);
+            tc::named_barrier(1, AM_SOFTMAX_THREADS);
             if (*rescale_flag) {
                 // rare: bring O^T and l to the new reference. PV(i-1) must have landed first.
                 if (i >= 1) { ok = tc::mbar_wait(&bars.pv_done, (i - 1) & 1, abort_flag, 63); if (!ok) break; }
@@ -360,31 +358,39 @@ attend_mma_kernel(AttendMmaArgs A) {
                 if (i >= 1) {
                     uint32_t r[32];
 #pragma unroll 1
-                    for (int cc = 0; cc < 8; ++cc) {   // 4 blocks x 2 halves of 32 head columns
-                        tc::tmem_ld32(TM_O + lane_base + cc * 32, r);
+                    for (int c = 0; c < 4; ++c) {   // this thread's dim lane, its 32 head columns of each block
+                        tc::tmem_ld32(TM_O + lane_base + c * 64 + h0, r);
                         tc::tmem_ld_wait();
 #pragma unroll
-                        for (int h = 0; h < 32; ++h) r[h] = __float_as_uint(__uint_as_float(r[h]) * s_fac[(cc & 1) * 32 + h]);
-                        tc::tmem_st32(TM_O + lane_base + cc * 32, r);
+                        for (int h = 0; h < 32; ++h) r[h] = __float_as_uint(__uint_as_float(r[h]) * s_fac[h0 + h]);
+                        tc::tmem_st32(TM_O + lane_base + c * 64 + h0, r);
                     }
                     tc::tmem_st_wait();
                 }
 #pragma unroll
-                for (int h = 0; h < AM_H; ++h) l_part[h] *= s_fac[h];
+                for (int h = 0; h < 32; ++h) l_part[h] *= s_fac[h0 + h];
                 tc::tc_fence_before();
+                tc::named_barrier(1, AM_SOFTMAX_THREADS);   // everyone has read the flag and the factors
+                if (tid == 0) *rescale_flag = 0;
             }
-            // P' = 2^(s2' - m) = weight * s_tok, two e4m3 terms; l accumulates the plain weight
+            // P'' = 2^(s2' - m) = weight * s_tok * 2^AM_POFF as two e4m3 terms (via f16: p <= 256 and the
+            // residual p - hi are exact enough in half precision); l accumulates the plain weight
             const float inv_tok = valid ? 1.0f / stok : 0.0f;
-            uint32_t hi_w[16], lo_w[16];
+            uint32_t hi_w[8], lo_w[8];
 #pragma unroll
-            for (int h = 0; h < AM_H; h += 2) {
-                const float p0 = valid ? exp2f(s2[h] - s_muse[h]) : 0.0f, p1 = valid ? exp2f(s2[h + 1] - s_muse[h + 1]) : 0.0f;   // s2 carries + AM_POFF
-                uint16_t ch, cl;
-                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(ch) : "f"(p1), "f"(p0));
-                const float2 hf = rv_e4m3x2_to_f32x2(ch);
-                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(cl) : "f"(p1 - hf.y), "f"(p0 - hf.x));
+            for (int h = 0; h < 32; h += 2) {
+                const float p0 = valid ? exp2f(s2[h] - s_muse[h0 + h]) : 0.0f;
+                const float p1 = valid ? exp2f(s2[h + 1] - s_muse[h0 + h + 1]) : 0.0f;
                 l_part[h] = fmaf(p0, inv_tok, l_part[h]);
                 l_part[h + 1] = fmaf(p1, inv_tok, l_part[h + 1]);
+                const __half2 ph = __floats2half2_rn(p0, p1);
+                const uint32_t phb = *reinterpret_cast<const uint32_t*>(&ph);
+                uint16_t ch, cl;
+                uint32_t hfb;
+                asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(ch) : "r"(phb));
+                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hfb) : "h"(ch));
+                const __half2 res = __hsub2(ph, *reinterpret_cast<const __half2*>(&hfb));
+                asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(cl) : "r"(*reinterpret_cast<const uint32_t*>(&res)));
                 if ((h & 2) == 0) { hi_w[h >> 2] = ch; lo_w[h >> 2] = cl; }
                 else { hi_w[h >> 2] |= (uint32_t)ch << 16; lo_w[h >> 2] |= (uint32_t)cl << 16; }
             }
@@ -393,10 +399,10 @@ attend_mma_kernel(AttendMmaArgs A) {
             {
                 uint8_t* prow = smem + SM_P;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(tid, c)) =
+                for (int c = 0; c < 2; ++c) {
+                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(row, hh * 2 + c)) =
                         make_uint4(hi_w[4 * c], hi_w[4 * c + 1], hi_w[4 * c + 2], hi_w[4 * c + 3]);
-                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(tid, 4 + c)) =
+                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(row, 4 + hh * 2 + c)) =
                         make_uint4(lo_w[4 * c], lo_w[4 * c + 1], lo_w[4 * c + 2], lo_w[4 * c + 3]);
                 }
             }
@@ -407,69 +413,61 @@ attend_mma_kernel(AttendMmaArgs A) {
         // ---- epilogue ----
         if (ok && ntiles > 0) ok = tc::mbar_wait(&bars.pv_done, (ntiles - 1) & 1, abort_flag, 65);
         tc::tc_fence_after();
-        // l per head: butterfly over the 32 token lanes, then across the 4 warps through shared memory
-        tc::named_barrier(1, 128);
+        // l per head: butterfly over the 32 token lanes, then across the 4 lane groups through shared memory
+        tc::named_barrier(1, AM_SOFTMAX_THREADS);
         {
-            float mine0 = 0.0f, mine1 = 0.0f;
+            float mine = 0.0f;
 #pragma unroll
-            for (int h = 0; h < AM_H; ++h) {
+            for (int h = 0; h < 32; ++h) {
                 const float v = rv_warp_sum(l_part[h]);
-                if ((h & 31) == lane) { if (h < 32) mine0 = v; else mine1 = v; }
+                if (h == lane) mine = v;
             }
-            s_wmax[warp * 64 + lane] = mine0;
-            s_wmax[warp * 64 + 32 + lane] = mine1;
+            s_wmax[q4 * 64 + h0 + lane] = mine;
         }
-        tc::named_barrier(1, 128);
-        if (warp == 0) {
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int h = lane + 32 * hh;
-                const float l = s_wmax[h] + s_wmax[64 + h] + s_wmax[128 + h] + s_wmax[192 + h];
-                const float mr = hh ? m_ref1 : m_ref0;
-                const float m_nat = (mr - AM_POFF) * 0.6931471805599453f;   // reference in natural-log units (l and O carry 2^AM_POFF)
-                if (A.n_splits > 1) {
-                    float* ml = A.partial + (size_t)b * A.n_splits * AM_H * (AM_KVL + 2) +
-                                (size_t)A.n_splits * AM_H * AM_KVL + ((size_t)split * AM_H + h) * 2;
-                    ml[0] = (l > 0.0f && ok) ? m_nat : -INFINITY;
-                    ml[1] = (l > 0.0f && ok) ? l : 0.0f;
-                } else {
-                    if (A.out_m) A.out_m[(size_t)b * AM_H + h] = l > 0.0f ? m_nat : -INFINITY;
-                    if (A.out_lse) A.out_lse[(size_t)b * AM_H + h] = l > 0.0f ? m_nat + logf(l) : -INFINITY;
-                }
-                s_wmax[h] = l > 0.0f ? 1.0f / l : 0.0f;
+        tc::named_barrier(1, AM_SOFTMAX_THREADS);
+        if (tid < AM_H) {
+            const int h = tid;
+            const float l = s_wmax[h] + s_wmax[64 + h] + s_wmax[128 + h] + s_wmax[192 + h];
+            const float m_nat = (m_ref - AM_POFF) * 0.6931471805599453f;   // natural-log units (l and O carry 2^AM_POFF)
+            if (A.n_splits > 1) {
+                float* ml = A.partial + (size_t)b * A.n_splits * AM_H * (AM_KVL + 2) +
+                            (size_t)A.n_splits * AM_H * AM_KVL + ((size_t)split * AM_H + h) * 2;
+                ml[0] = (l > 0.0f && ok) ? m_nat : -INFINITY;
+                ml[1] = (l > 0.0f && ok) ? l : 0.0f;
+            } else {
+                if (A.out_m) A.out_m[(size_t)b * AM_H + h] = l > 0.0f ? m_nat : -INFINITY;
+                if (A.out_lse) A.out_lse[(size_t)b * AM_H + h] = l > 0.0f ? m_nat + logf(l) : -INFINITY;
             }
+            s_muse[h] = l > 0.0f ? 1.0f / l : 0.0f;
         }
-        tc::named_barrier(1, 128);
-        // O^T: this thread's TMEM lane is one latent dim of each 128-dim block; 64 head columns each
+        tc::named_barrier(1, AM_SOFTMAX_THREADS);
+        // O^T: this thread's TMEM lane is one latent dim of each 128-dim block; its 32 head columns
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
-            const int dim = c * 128 + tid;
-#pragma unroll 1
-            for (int half = 0; half < 2; ++half) {
-                uint32_t r[32];
-                if (ntiles > 0 && ok) {
-                    tc::tmem_ld32(TM_O + lane_base + c * 64 + half * 32, r);
-                    tc::tmem_ld_wait();
-                } else {
+            const int dim = c * 128 + row;
+            uint32_t r[32];
+            if (ntiles > 0 && ok) {
+                tc::tmem_ld32(TM_O + lane_base + c * 64 + h0, r);
+                tc::tmem_ld_wait();
+            } else {
 #pragma unroll
-                    for (int h = 0; h < 32; ++h) r[h] = 0u;
-                }
+                for (int h = 0; h < 32; ++h) r[h] = 0u;
+            }
 #pragma unroll
-                for (int hq = 0; hq < 32; ++hq) {
-                    const int h = half * 32 + hq;
-                    const float v = __uint_as_float(r[hq]);
-                    if (A.n_splits > 1)
-                        A.partial[(size_t)b * A.n_splits * AM_H * (AM_KVL + 2) + ((size_t)split * AM_H + h) * AM_KVL + dim] = v;
-                    else
-                        A.out[((size_t)b * AM_H + h) * AM_KVL + dim] = rv_f32_to_bf16(v * s_wmax[h]);
-                }
+            for (int hq = 0; hq < 32; ++hq) {
+                const int h = h0 + hq;
+                const float v = __uint_as_float(r[hq]);
+                if (A.n_splits > 1)
+                    A.partial[(size_t)b * A.n_splits * AM_H * (AM_KVL + 2) + ((size_t)split * AM_H + h) * AM_KVL + dim] = v;
+                else
+                    A.out[((size_t)b * AM_H + h) * AM_KVL + dim] = rv_f32_to_bf16(v * s_muse[h]);
             }
         }
     }
 
     tc::tc_fence_before();
     __syncthreads();
-    if (warp == 4) tc::tmem_dealloc<512>(tmem);
+    if (warp == 8) tc::tmem_dealloc<512>(tmem);
     if (tid == 0 && *abort_flag) atomicCAS(A.err, 0, *abort_flag);
 }
 
