@@ -22,10 +22,12 @@
 //
 // One CTA per (sequence, split), 13 warps: 0-7 softmax + epilogue (TMEM lane group = warp % 4 =
 // tokens / dims, warps 0-3 own heads 0-31 and warps 4-7 heads 32-63), 8 MMA issue, 9-12 gather
-// (one thread per row, 36 x 16-byte cp.async into the swizzled tile).
-// Online softmax with a LAGGING reference max: O is rescaled only when a head's tile max
-// exceeds its reference by more than 2 (log2); P' is offset by 2^6 so that it stays <= 256 < 448
-// and typical weights keep both of their e4m3 terms in the normal range.
+// (a lane locates one row; copies go row by row, 32 lanes on 32 consecutive 16-byte chunks,
+// cp.async into the swizzled tile).
+// Online softmax with a LAGGING reference max: as long as no score of a tile exceeds its head's
+// reference by more than 3 (log2) the references stand (one barrier-with-OR per tile, no exchange);
+// otherwise the exact per-head maxima are taken and O is rescaled through TMEM. P' carries 2^5, so
+// it stays <= 256 < 448 and typical weights keep both e4m3 terms in the normal range.
 // All waits are bounded (tc_common.cuh).
 #include "codec.cuh"
 #include "common.cuh"
@@ -41,7 +43,7 @@ constexpr int AM_MAX_SPLITS = 16;
 // P'' = 2^(s2' - m_ref + AM_POFF) with m_ref lagging the true maximum by at most AM_LAG, so
 // P'' <= 2^(AM_POFF + AM_LAG) = 256 < 448 while typical weights (a few binades below the maximum)
 // land where BOTH e4m3 terms are normal numbers.
-constexpr float AM_POFF = 6.0f, AM_LAG = 2.0f;
+constexpr float AM_POFF = 5.0f, AM_LAG = 3.0f;
 
 // shared memory map (bytes); every operand tile is 1024-byte aligned
 constexpr int SM_K0 = 0;                 // 2 x (4 latent chunks x [128 rows][128 B]), 128-byte swizzle
@@ -65,6 +67,14 @@ struct AmBars {
 };
 static_assert(sizeof(AmBars) <= 128, "barrier block");
 static_assert(SM_TOTAL <= 232448, "shared memory budget");
+
+// Optional per-tile timeline of CTA (0, 0) for tuning builds (-DRIVOLI_DEBUG_TIMES); compiled out otherwise.
+#ifdef RIVOLI_DEBUG_TIMES
+__device__ long long g_am_times[64 * 16];
+#define AM_STAMP(tile, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) g_am_times[(tile) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define AM_STAMP(tile, slot) do { } while (0)
+#endif
 
 struct AttendMmaArgs {
     const uint8_t* qcodes;   // [B][128][576]: rows 0-63 q_hi codes, 64-127 q_lo codes
@@ -179,6 +189,7 @@ attend_mma_kernel(AttendMmaArgs A) {
         }
         if (tid < AM_H) s_ahi[tid] = A.qa[(size_t)b * AM_H + tid];
     }
+    if (tid < AM_H) { s_muse[tid] = -INFINITY; s_fac[tid] = 1.0f; }   // no reference yet: the first tile takes the exact path
     tc::fence_proxy_async();
     tc::tc_fence_before();
     __syncthreads();
@@ -207,31 +218,42 @@ attend_mma_kernel(AttendMmaArgs A) {
             }
         };
         locate(0);
+        // Each lane owns the address of one row, but the COPIES are issued row by row with the 32
+        // lanes of the warp on 32 consecutive 16-byte chunks (the row pointer travels by shuffle): one
+        // warp instruction then reads 512 contiguous bytes instead of 32 scattered 16-byte pieces.
+        const int pw = (warp - 9) * 32;      // first row of this warp
         for (int j = 0; j < ntiles && ok; ++j) {
             const int kb = j & 1;
-            ok = tc::mbar_wait(&bars.kv_empty[kb], ((j >> 1) & 1) ^ 1, abort_flag, 41) &&
-                 tc::mbar_wait(&bars.rope_free, (j & 1) ^ 1, abort_flag, 42);
+            ok = tc::mbar_wait(&bars.kv_empty[kb], ((j >> 1) & 1) ^ 1, abort_flag, 41);
             if (!ok) break;
+            if (p == 0) AM_STAMP(j, 0);
             uint8_t* kbuf = smem + SM_K0 + kb * SM_KBUF;
-            if (src) {
+            const unsigned long long sp = reinterpret_cast<unsigned long long>(src);
+            const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll 8
+            for (int it = 0; it < 32; ++it) {          // latent part: row pw + it, chunk = lane
+                const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, it));
+                uint8_t* dst = kbuf + (lane >> 3) * 16384 + tc::sw128_chunk(pw + it, lane & 7);
+                if (rs) tc::cp_async16(tc::smem_u32(dst), rs + lane * 16);
+                else *reinterpret_cast<uint4*>(dst) = z;   // rows past the end must be exact zeros:
+            }                                              // 0 x (stale NaN code) would poison O
+            // the single rope buffer is free as soon as the rope MMAs of the previous tile are done
+            ok = tc::mbar_wait(&bars.rope_free, (j & 1) ^ 1, abort_flag, 42);
+            if (!ok) break;
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    tc::cp_async16(tc::smem_u32(kbuf + (c >> 3) * 16384 + tc::sw128_chunk(p, c & 7)), src + c * 16);
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    tc::cp_async16(tc::smem_u32(smem + SM_ROPE + sw64_chunk(p, c)), src + 512 + c * 16);
-            } else {   // rows past the end must be exact zeros: 0 x (stale NaN code) would poison O
-                const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) *reinterpret_cast<uint4*>(kbuf + (c >> 3) * 16384 + tc::sw128_chunk(p, c & 7)) = z;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(smem + SM_ROPE + sw64_chunk(p, c)) = z;
+            for (int it = 0; it < 4; ++it) {           // rope part: 8 rows per instruction, 4 chunks each
+                const int rl = it * 8 + (lane >> 2);
+                const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, rl));
+                uint8_t* dst = smem + SM_ROPE + sw64_chunk(pw + rl, lane & 3);
+                if (rs) tc::cp_async16(tc::smem_u32(dst), rs + 512 + (lane & 3) * 16);
+                else *reinterpret_cast<uint4*>(dst) = z;
             }
             s_tok[kb * 128 + p] = scale;
             tc::cp_async_commit();
             locate(j + 1);               // next tile's address chain overlaps this tile's copies
             tc::cp_async_wait<0>();
             tc::fence_proxy_async();
+            if (p == 0) AM_STAMP(j, 1);
             tc::mbar_arrive(&bars.k_full[kb]);
         }
     } else if (warp == 8 && ntiles > 0) {
@@ -240,35 +262,45 @@ attend_mma_kernel(AttendMmaArgs A) {
         const uint32_t id_qk = tc::idesc_e4m3(128, 128, 0, 0), id_pv = tc::idesc_e4m3(128, 64, 1, 1);
         const uint32_t a_ql = tc::smem_u32(smem + SM_QL), a_qr = tc::smem_u32(smem + SM_QR);
         const uint32_t a_rope = tc::smem_u32(smem + SM_ROPE), a_p = tc::smem_u32(smem + SM_P);
-        for (int i = 0; i <= ntiles && ok; ++i) {
-            if (i < ntiles) {   // S^T(i) = K(i) . Qcat^T
-                const int kb = i & 1;
-                ok = tc::mbar_wait(&bars.k_full[kb], (i >> 1) & 1, abort_flag, 51) &&
-                     tc::mbar_wait(&bars.s_empty[kb], ((i >> 1) & 1) ^ 1, abort_flag, 52);
-                if (!ok) break;
+        // Two in-order instruction streams, QK(0..n-1) and PV(0..n-1), issued in READY order: whichever
+        // has its operands first goes first (PV preferred: it is what frees a K buffer for the gather).
+        int qk_next = 0, pv_next = 0, idle = 0;
+        while (ok && pv_next < ntiles) {
+            int can_pv = 0, can_qk = 0;
+            if (lane == 0) {
+                can_pv = pv_next < qk_next && tc::mbar_test(&bars.p_full, pv_next & 1);
+                if (!can_pv && qk_next < ntiles)
+                    can_qk = tc::mbar_test(&bars.k_full[qk_next & 1], (qk_next >> 1) & 1) &&
+                             tc::mbar_test(&bars.s_empty[qk_next & 1], ((qk_next >> 1) & 1) ^ 1);
+            }
+            can_pv = __shfl_sync(0xffffffffu, can_pv, 0);
+            can_qk = __shfl_sync(0xffffffffu, can_qk, 0);
+            if (can_qk) {   // S^T(i) = K(i) . Qcat^T
+                const int i = qk_next, kb = i & 1;
                 tc::tc_fence_after();
+                if (lane == 0) AM_STAMP(i, 2);
                 if (lane == 0) {
                     const uint32_t a_k = tc::smem_u32(smem + SM_K0 + kb * SM_KBUF);
                     const uint32_t d = TM_S0 + kb * 128;
+                    // rope columns first: their (single) buffer is released as soon as these two are done
+#pragma unroll
+                    for (int k = 0; k < 2; ++k)
+                        tc::mma_f8(d, smem_desc(a_rope + k * 32, 16, 512, 4), smem_desc(a_qr + k * 32, 16, 512, 4), id_qk, k != 0);
+                    tc::mma_commit(&bars.rope_free);
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             tc::mma_f8(d, smem_desc(a_k + c * 16384 + k * 32, 16, 1024, 2),
-                                       smem_desc(a_ql + c * 16384 + k * 32, 16, 1024, 2), id_qk, (c | k) != 0);
-#pragma unroll
-                    for (int k = 0; k < 2; ++k)
-                        tc::mma_f8(d, smem_desc(a_rope + k * 32, 16, 512, 4), smem_desc(a_qr + k * 32, 16, 512, 4), id_qk, 1);
+                                       smem_desc(a_ql + c * 16384 + k * 32, 16, 1024, 2), id_qk, 1);
                     tc::mma_commit(&bars.s_full[kb]);
-                    tc::mma_commit(&bars.rope_free);
                 }
                 __syncwarp();
-            }
-            if (i >= 1) {       // O^T += V(i-1)^T . P'(i-1)^T
-                const int j = i - 1, kb = j & 1;
-                ok = tc::mbar_wait(&bars.p_full, j & 1, abort_flag, 53);
-                if (!ok) break;
+                ++qk_next; idle = 0;
+            } else if (can_pv) {   // O^T += V(j)^T . P'(j)^T
+                const int j = pv_next, kb = j & 1;
                 tc::tc_fence_after();
+                if (lane == 0) AM_STAMP(j, 6);
                 if (lane == 0) {
                     const uint32_t a_k = tc::smem_u32(smem + SM_K0 + kb * SM_KBUF);
 #pragma unroll
@@ -287,6 +319,11 @@ attend_mma_kernel(AttendMmaArgs A) {
                     tc::mma_commit(&bars.pv_done);
                 }
                 __syncwarp();
+                ++pv_next; idle = 0;
+            } else {
+                if (++idle > 64 * tc::kMaxPolls) { *abort_flag = 54; ok = false; }   // bounded: nothing became ready
+                else if ((idle & 255) == 0 && *abort_flag) ok = false;
+                else __nanosleep(100);
             }
         }
     } else if (warp < 8) {
@@ -308,51 +345,71 @@ attend_mma_kernel(AttendMmaArgs A) {
                  tc::mbar_wait(&bars.s_full[kb], (i >> 1) & 1, abort_flag, 62);
             if (!ok) break;
             tc::tc_fence_after();
+            if (tid == 0) AM_STAMP(i, 3);
             const float stok = s_tok[kb * 128 + row];
             const bool valid = r_begin + i * AM_TILE + row < r_end && stok > 0.0f;
-            const float c2 = valid ? log2f(stok) + AM_POFF : 0.0f;   // P'' = weight * s_tok * 2^AM_POFF
+            // rows past the end are exact zeros in shared memory, so their raw scores are 0 and an
+            // additive -inf makes every weight of theirs exactly 0 without a select per element
+            const float c2 = valid ? log2f(stok) + AM_POFF : -INFINITY;   // P'' = weight * s_tok * 2^AM_POFF
+            const float inv_tok = valid ? 1.0f / stok : 0.0f;
             float s2[32];
+            float dmax = -INFINITY;               // max over this thread's heads of s2' - reference
             {
                 uint32_t rh[32], rl[32];
                 tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + h0, rh);
                 tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + 64 + h0, rl);
                 tc::tmem_ld_wait();
 #pragma unroll
-                for (int h = 0; h < 32; ++h) {
-                    const float raw = fmaf(__uint_as_float(rl[h]), 0.0625f, __uint_as_float(rh[h]));
-                    s2[h] = valid ? fmaf(raw, s_ahi[h0 + h] * stok, c2) : -INFINITY;
+                for (int h = 0; h < 32; h += 4) {
+                    const float4 a4 = *reinterpret_cast<const float4*>(s_ahi + h0 + h);
+                    const float4 m4 = *reinterpret_cast<const float4*>(s_muse + h0 + h);
+                    const float av[4] = {a4.x, a4.y, a4.z, a4.w}, mv[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float raw = fmaf(__uint_as_float(rl[h + e]), 0.0625f, __uint_as_float(rh[h + e]));
+                        s2[h + e] = fmaf(raw, av[e] * stok, c2);
+                        dmax = fmaxf(dmax, s2[h + e] - mv[e]);   // reference is -inf before the first tile
+                    }
                 }
             }
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&bars.s_empty[kb]);
+            if (tid == 0) AM_STAMP(i, 8);
 
-            // per-head tile max over the warp's 32 tokens, then across the 4 lane groups
+            // Fast path: no score of the tile exceeds its head's reference by more than AM_LAG, so the
+            // references stand and nothing has to be exchanged. One barrier-with-OR decides for the CTA.
+            uint32_t slow;
             {
-                float mine = -INFINITY;
+                const uint32_t mine_slow = dmax > AM_LAG ? 1u : 0u;   // NaN-free: dmax is -inf or finite
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+                             "bar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                             : "=r"(slow) : "r"(mine_slow), "n"(AM_SOFTMAX_THREADS) : "memory");
+            }
+            if (tid == 0) AM_STAMP(i, 10);
+            if (slow) {
+                // exact per-head tile max: warp reduce, then fold the 4 lane groups; move the references
+                {
+                    float mine = -INFINITY;
 #pragma unroll
-                for (int h = 0; h < 32; ++h) {
-                    float mx;
-                    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(mx) : "f"(s2[h]));
-                    if (h == lane) mine = mx;
+                    for (int h = 0; h < 32; ++h) {
+                        float mx;
+                        asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(mx) : "f"(s2[h]));
+                        if (h == lane) mine = mx;
+                    }
+                    s_wmax[q4 * 64 + h0 + lane] = mine;
                 }
-                s_wmax[q4 * 64 + h0 + lane] = mine;
-            }
-            tc::named_barrier(1, AM_SOFTMAX_THREADS);
-            if (tid < AM_H) {
-                const float tm = fmaxf(fmaxf(s_wmax[tid], s_wmax[64 + tid]), fmaxf(s_wmax[128 + tid], s_wmax[192 + tid]));
-                float fac = 1.0f;
-                int need = 0;
-                if (m_ref == -INFINITY) { if (tm > -INFINITY) m_ref = tm; }          // first live tile of this head
-                else if (tm > m_ref + AM_LAG) { fac = exp2f(m_ref - tm); m_ref = tm; need = 1; }
-                s_muse[tid] = m_ref;       // reference every thread uses for this tile
-                s_fac[tid] = fac;          // O / l rescale factor (1 when unchanged)
-                need = __any_sync(0xffffffffu, need);
-                if (lane == 0 && need) *rescale_flag = 1;
-            }
-            tc::named_barrier(1, AM_SOFTMAX_THREADS);
-            if (*rescale_flag) {
-                // rare: bring O^T and l to the new reference. PV(i-1) must have landed first.
+                tc::named_barrier(2, AM_SOFTMAX_THREADS);
+                if (tid < AM_H) {
+                    const float tm = fmaxf(fmaxf(s_wmax[tid], s_wmax[64 + tid]), fmaxf(s_wmax[128 + tid], s_wmax[192 + tid]));
+                    float fac = 1.0f;
+                    if (m_ref == -INFINITY) { if (tm > -INFINITY) m_ref = tm; }          // first live tile of this head
+                    else if (tm > m_ref) { fac = exp2f(m_ref - tm); m_ref = tm; }          // any growth is taken now
+                    s_muse[tid] = m_ref;
+                    s_fac[tid] = fac;
+                }
+                tc::named_barrier(2, AM_SOFTMAX_THREADS);
+                // bring O^T and l to the new references. PV(i-1) must have landed first.
                 if (i >= 1) { ok = tc::mbar_wait(&bars.pv_done, (i - 1) & 1, abort_flag, 63); if (!ok) break; }
                 tc::tc_fence_after();
                 if (i >= 1) {
@@ -370,30 +427,37 @@ attend_mma_kernel(AttendMmaArgs A) {
 #pragma unroll
                 for (int h = 0; h < 32; ++h) l_part[h] *= s_fac[h0 + h];
                 tc::tc_fence_before();
-                tc::named_barrier(1, AM_SOFTMAX_THREADS);   // everyone has read the flag and the factors
-                if (tid == 0) *rescale_flag = 0;
             }
+            if (tid == 0) AM_STAMP(i, 11);
             // P'' = 2^(s2' - m) = weight * s_tok * 2^AM_POFF as two e4m3 terms (via f16: p <= 256 and the
             // residual p - hi are exact enough in half precision); l accumulates the plain weight
-            const float inv_tok = valid ? 1.0f / stok : 0.0f;
             uint32_t hi_w[8], lo_w[8];
 #pragma unroll
-            for (int h = 0; h < 32; h += 2) {
-                const float p0 = valid ? exp2f(s2[h] - s_muse[h0 + h]) : 0.0f;
-                const float p1 = valid ? exp2f(s2[h + 1] - s_muse[h0 + h + 1]) : 0.0f;
-                l_part[h] = fmaf(p0, inv_tok, l_part[h]);
-                l_part[h + 1] = fmaf(p1, inv_tok, l_part[h + 1]);
-                const __half2 ph = __floats2half2_rn(p0, p1);
-                const uint32_t phb = *reinterpret_cast<const uint32_t*>(&ph);
-                uint16_t ch, cl;
-                uint32_t hfb;
-                asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(ch) : "r"(phb));
-                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hfb) : "h"(ch));
-                const __half2 res = __hsub2(ph, *reinterpret_cast<const __half2*>(&hfb));
-                asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(cl) : "r"(*reinterpret_cast<const uint32_t*>(&res)));
-                if ((h & 2) == 0) { hi_w[h >> 2] = ch; lo_w[h >> 2] = cl; }
-                else { hi_w[h >> 2] |= (uint32_t)ch << 16; lo_w[h >> 2] |= (uint32_t)cl << 16; }
+            for (int h = 0; h < 32; h += 4) {
+                const float4 m4 = *reinterpret_cast<const float4*>(s_muse + h0 + h);
+                const float mv[4] = {m4.x, m4.y, m4.z, m4.w};
+                uint32_t chs[2], cls[2];
+#pragma unroll
+                for (int e = 0; e < 4; e += 2) {
+                    float p0, p1;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(s2[h + e] - mv[e]));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(s2[h + e + 1] - mv[e + 1]));
+                    l_part[h + e] = fmaf(p0, inv_tok, l_part[h + e]);
+                    l_part[h + e + 1] = fmaf(p1, inv_tok, l_part[h + e + 1]);
+                    const __half2 ph = __floats2half2_rn(p0, p1);
+                    const uint32_t phb = *reinterpret_cast<const uint32_t*>(&ph);
+                    uint16_t ch, cl;
+                    uint32_t hfb;
+                    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(ch) : "r"(phb));
+                    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hfb) : "h"(ch));
+                    const __half2 res = __hsub2(ph, *reinterpret_cast<const __half2*>(&hfb));
+                    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(cl) : "r"(*reinterpret_cast<const uint32_t*>(&res)));
+                    chs[e >> 1] = ch; cls[e >> 1] = cl;
+                }
+                hi_w[h >> 2] = chs[0] | (chs[1] << 16);
+                lo_w[h >> 2] = cls[0] | (cls[1] << 16);
             }
+            if (tid == 0) AM_STAMP(i, 7);
             ok = tc::mbar_wait(&bars.p_empty, (i & 1) ^ 1, abort_flag, 64);
             if (!ok) break;
             {
@@ -407,6 +471,7 @@ attend_mma_kernel(AttendMmaArgs A) {
                 }
             }
             tc::fence_proxy_async();
+            if (tid == 0) AM_STAMP(i, 5);
             tc::mbar_arrive(&bars.p_full);
         }
 
@@ -534,3 +599,9 @@ extern "C" int rivoli_attend_mma_status(void* scratch, void* stream) {
     if (e != cudaSuccess) return -(int)e;
     return h ? 1008 : 0;
 }
+
+#ifdef RIVOLI_DEBUG_TIMES
+extern "C" __attribute__((visibility("default"))) int rivoli_attend_mma_debug_times(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_am_times, sizeof(long long) * 64 * 16);
+}
+#endif
