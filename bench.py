@@ -34,6 +34,9 @@ WORKLOADS = {
     "cfg3": dict(B=128, ctx=16384, n_heads=64, index_heads=32, index_dim=128, page_tokens=64, top_k=2048, seed=2),
 }
 KV_LORA, ROPE = 512, 64
+# dram__bytes_read.sum + dram__bytes_write.sum per sequence of the cfg3 shape, from the ncu capture
+# summarised in profiles/dram_traffic_hot_kernels_cfg3.md (stage totals / 128 sequences)
+TRAFFIC_PER_SEQ = {"index_select": (1.09 + 269.16 + 5.2 + 19.1) * 1e6 / 128, "attend": (9.45 + 184.9 + 0.9) * 1e6 / 128}
 METRIC = "DSA decode layer-steps/s (batch×ctx)"
 
 
@@ -246,9 +249,19 @@ def run_ours(args):
             peaks = json.load(open(pk))
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
-        # dominant kernel: the indexer (score + top-k), HBM bound
-        idx_ms = stage_ms[1]
-        achieved = ab["index"] * B / (idx_ms * 1e-3) / 1e9
+        # per-stage roofline; the headline object is the stage that takes longest (all are HBM bound:
+        # append / indexer by arithmetic intensity, attention sits at the tensor/HBM ridge)
+        names = ["append", "index_select", "attend"]
+        stage_bytes = {"append": ab["append"] * B, "index_select": ab["index"] * B, "attend": ab["attend"] * B}
+        stage_kernels = {"append": "kv_append_paged_kernel",
+                         "index_select": "index_q_prepare + index_score_mma (tcgen05) + index_select_refine",
+                         "attend": "attend_q_prepare + attend_mma (tcgen05)"}
+        per_stage = {n: {"ms": stage_ms[i], "bytes": stage_bytes[n],
+                         "gbs": stage_bytes[n] / (stage_ms[i] * 1e-3) / 1e9,
+                         "frac": stage_bytes[n] / (stage_ms[i] * 1e-3) / 1e9 / hbm_peak}
+                     for i, n in enumerate(names)}
+        dom = max(names, key=lambda n: per_stage[n]["ms"])
+        achieved = per_stage[dom]["gbs"]
         value = world * args.steps / (ms_total * 1e-3)
         line = {
             "metric": METRIC, "value": value, "unit": "layer-steps/s", "n_gpus": world, "steps": args.steps,
@@ -262,11 +275,13 @@ def run_ours(args):
                        "sequences_per_step": B * world},
             "e2e": {"value": world * args.steps / (ms_e2e * 1e-3), "unit": "layer-steps/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * 6,
+            "gpu_launches": args.steps * 6,   # append, 2 q-prepare, score, refine, attend (no combine at 1 split)
             "stage_ms": {"append": stage_ms[0], "index_select": stage_ms[1], "attend": stage_ms[2]},
-            "roofline": {"bound": "hbm", "kernel": "index_select (q quant + score + top-k)",
+            "roofline": {"bound": "hbm", "kernel": f"{dom} stage: {stage_kernels[dom]}",
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "peak_source": peak_src, "traffic": None,
+                         "peak_source": f"of {peak_src}", "traffic": TRAFFIC_PER_SEQ.get(dom, 0) * B or None,
+                         "traffic_source": "ncu dram read+write at cfg3 shape, per sequence x batch (profiles/)",
+                         "stages": per_stage,
                          "layer_step_bytes": sum(ab.values()) * B,
                          "layer_step_gbs": sum(ab.values()) * B / (ms_total / args.steps * 1e-3) / 1e9,
                          "attend_tflops": af["attend"] * B / (stage_ms[2] * 1e-3) / 1e12},
@@ -277,6 +292,28 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_profile(args):
+    import torch
+    w = dict(WORKLOADS[args.workload])
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g, layer, gen = build_layer(w, device, w["seed"])
+    x = step_inputs(w, device, gen)
+    row_pos = torch.full((w["B"],), w["ctx"] - 1, dtype=torch.int32, device=device)
+    seq_len = torch.full((w["B"],), w["ctx"], dtype=torch.int32, device=device)
+    layer.select(x["index_q"], x["index_w"], seq_len)      # rows for the attend-only mode
+    for _ in range(3):
+        if args.profile in ("step",):
+            layer.append(x["latent"], x["index_key"], row_pos)
+        if args.profile in ("select", "step"):
+            layer.select(x["index_q"], x["index_w"], seq_len)
+        if args.profile in ("attend", "step"):
+            layer.attend(x["q"])
+    torch.cuda.synchronize(device)
+    layer.check_status()
+    print("profile run ok:", args.profile, args.workload)
 
 
 def cpu_sample_state(w, n_seq, seed):
@@ -347,7 +384,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", default=None, choices=["select", "attend", "step"],
+                    help="build the workload, run 3 iterations of one stage (or the whole step) and exit: "
+                         "the command line the profiles/ summaries were captured with")
     args = ap.parse_args()
+    if args.profile:
+        return run_profile(args)
     if args.impl == "reference":
         run_reference(args)
     else:
