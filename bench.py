@@ -36,7 +36,7 @@ WORKLOADS = {
 KV_LORA, ROPE = 512, 64
 # dram__bytes_read.sum + dram__bytes_write.sum per sequence of the cfg3 shape, from the ncu capture
 # summarised in profiles/dram_traffic_hot_kernels_cfg3.md (stage totals / 128 sequences)
-TRAFFIC_PER_SEQ = {"index_select": (1.09 + 269.16 + 5.2 + 19.1) * 1e6 / 128, "attend": (9.45 + 184.9 + 0.9) * 1e6 / 128}
+TRAFFIC_PER_SEQ = {"index_select": (1.09 + 269.15 + 5.4 + 19.10) * 1e6 / 128, "attend": (9.45 + 184.98 + 0.9) * 1e6 / 128}
 METRIC = "DSA decode layer-steps/s (batch×ctx)"
 
 
@@ -297,6 +297,8 @@ def run_ours(args):
 def run_profile(args):
     import torch
     w = dict(WORKLOADS[args.workload])
+    if args.batch:
+        w["B"] = args.batch                                # a smaller case of the same shape for multi-pass captures
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     g, layer, gen = build_layer(w, device, w["seed"])
@@ -387,7 +389,11 @@ def main():
     ap.add_argument("--profile", default=None, choices=["select", "attend", "step"],
                     help="build the workload, run 3 iterations of one stage (or the whole step) and exit: "
                          "the command line the profiles/ summaries were captured with")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="with --profile only: sequences per GPU instead of the workload's own batch")
     args = ap.parse_args()
+    if args.batch and not args.profile:
+        ap.error("--batch is a --profile option; the bench always runs the workload's own batch")
     if args.profile:
         return run_profile(args)
     if args.impl == "reference":

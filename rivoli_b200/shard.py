@@ -68,6 +68,9 @@ class ShardOps:
 
 def _all_gather(t: torch.Tensor, group=None) -> torch.Tensor:
     world = dist.get_world_size(group)
+    if t.is_cuda and dist.get_backend(group) == "gloo":
+        # CPU transport for device tensors (ranks that share one GPU cannot form an NCCL group)
+        return _all_gather(t.cpu(), group).to(t.device)
     out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
     dist.all_gather(list(out.unbind(0)), t.contiguous(), group=group)   # views of `out`: filled in place
     return out
@@ -120,3 +123,38 @@ def page_range_step(ops: ShardOps, index_q, index_w, q, local_len: torch.Tensor,
     out = ops.merge(g_out, g_lse).reshape(B, H, kvl)
     rows_global = rows_att.to(torch.int64) + token_offset.to(torch.int64).unsqueeze(1)
     return out, rows_global, n_mine
+
+
+def gpu_shard_ops(layer) -> ShardOps:
+    """The CUDA library as the arithmetic of a page-range shard. ``layer`` is this rank's
+    ``DsaDecodeLayer`` holding the rank's slice of every sequence at local positions 0..n-1."""
+    from . import backend as be
+    g, B, dev = layer.g, layer.B, layer.dev
+
+    def score(index_q, index_w, local_len):
+        be.launch_index_q_quant(index_q, B * g.index_heads, g.index_dim, layer.qcodes, layer.qscales)
+        be.launch_index_score_paged(g, layer.qcodes, layer.qscales, index_w, layer.index_pool, layer.index_scale,
+                                    layer.block_table, local_len, B, layer.scores, layer.score_stride)
+        return layer.scores
+
+    def topk(scores, lens, k):
+        rows = torch.zeros((B, k), dtype=torch.int32, device=dev)
+        n = torch.zeros(B, dtype=torch.int32, device=dev)
+        scores = scores.contiguous()
+        be.launch_index_topk_batched(scores, scores.shape[1], lens.contiguous(), B, k, rows, n)
+        return rows, n
+
+    def attend(q, rows, n_rows):
+        rows = rows.contiguous()
+        be.launch_attend_paged_bf16(g, q, layer.latent_pool, layer.latent_scale, layer.block_table, rows,
+                                    rows.shape[1], n_rows.contiguous(), B, layer.out, layer.out_m, layer.out_lse,
+                                    layer.scratch)
+        return layer.out, layer.out_lse
+
+    def merge(part_out, part_lse):
+        G, n_vec, kvl = part_out.shape
+        out = torch.empty((n_vec, kvl), dtype=torch.bfloat16, device=dev)
+        be.launch_attend_merge_partials(part_out.contiguous(), part_lse.contiguous(), G, n_vec, kvl, out)
+        return out
+
+    return ShardOps(score, topk, attend, merge)
