@@ -40,6 +40,16 @@ TRAFFIC_PER_SEQ = {"index_select": (1.09 + 269.15 + 5.4 + 19.10) * 1e6 / 128, "a
 METRIC = "DSA decode layer-steps/s (batch×ctx)"
 
 
+def config_of(name, w, world):
+    """The `config` object of the JSON line; both arms print the same one."""
+    B, ctx = w["B"], w["ctx"]
+    return {"workload": f"{name}: batch {B}/GPU x ctx {ctx}, top-k {w['top_k']}, "
+                        f"{w['page_tokens']}-token pages scattered in a 1.25x pool, seed {w['seed']}",
+            "l2": "inputs larger than L2 (index keys + latents >> 126 MB)" if B * ctx * 132 > 2e8
+                  else "working set fits L2: latency-bound config",
+            "sequences_per_step": B * world}
+
+
 def algorithmic_bytes(w):
     """Per-sequence algorithmic bytes of one layer-step, by stage (append, index, attend)."""
     nt, k, H, nh, hd = w["ctx"], w["top_k"], w["n_heads"], w["index_heads"], w["index_dim"]
@@ -58,15 +68,41 @@ def algorithmic_flops(w):
 
 
 class ClockSampler:
-    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and clock-event reasons of one GPU through NVML (read-only queries)
+    from a thread, about every millisecond, so that even a timed region of a few milliseconds
+    holds samples; ``mark()`` brackets the timed region. Falls back to ``nvidia-smi -lms``."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, gpu_index: int):
-        self.idx, self.proc, self.lines = gpu_index, None, []
+        self.idx, self.proc, self.samples, self.marks = gpu_index, None, [], []
+        self.stop_flag, self.h, self.nv, self.t, self.max_mhz = False, None, None, None, None
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            try:
+                return int(vis.split(",")[self.idx])
+            except (ValueError, IndexError):
+                return None          # UUID list: use nvidia-smi's own mapping instead
+        return self.idx
 
     def start(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            pi = self._physical_index()
+            if pi is None:
+                raise RuntimeError("no index")
+            self.h, self.nv = nv.nvmlDeviceGetHandleByIndex(pi), nv
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM))
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return
+        except Exception:
+            self.nv = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -76,35 +112,60 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def _read(self):
-        for ln in self.proc.stdout:
-            self.lines.append(ln.strip())
+    def _poll(self):
+        nv, h = self.nv, self.h
+        while not self.stop_flag:
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                self.samples.append((time.perf_counter(), mhz, mask))
+            except Exception:
+                pass
+            time.sleep(0.001)
 
-    def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
+    def _read(self):
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        bits = {v: k for k, v in self.REASONS.items()}
+        for ln in self.proc.stdout:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                mhz, mx = float(f[1]), float(f[2])
             except ValueError:
                 continue
-            for n, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if not sm:
+            self.max_mhz = max(self.max_mhz or 0.0, mx)
+            mask = sum(bits[n] for n, v in zip(names, f[5:9]) if v.lower().startswith("active"))
+            self.samples.append((time.perf_counter(), mhz, mask))
+
+    def mark(self):
+        self.marks.append(time.perf_counter())
+
+    def stop(self):
+        self.stop_flag = True
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+        if self.t:
+            self.t.join(timeout=2)
+        if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        lo, hi = (self.marks + [None, None])[:2]
+        inside = [s for s in self.samples if lo is not None and hi is not None and lo <= s[0] <= hi]
+        use = inside or self.samples          # a region shorter than the sampling period: the whole loaded phase
+        mask = 0
+        for s in use:
+            mask |= s[2]
+        return {"sm_mhz": float(np.median([s[1] for s in use])), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(n for b, n in self.REASONS.items() if mask & b),
+                "samples": len(use), "samples_in_timed_region": len(inside),
+                "source": "nvml" if self.nv else "nvidia-smi"}
 
 
 def build_layer(w, device, seed):
@@ -203,38 +264,43 @@ def run_ours(args):
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark()
     t0.record()
     for i in range(args.steps):
         step(x, evs[i])
     t1.record()
     barrier()
+    sampler.mark()
     clocks = sampler.stop() if rank == 0 else None
     ms_total = t0.elapsed_time(t1)
     stage_ms = [float(np.mean([e[i].elapsed_time(e[i + 1]) for e in evs])) for i in range(3)]
 
     # ---- end to end through the host-facing call: pinned host inputs, device->host result ------------
+    # HostStepPipeline.submit is the call a host-resident caller makes: per step it uploads the step's
+    # inputs, runs the three operators and downloads the attention output (three streams, two slots).
+    from rivoli_b200.layer import HostStepPipeline
     xh = step_inputs(w, device, gen, pinned=True)
-    xd = {k: torch.empty_like(v, device=device) for k, v in xh.items()}
-    out_h = torch.empty((B, w["n_heads"], KV_LORA), dtype=torch.bfloat16).pin_memory()
+    pipe = HostStepPipeline(layer, depth=2)
+    outs_h = [torch.empty((B, w["n_heads"], KV_LORA), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
 
-    def e2e_step():
-        for k in xh:
-            xd[k].copy_(xh[k], non_blocking=True)
-        step(xd)
-        out_h.copy_(layer.out, non_blocking=True)
+    def e2e_step(i):
+        pipe.submit(xh, outs_h[i & 1], row_pos, seq_len)
 
-    for _ in range(3):
-        e2e_step()
+    for i in range(4):
+        e2e_step(i)
+    pipe.drain()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
+    e0.record(pipe.s_up)
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record(pipe.s_down)               # after the last download: every earlier leg precedes it
+    pipe.drain()
     barrier()
+    layer.check_status()
     ms_e2e = e0.elapsed_time(e1)
     h2d = int(sum(v.numel() * v.element_size() for v in xh.values()))
-    d2h = int(out_h.numel() * out_h.element_size())
+    d2h = int(outs_h[0].numel() * outs_h[0].element_size())
 
     if world > 1:
         t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
@@ -268,11 +334,7 @@ def run_ours(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": f"{args.workload}: batch {B}/GPU x ctx {ctx}, top-k {w['top_k']}, "
-                                   f"{w['page_tokens']}-token pages scattered in a 1.25x pool, seed {w['seed']}",
-                       "l2": "inputs larger than L2 (index keys + latents >> 126 MB)" if B * ctx * 132 > 2e8
-                             else "working set fits L2: latency-bound config",
-                       "sequences_per_step": B * world},
+            "config": config_of(args.workload, w, world),
             "e2e": {"value": world * args.steps / (ms_e2e * 1e-3), "unit": "layer-steps/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * 6,   # append, 2 q-prepare, score, refine, attend (no combine at 1 split)
@@ -355,7 +417,9 @@ def run_reference(args):
     w = WORKLOADS[args.workload]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     from oracle import oracle as orc
-    n_seq = max(1, min(w["B"], 8))
+    # bounded sample: about 11 ms of CPU work per cfg3 sequence; keep the whole run near two minutes
+    per_seq_s = 0.011 * w["ctx"] / 16384
+    n_seq = max(1, min(w["B"], 8, int(120.0 / max(1, args.steps + 1) / per_seq_s)))
     st = cpu_sample_state(w, n_seq, w["seed"])
     for _ in range(min(args.warmup, 1)):
         st.oracle_step()
@@ -370,7 +434,7 @@ def run_reference(args):
             "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / n_seq * w["B"] * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU)",
             "data": "synthetic",
-            "config": {"workload": f"{args.workload}: batch {w['B']} x ctx {w['ctx']}, top-k {w['top_k']}"},
+            "config": config_of(args.workload, w, world),
             "cpu_baseline": {"value": value, "unit": "layer-steps/s", "cores": orc.num_threads(), "kind": "port",
                              "sample": sample},
             "e2e": {"value": value, "unit": "layer-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -381,7 +445,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3", choices=list(WORKLOADS))

@@ -97,23 +97,27 @@ class DsaDecodeLayer:
         be.launch_index_topk_batched(self.scores, self.score_stride, seq_len, self.B, g.top_k, self.rows,
                                      self.n_sel, stream)
 
-    def attend(self, q: torch.Tensor, stream=None, dense_len: torch.Tensor | None = None) -> torch.Tensor:
-        """Attention over the selected rows (or, with ``dense_len``, over the whole prefix)."""
+    def attend(self, q: torch.Tensor, stream=None, dense_len: torch.Tensor | None = None,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+        """Attention over the selected rows (or, with ``dense_len``, over the whole prefix).
+        Writes ``self.out`` unless another bf16 ``[B, H, kv_lora]`` buffer is given."""
+        out = self.out if out is None else out
         if dense_len is not None:
             be.launch_attend_paged_bf16(self.g, q, self.latent_pool, self.latent_scale, self.block_table,
-                                        None, 0, dense_len, self.B, self.out, self.out_m, self.out_lse,
+                                        None, 0, dense_len, self.B, out, self.out_m, self.out_lse,
                                         self.scratch, stream)
         else:
             be.launch_attend_paged_bf16(self.g, q, self.latent_pool, self.latent_scale, self.block_table,
-                                        self.rows, self.g.top_k, self.n_sel, self.B, self.out, self.out_m,
+                                        self.rows, self.g.top_k, self.n_sel, self.B, out, self.out_m,
                                         self.out_lse, self.scratch, stream)
-        return self.out
+        return out
 
-    def step(self, latent, index_key, index_q, index_w, q, row_pos, seq_len, stream=None) -> torch.Tensor:
+    def step(self, latent, index_key, index_q, index_w, q, row_pos, seq_len, stream=None,
+             out: torch.Tensor | None = None) -> torch.Tensor:
         """One layer-step: append one token per sequence, select, attend."""
         self.append(latent, index_key, row_pos, None, stream)
         self.select(index_q, index_w, seq_len, stream)
-        return self.attend(q, stream)
+        return self.attend(q, stream, out=out)
 
     def check_status(self) -> None:
         """Raise if a kernel flagged a bad block-table entry since the last check (syncs)."""
@@ -123,6 +127,67 @@ class DsaDecodeLayer:
         if s:
             self.status.zero_()
             raise be.BackendError("kv_append_paged(status)", 1005)
+
+
+class HostStepPipeline:
+    """Layer-steps for a caller whose activations live in HOST memory (pinned): every step
+    copies its inputs host->device, runs append -> select -> attend, and copies the attention
+    output device->host. The three legs run on three streams with two device-side slots, so the
+    upload of step ``i+1`` and the download of step ``i-1`` overlap the kernels of step ``i``;
+    within a stream everything stays in program order, so results equal the serial order.
+
+    The caller owns the pinned host buffers and must not reuse an output buffer before
+    ``wait(ticket)`` (or ``drain()``) has returned for the step that fills it.
+    """
+    KEYS = ("latent", "index_key", "index_q", "index_w", "q")
+
+    def __init__(self, layer: DsaDecodeLayer, depth: int = 2):
+        self.layer, self.depth = layer, depth
+        g, B, d = layer.g, layer.B, layer.dev
+        W = g.kv_lora + g.rope_dim
+        bf, f32 = torch.bfloat16, torch.float32
+        shapes = dict(latent=((B, W), bf), index_key=((B, g.index_dim), bf),
+                      index_q=((B, g.index_heads, g.index_dim), bf), index_w=((B, g.index_heads), f32),
+                      q=((B, g.n_heads, W), bf))
+        self.slots = [{k: torch.empty(s, dtype=t, device=d) for k, (s, t) in shapes.items()} for _ in range(depth)]
+        self.outs = [torch.empty((B, g.n_heads, g.kv_lora), dtype=bf, device=d) for _ in range(depth)]
+        with torch.cuda.device(d):
+            self.s_up, self.s_run, self.s_down = (torch.cuda.Stream(d) for _ in range(3))
+            mk = lambda: [torch.cuda.Event() for _ in range(depth)]
+            self.ev_up, self.ev_run, self.ev_down = mk(), mk(), mk()
+        self.n = 0
+
+    def submit(self, host_in: dict, host_out: torch.Tensor, row_pos: torch.Tensor, seq_len: torch.Tensor) -> int:
+        """Enqueue one layer-step; returns a ticket for ``wait``. Never blocks the host."""
+        L, s = self.layer, self.n % self.depth
+        first = self.n < self.depth
+        if not first:
+            self.s_up.wait_event(self.ev_run[s])        # the step that last read this input slot is done
+        with torch.cuda.stream(self.s_up):
+            for k in self.KEYS:
+                self.slots[s][k].copy_(host_in[k], non_blocking=True)
+            self.ev_up[s].record(self.s_up)
+        self.s_run.wait_event(self.ev_up[s])
+        if not first:
+            self.s_run.wait_event(self.ev_down[s])      # this output slot has been downloaded
+        x = self.slots[s]
+        L.step(x["latent"], x["index_key"], x["index_q"], x["index_w"], x["q"], row_pos, seq_len,
+               stream=self.s_run, out=self.outs[s])
+        self.ev_run[s].record(self.s_run)
+        self.s_down.wait_event(self.ev_run[s])
+        with torch.cuda.stream(self.s_down):
+            host_out.copy_(self.outs[s], non_blocking=True)
+            self.ev_down[s].record(self.s_down)
+        self.n += 1
+        return self.n - 1
+
+    def wait(self, ticket: int) -> None:
+        """Block until the output of step ``ticket`` is in its host buffer (the slot's event belongs to
+        that step or to a later one on the same in-order stream, which implies it)."""
+        self.ev_down[ticket % self.depth].synchronize()
+
+    def drain(self) -> None:
+        self.s_down.synchronize()
 
 
 def bf16_bits(t: torch.Tensor) -> np.ndarray:
