@@ -176,7 +176,9 @@ int rivoli_index_select_status(const DsaGeom* g, int B, int score_stride, void* 
 int rivoli_index_select_band_stats(const DsaGeom* g, int B, int score_stride, void* scratch,
                                    uint32_t* host_band, void* stream);
 
-/* Bytes of scratch rivoli_mla_attend_paged_bf16 needs for B sequences (split partials). */
+/* Bytes of scratch rivoli_mla_attend_paged_bf16 needs for B sequences (an error word and the
+ * split partials). Zero its first 256 bytes once after allocation: the error word is sticky (first
+ * failure wins) until rivoli_mla_attend_paged_status reads and clears it. */
 size_t rivoli_mla_attend_paged_scratch_bytes(const DsaGeom* g, int B);
 
 /* Batched, paged form of rivoli_mla_attend (attn.hip:119-232 + combine :241-273).

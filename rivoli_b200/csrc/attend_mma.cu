@@ -63,7 +63,7 @@ constexpr int SM_MISC = SM_BARS + 128;
 constexpr int SM_TOTAL = SM_MISC + 64;   // 232,384 <= 232,448
 
 struct AmBars {
-    uint64_t k_full[2], kv_empty[2], s_full[2], s_empty[2], rope_free, p_full, p_empty, pv_done;
+    uint64_t k_full[2], kv_empty[2], s_full[2], s_empty[2], rope_free, p_full, p_empty, pv_done, q_full;
 };
 static_assert(sizeof(AmBars) <= 128, "barrier block");
 static_assert(SM_TOTAL <= 232448, "shared memory budget");
@@ -77,8 +77,8 @@ __device__ long long g_am_times[64 * 16];
 #endif
 
 struct AttendMmaArgs {
-    const uint8_t* qcodes;   // [B][128][576]: rows 0-63 q_hi codes, 64-127 q_lo codes
-    const float* qa;         // [B][64]: s_q[h] * softmax_scale * log2(e)
+    const uint16_t* q;       // [B][64][576] bf16: absorbed query, latent part then rope part
+    float softmax_scale;
     const uint8_t* pool; const float* pscale; const int32_t* block_table;
     const uint32_t* rows; long long row_stride; const int32_t* n_rows;
     int page_tokens, max_pages, n_pool_pages, n_splits;
@@ -99,41 +99,6 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
 }
 
 // ---------------------------------------------------------------------------------------------
-// q -> two e4m3 terms per head. One warp per head; 18 values per lane.
-//   hi = e4m3(q / s), s = absmax / 448;  lo = e4m3((q / s - hi) * 16)   =>  q ~ s * (hi + lo / 16)
-// ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
-attend_q_prepare_kernel(const uint16_t* __restrict__ q, int n_vec, float softmax_scale, uint8_t* __restrict__ qcodes,
-                        float* __restrict__ qa, int* __restrict__ err) {
-    const int v = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (blockIdx.x == 0 && threadIdx.x == 0) *err = 0;
-    if (v >= n_vec) return;
-    const int b = v / AM_H, h = v - b * AM_H;
-    const uint16_t* src = q + (size_t)v * AM_W;
-    float f[18];
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 18; ++i) { f[i] = rv_bf16_to_f32(src[lane + 32 * i]); amax = fmaxf(amax, fabsf(f[i])); }
-    amax = rv_warp_max(amax);
-    const float s = amax > 0.0f ? amax / 448.0f : 1.0f;
-    const float inv = 1.0f / s;
-    uint8_t* hi = qcodes + ((size_t)b * 128 + h) * AM_W;
-    uint8_t* lo = qcodes + ((size_t)b * 128 + 64 + h) * AM_W;
-#pragma unroll
-    for (int i = 0; i < 18; ++i) {
-        const float x = f[i] * inv;
-        uint16_t c;
-        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(0.0f), "f"(x));
-        const float xh = rv_e4m3x2_to_f32x2(c).x;
-        uint16_t c2;
-        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c2) : "f"(0.0f), "f"((x - xh) * 16.0f));
-        hi[lane + 32 * i] = (uint8_t)(c & 0xff);
-        lo[lane + 32 * i] = (uint8_t)(c2 & 0xff);
-    }
-    if (lane == 0) qa[v] = s * softmax_scale * 1.4426950408889634f;
-}
-
-// ---------------------------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(AM_THREADS, 1)
@@ -151,6 +116,7 @@ attend_mma_kernel(AttendMmaArgs A) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = blockIdx.y;
+    if (tid == 0) AM_STAMP(0, 12);
     const int P = A.page_tokens;
 
     int nr = A.n_rows[b];
@@ -165,30 +131,19 @@ attend_mma_kernel(AttendMmaArgs A) {
     const int ntiles = r_end > r_begin ? (r_end - r_begin + AM_TILE - 1) / AM_TILE : 0;
 
     if (tid == 0) {
-        tc::mbar_init(&bars.k_full[0], 128); tc::mbar_init(&bars.k_full[1], 128);
+        tc::mbar_init(&bars.k_full[0], 64); tc::mbar_init(&bars.k_full[1], 64);
         tc::mbar_init(&bars.kv_empty[0], 1); tc::mbar_init(&bars.kv_empty[1], 1);
         tc::mbar_init(&bars.s_full[0], 1); tc::mbar_init(&bars.s_full[1], 1);
         tc::mbar_init(&bars.s_empty[0], 8); tc::mbar_init(&bars.s_empty[1], 8);
         tc::mbar_init(&bars.rope_free, 1); tc::mbar_init(&bars.p_full, AM_SOFTMAX_THREADS);
         tc::mbar_init(&bars.p_empty, 1); tc::mbar_init(&bars.pv_done, 1);
+        tc::mbar_init(&bars.q_full, AM_SOFTMAX_THREADS);
         tc::mbar_init_fence();
         *abort_flag = 0;
         *rescale_flag = 0;
     }
     if (warp == 8) tc::tmem_alloc<512>(tmem_base_s);
 
-    // q codes -> swizzled shared tiles (generic stores, once per CTA)
-    if (ntiles > 0) {
-        const uint8_t* qc = A.qcodes + (size_t)b * 128 * AM_W;
-        for (int c = tid; c < 128 * 36; c += AM_THREADS) {
-            const int row = c / 36, j = c - row * 36;
-            const uint4 v = *reinterpret_cast<const uint4*>(qc + (size_t)row * AM_W + j * 16);
-            uint8_t* dst = j < 32 ? smem + SM_QL + (j >> 3) * 16384 + tc::sw128_chunk(row, j & 7)
-                                  : smem + SM_QR + sw64_chunk(row, j - 32);
-            *reinterpret_cast<uint4*>(dst) = v;
-        }
-        if (tid < AM_H) s_ahi[tid] = A.qa[(size_t)b * AM_H + tid];
-    }
     if (tid < AM_H) { s_muse[tid] = -INFINITY; s_fac[tid] = 1.0f; }   // no reference yet: the first tile takes the exact path
     tc::fence_proxy_async();
     tc::tc_fence_before();
@@ -197,64 +152,171 @@ attend_mma_kernel(AttendMmaArgs A) {
     const uint32_t tmem = *tmem_base_s;
     const uint32_t TM_S0 = tmem, TM_O = tmem + 256;
 
-    if (warp >= 9 && ntiles > 0) {
-        // ------------------------------ gather producers: thread = row of the tile ----------------
-        const int p = tid - 288;
-        bool ok = true;
-        const uint8_t* src = nullptr;
-        float scale = 0.0f;
-        auto locate = [&](int j) {   // row pointer + scale of this thread's row in tile j
-            src = nullptr; scale = 0.0f;
-            const int ri = r_begin + j * AM_TILE + p;
-            if (j < ntiles && ri < r_end) {
-                const uint32_t t = A.rows ? A.rows[(size_t)b * A.row_stride + ri] : (uint32_t)ri;
-                const int lp = (int)(t / (uint32_t)P);
-                int pg = lp < A.max_pages ? A.block_table[(size_t)b * A.max_pages + lp] : -1;
-                if (pg >= 0 && pg < A.n_pool_pages) {
-                    const size_t r = (size_t)pg * P + (t & (uint32_t)(P - 1));
-                    src = A.pool + r * AM_W;
-                    scale = A.pscale[r];
+    // q -> two e4m3 terms per head, written straight into the swizzled operand tiles (once per CTA):
+    //   hi = e4m3(q / s), s = absmax / 448;  lo = e4m3((q / s - hi) * 16)   =>  q ~ s * (hi + lo / 16)
+    // Warps 0-7 take 8 heads each; a head's 576 values are 72 chunks of 8 (lane, lane+32, lane+64).
+    // The gather warps do not wait for this: the MMA warp does (q_full) before its first QK.
+    if (tid == 0) AM_STAMP(0, 13);
+    if (warp < 8 && ntiles > 0) {
+        const uint16_t* qb = A.q + (size_t)b * AM_H * AM_W;
+#pragma unroll 1
+        for (int h4 = 0; h4 < 8; h4 += 4) {
+            uint4 v[4][3];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint16_t* src = qb + (size_t)(warp * 8 + h4 + u) * AM_W;
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    const int chunk = lane + 32 * c;
+                    v[u][c] = chunk < 72 ? *reinterpret_cast<const uint4*>(src + chunk * 8) : make_uint4(0, 0, 0, 0);
                 }
             }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int h = warp * 8 + h4 + u;
+                float f[3][8];
+                float amax = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    const uint32_t ww[4] = {v[u][c].x, v[u][c].y, v[u][c].z, v[u][c].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        f[c][2 * i] = __uint_as_float(ww[i] << 16);
+                        f[c][2 * i + 1] = __uint_as_float(ww[i] & 0xffff0000u);
+                        amax = fmaxf(amax, fmaxf(fabsf(f[c][2 * i]), fabsf(f[c][2 * i + 1])));
+                    }
+                }
+                amax = rv_warp_max(amax);
+                const float sq = amax > 0.0f ? amax / 448.0f : 1.0f;
+                const float inv = 1.0f / sq;
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    const int chunk = lane + 32 * c;
+                    if (chunk < 72) {
+                        uint32_t hi_w[2], lo_w[2];
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            uint32_t hw = 0u, lw = 0u;
+#pragma unroll
+                            for (int e = 0; e < 4; e += 2) {
+                                const float x0 = f[c][4 * i + e] * inv, x1 = f[c][4 * i + e + 1] * inv;
+                                uint16_t ch, cl;
+                                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(ch) : "f"(x1), "f"(x0));
+                                const float2 xh = rv_e4m3x2_to_f32x2(ch);
+                                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(cl) : "f"((x1 - xh.y) * 16.0f), "f"((x0 - xh.x) * 16.0f));
+                                hw |= (uint32_t)ch << (8 * e);
+                                lw |= (uint32_t)cl << (8 * e);
+                            }
+                            hi_w[i] = hw; lo_w[i] = lw;
+                        }
+                        const int j16 = chunk >> 1, half = (chunk & 1) * 8;
+                        uint8_t* dh = j16 < 32 ? smem + SM_QL + (j16 >> 3) * 16384 + tc::sw128_chunk(h, j16 & 7)
+                                               : smem + SM_QR + sw64_chunk(h, j16 - 32);
+                        uint8_t* dl = j16 < 32 ? smem + SM_QL + (j16 >> 3) * 16384 + tc::sw128_chunk(64 + h, j16 & 7)
+                                               : smem + SM_QR + sw64_chunk(64 + h, j16 - 32);
+                        *reinterpret_cast<uint2*>(dh + half) = make_uint2(hi_w[0], hi_w[1]);
+                        *reinterpret_cast<uint2*>(dl + half) = make_uint2(lo_w[0], lo_w[1]);
+                    }
+                }
+                if (lane == 0) s_ahi[h] = sq * A.softmax_scale * 1.4426950408889634f;
+            }
+        }
+        tc::fence_proxy_async();
+        tc::mbar_arrive(&bars.q_full);
+        if (tid == 0) AM_STAMP(0, 14);
+    }
+
+    if (warp >= 9 && ntiles > 0) {
+        // ------------------------------ gather producers ------------------------------------------
+        // Two independent groups of two warps: group 0 fills the even tiles (buffer 0), group 1 the odd
+        // ones (buffer 1), each in plain program order (wait for its buffer, copy, signal). With one
+        // group per buffer neither ever waits on the other's buffer, so two tiles are in flight
+        // whenever both buffers are free. A thread owns two rows of its group's tile.
+        const int grp = (warp - 9) >> 1, wi = (warp - 9) & 1;
+        const int pr[2] = {wi * 32 + lane, 64 + wi * 32 + lane};
+        bool ok = true;
+        // The address chain of a row (selected token -> page -> pool row -> scale) is three dependent
+        // global loads; it runs as a software pipeline three tiles deep, one load per stage and
+        // iteration, so no copy waits on it: t_n = token two tiles on, r_n = pool row one tile on,
+        // (src, scale) = the current tile ("tile" = the group's own sequence j, j+2, j+4, ...).
+        constexpr uint32_t NONE = 0xffffffffu;
+        const uint32_t* rowp = A.rows ? A.rows + (size_t)b * A.row_stride : nullptr;
+        const int32_t* btp = A.block_table + (size_t)b * A.max_pages;
+        auto load_t = [&](int j, int p) -> uint32_t {
+            const int ri = r_begin + j * AM_TILE + p;
+            if (j >= ntiles || ri >= r_end) return NONE;
+            return rowp ? rowp[ri] : (uint32_t)ri;
         };
-        locate(0);
-        // Each lane owns the address of one row, but the COPIES are issued row by row with the 32
-        // lanes of the warp on 32 consecutive 16-byte chunks (the row pointer travels by shuffle): one
-        // warp instruction then reads 512 contiguous bytes instead of 32 scattered 16-byte pieces.
-        const int pw = (warp - 9) * 32;      // first row of this warp
-        for (int j = 0; j < ntiles && ok; ++j) {
-            const int kb = j & 1;
-            ok = tc::mbar_wait(&bars.kv_empty[kb], ((j >> 1) & 1) ^ 1, abort_flag, 41);
+        auto load_r = [&](uint32_t t) -> uint32_t {
+            if (t == NONE) return NONE;
+            const int lp = (int)(t / (uint32_t)P);
+            const int pg = lp < A.max_pages ? btp[lp] : -1;
+            return (pg >= 0 && pg < A.n_pool_pages) ? (uint32_t)pg * (uint32_t)P + (t & (uint32_t)(P - 1)) : NONE;
+        };
+        const uint8_t* src[2];
+        float scale[2];
+        uint32_t t_n[2], r_n[2];
+        auto set_cur = [&](int u, uint32_t r) {
+            src[u] = nullptr; scale[u] = 0.0f;
+            if (r != NONE) { src[u] = A.pool + (size_t)r * AM_W; scale[u] = A.pscale[r]; }
+        };
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const uint32_t t0 = load_t(grp, pr[u]), t1 = load_t(grp + 2, pr[u]);
+            t_n[u] = load_t(grp + 4, pr[u]);
+            const uint32_t r0 = load_r(t0);
+            r_n[u] = load_r(t1);
+            set_cur(u, r0);
+        }
+        // Each lane owns the address of a row, but the COPIES are issued row by row with the 32 lanes of
+        // the warp on 32 consecutive 16-byte chunks (the row pointer travels by shuffle): one warp
+        // instruction then reads 512 contiguous bytes instead of 32 scattered 16-byte pieces.
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (int j = grp; j < ntiles && ok; j += 2) {
+            uint8_t* kbuf = smem + SM_K0 + grp * SM_KBUF;
+            ok = tc::mbar_wait(&bars.kv_empty[grp], ((j >> 1) & 1) ^ 1, abort_flag, 41);
             if (!ok) break;
-            if (p == 0) AM_STAMP(j, 0);
-            uint8_t* kbuf = smem + SM_K0 + kb * SM_KBUF;
-            const unsigned long long sp = reinterpret_cast<unsigned long long>(src);
-            const uint4 z = make_uint4(0, 0, 0, 0);
+            if (wi == 0 && lane == 0) AM_STAMP(j, 0);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {              // latent part: row pw + it, chunk = lane
+                const int pw = u * 64 + wi * 32;
+                const unsigned long long sp = reinterpret_cast<unsigned long long>(src[u]);
 #pragma unroll 8
-            for (int it = 0; it < 32; ++it) {          // latent part: row pw + it, chunk = lane
-                const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, it));
-                uint8_t* dst = kbuf + (lane >> 3) * 16384 + tc::sw128_chunk(pw + it, lane & 7);
-                if (rs) tc::cp_async16(tc::smem_u32(dst), rs + lane * 16);
-                else *reinterpret_cast<uint4*>(dst) = z;   // rows past the end must be exact zeros:
-            }                                              // 0 x (stale NaN code) would poison O
+                for (int it = 0; it < 32; ++it) {
+                    const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, it));
+                    uint8_t* dst = kbuf + (lane >> 3) * 16384 + tc::sw128_chunk(pw + it, lane & 7);
+                    if (rs) tc::cp_async16(tc::smem_u32(dst), rs + lane * 16);
+                    else *reinterpret_cast<uint4*>(dst) = z;   // rows past the end must be exact zeros:
+                }                                              // 0 x (stale NaN code) would poison O
+            }
             // the single rope buffer is free as soon as the rope MMAs of the previous tile are done
             ok = tc::mbar_wait(&bars.rope_free, (j & 1) ^ 1, abort_flag, 42);
             if (!ok) break;
 #pragma unroll
-            for (int it = 0; it < 4; ++it) {           // rope part: 8 rows per instruction, 4 chunks each
-                const int rl = it * 8 + (lane >> 2);
-                const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, rl));
-                uint8_t* dst = smem + SM_ROPE + sw64_chunk(pw + rl, lane & 3);
-                if (rs) tc::cp_async16(tc::smem_u32(dst), rs + 512 + (lane & 3) * 16);
-                else *reinterpret_cast<uint4*>(dst) = z;
+            for (int u = 0; u < 2; ++u) {              // rope part: 8 rows per instruction, 4 chunks each
+                const int pw = u * 64 + wi * 32;
+                const unsigned long long sp = reinterpret_cast<unsigned long long>(src[u]);
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int rl = it * 8 + (lane >> 2);
+                    const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, rl));
+                    uint8_t* dst = smem + SM_ROPE + sw64_chunk(pw + rl, lane & 3);
+                    if (rs) tc::cp_async16(tc::smem_u32(dst), rs + 512 + (lane & 3) * 16);
+                    else *reinterpret_cast<uint4*>(dst) = z;
+                }
+                s_tok[grp * 128 + pr[u]] = scale[u];
             }
-            s_tok[kb * 128 + p] = scale;
             tc::cp_async_commit();
-            locate(j + 1);               // next tile's address chain overlaps this tile's copies
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {              // the group's next tile becomes current
+                set_cur(u, r_n[u]);
+                r_n[u] = load_r(t_n[u]);
+                t_n[u] = load_t(j + 6, pr[u]);
+            }
             tc::cp_async_wait<0>();
             tc::fence_proxy_async();
-            if (p == 0) AM_STAMP(j, 1);
-            tc::mbar_arrive(&bars.k_full[kb]);
+            if (wi == 0 && lane == 0) AM_STAMP(j, 1);
+            tc::mbar_arrive(&bars.k_full[grp]);
         }
     } else if (warp == 8 && ntiles > 0) {
         // ------------------------------ MMA issuer ------------------------------------------------
@@ -265,6 +327,8 @@ attend_mma_kernel(AttendMmaArgs A) {
         // Two in-order instruction streams, QK(0..n-1) and PV(0..n-1), issued in READY order: whichever
         // has its operands first goes first (PV preferred: it is what frees a K buffer for the gather).
         int qk_next = 0, pv_next = 0, idle = 0;
+        ok = tc::mbar_wait(&bars.q_full, 0, abort_flag, 51);
+        tc::tc_fence_after();
         while (ok && pv_next < ntiles) {
             int can_pv = 0, can_qk = 0;
             if (lane == 0) {
@@ -477,6 +541,7 @@ attend_mma_kernel(AttendMmaArgs A) {
 
         // ---- epilogue ----
         if (ok && ntiles > 0) ok = tc::mbar_wait(&bars.pv_done, (ntiles - 1) & 1, abort_flag, 65);
+        if (tid == 0) AM_STAMP(0, 15);
         tc::tc_fence_after();
         // l per head: butterfly over the 32 token lanes, then across the 4 lane groups through shared memory
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
@@ -490,6 +555,7 @@ attend_mma_kernel(AttendMmaArgs A) {
             s_wmax[q4 * 64 + h0 + lane] = mine;
         }
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
+        if (tid == 0) AM_STAMP(1, 13);
         if (tid < AM_H) {
             const int h = tid;
             const float l = s_wmax[h] + s_wmax[64 + h] + s_wmax[128 + h] + s_wmax[192 + h];
@@ -506,7 +572,18 @@ attend_mma_kernel(AttendMmaArgs A) {
             s_muse[h] = l > 0.0f ? 1.0f / l : 0.0f;
         }
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
-        // O^T: this thread's TMEM lane is one latent dim of each 128-dim block; its 32 head columns
+        // O^T: this thread's TMEM lane is one latent dim of each 128-dim block; its 32 head columns.
+        // Single split: the sequence's [64][512] bf16 output is staged in the (now idle) K buffer 0 and
+        // written out as one contiguous 64 KiB block with 16-byte stores. Splits write f32 partials.
+        uint16_t* stage = reinterpret_cast<uint16_t*>(smem + SM_K0);
+        float inv_l[32];   // 1 / l of this thread's 32 heads (registers: the stores below must not wait on loads)
+#pragma unroll
+        for (int h = 0; h < 32; h += 4) {
+            const float4 m4 = *reinterpret_cast<const float4*>(s_muse + h0 + h);
+            inv_l[h] = m4.x; inv_l[h + 1] = m4.y; inv_l[h + 2] = m4.z; inv_l[h + 3] = m4.w;
+        }
+        float* part = A.n_splits > 1 ? A.partial + (size_t)b * A.n_splits * AM_H * (AM_KVL + 2) +
+                                           ((size_t)split * AM_H + h0) * AM_KVL : nullptr;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
             const int dim = c * 128 + row;
@@ -518,21 +595,32 @@ attend_mma_kernel(AttendMmaArgs A) {
 #pragma unroll
                 for (int h = 0; h < 32; ++h) r[h] = 0u;
             }
+            if (tid == 0) AM_STAMP(2, 12 + c);
+            if (part) {
 #pragma unroll
-            for (int hq = 0; hq < 32; ++hq) {
-                const int h = h0 + hq;
-                const float v = __uint_as_float(r[hq]);
-                if (A.n_splits > 1)
-                    A.partial[(size_t)b * A.n_splits * AM_H * (AM_KVL + 2) + ((size_t)split * AM_H + h) * AM_KVL + dim] = v;
-                else
-                    A.out[((size_t)b * AM_H + h) * AM_KVL + dim] = rv_f32_to_bf16(v * s_muse[h]);
+                for (int hq = 0; hq < 32; ++hq) part[hq * AM_KVL + dim] = __uint_as_float(r[hq]);
+            } else {
+                uint16_t* sp = stage + h0 * AM_KVL + dim;
+#pragma unroll
+                for (int hq = 0; hq < 32; ++hq) sp[hq * AM_KVL] = rv_f32_to_bf16(__uint_as_float(r[hq]) * inv_l[hq]);
             }
+        }
+        if (tid == 0) AM_STAMP(3, 12);
+        if (A.n_splits == 1) {
+            tc::named_barrier(1, AM_SOFTMAX_THREADS);
+            if (tid == 0) AM_STAMP(3, 13);
+            const uint4* sv = reinterpret_cast<const uint4*>(stage);
+            uint4* gv = reinterpret_cast<uint4*>(A.out + (size_t)b * AM_H * AM_KVL);
+#pragma unroll 4
+            for (int i = tid; i < AM_H * AM_KVL * 2 / 16; i += AM_SOFTMAX_THREADS) gv[i] = sv[i];
         }
     }
 
+    if (tid == 0) AM_STAMP(1, 14);
     tc::tc_fence_before();
     __syncthreads();
     if (warp == 8) tc::tmem_dealloc<512>(tmem);
+    if (tid == 0) AM_STAMP(1, 12);
     if (tid == 0 && *abort_flag) atomicCAS(A.err, 0, *abort_flag);
 }
 
@@ -551,10 +639,11 @@ extern "C" bool rivoli_attend_mma_supported(const DsaGeom* g) {
     return g->n_heads == AM_H && g->kv_lora == AM_KVL && g->rope_dim == AM_ROPE;
 }
 
-// scratch layout: [err 256 B][qa B*64 f32][qcodes B*128*576][partials]
+// scratch layout: [err 256 B][partials]. The error word is sticky: it keeps the first failure
+// until rivoli_attend_mma_status reads and clears it, so it must be zero before the first call.
 extern "C" size_t rivoli_attend_mma_scratch_bytes(const DsaGeom* g, int B) {
     const size_t part = mma_splits(B) > 1 ? (size_t)B * mma_splits(B) * AM_H * (AM_KVL + 2) * sizeof(float) : 0;
-    return 256 + align256((size_t)B * AM_H * 4) + align256((size_t)B * 128 * AM_W) + align256(part);
+    return 256 + align256(part);
 }
 
 extern "C" void rivoli_attend_combine_paged(const float* partial, int H, int kvl, int n_splits, int B, uint16_t* out,
@@ -566,19 +655,15 @@ extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q,
                                             uint16_t* out, float* out_m, float* out_lse, void* scratch,
                                             void* stream) {
     if (!scratch) return 1001;
-    if (((uintptr_t)latent_pool | (uintptr_t)scratch) & 15) return 1005;
+    if (((uintptr_t)latent_pool | (uintptr_t)scratch | (uintptr_t)q | (uintptr_t)out) & 15) return 1005;
     cudaStream_t st = (cudaStream_t)stream;
     uint8_t* sp = static_cast<uint8_t*>(scratch);
     int* err = reinterpret_cast<int*>(sp);
-    float* qa = reinterpret_cast<float*>(sp + 256);
-    uint8_t* qcodes = sp + 256 + align256((size_t)B * AM_H * 4);
-    float* partial = reinterpret_cast<float*>(qcodes + align256((size_t)B * 128 * AM_W));
+    float* partial = reinterpret_cast<float*>(sp + 256);
     const int n_splits = mma_splits(B);
 
     rv_drain_error();
-    attend_q_prepare_kernel<<<(B * AM_H + 7) / 8, 256, 0, st>>>(q, B * AM_H, g->softmax_scale, qcodes, qa, err);
-    if (int e = rv_launch_status()) return e;
-    AttendMmaArgs a{qcodes, qa, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
+    AttendMmaArgs a{q, g->softmax_scale, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
                     g->page_tokens, g->max_pages_per_seq, g->n_pool_pages, n_splits,
                     out, out_m, out_lse, n_splits > 1 ? partial : nullptr, err};
     cudaFuncSetAttribute(attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
@@ -597,6 +682,7 @@ extern "C" int rivoli_attend_mma_status(void* scratch, void* stream) {
     cudaError_t e = cudaMemcpyAsync(&h, scratch, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
     if (e != cudaSuccess) return -(int)e;
+    if (h) cudaMemsetAsync(scratch, 0, sizeof(int), (cudaStream_t)stream);
     return h ? 1008 : 0;
 }
 

@@ -31,6 +31,7 @@
 #include "tc_common.cuh"
 #include "tmap.hpp"
 #include "topk_core.cuh"
+#include <type_traits>
 
 namespace {
 
@@ -291,6 +292,17 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
 // ---------------------------------------------------------------------------------------------
 constexpr int RF_LIST = 2048;      // band tokens re-scored per round
 
+// Optional phase timeline of CTA 0 for tuning builds (-DRIVOLI_DEBUG_TIMES); compiled out otherwise.
+#ifdef RIVOLI_DEBUG_TIMES
+__device__ long long g_rf_times[16];
+#define RF_STAMP(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_rf_times[slot] = clock64(); } while (0)
+#else
+#define RF_STAMP(slot) do { } while (0)
+#endif
+
+// listed tokens a warp re-scores per pass: 4, or 2 where the key array leaves less shared memory
+__host__ __device__ constexpr int rf_tok(int ept) { return ept > 16 ? 2 : 4; }
+
 struct RefineArgs {
     DsaGeom g;
     const float* scores; int score_stride; const int32_t* seq_len;
@@ -298,20 +310,26 @@ struct RefineArgs {
     const uint8_t* index_pool; const float* index_scale; const int32_t* block_table;
     uint32_t* rows; int32_t* n_sel; int k;
     unsigned int* stats;   // [B][2]: band size, sure-in count (may be NULL)
+    int vec_ok;            // score rows and key scales allow 16-byte loads
 };
 
 template <int EPT>
 __global__ void __launch_bounds__(TK_THREADS)
 index_select_refine_kernel(RefineArgs A) {
+    // Thread t owns the EPT consecutive tokens t*EPT .. t*EPT+EPT-1 (keys in registers), so the
+    // score/scale loads are 16-byte vectors and the ascending write-out is one block-wide scan.
     extern __shared__ __align__(16) uint32_t rf_smem[];
-    __shared__ TkShared sh;
+    __shared__ TkSharedLite sh;
     __shared__ uint32_t list_n, n_band_total;
     const DsaGeom& g = A.g;
-    const int nh = g.index_heads, hd = g.index_dim, P = g.page_tokens;
+    constexpr int hd = IM_HD;                      // mma_geometry_ok: index_dim == IM_HD (one code word per lane)
+    constexpr int TOK = rf_tok(EPT);               // listed tokens a warp re-scores per pass
+    const int nh = g.index_heads, P = g.page_tokens;
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nt = min(A.seq_len[b], A.score_stride);
     const int kk = min(A.k, nt);
     uint32_t* out = A.rows + (size_t)b * A.k;
+    RF_STAMP(0);
     if (tid == 0) A.n_sel[b] = kk > 0 ? kk : 0;
     if (kk <= 0) return;
     if (kk == nt) {
@@ -319,126 +337,196 @@ index_select_refine_kernel(RefineArgs A) {
         if (tid == 0 && A.stats) { A.stats[b * 2] = 0; A.stats[b * 2 + 1] = (unsigned)nt; }
         return;
     }
-    // dynamic shared memory: keys[EPT*1024] | qf[hd][32] | kf[32 warps][hd] | list | bkey | pages
-    uint32_t* keys = rf_smem;
-    float* qf = reinterpret_cast<float*>(rf_smem + EPT * TK_THREADS);
+    // dynamic shared memory: qf[hd][32] | kf[32 warps][TOK tokens][hd] f32 | list | bkey | dec | keys[EPT*1024]
+    float* qf = reinterpret_cast<float*>(rf_smem);
     float* kfw = qf + hd * 32;
-    uint32_t* list = reinterpret_cast<uint32_t*>(kfw + TK_WARPS * hd);
-    uint32_t* bkey = list + RF_LIST;                      // exact keys of the listed tokens
-    int* s_pg = reinterpret_cast<int*>(bkey + RF_LIST);
+    uint32_t* list = reinterpret_cast<uint32_t*>(kfw + TK_WARPS * TOK * hd);
+    uint32_t* bkey = list + RF_LIST;               // exact keys of the listed tokens
+    uint32_t* dec = bkey + RF_LIST;                // 1 = the listed token is selected
+    uint32_t* keys = dec + RF_LIST;                // whole key array: tie-dominated (overflow) path only
 
-    const int n_pages = (nt + P - 1) / P;
-    for (int i = tid; i < n_pages; i += TK_THREADS) {
-        int pg = A.block_table[(size_t)b * g.max_pages_per_seq + i];
-        s_pg[i] = (pg < 0 || pg >= g.n_pool_pages) ? 0 : pg;
+    // ---- approximate keys: (unscaled tensor-core score) * key scale of the token -------------------
+    const float* s = A.scores + (size_t)b * A.score_stride;
+    const int32_t* bt = A.block_table + (size_t)b * g.max_pages_per_seq;
+    const int i0 = tid * EPT;
+    const int nvalid = max(0, min(EPT, nt - i0));
+    float sc[EPT], sk[EPT];
+    if (A.vec_ok && nvalid == EPT) {
+        size_t r[EPT / 4];
+#pragma unroll
+        for (int j4 = 0; j4 < EPT / 4; ++j4) {
+            const int i = i0 + j4 * 4;
+            int pg = bt[i / P];
+            pg = (pg < 0 || pg >= g.n_pool_pages) ? 0 : pg;
+            r[j4] = (size_t)pg * P + (i & (P - 1));
+        }
+#pragma unroll
+        for (int j4 = 0; j4 < EPT / 4; ++j4) {
+            const float4 a = *reinterpret_cast<const float4*>(s + i0 + j4 * 4);
+            const float4 c = *reinterpret_cast<const float4*>(A.index_scale + r[j4]);
+            sc[j4 * 4] = a.x; sc[j4 * 4 + 1] = a.y; sc[j4 * 4 + 2] = a.z; sc[j4 * 4 + 3] = a.w;
+            sk[j4 * 4] = c.x; sk[j4 * 4 + 1] = c.y; sk[j4 * 4 + 2] = c.z; sk[j4 * 4 + 3] = c.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int i = i0 + j;
+            sc[j] = 0.0f; sk[j] = 0.0f;
+            if (j < nvalid) {
+                int pg = bt[i / P];
+                pg = (pg < 0 || pg >= g.n_pool_pages) ? 0 : pg;
+                sc[j] = s[i];
+                sk[j] = A.index_scale[(size_t)pg * P + (i & (P - 1))];
+            }
+        }
     }
-    for (int e = tid; e < hd * 32; e += TK_THREADS) {   // e = h * hd + d: coalesced byte reads, transposed store
-        const int h = e / hd, d = e - h * hd;
-        qf[d * 32 + h] = h < nh ? rv_e4m3_to_f32(A.qcodes[((size_t)b * nh + h) * hd + d]) : 0.0f;
+    // q codes as f32, transposed to [dim][head] (lane = head on both sides: no bank conflicts)
+    for (int e = tid; e < 32 * (hd / 4); e += TK_THREADS) {
+        const int h = e & 31, d4 = e >> 5;
+        const uint32_t cw = h < nh ? *reinterpret_cast<const uint32_t*>(A.qcodes + ((size_t)b * nh + h) * hd + d4 * 4) : 0u;
+        const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw >> 16));
+        qf[(d4 * 4 + 0) * 32 + h] = x.x; qf[(d4 * 4 + 1) * 32 + h] = x.y;
+        qf[(d4 * 4 + 2) * 32 + h] = y.x; qf[(d4 * 4 + 3) * 32 + h] = y.y;
     }
     if (tid == 0) { list_n = 0; n_band_total = 0; }
-    __syncthreads();
-
-    // approximate score = (unscaled score from the tensor-core pass) * key scale of the token;
-    // keys live in registers (element j of this thread is token tid + 1024 j) and in shared memory
-    const float* s = A.scores + (size_t)b * A.score_stride;
     uint32_t key[EPT];
     float skm = 0.0f;
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
-        const int i = tid + j * TK_THREADS;
-        uint32_t u = 0u;
-        if (i < nt) {
-            const float sk = A.index_scale[(size_t)s_pg[i / P] * P + (i & (P - 1))];
-            u = topk_key(s[i] * sk);
-            skm = fmaxf(skm, sk);
-        }
-        key[j] = u;
-        keys[i] = u;
+        key[j] = j < nvalid ? topk_key(sc[j] * sk[j]) : 0u;
+        skm = fmaxf(skm, sk[j]);
     }
+    RF_STAMP(2);
     int buf = 0;
-    const float sk_max = __uint_as_float(tk_block_max(__float_as_uint(skm), sh, buf));
+    const float sk_max = __uint_as_float(tk_block_max(__float_as_uint(skm), sh, buf));   // also orders qf / list_n
     const float eps = sk_max * A.cb[b];
+    RF_STAMP(3);
 
     // k-th largest approximate score, located to 20 key bits: A_k lies in [T, T + 0xfff]
     const uint32_t T20 = tk_bisect<EPT>(key, (uint32_t)kk, 20, sh, buf);
     const float lo_f = topk_unkey(T20) - 2.0f * eps, hi_f = topk_unkey(T20 | 0xfffu) + 2.0f * eps;
     const uint32_t k_lo = lo_f == lo_f ? topk_key(lo_f) : 0u;
     const uint32_t k_hi = hi_f == hi_f ? topk_key(hi_f) : 0xffffffffu;
+    RF_STAMP(4);
+
+    // classify from registers: surely selected / band (re-scored exactly) / surely not
+    uint32_t m_in = 0u, m_band = 0u;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        if (j < nvalid) {
+            if (key[j] > k_hi) m_in |= 1u << j;
+            else if (key[j] >= k_lo) m_band |= 1u << j;
+        }
+    }
+    const uint32_t n_in = tk_block_sum((uint32_t)__popc(m_in), sh, buf);
+    // list positions: one shared-memory atomic per warp, order inside the list is irrelevant
+    uint32_t my_pos;
+    {
+        const uint32_t cnt = (uint32_t)__popc(m_band);
+        uint32_t incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        uint32_t wbase = 0u;
+        if (lane == 31 && incl) wbase = atomicAdd(&list_n, incl);
+        wbase = __shfl_sync(0xffffffffu, wbase, 31);
+        my_pos = wbase + incl - cnt;
+        uint32_t pos = my_pos;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j)
+            if (m_band & (1u << j)) { if (pos < RF_LIST) list[pos] = (uint32_t)(i0 + j); ++pos; }
+    }
+    __syncthreads();
+    const uint32_t n_band = list_n;
+    RF_STAMP(5);
 
     // this lane's head constants for the exact re-score (nh <= 32)
     const float my_sq = lane < nh ? A.qscales[(size_t)b * nh + lane] : 0.0f;
     const float my_wh = lane < nh ? __fmul_rn(A.w[(size_t)b * nh + lane], g.index_wscale) : 0.0f;
 
-    uint32_t my_in = 0;       // tokens this thread classified as surely selected
-    int rounds = 0;           // re-score rounds flushed so far (0 or 1 in the common case)
-#pragma unroll 1
-    for (int j = 0; j < EPT; ++j) {
-        const int i = tid + j * TK_THREADS;
-        bool band = false;
-        if (i < nt) {
-            const uint32_t u = keys[i];
-            if (u > k_hi) { keys[i] = 0xffffffffu; ++my_in; }   // surely selected
-            else if (u < k_lo) keys[i] = 0u;                      // surely not
-            else band = true;
-        }
-        const uint32_t mb = __ballot_sync(0xffffffffu, band);
-        uint32_t wbase = 0;
-        if (lane == 0 && mb) wbase = atomicAdd(&list_n, (uint32_t)__popc(mb));
-        wbase = __shfl_sync(0xffffffffu, wbase, 0);
-        if (band) list[wbase + __popc(mb & ((1u << lane) - 1u))] = (uint32_t)i;
-        __syncthreads();
-        const uint32_t ln = list_n;
-        if (ln > RF_LIST - TK_THREADS || j == EPT - 1) {
-            // exact re-score of the listed tokens: one warp per token, lane = head; the code dot
-            // is the sequential f32 fold of rivoli_index_score_paged, heads fold ascending
-            for (uint32_t q2 = warp; q2 < ln; q2 += TK_WARPS) {
-                const int t = (int)list[q2];
-                const size_t r = (size_t)s_pg[t / P] * P + (t & (P - 1));
-                float* kf = kfw + warp * hd;
-                for (int d4 = lane; d4 < hd / 4; d4 += 32) {
-                    const uint32_t cw = *reinterpret_cast<const uint32_t*>(A.index_pool + r * hd + d4 * 4);
-                    const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw >> 16));
-                    *reinterpret_cast<float4*>(kf + d4 * 4) = make_float4(x.x, x.y, y.x, y.y);
+    // exact score of listed tokens: a pass covers 32*TOK of them, warp w taking positions
+    // base + w, base + 32 + w, ... (an even split; their loads are in flight together and they
+    // share the q reads): lane = head; the code dot is the sequential f32 fold of
+    // rivoli_index_score_paged, heads fold ascending. Writes the exact key by list position
+    // (and into keys[] when asked).
+    auto rescore = [&](uint32_t ln, bool to_keys) {
+        float* kf = kfw + warp * (TOK * hd);
+        for (uint32_t base = 0; base < ln; base += TK_WARPS * TOK) {
+            if (base + warp >= ln) break;
+            const int n_here = min(TOK, (int)((ln - base - warp + TK_WARPS - 1) / TK_WARPS));   // warp-uniform, >= 1
+            uint32_t cw[TOK];
+            float skv[TOK];
+#pragma unroll
+            for (int e = 0; e < TOK; ++e) {
+                cw[e] = 0u; skv[e] = 0.0f;
+                if (e < n_here) {
+                    const int t = (int)list[base + e * TK_WARPS + warp];
+                    int pg = bt[t / P];
+                    pg = (pg < 0 || pg >= g.n_pool_pages) ? 0 : pg;
+                    const size_t r = (size_t)pg * P + (t & (P - 1));
+                    cw[e] = *reinterpret_cast<const uint32_t*>(A.index_pool + r * hd + lane * 4);
+                    skv[e] = A.index_scale[r];
                 }
-                const float sk = A.index_scale[r];
-                __syncwarp();
-                float cd = 0.0f;
+            }
+#pragma unroll
+            for (int e = 0; e < TOK; ++e) {
+                const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw[e] & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw[e] >> 16));
+                *reinterpret_cast<float4*>(kf + e * hd + lane * 4) = make_float4(x.x, x.y, y.x, y.y);
+            }
+            __syncwarp();
+            float cd[TOK];
+#pragma unroll
+            for (int e = 0; e < TOK; ++e) cd[e] = 0.0f;
+            auto fold = [&](auto ntok) {
+                constexpr int NT = decltype(ntok)::value < TOK ? decltype(ntok)::value : TOK;
 #pragma unroll 4
                 for (int d = 0; d < hd; d += 4) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(kf + d);   // broadcast read
-                    cd = fmaf(qf[(d + 0) * 32 + lane], k4.x, cd);
-                    cd = fmaf(qf[(d + 1) * 32 + lane], k4.y, cd);
-                    cd = fmaf(qf[(d + 2) * 32 + lane], k4.z, cd);
-                    cd = fmaf(qf[(d + 3) * 32 + lane], k4.w, cd);
+                    const float q0f = qf[(d + 0) * 32 + lane], q1f = qf[(d + 1) * 32 + lane];
+                    const float q2f = qf[(d + 2) * 32 + lane], q3f = qf[(d + 3) * 32 + lane];
+#pragma unroll
+                    for (int e = 0; e < NT; ++e) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(kf + e * hd + d);   // broadcast read
+                        cd[e] = fmaf(q0f, k4.x, cd[e]);
+                        cd[e] = fmaf(q1f, k4.y, cd[e]);
+                        cd[e] = fmaf(q2f, k4.z, cd[e]);
+                        cd[e] = fmaf(q3f, k4.w, cd[e]);
+                    }
                 }
-                const float dot = __fmul_rn(__fmul_rn(cd, my_sq), sk);
+            };
+            if (n_here >= TOK) fold(std::integral_constant<int, TOK>{});
+            else if (n_here == 1) fold(std::integral_constant<int, 1>{});
+            else if (n_here == 2) fold(std::integral_constant<int, 2>{});
+            else fold(std::integral_constant<int, 3>{});
+            __syncwarp();
+#pragma unroll
+            for (int e = 0; e < TOK; ++e) {
+                const float dot = __fmul_rn(__fmul_rn(cd[e], my_sq), skv[e]);
                 float rr = __fmul_rn(dot, g.index_dscale);
                 rr = rr > 0.0f ? rr : 0.0f;
-                const float cth = __fmul_rn(my_wh, rr);
+                kf[e * hd + lane] = __fmul_rn(my_wh, rr);
+            }
+            __syncwarp();
+            if (lane < n_here) {
                 float acc = 0.0f;
-                for (int h = 0; h < nh; ++h) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, cth, h));
-                if (lane == 0) {
-                    uint32_t ku = topk_key(acc);
-                    ku = ku == 0xffffffffu ? 0xfffffffeu : (ku == 0u ? 1u : ku);
-                    keys[t] = ku;
-                    bkey[q2] = ku;
-                }
-                __syncwarp();
+                for (int h = 0; h < nh; ++h) acc = __fadd_rn(acc, kf[lane * hd + h]);
+                uint32_t ku = topk_key(acc);
+                ku = ku == 0xffffffffu ? 0xfffffffeu : (ku == 0u ? 1u : ku);
+                const uint32_t q2 = base + lane * TK_WARPS + warp;
+                bkey[q2] = ku;
+                if (to_keys) keys[list[q2]] = ku;
             }
-            __syncthreads();
-            if (j != EPT - 1) {   // an early flush: the list does not hold the whole band any more
-                ++rounds;
-                if (tid == 0) { n_band_total += ln; list_n = 0; }
-                __syncthreads();
-            }
+            __syncwarp();
         }
-    }
-    const uint32_t n_band = list_n;           // tokens of the LAST round (all of them if rounds == 0)
-    if (rounds == 0) {
+    };
+
+    if (n_band <= RF_LIST) {
         // Common case: the whole band sits in list/bkey. Rank each band token among the band by
         // (exact key descending, index ascending); the selection takes the (kk - n_in) best.
-        const uint32_t n_in = tk_block_sum(my_in, sh, buf);
+        rescore(n_band, false);
+        __syncthreads();
+        RF_STAMP(6);
         const uint32_t take = (uint32_t)kk - n_in;   // >= 1: at most kk - 1 tokens lie above the band
         for (uint32_t q2 = warp; q2 < n_band; q2 += TK_WARPS) {
             const uint32_t kq = bkey[q2], tq = list[q2];
@@ -448,27 +536,48 @@ index_select_refine_kernel(RefineArgs A) {
                 c += (kj > kq || (kj == kq && list[j2] < tq)) ? 1u : 0u;
             }
             c = __reduce_add_sync(0xffffffffu, c);
-            if (lane == 0) keys[tq] = c < take ? 0xffffffffu : 0u;
+            if (lane == 0) dec[q2] = c < take ? 1u : 0u;
         }
         __syncthreads();
-        auto key_at = [&](int i) -> uint32_t { return keys[i]; };
-        tk_compact(key_at, nt, (uint32_t)kk, 0xfffffffeu, 0u, sh, out);
+        RF_STAMP(7);
+        uint32_t pos = my_pos;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            uint32_t u = (m_in >> j) & 1u;
+            if (m_band & (1u << j)) { u = dec[pos]; ++pos; }
+            key[j] = u ? 0xffffffffu : 0u;
+        }
+        tk_compact_contig<EPT>(key, nt, 0xfffffffeu, 0u, sh, out);
         if (tid == 0 && A.stats) { A.stats[b * 2] = n_band; A.stats[b * 2 + 1] = n_in; }
+        RF_STAMP(8);
         return;
     }
-    // Rare case (tie-dominated scores): the band did not fit one list. Exact selection over the
-    // whole key array: sure-in = max key, band = exact keys, sure-out = 0.
-    if (tid == 0) n_band_total += n_band;
+    // Rare case (tie-dominated scores): the band does not fit the list. The key array goes to
+    // shared memory (sure-in = max key, sure-out = 0), the band is re-scored in token chunks of
+    // RF_LIST (so a chunk's band always fits), then an exact selection runs over the whole array.
 #pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-        const int i = tid + j * TK_THREADS;
-        key[j] = i < nt ? keys[i] : 0u;
+    for (int j = 0; j < EPT; ++j)
+        if (j < nvalid) keys[i0 + j] = ((m_in >> j) & 1u) ? 0xffffffffu : 0u;
+    for (int c0 = 0; c0 < nt; c0 += RF_LIST) {
+        __syncthreads();
+        if (tid == 0) list_n = 0;
+        __syncthreads();
+        if (i0 >= c0 && i0 < c0 + RF_LIST) {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j)
+                if (m_band & (1u << j)) list[atomicAdd(&list_n, 1u)] = (uint32_t)(i0 + j);
+        }
+        __syncthreads();
+        const uint32_t ln = list_n;
+        rescore(ln, true);
+        if (tid == 0) n_band_total += ln;
     }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) key[j] = j < nvalid ? keys[i0 + j] : 0u;
     const uint32_t pivot = tk_bisect<EPT>(key, (uint32_t)kk, 32, sh, buf);
     const uint32_t need = (uint32_t)kk - tk_count_gt<EPT>(key, pivot, sh, buf);
-    __syncthreads();
-    auto key_at = [&](int i) -> uint32_t { return keys[i]; };
-    tk_compact(key_at, nt, (uint32_t)kk, pivot, need, sh, out);
+    tk_compact_contig<EPT>(key, nt, pivot, need, sh, out);
     if (tid == 0 && A.stats) { A.stats[b * 2] = n_band_total; A.stats[b * 2 + 1] = 0; }
 }
 
@@ -494,7 +603,7 @@ SelectScratch carve(const DsaGeom* g, int B, int score_stride, void* scratch, si
     return s;
 }
 
-constexpr int RF_MAX_NT = 32 * 1024;   // keys 128 KiB + q 16 + key rows 16 + list 8 + histograms 34 < 227 KiB
+constexpr int RF_MAX_NT = 32 * 1024;   // keys 128 KiB + q 16 + key rows 32 + lists 24 = 200 KiB < 227 KiB
 
 bool mma_geometry_ok(const DsaGeom* g, int score_stride) {
     return g->index_dim == IM_HD && g->index_heads <= IM_NPAD && g->page_tokens >= 16 && g->page_tokens <= IM_TILE &&
@@ -565,12 +674,12 @@ RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index
     if (int e = rv_launch_status()) return e;
 
     RefineArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb, s.skmax,
-                  index_pool, index_scale, block_table, rows, n_sel, g->top_k, s.stats};
-    const int n_pages_max = (score_stride + g->page_tokens - 1) / g->page_tokens;
+                  index_pool, index_scale, block_table, rows, n_sel, g->top_k, s.stats,
+                  (score_stride % 4 == 0 && ((uintptr_t)index_scale & 15) == 0 && g->page_tokens % 4 == 0) ? 1 : 0};
 #define RV_REFINE(EPT)                                                                                            \
     do {                                                                                                          \
-        const size_t smem2 = ((size_t)(EPT) * TK_THREADS + (size_t)hd * 32 + (size_t)TK_WARPS * hd + 2 * RF_LIST +\
-                              (size_t)n_pages_max) * 4;                                                           \
+        const size_t smem2 = ((size_t)(EPT) * TK_THREADS + (size_t)hd * 32 + (size_t)TK_WARPS * rf_tok(EPT) * hd +\
+                              3 * RF_LIST) * 4;                                                                   \
         cudaFuncSetAttribute(index_select_refine_kernel<EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
                              (int)smem2);                                                                         \
         index_select_refine_kernel<EPT><<<B, TK_THREADS, smem2, st>>>(ra);                                        \
@@ -607,3 +716,9 @@ RIVOLI_API int rivoli_index_select_band_stats(const DsaGeom* g, int B, int score
     if (e == cudaSuccess) e = cudaMemcpy2D(host_band, 4, s.stats, 8, 4, (size_t)B, cudaMemcpyDeviceToHost);
     return e == cudaSuccess ? 0 : -(int)e;
 }
+
+#ifdef RIVOLI_DEBUG_TIMES
+extern "C" __attribute__((visibility("default"))) int rivoli_refine_debug_times(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_rf_times, sizeof(long long) * 16);
+}
+#endif

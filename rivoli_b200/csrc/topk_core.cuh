@@ -27,10 +27,17 @@ struct TkShared {
     uint32_t pivot, need;
 };
 
+// The part of TkShared the register-resident primitives need (block reductions and scans).
+struct TkSharedLite {
+    uint32_t wcnt[TK_WARPS];
+    uint32_t red[2][TK_WARPS];
+};
+
 // Block-wide sum with ONE barrier per call: per-warp partials go to red[buf], every warp then
 // re-reduces the 32 partials. `buf` alternates between calls, which is what makes the single
 // barrier sufficient (a warp can be at most one call ahead of the slowest one).
-__device__ __forceinline__ uint32_t tk_block_sum(uint32_t v, TkShared& sh, int& buf) {
+template <class SH>
+__device__ __forceinline__ uint32_t tk_block_sum(uint32_t v, SH& sh, int& buf) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     v = __reduce_add_sync(0xffffffffu, v);
     if (lane == 0) sh.red[buf][warp] = v;
@@ -40,7 +47,8 @@ __device__ __forceinline__ uint32_t tk_block_sum(uint32_t v, TkShared& sh, int& 
     return t;
 }
 
-__device__ __forceinline__ uint32_t tk_block_max(uint32_t v, TkShared& sh, int& buf) {
+template <class SH>
+__device__ __forceinline__ uint32_t tk_block_max(uint32_t v, SH& sh, int& buf) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     v = __reduce_max_sync(0xffffffffu, v);
     if (lane == 0) sh.red[buf][warp] = v;
@@ -51,13 +59,13 @@ __device__ __forceinline__ uint32_t tk_block_max(uint32_t v, TkShared& sh, int& 
 }
 
 // k-th largest key by bisection on the key bits, MSB first, over keys held in REGISTERS
-// (element j of thread t is index t + j * 1024; slots past the end hold 0 and never count).
+// (any fixed assignment of elements to threads; slots past the end hold 0 and never count).
 // After `nbits` steps the result T has its low (32 - nbits) bits clear and satisfies
 //   #(key >= T) >= kk   and   #(key >= T + 2^(32-nbits)) < kk   (or that sum overflows),
 // so with nbits = 32 T is exactly the kk-th largest key. No atomics, no data-dependent cost:
 // tie-dominated arrays take the same time as random ones.
-template <int EPT>
-__device__ __forceinline__ uint32_t tk_bisect(const uint32_t (&key)[EPT], uint32_t kk, int nbits, TkShared& sh, int& buf) {
+template <int EPT, class SH>
+__device__ __forceinline__ uint32_t tk_bisect(const uint32_t (&key)[EPT], uint32_t kk, int nbits, SH& sh, int& buf) {
     uint32_t T = 0u;
     for (int bit = 31; bit >= 32 - nbits; --bit) {
         const uint32_t cand = T | (1u << bit);
@@ -69,8 +77,45 @@ __device__ __forceinline__ uint32_t tk_bisect(const uint32_t (&key)[EPT], uint32
     return T;
 }
 
-template <int EPT>
-__device__ __forceinline__ uint32_t tk_count_gt(const uint32_t (&key)[EPT], uint32_t T, TkShared& sh, int& buf) {
+// Ascending compaction for keys held in registers with CONTIGUOUS ownership (thread t holds
+// elements t*EPT .. t*EPT+EPT-1): one packed block-wide exclusive scan of (#key > pivot,
+// #key == pivot), then every thread writes its own selected indices in order. Same slot rule
+// as tk_compact. One barrier. Every thread must call it.
+template <int EPT, class SH>
+__device__ __forceinline__ void tk_compact_contig(const uint32_t (&key)[EPT], int nt, uint32_t pivot, uint32_t need,
+                                                  SH& sh, uint32_t* __restrict__ out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int i0 = tid * EPT;
+    uint32_t v = 0u;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const bool live = i0 + j < nt;
+        v += (live && key[j] > pivot) ? 1u : 0u;
+        v += (live && key[j] == pivot) ? 0x10000u : 0u;
+    }
+    uint32_t incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) sh.wcnt[warp] = incl;
+    __syncthreads();
+    const uint32_t cw = sh.wcnt[lane];
+    const uint32_t excl = __reduce_add_sync(0xffffffffu, lane < warp ? cw : 0u) + incl - v;
+    uint32_t g = excl & 0xffffu, e = excl >> 16;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const int i = i0 + j;
+        if (i < nt) {
+            if (key[j] > pivot) { out[g + (e < need ? e : need)] = (uint32_t)i; ++g; }
+            else if (key[j] == pivot) { if (e < need) out[g + e] = (uint32_t)i; ++e; }
+        }
+    }
+}
+
+template <int EPT, class SH>
+__device__ __forceinline__ uint32_t tk_count_gt(const uint32_t (&key)[EPT], uint32_t T, SH& sh, int& buf) {
     uint32_t c = 0;
 #pragma unroll
     for (int j = 0; j < EPT; ++j) c += key[j] > T ? 1u : 0u;
