@@ -237,15 +237,20 @@ def run_ours(args):
     row_pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=device)
     seq_len = torch.full((B,), ctx, dtype=torch.int32, device=device)
 
-    def step(inp, timed=None):
-        ev = timed
-        if ev: ev[0].record()
+    def step(inp):
+        # the call a device-resident caller makes: 4 launches (append + query prologue, scorer,
+        # selection, attention)
+        layer.step(inp["latent"], inp["index_key"], inp["index_q"], inp["index_w"], inp["q"], row_pos, seq_len)
+
+    def step_staged(inp, ev):
+        # the same work through the three separate operators, with an event between stages
+        ev[0].record()
         layer.append(inp["latent"], inp["index_key"], row_pos)
-        if ev: ev[1].record()
+        ev[1].record()
         layer.select(inp["index_q"], inp["index_w"], seq_len)
-        if ev: ev[2].record()
+        ev[2].record()
         layer.attend(inp["q"])
-        if ev: ev[3].record()
+        ev[3].record()
 
     def barrier():
         if world > 1:
@@ -261,18 +266,23 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     sampler.mark()
     t0.record()
     for i in range(args.steps):
-        step(x, evs[i])
+        step(x)
     t1.record()
     barrier()
     sampler.mark()
-    clocks = sampler.stop() if rank == 0 else None
     ms_total = t0.elapsed_time(t1)
+    # per-stage durations (for the roofline objects): separate operator calls, outside the timed region
+    n_st = min(args.steps, 100)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_st)]
+    for i in range(n_st):
+        step_staged(x, evs[i])
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
     stage_ms = [float(np.mean([e[i].elapsed_time(e[i + 1]) for e in evs])) for i in range(3)]
 
     # ---- end to end through the host-facing call: pinned host inputs, device->host result ------------
@@ -337,7 +347,7 @@ def run_ours(args):
             "config": config_of(args.workload, w, world),
             "e2e": {"value": world * args.steps / (ms_e2e * 1e-3), "unit": "layer-steps/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * 6,   # append, 2 q-prepare, score, refine, attend (no combine at 1 split)
+            "gpu_launches": args.steps * 4,   # append + query prologue, scorer, selection, attention (1 split: no combine)
             "stage_ms": {"append": stage_ms[0], "index_select": stage_ms[1], "attend": stage_ms[2]},
             "roofline": {"bound": "hbm", "kernel": f"{dom} stage: {stage_kernels[dom]}",
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
@@ -369,11 +379,11 @@ def run_profile(args):
     seq_len = torch.full((w["B"],), w["ctx"], dtype=torch.int32, device=device)
     layer.select(x["index_q"], x["index_w"], seq_len)      # rows for the attend-only mode
     for _ in range(3):
-        if args.profile in ("step",):
-            layer.append(x["latent"], x["index_key"], row_pos)
-        if args.profile in ("select", "step"):
+        if args.profile == "step":       # exactly what the bench's timed region launches
+            layer.step(x["latent"], x["index_key"], x["index_q"], x["index_w"], x["q"], row_pos, seq_len)
+        if args.profile == "select":
             layer.select(x["index_q"], x["index_w"], seq_len)
-        if args.profile in ("attend", "step"):
+        if args.profile == "attend":
             layer.attend(x["q"])
     torch.cuda.synchronize(device)
     layer.check_status()

@@ -168,6 +168,17 @@ int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index_q, const f
                               const int32_t* block_table, const int32_t* seq_len, int B,
                               int score_stride, uint32_t* rows, int32_t* n_sel, void* scratch,
                               void* stream);
+/* The first half of a decode layer-step in one call: append the step's new token of every
+ * sequence (row b of latent / index_key belongs to sequence b at position row_pos[b]) and select
+ * the attended rows; the append rides in the launch that prepares the indexer query, one launch
+ * fewer than rivoli_kv_append_paged + rivoli_index_select_paged and bit-identical to them.
+ * No counterpart in the reference, whose engine issues cache_and_absorb and the indexer launches
+ * separately (crates/engine/src/glm/attn.rs:119-222). */
+int rivoli_dsa_append_select_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,
+                                   const int32_t* row_pos, const int32_t* block_table, uint8_t* latent_pool,
+                                   float* latent_scale, uint8_t* index_pool, float* index_scale, int32_t* status,
+                                   const uint16_t* index_q, const float* w, const int32_t* seq_len, int B,
+                                   int score_stride, uint32_t* rows, int32_t* n_sel, void* scratch, void* stream);
 /* Synchronises `stream` and returns 1008 if a bounded device-side wait of the last
  * rivoli_index_select_paged call gave up (results are then undefined), else 0. */
 int rivoli_index_select_status(const DsaGeom* g, int B, int score_stride, void* scratch, void* stream);

@@ -209,6 +209,16 @@ def launch_index_select_paged(g: DsaGeom, index_q, w, index_pool, index_scale, b
                                                   _ptr(scratch), _stream(stream)), "index_select_paged")
 
 
+def launch_dsa_append_select_paged(g: DsaGeom, latent, index_key, row_pos, block_table, latent_pool, latent_scale,
+                                   index_pool, index_scale, status, index_q, w, seq_len, B: int, score_stride: int,
+                                   rows, n_sel, scratch, stream=None) -> None:
+    ensure_status(lib().rivoli_dsa_append_select_paged(
+        C.byref(g), _ptr(latent), _ptr(index_key), _ptr(row_pos), _ptr(block_table), _ptr(latent_pool),
+        _ptr(latent_scale), _ptr(index_pool), _ptr(index_scale), _ptr(status), _ptr(index_q), _ptr(w), _ptr(seq_len),
+        C.c_int(B), C.c_int(score_stride), _ptr(rows), _ptr(n_sel), _ptr(scratch), _stream(stream)),
+        "dsa_append_select_paged")
+
+
 def index_select_status(g: DsaGeom, B: int, score_stride: int, scratch, stream=None) -> None:
     """Synchronises; raises BackendError(1008) if a bounded device-side wait gave up."""
     ensure_status(lib().rivoli_index_select_status(C.byref(g), C.c_int(B), C.c_int(score_stride), _ptr(scratch),

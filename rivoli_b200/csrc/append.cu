@@ -10,6 +10,7 @@
 // IEEE division by the scale, packed code stores (16 bytes per lane on the latent row).
 #include "codec.cuh"
 #include "common.cuh"
+#include "quant.cuh"
 
 // ------------------------------------------------------------------------------------------
 // Reference layout: one token, f32 in, block of 128 per scale.
@@ -70,94 +71,6 @@ RIVOLI_API int rivoli_index_append(const float* k, unsigned short* kcache, int p
     return rv_launch_status();
 }
 
-// ------------------------------------------------------------------------------------------
-// Paged layout. One warp per token row; 4 rows per CTA.
-//   latent row (c_kv | k_rope, <= 1024 values, one scale): lane owns two 16-value chunks.
-//   key (index_dim <= 512, one scale):                      lane owns one 16-value chunk.
-// Every store is one 16-byte vector. A lane whose chunk lies past the vector's end
-// contributes 0 to the absmax and stores nothing, so any multiple of 16 works.
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void unpack8(const uint4& p, float* f) {
-    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-
-// Quantise a vector of `n` bf16 values (n % 16 == 0, n <= 512) cooperatively across a
-// warp; returns the scale (all lanes) and stores 16 codes per active lane.
-__device__ __forceinline__ float quant_vec16(const uint16_t* __restrict__ src, int n, uint8_t* __restrict__ dst,
-                                             int lane) {
-    float f[16];
-    const bool act = lane * 16 < n;
-    if (act) {
-        const uint4* p = reinterpret_cast<const uint4*>(src + lane * 16);
-        unpack8(p[0], f);
-        unpack8(p[1], f + 8);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) f[i] = 0.0f;
-    }
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
-    amax = rv_warp_max(amax);
-    const float scl = rv_scale_from_amax(amax);
-    if (act) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t lo = rv_f32x2_to_e4m3x2(__fdiv_rn(f[4 * i], scl), __fdiv_rn(f[4 * i + 1], scl));
-            uint32_t hi = rv_f32x2_to_e4m3x2(__fdiv_rn(f[4 * i + 2], scl), __fdiv_rn(f[4 * i + 3], scl));
-            w[i] = lo | (hi << 16);
-        }
-        *reinterpret_cast<uint4*>(dst + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    return scl;
-}
-
-// A row of up to 1024 bf16 values (n % 16 == 0) under ONE scale: lane owns the 16-value chunks
-// lane and lane + 32, so each store is still a single 16-byte vector.
-__device__ __forceinline__ float quant_row_wide(const uint16_t* __restrict__ src, int n, uint8_t* __restrict__ dst,
-                                                int lane) {
-    float f[2][16];
-    bool act[2];
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-        act[c] = (lane + 32 * c) * 16 < n;
-        if (act[c]) {
-            const uint4* p = reinterpret_cast<const uint4*>(src + (lane + 32 * c) * 16);
-            unpack8(p[0], f[c]);
-            unpack8(p[1], f[c] + 8);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) f[c][i] = 0.0f;
-        }
-    }
-    float amax = 0.0f;
-#pragma unroll
-    for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[c][i]));
-    amax = rv_warp_max(amax);
-    const float scl = rv_scale_from_amax(amax);
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-        if (!act[c]) continue;
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t lo = rv_f32x2_to_e4m3x2(__fdiv_rn(f[c][4 * i], scl), __fdiv_rn(f[c][4 * i + 1], scl));
-            uint32_t hi = rv_f32x2_to_e4m3x2(__fdiv_rn(f[c][4 * i + 2], scl), __fdiv_rn(f[c][4 * i + 3], scl));
-            w[i] = lo | (hi << 16);
-        }
-        *reinterpret_cast<uint4*>(dst + (lane + 32 * c) * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    return scl;
-}
-
 __global__ void __launch_bounds__(128)
 kv_append_paged_kernel(DsaGeom g, const uint16_t* __restrict__ latent, const uint16_t* __restrict__ index_key,
                        const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_pos, int n_rows,
@@ -167,26 +80,8 @@ kv_append_paged_kernel(DsaGeom g, const uint16_t* __restrict__ latent, const uin
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= n_rows) return;
-    const int seq = row_seq ? row_seq[row] : row;
-    const int pos = row_pos[row];
-    const int w = g.kv_lora + g.rope_dim;
-    const int lp = pos / g.page_tokens;
-    int page = -1;
-    if (pos >= 0 && lp < g.max_pages_per_seq) page = block_table[(size_t)seq * g.max_pages_per_seq + lp];
-    if (page < 0 || page >= g.n_pool_pages) {
-        if (lane == 0 && status) atomicOr(status, 1);
-        return;
-    }
-    const size_t r = (size_t)page * g.page_tokens + (pos & (g.page_tokens - 1));
-    const uint16_t* src = latent + (size_t)row * w;
-    uint8_t* dst = latent_pool + r * w;
-    const float s_l = quant_row_wide(src, w, dst, lane);   // c_kv and k_rope share one scale
-    const float s_i = quant_vec16(index_key + (size_t)row * g.index_dim, g.index_dim,
-                                  index_pool + r * g.index_dim, lane);
-    if (lane == 0) {
-        latent_scale[r] = s_l;
-        index_scale[r] = s_i;
-    }
+    append_row_paged(g, latent, index_key, row, row_seq ? row_seq[row] : row, row_pos[row], block_table, latent_pool,
+                     latent_scale, index_pool, index_scale, status, lane);
 }
 
 RIVOLI_API int rivoli_kv_append_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,

@@ -28,6 +28,7 @@
 // of sum |q_d k_d|; the tensor core measured 2^-21.9 on full-range random codes.
 #include "codec.cuh"
 #include "common.cuh"
+#include "quant.cuh"
 #include "tc_common.cuh"
 #include "tmap.hpp"
 #include "topk_core.cuh"
@@ -59,12 +60,11 @@ struct IndexMmaArgs {
 // ---------------------------------------------------------------------------------------------
 // 1. q quantisation + per-sequence error-bound constant. One CTA per sequence, one warp per head.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
-index_q_prepare_kernel(const uint16_t* __restrict__ q, const float* __restrict__ w, int nh, int hd, float wscale,
-                       float dscale, uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
-                       unsigned int* __restrict__ skmax, int* __restrict__ err) {
-    __shared__ float term[32];
-    const int b = blockIdx.x, h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+__device__ __forceinline__ void
+index_q_prepare_block(int b, const uint16_t* __restrict__ q, const float* __restrict__ w, int nh, int hd, float wscale,
+                      float dscale, uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
+                      unsigned int* __restrict__ skmax, int* __restrict__ err, float* term) {
+    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (h < nh) {
         const size_t v = (size_t)b * nh + h;
         // same codec path as rivoli_index_q_quant: 16 values per lane, absmax scale, e4m3 codes
@@ -113,6 +113,38 @@ index_q_prepare_kernel(const uint16_t* __restrict__ q, const float* __restrict__
         skmax[b] = 0u;
         if (b == 0) *err = 0;   // the scorer's error word starts clean on every call
     }
+}
+
+__global__ void __launch_bounds__(1024)
+index_q_prepare_kernel(const uint16_t* __restrict__ q, const float* __restrict__ w, int nh, int hd, float wscale,
+                       float dscale, uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
+                       unsigned int* __restrict__ skmax, int* __restrict__ err) {
+    __shared__ float term[32];
+    index_q_prepare_block(blockIdx.x, q, w, nh, hd, wscale, dscale, codes, scales, cb, skmax, err, term);
+}
+
+// Decode-step prologue in one launch: blocks [0, B) prepare the indexer query of sequence b,
+// blocks [B, B + ceil(B/32)) append the step's new token of 32 sequences each (one warp per row).
+// The two halves touch disjoint memory.
+struct AppendArgs {
+    const uint16_t* latent; const uint16_t* index_key; const int32_t* row_pos; const int32_t* block_table;
+    uint8_t* latent_pool; float* latent_scale; uint8_t* index_pool; float* index_scale; int32_t* status;
+};
+
+__global__ void __launch_bounds__(1024)
+step_prologue_kernel(DsaGeom g, AppendArgs ap, int B, const uint16_t* __restrict__ q, const float* __restrict__ w,
+                     uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
+                     unsigned int* __restrict__ skmax, int* __restrict__ err) {
+    __shared__ float term[32];
+    if ((int)blockIdx.x < B) {
+        index_q_prepare_block(blockIdx.x, q, w, g.index_heads, g.index_dim, g.index_wscale, g.index_dscale, codes, scales,
+                              cb, skmax, err, term);
+        return;
+    }
+    const int row = ((int)blockIdx.x - B) * 32 + (threadIdx.x >> 5);
+    if (row >= B) return;
+    append_row_paged(g, ap.latent, ap.index_key, row, row, ap.row_pos[row], ap.block_table, ap.latent_pool,
+                     ap.latent_scale, ap.index_pool, ap.index_scale, ap.status, threadIdx.x & 31);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -295,7 +327,10 @@ constexpr int RF_LIST = 2048;      // band tokens re-scored per round
 // Optional phase timeline of CTA 0 for tuning builds (-DRIVOLI_DEBUG_TIMES); compiled out otherwise.
 #ifdef RIVOLI_DEBUG_TIMES
 __device__ long long g_rf_times[16];
-#define RF_STAMP(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_rf_times[slot] = clock64(); } while (0)
+__device__ unsigned long long g_rf_span[1024][2];   // per CTA: globaltimer at entry and exit
+__device__ __forceinline__ unsigned long long rf_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define RF_STAMP(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_rf_times[slot] = clock64(); \
+                            if (threadIdx.x == 0 && blockIdx.x < 1024 && ((slot) == 0 || (slot) == 8)) g_rf_span[blockIdx.x][(slot) == 8] = rf_gtime(); } while (0)
 #else
 #define RF_STAMP(slot) do { } while (0)
 #endif
@@ -624,11 +659,18 @@ RIVOLI_API int rivoli_index_select_uses_mma(const DsaGeom* g, int score_stride) 
     return (g && mma_geometry_ok(g, score_stride)) ? 1 : 0;
 }
 
-RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index_q, const float* w,
-                                         const uint8_t* index_pool, const float* index_scale,
-                                         const int32_t* block_table, const int32_t* seq_len, int B,
-                                         int score_stride, uint32_t* rows, int32_t* n_sel, void* scratch,
-                                         void* stream) {
+RIVOLI_API int rivoli_kv_append_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,
+                                      const int32_t* row_seq, const int32_t* row_pos, int n_rows,
+                                      const int32_t* block_table, uint8_t* latent_pool, float* latent_scale,
+                                      uint8_t* index_pool, float* index_scale, int32_t* status, void* stream);
+
+// `ap` != NULL: the step's append (one new token per sequence) rides in the same launch as the
+// query preparation.
+static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* index_q, const float* w,
+                       const uint8_t* index_pool, const float* index_scale,
+                       const int32_t* block_table, const int32_t* seq_len, int B,
+                       int score_stride, uint32_t* rows, int32_t* n_sel, void* scratch,
+                       void* stream) {
     if (int e = rv_check_geom(g)) return e;
     if (B <= 0 || score_stride <= 0 || !index_q || !w || !index_pool || !index_scale || !block_table || !seq_len ||
         !rows || !n_sel || !scratch)
@@ -642,6 +684,11 @@ RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index
 
     if (!mma_geometry_ok(g, score_stride)) {
         // geometries outside the tensor-core kernel: the exact CUDA-core scorer + exact top-k
+        if (ap)
+            if (int e = rivoli_kv_append_paged(g, ap->latent, ap->index_key, nullptr, ap->row_pos, B, ap->block_table,
+                                               ap->latent_pool, ap->latent_scale, ap->index_pool, ap->index_scale,
+                                               ap->status, stream))
+                return e;
         int e = rivoli_index_q_quant(index_q, B * nh, hd, s.qcodes, s.qscales, stream);
         if (e) return e;
         e = rivoli_index_score_paged(g, s.qcodes, s.qscales, w, index_pool, index_scale, block_table, seq_len, B,
@@ -651,8 +698,12 @@ RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index
     }
 
     rv_drain_error();
-    index_q_prepare_kernel<<<B, 32 * nh, 0, st>>>(index_q, w, nh, hd, g->index_wscale, g->index_dscale, s.qcodes,
-                                                   s.qscales, s.cb, s.skmax, s.err);
+    if (ap)
+        step_prologue_kernel<<<B + (B + 31) / 32, 1024, 0, st>>>(*g, *ap, B, index_q, w, s.qcodes, s.qscales, s.cb,
+                                                                 s.skmax, s.err);
+    else
+        index_q_prepare_kernel<<<B, 32 * nh, 0, st>>>(index_q, w, nh, hd, g->index_wscale, g->index_dscale, s.qcodes,
+                                                       s.qscales, s.cb, s.skmax, s.err);
     if (int e = rv_launch_status()) return e;
 
     IndexMmaArgs ma{*g, s.qcodes, s.qscales, w, index_pool, index_scale, block_table, seq_len,
@@ -691,6 +742,38 @@ RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index
     return rv_launch_status();
 }
 
+RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index_q, const float* w,
+                                         const uint8_t* index_pool, const float* index_scale,
+                                         const int32_t* block_table, const int32_t* seq_len, int B,
+                                         int score_stride, uint32_t* rows, int32_t* n_sel, void* scratch,
+                                         void* stream) {
+    return select_impl(g, nullptr, index_q, w, index_pool, index_scale, block_table, seq_len, B, score_stride, rows,
+                       n_sel, scratch, stream);
+}
+
+// Decode step, first half: append the step's token of every sequence (row b belongs to sequence
+// b, position row_pos[b]) AND select the attended rows, with the append riding in the launch
+// that prepares the indexer query. Same results as rivoli_kv_append_paged followed by
+// rivoli_index_select_paged.
+RIVOLI_API int rivoli_dsa_append_select_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,
+                                              const int32_t* row_pos, const int32_t* block_table,
+                                              uint8_t* latent_pool, float* latent_scale, uint8_t* index_pool,
+                                              float* index_scale, int32_t* status, const uint16_t* index_q,
+                                              const float* w, const int32_t* seq_len, int B, int score_stride,
+                                              uint32_t* rows, int32_t* n_sel, void* scratch, void* stream) {
+    if (int e = rv_check_geom(g)) return e;
+    if (B <= 0 || !latent || !index_key || !row_pos || !block_table || !latent_pool || !latent_scale || !index_pool ||
+        !index_scale)
+        return 1001;
+    if ((g->rope_dim % 4) != 0 || ((g->kv_lora + g->rope_dim) % 16) != 0) return 1004;
+    if ((((uintptr_t)latent | (uintptr_t)index_key | (uintptr_t)latent_pool | (uintptr_t)index_pool) & 15) ||
+        ((uintptr_t)latent_scale & 3))
+        return 1005;
+    const AppendArgs ap{latent, index_key, row_pos, block_table, latent_pool, latent_scale, index_pool, index_scale, status};
+    return select_impl(g, &ap, index_q, w, index_pool, index_scale, block_table, seq_len, B, score_stride, rows, n_sel,
+                       scratch, stream);
+}
+
 // Reads back the tensor-core scorer's error word (0 = no bounded wait ever gave up) and
 // clears it. Synchronises the stream.
 RIVOLI_API int rivoli_index_select_status(const DsaGeom* g, int B, int score_stride, void* scratch, void* stream) {
@@ -720,5 +803,8 @@ RIVOLI_API int rivoli_index_select_band_stats(const DsaGeom* g, int B, int score
 #ifdef RIVOLI_DEBUG_TIMES
 extern "C" __attribute__((visibility("default"))) int rivoli_refine_debug_times(long long* host_out) {
     return (int)cudaMemcpyFromSymbol(host_out, g_rf_times, sizeof(long long) * 16);
+}
+extern "C" __attribute__((visibility("default"))) int rivoli_refine_debug_spans(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_rf_span, sizeof(unsigned long long) * 2048);
 }
 #endif

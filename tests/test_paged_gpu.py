@@ -324,3 +324,47 @@ def test_mma_attention_dense_long_prefix(be):
     be.attend_paged_status(g, scratch)
     check_mma_attention(u16(out), o_f32, True)
     assert np.abs(lse.cpu().numpy() - lse_w).max() < 2e-2
+
+
+@pytest.mark.parametrize("case", ["ragged", "cfg1"])
+def test_fused_append_select_equals_separate_calls(be, case):
+    """rivoli_dsa_append_select_paged == rivoli_kv_append_paged + rivoli_index_select_paged: pools,
+    scales, selected rows and counts bit for bit (tensor-core path on "ragged", CUDA-core on "cfg1")."""
+    st, g, d = build(be, case)
+    B = st.B
+    stride = int(st.seq_len.max())
+    nbytes = be.index_select_scratch_bytes(g, B, stride)
+
+    def run(fused):
+        pools = {k: d[k].clone() for k in ("latent_pool", "latent_scale", "index_pool", "index_scale")}
+        rows = torch.full((B, g.top_k), -1, dtype=torch.int32, device="cuda")
+        n_sel = torch.zeros(B, dtype=torch.int32, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        if fused:
+            be.launch_dsa_append_select_paged(g, dev(st.new_latent), dev(st.new_key), d["row_pos"], d["block_table"],
+                                              pools["latent_pool"], pools["latent_scale"], pools["index_pool"],
+                                              pools["index_scale"], status, dev(st.index_q), dev(st.index_w),
+                                              d["seq_len"], B, stride, rows, n_sel, scratch)
+        else:
+            be.launch_kv_append_paged(g, dev(st.new_latent), dev(st.new_key), None, d["row_pos"], B, d["block_table"],
+                                      pools["latent_pool"], pools["latent_scale"], pools["index_pool"],
+                                      pools["index_scale"], status)
+            be.launch_index_select_paged(g, dev(st.index_q), dev(st.index_w), pools["index_pool"], pools["index_scale"],
+                                         d["block_table"], d["seq_len"], B, stride, rows, n_sel, scratch)
+        be.device_sync()
+        be.index_select_status(g, B, stride, scratch)
+        assert int(status.item()) == 0
+        return pools, rows.cpu().numpy(), n_sel.cpu().numpy()
+
+    pa, ra, na = run(False)
+    pb, rb, nb = run(True)
+    for k in pa:
+        assert torch.equal(pa[k].view(torch.uint8), pb[k].view(torch.uint8)), k
+    np.testing.assert_array_equal(na, nb)
+    for b in range(B):
+        np.testing.assert_array_equal(ra[b, :na[b]], rb[b, :nb[b]])
+    want = st.oracle_step()
+    np.testing.assert_array_equal(nb, want["n_sel"])
+    for b in range(B):
+        np.testing.assert_array_equal(rb[b, :nb[b]].view(np.uint32), want["rows"][b, :nb[b]])
