@@ -25,7 +25,10 @@ class DsaDecodeLayer:
     """
 
     def __init__(self, geom: be.DsaGeom, n_seqs: int, device="cuda:0", max_ctx: int | None = None,
-                 shuffle_seed: int | None = None):
+                 shuffle_seed: int | None = None, pool: "be.PagePool | None" = None):
+        """``pool``: a page allocator shared with other layers of the same model (page ``p`` then names
+        row block ``p`` of every layer's pools and paging is done once per step, not per layer);
+        by default the layer owns one."""
         be.lib()  # fail loudly if the CUDA library is missing
         self.g = geom
         self.B = n_seqs
@@ -41,8 +44,8 @@ class DsaDecodeLayer:
         self.index_pool = torch.zeros(rows * geom.index_dim, dtype=u8, device=d)
         self.index_scale = torch.zeros(rows, dtype=f32, device=d)
         self.block_table = torch.full((n_seqs, geom.max_pages_per_seq), -1, dtype=i32, device=d)
-        self.pool = be.PagePool(geom.n_pool_pages, n_seqs, geom.max_pages_per_seq, P)
-        if shuffle_seed is not None:
+        self.pool = pool if pool is not None else be.PagePool(geom.n_pool_pages, n_seqs, geom.max_pages_per_seq, P)
+        if shuffle_seed is not None and pool is None:
             self.pool.shuffle(shuffle_seed)
         # per-step scratch
         self.score_stride = self.max_ctx
@@ -67,8 +70,8 @@ class DsaDecodeLayer:
     def release(self, seq: int) -> None:
         self.pool.release(seq)
 
-    def upload_block_table(self) -> None:
-        bt = torch.from_numpy(self.pool.block_table())
+    def upload_block_table(self, table: "np.ndarray | None" = None) -> None:
+        bt = torch.from_numpy(self.pool.block_table() if table is None else table)
         self.block_table.copy_(bt, non_blocking=False)
 
     # --- operators ----------------------------------------------------------------------------------

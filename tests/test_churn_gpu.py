@@ -1,0 +1,88 @@
+"""Continuous batching with eviction churn on the GPU (BASELINE config 5 at reduced scale): several
+layers share one page allocator, every step appends one token per sequence per layer, some
+sequences finish and their slots are refilled (pages go back to the free list and are drawn again,
+the replacement's context is prefilled through the same append operator). After every step the
+selected rows must equal the oracle's bit for bit and the attention output must be within the
+tolerance, for every layer - so no stale page, scale or row ever leaks from an evicted sequence."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests.helpers import attend_close_ref, bf16_normal, make_geom
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.uint16:
+        a = a.view(np.int16)
+    return torch.from_numpy(a).cuda()
+
+
+def test_churn_three_layers_match_oracle():
+    from rivoli_b200 import backend as be
+    from rivoli_b200.layer import DsaDecodeLayer
+    from rivoli_b200.scheduler import ContinuousBatcher, churn_plan
+    be.lib()
+    n_slots, n_layers, P, top_k, steps = 8, 3, 64, 256, 6
+    lo, hi = 60, 900
+    max_ctx = hi + steps + 2
+    max_pages = (max_ctx + P - 1) // P
+    n_pool = int(1.25 * n_slots * max_pages)
+    kw = dict(n_heads=64, kv_lora=512, rope_dim=64, index_heads=32, index_dim=128, page_tokens=P, top_k=top_k,
+              max_pages_per_seq=max_pages, n_pool_pages=n_pool)
+    g, og = make_geom(be.DsaGeom, **kw), make_geom(orc.Geom, **kw)
+    W, hd, rows_n = 576, 128, n_pool * P
+    sched = ContinuousBatcher(n_slots, n_pool, max_ctx, P, shuffle_seed=9)
+    layers = [DsaDecodeLayer(g, n_slots, max_ctx=max_pages * P, pool=sched.pool) for _ in range(n_layers)]
+    mirror = [dict(lp=np.zeros(rows_n * W, np.uint8), ls=np.zeros(rows_n, np.float32),
+                   ip=np.zeros(rows_n * hd, np.uint8), isc=np.zeros(rows_n, np.float32)) for _ in range(n_layers)]
+    rng = np.random.RandomState(5)
+
+    def prefill(slots, lens):
+        """Cache contents of freshly admitted sequences, every layer (GPU append + oracle append)."""
+        bt = sched.block_table()
+        seq = np.concatenate([np.full(n, s, np.int32) for s, n in zip(slots, lens)])
+        pos = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+        for L, M in zip(layers, mirror):
+            lat, key = bf16_normal(rng, (seq.size, W)), bf16_normal(rng, (seq.size, hd))
+            L.upload_block_table(bt)
+            L.append(dev(lat), dev(key), dev(pos), dev(seq))
+            assert orc.kv_append_paged(og, lat, key, seq, pos, bt, M["lp"], M["ls"], M["ip"], M["isc"]) == 0
+
+    first = rng.randint(lo, hi + 1, n_slots)
+    for s, n in enumerate(first):
+        sched.admit(s, int(n))
+    prefill(range(n_slots), first)
+    for step in range(steps):
+        row_pos, seq_len = sched.begin_step()
+        bt = sched.block_table()
+        for li, (L, M) in enumerate(zip(layers, mirror)):
+            lat, key = bf16_normal(rng, (n_slots, W)), bf16_normal(rng, (n_slots, hd))
+            iq = bf16_normal(rng, (n_slots, 32, hd))
+            iw = orc.bf16_to_f32(bf16_normal(rng, (n_slots, 32)))
+            q = bf16_normal(rng, (n_slots, 64, W))
+            L.upload_block_table(bt)
+            out = L.step(dev(lat), dev(key), dev(iq), dev(iw), dev(q), dev(row_pos), dev(seq_len))
+            be.device_sync()
+            L.check_status()
+            assert orc.kv_append_paged(og, lat, key, None, row_pos, bt, M["lp"], M["ls"], M["ip"], M["isc"]) == 0
+            qc, qs = orc.index_q_quant(iq, hd)
+            sc = orc.index_score_paged(og, qc, qs, iw, M["ip"], M["isc"], bt, seq_len, int(seq_len.max()))
+            rows, n_sel = orc.index_topk_batched(sc, seq_len, top_k)
+            _, want, _, _ = orc.mla_attend_paged(og, q, M["lp"], M["ls"], bt, rows, n_sel, want_f32=True)
+            got_rows, got_n = L.rows.cpu().numpy().view(np.uint32), L.n_sel.cpu().numpy()
+            np.testing.assert_array_equal(got_n, n_sel)
+            for b in range(n_slots):
+                np.testing.assert_array_equal(got_rows[b, :n_sel[b]], rows[b, :n_sel[b]], err_msg=f"step {step} layer {li} slot {b}")
+            ok, worst, rms = attend_close_ref(out.cpu().view(torch.int16).numpy().view(np.uint16), want)
+            assert ok and rms <= 1e-2, (step, li, worst, rms)
+            # the pools themselves: bit-identical everywhere a live sequence has a token
+            np.testing.assert_array_equal(L.latent_scale.cpu().numpy().view(np.uint32), M["ls"].view(np.uint32))
+            np.testing.assert_array_equal(L.index_pool.cpu().numpy(), M["ip"])
+        slots, lens = churn_plan(rng, n_slots, 0.25, lo, hi)      # 2 of 8 slots finish and are refilled
+        sched.finish(slots, lens)
+        prefill(slots, lens)
+    assert sched._next_id == n_slots + steps * 2
