@@ -36,7 +36,7 @@ WORKLOADS = {
 KV_LORA, ROPE = 512, 64
 # dram__bytes_read.sum + dram__bytes_write.sum per sequence of the cfg3 shape, from the ncu capture
 # summarised in profiles/dram_traffic_hot_kernels_cfg3.md (stage totals / 128 sequences)
-TRAFFIC_PER_SEQ = {"index_select": (1.09 + 269.15 + 5.4 + 19.10) * 1e6 / 128, "attend": (9.45 + 184.98 + 0.9) * 1e6 / 128}
+TRAFFIC_PER_SEQ = {"index_select": (1.32 + 269.16 + 5.3 + 19.12) * 1e6 / 128, "attend": (184.81 + 0.7) * 1e6 / 128}
 METRIC = "DSA decode layer-steps/s (batch×ctx)"
 
 
@@ -330,8 +330,8 @@ def run_ours(args):
         names = ["append", "index_select", "attend"]
         stage_bytes = {"append": ab["append"] * B, "index_select": ab["index"] * B, "attend": ab["attend"] * B}
         stage_kernels = {"append": "kv_append_paged_kernel",
-                         "index_select": "index_q_prepare + index_score_mma (tcgen05) + index_select_refine",
-                         "attend": "attend_q_prepare + attend_mma (tcgen05)"}
+                         "index_select": "index query prepare + index_score_mma (tcgen05) + index_select_refine",
+                         "attend": "attend_mma (tcgen05; q split, gather, QK, softmax, PV in one kernel)"}
         per_stage = {n: {"ms": stage_ms[i], "bytes": stage_bytes[n],
                          "gbs": stage_bytes[n] / (stage_ms[i] * 1e-3) / 1e9,
                          "frac": stage_bytes[n] / (stage_ms[i] * 1e-3) / 1e9 / hbm_peak}
