@@ -246,6 +246,16 @@ int rivoli_pagepool_seq_pages(const void* pool, int seq);
 const int32_t* rivoli_pagepool_block_table(const void* pool);   /* [n_seqs][max_pages_per_seq], -1 unmapped */
 const int32_t* rivoli_pagepool_free_list(const void* pool);     /* [n_free] */
 
+/* Diagnostic, not on any product path (bench.py --profile gather): average milliseconds of a
+ * launch in which each of n_ctas CTAs copies n_tiles tiles of 128 latent rows (576 bytes each,
+ * rows[cta][tile][128] = pool row numbers) from the pool into shared memory with `depth` (1..3)
+ * tiles in flight. method 0 = cp.async 16 B coalesced by row, 1 = cp.async.bulk per row,
+ * 2 = TMA tile::gather4 into the swizzled operand layout. Allocates no device memory;
+ * synchronises the stream. No counterpart in the reference. */
+int rivoli_probe_gather(int method, int depth, int n_ctas, int n_tiles, const uint8_t* pool,
+                        unsigned long long n_pool_rows, const float* scales, const uint32_t* rows, float* ms_out,
+                        void* stream);
+
 /* Library build tag, e.g. "sm_100a". */
 const char* rivoli_kernels_arch(void);
 

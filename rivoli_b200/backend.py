@@ -328,5 +328,15 @@ class PagePool:
         return np.ctypeslib.as_array(p, shape=(n,)).copy()
 
 
+def probe_gather(method: int, depth: int, n_ctas: int, n_tiles: int, pool, n_pool_rows: int, scales, rows,
+                 stream=None) -> float:
+    """Diagnostic gather roofline: milliseconds per launch (see include/rivoli_kernels.h)."""
+    ms = C.c_float(0.0)
+    ensure_status(lib().rivoli_probe_gather(C.c_int(method), C.c_int(depth), C.c_int(n_ctas), C.c_int(n_tiles),
+                                            _ptr(pool), C.c_ulonglong(n_pool_rows), _ptr(scales), _ptr(rows),
+                                            C.byref(ms), _stream(stream)), "probe_gather")
+    return float(ms.value)
+
+
 def kernels_arch() -> str:
     return lib().rivoli_kernels_arch().decode()
