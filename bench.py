@@ -384,10 +384,11 @@ def run_gather_probe(args):
     tok = k * 8 + torch.randint(0, 8, (max_ctas, n_tiles * 128), generator=gen, device=device)
     page = (torch.arange(max_ctas, device=device).unsqueeze(1) * 2654435761 + (tok // P) * 40503) % (n_rows // P)
     rows = (page * P + tok % P).to(torch.int32).contiguous()
-    names = {0: "cp.async 16 B, coalesced by row", 1: "cp.async.bulk 576 B per row", 2: "TMA tile::gather4 (swizzled)"}
+    names = {0: "cp.async 16 B, coalesced by row", 1: "cp.async.bulk 576 B per row", 2: "TMA tile::gather4 (swizzled)",
+             3: "cp.async 16 B + L2 prefetch 3 ahead"}
     bytes_per_cta = n_tiles * 128 * (KV_LORA + ROPE + 4)
     for n_ctas in (128, 148):
-        for method in (0, 1, 2):
+        for method in (0, 1, 2, 3):
             for depth in (1, 2, 3):
                 ms = be.probe_gather(method, depth, n_ctas, n_tiles, pool, n_rows, scales, rows)
                 print(f"{names[method]:34s} CTAs {n_ctas:3d} tiles in flight {depth}: {ms * 1e3:7.1f} us "

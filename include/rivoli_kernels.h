@@ -250,7 +250,8 @@ const int32_t* rivoli_pagepool_free_list(const void* pool);     /* [n_free] */
  * launch in which each of n_ctas CTAs copies n_tiles tiles of 128 latent rows (576 bytes each,
  * rows[cta][tile][128] = pool row numbers) from the pool into shared memory with `depth` (1..3)
  * tiles in flight. method 0 = cp.async 16 B coalesced by row, 1 = cp.async.bulk per row,
- * 2 = TMA tile::gather4 into the swizzled operand layout. Allocates no device memory;
+ * 2 = TMA tile::gather4 into the swizzled operand layout, 3 = method 0 with the rows three tiles
+ * on prefetched into L2. Allocates no device memory;
  * synchronises the stream. No counterpart in the reference. */
 int rivoli_probe_gather(int method, int depth, int n_ctas, int n_tiles, const uint8_t* pool,
                         unsigned long long n_pool_rows, const float* scales, const uint32_t* rows, float* ms_out,

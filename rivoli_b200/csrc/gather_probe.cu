@@ -6,6 +6,8 @@
 //   method 1: cp.async.bulk, one 576-byte row per thread (lands unswizzled)
 //   method 2: TMA tile::gather4, box 128 B x 1 row with the 128-byte swizzle (+ 64 B x 1 row with
 //             the 64-byte swizzle for the rope part): lands in the UMMA K-major operand layout
+//   method 3: method 0 with the rows of the tile `GP_AHEAD` tiles on prefetched into L2
+//             (cp.async.bulk.prefetch.L2, one 576-byte request per row)
 // All waits are bounded; a wait that gives up sets the error word and the probe returns 1008.
 #include "common.cuh"
 #include "tmap.hpp"
@@ -13,6 +15,7 @@
 namespace {
 
 constexpr int GP_ROWB = 576, GP_TILE = 128;
+constexpr int GP_AHEAD = 3;
 constexpr int GP_LATB = 65536, GP_ROPEB = 8192, GP_TILEB = GP_LATB + GP_ROPEB;   // = 128 * 576
 
 __device__ int g_gp_err;      // a bounded wait gave up
@@ -58,7 +61,11 @@ gather_probe_kernel(const __grid_constant__ CUtensorMap tm_lat, const __grid_con
         uint8_t* dst = gp_buf + (size_t)d * GP_TILEB;
         const uint32_t r = myrows[j * GP_TILE + tid];
         s_scale[d][tid] = scales[r];
-        if (METHOD == 0) {
+        if (METHOD == 3 && j + GP_AHEAD < ntiles) {
+            const uint32_t rp = myrows[(j + GP_AHEAD) * GP_TILE + tid];
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pool + (size_t)rp * GP_ROWB), "r"(GP_ROWB) : "memory");
+        }
+        if (METHOD == 0 || METHOD == 3) {
             const unsigned long long sp = (unsigned long long)(pool + (size_t)r * GP_ROWB);
             for (int it = 0; it < 32; ++it) {
                 const uint8_t* rs = (const uint8_t*)__shfl_sync(0xffffffffu, sp, it);
@@ -87,11 +94,16 @@ gather_probe_kernel(const __grid_constant__ CUtensorMap tm_lat, const __grid_con
                            "r"((int)q.z), "r"((int)q.w), "r"(gp_smem(&full[d])) : "memory");
         }
     };
+    if (METHOD == 3)
+        for (int j = 0; j < GP_AHEAD && j < ntiles; ++j) {
+            const uint32_t rp = myrows[j * GP_TILE + tid];
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pool + (size_t)rp * GP_ROWB), "r"(GP_ROWB) : "memory");
+        }
     for (int j = 0; j < DEPTH - 1 && j < ntiles; ++j) issue(j);
     for (int j = 0; j < ntiles; ++j) {
         if (j + DEPTH - 1 < ntiles) issue(j + DEPTH - 1);
         const int d = j % DEPTH;
-        if (METHOD == 0) {
+        if (METHOD == 0 || METHOD == 3) {
             const int pend = min(DEPTH - 1, ntiles - 1 - j);
             if (pend >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
             else if (pend == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -165,6 +177,7 @@ RIVOLI_API int rivoli_probe_gather(int method, int depth, int n_ctas, int n_tile
     GP_CASE(0, 1); GP_CASE(0, 2); GP_CASE(0, 3);
     GP_CASE(1, 1); GP_CASE(1, 2); GP_CASE(1, 3);
     GP_CASE(2, 1); GP_CASE(2, 2); GP_CASE(2, 3);
+    GP_CASE(3, 1); GP_CASE(3, 2); GP_CASE(3, 3);
 #undef GP_CASE
     return 1001;
 }
