@@ -246,6 +246,32 @@ int rivoli_pagepool_seq_pages(const void* pool, int seq);
 const int32_t* rivoli_pagepool_block_table(const void* pool);   /* [n_seqs][max_pages_per_seq], -1 unmapped */
 const int32_t* rivoli_pagepool_free_list(const void* pool);     /* [n_free] */
 
+/* ---- kv_b projections either side of attention (the step after the cache path) ------------------
+ * kv_b: e4m3 codes [H*(nope+vh) rows][kvl cols], scale[(row / block) * ceil(kvl / block) + col / block];
+ * head h owns rows [h*(nope+vh), +nope) (absorb) and the next vh rows (value).
+ * rivoli_mla_absorb_fp8 / rivoli_mla_value_fp8 replace crates/backend/kernels/mla.hip:192-231 (same
+ * arguments and guards: 1001 non-positive size, 1003 block not a power of two, 1004 nrow not 1 or 2,
+ * value only: 1002 kvl % 4 != 0); outputs are the left folds of the reference's host tests, bit for bit. */
+int rivoli_mla_absorb_fp8(const float* q, const unsigned char* kvb, const float* kvb_scale, int H, int qh, int nope,
+                          int vh, int kvl, int block, int nrow, float* qabs);
+int rivoli_mla_value_fp8(const float* clat, const unsigned char* kvb, const float* kvb_scale, int H, int nope, int vh,
+                         int kvl, int block, int nrow, float* ctx);
+/* Batched decode form, no counterpart in the reference. q bf16 [B][H][qh] (nope values to absorb, then
+ * the rope segment) -> q_abs bf16 [B][H][kvl + rope]: the absorbed query followed by the rope segment
+ * bit for bit, i.e. the row rivoli_mla_attend_paged_bf16 consumes (the reference's gather_rope repack,
+ * crates/backend/kernels/fwd.hip:73-84, folded in). clat bf16 [B][H][kvl] (the attention output)
+ * -> ctx bf16 [B][H][vh]. Tensor-core kernels (tcgen05, bf16 x exact-bf16 codes, f32 accumulate, block
+ * scales applied per scale run in the epilogue) for 128-blocks, kvl <= 512, nope <= 256, multiples of
+ * 64; CUDA-core kernels otherwise or when force_simt != 0. 1002: qh < nope + rope; 1005: alignment. */
+int rivoli_mla_absorb_batched_bf16(const uint16_t* q, const unsigned char* kvb, const float* kvb_scale, int H, int qh,
+                                   int nope, int vh, int kvl, int rope, int block, int B, uint16_t* q_abs,
+                                   int force_simt, void* stream);
+int rivoli_mla_value_batched_bf16(const uint16_t* clat, const unsigned char* kvb, const float* kvb_scale, int H,
+                                  int nope, int vh, int kvl, int block, int B, uint16_t* ctx, int force_simt,
+                                  void* stream);
+/* Synchronises `stream`; 1008 if a bounded wait of a tensor-core projection gave up since the last call. */
+int rivoli_kvb_proj_status(void* stream);
+
 /* Diagnostic, not on any product path (bench.py --profile gather): average milliseconds of a
  * launch in which each of n_ctas CTAs copies n_tiles tiles of 128 latent rows (576 bytes each,
  * rows[cta][tile][128] = pool row numbers) from the pool into shared memory with `depth` (1..3)

@@ -249,6 +249,51 @@ def attend_merge_partials(part_out, part_lse, kvl) -> np.ndarray:
     return out
 
 
+def mla_absorb_fp8(q, kvb, scale, H, qh, nope, vh, kvl, block, nrow=1) -> np.ndarray:
+    """f32 q ``[nrow, H*qh]`` through kv_b's absorb rows -> ``[nrow, H*kvl]`` (mla.hip:12-122)."""
+    q, kvb, scale = _c(q, np.float32), _c(kvb, np.uint8), _c(scale, np.float32)
+    out = np.zeros((nrow, H * kvl), dtype=np.float32)
+    lib().orc_mla_absorb_fp8(_p(q), _p(kvb), _p(scale), H, qh, nope, vh, kvl, block, nrow, _p(out))
+    return out
+
+
+def mla_value_fp8(clat, kvb, scale, H, nope, vh, kvl, block, nrow=1) -> np.ndarray:
+    """f32 clat ``[nrow, H*kvl]`` through kv_b's value rows -> ``[nrow, H*vh]`` (mla.hip:138-175)."""
+    clat, kvb, scale = _c(clat, np.float32), _c(kvb, np.uint8), _c(scale, np.float32)
+    out = np.zeros((nrow, H * vh), dtype=np.float32)
+    lib().orc_mla_value_fp8(_p(clat), _p(kvb), _p(scale), H, nope, vh, kvl, block, nrow, _p(out))
+    return out
+
+
+def mla_absorb_batched_bf16(q, kvb, scale, H, qh, nope, vh, kvl, rope, block):
+    """bf16 q ``[B, H, qh]`` -> (q_abs bf16 ``[B, H, kvl+rope]``, absorbed part in f32 ``[B, H, kvl]``)."""
+    q, kvb, scale = _c(q, np.uint16), _c(kvb, np.uint8), _c(scale, np.float32)
+    B = q.size // (H * qh)
+    out = np.zeros((B, H, kvl + rope), dtype=np.uint16)
+    f32 = np.zeros((B, H, kvl), dtype=np.float32)
+    lib().orc_mla_absorb_batched_bf16(_p(q), _p(kvb), _p(scale), H, qh, nope, vh, kvl, rope, block, B, _p(out), _p(f32))
+    return out, f32
+
+
+def mla_value_batched_bf16(clat, kvb, scale, H, nope, vh, kvl, block):
+    """bf16 clat ``[B, H, kvl]`` -> (ctx bf16 ``[B, H, vh]``, the same in f32)."""
+    clat, kvb, scale = _c(clat, np.uint16), _c(kvb, np.uint8), _c(scale, np.float32)
+    B = clat.size // (H * kvl)
+    out = np.zeros((B, H, vh), dtype=np.uint16)
+    f32 = np.zeros((B, H, vh), dtype=np.float32)
+    lib().orc_mla_value_batched_bf16(_p(clat), _p(kvb), _p(scale), H, nope, vh, kvl, block, B, _p(out), _p(f32))
+    return out, f32
+
+
+def kvb_fixture(r: "Lcg", rows, kvl, block):
+    """kv_b bytes then the block-scale grid, drawn in that order
+    (crates/engine/tests/kernel_attend.rs:127-132, tests/common/reference.rs:218-220)."""
+    packed = f32_to_e4m3(r.draws(rows * kvl))
+    n = ((rows + block - 1) // block) * ((kvl + block - 1) // block)
+    scale = (np.abs(r.draws(n) * np.float32(0.1)) + np.float32(0.01)).astype(np.float32)
+    return packed, scale
+
+
 class Pool:
     """LIFO page allocator of the oracle (see ``orc_pool_*``)."""
 

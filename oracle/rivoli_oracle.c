@@ -580,6 +580,99 @@ ORC_API const int32_t* orc_pool_block_table(const orc_pool* p) { return p->block
 ORC_API const int32_t* orc_pool_free_list(const orc_pool* p) { return p->free_list; }
 ORC_API int orc_pool_n_free(const orc_pool* p) { return p->n_free; }
 
+/* ---------------------------------------------------------------------------------------------
+ * kv_b projections either side of attention (the "next" row after the cache path).
+ *   kv_b: e4m3 codes [H*(nope+vh) rows][kvl cols], block-scaled: element (r, c) is
+ *   e4m3(code) * scale[(r / block) * ceil(kvl / block) + c / block]
+ *   (crates/backend/kernels/mla.hip:1-8; dequant rule crates/engine/tests/kernel_attend.rs:345-356,
+ *   scale ROW index clamped to the last tile row as that test does).
+ * Host references: every output is a LEFT FOLD from 0.0 of plain products
+ *   (kernel_attend.rs:361-390, per_output_sum); the device kernels fold q * (lut * s) in the
+ *   same d order (mla.hip:96-114) - restated as orc_mla_absorb_fp8 / orc_mla_value_fp8.
+ * ------------------------------------------------------------------------------------------- */
+static float kvb_at(const uint8_t* kvb, const float* scale, int rows, int kvl, int block, size_t r, int c) {
+    const int sc_rows = (rows + block - 1) / block, sc_cols = (kvl + block - 1) / block;
+    size_t rb = r / (size_t)block;
+    if (rb > (size_t)(sc_rows - 1)) rb = (size_t)(sc_rows - 1);
+    return orc_e4m3_to_f32(kvb[r * (size_t)kvl + c]) * scale[rb * sc_cols + c / block];
+}
+
+/* qabs[row][head][i] = sum_d q[row][head*qh + d] * kvb[head*(nope+vh) + d][i]; nrow rows of q are
+ * H*qh apart, of qabs H*kvl apart (mla.hip:27-31). */
+ORC_API void orc_mla_absorb_fp8(const float* q, const uint8_t* kvb, const float* scale, int H, int qh, int nope,
+                                int vh, int kvl, int block, int nrow, float* qabs) {
+    const int rows = H * (nope + vh);
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int r = 0; r < nrow; ++r)
+        for (int head = 0; head < H; ++head)
+            for (int i = 0; i < kvl; ++i) {
+                float acc = 0.0f;
+                for (int d = 0; d < nope; ++d)
+                    acc += q[(size_t)r * H * qh + (size_t)head * qh + d] *
+                           kvb_at(kvb, scale, rows, kvl, block, (size_t)head * (nope + vh) + d, i);
+                qabs[(size_t)r * H * kvl + (size_t)head * kvl + i] = acc;
+            }
+}
+
+/* ctx[row][head][j] = sum_i clat[row][head*kvl + i] * kvb[head*(nope+vh) + nope + j][i] (mla.hip:138-175). */
+ORC_API void orc_mla_value_fp8(const float* clat, const uint8_t* kvb, const float* scale, int H, int nope, int vh,
+                               int kvl, int block, int nrow, float* ctx) {
+    const int rows = H * (nope + vh);
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int r = 0; r < nrow; ++r)
+        for (int head = 0; head < H; ++head)
+            for (int j = 0; j < vh; ++j) {
+                float acc = 0.0f;
+                for (int i = 0; i < kvl; ++i)
+                    acc += clat[(size_t)r * H * kvl + (size_t)head * kvl + i] *
+                           kvb_at(kvb, scale, rows, kvl, block, (size_t)head * (nope + vh) + nope + j, i);
+                ctx[(size_t)r * H * vh + (size_t)head * vh + j] = acc;
+            }
+}
+
+/* Batched bf16 form (no reference counterpart): q bf16 [B][H][qh] with qh >= nope + rope; the
+ * output row is the absorbed query followed by the rope segment of q copied bit for bit -
+ * q_abs bf16 [B][H][kvl + rope], the layout the attention operator consumes (the reference's
+ * gather_rope repack, crates/backend/kernels/fwd.hip:73-84, folded in). f32 fold as above,
+ * one bf16 rounding at the store. qabs_f32 (may be NULL) receives the unrounded values. */
+ORC_API void orc_mla_absorb_batched_bf16(const uint16_t* q, const uint8_t* kvb, const float* scale, int H, int qh,
+                                         int nope, int vh, int kvl, int rope, int block, int B, uint16_t* q_abs,
+                                         float* qabs_f32) {
+    const int rows = H * (nope + vh), W = kvl + rope;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int b = 0; b < B; ++b)
+        for (int head = 0; head < H; ++head) {
+            const uint16_t* qr = q + ((size_t)b * H + head) * qh;
+            uint16_t* o = q_abs + ((size_t)b * H + head) * W;
+            for (int i = 0; i < kvl; ++i) {
+                float acc = 0.0f;
+                for (int d = 0; d < nope; ++d)
+                    acc += orc_bf16_to_f32(qr[d]) * kvb_at(kvb, scale, rows, kvl, block, (size_t)head * (nope + vh) + d, i);
+                o[i] = orc_f32_to_bf16(acc);
+                if (qabs_f32) qabs_f32[((size_t)b * H + head) * kvl + i] = acc;
+            }
+            for (int e = 0; e < rope; ++e) o[kvl + e] = qr[nope + e];
+        }
+}
+
+/* clat bf16 [B][H][kvl] -> ctx bf16 [B][H][vh]; ctx_f32 (may be NULL) receives the unrounded values. */
+ORC_API void orc_mla_value_batched_bf16(const uint16_t* clat, const uint8_t* kvb, const float* scale, int H, int nope,
+                                        int vh, int kvl, int block, int B, uint16_t* ctx, float* ctx_f32) {
+    const int rows = H * (nope + vh);
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int b = 0; b < B; ++b)
+        for (int head = 0; head < H; ++head) {
+            const uint16_t* cr = clat + ((size_t)b * H + head) * kvl;
+            for (int j = 0; j < vh; ++j) {
+                float acc = 0.0f;
+                for (int i = 0; i < kvl; ++i)
+                    acc += orc_bf16_to_f32(cr[i]) * kvb_at(kvb, scale, rows, kvl, block, (size_t)head * (nope + vh) + nope + j, i);
+                ctx[((size_t)b * H + head) * vh + j] = orc_f32_to_bf16(acc);
+                if (ctx_f32) ctx_f32[((size_t)b * H + head) * vh + j] = acc;
+            }
+        }
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

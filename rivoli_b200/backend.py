@@ -328,6 +328,39 @@ class PagePool:
         return np.ctypeslib.as_array(p, shape=(n,)).copy()
 
 
+def launch_mla_absorb(q, kvb, kvb_scale, H: int, qh: int, nope: int, vh: int, kvl: int, block: int, nrow: int,
+                      qabs) -> None:
+    ensure_status(lib().rivoli_mla_absorb_fp8(_ptr(q), _ptr(kvb), _ptr(kvb_scale), C.c_int(H), C.c_int(qh),
+                                              C.c_int(nope), C.c_int(vh), C.c_int(kvl), C.c_int(block), C.c_int(nrow),
+                                              _ptr(qabs)), "mla_absorb_fp8")
+
+
+def launch_mla_value(clat, kvb, kvb_scale, H: int, nope: int, vh: int, kvl: int, block: int, nrow: int, ctx) -> None:
+    ensure_status(lib().rivoli_mla_value_fp8(_ptr(clat), _ptr(kvb), _ptr(kvb_scale), C.c_int(H), C.c_int(nope),
+                                             C.c_int(vh), C.c_int(kvl), C.c_int(block), C.c_int(nrow), _ptr(ctx)),
+                  "mla_value_fp8")
+
+
+def launch_mla_absorb_batched_bf16(q, kvb, kvb_scale, H: int, qh: int, nope: int, vh: int, kvl: int, rope: int,
+                                   block: int, B: int, q_abs, force_simt: bool = False, stream=None) -> None:
+    ensure_status(lib().rivoli_mla_absorb_batched_bf16(_ptr(q), _ptr(kvb), _ptr(kvb_scale), C.c_int(H), C.c_int(qh),
+                                                       C.c_int(nope), C.c_int(vh), C.c_int(kvl), C.c_int(rope),
+                                                       C.c_int(block), C.c_int(B), _ptr(q_abs), C.c_int(int(force_simt)),
+                                                       _stream(stream)), "mla_absorb_batched_bf16")
+
+
+def launch_mla_value_batched_bf16(clat, kvb, kvb_scale, H: int, nope: int, vh: int, kvl: int, block: int, B: int, ctx,
+                                  force_simt: bool = False, stream=None) -> None:
+    ensure_status(lib().rivoli_mla_value_batched_bf16(_ptr(clat), _ptr(kvb), _ptr(kvb_scale), C.c_int(H), C.c_int(nope),
+                                                      C.c_int(vh), C.c_int(kvl), C.c_int(block), C.c_int(B), _ptr(ctx),
+                                                      C.c_int(int(force_simt)), _stream(stream)),
+                  "mla_value_batched_bf16")
+
+
+def kvb_proj_status(stream=None) -> None:
+    ensure_status(lib().rivoli_kvb_proj_status(_stream(stream)), "kvb_proj(status)")
+
+
 def probe_gather(method: int, depth: int, n_ctas: int, n_tiles: int, pool, n_pool_rows: int, scales, rows,
                  stream=None) -> float:
     """Diagnostic gather roofline: milliseconds per launch (see include/rivoli_kernels.h)."""

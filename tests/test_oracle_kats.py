@@ -234,3 +234,62 @@ def test_index_append_fixture():
     orc.index_append(k, cache, pos, hd)
     want = np.zeros((rows, hd), np.uint16); want[pos] = orc.f32_to_bf16(k)
     np.testing.assert_array_equal(cache.reshape(rows, hd), want)
+
+
+# --- kv_b projections (absorb / value): the reference's six seeded shapes -----------------------------
+MLA_SHAPES = [  # (seed, [h, qh, nope, vh, kvl, block]) - crates/engine/tests/kernel_attend.rs:322-331
+    (0x77, [4, 128, 128, 64, 256, 128]), (0x78, [3, 64, 48, 32, 37, 128]), (0x79, [2, 32, 16, 8, 64, 2]),
+    (0x7a, [2, 32, 16, 8, 64, 4]), (0x7b, [2, 32, 16, 8, 68, 64]), (0x7c, [2, 16, 8, 4, 2, 128]),
+]
+
+
+def _mla_numpy_reference(packed, scale, q, clat, dims):
+    """The host references of the reference's test restated independently in numpy
+    (kernel_attend.rs:345-390): dequantised kv_b, then a left fold of plain products."""
+    h, qh, nope, vh, kvl, block = dims
+    rows = h * (nope + vh)
+    sc_rows, sc_cols = -(-rows // block), -(-kvl // block)
+    r_idx = np.minimum(np.arange(rows) // block, sc_rows - 1)[:, None]
+    c_idx = (np.arange(kvl) // block)[None, :]
+    kvb = orc.e4m3_table()[packed.reshape(rows, kvl)] * scale.reshape(sc_rows, sc_cols)[r_idx, c_idx]
+    kvb = kvb.astype(np.float32)
+    absorb = np.zeros((h, kvl), np.float32)
+    value = np.zeros((h, vh), np.float32)
+    for head in range(h):
+        acc = np.zeros(kvl, np.float32)
+        for d in range(nope):
+            acc = (acc + q[head * qh + d] * kvb[head * (nope + vh) + d]).astype(np.float32)
+        absorb[head] = acc
+        acc = np.zeros(vh, np.float32)
+        for i in range(kvl):
+            acc = (acc + clat[head * kvl + i] * kvb[head * (nope + vh) + nope: head * (nope + vh) + nope + vh, i]).astype(np.float32)
+        value[head] = acc
+    return absorb.ravel(), value.ravel()
+
+
+@pytest.mark.parametrize("seed,dims", MLA_SHAPES)
+def test_mla_absorb_value_match_the_host_reference(seed, dims):
+    h, qh, nope, vh, kvl, block = dims
+    r = orc.Lcg(seed)
+    packed, scale = orc.kvb_fixture(r, h * (nope + vh), kvl, block)      # draw order of check_mla_fp8
+    q = r.draws(h * qh)
+    clat = r.draws(h * kvl)
+    want_abs, want_val = _mla_numpy_reference(packed, scale, q, clat, dims)
+    got_abs = orc.mla_absorb_fp8(q, packed, scale, h, qh, nope, vh, kvl, block)[0]
+    got_val = orc.mla_value_fp8(clat, packed, scale, h, nope, vh, kvl, block)[0]
+    np.testing.assert_array_equal(got_abs.view(np.uint32), want_abs.view(np.uint32))   # same fold, same bits
+    np.testing.assert_array_equal(got_val.view(np.uint32), want_val.view(np.uint32))
+
+
+def test_mla_batched_rows_equal_single_rows():
+    """Two q rows through one call == each row alone (kernel_attend.rs:431-493, seed 0xba7c)."""
+    h, qh, nope, vh, kvl, block = 3, 20, 12, 8, 16, 4
+    r = orc.Lcg(0xBA7C)
+    packed, scale = orc.kvb_fixture(r, h * (nope + vh), kvl, block)
+    qs = [r.draws(h * qh) for _ in range(2)]
+    cs = [r.draws(h * kvl) for _ in range(2)]
+    both_a = orc.mla_absorb_fp8(np.concatenate(qs), packed, scale, h, qh, nope, vh, kvl, block, nrow=2)
+    both_v = orc.mla_value_fp8(np.concatenate(cs), packed, scale, h, nope, vh, kvl, block, nrow=2)
+    for i in range(2):
+        np.testing.assert_array_equal(both_a[i], orc.mla_absorb_fp8(qs[i], packed, scale, h, qh, nope, vh, kvl, block)[0])
+        np.testing.assert_array_equal(both_v[i], orc.mla_value_fp8(cs[i], packed, scale, h, nope, vh, kvl, block)[0])
