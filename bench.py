@@ -359,11 +359,55 @@ def run_ours(args):
                          "attend_tflops": af["attend"] * B / (stage_ms[2] * 1e-3) / 1e12},
             "clocks": clocks,
         }
+        proj = time_projections(w, device)
+        if proj:
+            line["next_rows"] = {"what": "q absorption and value up-projection through kv_b (tcgen05 kind::f16), per launch "
+                                         "at this batch, L2 flushed between launches; not part of the layer-step metric",
+                                 **proj}
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(w, seconds=12.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def time_projections(w, device, steps=50):
+    """The rows either side of the cache path (q absorption, value up-projection) at the workload's
+    batch: CUDA-event time per launch and algorithmic GB/s. Not part of the layer-step metric."""
+    import torch
+    from rivoli_b200 import backend as be
+    if w["n_heads"] != 64:
+        return None
+    H, qh, nope, vh, kvl, rope, block, B = 64, 256, 192, 256, KV_LORA, ROPE, 128, w["B"]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(w["seed"] + 77)
+    rows = H * (nope + vh)
+    kvb = torch.randint(0, 0x7E, (rows * kvl,), generator=gen, device=device, dtype=torch.int32).to(torch.uint8)
+    scale = torch.rand(((rows // block) * (kvl // block),), generator=gen, device=device) * 0.01 + 0.002
+    q = torch.randn((B, H, qh), generator=gen, device=device).to(torch.bfloat16)
+    clat = torch.randn((B, H, kvl), generator=gen, device=device).to(torch.bfloat16)
+    q_abs = torch.empty((B, H, kvl + rope), dtype=torch.bfloat16, device=device)
+    ctx = torch.empty((B, H, vh), dtype=torch.bfloat16, device=device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)      # > L2: weights come from HBM each time
+    out = {}
+    for name, fn, nbytes, flops in (
+            ("absorb", lambda: be.launch_mla_absorb_batched_bf16(q, kvb, scale, H, qh, nope, vh, kvl, rope, block, B, q_abs),
+             H * nope * kvl + B * H * (nope + rope) * 2 + B * H * (kvl + rope) * 2, 2 * B * H * nope * kvl),
+            ("value", lambda: be.launch_mla_value_batched_bf16(clat, kvb, scale, H, nope, vh, kvl, block, B, ctx),
+             H * vh * kvl + B * H * kvl * 2 + B * H * vh * 2, 2 * B * H * vh * kvl)):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize(device)
+            ts.append(e0.elapsed_time(e1))
+        ms = float(np.median(ts))
+        out[name] = {"us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9, "tflops": flops / (ms * 1e-3) / 1e12}
+    be.kvb_proj_status()
+    return out
 
 
 def run_gather_probe(args):
@@ -402,6 +446,11 @@ def run_profile(args):
     import torch
     if args.profile == "gather":
         return run_gather_probe(args)
+    if args.profile == "proj":
+        torch.cuda.set_device(0)
+        print(time_projections(WORKLOADS[args.workload], torch.device("cuda", 0), steps=3))
+        print("profile run ok: proj")
+        return
     w = dict(WORKLOADS[args.workload])
     if args.batch:
         w["B"] = args.batch                                # a smaller case of the same shape for multi-pass captures
@@ -494,7 +543,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile", default=None, choices=["select", "attend", "step", "gather"],
+    ap.add_argument("--profile", default=None, choices=["select", "attend", "step", "gather", "proj"],
                     help="build the workload, run 3 iterations of one stage (or the whole step) and exit: "
                          "the command line the profiles/ summaries were captured with")
     ap.add_argument("--batch", type=int, default=0,

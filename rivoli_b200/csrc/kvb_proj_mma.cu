@@ -9,9 +9,9 @@
 //   absorb: q_abs[b][h][i] = sum_d q[b][h][d] * kvb[448 h + d][i]         M = 128 sequences, N = 128 of the
 //           512 latent columns (one scale column), K = nope = 192 = two runs (the head's rows straddle one
 //           block boundary); CTA = (column block, head); weights are the MN-major B operand.
-//   value:  ctx[b][h][j]  = sum_i o[b][h][i] * kvb[448 h + 192 + j][i]     M = 128 sequences, N = 64 of the 256
-//           value rows (one scale row), K = kvl = 512 = four runs (one per scale column); CTA = (row block,
-//           head); weights are the K-major B operand.
+//   value:  ctx[b][h][j]  = sum_i o[b][h][i] * kvb[448 h + 192 + j][i]     M = 128 sequences, N = 128 of the 256
+//           value rows (two scale rows, one per 64 columns), K = kvl = 512 = four runs (one per scale
+//           column); CTA = (row block, head) - 128 CTAs, one wave; weights are the K-major B operand.
 // Geometry outside these shapes takes the CUDA-core kernels of kvb_proj.cu.
 // All waits are bounded (tc_common.cuh); a wait that gives up sets g_kp_err (rivoli_kvb_proj_status).
 #include "codec.cuh"
@@ -20,8 +20,15 @@
 
 namespace {
 
-constexpr int KP_THREADS = 128;
+constexpr int KP_THREADS = 256;   // 8 warps: loaders by (warp = row, lane = chunk); epilogue by (lane quadrant, column half)
+constexpr int KP_WARPS = KP_THREADS / 32;
 __device__ int g_kp_err;
+#ifdef RIVOLI_DEBUG_TIMES
+__device__ long long g_kp_times[2][8];
+#define KP_STAMP(k, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_kp_times[k][slot] = clock64(); } while (0)
+#else
+#define KP_STAMP(k, slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint64_t kp_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
@@ -92,57 +99,96 @@ kvb_absorb_mma_kernel(KpArgs A) {
     const bool two_runs = cut < nope;
     const float s1 = two_runs ? A.scale[((rbase + cut) >> 7) * sc_cols + iblk] : 0.0f;
 
+    KP_STAMP(0, 0);
     if (tid == 0) { tc::mbar_init(&bar, 1); tc::mbar_init_fence(); abort_word = 0; }
     if (warp == 0) tc::tmem_alloc<256>(&tmem_slot);
-    // weights: row d, this CTA's 128 columns = 16 pieces of 8 codes -> bf16 chunks, MN-major tile
-    for (int p = tid; p < nope * 16; p += KP_THREADS) {
-        const int d = p >> 4, pc = p & 15;
-        const uint2 c = *reinterpret_cast<const uint2*>(A.kvb + (rbase + d) * kvl + iblk * 128 + pc * 8);
-        *reinterpret_cast<uint4*>(sB + (pc >> 3) * (nope * 128) + tc::sw128_chunk(d, pc & 7)) = kp_codes_to_bf16(c);
+    KP_STAMP(0, 1);
+    // activations of a batch tile: 128 sequences x nope bf16, K-major swizzled; warp = row, lane = 16-byte chunk;
+    // rows past B are zeros. Asynchronous: requested BEFORE the weights are fetched and converted.
+    auto load_acts = [&](int b0) {
+        const int chunks = nope / 8;
+        for (int row = warp; row < 128; row += KP_WARPS) {
+            const bool live = b0 + row < A.B;
+            const uint16_t* src = A.x + ((size_t)(live ? b0 + row : 0) * A.H + h) * A.xs;
+            for (int j = lane; j < chunks; j += 32) {
+                uint8_t* dst = sA + (j >> 3) * 16384 + tc::sw128_chunk(row, j & 7);
+                if (live) tc::cp_async16(tc::smem_u32(dst), src + j * 8);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        tc::cp_async_commit();
+    };
+    load_acts(0);
+    // weights: row d, this CTA's 128 columns = 16 pieces of 8 codes -> bf16 chunks, MN-major tile.
+    // Two rows per warp pass (lane = row half x piece), four passes in flight before the first conversion.
+    for (int d0 = warp * 2; d0 < nope; d0 += KP_WARPS * 2 * 4) {
+        uint2 c[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int d = d0 + u * KP_WARPS * 2 + (lane >> 4);
+            c[u] = d < nope ? *reinterpret_cast<const uint2*>(A.kvb + (rbase + d) * kvl + iblk * 128 + (lane & 15) * 8) : make_uint2(0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int d = d0 + u * KP_WARPS * 2 + (lane >> 4), pc = lane & 15;
+            if (d < nope)
+                *reinterpret_cast<uint4*>(sB + (pc >> 3) * (nope * 128) + tc::sw128_chunk(d, pc & 7)) = kp_codes_to_bf16(c[u]);
+        }
     }
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = tmem_slot;
+    KP_STAMP(0, 2);
     const uint32_t idesc = kp_idesc(128, 128, 1);
-    const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
+    const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;   // TMEM lane quadrant of this warp
+    const int erow = (warp & 3) * 32 + lane, chalf = warp >> 2;      // epilogue: sequence row, column half
     bool ok = true;
     int phase = 0;
     for (int b0 = 0; b0 < A.B && ok; b0 += 128, phase ^= 1) {
-        // activations: 128 sequences x nope bf16, K-major swizzled tile; rows past B are zeros
-        const int chunks = nope / 8;   // 16-byte chunks per row
-        for (int c = tid; c < 128 * chunks; c += KP_THREADS) {
-            const int row = c / chunks, j = c - row * chunks;
-            uint8_t* dst = sA + (j >> 3) * 16384 + tc::sw128_chunk(row, j & 7);
-            if (b0 + row < A.B) tc::cp_async16(tc::smem_u32(dst), A.x + ((size_t)(b0 + row) * A.H + h) * A.xs + j * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        if (b0 > 0) load_acts(b0);     // the first tile was requested before the weights
+        // the rope segment of q rides along (column block 0 only; thread = sequence row): its loads go out
+        // now and are stored after the MMAs were issued, off every wait's critical path
+        uint4 rope_v[8];
+        const bool rope_mine = iblk == 0 && tid < 128 && b0 + tid < A.B;
+        if (rope_mine) {
+            const uint4* src = reinterpret_cast<const uint4*>(A.x + ((size_t)(b0 + tid) * A.H + h) * A.xs + nope);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) rope_v[e] = e < A.rope / 8 ? src[e] : make_uint4(0, 0, 0, 0);
         }
-        tc::cp_async_commit();
         tc::cp_async_wait<0>();
         tc::fence_proxy_async();
         __syncthreads();
+        KP_STAMP(0, 3);
         if (tid == 0) {
             tc::tc_fence_after();
             const uint32_t a0 = tc::smem_u32(sA), b0a = tc::smem_u32(sB);
             for (int k = 0; k < nope / 16; ++k) {     // 16 bf16 per MMA; a run boundary is a multiple of 64
                 const int run = (k * 16 >= cut) ? 1 : 0;
                 const bool first = (k * 16 == 0) || (k * 16 == cut);
+#ifdef KP_TEST_KMAJOR   // timing experiment only (wrong numbers): the same tile described as K-major
+                kp_mma(tmem + run * 128, kp_desc(a0 + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                       kp_desc(b0a + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), kp_idesc(128, 128, 0), first ? 0u : 1u);
+#else
                 kp_mma(tmem + run * 128, kp_desc(a0 + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
                        kp_desc(b0a + k * 2048, (uint32_t)nope * 128, 1024), idesc, first ? 0u : 1u);
+#endif
             }
             tc::mma_commit(&bar);
+            KP_STAMP(0, 4);
         }
-        // the rope segment of q rides along (column block 0 only): 16-byte copies, row = sequence
-        if (iblk == 0 && b0 + tid < A.B) {
-            const uint4* src = reinterpret_cast<const uint4*>(A.x + ((size_t)(b0 + tid) * A.H + h) * A.xs + nope);
+        if (rope_mine) {
             uint4* dst = reinterpret_cast<uint4*>(A.out + ((size_t)(b0 + tid) * A.H + h) * W + kvl);
-            for (int e = 0; e < A.rope / 8; ++e) dst[e] = src[e];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (e < A.rope / 8) dst[e] = rope_v[e];
         }
         ok = tc::mbar_wait(&bar, phase, abort_flag, 71);
+        KP_STAMP(0, 5);
         tc::tc_fence_after();
         if (ok) {
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = chalf * 2; c < chalf * 2 + 2; ++c) {
                 uint32_t r0[32], r1[32];
                 tc::tmem_ld32(tmem + lane_base + c * 32, r0);
                 tc::tmem_ld32(tmem + lane_base + 128 + c * 32, r1);
@@ -151,7 +197,7 @@ kvb_absorb_mma_kernel(KpArgs A) {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) r1[e] = 0u;
                 }
-                if (b0 + tid < A.B) {
+                if (b0 + erow < A.B) {
                     uint32_t o[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
@@ -159,7 +205,7 @@ kvb_absorb_mma_kernel(KpArgs A) {
                         const float v1 = fmaf(__uint_as_float(r1[e + 1]), s1, __uint_as_float(r0[e + 1]) * s0);
                         o[e >> 1] = (uint32_t)rv_f32_to_bf16(v0) | ((uint32_t)rv_f32_to_bf16(v1) << 16);
                     }
-                    uint4* dst = reinterpret_cast<uint4*>(A.out + ((size_t)(b0 + tid) * A.H + h) * W + iblk * 128 + c * 32);
+                    uint4* dst = reinterpret_cast<uint4*>(A.out + ((size_t)(b0 + erow) * A.H + h) * W + iblk * 128 + c * 32);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) dst[e] = make_uint4(o[4 * e], o[4 * e + 1], o[4 * e + 2], o[4 * e + 3]);
                 }
@@ -167,92 +213,131 @@ kvb_absorb_mma_kernel(KpArgs A) {
         }
         tc::tc_fence_before();
         __syncthreads();   // TMEM and the A tile are free for the next batch tile
+        KP_STAMP(0, 6);
     }
     if (warp == 0) tc::tmem_dealloc<256>(tmem);
     if (tid == 0 && abort_word) atomicCAS(&g_kp_err, 0, abort_word);
 }
 
 // ---------------------------------------------------------------------------------------------
-// value: grid (vh / 64, H), 128 threads. Shared: A [kvl/64][128 rows][128 B] | B [kvl/64][64 rows][128 B].
+// value: grid (vh / 128, H), 256 threads; N = 128 value rows = two 64-row scale rows.
+// Shared: A half [kvl/128][128 rows][128 B] (the contraction is fed in two halves) | B [kvl/64][128 rows][128 B].
+// TMEM: one 128-column accumulator per scale column (kvl / 128 <= 4 runs).
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(KP_THREADS)
 kvb_value_mma_kernel(KpArgs A) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ uint64_t bar;
+    __shared__ uint64_t bar[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
-    __shared__ float s_sc[8];
+    __shared__ float s_sc[2][4];
     volatile int* abort_flag = &abort_word;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int jblk = blockIdx.x, h = blockIdx.y;
     const int kvl = A.kvl, vh = A.vh;
-    const int kch = kvl / 64;                 // 128-byte K chunks
+    const int kch = kvl / 64;                 // 128-byte K chunks in all
+    const int hch = kch / 2;                  // per half
     uint8_t* sA = smem;
-    uint8_t* sB = smem + kch * 16384;
-    const size_t row0 = (size_t)h * (A.nope + vh) + A.nope + (size_t)jblk * 64;   // 64 value rows in ONE scale row
+    uint8_t* sB = smem + hch * 16384;
+    const size_t row0 = (size_t)h * (A.nope + vh) + A.nope + (size_t)jblk * 128;   // 128 value rows = 2 scale rows
     const int sc_cols = kvl / 128;
-    if (tid < sc_cols) s_sc[tid] = A.scale[(row0 >> 7) * sc_cols + tid];
-    if (tid == 0) { tc::mbar_init(&bar, 1); tc::mbar_init_fence(); abort_word = 0; }
-    if (warp == 0) tc::tmem_alloc<256>(&tmem_slot);
-    // weights: 64 rows x kvl codes -> bf16, K-major swizzled tile
+    KP_STAMP(1, 0);
+    if (tid < 2 * sc_cols) s_sc[tid / sc_cols][tid % sc_cols] = A.scale[((row0 + (tid / sc_cols) * 64) >> 7) * sc_cols + tid % sc_cols];
+    if (tid == 0) { tc::mbar_init(&bar[0], 1); tc::mbar_init(&bar[1], 1); tc::mbar_init_fence(); abort_word = 0; }
+    if (warp == 0) tc::tmem_alloc<512>(&tmem_slot);
+    // activations of one half of the contraction for a batch tile: 128 sequences x kvl/2 bf16, K-major
+    // swizzled; warp = row, lane = 16-byte chunk; rows past B are zeros. Asynchronous.
+    auto load_acts = [&](int b0, int half) {
+        const int chunks = kvl / 16;
+        for (int row = warp; row < 128; row += KP_WARPS) {
+            const bool live = b0 + row < A.B;
+            const uint16_t* src = A.x + ((size_t)(live ? b0 + row : 0) * A.H + h) * A.xs + half * (kvl / 2);
+            for (int j = lane; j < chunks; j += 32) {
+                uint8_t* dst = sA + (j >> 3) * 16384 + tc::sw128_chunk(row, j & 7);
+                if (live) tc::cp_async16(tc::smem_u32(dst), src + j * 8);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        tc::cp_async_commit();
+    };
+    load_acts(0, 0);
+    // weights: 128 rows x kvl codes -> bf16, K-major swizzled tile; warp = row, lane = piece of 8 codes;
+    // eight rows (16 loads per lane) in flight before the first conversion
     const int pieces = kvl / 8;
-    for (int p = tid; p < 64 * pieces; p += KP_THREADS) {
-        const int j = p / pieces, pc = p - j * pieces;
-        const uint2 c = *reinterpret_cast<const uint2*>(A.kvb + (row0 + j) * kvl + pc * 8);
-        *reinterpret_cast<uint4*>(sB + (pc >> 3) * 8192 + tc::sw128_chunk(j, pc & 7)) = kp_codes_to_bf16(c);
+#pragma unroll 1
+    for (int r0 = 0; r0 < 16; r0 += 8) {
+        uint2 c[8][2];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const uint8_t* wrow = A.kvb + (row0 + warp + (r0 + r) * KP_WARPS) * kvl;
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                c[r][u] = lane + 32 * u < pieces ? *reinterpret_cast<const uint2*>(wrow + (lane + 32 * u) * 8) : make_uint2(0, 0);
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const int j = warp + (r0 + r) * KP_WARPS;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int pc = lane + 32 * u;
+                if (pc < pieces) *reinterpret_cast<uint4*>(sB + (pc >> 3) * 16384 + tc::sw128_chunk(j, pc & 7)) = kp_codes_to_bf16(c[r][u]);
+            }
+        }
     }
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    const uint32_t idesc = kp_idesc(128, 64, 0);
-    const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
+    KP_STAMP(1, 2);
+    const uint32_t idesc = kp_idesc(128, 128, 0);
+    const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;   // TMEM lane quadrant of this warp
+    const int erow = (warp & 3) * 32 + lane, chalf = warp >> 2;      // epilogue: sequence row, 64-column half
     bool ok = true;
     int phase = 0;
     for (int b0 = 0; b0 < A.B && ok; b0 += 128, phase ^= 1) {
-        const int chunks = kvl / 8;
-        for (int c = tid; c < 128 * chunks; c += KP_THREADS) {
-            const int row = c / chunks, j = c - row * chunks;
-            uint8_t* dst = sA + (j >> 3) * 16384 + tc::sw128_chunk(row, j & 7);
-            if (b0 + row < A.B) tc::cp_async16(tc::smem_u32(dst), A.x + ((size_t)(b0 + row) * A.H + h) * A.xs + j * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-        }
-        tc::cp_async_commit();
-        tc::cp_async_wait<0>();
-        tc::fence_proxy_async();
-        __syncthreads();
-        if (tid == 0) {
-            tc::tc_fence_after();
-            const uint32_t a0 = tc::smem_u32(sA), b0a = tc::smem_u32(sB);
-            for (int k = 0; k < kvl / 16; ++k) {      // 8 MMAs per scale column (128 latent dims)
-                const int run = k >> 3;
-                kp_mma(tmem + run * 64, kp_desc(a0 + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
-                       kp_desc(b0a + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024), idesc, (k & 7) ? 1u : 0u);
+        for (int half = 0; half < 2 && ok; ++half) {
+            if (b0 > 0 || half > 0) load_acts(b0, half);   // the very first request went out before the weights
+            tc::cp_async_wait<0>();
+            tc::fence_proxy_async();
+            __syncthreads();
+            if (half == 0) KP_STAMP(1, 3);
+            if (tid == 0) {
+                tc::tc_fence_after();
+                const uint32_t a0 = tc::smem_u32(sA), b0a = tc::smem_u32(sB);
+                const int ks = kvl / 32;                  // MMAs per half; 8 per scale column (128 latent dims)
+                for (int kk = 0; kk < ks; ++kk) {
+                    const int k = half * ks + kk;
+                    kp_mma(tmem + (k >> 3) * 128, kp_desc(a0 + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                           kp_desc(b0a + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), idesc, (k & 7) ? 1u : 0u);
+                }
+                tc::mma_commit(&bar[half]);
+                if (half == 1) KP_STAMP(1, 4);
             }
-            tc::mma_commit(&bar);
+            // the A half may be overwritten (and the accumulators read) only once these MMAs are done
+            ok = tc::mbar_wait(&bar[half], phase, abort_flag, 72 + half);
         }
-        ok = tc::mbar_wait(&bar, phase, abort_flag, 72);
+        KP_STAMP(1, 5);
         tc::tc_fence_after();
         if (ok) {
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
+            for (int c = chalf * 2; c < chalf * 2 + 2; ++c) {
                 float acc[32];
 #pragma unroll
                 for (int e = 0; e < 32; ++e) acc[e] = 0.0f;
                 for (int run = 0; run < sc_cols; ++run) {
                     uint32_t r[32];
-                    tc::tmem_ld32(tmem + lane_base + run * 64 + c * 32, r);
+                    tc::tmem_ld32(tmem + lane_base + run * 128 + c * 32, r);
                     tc::tmem_ld_wait();
-                    const float s = s_sc[run];
+                    const float sc = s_sc[chalf][run];
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) acc[e] = fmaf(__uint_as_float(r[e]), s, acc[e]);
+                    for (int e = 0; e < 32; ++e) acc[e] = fmaf(__uint_as_float(r[e]), sc, acc[e]);
                 }
-                if (b0 + tid < A.B) {
+                if (b0 + erow < A.B) {
                     uint32_t o[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2)
                         o[e >> 1] = (uint32_t)rv_f32_to_bf16(acc[e]) | ((uint32_t)rv_f32_to_bf16(acc[e + 1]) << 16);
-                    uint4* dst = reinterpret_cast<uint4*>(A.out + ((size_t)(b0 + tid) * A.H + h) * vh + jblk * 64 + c * 32);
+                    uint4* dst = reinterpret_cast<uint4*>(A.out + ((size_t)(b0 + erow) * A.H + h) * vh + jblk * 128 + c * 32);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) dst[e] = make_uint4(o[4 * e], o[4 * e + 1], o[4 * e + 2], o[4 * e + 3]);
                 }
@@ -260,19 +345,20 @@ kvb_value_mma_kernel(KpArgs A) {
         }
         tc::tc_fence_before();
         __syncthreads();
+        KP_STAMP(1, 6);
     }
-    if (warp == 0) tc::tmem_dealloc<256>(tmem);
+    if (warp == 0) tc::tmem_dealloc<512>(tmem);
     if (tid == 0 && abort_word) atomicCAS(&g_kp_err, 0, abort_word);
 }
 
 }  // namespace
 
-// The tensor-core kernels cover: 128 x 128 scale blocks; kvl a multiple of 128 up to 512; nope a multiple
-// of 64 up to 256 whose rows straddle at most one block boundary; vh and the head's row count multiples
-// of 64; 16-byte aligned activation rows.
+// The tensor-core kernels cover: 128 x 128 scale blocks; kvl 256 or 512; nope a multiple of 64 up to 256
+// whose rows straddle at most one block boundary; vh a multiple of 128; the head's row count a multiple
+// of 64; 16-byte aligned activation rows; rope <= 64.
 extern "C" int rivoli_kvb_mma_supported(int H, int qh, int nope, int vh, int kvl, int rope, int block) {
-    if (block != 128 || kvl % 128 || kvl > 512 || nope % 64 || nope > 256 || vh % 64 || (nope + vh) % 64) return 0;
-    if (qh % 8 || rope % 8 || H <= 0) return 0;
+    if (block != 128 || kvl % 256 || kvl > 512 || nope % 64 || nope > 256 || vh % 128 || (nope + vh) % 64) return 0;
+    if (qh % 8 || rope % 8 || rope > 64 || H <= 0) return 0;
     for (int h = 0; h < 2 && h < H; ++h) {          // the straddle pattern repeats with period <= 2 heads
         const int off = (h * (nope + vh)) & 127;
         if (nope > (128 - off) + 128) return 0;       // would need a third run
@@ -283,7 +369,10 @@ extern "C" int rivoli_kvb_mma_supported(int H, int qh, int nope, int vh, int kvl
 extern "C" int rivoli_kvb_absorb_mma(const uint16_t* q, const uint8_t* kvb, const float* scale, int H, int qh, int nope,
                                      int vh, int kvl, int rope, int block, int B, uint16_t* q_abs, cudaStream_t st) {
     const KpArgs a{q, kvb, scale, H, qh, nope, vh, kvl, rope, block, B, q_abs};
-    const size_t smem = (size_t)(nope / 64) * 16384 + (size_t)2 * nope * 128;
+    size_t smem = (size_t)(nope / 64) * 16384 + (size_t)2 * nope * 128;
+#ifdef KP_TEST_ONE_CTA   // timing experiment: one CTA per SM
+    if (smem < 120 * 1024) smem = 120 * 1024;
+#endif
     cudaFuncSetAttribute(kvb_absorb_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     rv_drain_error();
     kvb_absorb_mma_kernel<<<dim3(kvl / 128, H), KP_THREADS, smem, st>>>(a);
@@ -293,10 +382,10 @@ extern "C" int rivoli_kvb_absorb_mma(const uint16_t* q, const uint8_t* kvb, cons
 extern "C" int rivoli_kvb_value_mma(const uint16_t* clat, const uint8_t* kvb, const float* scale, int H, int nope, int vh,
                                     int kvl, int block, int B, uint16_t* ctx, cudaStream_t st) {
     const KpArgs a{clat, kvb, scale, H, kvl, nope, vh, kvl, 0, block, B, ctx};
-    const size_t smem = (size_t)(kvl / 64) * 16384 + (size_t)(kvl / 64) * 8192;
+    const size_t smem = (size_t)(kvl / 128) * 16384 + (size_t)(kvl / 64) * 16384;
     cudaFuncSetAttribute(kvb_value_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     rv_drain_error();
-    kvb_value_mma_kernel<<<dim3(vh / 64, H), KP_THREADS, smem, st>>>(a);
+    kvb_value_mma_kernel<<<dim3(vh / 128, H), KP_THREADS, smem, st>>>(a);
     return rv_launch_status();
 }
 
@@ -310,3 +399,9 @@ RIVOLI_API int rivoli_kvb_proj_status(void* stream) {
     if (h) { const int z = 0; cudaMemcpyToSymbol(g_kp_err, &z, sizeof(int)); }
     return h ? 1008 : 0;
 }
+
+#ifdef RIVOLI_DEBUG_TIMES
+extern "C" __attribute__((visibility("default"))) int rivoli_kvb_debug_times(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_kp_times, sizeof(long long) * 16);
+}
+#endif
