@@ -135,6 +135,35 @@ class DsaDecodeLayer:
             raise be.BackendError("kv_append_paged(status)", 1005)
 
 
+class KvbProjection:
+    """The two contractions through kv_b either side of attention, batched
+    (``crates/engine/src/glm/attn.rs:161-173,231-242`` run them per token): ``absorb`` turns the
+    per-head query (nope values + rope segment) into the 576-wide row the attention operator
+    consumes, ``value`` projects the attention output to per-head values. Weights are the
+    reference's fp8 block-scaled kv_b ``[H*(nope+vh), kvl]`` with one f32 scale per 128x128 block."""
+
+    def __init__(self, geom: be.DsaGeom, n_seqs: int, kvb: torch.Tensor, kvb_scale: torch.Tensor, nope: int, vh: int,
+                 block: int = 128):
+        self.g, self.B, self.kvb, self.scale = geom, n_seqs, kvb, kvb_scale
+        self.nope, self.vh, self.block = nope, vh, block
+        self.qh = nope + geom.rope_dim
+        d = kvb.device
+        self.q_abs = torch.zeros((n_seqs, geom.n_heads, geom.kv_lora + geom.rope_dim), dtype=torch.bfloat16, device=d)
+        self.ctx = torch.zeros((n_seqs, geom.n_heads, vh), dtype=torch.bfloat16, device=d)
+
+    def absorb(self, q: torch.Tensor, stream=None) -> torch.Tensor:
+        g = self.g
+        be.launch_mla_absorb_batched_bf16(q, self.kvb, self.scale, g.n_heads, self.qh, self.nope, self.vh, g.kv_lora,
+                                          g.rope_dim, self.block, self.B, self.q_abs, stream=stream)
+        return self.q_abs
+
+    def value(self, clat: torch.Tensor, stream=None) -> torch.Tensor:
+        g = self.g
+        be.launch_mla_value_batched_bf16(clat, self.kvb, self.scale, g.n_heads, self.nope, self.vh, g.kv_lora,
+                                         self.block, self.B, self.ctx, stream=stream)
+        return self.ctx
+
+
 class HostStepPipeline:
     """Layer-steps for a caller whose activations live in HOST memory (pinned): every step
     copies its inputs host->device, runs append -> select -> attend, and copies the attention

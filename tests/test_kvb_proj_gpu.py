@@ -127,3 +127,40 @@ def test_batched_absorb_and_value_at_model_geometry(be, B):
                 err = np.abs(orc.bf16_to_f32(got).astype(np.float64) - want)
                 tol = 2.0 ** -8 * np.abs(want) + 1e-3 * np.abs(want).max()
                 assert (err <= tol).all(), float((err / tol).max())
+
+
+def test_absorb_step_value_chain_matches_oracle(be):
+    """A whole attention block of a decode layer: per-head q -> absorb -> (append, select, attend)
+    -> value, every stage checked against the oracle fed with the oracle's own previous stage."""
+    from rivoli_b200.layer import DsaDecodeLayer, KvbProjection
+    from tests.helpers import State, attend_close_ref, make_geom
+    g0 = GLM
+    st = State(31, 4, [700, 2100, 64, 300], top_k=256)
+    g = make_geom(be.DsaGeom, **st.geom_kw)
+    packed, scale, rng = _glm_weights(5)
+    B = st.B
+    q_heads = bf16_normal(rng, (B, g0["H"], g0["qh"]))
+    layer = DsaDecodeLayer(g, B, max_ctx=int(g.max_pages_per_seq * g.page_tokens))
+    layer.latent_pool.copy_(dev(st.latent_pool)); layer.latent_scale.copy_(dev(st.latent_scale))
+    layer.index_pool.copy_(dev(st.index_pool)); layer.index_scale.copy_(dev(st.index_scale))
+    layer.upload_block_table(st.block_table)
+    proj = KvbProjection(g, B, dev(packed), dev(scale), g0["nope"], g0["vh"])
+    q_abs = proj.absorb(dev(q_heads))
+    out = layer.step(dev(st.new_latent), dev(st.new_key), dev(st.index_q), dev(st.index_w), q_abs, dev(st.row_pos), dev(st.seq_len))
+    ctx = proj.value(out)
+    be.device_sync(); layer.check_status(); be.kvb_proj_status()
+    # oracle chain
+    want_q, _ = orc.mla_absorb_batched_bf16(q_heads, packed, scale, g0["H"], g0["qh"], g0["nope"], g0["vh"], g0["kvl"], g0["rope"], g0["block"])
+    got_q = q_abs.cpu().view(torch.int16).numpy().view(np.uint16)
+    dq = np.abs(orc.bf16_to_f32(got_q).astype(np.float64) - orc.bf16_to_f32(want_q))
+    assert (dq <= 2.0 ** -7 * np.abs(orc.bf16_to_f32(want_q)) + 1e-3 * np.abs(orc.bf16_to_f32(want_q)).max()).all()
+    st.q = got_q                                   # the oracle attends with the GPU's absorbed q: stage-wise check
+    want = st.oracle_step()
+    np.testing.assert_array_equal(layer.n_sel.cpu().numpy(), want["n_sel"])
+    ok, worst, rms = attend_close_ref(out.cpu().view(torch.int16).numpy().view(np.uint16), want["out_f32"])
+    assert ok and rms <= 1e-2, (worst, rms)
+    got_out = out.cpu().view(torch.int16).numpy().view(np.uint16)
+    _, want_c32 = orc.mla_value_batched_bf16(got_out, packed, scale, g0["H"], g0["nope"], g0["vh"], g0["kvl"], g0["block"])
+    got_c = orc.bf16_to_f32(ctx.cpu().view(torch.int16).numpy().view(np.uint16)).astype(np.float64)
+    err = np.abs(got_c - want_c32)
+    assert (err <= 2.0 ** -8 * np.abs(want_c32) + 1e-3 * np.abs(want_c32).max()).all(), float(err.max())
