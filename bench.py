@@ -114,17 +114,20 @@ class ClockSampler:
 
     def _poll(self):
         nv, h = self.nv, self.h
+        mask, i = 0, 0
         while not self.stop_flag:
             try:
                 mhz = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-                try:
-                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
-                except Exception:
-                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                if i % 4 == 0:          # the reasons query is the slower of the two
+                    try:
+                        mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+                    except Exception:
+                        mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
                 self.samples.append((time.perf_counter(), mhz, mask))
             except Exception:
                 pass
-            time.sleep(0.001)
+            i += 1
+            time.sleep(0.0002)
 
     def _read(self):
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -484,6 +487,7 @@ def cpu_baseline(w, seconds=12.0, n_seq=None):
     """Times the oracle (C restatement of the reference's host arithmetic, OpenMP) on a bounded
     sample of the same workload and scales to whole-batch layer-steps/s."""
     from oracle import oracle as orc
+    orc.set_num_threads(len(os.sched_getaffinity(0)))      # all host threads this process may use
     n_seq = n_seq or max(1, min(w["B"], 8))
     st = cpu_sample_state(w, n_seq, w["seed"])
     t0 = time.perf_counter()
@@ -510,6 +514,7 @@ def run_reference(args):
     w = WORKLOADS[args.workload]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     from oracle import oracle as orc
+    orc.set_num_threads(len(os.sched_getaffinity(0)))      # torchrun exports OMP_NUM_THREADS=1; rank 0 runs alone
     # bounded sample: about 11 ms of CPU work per cfg3 sequence; keep the whole run near two minutes
     per_seq_s = 0.011 * w["ctx"] / 16384
     n_seq = max(1, min(w["B"], 8, int(120.0 / max(1, args.steps + 1) / per_seq_s)))

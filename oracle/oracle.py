@@ -332,5 +332,9 @@ class Pool:
         return np.ctypeslib.as_array(p, shape=(self.n_pages,))[: self.n_free].copy()
 
 
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(int(n))
+
+
 def num_threads() -> int:
     return lib().orc_num_threads()

@@ -673,6 +673,16 @@ ORC_API void orc_mla_value_batched_bf16(const uint16_t* clat, const uint8_t* kvb
         }
 }
 
+/* Launchers that start one process per GPU export OMP_NUM_THREADS=1; the CPU arm runs on one
+ * rank only and may take the host's cores back. */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
