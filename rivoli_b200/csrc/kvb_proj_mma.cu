@@ -25,7 +25,12 @@ constexpr int KP_WARPS = KP_THREADS / 32;
 __device__ int g_kp_err;
 #ifdef RIVOLI_DEBUG_TIMES
 __device__ long long g_kp_times[2][8];
-#define KP_STAMP(k, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_kp_times[k][slot] = clock64(); } while (0)
+__device__ unsigned long long g_kp_span[2][512][3];   // per CTA: globaltimer at entry / exit, SM id
+__device__ __forceinline__ unsigned long long kp_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ unsigned kp_smid() { unsigned v; asm volatile("mov.u32 %0, %smid;" : "=r"(v)); return v; }
+#define KP_STAMP(k, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_kp_times[k][slot] = clock64(); \
+    if (threadIdx.x == 0 && ((slot) == 0 || (slot) == 6)) { const int cta = blockIdx.y * gridDim.x + blockIdx.x; \
+        if (cta < 512) { g_kp_span[k][cta][(slot) == 6] = kp_gtime(); g_kp_span[k][cta][2] = kp_smid(); } } } while (0)
 #else
 #define KP_STAMP(k, slot) do { } while (0)
 #endif
@@ -120,17 +125,18 @@ kvb_absorb_mma_kernel(KpArgs A) {
     };
     load_acts(0);
     // weights: row d, this CTA's 128 columns = 16 pieces of 8 codes -> bf16 chunks, MN-major tile.
-    // Two rows per warp pass (lane = row half x piece), four passes in flight before the first conversion.
-    for (int d0 = warp * 2; d0 < nope; d0 += KP_WARPS * 2 * 4) {
-        uint2 c[4];
+    // Two rows per warp pass (lane = row half x piece); ALL passes (nope <= 256: at most 16) are in flight
+    // before the first conversion, so the tile costs one memory round trip.
+    {
+        uint2 c[16];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int d = d0 + u * KP_WARPS * 2 + (lane >> 4);
+        for (int u = 0; u < 16; ++u) {
+            const int d = warp * 2 + u * KP_WARPS * 2 + (lane >> 4);
             c[u] = d < nope ? *reinterpret_cast<const uint2*>(A.kvb + (rbase + d) * kvl + iblk * 128 + (lane & 15) * 8) : make_uint2(0, 0);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int d = d0 + u * KP_WARPS * 2 + (lane >> 4), pc = lane & 15;
+        for (int u = 0; u < 16; ++u) {
+            const int d = warp * 2 + u * KP_WARPS * 2 + (lane >> 4), pc = lane & 15;
             if (d < nope)
                 *reinterpret_cast<uint4*>(sB + (pc >> 3) * (nope * 128) + tc::sw128_chunk(d, pc & 7)) = kp_codes_to_bf16(c[u]);
         }
@@ -262,21 +268,20 @@ kvb_value_mma_kernel(KpArgs A) {
     };
     load_acts(0, 0);
     // weights: 128 rows x kvl codes -> bf16, K-major swizzled tile; warp = row, lane = piece of 8 codes;
-    // eight rows (16 loads per lane) in flight before the first conversion
+    // all sixteen rows of a warp (32 loads per lane) in flight before the first conversion
     const int pieces = kvl / 8;
-#pragma unroll 1
-    for (int r0 = 0; r0 < 16; r0 += 8) {
-        uint2 c[8][2];
+    {
+        uint2 c[16][2];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const uint8_t* wrow = A.kvb + (row0 + warp + (r0 + r) * KP_WARPS) * kvl;
+        for (int r = 0; r < 16; ++r) {
+            const uint8_t* wrow = A.kvb + (row0 + warp + r * KP_WARPS) * kvl;
 #pragma unroll
             for (int u = 0; u < 2; ++u)
                 c[r][u] = lane + 32 * u < pieces ? *reinterpret_cast<const uint2*>(wrow + (lane + 32 * u) * 8) : make_uint2(0, 0);
         }
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const int j = warp + (r0 + r) * KP_WARPS;
+        for (int r = 0; r < 16; ++r) {
+            const int j = warp + r * KP_WARPS;
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 const int pc = lane + 32 * u;
@@ -403,5 +408,8 @@ RIVOLI_API int rivoli_kvb_proj_status(void* stream) {
 #ifdef RIVOLI_DEBUG_TIMES
 extern "C" __attribute__((visibility("default"))) int rivoli_kvb_debug_times(long long* host_out) {
     return (int)cudaMemcpyFromSymbol(host_out, g_kp_times, sizeof(long long) * 16);
+}
+extern "C" __attribute__((visibility("default"))) int rivoli_kvb_debug_spans(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_kp_span, sizeof(unsigned long long) * 2 * 512 * 3);
 }
 #endif
