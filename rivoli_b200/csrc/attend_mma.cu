@@ -21,9 +21,13 @@
 // TMEM (512 columns): S double buffered (2 x 128) + O^T (4 x 64).
 //
 // One CTA per (sequence, split), 13 warps: 0-7 softmax + epilogue (TMEM lane group = warp % 4 =
-// tokens / dims, warps 0-3 own heads 0-31 and warps 4-7 heads 32-63), 8 MMA issue, 9-12 gather
-// (a lane locates one row; copies go row by row, 32 lanes on 32 consecutive 16-byte chunks,
-// cp.async into the swizzled tile).
+// tokens / dims, warps 0-3 own heads 0-31 and warps 4-7 heads 32-63), 8 MMA issue, 9-12 gather:
+// two independent groups of two warps, one per K buffer (even / odd tiles), so two tiles are in
+// flight whenever both buffers are free; a lane locates rows, copies go row by row with 32 lanes
+// on 32 consecutive 16-byte chunks (cp.async into the swizzled tile); the row address chain
+// (token -> page -> pool row -> scale) is software-pipelined three tiles deep.
+// q arrives as bf16 and is split into its two e4m3 terms by warps 0-7 inside the kernel while the
+// first tiles are gathered; the output is staged in the idle K buffer and written as one block.
 // Online softmax with a LAGGING reference max: as long as no score of a tile exceeds its head's
 // reference by more than 3 (log2) the references stand (one barrier-with-OR per tile, no exchange);
 // otherwise the exact per-head maxima are taken and O is rescaled through TMEM. P' carries 2^5, so
@@ -112,7 +116,6 @@ attend_mma_kernel(AttendMmaArgs A) {
     float* s_fac = reinterpret_cast<float*>(smem + SM_FAC);
     uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + SM_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_MISC + 4);
-    volatile int* rescale_flag = reinterpret_cast<volatile int*>(smem + SM_MISC + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = blockIdx.y;
@@ -140,7 +143,6 @@ attend_mma_kernel(AttendMmaArgs A) {
         tc::mbar_init(&bars.q_full, AM_SOFTMAX_THREADS);
         tc::mbar_init_fence();
         *abort_flag = 0;
-        *rescale_flag = 0;
     }
     if (warp == 8) tc::tmem_alloc<512>(tmem_base_s);
 

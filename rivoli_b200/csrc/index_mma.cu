@@ -6,14 +6,17 @@
 // in the last bits, which would move top-k indices at the cut. This file therefore does:
 //
 //   1. index_q_prepare_kernel   q -> e4m3 codes + per-head scale (bit-exact codec), plus one
-//                               error-bound constant per sequence.
+//                               error-bound constant per sequence. On the fused decode path
+//                               (rivoli_dsa_append_select_paged) the same work runs in
+//                               step_prologue_kernel, whose extra blocks append the step's tokens.
 //   2. index_score_mma_kernel   approximate scores a_t for every cached token: fp8 keys are
 //                               streamed page by page by TMA (one 2-D box per page) into swizzled
 //                               shared memory and consumed by tcgen05.mma kind::f8f6f4
 //                               (tokens = M 128, heads = N 32, dims = K 128), accumulators
 //                               in TMEM, scale/ReLU/head-weight epilogue from TMEM.
-//   3. index_select_refine_kernel  per sequence: radix-select the k-th approximate score
-//                               A_k; every token with |a_t - A_k| <= 2*eps is re-scored in
+//   3. index_select_refine_kernel  per sequence: locate the k-th approximate score A_k by bisection
+//                               over register-resident keys; every token with |a_t - A_k| <= 2*eps
+//                               (plus the bisection's residual width) is re-scored in
 //                               the exact order (sequential f32 fold, identical to
 //                               rivoli_index_score_paged); tokens above the band are in,
 //                               below are out; the final exact top-k (ties -> lower index)
@@ -40,7 +43,6 @@ constexpr int IM_TILE = 128;       // tokens per MMA tile (M)
 constexpr int IM_HD = 128;         // index dim = one 128-byte swizzle row
 constexpr int IM_NPAD = 32;        // heads padded to N = 32
 constexpr int IM_NS = 6;           // key-tile stages in flight
-constexpr int IM_LAG = 4;          // cp.async groups kept pending
 constexpr int IM_NACC = 4;         // TMEM accumulators (32 columns each)
 constexpr int IM_TPI = 16;         // tiles per work item
 constexpr int IM_THREADS = 192;    // warps 0-3 epilogue, 4 producer, 5 MMA
@@ -53,7 +55,6 @@ struct IndexMmaArgs {
     const uint8_t* qcodes; const float* qscales; const float* w;
     const uint8_t* index_pool; const float* index_scale; const int32_t* block_table; const int32_t* seq_len;
     float* scores; int score_stride; int B;
-    unsigned int* skmax;   // [B] max key scale seen, float bits (>= 0)
     int* err;              // device error word (0 = ok)
 };
 
@@ -63,7 +64,7 @@ struct IndexMmaArgs {
 __device__ __forceinline__ void
 index_q_prepare_block(int b, const uint16_t* __restrict__ q, const float* __restrict__ w, int nh, int hd, float wscale,
                       float dscale, uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
-                      unsigned int* __restrict__ skmax, int* __restrict__ err, float* term) {
+                      int* __restrict__ err, float* term) {
     const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (h < nh) {
         const size_t v = (size_t)b * nh + h;
@@ -110,7 +111,6 @@ index_q_prepare_block(int b, const uint16_t* __restrict__ q, const float* __rest
         for (int i = 0; i < nh; ++i) s += term[i];
         // ||kcode||_2 <= sqrt(hd) * 448; 1.01 covers the roundings of this very sum
         cb[b] = s * sqrtf((float)hd) * 448.0f * IM_EPS_REL * 1.01f;
-        skmax[b] = 0u;
         if (b == 0) *err = 0;   // the scorer's error word starts clean on every call
     }
 }
@@ -118,9 +118,9 @@ index_q_prepare_block(int b, const uint16_t* __restrict__ q, const float* __rest
 __global__ void __launch_bounds__(1024)
 index_q_prepare_kernel(const uint16_t* __restrict__ q, const float* __restrict__ w, int nh, int hd, float wscale,
                        float dscale, uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
-                       unsigned int* __restrict__ skmax, int* __restrict__ err) {
+                       int* __restrict__ err) {
     __shared__ float term[32];
-    index_q_prepare_block(blockIdx.x, q, w, nh, hd, wscale, dscale, codes, scales, cb, skmax, err, term);
+    index_q_prepare_block(blockIdx.x, q, w, nh, hd, wscale, dscale, codes, scales, cb, err, term);
 }
 
 // Decode-step prologue in one launch: blocks [0, B) prepare the indexer query of sequence b,
@@ -134,11 +134,11 @@ struct AppendArgs {
 __global__ void __launch_bounds__(1024)
 step_prologue_kernel(DsaGeom g, AppendArgs ap, int B, const uint16_t* __restrict__ q, const float* __restrict__ w,
                      uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
-                     unsigned int* __restrict__ skmax, int* __restrict__ err) {
+                     int* __restrict__ err) {
     __shared__ float term[32];
     if ((int)blockIdx.x < B) {
         index_q_prepare_block(blockIdx.x, q, w, g.index_heads, g.index_dim, g.index_wscale, g.index_dscale, codes, scales,
-                              cb, skmax, err, term);
+                              cb, err, term);
         return;
     }
     const int row = ((int)blockIdx.x - B) * 32 + (threadIdx.x >> 5);
@@ -341,7 +341,7 @@ __host__ __device__ constexpr int rf_tok(int ept) { return ept > 16 ? 2 : 4; }
 struct RefineArgs {
     DsaGeom g;
     const float* scores; int score_stride; const int32_t* seq_len;
-    const uint8_t* qcodes; const float* qscales; const float* w; const float* cb; const unsigned int* skmax;
+    const uint8_t* qcodes; const float* qscales; const float* w; const float* cb;
     const uint8_t* index_pool; const float* index_scale; const int32_t* block_table;
     uint32_t* rows; int32_t* n_sel; int k;
     unsigned int* stats;   // [B][2]: band size, sure-in count (may be NULL)
@@ -619,7 +619,7 @@ index_select_refine_kernel(RefineArgs A) {
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct SelectScratch {
-    uint8_t* qcodes; float* qscales; float* cb; unsigned int* skmax; int* err; unsigned int* stats; float* scores;
+    uint8_t* qcodes; float* qscales; float* cb; int* err; unsigned int* stats; float* scores;
 };
 
 SelectScratch carve(const DsaGeom* g, int B, int score_stride, void* scratch, size_t* total) {
@@ -630,7 +630,6 @@ SelectScratch carve(const DsaGeom* g, int B, int score_stride, void* scratch, si
     s.qcodes = take((size_t)B * g->index_heads * g->index_dim);
     s.qscales = reinterpret_cast<float*>(take((size_t)B * g->index_heads * 4));
     s.cb = reinterpret_cast<float*>(take((size_t)B * 4));
-    s.skmax = reinterpret_cast<unsigned int*>(take((size_t)B * 4));
     s.err = reinterpret_cast<int*>(take(4));
     s.stats = reinterpret_cast<unsigned int*>(take((size_t)B * 8));
     s.scores = reinterpret_cast<float*>(take((size_t)B * score_stride * 4));
@@ -700,14 +699,14 @@ static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* i
     rv_drain_error();
     if (ap)
         step_prologue_kernel<<<B + (B + 31) / 32, 1024, 0, st>>>(*g, *ap, B, index_q, w, s.qcodes, s.qscales, s.cb,
-                                                                 s.skmax, s.err);
+                                                                 s.err);
     else
         index_q_prepare_kernel<<<B, 32 * nh, 0, st>>>(index_q, w, nh, hd, g->index_wscale, g->index_dscale, s.qcodes,
-                                                       s.qscales, s.cb, s.skmax, s.err);
+                                                       s.qscales, s.cb, s.err);
     if (int e = rv_launch_status()) return e;
 
     IndexMmaArgs ma{*g, s.qcodes, s.qscales, w, index_pool, index_scale, block_table, seq_len,
-                    s.scores, score_stride, B, s.skmax, s.err};
+                    s.scores, score_stride, B, s.err};
     const size_t smem1 = (size_t)IM_NS * IM_STAGE_BYTES + 2 * IM_Q_BYTES + 1024;
     cudaFuncSetAttribute(index_score_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     int dev = 0, sms = 148;
@@ -724,7 +723,7 @@ static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* i
     index_score_mma_kernel<<<grid, IM_THREADS, smem1, st>>>(ma, tm_keys, tm_q);
     if (int e = rv_launch_status()) return e;
 
-    RefineArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb, s.skmax,
+    RefineArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb,
                   index_pool, index_scale, block_table, rows, n_sel, g->top_k, s.stats,
                   (score_stride % 4 == 0 && ((uintptr_t)index_scale & 15) == 0 && g->page_tokens % 4 == 0) ? 1 : 0};
 #define RV_REFINE(EPT)                                                                                            \

@@ -1,4 +1,4 @@
-"""Continuous batching with eviction churn on the GPU (BASELINE config 5 at reduced scale): several
+"""Continuous batching with eviction churn on the GPU (the 78-layer churn workload at reduced scale): several
 layers share one page allocator, every step appends one token per sequence per layer, some
 sequences finish and their slots are refilled (pages go back to the free list and are drawn again,
 the replacement's context is prefilled through the same append operator). After every step the

@@ -1,4 +1,4 @@
-"""BASELINE-sized shapes on the GPU, checked through size-independent properties and through
+"""Benchmark-sized shapes on the GPU, checked through size-independent properties and through
 the oracle on sampled sequences (the oracle runs one 16384-token sequence in well under a
 second): append round trip, fused tensor-core selection == exact chain bit for bit,
 determinism, attention against the oracle."""
@@ -122,7 +122,7 @@ def test_attention_at_full_selection_width(cfg3_like):
 
 
 def test_cfg2_dense_equivalent_shape():
-    """BASELINE config 2 whole: batch 32, ctx 2048, k = 2048 (selection is the identity)."""
+    """The dense-equivalent benchmark shape whole: batch 32, ctx 2048, k = 2048 (selection is the identity)."""
     w = dict(bench.WORKLOADS["cfg2"])
     dev = torch.device("cuda", 0)
     g, layer, gen = bench.build_layer(w, dev, 7)

@@ -32,7 +32,7 @@ def u16(t):
 def check_mma_attention(got_bits, want_f32, elementwise):
     """Gate of the tensor-core attention (q and P each carried as two e4m3 terms, ~2^-9
     relative, i.e. bf16-class): the reference's tolerance form with 2e-2 / 1e-3, an rms
-    bound of 0.5 % of rms(want), and - at 2048 attended rows and more, the BASELINE shapes -
+    bound of 0.5 % of rms(want), and - at 2048 attended rows and more, the benchmark shapes -
     the elementwise form |err| <= 2e-2 |want| + 1e-3 as well."""
     ok, worst, rms = attend_close_ref(got_bits, want_f32)
     assert ok, worst
@@ -43,7 +43,7 @@ def check_mma_attention(got_bits, want_f32, elementwise):
 
 
 CASES = {
-    # BASELINE config 1: 1 sequence, 256 cached + 1 appended, H=16, indexer 8x64, k=64, 16-token pages
+    # the smallest benchmark shape: 1 sequence, 256 cached + 1 appended, H=16, indexer 8x64, k=64, 16-token pages
     "cfg1": dict(seed=0, B=1, ctx=[257], n_heads=16, index_heads=8, index_dim=64, page_tokens=16, top_k=64,
                  pool_factor=1.0),
     # ragged batch, model dims, top-k smaller / larger than the contexts

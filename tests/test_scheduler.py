@@ -1,4 +1,4 @@
-"""Continuous batching with eviction churn (BASELINE config 5 at reduced scale): page tables
+"""Continuous batching with eviction churn (the 78-layer churn workload at reduced scale): page tables
 and free lists stay bit-identical to the oracle's allocator, no page is ever mapped twice,
 and a pool sized 1.25x the worst live set never runs dry."""
 import numpy as np
