@@ -272,6 +272,39 @@ int rivoli_mla_value_batched_bf16(const uint16_t* clat, const unsigned char* kvb
 /* Synchronises `stream`; 1008 if a bounded wait of a tensor-core projection gave up since the last call. */
 int rivoli_kvb_proj_status(void* stream);
 
+/* ---- indexer front end: what produces the indexer's key, queries and head weights ------------------
+ * rivoli_gemv_fp8 (+ _splitk), rivoli_layernorm, rivoli_rope_interleave replace
+ * crates/backend/kernels/linalg.hip:305-342, indexer.hip:259-266, activation.hip:551-559 (same arguments and
+ * guards). y[r][o] = sum_i (e4m3(W[o][i]) * scale[(o/block) * ceil(i_dim/block) + i/block]) * x[r][i] in the
+ * fold order of crates/artifact/src/quant/fp8.rs:32-42; layernorm with var = E[x^2] - mean^2; RoPE pairs
+ * (2j, 2j+1) -> (j, seg/2 + j) at angle pos * theta^(-2j/seg) computed in f64. */
+int rivoli_gemv_fp8(const float* x, const unsigned char* packed, const float* scale, int o_dim, int i_dim, int block,
+                    int nrow, float* y);
+int rivoli_gemv_fp8_splitk(const float* x, const unsigned char* packed, const float* scale, int o_dim, int i_dim,
+                           int block, int nrow, float* y);
+int rivoli_layernorm(const float* x, const float* w, const float* b, int n, float eps, float* y);
+int rivoli_rope_interleave(float* base, int count, int stride, int seg, int pos, double theta);
+/* Batched decode form, no counterpart in the reference: for every sequence b at position pos[b]
+ *   index_key[b]   = bf16(rope(layernorm(wk . x[b])))              [index_dim]
+ *   index_q[b][h]  = bf16(rope((wq_b . q_resid[b])[h]))            [index_heads][index_dim]
+ *   index_w[b]     = weights_proj . x[b]                           [index_heads] f32
+ * x bf16 [B][hidden], q_resid bf16 [B][q_lora]; the three weight matrices are e4m3 with block x block
+ * scales; the rotation covers [rope_off, rope_off + rope_seg) of every index_dim-wide vector. The outputs
+ * are the rows rivoli_kv_append_paged / rivoli_index_select_paged take. scratch =
+ * rivoli_index_frontend_scratch_bytes() (split-K partial sums; the split is fixed by the geometry and
+ * summed in order, so results are reproducible). */
+typedef struct IndexFrontGeom {
+    int32_t hidden, q_lora, index_heads, index_dim, rope_off, rope_seg, block;
+    float eps;       /* LayerNorm epsilon (the reference: 1e-6, crates/engine/src/indexer.rs:12) */
+    double theta;    /* RoPE base */
+} IndexFrontGeom;
+size_t rivoli_index_frontend_scratch_bytes(const IndexFrontGeom* g, int B);
+int rivoli_index_frontend_bf16(const IndexFrontGeom* g, const uint16_t* x, const uint16_t* q_resid, const int32_t* pos,
+                               int B, const unsigned char* wk, const float* wk_scale, const float* knorm_w,
+                               const float* knorm_b, const unsigned char* wq_b, const float* wq_b_scale,
+                               const unsigned char* wproj, const float* wproj_scale, uint16_t* index_key,
+                               uint16_t* index_q, float* index_w, void* scratch, void* stream);
+
 /* Diagnostic, not on any product path (bench.py --profile gather): average milliseconds of a
  * launch in which each of n_ctas CTAs copies n_tiles tiles of 128 latent rows (576 bytes each,
  * rows[cta][tile][128] = pool row numbers) from the pool into shared memory with `depth` (1..3)

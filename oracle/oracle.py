@@ -285,6 +285,40 @@ def mla_value_batched_bf16(clat, kvb, scale, H, nope, vh, kvl, block):
     return out, f32
 
 
+def gemv_fp8(x, packed, scale, o_dim, i_dim, block, nrow=1) -> np.ndarray:
+    """f32 x ``[nrow, i_dim]`` through e4m3 block-scaled ``W[o_dim, i_dim]`` (crates/artifact/src/quant/fp8.rs:32-42)."""
+    x, packed, scale = _c(x, np.float32), _c(packed, np.uint8), _c(scale, np.float32)
+    y = np.zeros((nrow, o_dim), dtype=np.float32)
+    lib().orc_gemv_fp8(_p(x), _p(packed), _p(scale), o_dim, i_dim, block, nrow, _p(y))
+    return y
+
+
+def layernorm(x, w, b, eps) -> np.ndarray:
+    x, w, b = _c(x, np.float32), _c(w, np.float32), _c(b, np.float32)
+    y = np.zeros_like(x)
+    lib().orc_layernorm(_p(x), _p(w), _p(b), x.size, C.c_float(eps), _p(y))
+    return y
+
+
+def rope_interleave(base, count, stride, seg, pos, theta) -> np.ndarray:
+    v = _c(base, np.float32).copy()
+    lib().orc_rope_interleave(_p(v), count, stride, seg, pos, C.c_double(theta))
+    return v
+
+
+def index_frontend_bf16(x, qr, pos, nh, hd, rope_off, rope_seg, theta, eps, block, wk, wk_s, kn_w, kn_b, wq, wq_s, wp, wp_s):
+    """Batched indexer front end; returns (index_key bf16, index_q bf16, index_w f32, key f32, q f32)."""
+    x, qr, pos = _c(x, np.uint16), _c(qr, np.uint16), _c(pos, np.int32)
+    B = pos.size
+    hidden, q_lora = x.size // B, qr.size // B
+    key = np.zeros((B, hd), np.uint16); q = np.zeros((B, nh, hd), np.uint16); w = np.zeros((B, nh), np.float32)
+    k32 = np.zeros((B, hd), np.float32); q32 = np.zeros((B, nh, hd), np.float32)
+    a = [_c(t, np.uint8) if t.dtype == np.uint8 else _c(t, np.float32) for t in (wk, wk_s, kn_w, kn_b, wq, wq_s, wp, wp_s)]
+    lib().orc_index_frontend_bf16(_p(x), _p(qr), _p(pos), B, hidden, q_lora, nh, hd, rope_off, rope_seg, C.c_double(theta),
+                                  C.c_float(eps), block, *[_p(t) for t in a], _p(key), _p(q), _p(w), _p(k32), _p(q32))
+    return key, q, w, k32, q32
+
+
 def kvb_fixture(r: "Lcg", rows, kvl, block):
     """kv_b bytes then the block-scale grid, drawn in that order
     (crates/engine/tests/kernel_attend.rs:127-132, tests/common/reference.rs:218-220)."""

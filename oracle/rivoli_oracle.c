@@ -673,6 +673,93 @@ ORC_API void orc_mla_value_batched_bf16(const uint16_t* clat, const uint8_t* kvb
         }
 }
 
+/* ---------------------------------------------------------------------------------------------
+ * Indexer front end: the operators that produce the indexer's key, queries and head weights
+ * (crates/backend/kernels/indexer.hip:1-13).
+ * ------------------------------------------------------------------------------------------- */
+/* y[r][o] = sum_i (e4m3(W[o][i]) * scale[(o/block)*ceil(i_dim/block) + i/block]) * x[r][i], left fold from 0
+ * (crates/artifact/src/quant/fp8.rs:32-42; scale row clamped like the kv_b dequant). */
+ORC_API void orc_gemv_fp8(const float* x, const uint8_t* packed, const float* scale, int o_dim, int i_dim, int block,
+                          int nrow, float* y) {
+    const int sc_cols = (i_dim + block - 1) / block;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int r = 0; r < nrow; ++r)
+        for (int o = 0; o < o_dim; ++o) {
+            float acc = 0.0f;
+            const uint8_t* row = packed + (size_t)o * i_dim;
+            const float* srow = scale + (size_t)(o / block) * sc_cols;
+            for (int i = 0; i < i_dim; ++i) acc += orc_e4m3_to_f32(row[i]) * srow[i / block] * x[(size_t)r * i_dim + i];
+            y[(size_t)r * o_dim + o] = acc;
+        }
+}
+
+/* y = (x - mean) / sqrt(var + eps) * w + b with var = E[x^2] - mean^2: f64 sums, f32 formula
+ * (crates/engine/tests/indexer_kernel.rs:60-72; kernel crates/backend/kernels/indexer.hip:22-50). */
+ORC_API void orc_layernorm(const float* x, const float* w, const float* b, int n, float eps, float* y) {
+    double s = 0.0, sq = 0.0;
+    for (int i = 0; i < n; ++i) { s += (double)x[i]; sq += (double)x[i] * (double)x[i]; }
+    const float mean = (float)(s / (double)n);
+    const float var = (float)(sq / (double)n) - mean * mean;
+    const float inv = 1.0f / sqrtf(var + eps);
+    for (int i = 0; i < n; ++i) y[i] = (x[i] - mean) * inv * w[i] + b[i];
+}
+
+/* Interleaved RoPE in place on `count` segments of `seg` floats, segment s at base + s*stride: the pair
+ * (2j, 2j+1) rotates by pos * theta^(-2j/seg) (angle in f64, cos/sin narrowed to f32) and lands at
+ * (j, seg/2 + j) (crates/backend/kernels/activation.hip:337-371; host crates/engine/tests/kernel_vector.rs:296-313). */
+ORC_API void orc_rope_interleave(float* base, int count, int stride, int seg, int pos, double theta) {
+    const int half = seg / 2;
+    float tmp[1024];
+    for (int s = 0; s < count; ++s) {
+        float* v = base + (size_t)s * stride;
+        for (int i = 0; i < seg && i < 1024; ++i) tmp[i] = v[i];
+        for (int j = 0; j < half; ++j) {
+            const float a = tmp[2 * j], b = tmp[2 * j + 1];
+            const double ang = (double)pos * pow(theta, -2.0 * (double)j / (double)seg);
+            const float cs = (float)cos(ang), sn = (float)sin(ang);
+            v[j] = a * cs - b * sn;
+            v[half + j] = b * cs + a * sn;
+        }
+    }
+}
+
+/* The batched decode form (no reference counterpart): per sequence b at position pos[b]
+ *   k   = rope(layernorm(wk . x_b))                      -> index_key bf16 [B][hd]
+ *   q_h = rope((wq_b . qr_b)[h])                          -> index_q  bf16 [B][nh][hd]
+ *   w   = wproj . x_b                                      -> index_w  f32 [B][nh]
+ * x bf16 [B][hidden], qr bf16 [B][q_lora]; weights fp8 block-scaled as for orc_gemv_fp8; the rope
+ * segment is [rope_off, rope_off + rope_seg) of each hd-wide vector. f32 arithmetic as above,
+ * one bf16 rounding at the stores. k32/q32 (may be NULL) receive the unrounded values. */
+ORC_API void orc_index_frontend_bf16(const uint16_t* x, const uint16_t* qr, const int32_t* pos, int B, int hidden,
+                                     int q_lora, int nh, int hd, int rope_off, int rope_seg, double theta, float eps,
+                                     int block, const uint8_t* wk, const float* wk_s, const float* kn_w,
+                                     const float* kn_b, const uint8_t* wq, const float* wq_s, const uint8_t* wp,
+                                     const float* wp_s, uint16_t* index_key, uint16_t* index_q, float* index_w,
+                                     float* k32, float* q32) {
+#pragma omp parallel for schedule(dynamic)
+    for (int b = 0; b < B; ++b) {
+        float* xf = (float*)malloc(sizeof(float) * (size_t)(hidden + q_lora + hd + hd + (size_t)nh * hd));
+        float* qf = xf + hidden;
+        float* k0 = qf + q_lora;
+        float* k1 = k0 + hd;
+        float* qq = k1 + hd;
+        for (int i = 0; i < hidden; ++i) xf[i] = orc_bf16_to_f32(x[(size_t)b * hidden + i]);
+        for (int i = 0; i < q_lora; ++i) qf[i] = orc_bf16_to_f32(qr[(size_t)b * q_lora + i]);
+        /* the nested calls run single-threaded inside this parallel region */
+        orc_gemv_fp8(xf, wk, wk_s, hd, hidden, block, 1, k0);
+        orc_layernorm(k0, kn_w, kn_b, hd, eps, k1);
+        orc_rope_interleave(k1 + rope_off, 1, hd, rope_seg, pos[b], theta);
+        orc_gemv_fp8(qf, wq, wq_s, nh * hd, q_lora, block, 1, qq);
+        orc_rope_interleave(qq + rope_off, nh, hd, rope_seg, pos[b], theta);
+        orc_gemv_fp8(xf, wp, wp_s, nh, hidden, block, 1, index_w + (size_t)b * nh);
+        for (int i = 0; i < hd; ++i) index_key[(size_t)b * hd + i] = orc_f32_to_bf16(k1[i]);
+        for (int i = 0; i < nh * hd; ++i) index_q[(size_t)b * nh * hd + i] = orc_f32_to_bf16(qq[i]);
+        if (k32) for (int i = 0; i < hd; ++i) k32[(size_t)b * hd + i] = k1[i];
+        if (q32) for (int i = 0; i < nh * hd; ++i) q32[(size_t)b * nh * hd + i] = qq[i];
+        free(xf);
+    }
+}
+
 /* Launchers that start one process per GPU export OMP_NUM_THREADS=1; the CPU arm runs on one
  * rank only and may take the host's cores back. */
 ORC_API void orc_set_num_threads(int n) {

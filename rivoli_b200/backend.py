@@ -77,6 +77,7 @@ def lib() -> C.CDLL:
         L.rivoli_mla_attend_paged_scratch_bytes.restype = C.c_size_t
         L.rivoli_attend_simt_scratch_bytes.restype = C.c_size_t
         L.rivoli_index_select_scratch_bytes.restype = C.c_size_t
+        L.rivoli_index_frontend_scratch_bytes.restype = C.c_size_t
         L.rivoli_kernels_arch.restype = C.c_char_p
         L.rivoli_pagepool_create.restype = C.c_void_p
         L.rivoli_pagepool_block_table.restype = C.POINTER(C.c_int32)
@@ -359,6 +360,38 @@ def launch_mla_value_batched_bf16(clat, kvb, kvb_scale, H: int, nope: int, vh: i
 
 def kvb_proj_status(stream=None) -> None:
     ensure_status(lib().rivoli_kvb_proj_status(_stream(stream)), "kvb_proj(status)")
+
+
+class IndexFrontGeom(C.Structure):
+    """``repr(C)`` mirror of ``IndexFrontGeom`` (include/rivoli_kernels.h)."""
+    _fields_ = [(n, C.c_int32) for n in ("hidden", "q_lora", "index_heads", "index_dim", "rope_off", "rope_seg", "block")] + \
+               [("eps", C.c_float), ("theta", C.c_double)]
+
+
+def launch_gemv_fp8(x, packed, scale, o_dim: int, i_dim: int, block: int, nrow: int, y) -> None:
+    ensure_status(lib().rivoli_gemv_fp8(_ptr(x), _ptr(packed), _ptr(scale), C.c_int(o_dim), C.c_int(i_dim), C.c_int(block),
+                                        C.c_int(nrow), _ptr(y)), "gemv_fp8")
+
+
+def launch_layernorm(x, w, b, n: int, eps: float, y) -> None:
+    ensure_status(lib().rivoli_layernorm(_ptr(x), _ptr(w), _ptr(b), C.c_int(n), C.c_float(eps), _ptr(y)), "layernorm")
+
+
+def launch_rope_interleave(base, count: int, stride: int, seg: int, pos: int, theta: float) -> None:
+    ensure_status(lib().rivoli_rope_interleave(_ptr(base), C.c_int(count), C.c_int(stride), C.c_int(seg), C.c_int(pos),
+                                               C.c_double(theta)), "rope_interleave")
+
+
+def index_frontend_scratch_bytes(g: IndexFrontGeom, B: int) -> int:
+    return int(lib().rivoli_index_frontend_scratch_bytes(C.byref(g), C.c_int(B)))
+
+
+def launch_index_frontend_bf16(g: IndexFrontGeom, x, q_resid, pos, B: int, wk, wk_scale, knorm_w, knorm_b, wq_b, wq_b_scale,
+                               wproj, wproj_scale, index_key, index_q, index_w, scratch, stream=None) -> None:
+    ensure_status(lib().rivoli_index_frontend_bf16(
+        C.byref(g), _ptr(x), _ptr(q_resid), _ptr(pos), C.c_int(B), _ptr(wk), _ptr(wk_scale), _ptr(knorm_w), _ptr(knorm_b),
+        _ptr(wq_b), _ptr(wq_b_scale), _ptr(wproj), _ptr(wproj_scale), _ptr(index_key), _ptr(index_q), _ptr(index_w),
+        _ptr(scratch), _stream(stream)), "index_frontend_bf16")
 
 
 def probe_gather(method: int, depth: int, n_ctas: int, n_tiles: int, pool, n_pool_rows: int, scales, rows,

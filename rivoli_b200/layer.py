@@ -100,18 +100,28 @@ class DsaDecodeLayer:
         be.launch_index_topk_batched(self.scores, self.score_stride, seq_len, self.B, g.top_k, self.rows,
                                      self.n_sel, stream)
 
+    def append_latent_only(self, latent: torch.Tensor, row_pos: torch.Tensor, stream=None) -> None:
+        """Cache the step's latent rows of a layer that owns no indexer: the index key that travels with the
+        operator is a constant zero row written to this layer's (unused) index pool."""
+        n = latent.shape[0]
+        if getattr(self, "_zero_key", None) is None or self._zero_key.shape[0] != n:
+            self._zero_key = torch.zeros((n, self.g.index_dim), dtype=torch.bfloat16, device=self.dev)
+        self.append(latent, self._zero_key, row_pos, None, stream)
+
     def attend(self, q: torch.Tensor, stream=None, dense_len: torch.Tensor | None = None,
-               out: torch.Tensor | None = None) -> torch.Tensor:
+               out: torch.Tensor | None = None, rows_from: "DsaDecodeLayer | None" = None) -> torch.Tensor:
         """Attention over the selected rows (or, with ``dense_len``, over the whole prefix).
-        Writes ``self.out`` unless another bf16 ``[B, H, kv_lora]`` buffer is given."""
+        Writes ``self.out`` unless another bf16 ``[B, H, kv_lora]`` buffer is given. ``rows_from``:
+        attend over another layer's selection (a layer that shares its predecessor's indexer)."""
         out = self.out if out is None else out
+        sel = self if rows_from is None else rows_from
         if dense_len is not None:
             be.launch_attend_paged_bf16(self.g, q, self.latent_pool, self.latent_scale, self.block_table,
                                         None, 0, dense_len, self.B, out, self.out_m, self.out_lse,
                                         self.scratch, stream)
         else:
             be.launch_attend_paged_bf16(self.g, q, self.latent_pool, self.latent_scale, self.block_table,
-                                        self.rows, self.g.top_k, self.n_sel, self.B, out, self.out_m,
+                                        sel.rows, self.g.top_k, sel.n_sel, self.B, out, self.out_m,
                                         self.out_lse, self.scratch, stream)
         return out
 
@@ -162,6 +172,27 @@ class KvbProjection:
         be.launch_mla_value_batched_bf16(clat, self.kvb, self.scale, g.n_heads, self.nope, self.vh, g.kv_lora,
                                          self.block, self.B, self.ctx, stream=stream)
         return self.ctx
+
+
+class IndexerFrontEnd:
+    """Produces what the indexer of a decode layer consumes - index key, index queries and head
+    weights - from the layer's hidden state and the compressed query (``crates/backend/kernels/indexer.hip:1-13``),
+    batched over sequences. Weights are fp8 block-scaled; ``positions`` are the tokens' positions."""
+
+    def __init__(self, fg: be.IndexFrontGeom, n_seqs: int, weights: dict, device="cuda:0"):
+        self.fg, self.B, self.w = fg, n_seqs, weights
+        d = torch.device(device)
+        self.index_key = torch.zeros((n_seqs, fg.index_dim), dtype=torch.bfloat16, device=d)
+        self.index_q = torch.zeros((n_seqs, fg.index_heads, fg.index_dim), dtype=torch.bfloat16, device=d)
+        self.index_w = torch.zeros((n_seqs, fg.index_heads), dtype=torch.float32, device=d)
+        self.scratch = torch.zeros(max(be.index_frontend_scratch_bytes(fg, n_seqs), 16), dtype=torch.uint8, device=d)
+
+    def run(self, x: torch.Tensor, q_resid: torch.Tensor, positions: torch.Tensor, stream=None):
+        w = self.w
+        be.launch_index_frontend_bf16(self.fg, x, q_resid, positions, self.B, w["wk"], w["wk_scale"], w["knorm_w"],
+                                      w["knorm_b"], w["wq_b"], w["wq_b_scale"], w["wproj"], w["wproj_scale"],
+                                      self.index_key, self.index_q, self.index_w, self.scratch, stream)
+        return self.index_key, self.index_q, self.index_w
 
 
 class HostStepPipeline:

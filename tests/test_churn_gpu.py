@@ -86,3 +86,40 @@ def test_churn_three_layers_match_oracle():
         sched.finish(slots, lens)
         prefill(slots, lens)
     assert sched._next_id == n_slots + steps * 2
+
+
+def test_shared_layers_attend_over_the_full_layers_selection():
+    """A full layer followed by two shared layers: the shared layers run no scorer / top-k, cache only their
+    latent rows, and their attention equals the oracle's attention over the FULL layer's rows on their own
+    latent cache."""
+    from rivoli_b200 import backend as be
+    from rivoli_b200.engine import DsaDecodeStack, indexer_layout
+    from tests.helpers import State
+    be.lib()
+    full = indexer_layout(["full", "shared", "shared"], 3, 32, 128, 256)
+    states = [State(50 + i, 3, [700, 300, 2100], top_k=256) for i in range(3)]     # same geometry, different contents
+    st0 = states[0]
+    g = make_geom(be.DsaGeom, **st0.geom_kw)
+    stack = DsaDecodeStack(g, st0.B, full, max_ctx=int(g.max_pages_per_seq * g.page_tokens))
+    for L, st in zip(stack.layers, states):          # every layer: its own cache contents, the SAME page table
+        L.latent_pool.copy_(dev(st.latent_pool)); L.latent_scale.copy_(dev(st.latent_scale))
+        L.index_pool.copy_(dev(st.index_pool)); L.index_scale.copy_(dev(st.index_scale))
+        L.upload_block_table(st0.block_table)
+    outs = []
+    for i, st in enumerate(states):
+        outs.append(stack.step_layer(i, dev(st.new_latent), dev(st.new_key) if full[i] else None,
+                                     dev(st.index_q) if full[i] else None, dev(st.index_w) if full[i] else None,
+                                     dev(st.q), dev(st0.row_pos), dev(st0.seq_len)).clone())
+    be.device_sync()
+    for L in stack.layers:
+        L.check_status()
+    want0 = st0.oracle_step()
+    rows, n_sel = want0["rows"], want0["n_sel"]
+    np.testing.assert_array_equal(stack.layers[0].n_sel.cpu().numpy(), n_sel)
+    for i, st in enumerate(states):
+        lp, ls = st.latent_pool.copy(), st.latent_scale.copy()
+        ip, isc = st.index_pool.copy(), st.index_scale.copy()
+        assert orc.kv_append_paged(st0.og, st.new_latent, st.new_key, None, st0.row_pos, st0.block_table, lp, ls, ip, isc) == 0
+        _, want, _, _ = orc.mla_attend_paged(st0.og, st.q, lp, ls, st0.block_table, rows, n_sel, want_f32=True)
+        ok, worst, rms = attend_close_ref(outs[i].cpu().view(torch.int16).numpy().view(np.uint16), want)
+        assert ok and rms <= 1e-2, (i, worst, rms)

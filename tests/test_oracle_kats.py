@@ -293,3 +293,76 @@ def test_mla_batched_rows_equal_single_rows():
     for i in range(2):
         np.testing.assert_array_equal(both_a[i], orc.mla_absorb_fp8(qs[i], packed, scale, h, qh, nope, vh, kvl, block)[0])
         np.testing.assert_array_equal(both_v[i], orc.mla_value_fp8(cs[i], packed, scale, h, nope, vh, kvl, block)[0])
+
+
+# --- indexer front end: fp8 GEMV, layernorm, interleaved RoPE ------------------------------------------
+def test_gemv_fp8_literal_kat():
+    """crates/artifact/src/quant/fp8.rs:275-284: 2x2 codes [[1,2],[-1,0]], per-element scales."""
+    y = orc.gemv_fp8(np.array([3.0, 5.0], np.float32), np.array([0x38, 0x40, 0xB8, 0x00], np.uint8),
+                     np.array([10.0, 100.0, 1000.0, 1.0], np.float32), 2, 2, 1)
+    assert y[0].tolist() == [1030.0, -3000.0]
+
+
+@pytest.mark.parametrize("seed,o_dim,i_dim,block", [(0x6E37, 130, 256, 128), (0x6E38, 64, 96, 32), (0x6E39, 7, 37, 4)])
+def test_gemv_fp8_matches_an_independent_fold(seed, o_dim, i_dim, block):
+    """Draw order weights, scales, x (crates/engine/tests/common/reference.rs:234-247); the ragged
+    o_dim = 130 at block 128 is the shape that makes o_dim / block wrong there."""
+    r = orc.Lcg(seed)
+    packed = orc.f32_to_e4m3(r.draws(o_dim * i_dim))
+    sc_rows, sc_cols = -(-o_dim // block), -(-i_dim // block)
+    scale = (np.abs(r.draws(sc_rows * sc_cols) * np.float32(0.1)) + np.float32(0.01)).astype(np.float32)
+    x = r.draws(i_dim)
+    w = (orc.e4m3_table()[packed.reshape(o_dim, i_dim)] *
+         scale.reshape(sc_rows, sc_cols)[(np.arange(o_dim) // block)[:, None], (np.arange(i_dim) // block)[None, :]]).astype(np.float32)
+    want = np.zeros(o_dim, np.float32)
+    for i in range(i_dim):
+        want = (want + (w[:, i] * x[i]).astype(np.float32)).astype(np.float32)
+    got = orc.gemv_fp8(x, packed, scale, o_dim, i_dim, block)[0]
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+    two = orc.gemv_fp8(np.concatenate([x, x[::-1]]), packed, scale, o_dim, i_dim, block, nrow=2)
+    np.testing.assert_array_equal(two[0], got)
+
+
+def test_layernorm_centres_scales_and_biases():
+    """crates/engine/tests/indexer_kernel.rs:53-111: n 1024, Lcg(0x1AE6), x + 1.5, w + 1, b * 0.25, eps 1e-6."""
+    n = 1024
+    r = orc.Lcg(0x1AE6)
+    x = (r.draws(n) + np.float32(1.5)).astype(np.float32)
+    w = (r.draws(n) + np.float32(1.0)).astype(np.float32)
+    b = (r.draws(n) * np.float32(0.25)).astype(np.float32)
+
+    def host(centre, bias):
+        mean = np.float32(x.astype(np.float64).sum() / n)
+        var = np.float32((x.astype(np.float64) ** 2).sum() / n) - mean * mean
+        inv = np.float32(1.0) / np.sqrt(np.float32(var + np.float32(1e-6)))
+        m = mean if centre else np.float32(0)
+        return ((x - m) * inv * w + (b if bias else 0)).astype(np.float32)
+
+    want = host(True, True)
+    rel = lambda a, c: float(np.abs(a - c).max() / np.abs(c).max())
+    assert rel(host(False, True), want) > 1e-2 and rel(host(True, False), want) > 1e-2     # the fixture can see both defects
+    assert rel(orc.layernorm(x, w, b, 1e-6), want) <= 1e-6
+
+
+def test_rope_interleave_is_a_permutation_at_position_zero():
+    """crates/engine/tests/kernel_vector.rs:280-319: count 5, stride 24, seg 16, theta 1e4, Lcg(0x2909)."""
+    count, stride, seg, theta = 5, 24, 16, 10000.0
+    half = seg // 2
+    base = orc.Lcg(0x2909).draws(count * stride)
+
+    def host(pos):
+        v = base.copy()
+        for s in range(count):
+            row = base[s * stride: s * stride + seg]
+            for j in range(half):
+                a, b = row[2 * j], row[2 * j + 1]
+                ang = pos * theta ** (-2.0 * j / seg)
+                cs, sn = np.float32(np.cos(ang)), np.float32(np.sin(ang))
+                v[s * stride + j] = a * cs - b * sn
+                v[s * stride + half + j] = b * cs + a * sn
+        return v
+
+    np.testing.assert_array_equal(orc.rope_interleave(base, count, stride, seg, 0, theta).view(np.uint32), host(0).view(np.uint32))
+    got, want = orc.rope_interleave(base, count, stride, seg, 137, theta), host(137)
+    assert float(np.abs(got - want).max() / np.abs(want).max()) <= 1e-6
+    np.testing.assert_array_equal(got.reshape(count, stride)[:, seg:], base.reshape(count, stride)[:, seg:])   # stride > seg untouched
