@@ -292,7 +292,9 @@ int rivoli_rope_interleave(float* base, int count, int stride, int seg, int pos,
  * scales; the rotation covers [rope_off, rope_off + rope_seg) of every index_dim-wide vector. The outputs
  * are the rows rivoli_kv_append_paged / rivoli_index_select_paged take. scratch =
  * rivoli_index_frontend_scratch_bytes() (split-K partial sums; the split is fixed by the geometry and
- * summed in order, so results are reproducible). */
+ * summed in order, so results are reproducible). The GEMMs run on the tensor cores (tcgen05 kind::f16, weights
+ * as bf16(code * scale)) for 128-blocks, contraction lengths multiple of 128 and output counts multiple of 128
+ * (or of 16 up to 128); on CUDA cores otherwise or when force_simt != 0. */
 typedef struct IndexFrontGeom {
     int32_t hidden, q_lora, index_heads, index_dim, rope_off, rope_seg, block;
     float eps;       /* LayerNorm epsilon (the reference: 1e-6, crates/engine/src/indexer.rs:12) */
@@ -303,7 +305,9 @@ int rivoli_index_frontend_bf16(const IndexFrontGeom* g, const uint16_t* x, const
                                int B, const unsigned char* wk, const float* wk_scale, const float* knorm_w,
                                const float* knorm_b, const unsigned char* wq_b, const float* wq_b_scale,
                                const unsigned char* wproj, const float* wproj_scale, uint16_t* index_key,
-                               uint16_t* index_q, float* index_w, void* scratch, void* stream);
+                               uint16_t* index_q, float* index_w, void* scratch, int force_simt, void* stream);
+/* Synchronises `stream`; 1008 if a bounded wait of the tensor-core front end gave up since the last call. */
+int rivoli_index_frontend_status(void* stream);
 
 /* Diagnostic, not on any product path (bench.py --profile gather): average milliseconds of a
  * launch in which each of n_ctas CTAs copies n_tiles tiles of 128 latent rows (576 bytes each,

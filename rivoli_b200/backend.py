@@ -387,11 +387,16 @@ def index_frontend_scratch_bytes(g: IndexFrontGeom, B: int) -> int:
 
 
 def launch_index_frontend_bf16(g: IndexFrontGeom, x, q_resid, pos, B: int, wk, wk_scale, knorm_w, knorm_b, wq_b, wq_b_scale,
-                               wproj, wproj_scale, index_key, index_q, index_w, scratch, stream=None) -> None:
+                               wproj, wproj_scale, index_key, index_q, index_w, scratch, force_simt: bool = False,
+                               stream=None) -> None:
     ensure_status(lib().rivoli_index_frontend_bf16(
         C.byref(g), _ptr(x), _ptr(q_resid), _ptr(pos), C.c_int(B), _ptr(wk), _ptr(wk_scale), _ptr(knorm_w), _ptr(knorm_b),
         _ptr(wq_b), _ptr(wq_b_scale), _ptr(wproj), _ptr(wproj_scale), _ptr(index_key), _ptr(index_q), _ptr(index_w),
-        _ptr(scratch), _stream(stream)), "index_frontend_bf16")
+        _ptr(scratch), C.c_int(int(force_simt)), _stream(stream)), "index_frontend_bf16")
+
+
+def index_frontend_status(stream=None) -> None:
+    ensure_status(lib().rivoli_index_frontend_status(_stream(stream)), "index_frontend(status)")
 
 
 def probe_gather(method: int, depth: int, n_ctas: int, n_tiles: int, pool, n_pool_rows: int, scales, rows,

@@ -15,6 +15,7 @@
 //       rivoli_index_select_paged take.
 #include "codec.cuh"
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
@@ -84,7 +85,7 @@ struct FrontJob {            // Y[b][o] (+)= sum over a K range of X[b][i] * W[o
     const uint16_t* x; int K;                         // activations bf16 [B][K]
     const uint8_t* w; const float* scale; int N;      // weights e4m3 [N][K], block scales
     float* partial;                                   // f32 [k_splits][B][N]
-    int n_tiles, k_splits, cta0;                      // tiles of 64 outputs, splits of the contraction, first CTA
+    int n_tiles, k_splits, cta0, tile_n;              // output tiles of tile_n columns, splits of the contraction, first CTA
 };
 struct FrontArgs { FrontJob job[3]; int B, block, n_cta; };
 
@@ -103,7 +104,7 @@ front_gemm_simt_kernel(FrontArgs A) {
     const int tile = local % J.n_tiles, split = local / J.n_tiles;
     const int kper = ((J.K + J.k_splits - 1) / J.k_splits + FT_KC - 1) / FT_KC * FT_KC;
     const int k0 = split * kper, k1 = min(J.K, k0 + kper);
-    const int o = tile * FT_N + (threadIdx.x & 63), bq = threadIdx.x >> 6;
+    const int o = tile * FT_N + (threadIdx.x & 63), bq = threadIdx.x >> 6;   // this kernel always plans tile_n == FT_N
     const int bsh = if_shift(A.block), sc_cols = (J.K + A.block - 1) / A.block;
     // sequences bq, bq + 4, ... ; at most 32 accumulators per thread per pass
     for (int b0 = 0; b0 < A.B; b0 += 128) {
@@ -138,6 +139,135 @@ front_gemm_simt_kernel(FrontArgs A) {
                 if (b < A.B) J.partial[((size_t)split * A.B + b) * J.N + o] = acc[r];
             }
     }
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// The same split-K GEMM on the tensor cores (tcgen05 kind::f16). CTA = (job, output tile, K split);
+// M = 128 sequences, N = the tile (128, or the whole of a narrower matrix), K fed in chunks of 64
+// through two shared-memory stages: activations arrive by cp.async (K-major, 128-byte swizzle), weights
+// are converted on the way in to bf16(code * block scale) (one rounding, 2^-9 relative; a 64-wide chunk of
+// a 128-aligned tile lies inside ONE scale block). The accumulator leaves as the f32 split partial.
+// ---------------------------------------------------------------------------------------------
+constexpr int FM_THREADS = 256, FM_WARPS = 8, FM_STAGE = 32768;   // stage = A 16 KiB | B up to 16 KiB
+
+__device__ __forceinline__ uint64_t fm_desc(uint32_t saddr) {     // K-major, 128-byte swizzle, 8-row groups 1024 B apart
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void fm_mma(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ int g_front_err;
+
+__global__ void __launch_bounds__(FM_THREADS)
+front_gemm_mma_kernel(FrontArgs A) {
+    extern __shared__ __align__(1024) uint8_t fm_smem[];
+    __shared__ uint64_t bar[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int jid = 0;
+    while (jid < 2 && (int)blockIdx.x >= A.job[jid + 1].cta0) ++jid;
+    const FrontJob& J = A.job[jid];
+    const int local = blockIdx.x - J.cta0;
+    const int tile = local % J.n_tiles, split = local / J.n_tiles;
+    const int TN = J.tile_n;
+    const int kper = ((J.K + J.k_splits - 1) / J.k_splits + 127) / 128 * 128;
+    const int k0 = split * kper, k1 = min(J.K, k0 + kper);
+    const int nch = k1 > k0 ? (k1 - k0) / 64 : 0;
+    const int sc_cols = J.K / 128;
+    const float* srow = J.scale + (size_t)((tile * TN) >> 7) * sc_cols;
+    if (tid == 0) { tc::mbar_init(&bar[0], 1); tc::mbar_init(&bar[1], 1); tc::mbar_init_fence(); abort_word = 0; }
+    if (warp == 0) tc::tmem_alloc<128>(&tmem_slot);
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    // instruction descriptor: bf16 x bf16 -> f32, both K-major, M = 128, N = TN
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
+    const int erow = (warp & 3) * 32 + lane, chalf = warp >> 2;
+    bool ok = true;
+    int done[2] = {0, 0};                                   // commits issued per stage so far
+    for (int b0 = 0; b0 < A.B && ok; b0 += 128) {
+        for (int c = 0; c < nch && ok; ++c) {
+            const int st = c & 1, kc = k0 + c * 64;
+            uint8_t* sA = fm_smem + st * FM_STAGE;
+            uint8_t* sB = sA + 16384;
+            if (done[st] > 0) ok = tc::mbar_wait(&bar[st], (done[st] - 1) & 1, abort_flag, 81 + st);   // the stage's last readers are done
+            if (!ok) break;
+            // activations: 128 sequences x 64 values; warp = row, lanes 0-7 = the row's eight 16-byte chunks (4 rows per pass)
+            for (int r0 = warp * 4; r0 < 128; r0 += FM_WARPS * 4) {
+                const int row = r0 + (lane >> 3), j = lane & 7;
+                uint8_t* dst = sA + tc::sw128_chunk(row, j);
+                if (b0 + row < A.B) tc::cp_async16(tc::smem_u32(dst), J.x + (size_t)(b0 + row) * J.K + kc + j * 8);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+            tc::cp_async_commit();
+            // weights: TN rows x 64 codes -> bf16(code * scale); lanes 0-7 = the row's eight pieces of 8 codes
+            const float sc = srow[kc >> 7];
+            for (int r0 = warp * 4; r0 < TN; r0 += FM_WARPS * 4) {
+                const int row = r0 + (lane >> 3), j = lane & 7;
+                const uint2 cw = *reinterpret_cast<const uint2*>(J.w + (size_t)(tile * TN + row) * J.K + kc + j * 8);
+                uint32_t o[4];
+                const uint32_t w2[2] = {cw.x, cw.y};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = rv_e4m3x2_to_f32x2((uint16_t)(w2[i >> 1] >> (16 * (i & 1))));
+                    o[i] = (uint32_t)rv_f32_to_bf16(f.x * sc) | ((uint32_t)rv_f32_to_bf16(f.y * sc) << 16);
+                }
+                *reinterpret_cast<uint4*>(sB + tc::sw128_chunk(row, j)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            tc::cp_async_wait<0>();
+            tc::fence_proxy_async();
+            __syncthreads();
+            if (tid == 0) {
+                tc::tc_fence_after();
+                const uint32_t a0 = tc::smem_u32(sA), b0a = tc::smem_u32(sB);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) fm_mma(tmem, fm_desc(a0 + k * 32), fm_desc(b0a + k * 32), idesc, (c | k) ? 1u : 0u);
+                tc::mma_commit(&bar[st]);
+            }
+            ++done[st];
+        }
+        // all MMAs of this batch tile: wait for the last commit of each stage
+        for (int st = 0; st < 2 && ok; ++st)
+            if (done[st] > 0) ok = tc::mbar_wait(&bar[st], (done[st] - 1) & 1, abort_flag, 83 + st);
+        tc::tc_fence_after();
+        if (ok && nch > 0) {
+            const int ncol_chunks = TN / 32;                 // 32-column chunks; warps 0-3 take the even ones, 4-7 the odd
+            for (int c = chalf; c < ncol_chunks; c += 2) {
+                uint32_t r[32];
+                tc::tmem_ld32(tmem + lane_base + c * 32, r);
+                tc::tmem_ld_wait();
+                if (b0 + erow < A.B) {
+                    float4* dst = reinterpret_cast<float4*>(J.partial + ((size_t)split * A.B + b0 + erow) * J.N + tile * TN + c * 32);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        dst[e] = make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]), __uint_as_float(r[4 * e + 2]),
+                                             __uint_as_float(r[4 * e + 3]));
+                }
+            }
+        } else if (ok) {                                     // an empty K range (more splits than 128-blocks): zeros
+            for (int e = tid; e < 128 * TN; e += FM_THREADS) {
+                const int row = e / TN, col = e - row * TN;
+                if (b0 + row < A.B) J.partial[((size_t)split * A.B + b0 + row) * J.N + tile * TN + col] = 0.0f;
+            }
+        }
+        tc::tc_fence_before();
+        __syncthreads();
+    }
+    if (warp == 0) tc::tmem_dealloc<128>(tmem);
+    if (tid == 0 && abort_word) atomicCAS(&g_front_err, 0, abort_word);
 }
 
 struct EpiArgs {
@@ -245,7 +375,20 @@ RIVOLI_API int rivoli_rope_interleave(float* base, int count, int stride, int se
     return rv_launch_status();
 }
 
-static void plan_jobs(const IndexFrontGeom* g, int B, FrontArgs* fa, size_t* floats) {
+// The tensor-core GEMM covers: 128-blocks, contraction lengths that are multiples of 128, output counts that
+// are multiples of 128 (tiled) or of 16 up to 128 (one tile), 16-byte aligned rows.
+static bool front_mma_ok(const IndexFrontGeom* g) {
+    const int N[3] = {g->index_dim, g->index_heads * g->index_dim, g->index_heads};
+    const int K[3] = {g->hidden, g->q_lora, g->hidden};
+    if (g->block != 128) return false;
+    for (int j = 0; j < 3; ++j) {
+        if (K[j] % 128) return false;
+        if (N[j] % 16 || (N[j] > 128 && N[j] % 128)) return false;
+    }
+    return true;
+}
+
+static void plan_jobs(const IndexFrontGeom* g, int B, bool mma, FrontArgs* fa, size_t* floats) {
     const int N[3] = {g->index_dim, g->index_heads * g->index_dim, g->index_heads};
     const int K[3] = {g->hidden, g->q_lora, g->hidden};
     int cta = 0;
@@ -253,7 +396,8 @@ static void plan_jobs(const IndexFrontGeom* g, int B, FrontArgs* fa, size_t* flo
     for (int j = 0; j < 3; ++j) {
         FrontJob& J = fa->job[j];
         J.N = N[j]; J.K = K[j];
-        J.n_tiles = ceil_div(N[j], FT_N);
+        J.tile_n = mma ? (N[j] < 128 ? N[j] : 128) : FT_N;
+        J.n_tiles = ceil_div(N[j], J.tile_n);
         // enough CTAs to fill the machine, at least 256 contraction values per split, at most 32 splits
         int splits = ceil_div(296, J.n_tiles * 3);
         if (splits > K[j] / 256) splits = K[j] / 256;
@@ -273,7 +417,7 @@ RIVOLI_API size_t rivoli_index_frontend_scratch_bytes(const IndexFrontGeom* g, i
     if (!g || B <= 0) return 0;
     FrontArgs fa;
     size_t floats = 0;
-    plan_jobs(g, B, &fa, &floats);
+    plan_jobs(g, B, front_mma_ok(g), &fa, &floats);   // the split count does not depend on the path
     return floats * sizeof(float);
 }
 
@@ -282,7 +426,7 @@ RIVOLI_API int rivoli_index_frontend_bf16(const IndexFrontGeom* g, const uint16_
                                           const float* knorm_w, const float* knorm_b, const unsigned char* wq_b,
                                           const float* wq_b_scale, const unsigned char* wproj,
                                           const float* wproj_scale, uint16_t* index_key, uint16_t* index_q,
-                                          float* index_w, void* scratch, void* stream) {
+                                          float* index_w, void* scratch, int force_simt, void* stream) {
     if (!g || B <= 0 || !x || !q_resid || !pos || !wk || !wk_scale || !knorm_w || !knorm_b || !wq_b || !wq_b_scale ||
         !wproj || !wproj_scale || !index_key || !index_q || !index_w || !scratch)
         return 1001;
@@ -292,9 +436,11 @@ RIVOLI_API int rivoli_index_frontend_bf16(const IndexFrontGeom* g, const uint16_
     if (g->index_heads > 256 || (size_t)(g->index_heads + 1) * g->index_dim * 4 > 200 * 1024) return 1002;
     if ((g->index_heads + 1) * (g->rope_seg / 2) > 8 * 256) return 1002;
     cudaStream_t st = (cudaStream_t)stream;
+    const bool mma = !force_simt && front_mma_ok(g) && (((uintptr_t)x | (uintptr_t)q_resid | (uintptr_t)wk | (uintptr_t)wq_b |
+                                                         (uintptr_t)wproj | (uintptr_t)scratch) & 15) == 0;
     FrontArgs fa;
     size_t floats = 0;
-    plan_jobs(g, B, &fa, &floats);
+    plan_jobs(g, B, mma, &fa, &floats);
     float* base = static_cast<float*>(scratch);
     const uint16_t* xs[3] = {x, q_resid, x};
     const unsigned char* ws[3] = {wk, wq_b, wproj};
@@ -304,7 +450,12 @@ RIVOLI_API int rivoli_index_frontend_bf16(const IndexFrontGeom* g, const uint16_
         fa.job[j].partial = base + reinterpret_cast<size_t>(fa.job[j].partial);
     }
     rv_drain_error();
-    front_gemm_simt_kernel<<<fa.n_cta, 256, 0, st>>>(fa);
+    if (mma) {
+        cudaFuncSetAttribute(front_gemm_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * FM_STAGE);
+        front_gemm_mma_kernel<<<fa.n_cta, FM_THREADS, 2 * FM_STAGE, st>>>(fa);
+    } else {
+        front_gemm_simt_kernel<<<fa.n_cta, 256, 0, st>>>(fa);
+    }
     if (int e = rv_launch_status()) return e;
     EpiArgs ea{fa.job[0].partial, fa.job[1].partial, fa.job[2].partial, fa.job[0].k_splits, fa.job[1].k_splits,
                fa.job[2].k_splits, knorm_w, knorm_b, pos, B, g->index_heads, g->index_dim, g->rope_off, g->rope_seg,
@@ -313,4 +464,15 @@ RIVOLI_API int rivoli_index_frontend_bf16(const IndexFrontGeom* g, const uint16_
     cudaFuncSetAttribute(front_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     front_epilogue_kernel<<<B, 256, smem, st>>>(ea);
     return rv_launch_status();
+}
+
+// Synchronises the stream; 1008 if a bounded wait of the tensor-core front end gave up since the last call.
+RIVOLI_API int rivoli_index_frontend_status(void* stream) {
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return -(int)e;
+    int h = 0;
+    e = cudaMemcpyFromSymbol(&h, g_front_err, sizeof(int));
+    if (e != cudaSuccess) return -(int)e;
+    if (h) { const int z = 0; cudaMemcpyToSymbol(g_front_err, &z, sizeof(int)); }
+    return h ? 1008 : 0;
 }

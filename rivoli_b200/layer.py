@@ -187,11 +187,11 @@ class IndexerFrontEnd:
         self.index_w = torch.zeros((n_seqs, fg.index_heads), dtype=torch.float32, device=d)
         self.scratch = torch.zeros(max(be.index_frontend_scratch_bytes(fg, n_seqs), 16), dtype=torch.uint8, device=d)
 
-    def run(self, x: torch.Tensor, q_resid: torch.Tensor, positions: torch.Tensor, stream=None):
+    def run(self, x: torch.Tensor, q_resid: torch.Tensor, positions: torch.Tensor, stream=None, force_simt: bool = False):
         w = self.w
         be.launch_index_frontend_bf16(self.fg, x, q_resid, positions, self.B, w["wk"], w["wk_scale"], w["knorm_w"],
                                       w["knorm_b"], w["wq_b"], w["wq_b_scale"], w["wproj"], w["wproj_scale"],
-                                      self.index_key, self.index_q, self.index_w, self.scratch, stream)
+                                      self.index_key, self.index_q, self.index_w, self.scratch, force_simt, stream)
         return self.index_key, self.index_q, self.index_w
 
 

@@ -98,14 +98,19 @@ def test_batched_front_end_matches_oracle(be, B, hidden, q_lora, nh, hd):
                                                   W["knorm_w"], W["knorm_b"], W["wq_b"], W["wq_b_scale"], W["wproj"], W["wproj_scale"])
     fg = be.IndexFrontGeom(hidden, q_lora, nh, hd, rope_off, rope_seg, block, eps, theta)
     fe = IndexerFrontEnd(fg, B, {k: dev(v) for k, v in W.items()})
-    gk, gq, gw = fe.run(dev(x), dev(qr), dev(pos))
-    be.device_sync()
-    # split-K sums differ from the oracle's single fold in the last bits; one bf16 rounding on top
+    for simt in (False, True):
+        gk, gq, gw = fe.run(dev(x), dev(qr), dev(pos), force_simt=simt)
+        be.index_frontend_status()
+        _check_front(gk, gq, gw, k32, q32, w)
+    assert gk.shape == (B, hd) and gq.shape == (B, nh, hd) and gw.shape == (B, nh)
+
+
+def _check_front(gk, gq, gw, k32, q32, w):
+    # split-K sums (and, on the tensor cores, weights rounded to bf16 after scaling) differ from the oracle's
+    # single f32 fold in the low bits; one bf16 rounding on top
     for got, want in ((orc.bf16_to_f32(gk.cpu().view(torch.int16).numpy().view(np.uint16)), k32),
                       (orc.bf16_to_f32(gq.cpu().view(torch.int16).numpy().view(np.uint16)), q32),
                       (gw.cpu().numpy(), w)):
         err = np.abs(got.astype(np.float64) - want)
         tol = 2.0 ** -7 * np.abs(want) + 2e-3 * np.abs(want).max()
         assert (err <= tol).all(), float((err / tol).max())
-    # and the result feeds the cache path: right shapes and dtypes for append / select
-    assert gk.shape == (B, hd) and gq.shape == (B, nh, hd) and gw.shape == (B, nh)
