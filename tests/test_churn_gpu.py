@@ -101,9 +101,15 @@ def test_shared_layers_attend_over_the_full_layers_selection():
     st0 = states[0]
     g = make_geom(be.DsaGeom, **st0.geom_kw)
     stack = DsaDecodeStack(g, st0.B, full, max_ctx=int(g.max_pages_per_seq * g.page_tokens))
-    for L, st in zip(stack.layers, states):          # every layer: its own cache contents, the SAME page table
-        L.latent_pool.copy_(dev(st.latent_pool)); L.latent_scale.copy_(dev(st.latent_scale))
-        L.index_pool.copy_(dev(st.index_pool)); L.index_scale.copy_(dev(st.index_scale))
+    caches = []
+    for L, st in zip(stack.layers, states):          # every layer: its own cache contents, ONE page table (layer 0's)
+        lp, ls = np.zeros_like(st0.latent_pool), np.zeros_like(st0.latent_scale)
+        ip, isc = np.zeros_like(st0.index_pool), np.zeros_like(st0.index_scale)
+        assert orc.kv_append_paged(st0.og, st.hist_latent, st.hist_key, st.hist_seq, st.hist_pos, st0.block_table,
+                                   lp, ls, ip, isc) == 0
+        caches.append((lp, ls, ip, isc))
+        L.latent_pool.copy_(dev(lp)); L.latent_scale.copy_(dev(ls))
+        L.index_pool.copy_(dev(ip)); L.index_scale.copy_(dev(isc))
         L.upload_block_table(st0.block_table)
     outs = []
     for i, st in enumerate(states):
@@ -117,8 +123,7 @@ def test_shared_layers_attend_over_the_full_layers_selection():
     rows, n_sel = want0["rows"], want0["n_sel"]
     np.testing.assert_array_equal(stack.layers[0].n_sel.cpu().numpy(), n_sel)
     for i, st in enumerate(states):
-        lp, ls = st.latent_pool.copy(), st.latent_scale.copy()
-        ip, isc = st.index_pool.copy(), st.index_scale.copy()
+        lp, ls, ip, isc = (a.copy() for a in caches[i])
         assert orc.kv_append_paged(st0.og, st.new_latent, st.new_key, None, st0.row_pos, st0.block_table, lp, ls, ip, isc) == 0
         _, want, _, _ = orc.mla_attend_paged(st0.og, st.q, lp, ls, st0.block_table, rows, n_sel, want_f32=True)
         ok, worst, rms = attend_close_ref(outs[i].cpu().view(torch.int16).numpy().view(np.uint16), want)
