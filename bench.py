@@ -364,7 +364,7 @@ def run_ours(args):
         }
         proj = time_projections(w, device)
         if proj:
-            line["next_rows"] = {"what": "q absorption and value up-projection through kv_b (tcgen05 kind::f16), per launch "
+            line["next_rows"] = {"what": "q absorption, value up-projection (kv_b) and the indexer front end (two launches), tcgen05 kind::f16, per call "
                                          "at this batch, L2 flushed between launches; not part of the layer-step metric",
                                  **proj}
         if not args.no_cpu_baseline and world == 1:
@@ -410,6 +410,34 @@ def time_projections(w, device, steps=50):
         ms = float(np.median(ts))
         out[name] = {"us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9, "tflops": flops / (ms * 1e-3) / 1e12}
     be.kvb_proj_status()
+    # indexer front end at the model geometry (hidden 6144, q_lora 2048, 32 x 128 index heads)
+    from rivoli_b200.layer import IndexerFrontEnd
+    hidden, q_lora, nh, hd = 6144, 2048, w["index_heads"], w["index_dim"]
+    fg = be.IndexFrontGeom(hidden, q_lora, nh, hd, 0, 64, block, 1e-6, 10000.0)
+
+    def fp8w(n, k):
+        return (torch.randint(0, 0x7E, (n * k,), generator=gen, device=device, dtype=torch.int32).to(torch.uint8),
+                torch.rand((((n + block - 1) // block) * (k // block),), generator=gen, device=device) * 0.01 + 0.002)
+    wk, wk_s = fp8w(hd, hidden); wq, wq_s = fp8w(nh * hd, q_lora); wp, wp_s = fp8w(nh, hidden)
+    fe = IndexerFrontEnd(fg, B, dict(wk=wk, wk_scale=wk_s, knorm_w=torch.ones(hd, device=device), knorm_b=torch.zeros(hd, device=device),
+                                     wq_b=wq, wq_b_scale=wq_s, wproj=wp, wproj_scale=wp_s), device=device)
+    xh = torch.randn((B, hidden), generator=gen, device=device).to(torch.bfloat16)
+    qr = torch.randn((B, q_lora), generator=gen, device=device).to(torch.bfloat16)
+    pos = torch.full((B,), w["ctx"] - 1, dtype=torch.int32, device=device)
+    nbytes = hd * hidden + nh * hd * q_lora + nh * hidden + B * (hidden + q_lora) * 2 + B * (hd + nh * hd) * 2 + B * nh * 4
+    for _ in range(3):
+        fe.run(xh, qr, pos)
+    ts = []
+    for _ in range(steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fe.run(xh, qr, pos); e1.record()
+        torch.cuda.synchronize(device)
+        ts.append(e0.elapsed_time(e1))
+    ms = float(np.median(ts))
+    be.index_frontend_status()
+    out["index_front_end"] = {"us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                              "tflops": 2 * B * (hd * hidden + nh * hd * q_lora + nh * hidden) / (ms * 1e-3) / 1e12}
     return out
 
 

@@ -145,11 +145,15 @@ front_gemm_simt_kernel(FrontArgs A) {
 // ---------------------------------------------------------------------------------------------
 // The same split-K GEMM on the tensor cores (tcgen05 kind::f16). CTA = (job, output tile, K split);
 // M = 128 sequences, N = the tile (128, or the whole of a narrower matrix), K fed in chunks of 64
-// through two shared-memory stages: activations arrive by cp.async (K-major, 128-byte swizzle), weights
-// are converted on the way in to bf16(code * block scale) (one rounding, 2^-9 relative; a 64-wide chunk of
+// through three shared-memory stages: activations and raw weight codes arrive by cp.async (two chunks requested
+// ahead), the codes of the current chunk are converted to bf16(code * block scale) (one rounding, 2^-9 relative; a 64-wide chunk of
 // a 128-aligned tile lies inside ONE scale block). The accumulator leaves as the f32 split partial.
 // ---------------------------------------------------------------------------------------------
-constexpr int FM_THREADS = 256, FM_WARPS = 8, FM_STAGE = 32768;   // stage = A 16 KiB | B up to 16 KiB
+constexpr int FM_THREADS = 256, FM_WARPS = 8;
+constexpr int FM_NST = 3;                      // stages of (activations 16 KiB | raw weight codes 8 KiB) in flight
+constexpr int FM_STAGE = 16384 + 8192;
+constexpr int FM_BOFF = FM_NST * FM_STAGE;     // two converted weight tiles (bf16, 16 KiB each) follow the stages
+constexpr int FM_SMEM = FM_BOFF + 2 * 16384;   // 104 KiB: two CTAs per SM
 
 __device__ __forceinline__ uint64_t fm_desc(uint32_t saddr) {     // K-major, 128-byte swizzle, 8-row groups 1024 B apart
     uint64_t d = 0;
@@ -166,6 +170,13 @@ __device__ __forceinline__ void fm_mma(uint32_t d_tmem, uint64_t da, uint64_t db
                  ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ int g_front_err;
+#ifdef RIVOLI_DEBUG_TIMES
+__device__ long long g_fm_times[64];
+#define FM_STAMP(slot) do { if (blockIdx.x == FM_DBG_CTA && threadIdx.x == 0 && (slot) < 64) g_fm_times[slot] = clock64(); } while (0)
+constexpr int FM_DBG_CTA = 40;    // a CTA of the widest job
+#else
+#define FM_STAMP(slot) do { } while (0)
+#endif
 
 __global__ void __launch_bounds__(FM_THREADS)
 front_gemm_mma_kernel(FrontArgs A) {
@@ -186,63 +197,104 @@ front_gemm_mma_kernel(FrontArgs A) {
     const int nch = k1 > k0 ? (k1 - k0) / 64 : 0;
     const int sc_cols = J.K / 128;
     const float* srow = J.scale + (size_t)((tile * TN) >> 7) * sc_cols;
+    FM_STAMP(0);
     if (tid == 0) { tc::mbar_init(&bar[0], 1); tc::mbar_init(&bar[1], 1); tc::mbar_init_fence(); abort_word = 0; }
     if (warp == 0) tc::tmem_alloc<128>(&tmem_slot);
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = tmem_slot;
+    FM_STAMP(1);
     // instruction descriptor: bf16 x bf16 -> f32, both K-major, M = 128, N = TN
     const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
     const int erow = (warp & 3) * 32 + lane, chalf = warp >> 2;
     bool ok = true;
-    int done[2] = {0, 0};                                   // commits issued per stage so far
+    int done[2] = {0, 0};                                   // commits issued per weight buffer so far
     for (int b0 = 0; b0 < A.B && ok; b0 += 128) {
-        for (int c = 0; c < nch && ok; ++c) {
-            const int st = c & 1, kc = k0 + c * 64;
-            uint8_t* sA = fm_smem + st * FM_STAGE;
-            uint8_t* sB = sA + 16384;
-            if (done[st] > 0) ok = tc::mbar_wait(&bar[st], (done[st] - 1) & 1, abort_flag, 81 + st);   // the stage's last readers are done
-            if (!ok) break;
-            // activations: 128 sequences x 64 values; warp = row, lanes 0-7 = the row's eight 16-byte chunks (4 rows per pass)
-            for (int r0 = warp * 4; r0 < 128; r0 += FM_WARPS * 4) {
-                const int row = r0 + (lane >> 3), j = lane & 7;
-                uint8_t* dst = sA + tc::sw128_chunk(row, j);
-                if (b0 + row < A.B) tc::cp_async16(tc::smem_u32(dst), J.x + (size_t)(b0 + row) * J.K + kc + j * 8);
-                else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        // request chunk c: activations (128 sequences x 64 bf16, swizzled K-major; rows past B are zeros) and
+        // the raw codes of TN weight rows x 64; one cp.async group per chunk, requested chunks or not
+        // per-thread copy plan, fixed for the batch tile: 4 activation rows and up to 2 weight rows per thread
+        const uint16_t* pa[4]; uint32_t da[4]; bool la[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = warp * 4 + i * FM_WARPS * 4 + (lane >> 3), j = lane & 7;
+            la[i] = b0 + row < A.B;
+            pa[i] = J.x + (size_t)(la[i] ? b0 + row : 0) * J.K + k0 + j * 8;
+            da[i] = tc::sw128_chunk(row, j);
+        }
+        const uint8_t* pw[2]; uint32_t dw[2]; bool lw[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int row = warp * 8 + i * FM_WARPS * 8 + (lane >> 2), j = lane & 3;
+            lw[i] = row < TN;
+            pw[i] = J.w + (size_t)(tile * TN + (lw[i] ? row : 0)) * J.K + k0 + j * 16;
+            dw[i] = 16384 + row * 64 + j * 16;
+        }
+        const uint32_t smem0 = tc::smem_u32(fm_smem);
+        auto request = [&](int c) {
+            if (c < nch) {
+                const uint32_t st = smem0 + (c % FM_NST) * FM_STAGE;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (la[i]) tc::cp_async16(st + da[i], pa[i] + c * 64);
+                    else *reinterpret_cast<uint4*>(fm_smem + (c % FM_NST) * FM_STAGE + da[i]) = make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    if (lw[i]) tc::cp_async16(st + dw[i], pw[i] + c * 64);
             }
             tc::cp_async_commit();
-            // weights: TN rows x 64 codes -> bf16(code * scale); lanes 0-7 = the row's eight pieces of 8 codes
-            const float sc = srow[kc >> 7];
-            for (int r0 = warp * 4; r0 < TN; r0 += FM_WARPS * 4) {
+        };
+        request(0);
+        request(1);
+        for (int c = 0; c < nch && ok; ++c) {
+            const int wb = c & 1;
+            // stage (c + 2) % 3 was read by the MMAs of chunk c - 1, weight buffer wb by those of chunk c - 2
+            if (c >= 1) ok = tc::mbar_wait(&bar[(c - 1) & 1], (done[(c - 1) & 1] - 1) & 1, abort_flag, 81);
+            if (!ok) break;
+            FM_STAMP(4 + c * 5);
+            request(c + 2);
+            FM_STAMP(5 + c * 5);
+            tc::cp_async_wait<2>();                          // chunk c has landed (two younger groups may be pending)
+            __syncthreads();
+            FM_STAMP(6 + c * 5);
+            const uint8_t* sA = fm_smem + (c % FM_NST) * FM_STAGE;
+            const uint8_t* sW = sA + 16384;
+            uint8_t* sB = fm_smem + FM_BOFF + wb * 16384;
+            const float sc = srow[(k0 + c * 64) >> 7];
+            for (int r0 = warp * 4; r0 < TN; r0 += FM_WARPS * 4) {     // codes -> bf16(code * scale), swizzled K-major
                 const int row = r0 + (lane >> 3), j = lane & 7;
-                const uint2 cw = *reinterpret_cast<const uint2*>(J.w + (size_t)(tile * TN + row) * J.K + kc + j * 8);
+                const uint2 cw = *reinterpret_cast<const uint2*>(sW + row * 64 + j * 8);
                 uint32_t o[4];
                 const uint32_t w2[2] = {cw.x, cw.y};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float2 f = rv_e4m3x2_to_f32x2((uint16_t)(w2[i >> 1] >> (16 * (i & 1))));
-                    o[i] = (uint32_t)rv_f32_to_bf16(f.x * sc) | ((uint32_t)rv_f32_to_bf16(f.y * sc) << 16);
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(f.x * sc, f.y * sc);   // finite values: plain RNE
+                    o[i] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 *reinterpret_cast<uint4*>(sB + tc::sw128_chunk(row, j)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
-            tc::cp_async_wait<0>();
             tc::fence_proxy_async();
             __syncthreads();
+            FM_STAMP(7 + c * 5);
             if (tid == 0) {
                 tc::tc_fence_after();
-                const uint32_t a0 = tc::smem_u32(sA), b0a = tc::smem_u32(sB);
+                const uint64_t da0 = fm_desc(tc::smem_u32(sA)), db0 = fm_desc(tc::smem_u32(sB));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) fm_mma(tmem, fm_desc(a0 + k * 32), fm_desc(b0a + k * 32), idesc, (c | k) ? 1u : 0u);
-                tc::mma_commit(&bar[st]);
+                for (int k = 0; k < 4; ++k) fm_mma(tmem, da0 + 2 * k, db0 + 2 * k, idesc, (c | k) ? 1u : 0u);   // +32 bytes = +2 in the address field
+                tc::mma_commit(&bar[wb]);
             }
-            ++done[st];
+            FM_STAMP(8 + c * 5);
+            ++done[wb];
         }
-        // all MMAs of this batch tile: wait for the last commit of each stage
+        tc::cp_async_wait<0>();
+        // all MMAs of this batch tile: wait for the last commit of each weight buffer
         for (int st = 0; st < 2 && ok; ++st)
             if (done[st] > 0) ok = tc::mbar_wait(&bar[st], (done[st] - 1) & 1, abort_flag, 83 + st);
         tc::tc_fence_after();
+        FM_STAMP(2);
         if (ok && nch > 0) {
             const int ncol_chunks = TN / 32;                 // 32-column chunks; warps 0-3 take the even ones, 4-7 the odd
             for (int c = chalf; c < ncol_chunks; c += 2) {
@@ -266,6 +318,7 @@ front_gemm_mma_kernel(FrontArgs A) {
         tc::tc_fence_before();
         __syncthreads();
     }
+    FM_STAMP(3);
     if (warp == 0) tc::tmem_dealloc<128>(tmem);
     if (tid == 0 && abort_word) atomicCAS(&g_front_err, 0, abort_word);
 }
@@ -279,23 +332,62 @@ struct EpiArgs {
 };
 
 // One CTA per sequence: reduce the split partials in split order, LayerNorm the key, rotate key and
-// queries at the sequence's position, store bf16 (and the f32 head weights).
+// queries at the sequence's position, store bf16 (and the f32 head weights). The rotation angles depend
+// only on (position, pair index): rope_seg / 2 (cos, sin) pairs are computed once in f64 and shared by
+// all index_heads + 1 vectors.
 __global__ void __launch_bounds__(256)
 front_epilogue_kernel(EpiArgs A) {
     extern __shared__ float fe_smem[];          // (nh + 1) * hd values: queries then key
     __shared__ double ss[256], sq[256];
+    __shared__ float s_cs[512], s_sn[512];
     const int b = blockIdx.x, t = threadIdx.x, nh = A.nh, hd = A.hd;
     float* qv = fe_smem;
     float* kv = fe_smem + (size_t)nh * hd;
-    for (int e = t; e < nh * hd; e += 256) {
-        float a = 0.0f;
-        for (int s = 0; s < A.sq; ++s) a = __fadd_rn(a, A.pq[((size_t)s * A.B + b) * nh * hd + e]);
-        qv[e] = a;
+    const int half = A.rope_seg / 2, pos = A.pos[b];
+    for (int j = t; j < half; j += 256) {
+        const double ang = (double)pos * pow(A.theta, -2.0 * (double)j / (double)A.rope_seg);
+        s_cs[j] = (float)cos(ang); s_sn[j] = (float)sin(ang);
+    }
+    const int nq4 = nh * hd / 4;                 // index_dim is a multiple of 4 (checked by the launcher)
+    for (int e0 = t; e0 < nq4; e0 += 256 * 4) {      // four elements x up to eight splits of loads in flight per thread
+        float4 a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) a[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < A.sq; s0 += 8) {
+            float4 p[4][8];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    const int e = e0 + u * 256;
+                    p[u][s] = (e < nq4 && s0 + s < A.sq)
+                                  ? *reinterpret_cast<const float4*>(A.pq + ((size_t)(s0 + s) * A.B + b) * nh * hd + e * 4)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    if (s0 + s < A.sq) {            // split order; the guard keeps "+ 0" out of the fold
+                        a[u].x = __fadd_rn(a[u].x, p[u][s].x); a[u].y = __fadd_rn(a[u].y, p[u][s].y);
+                        a[u].z = __fadd_rn(a[u].z, p[u][s].z); a[u].w = __fadd_rn(a[u].w, p[u][s].w);
+                    }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (e0 + u * 256 < nq4) *reinterpret_cast<float4*>(qv + (e0 + u * 256) * 4) = a[u];
     }
     double s1 = 0.0, s2 = 0.0;
     for (int e = t; e < hd; e += 256) {
         float a = 0.0f;
-        for (int s = 0; s < A.sk; ++s) a = __fadd_rn(a, A.pk[((size_t)s * A.B + b) * hd + e]);
+        for (int s0 = 0; s0 < A.sk; s0 += 8) {       // eight loads in flight, folded in split order
+            float p[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) p[s] = s0 + s < A.sk ? A.pk[((size_t)(s0 + s) * A.B + b) * hd + e] : 0.0f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                if (s0 + s < A.sk) a = __fadd_rn(a, p[s]);
+        }
         kv[e] = a;
         s1 += (double)a; s2 += (double)a * (double)a;
     }
@@ -316,15 +408,16 @@ front_epilogue_kernel(EpiArgs A) {
     for (int e = t; e < hd; e += 256)
         kv[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(kv[e], mean), inv), A.kn_w[e]), A.kn_b[e]);
     __syncthreads();
-    // rotation: (nh + 1) segments of rope_seg at rope_off; pairs are read into registers first
-    const int half = A.rope_seg / 2, pos = A.pos[b];
+    // rotation: (nh + 1) segments of rope_seg at rope_off; every pair is read into registers before any write
     const int npairs = (nh + 1) * half;
     float lo[8], hi[8];
     int cnt = 0;
     for (int p = t; p < npairs && cnt < 8; p += 256, ++cnt) {
         const int seg = p / half, j = p - seg * half;
         const float* v = fe_smem + (size_t)seg * hd + A.rope_off;
-        rope_pair(v[2 * j], v[2 * j + 1], j, A.rope_seg, pos, A.theta, &lo[cnt], &hi[cnt]);
+        const float a = v[2 * j], c = v[2 * j + 1], cs = s_cs[j], sn = s_sn[j];
+        lo[cnt] = __fsub_rn(__fmul_rn(a, cs), __fmul_rn(c, sn));
+        hi[cnt] = __fadd_rn(__fmul_rn(c, cs), __fmul_rn(a, sn));
     }
     __syncthreads();
     cnt = 0;
@@ -334,7 +427,10 @@ front_epilogue_kernel(EpiArgs A) {
         v[j] = lo[cnt]; v[half + j] = hi[cnt];
     }
     __syncthreads();
-    for (int e = t; e < nh * hd; e += 256) A.index_q[(size_t)b * nh * hd + e] = rv_f32_to_bf16(qv[e]);
+    for (int e = t; e < nh * hd / 2; e += 256) {   // two values per 32-bit store
+        const uint32_t w2 = (uint32_t)rv_f32_to_bf16(qv[2 * e]) | ((uint32_t)rv_f32_to_bf16(qv[2 * e + 1]) << 16);
+        reinterpret_cast<uint32_t*>(A.index_q + (size_t)b * nh * hd)[e] = w2;
+    }
     for (int e = t; e < hd; e += 256) A.index_key[(size_t)b * hd + e] = rv_f32_to_bf16(kv[e]);
 }
 
@@ -434,7 +530,7 @@ RIVOLI_API int rivoli_index_frontend_bf16(const IndexFrontGeom* g, const uint16_
     if (g->block & (g->block - 1)) return 1003;
     if (g->rope_seg <= 0 || (g->rope_seg & 1) || g->rope_off < 0 || g->rope_off + g->rope_seg > g->index_dim) return 1002;
     if (g->index_heads > 256 || (size_t)(g->index_heads + 1) * g->index_dim * 4 > 200 * 1024) return 1002;
-    if ((g->index_heads + 1) * (g->rope_seg / 2) > 8 * 256) return 1002;
+    if ((g->index_heads + 1) * (g->rope_seg / 2) > 8 * 256 || g->rope_seg > 1024 || (g->index_dim & 3)) return 1002;
     cudaStream_t st = (cudaStream_t)stream;
     const bool mma = !force_simt && front_mma_ok(g) && (((uintptr_t)x | (uintptr_t)q_resid | (uintptr_t)wk | (uintptr_t)wq_b |
                                                          (uintptr_t)wproj | (uintptr_t)scratch) & 15) == 0;
@@ -451,8 +547,8 @@ RIVOLI_API int rivoli_index_frontend_bf16(const IndexFrontGeom* g, const uint16_
     }
     rv_drain_error();
     if (mma) {
-        cudaFuncSetAttribute(front_gemm_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * FM_STAGE);
-        front_gemm_mma_kernel<<<fa.n_cta, FM_THREADS, 2 * FM_STAGE, st>>>(fa);
+        cudaFuncSetAttribute(front_gemm_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FM_SMEM);
+        front_gemm_mma_kernel<<<fa.n_cta, FM_THREADS, FM_SMEM, st>>>(fa);
     } else {
         front_gemm_simt_kernel<<<fa.n_cta, 256, 0, st>>>(fa);
     }
@@ -476,3 +572,9 @@ RIVOLI_API int rivoli_index_frontend_status(void* stream) {
     if (h) { const int z = 0; cudaMemcpyToSymbol(g_front_err, &z, sizeof(int)); }
     return h ? 1008 : 0;
 }
+
+#ifdef RIVOLI_DEBUG_TIMES
+extern "C" __attribute__((visibility("default"))) int rivoli_front_debug_times(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_fm_times, sizeof(long long) * 64);
+}
+#endif
