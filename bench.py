@@ -32,6 +32,10 @@ WORKLOADS = {
     "cfg1": dict(B=1, ctx=257, n_heads=16, index_heads=8, index_dim=64, page_tokens=16, top_k=64, seed=0),
     "cfg2": dict(B=32, ctx=2048, n_heads=64, index_heads=32, index_dim=128, page_tokens=64, top_k=2048, seed=1),
     "cfg3": dict(B=128, ctx=16384, n_heads=64, index_heads=32, index_dim=128, page_tokens=64, top_k=2048, seed=2),
+    # continuous batching with churn: 78 layers, 32 sequences per GPU (256 over 8 GPUs), ragged contexts; the upper
+    # bound leaves a sequence 128 tokens to grow inside the 32,768-token limit of the tensor-core selection
+    "cfg5": dict(B=32, ctx_lo=512, ctx_hi=32640, layers=78, n_heads=64, index_heads=32, index_dim=128, page_tokens=64,
+                 top_k=2048, seed=4),
 }
 KV_LORA, ROPE = 512, 64
 # dram__bytes_read.sum + dram__bytes_write.sum per sequence of the cfg3 shape, from the ncu capture
@@ -441,6 +445,85 @@ def time_projections(w, device, steps=50):
     return out
 
 
+def run_churn(args):
+    """Continuous batching with eviction churn: `layers` decode layers behind one page allocator, a ragged
+    batch (contexts U[512, 32768]), every token-step appends one token per sequence per layer, selects and
+    attends; after each token-step 10 % of the sequences finish, their pages return to the free list and
+    replacements with fresh contexts are admitted (their prefill is NOT timed). Prints one JSON line."""
+    import torch
+    from rivoli_b200 import backend as be
+    from rivoli_b200.engine import DsaDecodeStack
+    from rivoli_b200.scheduler import ContinuousBatcher, churn_plan
+    w = WORKLOADS["cfg5"]
+    n_layers = args.layers or w["layers"]
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    B, P, lo, hi = w["B"], w["page_tokens"], w["ctx_lo"], w["ctx_hi"]
+    max_ctx = 32768
+    assert hi + args.steps + args.warmup < max_ctx, "too many token-steps for the context bound"
+    max_pages = (max_ctx + P - 1) // P
+    n_pool = int(1.25 * B * max_pages)
+    g = be.DsaGeom.make(n_heads=w["n_heads"], kv_lora=KV_LORA, rope_dim=ROPE, index_heads=w["index_heads"],
+                        index_dim=w["index_dim"], page_tokens=P, top_k=w["top_k"], max_pages_per_seq=max_pages,
+                        n_pool_pages=n_pool)
+    stack = DsaDecodeStack(g, B, [True] * n_layers, device=device, max_ctx=max_pages * P, shuffle_seed=w["seed"])
+    sched = ContinuousBatcher(B, n_pool, max_ctx, P, pool=stack.pool)
+    rng = np.random.RandomState(w["seed"])
+    gen = torch.Generator(device=device)
+    gen.manual_seed(w["seed"])
+    W = KV_LORA + ROPE
+    blk = 1 << 15                                  # one block of random rows serves every prefill (contents are irrelevant here)
+    lat_blk = torch.randn((blk, W), generator=gen, device=device).to(torch.bfloat16)
+    key_blk = torch.randn((blk, w["index_dim"]), generator=gen, device=device).to(torch.bfloat16)
+
+    def prefill(slots, lens):
+        stack.upload_block_table()
+        for s_, n in zip(slots, lens):
+            for o in range(0, int(n), blk):
+                m = min(blk, int(n) - o)
+                pos = torch.arange(o, o + m, dtype=torch.int32, device=device)
+                seq = torch.full((m,), int(s_), dtype=torch.int32, device=device)
+                for L in stack.layers:
+                    L.append(lat_blk[:m], key_blk[:m], pos, seq)
+
+    first = rng.randint(lo, hi + 1, B)
+    for s_, n in enumerate(first):
+        sched.admit(s_, int(n))
+    prefill(range(B), first)
+    x = step_inputs(dict(w, B=B), device, gen)
+    torch.cuda.synchronize(device)
+    times, appended = [], 0
+    for it in range(args.warmup + args.steps):
+        row_pos, seq_len = sched.begin_step()          # host: one page-table update for all layers
+        rp, sl = torch.from_numpy(row_pos).to(device), torch.from_numpy(seq_len).to(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        stack.upload_block_table()
+        for i in range(n_layers):
+            stack.step_layer(i, x["latent"], x["index_key"], x["index_q"], x["index_w"], x["q"], rp, sl)
+        e1.record()
+        torch.cuda.synchronize(device)
+        if it >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+            appended += B
+        slots, lens = churn_plan(rng, B, 0.10, lo, hi)
+        sched.finish(slots, lens)
+        prefill(slots, lens)                          # untimed
+        torch.cuda.synchronize(device)
+    for L in stack.layers[:2]:
+        L.check_status()
+    ms = float(np.mean(times))
+    line = {"metric": METRIC, "value": n_layers / (ms * 1e-3), "unit": "layer-steps/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / n_layers, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"cfg5 slice: {n_layers} layers x batch {B}/GPU, contexts U[{lo},{hi}], top-k {w['top_k']}, "
+                                   f"{P}-token pages from one shared free list, 10 % of sequences replaced per token-step "
+                                   f"(prefill untimed), seed {w['seed']}",
+                       "token_step_ms": ms, "mean_context": float(sched.seq_len.mean())},
+            "gpu_launches": args.steps * n_layers * 4}
+    print(json.dumps(line), flush=True)
+
+
 def run_gather_probe(args):
     """Gather roofline of the attention access pattern: 1 of every 8 tokens of 64-token pages
     scattered in a 1.25x pool, 16 tiles of 128 rows per CTA (the cfg3 attention shape)."""
@@ -579,6 +662,7 @@ def main():
     ap.add_argument("--profile", default=None, choices=["select", "attend", "step", "gather", "proj"],
                     help="build the workload, run 3 iterations of one stage (or the whole step) and exit: "
                          "the command line the profiles/ summaries were captured with")
+    ap.add_argument("--layers", type=int, default=0, help="cfg5 only: number of layers (default 78)")
     ap.add_argument("--batch", type=int, default=0,
                     help="with --profile only: sequences per GPU instead of the workload's own batch")
     args = ap.parse_args()
@@ -586,6 +670,13 @@ def main():
         ap.error("--batch is a --profile option; the bench always runs the workload's own batch")
     if args.profile:
         return run_profile(args)
+    if args.workload == "cfg5":
+        if args.impl == "reference" or args.gpus != 1:
+            ap.error("the churn workload runs on one GPU with the CUDA arm only (it is a parity / capacity case, "
+                     "not the headline line)")
+        if args.steps == 400:
+            args.steps = 8               # token-steps of 78 layer-steps each
+        return run_churn(args)
     if args.impl == "reference":
         run_reference(args)
     else:

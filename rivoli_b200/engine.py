@@ -64,6 +64,8 @@ class DsaDecodeStack:
         if shuffle_seed is not None:
             self.pool.shuffle(shuffle_seed)
         self.layers = [DsaDecodeLayer(geom, n_seqs, device=device, max_ctx=max_ctx, pool=self.pool) for _ in full]
+        for L in self.layers[1:]:           # ONE device block table for the whole stack: one upload per step
+            L.block_table = self.layers[0].block_table
         self.owner = []                     # index of the full layer whose rows layer i attends over
         last = 0
         for i, f in enumerate(full):
@@ -72,9 +74,7 @@ class DsaDecodeStack:
             self.owner.append(last)
 
     def upload_block_table(self) -> None:
-        bt = self.pool.block_table()
-        for L in self.layers:
-            L.upload_block_table(bt)
+        self.layers[0].upload_block_table(self.pool.block_table())
 
     def step_layer(self, i: int, latent, index_key, index_q, index_w, q, row_pos, seq_len, stream=None):
         """One layer-step of layer ``i``. Shared layers ignore ``index_key``/``index_q``/``index_w`` (they may be

@@ -70,9 +70,9 @@ class DsaDecodeLayer:
     def release(self, seq: int) -> None:
         self.pool.release(seq)
 
-    def upload_block_table(self, table: "np.ndarray | None" = None) -> None:
+    def upload_block_table(self, table: "np.ndarray | None" = None, non_blocking: bool = False) -> None:
         bt = torch.from_numpy(self.pool.block_table() if table is None else table)
-        self.block_table.copy_(bt, non_blocking=False)
+        self.block_table.copy_(bt, non_blocking=non_blocking)
 
     # --- operators ----------------------------------------------------------------------------------
     def append(self, latent: torch.Tensor, index_key: torch.Tensor, row_pos: torch.Tensor,

@@ -144,3 +144,24 @@ def test_cfg2_dense_equivalent_shape():
                                               np.array([ctx], np.int32), want_f32=True)
         ok, worst = attend_close(u16(out[b:b + 1]), o_f32)
         assert ok, worst
+
+
+def test_selection_beyond_16384_tokens_uses_the_wide_kernel_and_stays_exact():
+    """Contexts in (16384, 32768] take the 32-keys-per-thread instantiation of the selection kernel: fused
+    tensor-core selection == exact CUDA-core chain, bit for bit, on a ragged pair of long contexts."""
+    import torch
+    from rivoli_b200 import backend as be
+    w = dict(bench.WORKLOADS["cfg3"]); w["B"] = 2; w["ctx"] = 30000
+    g, layer, gen = bench.build_layer(w, torch.device("cuda", 0), 9)
+    x = bench.step_inputs(w, torch.device("cuda", 0), gen)
+    seq_len = torch.tensor([30000, 17001], dtype=torch.int32, device="cuda")
+    assert be.index_select_uses_mma(g, layer.score_stride)
+    layer.select(x["index_q"], x["index_w"], seq_len)
+    be.device_sync(); layer.check_status()
+    rows_f, n_f = layer.rows.clone(), layer.n_sel.clone()
+    layer.select_unfused(x["index_q"], x["index_w"], seq_len)
+    be.device_sync()
+    assert torch.equal(n_f, layer.n_sel)
+    for b in range(2):
+        n = int(n_f[b])
+        assert n == 2048 and torch.equal(rows_f[b, :n], layer.rows[b, :n])
