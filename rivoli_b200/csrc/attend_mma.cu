@@ -122,17 +122,6 @@ attend_mma_kernel(AttendMmaArgs A) {
     if (tid == 0) AM_STAMP(0, 12);
     const int P = A.page_tokens;
 
-    int nr = A.n_rows[b];
-    {
-        const long long cap = A.rows ? A.row_stride : (long long)A.max_pages * P;
-        nr = (int)max(0LL, min((long long)nr, cap));
-    }
-    const int ntiles_all = (nr + AM_TILE - 1) / AM_TILE;
-    const int tps = (ntiles_all + A.n_splits - 1) / A.n_splits;
-    const int r_begin = split * tps * AM_TILE;
-    const int r_end = min(nr, r_begin + tps * AM_TILE);
-    const int ntiles = r_end > r_begin ? (r_end - r_begin + AM_TILE - 1) / AM_TILE : 0;
-
     if (tid == 0) {
         tc::mbar_init(&bars.k_full[0], 64); tc::mbar_init(&bars.k_full[1], 64);
         tc::mbar_init(&bars.kv_empty[0], 1); tc::mbar_init(&bars.kv_empty[1], 1);
@@ -159,7 +148,7 @@ attend_mma_kernel(AttendMmaArgs A) {
     // Warps 0-7 take 8 heads each; a head's 576 values are 72 chunks of 8 (lane, lane+32, lane+64).
     // The gather warps do not wait for this: the MMA warp does (q_full) before its first QK.
     if (tid == 0) AM_STAMP(0, 13);
-    if (warp < 8 && ntiles > 0) {
+    if (warp < 8) {
         const uint16_t* qb = A.q + (size_t)b * AM_H * AM_W;
 #pragma unroll 1
         for (int h4 = 0; h4 < 8; h4 += 4) {
@@ -227,6 +216,21 @@ attend_mma_kernel(AttendMmaArgs A) {
         tc::mbar_arrive(&bars.q_full);
         if (tid == 0) AM_STAMP(0, 14);
     }
+
+    // Everything above reads only this kernel's own inputs, so under a programmatic dependent launch it
+    // overlaps the tail of the selection kernel; the selected rows and their counts are read below.
+    rv_grid_dep_wait();
+    int nr = A.n_rows[b];
+    {
+        const long long cap = A.rows ? A.row_stride : (long long)A.max_pages * P;
+        nr = (int)max(0LL, min((long long)nr, cap));
+    }
+    const int ntiles_all = (nr + AM_TILE - 1) / AM_TILE;
+    const int tps = (ntiles_all + A.n_splits - 1) / A.n_splits;
+    const int r_begin = split * tps * AM_TILE;
+    const int r_end = min(nr, r_begin + tps * AM_TILE);
+    const int ntiles = r_end > r_begin ? (r_end - r_begin + AM_TILE - 1) / AM_TILE : 0;
+
 
     if (warp >= 9 && ntiles > 0) {
         // ------------------------------ gather producers ------------------------------------------
@@ -669,7 +673,7 @@ extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q,
                     g->page_tokens, g->max_pages_per_seq, g->n_pool_pages, n_splits,
                     out, out_m, out_lse, n_splits > 1 ? partial : nullptr, err};
     cudaFuncSetAttribute(attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
-    attend_mma_kernel<<<dim3(n_splits, B), AM_THREADS, SM_TOTAL, st>>>(a);
+    rv_launch_dependent(attend_mma_kernel, dim3(n_splits, B), dim3(AM_THREADS), (size_t)SM_TOTAL, st, a);
     if (int e = rv_launch_status()) return e;
     if (n_splits > 1) {
         rivoli_attend_combine_paged(partial, AM_H, AM_KVL, n_splits, B, out, out_m, out_lse, st);

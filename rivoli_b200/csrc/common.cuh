@@ -16,6 +16,26 @@ static inline int rv_launch_status() {
     return e == cudaSuccess ? 0 : -(int)e;
 }
 
+// Programmatic dependent launch: a kernel launched this way may begin (its prologue, up to its own
+// rv_grid_dep_wait()) while the kernel before it in the stream is still running, once every CTA of that
+// kernel has called rv_grid_dep_trigger() or exited. rv_grid_dep_wait() returns when the preceding kernel
+// has completed and its writes are visible. Both are no-ops in a kernel launched the ordinary way.
+#ifdef __CUDACC__
+__device__ __forceinline__ void rv_grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void rv_grid_dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <class... KArgs, class... Args>
+static inline void rv_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, kernel, args...);   // the caller reads the launch status afterwards
+}
+#endif
+
 static inline bool rv_is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
 
 // Geometry guard shared by every paged entry point. Decided on the host; nothing is

@@ -120,6 +120,7 @@ index_q_prepare_kernel(const uint16_t* __restrict__ q, const float* __restrict__
                        float dscale, uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
                        int* __restrict__ err) {
     __shared__ float term[32];
+    rv_grid_dep_trigger();   // the scorer may set itself up while this runs; it waits before reading these outputs
     index_q_prepare_block(blockIdx.x, q, w, nh, hd, wscale, dscale, codes, scales, cb, err, term);
 }
 
@@ -136,6 +137,7 @@ step_prologue_kernel(DsaGeom g, AppendArgs ap, int B, const uint16_t* __restrict
                      uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ cb,
                      int* __restrict__ err) {
     __shared__ float term[32];
+    rv_grid_dep_trigger();   // the scorer may set itself up while this runs; it waits before reading these outputs
     if ((int)blockIdx.x < B) {
         index_q_prepare_block(blockIdx.x, q, w, g.index_heads, g.index_dim, g.index_wscale, g.index_dscale, codes, scales,
                               cb, err, term);
@@ -186,6 +188,8 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = tmem_base_s;
+    rv_grid_dep_trigger();   // the selection kernel may be scheduled; it waits for this grid before reading scores
+    rv_grid_dep_wait();      // query codes, head scales and this step's appended keys come from the kernel before
 
     const int max_tiles = (A.score_stride + IM_TILE - 1) / IM_TILE;
     const int chunks = (max_tiles + IM_TPI - 1) / IM_TPI;
@@ -361,6 +365,8 @@ index_select_refine_kernel(RefineArgs A) {
     constexpr int TOK = rf_tok(EPT);               // listed tokens a warp re-scores per pass
     const int nh = g.index_heads, P = g.page_tokens;
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    rv_grid_dep_trigger();   // the attention kernel may start converting its queries; it waits before reading rows
+    rv_grid_dep_wait();      // scores come from the kernel before
     const int nt = min(A.seq_len[b], A.score_stride);
     const int kk = min(A.k, nt);
     uint32_t* out = A.rows + (size_t)b * A.k;
@@ -720,7 +726,7 @@ static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* i
                                              (uint32_t)g->page_tokens))
         return e;
     if (int e = rivoli::make_tmap_rows_sw128(&tm_q, s.qcodes, (uint64_t)B * nh, IM_HD, (uint32_t)nh)) return e;
-    index_score_mma_kernel<<<grid, IM_THREADS, smem1, st>>>(ma, tm_keys, tm_q);
+    rv_launch_dependent(index_score_mma_kernel, dim3(grid), dim3(IM_THREADS), smem1, st, ma, tm_keys, tm_q);
     if (int e = rv_launch_status()) return e;
 
     RefineArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb,
@@ -732,7 +738,7 @@ static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* i
                               3 * RF_LIST) * 4;                                                                   \
         cudaFuncSetAttribute(index_select_refine_kernel<EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
                              (int)smem2);                                                                         \
-        index_select_refine_kernel<EPT><<<B, TK_THREADS, smem2, st>>>(ra);                                        \
+        rv_launch_dependent(index_select_refine_kernel<EPT>, dim3(B), dim3(TK_THREADS), smem2, st, ra);           \
     } while (0)
     if (score_stride <= 8 * TK_THREADS) RV_REFINE(8);
     else if (score_stride <= 16 * TK_THREADS) RV_REFINE(16);
