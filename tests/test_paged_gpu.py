@@ -368,3 +368,34 @@ def test_fused_append_select_equals_separate_calls(be, case):
     np.testing.assert_array_equal(nb, want["n_sel"])
     for b in range(B):
         np.testing.assert_array_equal(rb[b, :nb[b]].view(np.uint32), want["rows"][b, :nb[b]])
+
+
+def test_empty_and_single_token_sequences(be):
+    """A batch holding an empty sequence, a one-token sequence and an ordinary one: the empty one selects
+    nothing and attends to zeros (lse = -inf), the others are unaffected by their neighbour."""
+    st, g, d = build(be, "ragged")
+    B = st.B
+    seq_len = st.seq_len.copy()
+    seq_len[1] = 0                                   # sequence 1 is empty this step; sequence 0 has one token
+    from rivoli_b200.layer import DsaDecodeLayer
+    layer = DsaDecodeLayer(g, B, max_ctx=int(g.max_pages_per_seq * g.page_tokens))
+    layer.latent_pool.copy_(d["latent_pool"]); layer.latent_scale.copy_(d["latent_scale"])
+    layer.index_pool.copy_(d["index_pool"]); layer.index_scale.copy_(d["index_scale"])
+    layer.upload_block_table(st.block_table)
+    # the step's token is appended everywhere but in the empty sequence
+    keep = np.array([b for b in range(B) if b != 1], np.int32)
+    layer.append(dev(st.new_latent[keep]), dev(st.new_key[keep]), dev(st.row_pos[keep]), dev(keep))
+    sl = dev(seq_len)
+    layer.select(dev(st.index_q), dev(st.index_w), sl)
+    out = layer.attend(dev(st.q))
+    be.device_sync(); layer.check_status()
+    n_sel = layer.n_sel.cpu().numpy()
+    assert n_sel[1] == 0 and n_sel[0] == 1
+    assert int(layer.rows[0, 0]) == 0
+    o = out.float().cpu().numpy()
+    assert np.all(o[1] == 0.0) and np.all(np.isneginf(layer.out_lse.cpu().numpy()[1]))
+    want = st.oracle_step()
+    for b in (0, 2, 3, 4):
+        np.testing.assert_array_equal(layer.rows[b, :n_sel[b]].cpu().numpy().view(np.uint32), want["rows"][b, :want["n_sel"][b]])
+    ok, worst, rms = attend_close_ref(u16(out)[[0, 2, 3, 4]], want["out_f32"][[0, 2, 3, 4]])
+    assert ok and rms <= 1e-2, (worst, rms)
