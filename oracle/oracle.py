@@ -1,4 +1,4 @@
-"""ctypes binding of the CPU oracle (``liboracle.so``, built from ``rivoli_oracle.c``).
+"""ctypes binding of the CPU oracle (``liboracle.so``, built from ``rivoli_oracle.c`` and ``v4_oracle.c``).
 
 Test infrastructure only: imported by ``tests/``, by the smoke check and by the
 ``cpu_baseline`` / ``--impl reference`` legs of the benchmark. The product package never
@@ -18,8 +18,8 @@ _SO = os.path.join(_HERE, "liboracle.so")
 
 def build(force: bool = False) -> str:
     """Compile ``liboracle.so`` beside its source if it is missing or stale."""
-    src = os.path.join(_HERE, "rivoli_oracle.c")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, n) for n in ("rivoli_oracle.c", "v4_oracle.c")]
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < max(os.path.getmtime(p) for p in srcs):
         subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
                        stdout=subprocess.DEVNULL)
     return _SO
@@ -372,3 +372,87 @@ def set_num_threads(n: int) -> None:
 
 def num_threads() -> int:
     return lib().orc_num_threads()
+
+
+# --- V4 cousin path (v4_oracle.c) -----------------------------------------------------------------
+class V4Geom(C.Structure):
+    """Mirror of ``orc_v4_geom`` (same field order as the product's ``V4Geom``)."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "n_heads", "head_dim", "window", "index_heads", "index_dim", "index_topk", "ratio",
+        "max_comp")] + [("softmax_scale", C.c_float)]
+
+
+def e2m1_decode(nib: int) -> float:
+    f = lib().orc_e2m1_decode
+    f.restype, f.argtypes = C.c_float, [C.c_uint8]
+    return float(f(nib))
+
+
+def e2m1_encode(x: float) -> int:
+    f = lib().orc_e2m1_encode
+    f.restype, f.argtypes = C.c_uint8, [C.c_float]
+    return int(f(x))
+
+
+def fast_round_scale(amax: float, max_inv: float) -> float:
+    f = lib().orc_fast_round_scale
+    f.restype, f.argtypes = C.c_float, [C.c_float, C.c_float]
+    return float(f(amax, max_inv))
+
+
+def v4_hadamard(row) -> np.ndarray:
+    r = _c(row, np.float32).copy()
+    lib().orc_v4_hadamard(_p(r), C.c_int(r.size))
+    return r
+
+
+def v4_spread(x, d) -> tuple[int, np.ndarray]:
+    """Hadamard + bf16 + fp4 block-32 + bf16 on every row of ``x`` ([rows, d] f32)."""
+    r = _c(x, np.float32).reshape(-1, d).copy() if d > 0 and np.size(x) else np.zeros((0, max(d, 1)), np.float32)
+    rc = lib().orc_v4_spread(_p(r), C.c_int(r.shape[0]), C.c_int(d))
+    return int(rc), r
+
+
+def v4_index_score_blocks(q, kv, w, s, n_comp, heads, hd) -> tuple[int, np.ndarray]:
+    q, kv, w = _c(q, np.float32), _c(kv, np.float32), _c(w, np.float32)
+    out = np.zeros((max(s, 0), max(n_comp, 0)), np.float32)
+    rc = lib().orc_v4_index_score_blocks(_p(q), _p(kv), _p(w), _p(out), C.c_int(s), C.c_int(n_comp),
+                                         C.c_int(heads), C.c_int(hd))
+    return int(rc), out
+
+
+def v4_scored_row(scores, limit, k, offset, width) -> np.ndarray:
+    sc = _c(scores, np.float32)
+    out = np.zeros(width, np.int32)
+    lib().orc_v4_scored_row(_p(sc), C.c_int(limit), C.c_int(k), C.c_int(offset), C.c_int(width), _p(out))
+    return out
+
+
+def v4_window_row(win, start_pos) -> np.ndarray:
+    out = np.zeros(win, np.int32)
+    lib().orc_v4_window_row(C.c_int(win), C.c_int(start_pos), _p(out))
+    return out
+
+
+def v4_sparse_attn(q, kv, sink, idxs, m, h, d, topk, scale) -> tuple[int, np.ndarray]:
+    q, kv, sink = _c(q, np.float32), _c(kv, np.float32), _c(sink, np.float32)
+    idxs = _c(idxs, np.int32)
+    o = np.zeros((max(m, 0), max(h, 0), max(d, 0)), np.float32)
+    rc = lib().orc_v4_sparse_attn(_p(q), _p(kv), _p(sink), _p(idxs), C.c_int(m), C.c_int(h), C.c_int(d),
+                                  C.c_int(topk), C.c_float(scale), _p(o))
+    return int(rc), o
+
+
+def v4_decode_step_bf16(g: V4Geom, pos, q, kv_cache, sink, iq, iw, ikv, want_scores=False):
+    """Batched decode step over bf16 storage. Returns (sel [B, window+topk] i32, out [B,H,D] u16
+    [, scores [B, max_comp] f32])."""
+    pos = _c(pos, np.int32)
+    B = pos.size
+    q, kv_cache, iq, ikv = (_c(a, np.uint16) for a in (q, kv_cache, iq, ikv))
+    sink, iw = _c(sink, np.float32), _c(iw, np.float32)
+    sel = np.zeros((B, g.window + g.index_topk), np.int32)
+    out = np.zeros((B, g.n_heads, g.head_dim), np.uint16)
+    sc = np.zeros((B, g.max_comp), np.float32) if want_scores else None
+    lib().orc_v4_decode_step_bf16(C.byref(g), C.c_int(B), _p(pos), _p(q), _p(kv_cache), _p(sink), _p(iq),
+                                  _p(iw), _p(ikv), _p(sel), _p(sc), _p(out))
+    return (sel, out, sc) if want_scores else (sel, out)
