@@ -309,6 +309,61 @@ int rivoli_index_frontend_bf16(const IndexFrontGeom* g, const uint16_t* x, const
 /* Synchronises `stream`; 1008 if a bounded wait of the tensor-core front end gave up since the last call. */
 int rivoli_index_frontend_status(void* stream);
 
+/* ---- V4 cousin path: block indexer, scored block selection, MQA sparse attention with a sink --------
+ *
+ * The first three are the reference's own symbols with identical signatures and guard codes
+ * (f32 activations holding bf16 values, one sequence). */
+
+/* crates/backend/kernels/blockindex.hip:263-282 (kernel :97-138). In place on `rows` rows of width d:
+ * natural-order Walsh-Hadamard butterfly * 1/sqrt(d), bf16 store, fp4 (e2m1) block-32 quantise-dequantise
+ * with a power-of-two scale, bf16 store. Bit-identical to the host rule. 1001 rows/d <= 0, 1002 d > 256,
+ * 1003 d not a power of two, 1004 d % 32 != 0. */
+int rivoli_act_quant_f4_rotated(float* x, int rows, int d, void* stream);
+
+/* crates/backend/kernels/blockindex.hip:284-306 (kernel :234-261).
+ * score[t][c] = bf16( sum_h bf16( relu(bf16(q[t][h] . kv[c])) * w[t][h] ) ); the dot and the head sum are
+ * ascending f32 folds with one rounding per operation (no fused multiply-add), so the result is
+ * bit-identical to the host fold. 1001 s/heads/hd <= 0, 1005 n_comp <= 0. */
+int rivoli_index_score_blocks(const float* q, const float* kv, const float* w, float* score, int s, int n_comp,
+                              int heads, int hd, void* stream);
+
+/* crates/backend/kernels/attn.hip:442-465 (kernel :358-440). o[t][head] = softmax over the slots
+ * idxs[t][0..topk) (-1 = masked) of q[t][head] . kv[idx] * scale, times kv[idx]; sink[head] joins the
+ * softmax DENOMINATOR only (max-shifted). Output rounded to bf16. A query with every slot masked writes
+ * NaN. 1001 non-positive sizes, 1002 d > 1024, 1006 (d + topk) floats + reduction scratch over 64 KiB. */
+int rivoli_gather_attn_shared_kv(const float* q, const float* kv, const float* sink, const int* idxs, int m, int h,
+                                 int d, int topk, float scale, float* o, void* stream);
+
+/* Batched decode form over bf16 storage (no counterpart in the reference, whose V4 engine is one sequence
+ * at a time: crates/engine/src/v4/select.rs:78-86). Per sequence b:
+ *   kv_cache[b]  bf16 [window + max_comp][head_dim]: ring slots, then the compressed rows in block order;
+ *   index_kv[b]  bf16 [max_comp][index_dim]: the indexer's compressed rows (already spread);
+ *   pos[b] = position of the query token (already written to the ring); n_comp = (pos+1) / ratio. */
+typedef struct V4Geom {
+    int32_t n_heads, head_dim, window, index_heads, index_dim, index_topk, ratio, max_comp;
+    float softmax_scale;
+} V4Geom;
+
+/* Selection rows sel[b][window + index_topk] (crates/engine/src/v4/select.rs:153-232,395-447):
+ * the ring in oldest-first order (-1 past the live slots before it fills), then the compressed columns:
+ * every closed block in order while n_comp <= index_topk, otherwise the index_topk best by score
+ * (total order on f32, ties toward the lower block), ascending, each shifted by `window`; -1 pads the row.
+ * index_q bf16 [B][index_heads][index_dim] (already spread), index_w f32 [B][index_heads].
+ * scores (optional, may be null) receives the score rows [B][max_comp] of the sequences that ranked.
+ * Bit-exact in indices and scores. 1001 bad sizes, 1002 index_heads > 64 or index_dim > 256 or
+ * max_comp > 65536, 1004 index_dim % 32 != 0. */
+int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const int32_t* pos, const uint16_t* index_q,
+                                 const float* index_w, const uint16_t* index_kv, int32_t* sel, float* scores,
+                                 void* stream);
+
+/* out[b][head] bf16 = sparse attention of q[b] bf16 [n_heads][head_dim] over kv_cache[b] rows sel[b][0..cols)
+ * with the sink in the denominator. n_heads == 64 and head_dim == 512 run on the tensor cores (one CTA per
+ * sequence: the gathered rows are staged once in shared memory and shared by all heads); other shapes on
+ * CUDA cores. 1001 bad sizes, 1002 head_dim > 1024, 1006 cols too large for the CUDA-core staging. */
+int rivoli_v4_sparse_attend_bf16(const V4Geom* g, int n_seqs, const uint16_t* q, const uint16_t* kv_cache,
+                                 const float* sink, const int32_t* sel, int cols, uint16_t* out, int force_simt,
+                                 void* stream);
+
 /* Diagnostic, not on any product path (bench.py --profile gather): average milliseconds of a
  * launch in which each of n_ctas CTAs copies n_tiles tiles of 128 latent rows (576 bytes each,
  * rows[cta][tile][128] = pool row numbers) from the pool into shared memory with `depth` (1..3)

@@ -399,6 +399,52 @@ def index_frontend_status(stream=None) -> None:
     ensure_status(lib().rivoli_index_frontend_status(_stream(stream)), "index_frontend(status)")
 
 
+class V4Geom(C.Structure):
+    """``V4Geom`` of include/rivoli_kernels.h: the V4 cousin path's batched decode geometry."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "n_heads", "head_dim", "window", "index_heads", "index_dim", "index_topk", "ratio", "max_comp")] + [
+        ("softmax_scale", C.c_float)]
+
+    @classmethod
+    def make(cls, *, n_heads=64, head_dim=512, window=128, index_heads=64, index_dim=128, index_topk=512, ratio=4,
+             max_comp, softmax_scale=None) -> "V4Geom":
+        import numpy as np
+        return cls(n_heads, head_dim, window, index_heads, index_dim, index_topk, ratio, max_comp,
+                   float(np.float32(head_dim) ** np.float32(-0.5)) if softmax_scale is None else softmax_scale)
+
+
+def launch_act_quant_f4_rotated(x, rows: int, d: int, stream=None) -> None:
+    """crates/backend/src/hip.rs launcher of ``rivoli_act_quant_f4_rotated`` (in place on f32 rows)."""
+    ensure_status(lib().rivoli_act_quant_f4_rotated(_ptr(x), C.c_int(rows), C.c_int(d), _stream(stream)),
+                  "act_quant_f4_rotated")
+
+
+def launch_index_score_blocks(q, kv, w, score, s: int, n_comp: int, heads: int, hd: int, stream=None) -> None:
+    ensure_status(lib().rivoli_index_score_blocks(_ptr(q), _ptr(kv), _ptr(w), _ptr(score), C.c_int(s), C.c_int(n_comp),
+                                                  C.c_int(heads), C.c_int(hd), _stream(stream)), "index_score_blocks")
+
+
+def launch_gather_attn_shared_kv(q, kv, sink, idxs, m: int, h: int, d: int, topk: int, scale: float, o,
+                                 stream=None) -> None:
+    ensure_status(lib().rivoli_gather_attn_shared_kv(_ptr(q), _ptr(kv), _ptr(sink), _ptr(idxs), C.c_int(m), C.c_int(h),
+                                                     C.c_int(d), C.c_int(topk), C.c_float(scale), _ptr(o),
+                                                     _stream(stream)), "gather_attn_shared_kv")
+
+
+def launch_v4_select_blocks_bf16(g: V4Geom, n_seqs: int, pos, index_q, index_w, index_kv, sel, scores=None,
+                                 stream=None) -> None:
+    ensure_status(lib().rivoli_v4_select_blocks_bf16(C.byref(g), C.c_int(n_seqs), _ptr(pos), _ptr(index_q), _ptr(index_w),
+                                                     _ptr(index_kv), _ptr(sel), _ptr(scores), _stream(stream)),
+                  "v4_select_blocks_bf16")
+
+
+def launch_v4_sparse_attend_bf16(g: V4Geom, n_seqs: int, q, kv_cache, sink, sel, cols: int, out,
+                                 force_simt: bool = False, stream=None) -> None:
+    ensure_status(lib().rivoli_v4_sparse_attend_bf16(C.byref(g), C.c_int(n_seqs), _ptr(q), _ptr(kv_cache), _ptr(sink),
+                                                     _ptr(sel), C.c_int(cols), _ptr(out), C.c_int(int(force_simt)),
+                                                     _stream(stream)), "v4_sparse_attend_bf16")
+
+
 def probe_gather(method: int, depth: int, n_ctas: int, n_tiles: int, pool, n_pool_rows: int, scales, rows,
                  stream=None) -> float:
     """Diagnostic gather roofline: milliseconds per launch (see include/rivoli_kernels.h)."""

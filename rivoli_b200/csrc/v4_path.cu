@@ -1,0 +1,657 @@
+// V4 cousin of the decode path: Hadamard + fp4 spread, block scorer, scored block selection and MQA
+// sparse attention with a per-head sink.
+//
+// Reference behaviour: crates/backend/kernels/blockindex.hip:97-138,234-306 (spread, block scorer),
+// crates/backend/kernels/attn.hip:358-465 (gather attention), crates/engine/src/v4/select.rs:153-232
+// (selection rows). The spread, the scores and the selected indices are bit-exact against the host
+// rules: every add and multiply on those paths is an explicit round-to-nearest intrinsic, so nothing
+// is contracted into a fused multiply-add, and every fold runs in the host's order.
+//
+// Storage on this side is bf16 (the reference keeps bf16 VALUES in f32 arrays: every producer on the
+// path ends in a bf16 store), which halves the gathered bytes and feeds the tensor cores directly.
+#include "codec.cuh"
+#include "common.cuh"
+#include "topk_core.cuh"
+
+namespace {
+
+__device__ __forceinline__ float v4_rbf16(float x) { return rv_bf16_to_f32(rv_f32_to_bf16(x)); }
+
+// ---------------------------------------------------------------------------------------------------
+// spread
+// ---------------------------------------------------------------------------------------------------
+constexpr int V4_ROT_MAX = 256;
+constexpr float V4_FP4_MAX = 6.0f;
+
+// e2m1 round trip of q (already clamped to [-6, 6]): nearest grid point, midpoints to the even code.
+__device__ __forceinline__ float v4_e2m1_roundtrip(float q) {
+    const float a = fabsf(q);
+    int code = 0;
+    code += a > 0.25f;
+    code += a >= 0.75f;
+    code += a > 1.25f;
+    code += a >= 1.75f;
+    code += a > 2.5f;
+    code += a >= 3.5f;
+    code += a > 5.0f;
+    const float mag = code < 4 ? 0.5f * (float)code : (code == 4 ? 2.0f : (code == 5 ? 3.0f : (code == 6 ? 4.0f : 6.0f)));
+    return signbit(q) ? -mag : mag;
+}
+
+// Smallest power of two >= amax / 6, from the exponent field of the product.
+__device__ __forceinline__ float v4_round_scale(float amax) {
+    const uint32_t b = __float_as_uint(__fmul_rn(amax, __fdiv_rn(1.0f, V4_FP4_MAX)));
+    const int e = (int)((b >> 23) & 0xffu) - 127 + ((b & 0x7fffffu) ? 1 : 0);
+    return __uint_as_float((uint32_t)(e + 127) << 23);
+}
+
+// One CTA per row. The butterfly visits the operand pairs (j, j + h) stage by stage exactly as the host
+// loop does; which thread evaluates a pair does not change the value.
+__global__ void __launch_bounds__(128) v4_spread_kernel(float* __restrict__ x, int d) {
+    __shared__ float sh[V4_ROT_MAX];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float* row = x + (size_t)blockIdx.x * d;
+    for (int i = tid; i < d; i += 128) sh[i] = row[i];
+    __syncthreads();
+    for (int h = 1; h < d; h <<= 1) {
+        for (int t = tid; t < (d >> 1); t += 128) {
+            const int j = 2 * t - (t & (h - 1));
+            const float a = sh[j], b = sh[j + h];
+            sh[j] = __fadd_rn(a, b);
+            sh[j + h] = __fsub_rn(a, b);
+        }
+        __syncthreads();
+    }
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)d));
+    for (int i = tid; i < d; i += 128) sh[i] = v4_rbf16(__fmul_rn(sh[i], scale));
+    __syncthreads();
+    // one warp per block of 32: the maximum is exact under any association
+    const float floor_ = __fmul_rn(V4_FP4_MAX, __uint_as_float(1u << 23));
+    for (int b = warp; b < d / 32; b += 4) {
+        const float v = sh[b * 32 + lane];
+        const float amax = fmaxf(rv_warp_max(fabsf(v)), floor_);
+        const float s = v4_round_scale(amax);
+        float q = __fdiv_rn(v, s);
+        q = q < -V4_FP4_MAX ? -V4_FP4_MAX : (q > V4_FP4_MAX ? V4_FP4_MAX : q);
+        sh[b * 32 + lane] = v4_rbf16(__fmul_rn(v4_e2m1_roundtrip(q), s));
+    }
+    __syncthreads();
+    for (int i = tid; i < d; i += 128) row[i] = sh[i];
+}
+
+// ---------------------------------------------------------------------------------------------------
+// block scorer
+// ---------------------------------------------------------------------------------------------------
+constexpr int SC_CB = 4;          // blocks a warp scores per iteration
+constexpr int SC_MAX_HEADS = 64;  // two lanes-worth of heads
+constexpr int SC_MAX_HD = 128;
+
+__device__ __forceinline__ float v4_load_f32(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float v4_load_f32(const uint16_t* p, size_t i) { return rv_bf16_to_f32(p[i]); }
+
+// Scores of blocks [c0, c0 + SC_CB) for one query row, by one warp. Lane l owns heads l and l + 32: each
+// dot is an ascending fold over the hd terms (separate multiply and add), exactly the host's; the head
+// sum is then an ascending f32 fold over the bf16 terms, evaluated redundantly by every lane.
+// qT: shared [hd][64] f32 (transposed: lanes read consecutive words); wsh: shared [64] f32;
+// stage: this warp's shared [SC_CB][hd] f32. Returns through out[SC_CB] (same value in every lane).
+template <class T>
+__device__ __forceinline__ void v4_score_blocks_warp(const float* __restrict__ qT, const float* __restrict__ wsh,
+                                                     float* __restrict__ stage, const T* __restrict__ kv, int c0,
+                                                     int n_comp, int heads, int hd, float (&out)[SC_CB]) {
+    const int lane = threadIdx.x & 31;
+    __syncwarp();
+    for (int i = lane; i < SC_CB * hd; i += 32) {
+        const int cb = i / hd, e = i - cb * hd;
+        stage[i] = c0 + cb < n_comp ? v4_load_f32(kv, (size_t)(c0 + cb) * hd + e) : 0.0f;
+    }
+    __syncwarp();
+    float dot[SC_CB][2];
+#pragma unroll
+    for (int cb = 0; cb < SC_CB; ++cb) dot[cb][0] = dot[cb][1] = 0.0f;
+    for (int i = 0; i < hd; i += 4) {
+        float4 kvv[SC_CB];
+#pragma unroll
+        for (int cb = 0; cb < SC_CB; ++cb) kvv[cb] = *reinterpret_cast<const float4*>(stage + cb * hd + i);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float q0 = qT[(i + e) * SC_MAX_HEADS + lane], q1 = qT[(i + e) * SC_MAX_HEADS + 32 + lane];
+#pragma unroll
+            for (int cb = 0; cb < SC_CB; ++cb) {
+                const float kvx = e == 0 ? kvv[cb].x : (e == 1 ? kvv[cb].y : (e == 2 ? kvv[cb].z : kvv[cb].w));
+                dot[cb][0] = __fadd_rn(dot[cb][0], __fmul_rn(q0, kvx));
+                dot[cb][1] = __fadd_rn(dot[cb][1], __fmul_rn(q1, kvx));
+            }
+        }
+    }
+    const float w0 = wsh[lane], w1 = wsh[32 + lane];
+#pragma unroll
+    for (int cb = 0; cb < SC_CB; ++cb) {
+        // bf16 store, relu, times the (signed) head weight, bf16 store
+        const float t0 = v4_rbf16(__fmul_rn(fmaxf(v4_rbf16(dot[cb][0]), 0.0f), w0));
+        const float t1 = v4_rbf16(__fmul_rn(fmaxf(v4_rbf16(dot[cb][1]), 0.0f), w1));
+        float acc = 0.0f;
+        const int n0 = heads < 32 ? heads : 32;
+        for (int hh = 0; hh < n0; ++hh) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, t0, hh));
+        for (int hh = 32; hh < heads; ++hh) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, t1, hh - 32));
+        out[cb] = v4_rbf16(acc);
+    }
+}
+
+// Stage one query row's index q transposed ([hd][64], zero beyond `heads`) and its head weights.
+template <class T>
+__device__ __forceinline__ void v4_stage_q(const T* __restrict__ q, const float* __restrict__ w, int heads, int hd,
+                                           float* __restrict__ qT, float* __restrict__ wsh) {
+    for (int i = threadIdx.x; i < hd * SC_MAX_HEADS; i += blockDim.x) {
+        const int e = i / SC_MAX_HEADS, hh = i - e * SC_MAX_HEADS;
+        qT[i] = hh < heads ? v4_load_f32(q, (size_t)hh * hd + e) : 0.0f;
+    }
+    for (int i = threadIdx.x; i < SC_MAX_HEADS; i += blockDim.x) wsh[i] = i < heads ? w[i] : 0.0f;
+}
+
+constexpr int SCK_THREADS = 256;
+constexpr int SCK_BLOCKS_PER_CTA = 256;   // blocks one CTA of the one-sequence scorer covers
+
+// Reference-layout scorer: f32 arrays, s query rows against one shared block array.
+__global__ void __launch_bounds__(SCK_THREADS) v4_score_blocks_kernel(const float* __restrict__ q,
+                                                                      const float* __restrict__ kv,
+                                                                      const float* __restrict__ w,
+                                                                      float* __restrict__ score, int n_comp, int heads,
+                                                                      int hd) {
+    extern __shared__ __align__(16) float sc_smem[];
+    float* qT = sc_smem;
+    float* wsh = qT + hd * SC_MAX_HEADS;
+    float* stage = wsh + SC_MAX_HEADS;
+    const int t = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    v4_stage_q(q + (size_t)t * heads * hd, w + (size_t)t * heads, heads, hd, qT, wsh);
+    __syncthreads();
+    const int c_begin = blockIdx.x * SCK_BLOCKS_PER_CTA;
+    const int c_end = min(n_comp, c_begin + SCK_BLOCKS_PER_CTA);
+    for (int c0 = c_begin + warp * SC_CB; c0 < c_end; c0 += (SCK_THREADS / 32) * SC_CB) {
+        float out[SC_CB];
+        v4_score_blocks_warp(qT, wsh, stage + warp * SC_CB * hd, kv, c0, n_comp, heads, hd, out);
+        if (lane < SC_CB && c0 + lane < c_end) {
+            float v = out[0];
+#pragma unroll
+            for (int cb = 1; cb < SC_CB; ++cb) v = lane == cb ? out[cb] : v;
+            score[(size_t)t * n_comp + c0 + lane] = v;
+        }
+    }
+}
+
+// Any shape: one thread per (t, c), everything sequential.
+__global__ void v4_score_blocks_serial_kernel(const float* __restrict__ q, const float* __restrict__ kv,
+                                              const float* __restrict__ w, float* __restrict__ score, int s,
+                                              int n_comp, int heads, int hd) {
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= (size_t)s * (size_t)n_comp) return;
+    const int t = (int)(id / (size_t)n_comp), c = (int)(id % (size_t)n_comp);
+    float acc = 0.0f;
+    for (int hh = 0; hh < heads; ++hh) {
+        const float* qh = q + ((size_t)t * heads + hh) * hd;
+        float dot = 0.0f;
+        for (int i = 0; i < hd; ++i) dot = __fadd_rn(dot, __fmul_rn(qh[i], kv[(size_t)c * hd + i]));
+        dot = fmaxf(v4_rbf16(dot), 0.0f);
+        acc = __fadd_rn(acc, v4_rbf16(__fmul_rn(dot, w[(size_t)t * heads + hh])));
+    }
+    score[id] = v4_rbf16(acc);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// batched selection: window row + positional or scored compressed columns, one CTA per sequence
+// ---------------------------------------------------------------------------------------------------
+constexpr int SEL_MAX_COMP = 16384;
+
+// f32 total order (sign-magnitude), the order the reference ranks by: -0.0 below +0.0.
+__device__ __forceinline__ uint32_t v4_total_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return b ^ ((uint32_t)((int32_t)b >> 31) | 0x80000000u);
+}
+
+struct SelSmem {
+    TkShared tk;
+    float wsh[SC_MAX_HEADS];
+};
+
+__global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const int32_t* __restrict__ pos,
+                                                               const uint16_t* __restrict__ index_q,
+                                                               const float* __restrict__ index_w,
+                                                               const uint16_t* __restrict__ index_kv,
+                                                               int32_t* __restrict__ sel,
+                                                               float* __restrict__ scores_out) {
+    extern __shared__ __align__(16) unsigned char sel_smem_raw[];
+    SelSmem& sh = *reinterpret_cast<SelSmem*>(sel_smem_raw);
+    float* qT = reinterpret_cast<float*>(sel_smem_raw + ((sizeof(SelSmem) + 15) & ~(size_t)15));
+    float* stage = qT + g.index_dim * SC_MAX_HEADS;
+    float* sc = stage + TK_WARPS * SC_CB * g.index_dim;
+    uint32_t* picked = reinterpret_cast<uint32_t*>(sc + g.max_comp);
+
+    const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int W = g.window, K = g.index_topk, p = pos[b];
+    int32_t* row = sel + (size_t)b * (W + K);
+    // the ring: oldest first once full, live slots then -1 before that
+    if (p >= W - 1) {
+        const int cut = p % W;
+        for (int j = tid; j < W; j += TK_THREADS) row[j] = j < W - 1 - cut ? cut + 1 + j : j - (W - 1 - cut);
+    } else {
+        for (int j = tid; j < W; j += TK_THREADS) row[j] = j <= p ? j : -1;
+    }
+    int n_comp = (p + 1) / g.ratio;
+    n_comp = n_comp < g.max_comp ? n_comp : g.max_comp;
+    if (n_comp <= K) {   // every closed block, in order
+        for (int c = tid; c < K; c += TK_THREADS) row[W + c] = c < n_comp ? W + c : -1;
+        return;
+    }
+    v4_stage_q(index_q + (size_t)b * g.index_heads * g.index_dim, index_w + (size_t)b * g.index_heads, g.index_heads,
+               g.index_dim, qT, sh.wsh);
+    __syncthreads();
+    const uint16_t* kv = index_kv + (size_t)b * g.max_comp * g.index_dim;
+    for (int c0 = warp * SC_CB; c0 < n_comp; c0 += TK_WARPS * SC_CB) {
+        float out[SC_CB];
+        v4_score_blocks_warp(qT, sh.wsh, stage + warp * SC_CB * g.index_dim, kv, c0, n_comp, g.index_heads,
+                             g.index_dim, out);
+        if (lane < SC_CB && c0 + lane < n_comp) {
+            float v = out[0];
+#pragma unroll
+            for (int cb = 1; cb < SC_CB; ++cb) v = lane == cb ? out[cb] : v;
+            sc[c0 + lane] = v;
+            if (scores_out) scores_out[(size_t)b * g.max_comp + c0 + lane] = v;
+        }
+    }
+    __syncthreads();
+    auto key_at = [&](int i) { return v4_total_key(sc[i]); };
+    uint32_t pivot, need;
+    tk_radix_select(key_at, n_comp, (uint32_t)K, sh.tk, pivot, need);
+    tk_compact(key_at, n_comp, (uint32_t)K, pivot, need, sh.tk, picked);
+    __syncthreads();
+    for (int j = tid; j < K; j += TK_THREADS) row[W + j] = W + (int32_t)picked[j];
+}
+
+// ---------------------------------------------------------------------------------------------------
+// sparse attention, CUDA cores: any shape, f32 or bf16 storage. One CTA per (query row, head).
+// ---------------------------------------------------------------------------------------------------
+constexpr int GA_THREADS = 256;
+constexpr int GA_ACC = 4;
+
+__device__ __forceinline__ void v4_store_out(float* o, size_t i, float v) { o[i] = v4_rbf16(v); }
+__device__ __forceinline__ void v4_store_out(uint16_t* o, size_t i, float v) { o[i] = rv_f32_to_bf16(v); }
+
+template <class T>
+__global__ void __launch_bounds__(GA_THREADS) v4_gather_attn_kernel(const T* __restrict__ q, const T* __restrict__ kv,
+                                                                    size_t kv_row_stride_per_t,
+                                                                    const float* __restrict__ sink,
+                                                                    const int* __restrict__ idxs, int h, int d,
+                                                                    int topk, float scale, T* __restrict__ o) {
+    extern __shared__ __align__(16) float ga_smem[];
+    float* qs = ga_smem;      // [d]
+    float* lg = ga_smem + d;  // [topk] logits, then softmax weights
+    __shared__ float red[GA_THREADS / 32];
+    __shared__ float bc;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int head = blockIdx.x, t = blockIdx.y;
+    const T* kvt = kv + (size_t)t * kv_row_stride_per_t;
+    const int* ix = idxs + (size_t)t * topk;
+    for (int i = tid; i < d; i += GA_THREADS) qs[i] = v4_load_f32(q, ((size_t)t * h + head) * d + i);
+    __syncthreads();
+    // logits: one warp per slot, lanes across the row
+    float mx = -INFINITY;
+    for (int j = warp; j < topk; j += GA_THREADS / 32) {
+        const int p = ix[j];
+        float l = -INFINITY;
+        if (p >= 0) {
+            float a = 0.0f;
+            for (int i = lane; i < d; i += 32) a = fmaf(qs[i], v4_load_f32(kvt, (size_t)p * d + i), a);
+            l = rv_warp_sum(a) * scale;
+        }
+        if (lane == 0) lg[j] = l;
+        mx = fmaxf(mx, l);
+    }
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int i = 1; i < GA_THREADS / 32; ++i) mx = fmaxf(mx, red[i]);
+    __syncthreads();
+    float ps = 0.0f;
+    for (int j = tid; j < topk; j += GA_THREADS) {
+        const float e = ix[j] >= 0 ? expf(lg[j] - mx) : 0.0f;
+        lg[j] = e;
+        ps += e;
+    }
+    ps = rv_warp_sum(ps);
+    if (lane == 0) red[warp] = ps;
+    __syncthreads();
+    if (tid == 0) {
+        float s = 0.0f;
+        for (int i = 0; i < GA_THREADS / 32; ++i) s += red[i];
+        // a query with every slot masked is made loud, not zero
+        bc = isfinite(mx) ? s + expf(sink[head] - mx) : NAN;
+    }
+    __syncthreads();
+    const float denom = bc;
+    float acc[GA_ACC];
+#pragma unroll
+    for (int c = 0; c < GA_ACC; ++c) acc[c] = 0.0f;
+    for (int j = 0; j < topk; ++j) {
+        const int p = ix[j];
+        if (p < 0) continue;
+        const float e = lg[j];
+#pragma unroll
+        for (int c = 0; c < GA_ACC; ++c) {
+            const int i = tid + c * GA_THREADS;
+            if (i < d) acc[c] = fmaf(e, v4_load_f32(kvt, (size_t)p * d + i), acc[c]);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < GA_ACC; ++c) {
+        const int i = tid + c * GA_THREADS;
+        if (i < d) v4_store_out(o, ((size_t)t * h + head) * d + i, acc[c] / denom);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// sparse attention, tensor cores: 64 heads x 512 dims, one CTA per sequence.
+//
+// The selected rows are gathered ONCE per sequence into shared memory (64-token tiles, two buffers,
+// cp.async) and serve every head twice: as K of S = q K^T and as V of O += P V. 16 warps:
+//   scores   warp (hg, tq): heads 16hg..+15 x tokens 16tq..+15, 32 k-steps of m16n8k16 over the 512 dims;
+//   softmax  8 threads per head over the tile's 64 tokens, running max / sum in registers;
+//   values   warp (hg, dq): heads 16hg..+15 x dims 128dq..+127, 4 k-steps over the tile's tokens.
+// Rows are 1024 B; the 16-byte chunk c of row r sits at chunk (c ^ (r & 7)) so that the eight rows of an
+// 8x8 ldmatrix tile fall in eight different bank groups.
+// ---------------------------------------------------------------------------------------------------
+constexpr int SA_H = 64, SA_D = 512, SA_TILE = 64, SA_THREADS = 512;
+constexpr int SA_ROW_BYTES = SA_D * 2;
+constexpr int SA_SQ = 0;                                   // [64 heads][1024 B]
+constexpr int SA_SK = SA_SQ + SA_H * SA_ROW_BYTES;         // 2 x [64 tokens][1024 B]
+constexpr int SA_SS = SA_SK + 2 * SA_TILE * SA_ROW_BYTES;  // f32 [64 heads][68]
+constexpr int SA_SS_LD = 68;
+constexpr int SA_SP = SA_SS + SA_H * SA_SS_LD * 4;         // bf16 [64 heads][64 tokens], chunk-swizzled
+constexpr int SA_FAC = SA_SP + SA_H * SA_TILE * 2;         // f32 [64] rescale of the running output
+constexpr int SA_INV = SA_FAC + SA_H * 4;                  // f32 [64] 1 / denominator
+constexpr int SA_IDX = SA_INV + SA_H * 4;                  // i32 [2][64] the tile's slots
+constexpr int SA_TOTAL = SA_IDX + 2 * SA_TILE * 4;
+
+__device__ __forceinline__ uint32_t v4_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void v4_cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void v4_ldsm4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void v4_ldsm4_t(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void v4_mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(const uint16_t* __restrict__ q,
+                                                                             const uint16_t* __restrict__ kv_cache,
+                                                                             size_t kv_rows,
+                                                                             const float* __restrict__ sink,
+                                                                             const int32_t* __restrict__ sel, int cols,
+                                                                             float scale_log2,
+                                                                             uint16_t* __restrict__ out) {
+    extern __shared__ __align__(1024) unsigned char sa_smem[];
+    const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t sbase = v4_smem_u32(sa_smem);
+    float* sS = reinterpret_cast<float*>(sa_smem + SA_SS);
+    float* sFac = reinterpret_cast<float*>(sa_smem + SA_FAC);
+    float* sInv = reinterpret_cast<float*>(sa_smem + SA_INV);
+    int32_t* sIdx = reinterpret_cast<int32_t*>(sa_smem + SA_IDX);
+    const uint16_t* kvb = kv_cache + (size_t)b * kv_rows * SA_D;
+    const int32_t* ix = sel + (size_t)b * cols;
+    const int n_tiles = (cols + SA_TILE - 1) / SA_TILE;
+
+    // chunk (row, c) -> byte offset inside a [rows][1024 B] operand
+    auto swz = [](int row, int c) { return row * SA_ROW_BYTES + ((c ^ (row & 7)) << 4); };
+
+    auto gather = [&](int t, int buf) {
+        const uint32_t dst0 = sbase + SA_SK + buf * SA_TILE * SA_ROW_BYTES;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int ch = tid + it * SA_THREADS, row = ch >> 6, c = ch & 63;
+            const int j = t * SA_TILE + row;
+            const int p = j < cols ? ix[j] : -1;
+            if (c == 0) sIdx[buf * SA_TILE + row] = p;
+            if (p >= 0) v4_cp_async16(dst0 + swz(row, c), kvb + (size_t)p * SA_D + c * 8);
+            else *reinterpret_cast<uint4*>(sa_smem + SA_SK + buf * SA_TILE * SA_ROW_BYTES + swz(row, c)) = make_uint4(0, 0, 0, 0);
+        }
+    };
+
+    // q of this sequence, then the first tile
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int ch = tid + it * SA_THREADS, row = ch >> 6, c = ch & 63;
+        v4_cp_async16(sbase + SA_SQ + swz(row, c), q + ((size_t)b * SA_H + row) * SA_D + c * 8);
+    }
+    gather(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    // softmax state of head (tid >> 3), replicated in its 8 threads
+    float m_run = -INFINITY, l_run = 0.0f;
+    // output accumulators of warp (hg, dq): 16 n-tiles of 8 dims
+    float acc[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+
+    const int hg = warp & 3, wq = warp >> 2;   // wq = token quarter (scores) / dim quarter (values)
+    const int mi = lane >> 3, l7 = lane & 7;
+
+    for (int t = 0; t < n_tiles; ++t) {
+        const int buf = t & 1;
+        if (t + 1 < n_tiles) {
+            gather(t + 1, buf ^ 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const uint32_t sK = sbase + SA_SK + buf * SA_TILE * SA_ROW_BYTES;
+
+        // ---- scores: S[16 heads][16 tokens] per warp
+        {
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            const int arow = 16 * hg + ((mi & 1) << 3) + l7;
+            const int brow = 16 * wq + ((mi >> 1) << 3) + l7;
+#pragma unroll 4
+            for (int ks = 0; ks < SA_D / 16; ++ks) {
+                uint32_t a[4], bb[4];
+                v4_ldsm4(sbase + SA_SQ + swz(arow, 2 * ks + (mi >> 1)), a);
+                v4_ldsm4(sK + swz(brow, 2 * ks + (mi & 1)), bb);
+                v4_mma_bf16(s0, a, bb[0], bb[1]);
+                v4_mma_bf16(s1, a, bb[2], bb[3]);
+            }
+            const int r0 = 16 * hg + (lane >> 2), c0 = 16 * wq + (lane & 3) * 2;
+            *reinterpret_cast<float2*>(sS + r0 * SA_SS_LD + c0) = make_float2(s0[0] * scale_log2, s0[1] * scale_log2);
+            *reinterpret_cast<float2*>(sS + (r0 + 8) * SA_SS_LD + c0) = make_float2(s0[2] * scale_log2, s0[3] * scale_log2);
+            *reinterpret_cast<float2*>(sS + r0 * SA_SS_LD + c0 + 8) = make_float2(s1[0] * scale_log2, s1[1] * scale_log2);
+            *reinterpret_cast<float2*>(sS + (r0 + 8) * SA_SS_LD + c0 + 8) = make_float2(s1[2] * scale_log2, s1[3] * scale_log2);
+        }
+        __syncthreads();
+
+        // ---- softmax over the tile: head = tid / 8, tokens 8 * (tid % 8) .. +7
+        {
+            const int head = tid >> 3, part = tid & 7;
+            float sv[8];
+            const float4 x0 = *reinterpret_cast<const float4*>(sS + head * SA_SS_LD + part * 8);
+            const float4 x1 = *reinterpret_cast<const float4*>(sS + head * SA_SS_LD + part * 8 + 4);
+            sv[0] = x0.x; sv[1] = x0.y; sv[2] = x0.z; sv[3] = x0.w; sv[4] = x1.x; sv[5] = x1.y; sv[6] = x1.z; sv[7] = x1.w;
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (sIdx[buf * SA_TILE + part * 8 + j] < 0) sv[j] = -INFINITY;
+                tmax = fmaxf(tmax, sv[j]);
+            }
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+            const float m_new = fmaxf(m_run, tmax);
+            const float fac = m_new == -INFINITY ? 1.0f : exp2f(m_run - m_new);
+            uint32_t pk[4];
+            float psum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const float p0 = m_new == -INFINITY ? 0.0f : exp2f(sv[j] - m_new);
+                const float p1 = m_new == -INFINITY ? 0.0f : exp2f(sv[j + 1] - m_new);
+                const uint16_t b0 = rv_f32_to_bf16(p0), b1 = rv_f32_to_bf16(p1);
+                psum += rv_bf16_to_f32(b0) + rv_bf16_to_f32(b1);   // the sum of what the value product sees
+                pk[j >> 1] = (uint32_t)b0 | ((uint32_t)b1 << 16);
+            }
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 4);
+            l_run = l_run * fac + psum;
+            m_run = m_new;
+            *reinterpret_cast<uint4*>(sa_smem + SA_SP + head * (SA_TILE * 2) + ((part ^ (head & 7)) << 4)) =
+                make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            if (part == 0) sFac[head] = fac;
+        }
+        __syncthreads();
+
+        // ---- values: O[16 heads][128 dims] += P[16 heads][64 tokens] V[64 tokens][128 dims]
+        {
+            const float f0 = sFac[16 * hg + (lane >> 2)], f1 = sFac[16 * hg + (lane >> 2) + 8];
+            if (f0 != 1.0f || f1 != 1.0f) {
+#pragma unroll
+                for (int n = 0; n < 16; ++n) { acc[n][0] *= f0; acc[n][1] *= f0; acc[n][2] *= f1; acc[n][3] *= f1; }
+            }
+            const int prow = 16 * hg + ((mi & 1) << 3) + l7;
+#pragma unroll
+            for (int ks = 0; ks < SA_TILE / 16; ++ks) {
+                uint32_t a[4];
+                v4_ldsm4(sbase + SA_SP + prow * (SA_TILE * 2) + (((2 * ks + (mi >> 1)) ^ (prow & 7)) << 4), a);
+                const int vrow = 16 * ks + ((mi & 1) << 3) + l7;
+#pragma unroll
+                for (int np = 0; np < 8; ++np) {
+                    uint32_t bb[4];
+                    v4_ldsm4_t(sK + swz(vrow, 16 * wq + 2 * np + (mi >> 1)), bb);
+                    v4_mma_bf16(acc[2 * np], a, bb[0], bb[1]);
+                    v4_mma_bf16(acc[2 * np + 1], a, bb[2], bb[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // the sink joins the denominator only, shifted by the same running max
+    {
+        const int head = tid >> 3;
+        if ((tid & 7) == 0) {
+            const float l = l_run + exp2f(sink[head] * 1.4426950408889634f - m_run);
+            sInv[head] = m_run == -INFINITY ? NAN : 1.0f / l;
+        }
+    }
+    __syncthreads();
+    {
+        const int r0 = 16 * hg + (lane >> 2);
+        const float i0 = sInv[r0], i1 = sInv[r0 + 8];
+        uint16_t* o0 = out + ((size_t)b * SA_H + r0) * SA_D + 128 * wq + (lane & 3) * 2;
+        uint16_t* o1 = o0 + 8 * SA_D;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            const uint32_t v0 = (uint32_t)rv_f32_to_bf16(acc[n][0] * i0) | ((uint32_t)rv_f32_to_bf16(acc[n][1] * i0) << 16);
+            const uint32_t v1 = (uint32_t)rv_f32_to_bf16(acc[n][2] * i1) | ((uint32_t)rv_f32_to_bf16(acc[n][3] * i1) << 16);
+            *reinterpret_cast<uint32_t*>(o0 + 8 * n) = v0;
+            *reinterpret_cast<uint32_t*>(o1 + 8 * n) = v1;
+        }
+    }
+}
+
+static int v4_check_geom(const V4Geom* g, int n_seqs) {
+    if (!g || n_seqs <= 0) return 1001;
+    if (g->n_heads <= 0 || g->head_dim <= 0 || g->window <= 0 || g->index_heads <= 0 || g->index_dim <= 0 ||
+        g->index_topk <= 0 || g->ratio <= 1 || g->max_comp <= 0)
+        return 1001;
+    return 0;
+}
+
+}  // namespace
+
+RIVOLI_API int rivoli_act_quant_f4_rotated(float* x, int rows, int d, void* stream) {
+    if (rows <= 0 || d <= 0) return 1001;
+    if (d > V4_ROT_MAX) return 1002;
+    if (d & (d - 1)) return 1003;
+    if (d % 32) return 1004;
+    rv_drain_error();
+    v4_spread_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(x, d);
+    return rv_launch_status();
+}
+
+RIVOLI_API int rivoli_index_score_blocks(const float* q, const float* kv, const float* w, float* score, int s,
+                                         int n_comp, int heads, int hd, void* stream) {
+    if (s <= 0 || heads <= 0 || hd <= 0) return 1001;
+    if (n_comp <= 0) return 1005;   // an empty compressed region has no score row to write
+    rv_drain_error();
+    cudaStream_t st = (cudaStream_t)stream;
+    if (heads <= SC_MAX_HEADS && hd <= SC_MAX_HD && hd % 4 == 0 && s <= 65535) {
+        const size_t smem = ((size_t)hd * SC_MAX_HEADS + SC_MAX_HEADS + (size_t)(SCK_THREADS / 32) * SC_CB * hd) * sizeof(float);
+        cudaFuncSetAttribute(v4_score_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        dim3 grid((unsigned)((n_comp + SCK_BLOCKS_PER_CTA - 1) / SCK_BLOCKS_PER_CTA), (unsigned)s);
+        v4_score_blocks_kernel<<<grid, SCK_THREADS, smem, st>>>(q, kv, w, score, n_comp, heads, hd);
+    } else {
+        const size_t total = (size_t)s * (size_t)n_comp;
+        v4_score_blocks_serial_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(q, kv, w, score, s, n_comp, heads, hd);
+    }
+    return rv_launch_status();
+}
+
+RIVOLI_API int rivoli_gather_attn_shared_kv(const float* q, const float* kv, const float* sink, const int* idxs, int m,
+                                            int h, int d, int topk, float scale, float* o, void* stream) {
+    if (m <= 0 || h <= 0 || d <= 0 || topk <= 0) return 1001;
+    if (d > GA_THREADS * GA_ACC) return 1002;   // dims past the per-thread accumulators would never be written
+    const size_t smem = ((size_t)d + (size_t)topk) * sizeof(float);
+    if (smem + sizeof(float) * (GA_THREADS + 2) > 65536) return 1006;
+    rv_drain_error();
+    cudaFuncSetAttribute(v4_gather_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    v4_gather_attn_kernel<float><<<dim3((unsigned)h, (unsigned)m), GA_THREADS, smem, (cudaStream_t)stream>>>(
+        q, kv, 0, sink, idxs, h, d, topk, scale, o);
+    return rv_launch_status();
+}
+
+RIVOLI_API int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const int32_t* pos, const uint16_t* index_q,
+                                            const float* index_w, const uint16_t* index_kv, int32_t* sel,
+                                            float* scores, void* stream) {
+    if (int rc = v4_check_geom(g, n_seqs)) return rc;
+    if (g->index_heads > SC_MAX_HEADS || g->index_dim > SC_MAX_HD || g->max_comp > SEL_MAX_COMP || g->index_topk > 4096)
+        return 1002;
+    if (g->index_dim % 32) return 1004;
+    const size_t smem = ((sizeof(SelSmem) + 15) & ~(size_t)15) +
+                        ((size_t)g->index_dim * SC_MAX_HEADS + (size_t)TK_WARPS * SC_CB * g->index_dim + (size_t)g->max_comp +
+                         (size_t)g->index_topk) * 4;
+    if (smem > 227 * 1024) return 1002;
+    rv_drain_error();
+    cudaFuncSetAttribute(v4_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    v4_select_kernel<<<(unsigned)n_seqs, TK_THREADS, smem, (cudaStream_t)stream>>>(*g, pos, index_q, index_w, index_kv, sel,
+                                                                                   scores);
+    return rv_launch_status();
+}
+
+RIVOLI_API int rivoli_v4_sparse_attend_bf16(const V4Geom* g, int n_seqs, const uint16_t* q, const uint16_t* kv_cache,
+                                            const float* sink, const int32_t* sel, int cols, uint16_t* out,
+                                            int force_simt, void* stream) {
+    if (int rc = v4_check_geom(g, n_seqs)) return rc;
+    if (cols <= 0) return 1001;
+    if (g->head_dim > GA_THREADS * GA_ACC) return 1002;
+    const size_t kv_rows = (size_t)g->window + (size_t)g->max_comp;
+    rv_drain_error();
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!force_simt && g->n_heads == SA_H && g->head_dim == SA_D) {
+        cudaFuncSetAttribute(v4_sparse_attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SA_TOTAL);
+        v4_sparse_attend_mma_kernel<<<(unsigned)n_seqs, SA_THREADS, SA_TOTAL, st>>>(
+            q, kv_cache, kv_rows, sink, sel, cols, g->softmax_scale * 1.4426950408889634f, out);
+        return rv_launch_status();
+    }
+    const size_t smem = ((size_t)g->head_dim + (size_t)cols) * sizeof(float);
+    if (smem > 200 * 1024) return 1006;
+    if (n_seqs > 65535) return 1002;
+    cudaFuncSetAttribute(v4_gather_attn_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    v4_gather_attn_kernel<uint16_t><<<dim3((unsigned)g->n_heads, (unsigned)n_seqs), GA_THREADS, smem, st>>>(
+        q, kv_cache, kv_rows * (size_t)g->head_dim, sink, sel, g->n_heads, g->head_dim, cols, g->softmax_scale, out);
+    return rv_launch_status();
+}

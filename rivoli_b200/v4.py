@@ -1,0 +1,40 @@
+"""Caller-side sequencing of the V4 cousin path's decode step: selection rows, then sparse attention.
+
+Mirrors what ``crates/engine/src/v4/blocksel.rs:361-417`` (scored selection) and
+``crates/engine/src/v4/attn.rs`` (the gather-attention call) do per layer, batched over sequences and
+over bf16 storage. Device memory is owned here through torch; every launch goes through the C ABI.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import backend as be
+
+
+class V4DecodeLayer:
+    """One layer's ring + compressed KV, the indexer's compressed rows, and the two launches of a step."""
+
+    def __init__(self, g: be.V4Geom, n_seqs: int, device="cuda"):
+        self.g, self.B = g, n_seqs
+        dev = torch.device(device)
+        self.kv_rows = g.window + g.max_comp
+        self.kv_cache = torch.zeros((n_seqs, self.kv_rows, g.head_dim), dtype=torch.uint16, device=dev)
+        self.index_kv = torch.zeros((n_seqs, g.max_comp, g.index_dim), dtype=torch.uint16, device=dev)
+        self.sink = torch.zeros(g.n_heads, dtype=torch.float32, device=dev)
+        self.cols = g.window + g.index_topk
+        self.sel = torch.full((n_seqs, self.cols), -1, dtype=torch.int32, device=dev)
+        self.out = torch.zeros((n_seqs, g.n_heads, g.head_dim), dtype=torch.uint16, device=dev)
+
+    def select(self, pos, index_q, index_w, scores=None, stream=None):
+        be.launch_v4_select_blocks_bf16(self.g, self.B, pos, index_q, index_w, self.index_kv, self.sel, scores, stream)
+        return self.sel
+
+    def attend(self, q, force_simt: bool = False, stream=None):
+        be.launch_v4_sparse_attend_bf16(self.g, self.B, q, self.kv_cache, self.sink, self.sel, self.cols, self.out,
+                                        force_simt, stream)
+        return self.out
+
+    def step(self, pos, q, index_q, index_w, stream=None):
+        """Selection then attention for one decode step; returns the bf16 output [B, H, D]."""
+        self.select(pos, index_q, index_w, None, stream)
+        return self.attend(q, False, stream)

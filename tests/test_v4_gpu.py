@@ -1,0 +1,208 @@
+"""GPU parity of the V4 cousin path (spread, block scorer, selection rows, sparse attention with sink)
+against the CPU oracle, through the C ABI. Bit-exact for the spread, the scores and the selected indices;
+the reference's own bar (error <= 1/128 of the largest expected element) for the attention output."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from oracle import oracle as orc
+from oracle import v4_workload as wl
+
+
+def _be():
+    from rivoli_b200 import backend as be
+    return be
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("d", [32, 128, 256])
+def test_spread_is_bit_identical(d):
+    be = _be()
+    rng = np.random.default_rng(d)
+    x = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((97, d)).astype(np.float32)))
+    # rows scaled across sixty binades so the power-of-two scale is exercised widely
+    x *= (2.0 ** (np.arange(97) % 60 - 30)).astype(np.float32)[:, None]
+    x = orc.bf16_to_f32(orc.f32_to_bf16(x))
+    x[5] = 0.0
+    rc, want = orc.v4_spread(x, d)
+    assert rc == 0
+    t = dev(x)
+    be.launch_act_quant_f4_rotated(t, 97, d)
+    assert np.array_equal(bits(t.cpu().numpy()), bits(want))
+
+
+def test_spread_and_score_guards():
+    be = _be()
+    t = torch.zeros(1024, device="cuda")
+    for rows, d, code in [(0, 128, 1001), (1, 512, 1002), (1, 96, 1003), (1, 16, 1004)]:
+        with pytest.raises(be.BackendError) as e:
+            be.launch_act_quant_f4_rotated(t, rows, d)
+        assert e.value.code == code
+    with pytest.raises(be.BackendError) as e:
+        be.launch_index_score_blocks(t, t, t, t, 0, 1, 1, 1)
+    assert e.value.code == 1001
+    with pytest.raises(be.BackendError) as e:
+        be.launch_index_score_blocks(t, t, t, t, 1, 0, 1, 1)
+    assert e.value.code == 1005
+    i = torch.zeros(8, dtype=torch.int32, device="cuda")
+    for d, topk, code in [(1025, 8, 1002), (1024, 1 << 20, 1006), (0, 8, 1001)]:
+        with pytest.raises(be.BackendError) as e:
+            be.launch_gather_attn_shared_kv(t, t, t, i, 1, 1, d, topk, 1.0, t)
+        assert e.value.code == code
+
+
+@pytest.mark.parametrize("s,n_comp,heads,hd", [(1, 1, 64, 128), (3, 37, 64, 128), (2, 301, 5, 32), (2, 19, 70, 24),
+                                               (1, 1000, 33, 64)])
+def test_block_scores_are_bit_identical(s, n_comp, heads, hd):
+    be = _be()
+    rng = np.random.default_rng(n_comp)
+    if hd % 32 == 0:
+        q = orc.v4_spread(orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((s * heads, hd)).astype(np.float32))), hd)[1]
+        kv = orc.v4_spread(orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((n_comp, hd)).astype(np.float32))), hd)[1]
+    else:
+        q = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((s * heads, hd)).astype(np.float32)))
+        kv = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((n_comp, hd)).astype(np.float32)))
+    w = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((s, heads)).astype(np.float32)))
+    if (s, n_comp) == (1, 1):  # the f32-accumulate case: 1 + 63 * 2^-9 rounds once to 1.125
+        q[:], kv[:], w[:] = 0, 0, 1
+        kv[0, 0] = 1.0
+        q[:, 0] = 2.0 ** -9
+        q[0, 0] = 1.0
+    rc, want = orc.v4_index_score_blocks(q, kv, w, s, n_comp, heads, hd)
+    assert rc == 0
+    out = torch.zeros((s, n_comp), device="cuda")
+    be.launch_index_score_blocks(dev(q), dev(kv), dev(w), out, s, n_comp, heads, hd)
+    got = out.cpu().numpy()
+    assert np.array_equal(bits(got), bits(want))
+    if (s, n_comp) == (1, 1):
+        assert got[0, 0] == np.float32(1.125)
+
+
+def test_unspread_inputs_score_bit_identically():
+    """Full-precision bf16 inputs round at every step of the fold: the order and the unfused ops matter."""
+    be = _be()
+    rng = np.random.default_rng(2)
+    s, n_comp, heads, hd = 2, 200, 64, 128
+    q = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((s * heads, hd)).astype(np.float32)))
+    kv = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((n_comp, hd)).astype(np.float32)))
+    w = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((s, heads)).astype(np.float32)))
+    rc, want = orc.v4_index_score_blocks(q, kv, w, s, n_comp, heads, hd)
+    out = torch.zeros((s, n_comp), device="cuda")
+    be.launch_index_score_blocks(dev(q), dev(kv), dev(w), out, s, n_comp, heads, hd)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+
+
+def test_gather_attn_reference_layout():
+    be = _be()
+    rng = np.random.default_rng(9)
+    m, h, d, n, topk = 3, 8, 512, 300, 160
+    bf = lambda a: orc.bf16_to_f32(orc.f32_to_bf16(a.astype(np.float32)))
+    q, kv = bf(rng.standard_normal((m, h, d))), bf(rng.standard_normal((n, d)))
+    sink = rng.standard_normal(h).astype(np.float32)
+    idx = np.stack([rng.permutation(n)[:topk] for _ in range(m)]).astype(np.int32)
+    idx[0, ::7] = -1
+    idx[2, :] = -1
+    rc, want = orc.v4_sparse_attn(q, kv, sink, idx, m, h, d, topk, d ** -0.5)
+    out = torch.zeros((m, h, d), device="cuda")
+    be.launch_gather_attn_shared_kv(dev(q), dev(kv), dev(sink), dev(idx), m, h, d, topk, d ** -0.5, out)
+    got = out.cpu().numpy()
+    assert np.all(np.isnan(got[2])) and np.all(np.isnan(want[2]))
+    ok, worst = wl.attend_close(orc.f32_to_bf16(got[:2]), orc.f32_to_bf16(want[:2]))
+    assert ok, worst
+    assert np.array_equal(bits(got[:2]), bits(orc.bf16_to_f32(orc.f32_to_bf16(got[:2]))))  # stored on the bf16 grid
+
+
+def _run_step(g, inp, force_simt=False, want_scores=True):
+    be = _be()
+    from rivoli_b200.v4 import V4DecodeLayer
+    B = inp["pos"].size
+    bg = be.V4Geom(*[getattr(g, n) for n, _ in orc.V4Geom._fields_])
+    layer = V4DecodeLayer(bg, B)
+    layer.kv_cache.copy_(dev(inp["kv_cache"]))
+    layer.index_kv.copy_(dev(inp["ikv"]))
+    layer.sink.copy_(dev(inp["sink"]))
+    scores = torch.zeros((B, g.max_comp), device="cuda") if want_scores else None
+    layer.select(dev(inp["pos"]), dev(inp["iq"]), dev(inp["iw"]), scores)
+    layer.attend(dev(inp["q"]), force_simt)
+    torch.cuda.synchronize()
+    return layer.sel.cpu().numpy(), layer.out.cpu().numpy(), (scores.cpu().numpy() if want_scores else None)
+
+
+def test_batched_step_small_shapes():
+    g = wl.make_geom(n_heads=4, head_dim=64, window=8, index_heads=4, index_dim=32, index_topk=4, max_comp=16)
+    pos = np.array([0, 5, 30, 63, 7, 18], np.int32)
+    inp = wl.make_inputs(g, pos.size, pos, seed=1)
+    want_sel, want_out, want_sc = orc.v4_decode_step_bf16(g, pos, inp["q"], inp["kv_cache"], inp["sink"], inp["iq"],
+                                                          inp["iw"], inp["ikv"], want_scores=True)
+    sel, out, sc = _run_step(g, inp)
+    assert np.array_equal(sel, want_sel)
+    for b in range(pos.size):
+        n_comp = (pos[b] + 1) // g.ratio
+        if n_comp > g.index_topk:
+            assert np.array_equal(bits(sc[b, :n_comp]), bits(want_sc[b, :n_comp]))
+    ok, worst = wl.attend_close(out, want_out)
+    assert ok, worst
+
+
+@pytest.mark.parametrize("force_simt", [False, True])
+def test_batched_step_model_shapes(force_simt):
+    g = wl.make_geom(max_comp=640, index_topk=96)
+    pos = np.array([3, 126, 127, 500, 2559, 1023, 1500, 390], np.int32)  # ring filling / full; positional and scored
+    inp = wl.make_inputs(g, pos.size, pos, seed=4)
+    inp["iw"][1] = np.abs(inp["iw"][1])
+    want_sel, want_out, want_sc = orc.v4_decode_step_bf16(g, pos, inp["q"], inp["kv_cache"], inp["sink"], inp["iq"],
+                                                          inp["iw"], inp["ikv"], want_scores=True)
+    sel, out, sc = _run_step(g, inp, force_simt)
+    assert np.array_equal(sel, want_sel)
+    for b in range(pos.size):
+        n_comp = (pos[b] + 1) // g.ratio
+        if n_comp > g.index_topk:
+            assert np.array_equal(bits(sc[b, :n_comp]), bits(want_sc[b, :n_comp]))
+    ok, worst = wl.attend_close(out, want_out)
+    assert ok, worst
+
+
+def test_tie_heavy_scores_select_the_lower_blocks():
+    """All-zero head weights make every score +0: the selection must be the first index_topk blocks."""
+    g = wl.make_geom(max_comp=640, index_topk=96)
+    pos = np.array([2559, 2001], np.int32)
+    inp = wl.make_inputs(g, 2, pos, seed=6)
+    inp["iw"][:] = 0.0
+    sel, _, _ = _run_step(g, inp, want_scores=False)
+    for b in range(2):
+        assert sel[b, g.window:].tolist() == list(range(g.window, g.window + g.index_topk))
+
+
+def test_fully_masked_row_is_nan_and_masked_slots_are_ignored():
+    be = _be()
+    g = wl.make_geom(max_comp=64, index_topk=32)
+    bg = be.V4Geom(*[getattr(g, n) for n, _ in orc.V4Geom._fields_])
+    B, cols = 3, g.window + g.index_topk
+    inp = wl.make_inputs(g, B, np.array([200, 200, 200], np.int32), seed=8)
+    rng = np.random.default_rng(0)
+    sel = np.stack([rng.permutation(g.window + 50)[:cols] for _ in range(B)]).astype(np.int32)
+    sel[0, :] = -1
+    sel[1, 1::2] = -1
+    sel[2, :cols - 3] = -1
+    want = np.zeros((B, g.n_heads, g.head_dim), np.uint16)
+    for b in range(B):
+        rc, o = orc.v4_sparse_attn(orc.bf16_to_f32(inp["q"][b]), orc.bf16_to_f32(inp["kv_cache"][b]), inp["sink"],
+                                   sel[b], 1, g.n_heads, g.head_dim, cols, g.softmax_scale)
+        want[b] = orc.f32_to_bf16(o[0])
+    for force in (False, True):
+        out = torch.zeros((B, g.n_heads, g.head_dim), dtype=torch.uint16, device="cuda")
+        be.launch_v4_sparse_attend_bf16(bg, B, dev(inp["q"]), dev(inp["kv_cache"]), dev(inp["sink"]), dev(sel), cols,
+                                        out, force)
+        got = out.cpu().numpy()
+        assert np.all(np.isnan(orc.bf16_to_f32(got[0])))
+        ok, worst = wl.attend_close(got[1:], want[1:])
+        assert ok, (force, worst)
