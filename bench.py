@@ -36,6 +36,10 @@ WORKLOADS = {
     # bound leaves a sequence 128 tokens to grow inside the 32,768-token limit of the tensor-core selection
     "cfg5": dict(B=32, ctx_lo=512, ctx_hi=32640, layers=78, n_heads=64, index_heads=32, index_dim=128, page_tokens=64,
                  top_k=2048, seed=4),
+    # the V4 cousin path (a next-row measurement, not the headline): MQA over one shared 512-wide bf16 entry per
+    # position, 128-slot ring + 512 scored compressed blocks of a ratio-4 compressor, 64-head block indexer
+    "v4": dict(B=128, ctx=8192, n_heads=64, head_dim=512, window=128, index_heads=64, index_dim=128, index_topk=512,
+               ratio=4, seed=5),
 }
 KV_LORA, ROPE = 512, 64
 # dram__bytes_read.sum + dram__bytes_write.sum per sequence of the cfg3 shape, from the ncu capture
@@ -524,6 +528,120 @@ def run_churn(args):
     print(json.dumps(line), flush=True)
 
 
+def run_v4(args):
+    """One decode step of the V4 cousin path per "step": block scores + exact top-k selection rows, then sparse
+    MQA attention with the sink, for every sequence of the batch. Prints one JSON line (same keys as the
+    headline line; the CPU arm is the oracle on a bounded sample of the same sequences)."""
+    import torch
+    from oracle import oracle as orc
+    from oracle import v4_workload as wl
+    from rivoli_b200 import backend as be
+    from rivoli_b200.v4 import V4DecodeLayer
+    w = WORKLOADS["v4"]
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    B, max_comp = w["B"], w["ctx"] // w["ratio"]
+    og = wl.make_geom(n_heads=w["n_heads"], head_dim=w["head_dim"], window=w["window"], index_heads=w["index_heads"],
+                      index_dim=w["index_dim"], index_topk=w["index_topk"], ratio=w["ratio"], max_comp=max_comp)
+    g = be.V4Geom(*[getattr(og, n) for n, _ in orc.V4Geom._fields_])
+    pos = np.full(B, w["ctx"] - 1, np.int32)
+    n_cpu = 2                                             # sequences the CPU arm and the parity check cover
+    host = wl.make_inputs(og, n_cpu, pos[:n_cpu], seed=w["seed"])
+    layer = V4DecodeLayer(g, B, device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(w["seed"])
+    rnd = lambda *shape: torch.randn(shape, generator=gen, device=device).to(torch.bfloat16).view(torch.uint16)
+    layer.kv_cache.copy_(rnd(B, layer.kv_rows, g.head_dim))
+    spread = torch.randn((B * max_comp, g.index_dim), generator=gen, device=device).to(torch.bfloat16).float()
+    be.launch_act_quant_f4_rotated(spread, B * max_comp, g.index_dim)
+    layer.index_kv.copy_(spread.to(torch.bfloat16).view(torch.uint16).view(B, max_comp, g.index_dim))
+    iq = torch.randn((B * g.index_heads, g.index_dim), generator=gen, device=device).to(torch.bfloat16).float()
+    be.launch_act_quant_f4_rotated(iq, B * g.index_heads, g.index_dim)
+    iq = iq.to(torch.bfloat16).view(torch.uint16).view(B, g.index_heads, g.index_dim).contiguous()
+    iw = (torch.randn((B, g.index_heads), generator=gen, device=device) * g.index_heads ** -0.5).to(torch.bfloat16).float()
+    q = rnd(B, g.n_heads, g.head_dim)
+    layer.sink.copy_(torch.randn(g.n_heads, generator=gen, device=device))
+    # the first n_cpu sequences carry the oracle's inputs so the run checks itself
+    for name, dst in (("kv_cache", layer.kv_cache), ("ikv", layer.index_kv), ("iq", iq), ("q", q)):
+        dst[:n_cpu].copy_(torch.from_numpy(host[name]).to(device))
+    iw[:n_cpu].copy_(torch.from_numpy(host["iw"]).to(device))
+    layer.sink.copy_(torch.from_numpy(host["sink"]).to(device))
+    d_pos = torch.from_numpy(pos).to(device)
+    t0 = time.perf_counter()
+    want_sel, want_out = orc.v4_decode_step_bf16(og, pos[:n_cpu], host["q"], host["kv_cache"], host["sink"], host["iq"],
+                                                 host["iw"], host["ikv"])
+    cpu_s = time.perf_counter() - t0
+    layer.step(d_pos, q, iq, iw)
+    torch.cuda.synchronize(device)
+    assert np.array_equal(layer.sel[:n_cpu].cpu().numpy(), want_sel), "selection rows differ from the oracle"
+    ok, worst = wl.attend_close(layer.out[:n_cpu].cpu().numpy(), want_out)
+    assert ok, f"attention differs from the oracle: {worst}"
+
+    sampler = ClockSampler(0)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    t_sel = t_att = 0.0
+    for it in range(args.warmup + args.steps):
+        if it == args.warmup:
+            sampler.start()
+            sampler.mark()
+        ev[0].record()
+        layer.select(d_pos, iq, iw)
+        ev[1].record()
+        layer.attend(q)
+        ev[2].record()
+        torch.cuda.synchronize(device)
+        if it >= args.warmup:
+            t_sel += ev[0].elapsed_time(ev[1])
+            t_att += ev[1].elapsed_time(ev[2])
+    sampler.mark()
+    clocks = sampler.stop()
+    assert not layer.refolded.any().item(), "the integer scorer handed spread rows to the ordered fold"
+    t_sel, t_att = t_sel / args.steps, t_att / args.steps
+    # end to end: pinned host inputs up, bf16 output down, every step
+    h_in = [t.cpu().pin_memory() for t in (d_pos, q, iq, iw)]
+    h_out = torch.empty(layer.out.shape, dtype=torch.uint16).pin_memory()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_e2e = max(3, args.steps // 4)
+    e0.record()
+    for _ in range(n_e2e):
+        dp, dq, diq, diw = (t.to(device, non_blocking=True) for t in h_in)
+        h_out.copy_(layer.step(dp, dq, diq, diw), non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize(device)
+    e2e_ms = e0.elapsed_time(e1) / n_e2e
+    ms = t_sel + t_att
+    peaks = {}
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peaks = json.load(open(pk))
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    cols = g.window + g.index_topk
+    att_bytes = B * (cols * g.head_dim * 2 + 2 * g.n_heads * g.head_dim * 2 + cols * 4)
+    sel_bytes = B * (max_comp * g.index_dim * 2 + g.index_heads * g.index_dim * 2 + cols * 4)
+    dom, dom_ms, dom_bytes = ("sparse_attend", t_att, att_bytes) if t_att >= t_sel else ("select_blocks", t_sel, sel_bytes)
+    ach = dom_bytes / (dom_ms * 1e-3) / 1e9
+    line = {"metric": "V4 sparse-attention decode layer-steps/s (batch x ctx)", "value": 1e3 / ms, "unit": "layer-steps/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 accumulate; block scores exact f32 folds",
+            "data": "synthetic",
+            "config": {"workload": f"v4: batch {B} x context {w['ctx']}, {g.n_heads} heads x {g.head_dim}, ring {g.window} + "
+                                   f"top-{g.index_topk} of {max_comp} ratio-{g.ratio} blocks, {g.index_heads}-head indexer, seed {w['seed']}",
+                       "l2": "inputs larger than L2 (kv 285 MB, indexer rows 67 MB)",
+                       "stage_ms": {"select_blocks": t_sel, "sparse_attend": t_att}},
+            "e2e": {"value": 1e3 / e2e_ms, "unit": "layer-steps/s",
+                    "h2d_bytes_per_step": int(sum(t.numel() * t.element_size() for t in h_in)),
+                    "d2h_bytes_per_step": int(h_out.numel() * 2)},
+            "gpu_launches": args.steps * 3, "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": ach / hbm_peak, "traffic": None,
+                         "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
+                         "stages": {"select_blocks": sel_bytes / (t_sel * 1e-3) / 1e9 / hbm_peak,
+                                    "sparse_attend": att_bytes / (t_att * 1e-3) / 1e9 / hbm_peak}},
+            "cpu_baseline": {"value": n_cpu / B / cpu_s, "unit": "layer-steps/s", "cores": orc.num_threads(), "kind": "port",
+                             "sample": f"{n_cpu} of the {B} sequences, one step, scaled by {B}/{n_cpu}"}}
+    print(json.dumps(line), flush=True)
+
+
 def run_gather_probe(args):
     """Gather roofline of the attention access pattern: 1 of every 8 tokens of 64-token pages
     scattered in a 1.25x pool, 16 tiles of 128 rows per CTA (the cfg3 attention shape)."""
@@ -670,6 +788,12 @@ def main():
         ap.error("--batch is a --profile option; the bench always runs the workload's own batch")
     if args.profile:
         return run_profile(args)
+    if args.workload == "v4":
+        if args.impl == "reference" or args.gpus != 1:
+            ap.error("the V4 workload is a one-GPU next-row measurement of the CUDA arm (its CPU arm is in the same line)")
+        if args.steps == 400:
+            args.steps = 50
+        return run_v4(args)
     if args.workload == "cfg5":
         if args.impl == "reference" or args.gpus != 1:
             ap.error("the churn workload runs on one GPU with the CUDA arm only (it is a parity / capacity case, "

@@ -349,12 +349,18 @@ typedef struct V4Geom {
  * every closed block in order while n_comp <= index_topk, otherwise the index_topk best by score
  * (total order on f32, ties toward the lower block), ascending, each shifted by `window`; -1 pads the row.
  * index_q bf16 [B][index_heads][index_dim] (already spread), index_w f32 [B][index_heads].
- * scores (optional, may be null) receives the score rows [B][max_comp] of the sequences that ranked.
- * Bit-exact in indices and scores. 1001 bad sizes, 1002 index_heads > 64 or index_dim > 256 or
- * max_comp > 65536, 1004 index_dim % 32 != 0. */
+ * scratch = rivoli_v4_select_scratch_bytes(): the score rows f32 [B][max_comp] of the sequences that ranked
+ * (readable after the call), then one flag per sequence.
+ * Scores are bit-exact. With index_dim == 128 they are computed on the integer tensor cores
+ * (mma.m16n8k32.s8 per block of 32, exact) whenever the rows have the form the spread produces and the
+ * block exponents of a (head, block) pair span at most 9 binades, which makes the host's ordered f32 fold
+ * exact as well; any sequence with a row or pair outside that is re-scored by the ordered CUDA-core fold
+ * (force_fold != 0 sends every sequence there). Indices are bit-exact. 1001 bad sizes / null scratch,
+ * 1002 index_heads > 64 or index_dim > 128 or max_comp > 16384 or index_topk > 4096, 1004 index_dim % 32 != 0. */
+size_t rivoli_v4_select_scratch_bytes(const V4Geom* g, int n_seqs);
 int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const int32_t* pos, const uint16_t* index_q,
-                                 const float* index_w, const uint16_t* index_kv, int32_t* sel, float* scores,
-                                 void* stream);
+                                 const float* index_w, const uint16_t* index_kv, int32_t* sel, void* scratch,
+                                 int force_fold, void* stream);
 
 /* out[b][head] bf16 = sparse attention of q[b] bf16 [n_heads][head_dim] over kv_cache[b] rows sel[b][0..cols)
  * with the sink in the denominator. n_heads == 64 and head_dim == 512 run on the tensor cores (one CTA per

@@ -78,6 +78,7 @@ def lib() -> C.CDLL:
         L.rivoli_attend_simt_scratch_bytes.restype = C.c_size_t
         L.rivoli_index_select_scratch_bytes.restype = C.c_size_t
         L.rivoli_index_frontend_scratch_bytes.restype = C.c_size_t
+        L.rivoli_v4_select_scratch_bytes.restype = C.c_size_t
         L.rivoli_kernels_arch.restype = C.c_char_p
         L.rivoli_pagepool_create.restype = C.c_void_p
         L.rivoli_pagepool_block_table.restype = C.POINTER(C.c_int32)
@@ -431,11 +432,15 @@ def launch_gather_attn_shared_kv(q, kv, sink, idxs, m: int, h: int, d: int, topk
                                                      _stream(stream)), "gather_attn_shared_kv")
 
 
-def launch_v4_select_blocks_bf16(g: V4Geom, n_seqs: int, pos, index_q, index_w, index_kv, sel, scores=None,
-                                 stream=None) -> None:
+def v4_select_scratch_bytes(g: V4Geom, n_seqs: int) -> int:
+    return int(lib().rivoli_v4_select_scratch_bytes(C.byref(g), C.c_int(n_seqs)))
+
+
+def launch_v4_select_blocks_bf16(g: V4Geom, n_seqs: int, pos, index_q, index_w, index_kv, sel, scratch,
+                                 force_fold: bool = False, stream=None) -> None:
     ensure_status(lib().rivoli_v4_select_blocks_bf16(C.byref(g), C.c_int(n_seqs), _ptr(pos), _ptr(index_q), _ptr(index_w),
-                                                     _ptr(index_kv), _ptr(sel), _ptr(scores), _stream(stream)),
-                  "v4_select_blocks_bf16")
+                                                     _ptr(index_kv), _ptr(sel), _ptr(scratch), C.c_int(int(force_fold)),
+                                                     _stream(stream)), "v4_select_blocks_bf16")
 
 
 def launch_v4_sparse_attend_bf16(g: V4Geom, n_seqs: int, q, kv_cache, sink, sel, cols: int, out,

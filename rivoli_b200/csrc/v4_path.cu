@@ -197,6 +197,175 @@ __global__ void v4_score_blocks_serial_kernel(const float* __restrict__ q, const
 }
 
 // ---------------------------------------------------------------------------------------------------
+// block scorer on the integer tensor cores, exact
+//
+// Rows that came through the spread are, block of 32 by block of 32, small integers times one power of
+// two: v = m * 2^e with |m| < 16 once e = (exponent of the block's largest magnitude) - 3. A block's share of
+// a dot product is then I_j * 2^(eq_j + ek_j) with I_j = sum of 32 integer products, which
+// mma.m16n8k32.s8 returns exactly (K = 32 is one block). The host's ascending f32 fold over the 128
+// products never rounds as long as every partial sum is representable: all of them are multiples of
+// 2^Emin and smaller than 2^(Emax + 15) (4 blocks x 32 terms x 15 x 15 < 2^15), so Emax - Emin <= 9
+// suffices, and then the fold equals the exact sum, which is what sum_j float(I_j) * 2^E_j gives here.
+// Everything after the dot (bf16 store, relu, head weight, bf16 store, ascending head sum) is evaluated
+// in the host's order on CUDA cores. A pair that misses the condition, or a row that is not of that form
+// (a value that is not an integer multiple of its block's unit, a subnormal, an exponent near the range
+// ends), raises the sequence's flag and the selection kernel re-scores that sequence with the ordered
+// CUDA-core fold: the result is exact either way.
+// ---------------------------------------------------------------------------------------------------
+constexpr int SI_THREADS = 256;
+constexpr int SI_CHUNK = 256;       // blocks (columns) per CTA
+constexpr int SI_SPAN = 9;
+
+__device__ __forceinline__ void v4_mma_s8(int (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1), "r"(0));
+}
+
+// Four bf16 values (two 32-bit words) -> four int8 in units of 2^(pb - 130) (pb = biased exponent of the
+// block's largest magnitude). ok is cleared when a value is not an integer multiple of the unit.
+__device__ __forceinline__ uint32_t v4_pack4(uint32_t w0, uint32_t w1, int pb, bool& ok) {
+    uint32_t out = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t h = (i < 2 ? w0 : w1) >> ((i & 1) * 16) & 0xffffu;
+        const int ex = (h >> 7) & 0xff;
+        const uint32_t man = h & 0x7fu;
+        int m = 0;
+        if (ex != 0) {
+            const int sh = 4 + pb - ex;                 // >= 4
+            const uint32_t sig = 0x80u | man;
+            if (sh > 7 || (sig & ((1u << sh) - 1u))) ok = false;
+            m = sh > 7 ? 0 : (int)(sig >> sh);
+            if (h & 0x8000u) m = -m;
+        } else if (man) {
+            ok = false;                                  // subnormal
+        }
+        out |= ((uint32_t)m & 0xffu) << (8 * i);
+    }
+    return out;
+}
+__device__ __forceinline__ int v4_max_exp4(uint32_t w0, uint32_t w1) {
+    const int e0 = (w0 >> 7) & 0xff, e1 = (w0 >> 23) & 0xff, e2 = (w1 >> 7) & 0xff, e3 = (w1 >> 23) & 0xff;
+    return max(max(e0, e1), max(e2, e3));
+}
+
+__global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, const int32_t* __restrict__ pos,
+                                                                   const uint16_t* __restrict__ index_q,
+                                                                   const float* __restrict__ index_w,
+                                                                   const uint16_t* __restrict__ index_kv,
+                                                                   float* __restrict__ scores,
+                                                                   int32_t* __restrict__ flags) {
+    __shared__ __align__(16) uint32_t qfrag[4 * 4 * 32 * 4];   // [m-tile][block][lane][4 regs]: A fragments, 8 KB
+    __shared__ uint32_t qexp[64];                              // per head: 4 biased block exponents (0 = empty block)
+    __shared__ float wsh[64];
+    __shared__ float terms[SI_THREADS / 32][64][8];
+    const int b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_comp = min((pos[b] + 1) / g.ratio, g.max_comp);
+    const int c_begin = blockIdx.x * SI_CHUNK;
+    if (n_comp <= g.index_topk || c_begin >= n_comp) return;   // positional sequences are not scored
+    const int heads = g.index_heads;
+    bool ok = true;
+    // ---- q of this sequence: one thread per (head, block of 32)
+    {
+        const int hh = tid >> 2, j = tid & 3;
+        uint32_t wv[16];
+        int pb = 0;
+        if (hh < heads) {
+            const uint4* src = reinterpret_cast<const uint4*>(index_q + ((size_t)b * heads + hh) * 128 + j * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = src[i];
+                wv[4 * i] = v.x; wv[4 * i + 1] = v.y; wv[4 * i + 2] = v.z; wv[4 * i + 3] = v.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) pb = max(pb, v4_max_exp4(wv[i], wv[i + 1]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) wv[i] = 0;
+        }
+        const int mt = hh >> 4, r = hh & 15;
+#pragma unroll
+        for (int k4 = 0; k4 < 8; ++k4) {                       // values 4 k4 .. 4 k4 + 3 of the block
+            const uint32_t packed = v4_pack4(wv[2 * k4], wv[2 * k4 + 1], pb, ok);
+            const int kk = 4 * k4, fl = (r & 7) * 4 + ((kk & 15) >> 2), reg = (r >> 3) + 2 * (kk >> 4);
+            qfrag[((mt * 4 + j) * 32 + fl) * 4 + reg] = packed;
+        }
+        // the four exponents of a head sit in four neighbouring threads
+        uint32_t e4 = (uint32_t)pb << (8 * j);
+        e4 |= __shfl_xor_sync(0xffffffffu, e4, 1);
+        e4 |= __shfl_xor_sync(0xffffffffu, e4, 2);
+        if (j == 0) qexp[hh] = e4;
+        if (tid < 64) wsh[tid] = tid < heads ? index_w[(size_t)b * heads + tid] : 0.0f;
+    }
+    __syncthreads();
+    const uint16_t* kv = index_kv + (size_t)b * g.max_comp * 128;
+    const int grp = lane >> 2, quad = lane & 3;
+    const int c_end = min(n_comp, c_begin + SI_CHUNK);
+    for (int c0 = c_begin + warp * 8; c0 < c_end; c0 += (SI_THREADS / 32) * 8) {
+        // ---- B fragments: row c0 + grp, this thread's 8 values of each block
+        const int c = c0 + grp;
+        uint32_t b0[4], b1[4], kexp = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint2 lo = make_uint2(0, 0), hi = make_uint2(0, 0);
+            if (c < n_comp) {
+                lo = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + quad * 4);
+                hi = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + 16 + quad * 4);
+            }
+            int pb = max(v4_max_exp4(lo.x, lo.y), v4_max_exp4(hi.x, hi.y));
+            pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 1));
+            pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 2));
+            b0[j] = v4_pack4(lo.x, lo.y, pb, ok);
+            b1[j] = v4_pack4(hi.x, hi.y, pb, ok);
+            kexp |= (uint32_t)pb << (8 * j);
+        }
+        // exponents of the two columns this thread's accumulators belong to
+        const uint32_t kexpA = __shfl_sync(0xffffffffu, kexp, (quad * 2) * 4);
+        const uint32_t kexpB = __shfl_sync(0xffffffffu, kexp, (quad * 2 + 1) * 4);
+        __syncwarp();
+#pragma unroll 1
+        for (int mt = 0; mt < 4; ++mt) {
+            int acc[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 a = *reinterpret_cast<const uint4*>(&qfrag[((mt * 4 + j) * 32 + lane) * 4]);
+                v4_mma_s8(acc[j], a, b0[j], b1[j]);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {                      // (row half, column) of the accumulator
+                const int hh = 16 * mt + grp + ((e >> 1) << 3);
+                const uint32_t qe = qexp[hh], ke = (e & 1) ? kexpB : kexpA;
+                float dsum = 0.0f;
+                int emax = -100000, emin = 100000;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int eq = (qe >> (8 * j)) & 0xff, ek = (ke >> (8 * j)) & 0xff;
+                    if (eq != 0 && ek != 0) {
+                        const int E = eq + ek - 260;           // (eq - 130) + (ek - 130)
+                        if (E < -120 || E > 100) ok = false;   // keep 2^E and every partial sum in the normal range
+                        emax = max(emax, E);
+                        emin = min(emin, E);
+                        dsum = fmaf((float)acc[j][e], __int_as_float((E + 127) << 23), dsum);
+                    }
+                }
+                if (emax - emin > SI_SPAN && emax > -100000) ok = false;
+                const float t = v4_rbf16(__fmul_rn(fmaxf(v4_rbf16(dsum), 0.0f), wsh[hh]));
+                terms[warp][hh][quad * 2 + (e & 1)] = t;
+            }
+        }
+        __syncwarp();
+        if (lane < 8 && c0 + lane < c_end) {
+            float acc = 0.0f;
+#pragma unroll 8
+            for (int hh = 0; hh < heads; ++hh) acc = __fadd_rn(acc, terms[warp][hh][lane]);
+            scores[(size_t)b * g.max_comp + c0 + lane] = v4_rbf16(acc);
+        }
+    }
+    if (!ok) atomicOr(&flags[b], 1);
+}
+
+// ---------------------------------------------------------------------------------------------------
 // batched selection: window row + positional or scored compressed columns, one CTA per sequence
 // ---------------------------------------------------------------------------------------------------
 constexpr int SEL_MAX_COMP = 16384;
@@ -217,7 +386,8 @@ __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const i
                                                                const float* __restrict__ index_w,
                                                                const uint16_t* __restrict__ index_kv,
                                                                int32_t* __restrict__ sel,
-                                                               float* __restrict__ scores_out) {
+                                                               float* __restrict__ scores,
+                                                               const int32_t* __restrict__ flags, int force_fold) {
     extern __shared__ __align__(16) unsigned char sel_smem_raw[];
     SelSmem& sh = *reinterpret_cast<SelSmem*>(sel_smem_raw);
     float* qT = reinterpret_cast<float*>(sel_smem_raw + ((sizeof(SelSmem) + 15) & ~(size_t)15));
@@ -241,21 +411,27 @@ __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const i
         for (int c = tid; c < K; c += TK_THREADS) row[W + c] = c < n_comp ? W + c : -1;
         return;
     }
-    v4_stage_q(index_q + (size_t)b * g.index_heads * g.index_dim, index_w + (size_t)b * g.index_heads, g.index_heads,
-               g.index_dim, qT, sh.wsh);
-    __syncthreads();
-    const uint16_t* kv = index_kv + (size_t)b * g.max_comp * g.index_dim;
-    for (int c0 = warp * SC_CB; c0 < n_comp; c0 += TK_WARPS * SC_CB) {
-        float out[SC_CB];
-        v4_score_blocks_warp(qT, sh.wsh, stage + warp * SC_CB * g.index_dim, kv, c0, n_comp, g.index_heads,
-                             g.index_dim, out);
-        if (lane < SC_CB && c0 + lane < n_comp) {
-            float v = out[0];
+    float* srow = scores + (size_t)b * g.max_comp;
+    if (force_fold || flags[b]) {
+        // the ordered CUDA-core fold: rows the integer scorer could not take, or every row on request
+        v4_stage_q(index_q + (size_t)b * g.index_heads * g.index_dim, index_w + (size_t)b * g.index_heads, g.index_heads,
+                   g.index_dim, qT, sh.wsh);
+        __syncthreads();
+        const uint16_t* kv = index_kv + (size_t)b * g.max_comp * g.index_dim;
+        for (int c0 = warp * SC_CB; c0 < n_comp; c0 += TK_WARPS * SC_CB) {
+            float out[SC_CB];
+            v4_score_blocks_warp(qT, sh.wsh, stage + warp * SC_CB * g.index_dim, kv, c0, n_comp, g.index_heads,
+                                 g.index_dim, out);
+            if (lane < SC_CB && c0 + lane < n_comp) {
+                float v = out[0];
 #pragma unroll
-            for (int cb = 1; cb < SC_CB; ++cb) v = lane == cb ? out[cb] : v;
-            sc[c0 + lane] = v;
-            if (scores_out) scores_out[(size_t)b * g.max_comp + c0 + lane] = v;
+                for (int cb = 1; cb < SC_CB; ++cb) v = lane == cb ? out[cb] : v;
+                sc[c0 + lane] = v;
+                srow[c0 + lane] = v;
+            }
         }
+    } else {
+        for (int c = tid; c < n_comp; c += TK_THREADS) sc[c] = srow[c];
     }
     __syncthreads();
     auto key_at = [&](int i) { return v4_total_key(sc[i]); };
@@ -614,10 +790,16 @@ RIVOLI_API int rivoli_gather_attn_shared_kv(const float* q, const float* kv, con
     return rv_launch_status();
 }
 
+RIVOLI_API size_t rivoli_v4_select_scratch_bytes(const V4Geom* g, int n_seqs) {
+    if (!g || n_seqs <= 0 || g->max_comp <= 0) return 0;
+    return ((size_t)n_seqs * (size_t)g->max_comp + (size_t)n_seqs) * 4;   // score rows, then one flag per sequence
+}
+
 RIVOLI_API int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const int32_t* pos, const uint16_t* index_q,
                                             const float* index_w, const uint16_t* index_kv, int32_t* sel,
-                                            float* scores, void* stream) {
+                                            void* scratch, int force_fold, void* stream) {
     if (int rc = v4_check_geom(g, n_seqs)) return rc;
+    if (!scratch) return 1001;
     if (g->index_heads > SC_MAX_HEADS || g->index_dim > SC_MAX_HD || g->max_comp > SEL_MAX_COMP || g->index_topk > 4096)
         return 1002;
     if (g->index_dim % 32) return 1004;
@@ -626,9 +808,18 @@ RIVOLI_API int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const i
                          (size_t)g->index_topk) * 4;
     if (smem > 227 * 1024) return 1002;
     rv_drain_error();
+    cudaStream_t st = (cudaStream_t)stream;
+    float* scores = static_cast<float*>(scratch);
+    int32_t* flags = reinterpret_cast<int32_t*>(scores + (size_t)n_seqs * g->max_comp);
+    const bool tensor = !force_fold && g->index_dim == 128 && n_seqs <= 65535;
+    if (tensor) {
+        cudaMemsetAsync(flags, 0, (size_t)n_seqs * 4, st);
+        dim3 grid((unsigned)((g->max_comp + SI_CHUNK - 1) / SI_CHUNK), (unsigned)n_seqs);
+        v4_score_int8_kernel<<<grid, SI_THREADS, 0, st>>>(*g, pos, index_q, index_w, index_kv, scores, flags);
+    }
     cudaFuncSetAttribute(v4_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    v4_select_kernel<<<(unsigned)n_seqs, TK_THREADS, smem, (cudaStream_t)stream>>>(*g, pos, index_q, index_w, index_kv, sel,
-                                                                                   scores);
+    v4_select_kernel<<<(unsigned)n_seqs, TK_THREADS, smem, st>>>(*g, pos, index_q, index_w, index_kv, sel, scores, flags,
+                                                                 tensor ? 0 : 1);
     return rv_launch_status();
 }
 

@@ -24,9 +24,21 @@ class V4DecodeLayer:
         self.cols = g.window + g.index_topk
         self.sel = torch.full((n_seqs, self.cols), -1, dtype=torch.int32, device=dev)
         self.out = torch.zeros((n_seqs, g.n_heads, g.head_dim), dtype=torch.uint16, device=dev)
+        # score rows f32 [B][max_comp] of the sequences that ranked, then one flag per sequence
+        self.scratch = torch.zeros(be.v4_select_scratch_bytes(g, n_seqs) // 4, dtype=torch.float32, device=dev)
 
-    def select(self, pos, index_q, index_w, scores=None, stream=None):
-        be.launch_v4_select_blocks_bf16(self.g, self.B, pos, index_q, index_w, self.index_kv, self.sel, scores, stream)
+    @property
+    def scores(self):
+        return self.scratch[: self.B * self.g.max_comp].view(self.B, self.g.max_comp)
+
+    @property
+    def refolded(self):
+        """Per sequence: 1 if the integer scorer handed it to the ordered CUDA-core fold in the last select()."""
+        return self.scratch[self.B * self.g.max_comp:].view(torch.int32)
+
+    def select(self, pos, index_q, index_w, force_fold: bool = False, stream=None):
+        be.launch_v4_select_blocks_bf16(self.g, self.B, pos, index_q, index_w, self.index_kv, self.sel, self.scratch,
+                                        force_fold, stream)
         return self.sel
 
     def attend(self, q, force_simt: bool = False, stream=None):
@@ -36,5 +48,5 @@ class V4DecodeLayer:
 
     def step(self, pos, q, index_q, index_w, stream=None):
         """Selection then attention for one decode step; returns the bf16 output [B, H, D]."""
-        self.select(pos, index_q, index_w, None, stream)
+        self.select(pos, index_q, index_w, False, stream)
         return self.attend(q, False, stream)

@@ -121,7 +121,7 @@ def test_gather_attn_reference_layout():
     assert np.array_equal(bits(got[:2]), bits(orc.bf16_to_f32(orc.f32_to_bf16(got[:2]))))  # stored on the bf16 grid
 
 
-def _run_step(g, inp, force_simt=False, want_scores=True):
+def _run_step(g, inp, force_simt=False, want_scores=True, force_fold=False, want_flags=False):
     be = _be()
     from rivoli_b200.v4 import V4DecodeLayer
     B = inp["pos"].size
@@ -130,11 +130,11 @@ def _run_step(g, inp, force_simt=False, want_scores=True):
     layer.kv_cache.copy_(dev(inp["kv_cache"]))
     layer.index_kv.copy_(dev(inp["ikv"]))
     layer.sink.copy_(dev(inp["sink"]))
-    scores = torch.zeros((B, g.max_comp), device="cuda") if want_scores else None
-    layer.select(dev(inp["pos"]), dev(inp["iq"]), dev(inp["iw"]), scores)
+    layer.select(dev(inp["pos"]), dev(inp["iq"]), dev(inp["iw"]), force_fold)
     layer.attend(dev(inp["q"]), force_simt)
     torch.cuda.synchronize()
-    return layer.sel.cpu().numpy(), layer.out.cpu().numpy(), (scores.cpu().numpy() if want_scores else None)
+    res = (layer.sel.cpu().numpy(), layer.out.cpu().numpy(), (layer.scores.cpu().numpy() if want_scores else None))
+    return res + (layer.refolded.cpu().numpy(),) if want_flags else res
 
 
 def test_batched_step_small_shapes():
@@ -153,15 +153,17 @@ def test_batched_step_small_shapes():
     assert ok, worst
 
 
-@pytest.mark.parametrize("force_simt", [False, True])
-def test_batched_step_model_shapes(force_simt):
+@pytest.mark.parametrize("force_simt,force_fold", [(False, False), (True, True)])
+def test_batched_step_model_shapes(force_simt, force_fold):
     g = wl.make_geom(max_comp=640, index_topk=96)
     pos = np.array([3, 126, 127, 500, 2559, 1023, 1500, 390], np.int32)  # ring filling / full; positional and scored
     inp = wl.make_inputs(g, pos.size, pos, seed=4)
     inp["iw"][1] = np.abs(inp["iw"][1])
     want_sel, want_out, want_sc = orc.v4_decode_step_bf16(g, pos, inp["q"], inp["kv_cache"], inp["sink"], inp["iq"],
                                                           inp["iw"], inp["ikv"], want_scores=True)
-    sel, out, sc = _run_step(g, inp, force_simt)
+    sel, out, sc, flags = _run_step(g, inp, force_simt, force_fold=force_fold, want_flags=True)
+    if not force_fold:
+        assert not flags.any()      # spread rows are what the integer scorer takes whole
     assert np.array_equal(sel, want_sel)
     for b in range(pos.size):
         n_comp = (pos[b] + 1) // g.ratio
@@ -206,3 +208,24 @@ def test_fully_masked_row_is_nan_and_masked_slots_are_ignored():
         assert np.all(np.isnan(orc.bf16_to_f32(got[0])))
         ok, worst = wl.attend_close(got[1:], want[1:])
         assert ok, (force, worst)
+
+
+def test_rows_outside_the_integer_form_are_refolded_exactly():
+    """Arbitrary bf16 index rows (not spread): the integer scorer must notice and hand the sequence to the
+    ordered fold; scores and indices stay bit-exact. One sequence keeps spread rows and stays on the
+    tensor path; one has a single block pair whose exponents are far apart."""
+    g = wl.make_geom(max_comp=640, index_topk=96)
+    pos = np.array([2559, 2559, 2559, 2559], np.int32)
+    inp = wl.make_inputs(g, 4, pos, seed=12)
+    rng = np.random.default_rng(1)
+    inp["ikv"][1] = orc.f32_to_bf16(rng.standard_normal((g.max_comp, g.index_dim)).astype(np.float32))
+    inp["iq"][2] = orc.f32_to_bf16(rng.standard_normal((g.index_heads, g.index_dim)).astype(np.float32))
+    row = orc.bf16_to_f32(inp["ikv"][3, 17]).copy()
+    row[:32] *= np.float32(2.0 ** 14)      # one block of one row 14 binades above its neighbours
+    inp["ikv"][3, 17] = orc.f32_to_bf16(row)
+    want_sel, want_out, want_sc = orc.v4_decode_step_bf16(g, pos, inp["q"], inp["kv_cache"], inp["sink"], inp["iq"],
+                                                          inp["iw"], inp["ikv"], want_scores=True)
+    sel, out, sc, flags = _run_step(g, inp, want_flags=True)
+    assert flags.tolist() == [0, 1, 1, 1]
+    assert np.array_equal(bits(sc), bits(want_sc))
+    assert np.array_equal(sel, want_sel)
