@@ -792,7 +792,7 @@ def main():
         if args.impl == "reference" or args.gpus != 1:
             ap.error("the V4 workload is a one-GPU next-row measurement of the CUDA arm (its CPU arm is in the same line)")
         if args.steps == 400:
-            args.steps = 50
+            args.steps = 2000            # 0.14 ms each: long enough for the clock sampler to see the timed region
         return run_v4(args)
     if args.workload == "cfg5":
         if args.impl == "reference" or args.gpus != 1:

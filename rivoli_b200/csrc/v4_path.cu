@@ -221,34 +221,35 @@ __device__ __forceinline__ void v4_mma_s8(int (&d)[4], const uint4& a, uint32_t 
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                  : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1), "r"(0));
 }
+__device__ __forceinline__ float v4_rbf16_hw(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }  // finite inputs
 
-// Four bf16 values (two 32-bit words) -> four int8 in units of 2^(pb - 130) (pb = biased exponent of the
-// block's largest magnitude). ok is cleared when a value is not an integer multiple of the unit.
-__device__ __forceinline__ uint32_t v4_pack4(uint32_t w0, uint32_t w1, int pb, bool& ok) {
-    uint32_t out = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t h = (i < 2 ? w0 : w1) >> ((i & 1) * 16) & 0xffffu;
-        const int ex = (h >> 7) & 0xff;
-        const uint32_t man = h & 0x7fu;
-        int m = 0;
-        if (ex != 0) {
-            const int sh = 4 + pb - ex;                 // >= 4
-            const uint32_t sig = 0x80u | man;
-            if (sh > 7 || (sig & ((1u << sh) - 1u))) ok = false;
-            m = sh > 7 ? 0 : (int)(sig >> sh);
-            if (h & 0x8000u) m = -m;
-        } else if (man) {
-            ok = false;                                  // subnormal
-        }
-        out |= ((uint32_t)m & 0xffu) << (8 * i);
-    }
+// Largest biased exponent among the bf16 values packed in w0, w1.
+__device__ __forceinline__ int v4_max_exp4(uint32_t w0, uint32_t w1) {
+    const uint32_t a = max(w0 & 0x7f800000u, w1 & 0x7f800000u), b = max((w0 << 16) & 0x7f800000u, (w1 << 16) & 0x7f800000u);
+    return (int)(max(a, b) >> 23);
+}
+// Four bf16 values (two words) times `scale` (a power of two) -> four int8. ok is cleared when a product is
+// not an integer (the value is not a multiple of the block's unit).
+__device__ __forceinline__ uint32_t v4_pack4(uint32_t w0, uint32_t w1, float scale, bool& ok) {
+    const float x0 = __uint_as_float(w0 << 16) * scale, x1 = __uint_as_float(w0 & 0xffff0000u) * scale;
+    const float x2 = __uint_as_float(w1 << 16) * scale, x3 = __uint_as_float(w1 & 0xffff0000u) * scale;
+    const int m0 = __float2int_rn(x0), m1 = __float2int_rn(x1), m2 = __float2int_rn(x2), m3 = __float2int_rn(x3);
+    ok = ok && (float)m0 == x0 && (float)m1 == x1 && (float)m2 == x2 && (float)m3 == x3;
+    if (scale == 0.0f) ok = ok && ((w0 | w1) & 0x7fff7fffu) == 0;   // an "empty" block must really be zeros
+    // cvt.pack d, a, b, c: d[7:0] = sat(b), d[15:8] = sat(a), d[31:16] = c[15:0]
+    uint32_t hi, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(m3), "r"(m2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(m1), "r"(m0), "r"(hi));
     return out;
 }
-__device__ __forceinline__ int v4_max_exp4(uint32_t w0, uint32_t w1) {
-    const int e0 = (w0 >> 7) & 0xff, e1 = (w0 >> 23) & 0xff, e2 = (w1 >> 7) & 0xff, e3 = (w1 >> 23) & 0xff;
-    return max(max(e0, e1), max(e2, e3));
+// 2^(130 - pb): turns values of a block whose largest exponent is pb into integers below 16. Blocks whose
+// exponent sits at the very bottom of the range are left to the ordered fold.
+__device__ __forceinline__ float v4_unit_inv(int pb, bool& ok) {
+    if (pb < 4) { ok = ok && pb == 0; return 0.0f; }
+    return __int_as_float((257 - pb) << 23);
 }
+// 2^(pb - 130), or 0 for an empty block.
+__device__ __forceinline__ float v4_unit(int pb) { return pb < 4 ? 0.0f : __int_as_float((pb - 3) << 23); }
 
 __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, const int32_t* __restrict__ pos,
                                                                    const uint16_t* __restrict__ index_q,
@@ -257,15 +258,18 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
                                                                    float* __restrict__ scores,
                                                                    int32_t* __restrict__ flags) {
     __shared__ __align__(16) uint32_t qfrag[4 * 4 * 32 * 4];   // [m-tile][block][lane][4 regs]: A fragments, 8 KB
-    __shared__ uint32_t qexp[64];                              // per head: 4 biased block exponents (0 = empty block)
+    __shared__ __align__(16) float qunit[64][4];               // per head: 2^(e - 130) of its four blocks (0 = empty)
     __shared__ float wsh[64];
-    __shared__ float terms[SI_THREADS / 32][64][8];
+    __shared__ int qstat[3];                                   // over the heads: min / max block exponent, widest span
+    __shared__ __align__(16) float terms[SI_THREADS / 32][64][8];   // written as float2: needs the alignment
     const int b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_comp = min((pos[b] + 1) / g.ratio, g.max_comp);
     const int c_begin = blockIdx.x * SI_CHUNK;
     if (n_comp <= g.index_topk || c_begin >= n_comp) return;   // positional sequences are not scored
     const int heads = g.index_heads;
     bool ok = true;
+    if (tid == 0) { qstat[0] = 1000; qstat[1] = -1000; qstat[2] = 0; }
+    __syncthreads();
     // ---- q of this sequence: one thread per (head, block of 32)
     {
         const int hh = tid >> 2, j = tid & 3;
@@ -284,28 +288,33 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
 #pragma unroll
             for (int i = 0; i < 16; ++i) wv[i] = 0;
         }
+        const float inv = v4_unit_inv(pb, ok);
         const int mt = hh >> 4, r = hh & 15;
 #pragma unroll
         for (int k4 = 0; k4 < 8; ++k4) {                       // values 4 k4 .. 4 k4 + 3 of the block
-            const uint32_t packed = v4_pack4(wv[2 * k4], wv[2 * k4 + 1], pb, ok);
+            const uint32_t packed = v4_pack4(wv[2 * k4], wv[2 * k4 + 1], inv, ok);
             const int kk = 4 * k4, fl = (r & 7) * 4 + ((kk & 15) >> 2), reg = (r >> 3) + 2 * (kk >> 4);
             qfrag[((mt * 4 + j) * 32 + fl) * 4 + reg] = packed;
         }
-        // the four exponents of a head sit in four neighbouring threads
-        uint32_t e4 = (uint32_t)pb << (8 * j);
-        e4 |= __shfl_xor_sync(0xffffffffu, e4, 1);
-        e4 |= __shfl_xor_sync(0xffffffffu, e4, 2);
-        if (j == 0) qexp[hh] = e4;
+        qunit[hh][j] = v4_unit(pb);
+        // exponent range of the head's non-empty blocks (its four threads are neighbours)
+        int lo = pb >= 4 ? pb : 1000, hi = pb >= 4 ? pb : -1000;
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, 1)); hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, 1));
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, 2)); hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, 2));
+        if (j == 0 && hi >= lo) { atomicMin(&qstat[0], lo); atomicMax(&qstat[1], hi); atomicMax(&qstat[2], hi - lo); }
         if (tid < 64) wsh[tid] = tid < heads ? index_w[(size_t)b * heads + tid] : 0.0f;
     }
     __syncthreads();
+    const int q_lo = qstat[0], q_hi = qstat[1], q_span = qstat[2];
     const uint16_t* kv = index_kv + (size_t)b * g.max_comp * 128;
     const int grp = lane >> 2, quad = lane & 3;
     const int c_end = min(n_comp, c_begin + SI_CHUNK);
     for (int c0 = c_begin + warp * 8; c0 < c_end; c0 += (SI_THREADS / 32) * 8) {
         // ---- B fragments: row c0 + grp, this thread's 8 values of each block
         const int c = c0 + grp;
-        uint32_t b0[4], b1[4], kexp = 0;
+        uint32_t b0[4], b1[4];
+        float ku[4];
+        int k_lo = 1000, k_hi = -1000;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             uint2 lo = make_uint2(0, 0), hi = make_uint2(0, 0);
@@ -316,14 +325,24 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
             int pb = max(v4_max_exp4(lo.x, lo.y), v4_max_exp4(hi.x, hi.y));
             pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 1));
             pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 2));
-            b0[j] = v4_pack4(lo.x, lo.y, pb, ok);
-            b1[j] = v4_pack4(hi.x, hi.y, pb, ok);
-            kexp |= (uint32_t)pb << (8 * j);
+            const float inv = v4_unit_inv(pb, ok);
+            b0[j] = v4_pack4(lo.x, lo.y, inv, ok);
+            b1[j] = v4_pack4(hi.x, hi.y, inv, ok);
+            ku[j] = v4_unit(pb);
+            if (pb >= 4) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
         }
-        // exponents of the two columns this thread's accumulators belong to
-        const uint32_t kexpA = __shfl_sync(0xffffffffu, kexp, (quad * 2) * 4);
-        const uint32_t kexpB = __shfl_sync(0xffffffffu, kexp, (quad * 2 + 1) * 4);
-        __syncwarp();
+        // Every (head, this row) pair: block exponents E_j = eq_j + ek_j - 260 span at most span_q + span_k, and lie
+        // inside [q_lo + k_lo, q_hi + k_hi] - 260. Inside the limits the ordered f32 fold is exact.
+        if (k_hi >= k_lo && q_hi >= q_lo &&
+            (q_span + (k_hi - k_lo) > SI_SPAN || q_lo + k_lo - 260 < -120 || q_hi + k_hi - 260 > 100))
+            ok = false;
+        // units of the two columns this thread's accumulators belong to
+        float kuA[4], kuB[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            kuA[j] = __shfl_sync(0xffffffffu, ku[j], (quad * 2) * 4);
+            kuB[j] = __shfl_sync(0xffffffffu, ku[j], (quad * 2 + 1) * 4);
+        }
 #pragma unroll 1
         for (int mt = 0; mt < 4; ++mt) {
             int acc[4][4];
@@ -333,25 +352,19 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
                 v4_mma_s8(acc[j], a, b0[j], b1[j]);
             }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {                      // (row half, column) of the accumulator
-                const int hh = 16 * mt + grp + ((e >> 1) << 3);
-                const uint32_t qe = qexp[hh], ke = (e & 1) ? kexpB : kexpA;
-                float dsum = 0.0f;
-                int emax = -100000, emin = 100000;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int eq = (qe >> (8 * j)) & 0xff, ek = (ke >> (8 * j)) & 0xff;
-                    if (eq != 0 && ek != 0) {
-                        const int E = eq + ek - 260;           // (eq - 130) + (ek - 130)
-                        if (E < -120 || E > 100) ok = false;   // keep 2^E and every partial sum in the normal range
-                        emax = max(emax, E);
-                        emin = min(emin, E);
-                        dsum = fmaf((float)acc[j][e], __int_as_float((E + 127) << 23), dsum);
-                    }
-                }
-                if (emax - emin > SI_SPAN && emax > -100000) ok = false;
-                const float t = v4_rbf16(__fmul_rn(fmaxf(v4_rbf16(dsum), 0.0f), wsh[hh]));
-                terms[warp][hh][quad * 2 + (e & 1)] = t;
+            for (int rh = 0; rh < 2; ++rh) {                   // row half of the accumulator
+                const int hh = 16 * mt + grp + 8 * rh;
+                const float4 qu = *reinterpret_cast<const float4*>(qunit[hh]);
+                const float wv = wsh[hh];
+                float dA = 0.0f, dB = 0.0f;
+                dA = fmaf((float)acc[0][2 * rh], qu.x * kuA[0], dA); dB = fmaf((float)acc[0][2 * rh + 1], qu.x * kuB[0], dB);
+                dA = fmaf((float)acc[1][2 * rh], qu.y * kuA[1], dA); dB = fmaf((float)acc[1][2 * rh + 1], qu.y * kuB[1], dB);
+                dA = fmaf((float)acc[2][2 * rh], qu.z * kuA[2], dA); dB = fmaf((float)acc[2][2 * rh + 1], qu.z * kuB[2], dB);
+                dA = fmaf((float)acc[3][2 * rh], qu.w * kuA[3], dA); dB = fmaf((float)acc[3][2 * rh + 1], qu.w * kuB[3], dB);
+                // bf16 store, relu, times the (signed) head weight, bf16 store
+                const float tA = v4_rbf16_hw(__fmul_rn(fmaxf(v4_rbf16_hw(dA), 0.0f), wv));
+                const float tB = v4_rbf16_hw(__fmul_rn(fmaxf(v4_rbf16_hw(dB), 0.0f), wv));
+                *reinterpret_cast<float2*>(&terms[warp][hh][quad * 2]) = make_float2(tA, tB);
             }
         }
         __syncwarp();
@@ -359,8 +372,9 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
             float acc = 0.0f;
 #pragma unroll 8
             for (int hh = 0; hh < heads; ++hh) acc = __fadd_rn(acc, terms[warp][hh][lane]);
-            scores[(size_t)b * g.max_comp + c0 + lane] = v4_rbf16(acc);
+            scores[(size_t)b * g.max_comp + c0 + lane] = v4_rbf16_hw(acc);
         }
+        __syncwarp();
     }
     if (!ok) atomicOr(&flags[b], 1);
 }
