@@ -370,6 +370,50 @@ int rivoli_v4_sparse_attend_bf16(const V4Geom* g, int n_seqs, const uint16_t* q,
                                  const float* sink, const int32_t* sel, int cols, uint16_t* out, int force_simt,
                                  void* stream);
 
+/* ---- V4 KV compressor, decode arm (crates/backend/kernels/kvcompress.hip; struct layouts of
+ * crates/backend/src/abi.rs:24-45) -------------------------------------------------------------------- */
+typedef struct CompGeom {
+    int32_t ratio;   /* positions pooled per block */
+    int32_t coff;    /* 1 + overlap */
+    int32_t d;       /* this compressor's head_dim */
+    int32_t cd;      /* coff * d: width of the projected rows and of ape's rows */
+    int32_t ents;    /* coff * ratio: entries in one pooling window */
+    int32_t rd;      /* rope_head_dim: only the LAST rd dims of a pooled row are rotated */
+    float eps;       /* norm_eps */
+} CompGeom;
+typedef struct CompFinish {
+    const float* norm;   /* [d] RMSNorm gain */
+    const float* freqs;  /* [positions][rd]: (cos, sin) pairs */
+    float* out;          /* [d] the pooled, normed, rotated row (before the finishing quantisation) */
+} CompFinish;
+
+/* crates/backend/kernels/mla.hip:527-550 (kernel :319-338): fp8 (e4m3, round to nearest even) quantise-dequantise
+ * of the first n values of each row in blocks of `block`, power-of-two scale, amax floor 1e-4. Bit-identical to
+ * the host rule. 1001 sizes, 1002 out of place with a tail, 1004 n % block. */
+int rivoli_act_quant_f8_prefix(const float* src, float* dst, int rows, int row_stride, int n, int block, void* stream);
+/* kvcompress.hip `rivoli_kv_compress_deposit`: s projected rows [s][cd] (kv, score) into the pooling state
+ * [ents][cd]: with overlap the last full block becomes the overlap half; the s % ratio rows of the open block
+ * land from slot0 on; score rows get ape added. 1000 null geometry, 1001-1004/1010 geometry, 1005 s <= 0, 1008 slot0. */
+int rivoli_kv_compress_deposit(const float* kv, const float* score, const float* ape, float* kv_state,
+                               float* score_state, const CompGeom* p, int s, int slot0, void* stream);
+/* kvcompress.hip `rivoli_kv_compress_decode`: pool the state (softmax over the entry axis per feature), bf16 store,
+ * RMSNorm, rotate the last rd dims at the block's first position, bf16 store -> f->out; then the overlap half of the
+ * state moves down. 1007 start_pos <= 0, 1009 (start_pos + 1) % ratio != 0. Tolerance: expf and the norm's
+ * reduction order differ from the host's by rounding. */
+int rivoli_kv_compress_decode(float* kv_state, float* score_state, const CompFinish* f, const CompGeom* p,
+                              int start_pos, void* stream);
+/* Batched decode step (no counterpart in the reference: crates/engine/src/v4/kvcompress.rs drives one sequence):
+ * per sequence b, deposit the token's projected rows kv_proj[b], score_proj[b] ([cd] f32) at slot pos[b] % ratio of
+ * its state ([B][ents][cd] f32); if the block closes, pool + norm + rotate as above, finish with the spread
+ * (rotate != 0: the indexer's compressor, blockindex.hip:97-138) or the fp8 block-64 quantisation of the d - rd
+ * un-rotated dims (the attention compressor, crates/oracles/src/v4oracle/compress.rs:235-247), and store the row as
+ * bf16 at cache[(b * cache_rows + cache_row0 + pos[b] / ratio) * d]. prequant (optional) receives the row before
+ * the finishing quantisation, [B][d] f32. */
+int rivoli_v4_compress_step_bf16(const CompGeom* p, int n_seqs, const int32_t* pos, const float* kv_proj,
+                                 const float* score_proj, const float* ape, float* kv_state, float* score_state,
+                                 const float* norm, const float* freqs, int rotate, uint16_t* cache, int cache_rows,
+                                 int cache_row0, float* prequant, void* stream);
+
 /* Diagnostic, not on any product path (bench.py --profile gather): average milliseconds of a
  * launch in which each of n_ctas CTAs copies n_tiles tiles of 128 latent rows (576 bytes each,
  * rows[cta][tile][128] = pool row numbers) from the pool into shared memory with `depth` (1..3)

@@ -456,3 +456,33 @@ def v4_decode_step_bf16(g: V4Geom, pos, q, kv_cache, sink, iq, iw, ikv, want_sco
     lib().orc_v4_decode_step_bf16(C.byref(g), C.c_int(B), _p(pos), _p(q), _p(kv_cache), _p(sink), _p(iq),
                                   _p(iw), _p(ikv), _p(sel), _p(sc), _p(out))
     return (sel, out, sc) if want_scores else (sel, out)
+
+
+class CompGeom(C.Structure):
+    """Mirror of ``orc_comp_geom`` (the reference's CompGeom)."""
+    _fields_ = [(n, C.c_int32) for n in ("ratio", "coff", "d", "cd", "ents", "rd")] + [("eps", C.c_float)]
+
+    @classmethod
+    def make(cls, ratio=4, d=512, rd=64, eps=1e-6):
+        coff = 2 if ratio == 4 else 1
+        return cls(ratio, coff, d, coff * d, coff * ratio, rd, eps)
+
+
+def act_quant_f8_prefix(src, rows, row_stride, n, block):
+    a = _c(src, np.float32).copy()
+    rc = lib().orc_act_quant_f8_prefix(_p(a), _p(a), C.c_int(rows), C.c_int(row_stride), C.c_int(n), C.c_int(block))
+    return int(rc), a
+
+
+def v4_compress_deposit_token(kv, score, ape, kv_state, score_state, p: CompGeom, start_pos) -> int:
+    """In place on kv_state / score_state (float32 C-contiguous arrays)."""
+    return int(lib().orc_v4_compress_deposit_token(_p(_c(kv, np.float32)), _p(_c(score, np.float32)), _p(_c(ape, np.float32)),
+                                                   _p(kv_state), _p(score_state), C.byref(p), C.c_int(start_pos)))
+
+
+def v4_compress_decode(kv_state, score_state, norm, freqs, p: CompGeom, start_pos):
+    """Pools in place (the overlap half moves down). Returns (rc, row before the finishing quantisation)."""
+    out = np.zeros(p.d, np.float32)
+    rc = lib().orc_v4_compress_decode(_p(kv_state), _p(score_state), _p(_c(norm, np.float32)), _p(_c(freqs, np.float32)),
+                                      _p(out), C.byref(p), C.c_int(start_pos))
+    return int(rc), out

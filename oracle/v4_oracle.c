@@ -283,3 +283,126 @@ ORC_API void orc_v4_decode_step_bf16(const orc_v4_geom* g, int n_seqs, const int
     }
     free(qf); free(kf); free(of);
 }
+
+/* ---- KV compressor, decode arm -----------------------------------------------------------------
+ * crates/oracles/src/v4oracle/compress.rs:42-200 (decode branch :131-174, finish :176-200);
+ * device form crates/backend/kernels/kvcompress.hip (deposit, decode, pool_row, finish_row). */
+typedef struct {
+    int32_t ratio, coff, d, cd, ents, rd;
+    float eps;
+} orc_comp_geom;
+
+static int comp_guard(const orc_comp_geom* p) {
+    if (p->ratio <= 1 || p->d <= 0 || p->rd <= 0 || p->coff < 1 || p->coff > 2) return 1001;
+    if (p->rd > p->d || (p->rd & 1)) return 1002;
+    if (p->cd != p->coff * p->d || p->ents != p->coff * p->ratio) return 1003;
+    if (p->ents > 128) return 1004;
+    if ((p->coff == 2) != (p->ratio == 4)) return 1010;
+    return 0;
+}
+
+/* One decode token: score += ape[slot], then both rows land in slot (state_off + slot) of the state.
+ * compress.rs:131-144. */
+ORC_API int orc_v4_compress_deposit_token(const float* kv, const float* score, const float* ape, float* kv_state,
+                                          float* score_state, const orc_comp_geom* p, int start_pos) {
+    const int g = comp_guard(p);
+    if (g) return g;
+    const int slot = start_pos % p->ratio, state_off = p->coff == 2 ? p->ratio : 0;
+    const size_t dst = (size_t)(state_off + slot) * p->cd;
+    for (int e = 0; e < p->cd; ++e) {
+        kv_state[dst + e] = kv[e];
+        score_state[dst + e] = score[e] + ape[(size_t)slot * p->cd + e];
+    }
+    return 0;
+}
+
+/* e4m3 with round-to-nearest-even everywhere (the V4 rule: numerics.rs:45-140), as a round trip. */
+static float e4m3_rne_roundtrip(float x) {
+    if (x != x) return NAN;
+    const float a = fabsf(x);
+    const float sgn = signbit(x) ? -1.0f : 1.0f;
+    if (a >= 464.0f) return sgn * 448.0f;
+    if (a <= 1.0f / 1024.0f) return sgn * 0.0f;
+    int e;
+    (void)frexpf(a, &e);
+    e -= 1;                                   /* a = 1.m * 2^e */
+    const float q = e < -6 ? 1.0f / 512.0f : ldexpf(1.0f, e - 3);   /* spacing of the grid around a */
+    const float r = nearbyintf(a / q) * q;   /* default rounding mode: nearest even; a / q is exact */
+    return sgn * (r > 448.0f ? 448.0f : r);
+}
+
+/* fp8 block quantise-dequantise of the first n values of each row, power-of-two scale, amax floor 1e-4:
+ * numerics.rs:245-285, device form crates/backend/kernels/mla.hip:319-338. src == dst allowed. */
+ORC_API int orc_act_quant_f8_prefix(const float* src, float* dst, int rows, int row_stride, int n, int block) {
+    if (rows <= 0 || n <= 0 || block <= 0 || row_stride < n) return 1001;
+    if (src != dst && n != row_stride) return 1002;
+    if (n % block) return 1004;
+    for (int r = 0; r < rows; ++r)
+        for (int b0 = 0; b0 < n; b0 += block) {
+            const float* seg = src + (size_t)r * row_stride + b0;
+            float* out = dst + (size_t)r * row_stride + b0;
+            float amax = 0.0f;
+            for (int i = 0; i < block; ++i) amax = fmaxf(amax, fabsf(seg[i]));
+            amax = fmaxf(amax, 1e-4f);
+            const float s = orc_fast_round_scale(amax, 1.0f / 448.0f);
+            for (int i = 0; i < block; ++i) {
+                float q = seg[i] / s;
+                q = q < -448.0f ? -448.0f : (q > 448.0f ? 448.0f : q);
+                out[i] = e4m3_rne_roundtrip(q) * s;
+            }
+        }
+    return 0;
+}
+
+/* Pool the `ents` state entries into one row per feature (softmax over the ENTRY axis, entries below
+ * `ratio` contribute their first d dims, the others their last d when coff == 2), bf16 store, RMSNorm
+ * with bf16 store, adjacent-pair rotation of the last rd dims at the block's FIRST position, bf16 store;
+ * then the overlap half of the state moves down. compress.rs:145-193. `freqs` holds (cos, sin) pairs,
+ * rd/2 per position. Writes the d-wide row BEFORE the final quantisation into `out`. */
+ORC_API int orc_v4_compress_decode(float* kv_state, float* score_state, const float* norm, const float* freqs,
+                                   float* out, const orc_comp_geom* p, int start_pos) {
+    const int g = comp_guard(p);
+    if (g) return g;
+    if (start_pos <= 0) return 1007;
+    if ((start_pos + 1) % p->ratio != 0) return 1009;
+    const int d = p->d, cd = p->cd, ents = p->ents, overlap = p->coff == 2;
+    for (int e = 0; e < d; ++e) {
+        float m = -INFINITY;
+        for (int j = 0; j < ents; ++j) {
+            const int half = (overlap && j >= p->ratio) ? d : 0;
+            m = fmaxf(m, score_state[(size_t)j * cd + half + e]);
+        }
+        if (!isfinite(m)) { out[e] = 0.0f; continue; }
+        float s = 0.0f;
+        for (int j = 0; j < ents; ++j) {
+            const int half = (overlap && j >= p->ratio) ? d : 0;
+            s += expf(score_state[(size_t)j * cd + half + e] - m);
+        }
+        float acc = 0.0f;
+        for (int j = 0; j < ents; ++j) {
+            const int half = (overlap && j >= p->ratio) ? d : 0;
+            acc += kv_state[(size_t)j * cd + half + e] * (expf(score_state[(size_t)j * cd + half + e] - m) / s);
+        }
+        out[e] = acc;
+    }
+    if (overlap) {
+        const size_t n = (size_t)p->ratio * cd;
+        memmove(kv_state, kv_state + n, n * sizeof(float));
+        memmove(score_state, score_state + n, n * sizeof(float));
+    }
+    for (int e = 0; e < d; ++e) out[e] = rbf16(out[e]);
+    float var = 0.0f;
+    for (int e = 0; e < d; ++e) var += out[e] * out[e];
+    const float rs = 1.0f / sqrtf(var / (float)d + p->eps);
+    for (int e = 0; e < d; ++e) out[e] = rbf16(norm[e] * (out[e] * rs));
+    const int pos = (start_pos / p->ratio) * p->ratio;
+    float* seg = out + (d - p->rd);
+    for (int i = 0; i < p->rd / 2; ++i) {
+        const float c = freqs[(size_t)pos * p->rd + 2 * i], sn = freqs[(size_t)pos * p->rd + 2 * i + 1];
+        const float a = seg[2 * i], b = seg[2 * i + 1];
+        seg[2 * i] = a * c - b * sn;
+        seg[2 * i + 1] = a * sn + b * c;
+    }
+    for (int e = 0; e < d; ++e) out[e] = rbf16(out[e]);
+    return 0;
+}

@@ -450,6 +450,46 @@ def launch_v4_sparse_attend_bf16(g: V4Geom, n_seqs: int, q, kv_cache, sink, sel,
                                                      _stream(stream)), "v4_sparse_attend_bf16")
 
 
+class CompGeom(C.Structure):
+    """``CompGeom`` of include/rivoli_kernels.h (the reference's crates/backend/src/abi.rs:24-45)."""
+    _fields_ = [(n, C.c_int32) for n in ("ratio", "coff", "d", "cd", "ents", "rd")] + [("eps", C.c_float)]
+
+    @classmethod
+    def make(cls, *, ratio=4, d=512, rd=64, eps=1e-6) -> "CompGeom":
+        coff = 2 if ratio == 4 else 1
+        return cls(ratio, coff, d, coff * d, coff * ratio, rd, eps)
+
+
+class CompFinish(C.Structure):
+    _fields_ = [("norm", C.c_void_p), ("freqs", C.c_void_p), ("out", C.c_void_p)]
+
+
+def launch_act_quant_f8_prefix(src, dst, rows: int, row_stride: int, n: int, block: int, stream=None) -> None:
+    ensure_status(lib().rivoli_act_quant_f8_prefix(_ptr(src), _ptr(dst), C.c_int(rows), C.c_int(row_stride), C.c_int(n),
+                                                   C.c_int(block), _stream(stream)), "act_quant_f8_prefix")
+
+
+def launch_kv_compress_deposit(kv, score, ape, kv_state, score_state, p: CompGeom, s: int, slot0: int, stream=None) -> None:
+    ensure_status(lib().rivoli_kv_compress_deposit(_ptr(kv), _ptr(score), _ptr(ape), _ptr(kv_state), _ptr(score_state),
+                                                   C.byref(p) if p is not None else None, C.c_int(s), C.c_int(slot0),
+                                                   _stream(stream)), "kv_compress_deposit")
+
+
+def launch_kv_compress_decode(kv_state, score_state, norm, freqs, out, p: CompGeom, start_pos: int, stream=None) -> None:
+    f = CompFinish(_ptr(norm), _ptr(freqs), _ptr(out))
+    ensure_status(lib().rivoli_kv_compress_decode(_ptr(kv_state), _ptr(score_state), C.byref(f), C.byref(p),
+                                                  C.c_int(start_pos), _stream(stream)), "kv_compress_decode")
+
+
+def launch_v4_compress_step_bf16(p: CompGeom, n_seqs: int, pos, kv_proj, score_proj, ape, kv_state, score_state, norm,
+                                 freqs, rotate: bool, cache, cache_rows: int, cache_row0: int, prequant=None,
+                                 stream=None) -> None:
+    ensure_status(lib().rivoli_v4_compress_step_bf16(
+        C.byref(p), C.c_int(n_seqs), _ptr(pos), _ptr(kv_proj), _ptr(score_proj), _ptr(ape), _ptr(kv_state),
+        _ptr(score_state), _ptr(norm), _ptr(freqs), C.c_int(int(rotate)), _ptr(cache), C.c_int(cache_rows),
+        C.c_int(cache_row0), _ptr(prequant), _stream(stream)), "v4_compress_step_bf16")
+
+
 def probe_gather(method: int, depth: int, n_ctas: int, n_tiles: int, pool, n_pool_rows: int, scales, rows,
                  stream=None) -> float:
     """Diagnostic gather roofline: milliseconds per launch (see include/rivoli_kernels.h)."""

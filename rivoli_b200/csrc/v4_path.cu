@@ -410,6 +410,7 @@ __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const i
     uint32_t* picked = reinterpret_cast<uint32_t*>(sc + g.max_comp);
 
     const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    rv_grid_dep_trigger();   // the attention kernel may start staging its queries
     const int W = g.window, K = g.index_topk, p = pos[b];
     int32_t* row = sel + (size_t)b * (W + K);
     // the ring: oldest first once full, live slots then -1 before that
@@ -426,6 +427,7 @@ __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const i
         return;
     }
     float* srow = scores + (size_t)b * g.max_comp;
+    rv_grid_dep_wait();      // the scorer's rows and flags
     if (force_fold || flags[b]) {
         // the ordered CUDA-core fold: rows the integer scorer could not take, or every row on request
         v4_stage_q(index_q + (size_t)b * g.index_heads * g.index_dim, index_w + (size_t)b * g.index_heads, g.index_heads,
@@ -543,9 +545,12 @@ __global__ void __launch_bounds__(GA_THREADS) v4_gather_attn_kernel(const T* __r
 //
 // The selected rows are gathered ONCE per sequence into shared memory (64-token tiles, two buffers,
 // cp.async) and serve every head twice: as K of S = q K^T and as V of O += P V. 16 warps:
-//   scores   warp (hg, tq): heads 16hg..+15 x tokens 16tq..+15, 32 k-steps of m16n8k16 over the 512 dims;
+//   scores   warp (hg, tq, kh): heads 32hg..+31 x tokens 16tq..+15 over half of the 512 dims (16 k-steps of
+//            m16n8k16); the two halves meet in shared memory through one add each (two addends: the sum does
+//            not depend on their order);
 //   softmax  8 threads per head over the tile's 64 tokens, running max / sum in registers;
-//   values   warp (hg, dq): heads 16hg..+15 x dims 128dq..+127, 4 k-steps over the tile's tokens.
+//   values   warp (hg, dg): heads 32hg..+31 x dims 64dg..+63, 4 k-steps over the tile's tokens.
+// Two m-tiles per warp halve the operand reloads from shared memory, which is what bounds this kernel.
 // Rows are 1024 B; the 16-byte chunk c of row r sits at chunk (c ^ (r & 7)) so that the eight rows of an
 // 8x8 ldmatrix tile fall in eight different bank groups.
 // ---------------------------------------------------------------------------------------------------
@@ -559,7 +564,17 @@ constexpr int SA_SP = SA_SS + SA_H * SA_SS_LD * 4;         // bf16 [64 heads][64
 constexpr int SA_FAC = SA_SP + SA_H * SA_TILE * 2;         // f32 [64] rescale of the running output
 constexpr int SA_INV = SA_FAC + SA_H * 4;                  // f32 [64] 1 / denominator
 constexpr int SA_IDX = SA_INV + SA_H * 4;                  // i32 [2][64] the tile's slots
-constexpr int SA_TOTAL = SA_IDX + 2 * SA_TILE * 4;
+constexpr int SA_SEL = SA_IDX + 2 * SA_TILE * 4;            // i32 [SA_SEL_MAX] the sequence's selection row
+constexpr int SA_SEL_MAX = 2048;
+constexpr int SA_TOTAL = SA_SEL + SA_SEL_MAX * 4;
+
+// Optional per-tile timeline of CTA 0, thread 0 for tuning builds (-DRIVOLI_DEBUG_TIMES); compiled out otherwise.
+#ifdef RIVOLI_DEBUG_TIMES
+__device__ long long g_v4_times[32 * 8];
+#define V4_STAMP(tile, slot) do { if (blockIdx.x == 0 && threadIdx.x == 0 && (tile) < 32) g_v4_times[(tile) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define V4_STAMP(tile, slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t v4_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void v4_cp_async16(uint32_t dst, const void* src) {
@@ -572,6 +587,18 @@ __device__ __forceinline__ void v4_ldsm4(uint32_t addr, uint32_t (&r)[4]) {
 __device__ __forceinline__ void v4_ldsm4_t(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ float v4_ex2(float x) {   // 2^x, -inf -> 0; relative error 2^-22
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Two f32 -> packed bf16x2 (lo = a), round to nearest even, and the two rounded values' sum.
+__device__ __forceinline__ uint32_t v4_pack_bf16x2(float a, float b, float& sum) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    sum += __uint_as_float(r << 16) + __uint_as_float(r & 0xffff0000u);
+    return r;
 }
 __device__ __forceinline__ void v4_mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -588,6 +615,7 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
                                                                              uint16_t* __restrict__ out) {
     extern __shared__ __align__(1024) unsigned char sa_smem[];
     const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    V4_STAMP(30, 0);
     const uint32_t sbase = v4_smem_u32(sa_smem);
     float* sS = reinterpret_cast<float*>(sa_smem + SA_SS);
     float* sFac = reinterpret_cast<float*>(sa_smem + SA_FAC);
@@ -596,82 +624,127 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
     const uint16_t* kvb = kv_cache + (size_t)b * kv_rows * SA_D;
     const int32_t* ix = sel + (size_t)b * cols;
     const int n_tiles = (cols + SA_TILE - 1) / SA_TILE;
-
     // chunk (row, c) -> byte offset inside a [rows][1024 B] operand
     auto swz = [](int row, int c) { return row * SA_ROW_BYTES + ((c ^ (row & 7)) << 4); };
 
-    auto gather = [&](int t, int buf) {
-        const uint32_t dst0 = sbase + SA_SK + buf * SA_TILE * SA_ROW_BYTES;
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {
-            const int ch = tid + it * SA_THREADS, row = ch >> 6, c = ch & 63;
-            const int j = t * SA_TILE + row;
-            const int p = j < cols ? ix[j] : -1;
-            if (c == 0) sIdx[buf * SA_TILE + row] = p;
-            if (p >= 0) v4_cp_async16(dst0 + swz(row, c), kvb + (size_t)p * SA_D + c * 8);
-            else *reinterpret_cast<uint4*>(sa_smem + SA_SK + buf * SA_TILE * SA_ROW_BYTES + swz(row, c)) = make_uint4(0, 0, 0, 0);
-        }
+    // chunk `it` (0..7) of this thread's share of tile t: one 16-byte piece of one row
+    auto gather_piece = [&](int t, int buf, int it) {
+        const int ch = tid + it * SA_THREADS, row = ch >> 6, c = ch & 63;
+        const int j = t * SA_TILE + row;
+        const int p = j < cols ? ix[j] : -1;
+        if (c == 0) sIdx[buf * SA_TILE + row] = p;
+        const int off = SA_SK + buf * SA_TILE * SA_ROW_BYTES + swz(row, c);
+        if (p >= 0) v4_cp_async16(sbase + off, kvb + (size_t)p * SA_D + c * 8);
+        else *reinterpret_cast<uint4*>(sa_smem + off) = make_uint4(0, 0, 0, 0);   // masked slot: a row of zeros
     };
 
-    // q of this sequence, then the first tile
+    // q of this sequence (not produced by the kernel before this one), then that kernel's selection row, then
+    // the first tile
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
         const int ch = tid + it * SA_THREADS, row = ch >> 6, c = ch & 63;
         v4_cp_async16(sbase + SA_SQ + swz(row, c), q + ((size_t)b * SA_H + row) * SA_D + c * 8);
     }
-    gather(0, 0);
+    rv_grid_dep_wait();
+    if (cols <= SA_SEL_MAX) {   // read the row once; the per-tile gathers then take their slots from shared memory
+        int32_t* sSel = reinterpret_cast<int32_t*>(sa_smem + SA_SEL);
+        for (int i = tid; i < cols; i += SA_THREADS) sSel[i] = ix[i];
+        ix = sSel;
+        __syncthreads();
+    }
+#pragma unroll
+    for (int it = 0; it < 8; ++it) gather_piece(0, 0, it);
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     // softmax state of head (tid >> 3), replicated in its 8 threads
     float m_run = -INFINITY, l_run = 0.0f;
-    // output accumulators of warp (hg, dq): 16 n-tiles of 8 dims
-    float acc[16][4];
+    // output accumulators of warp (hg, dg): 2 m-tiles x 8 n-tiles of 8 dims
+    float acc[2][8][4];
 #pragma unroll
-    for (int n = 0; n < 16; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < 8; ++n) acc[m][n][0] = acc[m][n][1] = acc[m][n][2] = acc[m][n][3] = 0.0f;
 
-    const int hg = warp & 3, wq = warp >> 2;   // wq = token quarter (scores) / dim quarter (values)
+    const int hg = warp & 1;                        // heads 32 hg .. +31
+    const int tq = (warp >> 1) & 3, kh = warp >> 3; // scores: token quarter, half of the dims
+    const int dg = warp >> 1;                       // values: dims 64 dg .. +63
     const int mi = lane >> 3, l7 = lane & 7;
 
     for (int t = 0; t < n_tiles; ++t) {
         const int buf = t & 1;
+        V4_STAMP(t, 0);
         if (t + 1 < n_tiles) {
-            gather(t + 1, buf ^ 1);
+#pragma unroll
+            for (int it = 0; it < 8; ++it) gather_piece(t + 1, buf ^ 1, it);
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
+        V4_STAMP(t, 1);
         __syncthreads();
+        V4_STAMP(t, 2);
         const uint32_t sK = sbase + SA_SK + buf * SA_TILE * SA_ROW_BYTES;
 
-        // ---- scores: S[16 heads][16 tokens] per warp
+        // ---- scores: S[32 heads][16 tokens] over this warp's half of the dims
         {
-            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-            const int arow = 16 * hg + ((mi & 1) << 3) + l7;
-            const int brow = 16 * wq + ((mi >> 1) << 3) + l7;
-#pragma unroll 4
-            for (int ks = 0; ks < SA_D / 16; ++ks) {
-                uint32_t a[4], bb[4];
-                v4_ldsm4(sbase + SA_SQ + swz(arow, 2 * ks + (mi >> 1)), a);
-                v4_ldsm4(sK + swz(brow, 2 * ks + (mi & 1)), bb);
-                v4_mma_bf16(s0, a, bb[0], bb[1]);
-                v4_mma_bf16(s1, a, bb[2], bb[3]);
+            float sc[2][2][4];
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int n = 0; n < 2; ++n) sc[m][n][0] = sc[m][n][1] = sc[m][n][2] = sc[m][n][3] = 0.0f;
+            const int arow = 32 * hg + ((mi & 1) << 3) + l7;
+            const int brow = 16 * tq + ((mi >> 1) << 3) + l7;
+            const int ks0 = kh * (SA_D / 32);
+            uint32_t a0[2][4], a1[2][4], bb[2][4];
+            v4_ldsm4(sbase + SA_SQ + swz(arow, 2 * ks0 + (mi >> 1)), a0[0]);
+            v4_ldsm4(sbase + SA_SQ + swz(arow + 16, 2 * ks0 + (mi >> 1)), a1[0]);
+            v4_ldsm4(sK + swz(brow, 2 * ks0 + (mi & 1)), bb[0]);
+#pragma unroll
+            for (int i = 0; i < SA_D / 32; ++i) {
+                const int cur = i & 1, nxt = cur ^ 1, ks = ks0 + i + 1;
+                if (i + 1 < SA_D / 32) {
+                    v4_ldsm4(sbase + SA_SQ + swz(arow, 2 * ks + (mi >> 1)), a0[nxt]);
+                    v4_ldsm4(sbase + SA_SQ + swz(arow + 16, 2 * ks + (mi >> 1)), a1[nxt]);
+                    v4_ldsm4(sK + swz(brow, 2 * ks + (mi & 1)), bb[nxt]);
+                }
+                v4_mma_bf16(sc[0][0], a0[cur], bb[cur][0], bb[cur][1]);
+                v4_mma_bf16(sc[0][1], a0[cur], bb[cur][2], bb[cur][3]);
+                v4_mma_bf16(sc[1][0], a1[cur], bb[cur][0], bb[cur][1]);
+                v4_mma_bf16(sc[1][1], a1[cur], bb[cur][2], bb[cur][3]);
             }
-            const int r0 = 16 * hg + (lane >> 2), c0 = 16 * wq + (lane & 3) * 2;
-            *reinterpret_cast<float2*>(sS + r0 * SA_SS_LD + c0) = make_float2(s0[0] * scale_log2, s0[1] * scale_log2);
-            *reinterpret_cast<float2*>(sS + (r0 + 8) * SA_SS_LD + c0) = make_float2(s0[2] * scale_log2, s0[3] * scale_log2);
-            *reinterpret_cast<float2*>(sS + r0 * SA_SS_LD + c0 + 8) = make_float2(s1[0] * scale_log2, s1[1] * scale_log2);
-            *reinterpret_cast<float2*>(sS + (r0 + 8) * SA_SS_LD + c0 + 8) = make_float2(s1[2] * scale_log2, s1[3] * scale_log2);
+            // the two halves meet in shared memory: the lower half stores, the upper half adds (a + b: no order to pick)
+            if (kh == 1) __syncthreads();
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int n = 0; n < 2; ++n) {
+                    float2* p0 = reinterpret_cast<float2*>(sS + (32 * hg + 16 * m + (lane >> 2)) * SA_SS_LD + 16 * tq + 8 * n + (lane & 3) * 2);
+                    float2* p1 = p0 + 4 * SA_SS_LD;   // 8 rows down
+                    if (kh == 0) {
+                        *p0 = make_float2(sc[m][n][0], sc[m][n][1]);
+                        *p1 = make_float2(sc[m][n][2], sc[m][n][3]);
+                    } else {
+                        const float2 u = *p0, v = *p1;
+                        *p0 = make_float2(u.x + sc[m][n][0], u.y + sc[m][n][1]);
+                        *p1 = make_float2(v.x + sc[m][n][2], v.y + sc[m][n][3]);
+                    }
+                }
+            if (kh == 0) __syncthreads();
         }
+        V4_STAMP(t, 3);
         __syncthreads();
+        V4_STAMP(t, 4);
 
         // ---- softmax over the tile: head = tid / 8, tokens 8 * (tid % 8) .. +7
         {
             const int head = tid >> 3, part = tid & 7;
             float sv[8];
-            const float4 x0 = *reinterpret_cast<const float4*>(sS + head * SA_SS_LD + part * 8);
-            const float4 x1 = *reinterpret_cast<const float4*>(sS + head * SA_SS_LD + part * 8 + 4);
+            const float4* srow = reinterpret_cast<const float4*>(sS + head * SA_SS_LD + part * 8);
+            const float4 x0 = srow[0], x1 = srow[1];
             sv[0] = x0.x; sv[1] = x0.y; sv[2] = x0.z; sv[3] = x0.w; sv[4] = x1.x; sv[5] = x1.y; sv[6] = x1.z; sv[7] = x1.w;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sv[j] *= scale_log2;
             float tmax = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -682,17 +755,12 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
             const float m_new = fmaxf(m_run, tmax);
-            const float fac = m_new == -INFINITY ? 1.0f : exp2f(m_run - m_new);
+            const float fac = m_new == -INFINITY ? 1.0f : v4_ex2(m_run - m_new);
+            const float m_use = m_new == -INFINITY ? 0.0f : m_new;    // every slot masked so far: all p are 2^-inf = 0
             uint32_t pk[4];
-            float psum = 0.0f;
+            float psum = 0.0f;                                         // the sum of what the value product sees
 #pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-                const float p0 = m_new == -INFINITY ? 0.0f : exp2f(sv[j] - m_new);
-                const float p1 = m_new == -INFINITY ? 0.0f : exp2f(sv[j + 1] - m_new);
-                const uint16_t b0 = rv_f32_to_bf16(p0), b1 = rv_f32_to_bf16(p1);
-                psum += rv_bf16_to_f32(b0) + rv_bf16_to_f32(b1);   // the sum of what the value product sees
-                pk[j >> 1] = (uint32_t)b0 | ((uint32_t)b1 << 16);
-            }
+            for (int j = 0; j < 8; j += 2) pk[j >> 1] = v4_pack_bf16x2(v4_ex2(sv[j] - m_use), v4_ex2(sv[j + 1] - m_use), psum);
             psum += __shfl_xor_sync(0xffffffffu, psum, 1);
             psum += __shfl_xor_sync(0xffffffffu, psum, 2);
             psum += __shfl_xor_sync(0xffffffffu, psum, 4);
@@ -703,54 +771,277 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
             if (part == 0) sFac[head] = fac;
         }
         __syncthreads();
+        V4_STAMP(t, 5);
 
-        // ---- values: O[16 heads][128 dims] += P[16 heads][64 tokens] V[64 tokens][128 dims]
+        // ---- values: O[32 heads][64 dims] += P[32 heads][64 tokens] V[64 tokens][64 dims]
         {
-            const float f0 = sFac[16 * hg + (lane >> 2)], f1 = sFac[16 * hg + (lane >> 2) + 8];
-            if (f0 != 1.0f || f1 != 1.0f) {
 #pragma unroll
-                for (int n = 0; n < 16; ++n) { acc[n][0] *= f0; acc[n][1] *= f0; acc[n][2] *= f1; acc[n][3] *= f1; }
+            for (int m = 0; m < 2; ++m) {
+                const float f0 = sFac[32 * hg + 16 * m + (lane >> 2)], f1 = sFac[32 * hg + 16 * m + (lane >> 2) + 8];
+                if (f0 != 1.0f || f1 != 1.0f) {
+#pragma unroll
+                    for (int n = 0; n < 8; ++n) { acc[m][n][0] *= f0; acc[m][n][1] *= f0; acc[m][n][2] *= f1; acc[m][n][3] *= f1; }
+                }
             }
-            const int prow = 16 * hg + ((mi & 1) << 3) + l7;
+            const int prow = 32 * hg + ((mi & 1) << 3) + l7;
 #pragma unroll
             for (int ks = 0; ks < SA_TILE / 16; ++ks) {
-                uint32_t a[4];
-                v4_ldsm4(sbase + SA_SP + prow * (SA_TILE * 2) + (((2 * ks + (mi >> 1)) ^ (prow & 7)) << 4), a);
+                uint32_t a0[4], a1[4];
+                v4_ldsm4(sbase + SA_SP + prow * (SA_TILE * 2) + (((2 * ks + (mi >> 1)) ^ (prow & 7)) << 4), a0);
+                v4_ldsm4(sbase + SA_SP + (prow + 16) * (SA_TILE * 2) + (((2 * ks + (mi >> 1)) ^ (prow & 7)) << 4), a1);
                 const int vrow = 16 * ks + ((mi & 1) << 3) + l7;
 #pragma unroll
-                for (int np = 0; np < 8; ++np) {
+                for (int np = 0; np < 4; ++np) {
                     uint32_t bb[4];
-                    v4_ldsm4_t(sK + swz(vrow, 16 * wq + 2 * np + (mi >> 1)), bb);
-                    v4_mma_bf16(acc[2 * np], a, bb[0], bb[1]);
-                    v4_mma_bf16(acc[2 * np + 1], a, bb[2], bb[3]);
+                    v4_ldsm4_t(sK + swz(vrow, 8 * dg + 2 * np + (mi >> 1)), bb);
+                    v4_mma_bf16(acc[0][2 * np], a0, bb[0], bb[1]);
+                    v4_mma_bf16(acc[0][2 * np + 1], a0, bb[2], bb[3]);
+                    v4_mma_bf16(acc[1][2 * np], a1, bb[0], bb[1]);
+                    v4_mma_bf16(acc[1][2 * np + 1], a1, bb[2], bb[3]);
                 }
             }
         }
+        V4_STAMP(t, 6);
         __syncthreads();
+        V4_STAMP(t, 7);
     }
 
+    V4_STAMP(30, 1);
     // the sink joins the denominator only, shifted by the same running max
     {
         const int head = tid >> 3;
         if ((tid & 7) == 0) {
-            const float l = l_run + exp2f(sink[head] * 1.4426950408889634f - m_run);
+            const float l = l_run + v4_ex2(sink[head] * 1.4426950408889634f - m_run);
             sInv[head] = m_run == -INFINITY ? NAN : 1.0f / l;
         }
     }
     __syncthreads();
-    {
-        const int r0 = 16 * hg + (lane >> 2);
-        const float i0 = sInv[r0], i1 = sInv[r0 + 8];
-        uint16_t* o0 = out + ((size_t)b * SA_H + r0) * SA_D + 128 * wq + (lane & 3) * 2;
-        uint16_t* o1 = o0 + 8 * SA_D;
+    // bf16 output staged in the q region (q is dead after the last score pass), then whole rows go out in
+    // 16-byte pieces
 #pragma unroll
-        for (int n = 0; n < 16; ++n) {
-            const uint32_t v0 = (uint32_t)rv_f32_to_bf16(acc[n][0] * i0) | ((uint32_t)rv_f32_to_bf16(acc[n][1] * i0) << 16);
-            const uint32_t v1 = (uint32_t)rv_f32_to_bf16(acc[n][2] * i1) | ((uint32_t)rv_f32_to_bf16(acc[n][3] * i1) << 16);
-            *reinterpret_cast<uint32_t*>(o0 + 8 * n) = v0;
-            *reinterpret_cast<uint32_t*>(o1 + 8 * n) = v1;
+    for (int m = 0; m < 2; ++m) {
+        const int r0 = 32 * hg + 16 * m + (lane >> 2);
+        const float i0 = sInv[r0], i1 = sInv[r0 + 8];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            float unused = 0.0f;
+            const int c = 8 * dg + n;                         // 16-byte chunk of the row: dims 8c .. 8c+7
+            const int off = ((lane & 3) << 2);
+            *reinterpret_cast<uint32_t*>(sa_smem + SA_SQ + swz(r0, c) + off) =
+                v4_pack_bf16x2(acc[m][n][0] * i0, acc[m][n][1] * i0, unused);
+            *reinterpret_cast<uint32_t*>(sa_smem + SA_SQ + swz(r0 + 8, c) + off) =
+                v4_pack_bf16x2(acc[m][n][2] * i1, acc[m][n][3] * i1, unused);
         }
     }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int ch = tid + it * SA_THREADS, row = ch >> 6, c = ch & 63;
+        *reinterpret_cast<uint4*>(out + ((size_t)b * SA_H + row) * SA_D + c * 8) =
+            *reinterpret_cast<const uint4*>(sa_smem + SA_SQ + swz(row, c));
+    }
+    V4_STAMP(30, 2);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// KV compressor, decode arm: deposit one token into the pooling state; when a block closes, pool it
+// (softmax over the ENTRY axis per feature), bf16 store, RMSNorm, rotate the last rd dims at the block's
+// first position, then the finishing quantisation (spread for the indexer's compressor, fp8 block-64
+// on the un-rotated dims for the attention compressor).
+// Reference: crates/backend/kernels/kvcompress.hip (deposit / decode / pool_row / finish_row),
+// crates/oracles/src/v4oracle/compress.rs:131-200.
+// ---------------------------------------------------------------------------------------------------
+constexpr int CP_THREADS = 256;
+constexpr int CP_ENTS_MAX = 128;
+constexpr float CP_FP8_MAX = 448.0f;
+
+__device__ __forceinline__ float cp_block_sum(float v, float* red) {   // red: CP_THREADS / 32 floats
+    v = rv_warp_sum(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < CP_THREADS / 32; ++i) t += red[i];
+    __syncthreads();
+    return t;
+}
+
+// e4m3 round trip with round-to-nearest-even everywhere and saturation at 448: the hardware converter's rule.
+__device__ __forceinline__ float cp_e4m3_roundtrip(float q) {
+    uint16_t c;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(c) : "f"(q), "f"(0.0f));
+    return rv_e4m3x2_to_f32x2(c).x;
+}
+
+// fp8 quantise-dequantise of one block of `block` values starting at seg (one warp; power-of-two scale,
+// amax floor 1e-4): crates/backend/kernels/mla.hip:319-338. Exact: the maximum is associative, the rest is
+// per element.
+__device__ __forceinline__ void cp_act_quant_block(const float* seg, float* out, int block) {
+    const int lane = threadIdx.x & 31;
+    float amax = 1e-4f;
+    for (int i = lane; i < block; i += 32) amax = fmaxf(amax, fabsf(seg[i]));
+    amax = rv_warp_max(amax);
+    const uint32_t bits = __float_as_uint(__fmul_rn(amax, __fdiv_rn(1.0f, CP_FP8_MAX)));
+    const int e = (int)((bits >> 23) & 0xffu) - 127 + ((bits & 0x7fffffu) ? 1 : 0);
+    const float s = __uint_as_float((uint32_t)(e + 127) << 23);
+    for (int i = lane; i < block; i += 32) {
+        float q = __fdiv_rn(seg[i], s);
+        q = q < -CP_FP8_MAX ? -CP_FP8_MAX : (q > CP_FP8_MAX ? CP_FP8_MAX : q);
+        out[i] = __fmul_rn(cp_e4m3_roundtrip(q), s);
+    }
+}
+
+__global__ void cp_act_quant_f8_prefix_kernel(const float* src, float* dst, int rows, int row_stride, int n, int block) {
+    const int nb = n / block;
+    const size_t id = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // one warp per block
+    if (id >= (size_t)rows * (size_t)nb) return;
+    const size_t off = (size_t)(id / nb) * row_stride + (size_t)(id % nb) * block;
+    cp_act_quant_block(src + off, dst + off, block);
+}
+
+struct CpState {
+    float* kv;      // [ents][cd]
+    float* score;   // [ents][cd]
+};
+
+// Pool + bf16 + RMSNorm + rotation of one sequence's state into row[d] (shared or global), by one CTA;
+// then the overlap half of the state moves down. red: CP_THREADS / 32 floats of shared memory.
+__device__ __forceinline__ void cp_pool_finish(CpState st, const float* __restrict__ norm,
+                                               const float* __restrict__ freqs, float* row, CompGeom p,
+                                               int start_pos, float* red) {
+    const int tid = threadIdx.x, d = p.d, cd = p.cd, overlap = p.coff == 2;
+    for (int e = tid; e < d; e += CP_THREADS) {
+        float mx = -INFINITY;
+        for (int j = 0; j < p.ents; ++j) mx = fmaxf(mx, st.score[(size_t)j * cd + ((overlap && j >= p.ratio) ? d : 0) + e]);
+        float o = 0.0f;
+        if (isfinite(mx)) {
+            float sum = 0.0f;
+            for (int j = 0; j < p.ents; ++j)
+                sum += expf(st.score[(size_t)j * cd + ((overlap && j >= p.ratio) ? d : 0) + e] - mx);
+            for (int j = 0; j < p.ents; ++j) {
+                const size_t a = (size_t)j * cd + ((overlap && j >= p.ratio) ? d : 0) + e;
+                o += st.kv[a] * (expf(st.score[a] - mx) / sum);
+            }
+        }
+        row[e] = v4_rbf16(o);
+    }
+    __syncthreads();
+    float part = 0.0f;
+    for (int e = tid; e < d; e += CP_THREADS) part += row[e] * row[e];
+    const float rs = 1.0f / sqrtf(cp_block_sum(part, red) / (float)d + p.eps);
+    for (int e = tid; e < d; e += CP_THREADS) row[e] = v4_rbf16(norm[e] * (row[e] * rs));
+    __syncthreads();
+    const int pos = (start_pos / p.ratio) * p.ratio;
+    float* seg = row + (d - p.rd);
+    for (int i = tid; i < p.rd / 2; i += CP_THREADS) {
+        const float c = freqs[(size_t)pos * p.rd + 2 * i], sn = freqs[(size_t)pos * p.rd + 2 * i + 1];
+        const float a = seg[2 * i], b = seg[2 * i + 1];
+        seg[2 * i] = v4_rbf16(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn)));
+        seg[2 * i + 1] = v4_rbf16(__fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c)));
+    }
+    if (overlap) {   // every pooling read is done (barriers above): the overlap half moves down
+        const size_t n = (size_t)p.ratio * cd;
+        for (size_t i = tid; i < n; i += CP_THREADS) {
+            st.kv[i] = st.kv[n + i];
+            st.score[i] = st.score[n + i];
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(CP_THREADS) cp_deposit_kernel(const float* __restrict__ kv,
+                                                                const float* __restrict__ score,
+                                                                const float* __restrict__ ape, float* kv_state,
+                                                                float* score_state, CompGeom p, int s, int slot0) {
+    const int remainder = s % p.ratio, cutoff = s - remainder, overlap = p.coff == 2;
+    const int state_off = overlap ? p.ratio : 0;
+    const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (overlap && cutoff >= p.ratio) {   // the last full block's rows become the overlap half
+        const size_t n = (size_t)p.ratio * p.cd;
+        for (size_t i = tid; i < n; i += stride) {
+            const size_t src = (size_t)(cutoff - p.ratio) * p.cd + i;
+            kv_state[i] = kv[src];
+            score_state[i] = score[src] + ape[i];
+        }
+    }
+    if (remainder > 0) {                  // the open block's rows, from slot0 on
+        const size_t n = (size_t)remainder * p.cd, dst0 = (size_t)(state_off + slot0) * p.cd;
+        for (size_t i = tid; i < n; i += stride) {
+            const size_t src = (size_t)cutoff * p.cd + i;
+            kv_state[dst0 + i] = kv[src];
+            score_state[dst0 + i] = score[src] + ape[(size_t)slot0 * p.cd + i];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(CP_THREADS) cp_decode_kernel(float* kv_state, float* score_state, CompFinish f,
+                                                               CompGeom p, int start_pos) {
+    __shared__ float red[CP_THREADS / 32];
+    cp_pool_finish(CpState{kv_state, score_state}, f.norm, f.freqs, f.out, p, start_pos, red);
+}
+
+// Batched decode step: one CTA per sequence. cache row = cache + (b * cache_rows + cache_row0 + block) * d (bf16).
+__global__ void __launch_bounds__(CP_THREADS) cp_step_kernel(CompGeom p, const int32_t* __restrict__ pos,
+                                                             const float* __restrict__ kv_proj,
+                                                             const float* __restrict__ score_proj,
+                                                             const float* __restrict__ ape, float* kv_state,
+                                                             float* score_state, const float* __restrict__ norm,
+                                                             const float* __restrict__ freqs, int rotate,
+                                                             uint16_t* __restrict__ cache, int cache_rows,
+                                                             int cache_row0, float* __restrict__ prequant) {
+    extern __shared__ __align__(16) float cp_row[];   // [d]
+    __shared__ float red[CP_THREADS / 32];
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sp = pos[b], slot = sp % p.ratio, d = p.d;
+    const size_t st_n = (size_t)p.ents * p.cd;
+    CpState st{kv_state + (size_t)b * st_n, score_state + (size_t)b * st_n};
+    const size_t dst = (size_t)((p.coff == 2 ? p.ratio : 0) + slot) * p.cd;
+    for (int e = tid; e < p.cd; e += CP_THREADS) {
+        st.kv[dst + e] = kv_proj[(size_t)b * p.cd + e];
+        st.score[dst + e] = score_proj[(size_t)b * p.cd + e] + ape[(size_t)slot * p.cd + e];
+    }
+    if ((sp + 1) % p.ratio != 0) return;   // the block is still open
+    __syncthreads();
+    cp_pool_finish(st, norm, freqs, cp_row, p, sp, red);
+    if (prequant) for (int e = tid; e < d; e += CP_THREADS) prequant[(size_t)b * d + e] = cp_row[e];
+    if (rotate) {
+        // the spread of blockindex.hip:97-138 on the row in shared memory
+        for (int h = 1; h < d; h <<= 1) {
+            for (int t = tid; t < (d >> 1); t += CP_THREADS) {
+                const int j = 2 * t - (t & (h - 1));
+                const float a = cp_row[j], c = cp_row[j + h];
+                cp_row[j] = __fadd_rn(a, c);
+                cp_row[j + h] = __fsub_rn(a, c);
+            }
+            __syncthreads();
+        }
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)d));
+        for (int i = tid; i < d; i += CP_THREADS) cp_row[i] = v4_rbf16(__fmul_rn(cp_row[i], scale));
+        __syncthreads();
+        const float floor_ = __fmul_rn(V4_FP4_MAX, __uint_as_float(1u << 23));
+        for (int blk = warp; blk < d / 32; blk += CP_THREADS / 32) {
+            const float v = cp_row[blk * 32 + lane];
+            const float s = v4_round_scale(fmaxf(rv_warp_max(fabsf(v)), floor_));
+            float q = __fdiv_rn(v, s);
+            q = q < -V4_FP4_MAX ? -V4_FP4_MAX : (q > V4_FP4_MAX ? V4_FP4_MAX : q);
+            cp_row[blk * 32 + lane] = __fmul_rn(v4_e2m1_roundtrip(q), s);
+        }
+    } else {
+        // fp8 block-64 on the dims that were not rotated (crates/oracles/src/v4oracle/compress.rs:235-247)
+        for (int blk = warp; blk < (d - p.rd) / 64; blk += CP_THREADS / 32) cp_act_quant_block(cp_row + blk * 64, cp_row + blk * 64, 64);
+    }
+    __syncthreads();
+    uint16_t* out = cache + ((size_t)b * cache_rows + cache_row0 + sp / p.ratio) * d;
+    for (int e = tid; e < d; e += CP_THREADS) out[e] = rv_f32_to_bf16(cp_row[e]);
+}
+
+static int cp_guard(const CompGeom& p) {
+    if (p.ratio <= 1 || p.d <= 0 || p.rd <= 0 || p.coff < 1 || p.coff > 2) return 1001;
+    if (p.rd > p.d || (p.rd & 1)) return 1002;
+    if (p.cd != p.coff * p.d || p.ents != p.coff * p.ratio) return 1003;
+    if (p.ents > CP_ENTS_MAX) return 1004;
+    if ((p.coff == 2) != (p.ratio == 4)) return 1010;
+    return 0;
 }
 
 static int v4_check_geom(const V4Geom* g, int n_seqs) {
@@ -762,6 +1053,12 @@ static int v4_check_geom(const V4Geom* g, int n_seqs) {
 }
 
 }  // namespace
+
+#ifdef RIVOLI_DEBUG_TIMES
+RIVOLI_API int rivoli_v4_debug_times(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_v4_times, sizeof(long long) * 32 * 8);
+}
+#endif
 
 RIVOLI_API int rivoli_act_quant_f4_rotated(float* x, int rows, int d, void* stream) {
     if (rows <= 0 || d <= 0) return 1001;
@@ -804,6 +1101,63 @@ RIVOLI_API int rivoli_gather_attn_shared_kv(const float* q, const float* kv, con
     return rv_launch_status();
 }
 
+RIVOLI_API int rivoli_act_quant_f8_prefix(const float* src, float* dst, int rows, int row_stride, int n, int block,
+                                          void* stream) {
+    if (rows <= 0 || n <= 0 || block <= 0 || row_stride < n) return 1001;
+    if (src != dst && n != row_stride) return 1002;   // the untouched tail of a row only survives in place
+    if (n % block) return 1004;
+    const size_t total = (size_t)rows * (size_t)(n / block);
+    rv_drain_error();
+    cp_act_quant_f8_prefix_kernel<<<(unsigned)((total + 7) / 8), 256, 0, (cudaStream_t)stream>>>(src, dst, rows, row_stride,
+                                                                                                n, block);
+    return rv_launch_status();
+}
+
+RIVOLI_API int rivoli_kv_compress_deposit(const float* kv, const float* score, const float* ape, float* kv_state,
+                                          float* score_state, const CompGeom* pp, int s, int slot0, void* stream) {
+    if (!pp) return 1000;
+    const CompGeom p = *pp;
+    if (int g = cp_guard(p)) return g;
+    if (s <= 0) return 1005;
+    if (slot0 < 0 || slot0 + s % p.ratio > p.ratio) return 1008;
+    const int rem = s % p.ratio;
+    const size_t n = (size_t)(p.ratio > rem ? p.ratio : rem) * p.cd;
+    rv_drain_error();
+    cp_deposit_kernel<<<(unsigned)((n + CP_THREADS - 1) / CP_THREADS), CP_THREADS, 0, (cudaStream_t)stream>>>(
+        kv, score, ape, kv_state, score_state, p, s, slot0);
+    return rv_launch_status();
+}
+
+RIVOLI_API int rivoli_kv_compress_decode(float* kv_state, float* score_state, const CompFinish* ff, const CompGeom* pp,
+                                         int start_pos, void* stream) {
+    if (!pp || !ff) return 1000;
+    const CompGeom p = *pp;
+    if (int g = cp_guard(p)) return g;
+    if (start_pos <= 0) return 1007;                 // position 0 belongs to the prefill arm
+    if ((start_pos + 1) % p.ratio != 0) return 1009; // the block has not closed
+    rv_drain_error();
+    cp_decode_kernel<<<1, CP_THREADS, 0, (cudaStream_t)stream>>>(kv_state, score_state, *ff, p, start_pos);
+    return rv_launch_status();
+}
+
+RIVOLI_API int rivoli_v4_compress_step_bf16(const CompGeom* pp, int n_seqs, const int32_t* pos, const float* kv_proj,
+                                            const float* score_proj, const float* ape, float* kv_state,
+                                            float* score_state, const float* norm, const float* freqs, int rotate,
+                                            uint16_t* cache, int cache_rows, int cache_row0, float* prequant,
+                                            void* stream) {
+    if (!pp) return 1000;
+    const CompGeom p = *pp;
+    if (int g = cp_guard(p)) return g;
+    if (n_seqs <= 0 || cache_rows <= 0 || cache_row0 < 0) return 1001;
+    if (rotate && (p.d > V4_ROT_MAX || (p.d & (p.d - 1)) || p.d % 32)) return 1002;
+    if (!rotate && (p.d - p.rd) % 64) return 1004;
+    if ((size_t)p.d * 4 > 48 * 1024) return 1002;
+    rv_drain_error();
+    cp_step_kernel<<<(unsigned)n_seqs, CP_THREADS, (size_t)p.d * 4, (cudaStream_t)stream>>>(
+        p, pos, kv_proj, score_proj, ape, kv_state, score_state, norm, freqs, rotate, cache, cache_rows, cache_row0, prequant);
+    return rv_launch_status();
+}
+
 RIVOLI_API size_t rivoli_v4_select_scratch_bytes(const V4Geom* g, int n_seqs) {
     if (!g || n_seqs <= 0 || g->max_comp <= 0) return 0;
     return ((size_t)n_seqs * (size_t)g->max_comp + (size_t)n_seqs) * 4;   // score rows, then one flag per sequence
@@ -832,8 +1186,8 @@ RIVOLI_API int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const i
         v4_score_int8_kernel<<<grid, SI_THREADS, 0, st>>>(*g, pos, index_q, index_w, index_kv, scores, flags);
     }
     cudaFuncSetAttribute(v4_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    v4_select_kernel<<<(unsigned)n_seqs, TK_THREADS, smem, st>>>(*g, pos, index_q, index_w, index_kv, sel, scores, flags,
-                                                                 tensor ? 0 : 1);
+    rv_launch_dependent(v4_select_kernel, dim3((unsigned)n_seqs), dim3(TK_THREADS), smem, st, *g, pos, index_q, index_w,
+                        index_kv, sel, scores, (const int32_t*)flags, tensor ? 0 : 1);
     return rv_launch_status();
 }
 
@@ -848,8 +1202,8 @@ RIVOLI_API int rivoli_v4_sparse_attend_bf16(const V4Geom* g, int n_seqs, const u
     cudaStream_t st = (cudaStream_t)stream;
     if (!force_simt && g->n_heads == SA_H && g->head_dim == SA_D) {
         cudaFuncSetAttribute(v4_sparse_attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SA_TOTAL);
-        v4_sparse_attend_mma_kernel<<<(unsigned)n_seqs, SA_THREADS, SA_TOTAL, st>>>(
-            q, kv_cache, kv_rows, sink, sel, cols, g->softmax_scale * 1.4426950408889634f, out);
+        rv_launch_dependent(v4_sparse_attend_mma_kernel, dim3((unsigned)n_seqs), dim3(SA_THREADS), (size_t)SA_TOTAL, st, q,
+                            kv_cache, kv_rows, sink, sel, cols, g->softmax_scale * 1.4426950408889634f, out);
         return rv_launch_status();
     }
     const size_t smem = ((size_t)g->head_dim + (size_t)cols) * sizeof(float);

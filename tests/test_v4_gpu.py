@@ -229,3 +229,138 @@ def test_rows_outside_the_integer_form_are_refolded_exactly():
     assert flags.tolist() == [0, 1, 1, 1]
     assert np.array_equal(bits(sc), bits(want_sc))
     assert np.array_equal(sel, want_sel)
+
+
+# ---- KV compressor, decode arm ------------------------------------------------------------------------
+def test_act_quant_f8_prefix_is_bit_identical():
+    be = _be()
+    rng = np.random.default_rng(31)
+    rows, stride, n, block = 37, 512, 448, 64
+    x = rng.standard_normal((rows, stride)).astype(np.float32)
+    x *= (2.0 ** rng.integers(-20, 12, (rows, 1))).astype(np.float32)
+    x[3, :64] = 0.0
+    x[4, :64] = 3e-5
+    rc, want = orc.act_quant_f8_prefix(x, rows, stride, n, block)
+    assert rc == 0
+    t = dev(x)
+    be.launch_act_quant_f8_prefix(t, t, rows, stride, n, block)
+    got = t.cpu().numpy()
+    assert np.array_equal(bits(got), bits(want.reshape(rows, stride)))
+    assert np.array_equal(got[:, n:], x[:, n:])          # the tail is untouched
+    for args, code in [((0, 64, 64, 64), 1001), ((1, 64, 48, 32), 1004), ((1, 32, 64, 64), 1001)]:
+        with pytest.raises(be.BackendError) as e:
+            be.launch_act_quant_f8_prefix(t, t, *args)
+        assert e.value.code == code
+    with pytest.raises(be.BackendError) as e:
+        be.launch_act_quant_f8_prefix(t, dev(x), 1, 128, 64, 64)
+    assert e.value.code == 1002
+
+
+def _comp_fixture(rng, p, n_pos):
+    norm = orc.bf16_to_f32(orc.f32_to_bf16(1.0 + 0.1 * rng.standard_normal(p.d).astype(np.float32)))
+    ang = rng.uniform(0, 2 * np.pi, (n_pos, p.rd // 2))
+    freqs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32).reshape(n_pos, p.rd)
+    ape = (0.5 * rng.standard_normal((p.ratio, p.cd))).astype(np.float32)
+    return norm, freqs, ape
+
+
+def _row_close(got, want, tol=1.0 / 64.0):
+    return float(np.abs(got.astype(np.float64) - want).max() / max(np.abs(want).max(), 1e-30)) <= tol
+
+
+@pytest.mark.parametrize("ratio,d,rd", [(4, 512, 64), (4, 128, 64), (128, 512, 64)])
+def test_compressor_reference_layout_decode(ratio, d, rd):
+    """Token by token through rivoli_kv_compress_deposit / _decode against the oracle: state bit-exact, pooled row
+    within rounding (expf and the norm's reduction order), guards by code."""
+    be = _be()
+    rng = np.random.default_rng(ratio + d)
+    op = orc.CompGeom.make(ratio=ratio, d=d, rd=rd)
+    bp = be.CompGeom(*[getattr(op, n) for n, _ in orc.CompGeom._fields_])
+    n_pos = 2 * ratio + 3
+    norm, freqs, ape = _comp_fixture(rng, op, n_pos)
+    kv_state = np.zeros((op.ents, op.cd), np.float32)
+    score_state = np.full((op.ents, op.cd), -np.inf, np.float32)
+    d_kv, d_sc = dev(kv_state), dev(score_state)
+    d_norm, d_freqs, d_ape = dev(norm), dev(freqs), dev(ape)
+    out = torch.zeros(d, device="cuda")
+    closed = 0
+    for pos in range(1, n_pos):
+        kv, sc = rng.standard_normal(op.cd).astype(np.float32), rng.standard_normal(op.cd).astype(np.float32)
+        orc.v4_compress_deposit_token(kv, sc, ape, kv_state, score_state, op, pos)
+        be.launch_kv_compress_deposit(dev(kv), dev(sc), d_ape, d_kv, d_sc, bp, 1, pos % ratio)
+        assert np.array_equal(bits(d_kv.cpu().numpy()), bits(kv_state))
+        assert np.array_equal(bits(d_sc.cpu().numpy()), bits(score_state))
+        if (pos + 1) % ratio:
+            with pytest.raises(be.BackendError) as e:
+                be.launch_kv_compress_decode(d_kv, d_sc, d_norm, d_freqs, out, bp, pos)
+            assert e.value.code == 1009
+            continue
+        rc, want = orc.v4_compress_decode(kv_state, score_state, norm, freqs, op, pos)
+        be.launch_kv_compress_decode(d_kv, d_sc, d_norm, d_freqs, out, bp, pos)
+        got = out.cpu().numpy()
+        assert _row_close(got, want), pos
+        assert np.array_equal(bits(got), bits(orc.bf16_to_f32(orc.f32_to_bf16(got))))
+        assert np.array_equal(bits(d_kv.cpu().numpy()), bits(kv_state))     # the overlap half moved down
+        closed += 1
+    assert closed == 2
+    with pytest.raises(be.BackendError) as e:
+        be.launch_kv_compress_decode(d_kv, d_sc, d_norm, d_freqs, out, bp, 0)
+    assert e.value.code == 1007
+    bad = be.CompGeom(4, 2, 64, 128, 7, 16, 1e-6)
+    with pytest.raises(be.BackendError) as e:
+        be.launch_kv_compress_deposit(d_kv, d_sc, d_ape, d_kv, d_sc, bad, 1, 0)
+    assert e.value.code == 1003
+    with pytest.raises(be.BackendError) as e:
+        be.launch_kv_compress_deposit(d_kv, d_sc, d_ape, d_kv, d_sc, bp, 1, ratio)
+    assert e.value.code == 1008
+
+
+@pytest.mark.parametrize("rotate,d", [(False, 512), (True, 128)])
+def test_compressor_batched_step(rotate, d):
+    """Several sequences at different phases of their block, stepped together for a few tokens. The row before the
+    finishing quantisation is within rounding of the oracle's; the stored row is EXACTLY the oracle's finish
+    (spread, or fp8 block-64 + bf16) applied to the device's own pre-quantisation row; untouched cache rows stay."""
+    be = _be()
+    rng = np.random.default_rng(40 + d)
+    op = orc.CompGeom.make(ratio=4, d=d, rd=64)
+    bp = be.CompGeom(*[getattr(op, n) for n, _ in orc.CompGeom._fields_])
+    B, steps, cache_rows, row0 = 6, 6, 40, 8
+    pos0 = np.array([1, 2, 3, 4, 9, 14], np.int32)
+    norm, freqs, ape = _comp_fixture(rng, op, 64)
+    kv_state = np.zeros((B, op.ents, op.cd), np.float32)
+    score_state = np.full((B, op.ents, op.cd), -np.inf, np.float32)
+    # some history so the overlap halves are live
+    kv_state[:, : op.ratio] = rng.standard_normal((B, op.ratio, op.cd)).astype(np.float32)
+    score_state[:, : op.ratio] = rng.standard_normal((B, op.ratio, op.cd)).astype(np.float32)
+    d_kv, d_sc = dev(kv_state), dev(score_state)
+    cache = torch.full((B, cache_rows, d), 0x1234, dtype=torch.uint16, device="cuda")
+    preq = torch.zeros((B, d), device="cuda")
+    written = set()
+    for t in range(steps):
+        pos = pos0 + t
+        kvp = rng.standard_normal((B, op.cd)).astype(np.float32)
+        scp = rng.standard_normal((B, op.cd)).astype(np.float32)
+        be.launch_v4_compress_step_bf16(bp, B, dev(pos), dev(kvp), dev(scp), dev(ape), d_kv, d_sc, dev(norm), dev(freqs),
+                                        rotate, cache, cache_rows, row0, preq)
+        got_pre, got_cache = preq.cpu().numpy(), cache.cpu().numpy()
+        for b in range(B):
+            orc.v4_compress_deposit_token(kvp[b], scp[b], ape, kv_state[b], score_state[b], op, int(pos[b]))
+            if (pos[b] + 1) % op.ratio:
+                continue
+            rc, want = orc.v4_compress_decode(kv_state[b], score_state[b], norm, freqs, op, int(pos[b]))
+            assert rc == 0 and _row_close(got_pre[b], want), (t, b)
+            if rotate:
+                fin = orc.v4_spread(got_pre[b].copy(), d)[1][0]
+            else:
+                fin = orc.act_quant_f8_prefix(got_pre[b].copy(), 1, d, d - op.rd, 64)[1]
+            blk = int(pos[b]) // op.ratio
+            assert np.array_equal(got_cache[b, row0 + blk], orc.f32_to_bf16(fin)), (t, b)
+            written.add((b, row0 + blk))
+        assert np.array_equal(bits(d_kv.cpu().numpy()), bits(kv_state))
+        assert np.array_equal(bits(d_sc.cpu().numpy()), bits(score_state))
+    got_cache = cache.cpu().numpy()
+    for b in range(B):
+        for r in range(cache_rows):
+            if (b, r) not in written:
+                assert np.all(got_cache[b, r] == 0x1234)
+    assert len(written) >= B

@@ -181,3 +181,75 @@ def test_batched_step_equals_the_row_functions():
         rc, o = orc.v4_sparse_attn(orc.bf16_to_f32(q[b]), orc.bf16_to_f32(kvc[b]), sink, sel[b], 1, 4, 64, 12,
                                    64 ** -0.5)
         assert np.array_equal(orc.f32_to_bf16(o[0]), out[b])
+
+
+def test_e4m3_round_to_nearest_even_round_trip():
+    """The V4 act-quant codec: every finite e4m3 value survives; midpoints go to the even mantissa; 448 saturates."""
+    tab = orc.e4m3_table()
+    vals = tab[np.isfinite(tab)]
+    rc, out = orc.act_quant_f8_prefix(np.concatenate([vals, np.zeros(256 - vals.size, np.float32)]), 1, 256, 256, 256)
+    # scale: amax 448 -> 448/448 = 1 -> power of two 1: the round trip is the codec itself
+    assert rc == 0 and np.array_equal(out[:vals.size], vals)
+    row = np.zeros(64, np.float32)
+    row[0] = 448.0
+    row[1:6] = [17.0, 19.0, 0.0009765625, 0.0029296875, -447.0]   # ties: 17 -> 16, 19 -> 20 (even mantissas)
+    rc, out = orc.act_quant_f8_prefix(row, 1, 64, 64, 64)
+    assert out[:6].tolist() == [448.0, 16.0, 20.0, 0.0, 0.00390625, -448.0]
+    assert orc.act_quant_f8_prefix(row, 1, 64, 48, 32)[0] == 1004
+    assert orc.act_quant_f8_prefix(row, 0, 64, 64, 64)[0] == 1001
+
+
+def test_act_quant_scale_is_a_power_of_two_with_a_floor():
+    row = np.full(64, 3e-5, np.float32)     # below the 1e-4 floor: the scale comes from the floor
+    rc, out = orc.act_quant_f8_prefix(row, 1, 64, 64, 64)
+    s = 2.0 ** np.ceil(np.log2(1e-4 / 448))
+    assert np.all(out / np.float32(s) == np.round(out / np.float32(s)))
+
+
+def _comp_fixture(rng, p, n_pos):
+    norm = orc.bf16_to_f32(orc.f32_to_bf16(1.0 + 0.1 * rng.standard_normal(p.d).astype(np.float32)))
+    ang = rng.uniform(0, 2 * np.pi, (n_pos, p.rd // 2))
+    freqs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32).reshape(n_pos, p.rd)
+    ape = (0.5 * rng.standard_normal((p.ratio, p.cd))).astype(np.float32)
+    return norm, freqs, ape
+
+
+def test_compressor_decode_pools_by_entry_softmax_and_shifts_the_overlap():
+    rng = np.random.default_rng(21)
+    p = orc.CompGeom.make(ratio=4, d=64, rd=16)
+    norm, freqs, ape = _comp_fixture(rng, p, 16)
+    kv_state = np.zeros((p.ents, p.cd), np.float32)
+    score_state = np.full((p.ents, p.cd), -np.inf, np.float32)
+    toks = []
+    for pos in range(1, 8):
+        kv, sc = rng.standard_normal(p.cd).astype(np.float32), rng.standard_normal(p.cd).astype(np.float32)
+        toks.append((pos, kv, sc))
+        assert orc.v4_compress_deposit_token(kv, sc, ape, kv_state, score_state, p, pos) == 0
+        slot = p.ratio + pos % p.ratio
+        assert np.array_equal(kv_state[slot], kv) and np.array_equal(score_state[slot], sc + ape[pos % p.ratio])
+        if (pos + 1) % p.ratio:
+            assert orc.v4_compress_decode(kv_state, score_state, norm, freqs, p, pos)[0] == 1009
+            continue
+        before_kv, before_sc = kv_state.copy(), score_state.copy()
+        rc, row = orc.v4_compress_decode(kv_state, score_state, norm, freqs, p, pos)
+        assert rc == 0
+        # the overlap half moved down
+        assert np.array_equal(kv_state[:p.ratio], before_kv[p.ratio:]) and np.array_equal(score_state[:p.ratio], before_sc[p.ratio:])
+        # reference in float64: entries below ratio give their first d dims, the others their last d
+        k = np.concatenate([before_kv[:p.ratio, :p.d], before_kv[p.ratio:, p.d:]]).astype(np.float64)
+        s = np.concatenate([before_sc[:p.ratio, :p.d], before_sc[p.ratio:, p.d:]]).astype(np.float64)
+        live = np.isfinite(s).any(axis=0)
+        w = np.exp(s - s.max(axis=0, where=np.isfinite(s), initial=-1e300))
+        pooled = np.where(live, (k * w).sum(axis=0) / np.maximum(w.sum(axis=0), 1e-300), 0.0)
+        pooled = orc.bf16_to_f32(orc.f32_to_bf16(pooled.astype(np.float32))).astype(np.float64)
+        x = norm * (pooled / np.sqrt((pooled ** 2).mean() + p.eps))
+        x = orc.bf16_to_f32(orc.f32_to_bf16(x.astype(np.float32))).astype(np.float64)
+        blk = (pos // p.ratio) * p.ratio
+        c, sn = freqs[blk, 0::2], freqs[blk, 1::2]
+        a, b = x[p.d - p.rd::2].copy(), x[p.d - p.rd + 1::2].copy()
+        x[p.d - p.rd::2], x[p.d - p.rd + 1::2] = a * c - b * sn, a * sn + b * c
+        assert np.allclose(row, x, rtol=0, atol=np.abs(x).max() / 64)
+        assert np.array_equal(row, orc.bf16_to_f32(orc.f32_to_bf16(row)))
+    assert orc.v4_compress_decode(kv_state, score_state, norm, freqs, p, 0)[0] == 1007
+    bad = orc.CompGeom(4, 2, 64, 128, 7, 16, 1e-6)
+    assert orc.v4_compress_decode(kv_state, score_state, norm, freqs, bad, 3)[0] == 1003
