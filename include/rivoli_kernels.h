@@ -359,8 +359,19 @@ typedef struct V4Geom {
  * 1002 index_heads > 64 or index_dim > 128 or max_comp > 16384 or index_topk > 4096, 1004 index_dim % 32 != 0. */
 size_t rivoli_v4_select_scratch_bytes(const V4Geom* g, int n_seqs);
 int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const int32_t* pos, const uint16_t* index_q,
-                                 const float* index_w, const uint16_t* index_kv, int32_t* sel, void* scratch,
-                                 int force_fold, void* stream);
+                                 const float* index_w, const uint16_t* index_kv, const unsigned char* packed,
+                                 const uint32_t* packed_exp, int32_t* sel, void* scratch, int force_fold, void* stream);
+
+/* Optional second form of the indexer's compressed rows, written ONCE when a row enters the cache, so that the
+ * scorer does not convert every row from bf16 on every step: packed int8 [B][max_comp][128] (each block of 32 in
+ * units of 2^(e - 130), e = biased exponent of the block's largest magnitude) and packed_exp u32 [B][max_comp]
+ * (the four block exponents, one byte each; 0 = empty block, 0xff = block not of that form). Packs rows
+ * [row_begin[b], row_end[b]) of every sequence (row_begin may be null = 0; max_rows = the largest count, sizes the
+ * grid). Pass both arrays to rivoli_v4_select_blocks_bf16 (or two nulls); index_kv is still read by the ordered
+ * fold. 1001 nulls / sizes, 1002 index_dim != 128. */
+int rivoli_v4_index_pack_bf16(const V4Geom* g, int n_seqs, const int32_t* row_begin, const int32_t* row_end,
+                              int max_rows, const uint16_t* index_kv, unsigned char* packed, uint32_t* packed_exp,
+                              void* stream);
 
 /* out[b][head] bf16 = sparse attention of q[b] bf16 [n_heads][head_dim] over kv_cache[b] rows sel[b][0..cols)
  * with the sink in the denominator. n_heads == 64 and head_dim == 512 run on the tensor cores (one CTA per

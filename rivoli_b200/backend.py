@@ -437,10 +437,18 @@ def v4_select_scratch_bytes(g: V4Geom, n_seqs: int) -> int:
 
 
 def launch_v4_select_blocks_bf16(g: V4Geom, n_seqs: int, pos, index_q, index_w, index_kv, sel, scratch,
-                                 force_fold: bool = False, stream=None) -> None:
+                                 force_fold: bool = False, packed=None, packed_exp=None, stream=None) -> None:
     ensure_status(lib().rivoli_v4_select_blocks_bf16(C.byref(g), C.c_int(n_seqs), _ptr(pos), _ptr(index_q), _ptr(index_w),
-                                                     _ptr(index_kv), _ptr(sel), _ptr(scratch), C.c_int(int(force_fold)),
-                                                     _stream(stream)), "v4_select_blocks_bf16")
+                                                     _ptr(index_kv), _ptr(packed), _ptr(packed_exp), _ptr(sel),
+                                                     _ptr(scratch), C.c_int(int(force_fold)), _stream(stream)),
+                  "v4_select_blocks_bf16")
+
+
+def launch_v4_index_pack_bf16(g: V4Geom, n_seqs: int, row_begin, row_end, max_rows: int, index_kv, packed, packed_exp,
+                              stream=None) -> None:
+    ensure_status(lib().rivoli_v4_index_pack_bf16(C.byref(g), C.c_int(n_seqs), _ptr(row_begin), _ptr(row_end),
+                                                  C.c_int(max_rows), _ptr(index_kv), _ptr(packed), _ptr(packed_exp),
+                                                  _stream(stream)), "v4_index_pack_bf16")
 
 
 def launch_v4_sparse_attend_bf16(g: V4Geom, n_seqs: int, q, kv_cache, sink, sel, cols: int, out,

@@ -251,10 +251,15 @@ __device__ __forceinline__ float v4_unit_inv(int pb, bool& ok) {
 // 2^(pb - 130), or 0 for an empty block.
 __device__ __forceinline__ float v4_unit(int pb) { return pb < 4 ? 0.0f : __int_as_float((pb - 3) << 23); }
 
+// PACKED: the rows come as int8 + block exponents (rivoli_v4_index_pack_bf16), written once when a row enters
+// the cache; otherwise every row is converted from bf16 on every step.
+template <bool PACKED>
 __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, const int32_t* __restrict__ pos,
                                                                    const uint16_t* __restrict__ index_q,
                                                                    const float* __restrict__ index_w,
                                                                    const uint16_t* __restrict__ index_kv,
+                                                                   const uint8_t* __restrict__ packed,
+                                                                   const uint32_t* __restrict__ packed_exp,
                                                                    float* __restrict__ scores,
                                                                    int32_t* __restrict__ flags) {
     __shared__ __align__(16) uint32_t qfrag[4 * 4 * 32 * 4];   // [m-tile][block][lane][4 regs]: A fragments, 8 KB
@@ -315,21 +320,38 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
         uint32_t b0[4], b1[4];
         float ku[4];
         int k_lo = 1000, k_hi = -1000;
+        if (PACKED) {
+            const uint8_t* prow = packed + ((size_t)b * g.max_comp + c) * 128;
+            const uint32_t e4 = c < n_comp ? packed_exp[(size_t)b * g.max_comp + c] : 0u;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint2 lo = make_uint2(0, 0), hi = make_uint2(0, 0);
-            if (c < n_comp) {
-                lo = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + quad * 4);
-                hi = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + 16 + quad * 4);
+            for (int j = 0; j < 4; ++j) {
+                b0[j] = b1[j] = 0u;
+                if (c < n_comp) {
+                    b0[j] = *reinterpret_cast<const uint32_t*>(prow + j * 32 + quad * 4);
+                    b1[j] = *reinterpret_cast<const uint32_t*>(prow + j * 32 + 16 + quad * 4);
+                }
+                const int pb = (e4 >> (8 * j)) & 0xff;
+                if (pb == 0xff) ok = false;                 // the packer could not take this block
+                ku[j] = pb == 0xff ? 0.0f : v4_unit(pb);
+                if (pb >= 4 && pb != 0xff) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
             }
-            int pb = max(v4_max_exp4(lo.x, lo.y), v4_max_exp4(hi.x, hi.y));
-            pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 1));
-            pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 2));
-            const float inv = v4_unit_inv(pb, ok);
-            b0[j] = v4_pack4(lo.x, lo.y, inv, ok);
-            b1[j] = v4_pack4(hi.x, hi.y, inv, ok);
-            ku[j] = v4_unit(pb);
-            if (pb >= 4) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint2 lo = make_uint2(0, 0), hi = make_uint2(0, 0);
+                if (c < n_comp) {
+                    lo = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + quad * 4);
+                    hi = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + 16 + quad * 4);
+                }
+                int pb = max(v4_max_exp4(lo.x, lo.y), v4_max_exp4(hi.x, hi.y));
+                pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 1));
+                pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 2));
+                const float inv = v4_unit_inv(pb, ok);
+                b0[j] = v4_pack4(lo.x, lo.y, inv, ok);
+                b1[j] = v4_pack4(hi.x, hi.y, inv, ok);
+                ku[j] = v4_unit(pb);
+                if (pb >= 4) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
+            }
         }
         // Every (head, this row) pair: block exponents E_j = eq_j + ek_j - 260 span at most span_q + span_k, and lie
         // inside [q_lo + k_lo, q_hi + k_hi] - 260. Inside the limits the ordered f32 fold is exact.
@@ -377,6 +399,44 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
         __syncwarp();
     }
     if (!ok) atomicOr(&flags[b], 1);
+}
+
+// One thread per (row, block of 32): the block's values as int8 multiples of 2^(pb - 130), pb = biased exponent of the
+// block's largest magnitude, stored in the row's exponent word (0 = empty block, 0xff = not of the integer form: the
+// scorer then hands the sequence to the ordered fold, which reads the bf16 rows).
+__global__ void v4_index_pack_kernel(V4Geom g, const int32_t* __restrict__ row_begin, const int32_t* __restrict__ row_end,
+                                     const uint16_t* __restrict__ index_kv, uint8_t* __restrict__ packed,
+                                     uint32_t* __restrict__ packed_exp) {
+    const int b = blockIdx.y;
+    const int r0 = row_begin ? row_begin[b] : 0, r1 = min(row_end[b], g.max_comp);
+    const int id = blockIdx.x * blockDim.x + threadIdx.x, row = r0 + (id >> 2), j = id & 3;
+    uint32_t e = 0;
+    if (row < r1) {
+        const size_t off = ((size_t)b * g.max_comp + row) * 128 + j * 32;
+        const uint4* src = reinterpret_cast<const uint4*>(index_kv + off);
+        uint32_t wv[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 v = src[i];
+            wv[4 * i] = v.x; wv[4 * i + 1] = v.y; wv[4 * i + 2] = v.z; wv[4 * i + 3] = v.w;
+        }
+        int pb = 0;
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) pb = max(pb, v4_max_exp4(wv[i], wv[i + 1]));
+        bool ok = pb < 0xff;
+        const float inv = v4_unit_inv(pb, ok);
+        uint32_t out[8];
+#pragma unroll
+        for (int k4 = 0; k4 < 8; ++k4) out[k4] = v4_pack4(wv[2 * k4], wv[2 * k4 + 1], inv, ok);
+        uint4* dst = reinterpret_cast<uint4*>(packed + off);
+        dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+        dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+        e = (uint32_t)(ok ? pb : 0xff) << (8 * j);
+    }
+    // the four blocks of a row sit in four neighbouring threads
+    e |= __shfl_xor_sync(0xffffffffu, e, 1);
+    e |= __shfl_xor_sync(0xffffffffu, e, 2);
+    if (row < r1 && j == 0) packed_exp[(size_t)b * g.max_comp + row] = e;
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -1163,11 +1223,24 @@ RIVOLI_API size_t rivoli_v4_select_scratch_bytes(const V4Geom* g, int n_seqs) {
     return ((size_t)n_seqs * (size_t)g->max_comp + (size_t)n_seqs) * 4;   // score rows, then one flag per sequence
 }
 
-RIVOLI_API int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const int32_t* pos, const uint16_t* index_q,
-                                            const float* index_w, const uint16_t* index_kv, int32_t* sel,
-                                            void* scratch, int force_fold, void* stream) {
+RIVOLI_API int rivoli_v4_index_pack_bf16(const V4Geom* g, int n_seqs, const int32_t* row_begin, const int32_t* row_end,
+                                         int max_rows, const uint16_t* index_kv, unsigned char* packed,
+                                         uint32_t* packed_exp, void* stream) {
     if (int rc = v4_check_geom(g, n_seqs)) return rc;
-    if (!scratch) return 1001;
+    if (!row_end || !packed || !packed_exp || max_rows <= 0) return 1001;
+    if (g->index_dim != 128 || n_seqs > 65535) return 1002;
+    rv_drain_error();
+    dim3 grid((unsigned)((max_rows * 4 + 255) / 256), (unsigned)n_seqs);
+    v4_index_pack_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*g, row_begin, row_end, index_kv, packed, packed_exp);
+    return rv_launch_status();
+}
+
+RIVOLI_API int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const int32_t* pos, const uint16_t* index_q,
+                                            const float* index_w, const uint16_t* index_kv, const unsigned char* packed,
+                                            const uint32_t* packed_exp, int32_t* sel, void* scratch, int force_fold,
+                                            void* stream) {
+    if (int rc = v4_check_geom(g, n_seqs)) return rc;
+    if (!scratch || ((packed != nullptr) != (packed_exp != nullptr))) return 1001;
     if (g->index_heads > SC_MAX_HEADS || g->index_dim > SC_MAX_HD || g->max_comp > SEL_MAX_COMP || g->index_topk > 4096)
         return 1002;
     if (g->index_dim % 32) return 1004;
@@ -1183,7 +1256,12 @@ RIVOLI_API int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const i
     if (tensor) {
         cudaMemsetAsync(flags, 0, (size_t)n_seqs * 4, st);
         dim3 grid((unsigned)((g->max_comp + SI_CHUNK - 1) / SI_CHUNK), (unsigned)n_seqs);
-        v4_score_int8_kernel<<<grid, SI_THREADS, 0, st>>>(*g, pos, index_q, index_w, index_kv, scores, flags);
+        if (packed)
+            v4_score_int8_kernel<true><<<grid, SI_THREADS, 0, st>>>(*g, pos, index_q, index_w, index_kv, packed, packed_exp,
+                                                                    scores, flags);
+        else
+            v4_score_int8_kernel<false><<<grid, SI_THREADS, 0, st>>>(*g, pos, index_q, index_w, index_kv, packed, packed_exp,
+                                                                     scores, flags);
     }
     cudaFuncSetAttribute(v4_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     rv_launch_dependent(v4_select_kernel, dim3((unsigned)n_seqs), dim3(TK_THREADS), smem, st, *g, pos, index_q, index_w,

@@ -121,7 +121,7 @@ def test_gather_attn_reference_layout():
     assert np.array_equal(bits(got[:2]), bits(orc.bf16_to_f32(orc.f32_to_bf16(got[:2]))))  # stored on the bf16 grid
 
 
-def _run_step(g, inp, force_simt=False, want_scores=True, force_fold=False, want_flags=False):
+def _run_step(g, inp, force_simt=False, want_scores=True, force_fold=False, want_flags=False, pack=False):
     be = _be()
     from rivoli_b200.v4 import V4DecodeLayer
     B = inp["pos"].size
@@ -130,6 +130,9 @@ def _run_step(g, inp, force_simt=False, want_scores=True, force_fold=False, want
     layer.kv_cache.copy_(dev(inp["kv_cache"]))
     layer.index_kv.copy_(dev(inp["ikv"]))
     layer.sink.copy_(dev(inp["sink"]))
+    if pack:   # the int8 + exponent form of the rows, as a cache writer would leave it
+        n_rows = (inp["pos"] + 1) // g.ratio
+        layer.pack_index_rows(None, dev(n_rows.astype(np.int32)), int(n_rows.max()))
     layer.select(dev(inp["pos"]), dev(inp["iq"]), dev(inp["iw"]), force_fold)
     layer.attend(dev(inp["q"]), force_simt)
     torch.cuda.synchronize()
@@ -153,15 +156,15 @@ def test_batched_step_small_shapes():
     assert ok, worst
 
 
-@pytest.mark.parametrize("force_simt,force_fold", [(False, False), (True, True)])
-def test_batched_step_model_shapes(force_simt, force_fold):
+@pytest.mark.parametrize("force_simt,force_fold,pack", [(False, False, False), (True, True, False), (False, False, True)])
+def test_batched_step_model_shapes(force_simt, force_fold, pack):
     g = wl.make_geom(max_comp=640, index_topk=96)
     pos = np.array([3, 126, 127, 500, 2559, 1023, 1500, 390], np.int32)  # ring filling / full; positional and scored
     inp = wl.make_inputs(g, pos.size, pos, seed=4)
     inp["iw"][1] = np.abs(inp["iw"][1])
     want_sel, want_out, want_sc = orc.v4_decode_step_bf16(g, pos, inp["q"], inp["kv_cache"], inp["sink"], inp["iq"],
                                                           inp["iw"], inp["ikv"], want_scores=True)
-    sel, out, sc, flags = _run_step(g, inp, force_simt, force_fold=force_fold, want_flags=True)
+    sel, out, sc, flags = _run_step(g, inp, force_simt, force_fold=force_fold, want_flags=True, pack=pack)
     if not force_fold:
         assert not flags.any()      # spread rows are what the integer scorer takes whole
     assert np.array_equal(sel, want_sel)
@@ -225,10 +228,11 @@ def test_rows_outside_the_integer_form_are_refolded_exactly():
     inp["ikv"][3, 17] = orc.f32_to_bf16(row)
     want_sel, want_out, want_sc = orc.v4_decode_step_bf16(g, pos, inp["q"], inp["kv_cache"], inp["sink"], inp["iq"],
                                                           inp["iw"], inp["ikv"], want_scores=True)
-    sel, out, sc, flags = _run_step(g, inp, want_flags=True)
-    assert flags.tolist() == [0, 1, 1, 1]
-    assert np.array_equal(bits(sc), bits(want_sc))
-    assert np.array_equal(sel, want_sel)
+    for pack in (False, True):
+        sel, out, sc, flags = _run_step(g, inp, want_flags=True, pack=pack)
+        assert flags.tolist() == [0, 1, 1, 1]
+        assert np.array_equal(bits(sc), bits(want_sc))
+        assert np.array_equal(sel, want_sel)
 
 
 # ---- KV compressor, decode arm ------------------------------------------------------------------------
