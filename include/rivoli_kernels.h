@@ -407,6 +407,11 @@ int rivoli_act_quant_f8_prefix(const float* src, float* dst, int rows, int row_s
  * land from slot0 on; score rows get ape added. 1000 null geometry, 1001-1004/1010 geometry, 1005 s <= 0, 1008 slot0. */
 int rivoli_kv_compress_deposit(const float* kv, const float* score, const float* ape, float* kv_state,
                                float* score_state, const CompGeom* p, int s, int slot0, void* stream);
+/* kvcompress.hip `rivoli_kv_compress_prefill`: blocks 0 .. nblk-1 of a prompt that starts at position 0, from its
+ * projected rows kv, score [s][cd]: each block pooled over its own rows and (with overlap) the previous block's,
+ * finished at position b * ratio -> f->out[b][d]. 1006 nblk <= 0. Same tolerance as the decode arm. */
+int rivoli_kv_compress_prefill(const float* kv, const float* score, const float* ape, const CompFinish* f,
+                               const CompGeom* p, int nblk, void* stream);
 /* kvcompress.hip `rivoli_kv_compress_decode`: pool the state (softmax over the entry axis per feature), bf16 store,
  * RMSNorm, rotate the last rd dims at the block's first position, bf16 store -> f->out; then the overlap half of the
  * state moves down. 1007 start_pos <= 0, 1009 (start_pos + 1) % ratio != 0. Tolerance: expf and the norm's

@@ -486,3 +486,15 @@ def v4_compress_decode(kv_state, score_state, norm, freqs, p: CompGeom, start_po
     rc = lib().orc_v4_compress_decode(_p(kv_state), _p(score_state), _p(_c(norm, np.float32)), _p(_c(freqs, np.float32)),
                                       _p(out), C.byref(p), C.c_int(start_pos))
     return int(rc), out
+
+
+def v4_compress_deposit_prefill(kv, score, ape, kv_state, score_state, p: CompGeom, s) -> int:
+    return int(lib().orc_v4_compress_deposit_prefill(_p(_c(kv, np.float32)), _p(_c(score, np.float32)), _p(_c(ape, np.float32)),
+                                                     _p(kv_state), _p(score_state), C.byref(p), C.c_int(s)))
+
+
+def v4_compress_prefill(kv, score, ape, norm, freqs, p: CompGeom, nblk):
+    out = np.zeros((max(nblk, 0), p.d), np.float32)
+    rc = lib().orc_v4_compress_prefill(_p(_c(kv, np.float32)), _p(_c(score, np.float32)), _p(_c(ape, np.float32)),
+                                       _p(_c(norm, np.float32)), _p(_c(freqs, np.float32)), _p(out), C.byref(p), C.c_int(nblk))
+    return int(rc), out

@@ -406,3 +406,89 @@ ORC_API int orc_v4_compress_decode(float* kv_state, float* score_state, const fl
     for (int e = 0; e < d; ++e) out[e] = rbf16(out[e]);
     return 0;
 }
+
+/* ---- KV compressor, prefill arm: crates/oracles/src/v4oracle/compress.rs:52-128 ------------------
+ * kv, score: [s][cd] projected rows of a prompt that starts at position 0. */
+
+/* State left behind by a prompt of s tokens (compress.rs:57-79): with overlap the last FULL block's rows
+ * (scores + ape) become the overlap half; the s % ratio rows of the open block land from slot 0. */
+ORC_API int orc_v4_compress_deposit_prefill(const float* kv, const float* score, const float* ape, float* kv_state,
+                                            float* score_state, const orc_comp_geom* p, int s) {
+    const int g = comp_guard(p);
+    if (g) return g;
+    if (s <= 0) return 1005;
+    const int ratio = p->ratio, cd = p->cd, overlap = p->coff == 2;
+    const int remainder = s % ratio, cutoff = s - remainder, state_off = overlap ? ratio : 0;
+    if (overlap && cutoff >= ratio)
+        for (int j = 0; j < ratio; ++j)
+            for (int e = 0; e < cd; ++e) {
+                const size_t src = (size_t)(cutoff - ratio + j) * cd + e;
+                kv_state[(size_t)j * cd + e] = kv[src];
+                score_state[(size_t)j * cd + e] = score[src] + ape[(size_t)j * cd + e];
+            }
+    for (int j = 0; j < remainder; ++j)
+        for (int e = 0; e < cd; ++e) {
+            const size_t src = (size_t)(cutoff + j) * cd + e, dst = (size_t)(state_off + j) * cd + e;
+            kv_state[dst] = kv[src];
+            score_state[dst] = score[src] + ape[(size_t)j * cd + e];
+        }
+    return 0;
+}
+
+/* The finish shared by both arms: bf16 store, RMSNorm + bf16, adjacent-pair rotation at `pos`, bf16. */
+static void comp_finish_row(float* out, const float* norm, const float* freqs, const orc_comp_geom* p, int pos) {
+    const int d = p->d;
+    for (int e = 0; e < d; ++e) out[e] = rbf16(out[e]);
+    float var = 0.0f;
+    for (int e = 0; e < d; ++e) var += out[e] * out[e];
+    const float rs = 1.0f / sqrtf(var / (float)d + p->eps);
+    for (int e = 0; e < d; ++e) out[e] = rbf16(norm[e] * (out[e] * rs));
+    float* seg = out + (d - p->rd);
+    for (int i = 0; i < p->rd / 2; ++i) {
+        const float c = freqs[(size_t)pos * p->rd + 2 * i], sn = freqs[(size_t)pos * p->rd + 2 * i + 1];
+        const float a = seg[2 * i], b = seg[2 * i + 1];
+        seg[2 * i] = a * c - b * sn;
+        seg[2 * i + 1] = a * sn + b * c;
+    }
+    for (int e = 0; e < d; ++e) out[e] = rbf16(out[e]);
+}
+
+/* Blocks 0 .. nblk-1 of the prompt, each pooled over its ratio rows (second halves) and, with overlap, the
+ * previous block's rows (first halves; absent for block 0), scores + ape per position within the block;
+ * finished at position b * ratio. out: [nblk][d] rows before the final quantisation. compress.rs:83-128. */
+ORC_API int orc_v4_compress_prefill(const float* kv, const float* score, const float* ape, const float* norm,
+                                    const float* freqs, float* out, const orc_comp_geom* p, int nblk) {
+    const int g = comp_guard(p);
+    if (g) return g;
+    if (nblk <= 0) return 1006;
+    const int ratio = p->ratio, d = p->d, cd = p->cd, ents = p->ents, overlap = p->coff == 2;
+    for (int b = 0; b < nblk; ++b) {
+        float* row = out + (size_t)b * d;
+        for (int e = 0; e < d; ++e) {
+            float sc[128], kvv[128];
+            int live[128];
+            for (int j = 0; j < ents; ++j) {
+                int sblk, src_j, half;
+                live[j] = 1;
+                if (!overlap) { sblk = b; src_j = j; half = 0; }
+                else if (j >= ratio) { sblk = b; src_j = j - ratio; half = d; }
+                else if (b > 0) { sblk = b - 1; src_j = j; half = 0; }
+                else { live[j] = 0; sc[j] = -INFINITY; kvv[j] = 0.0f; continue; }
+                const size_t src = (size_t)(sblk * ratio + src_j) * cd + half + e;
+                kvv[j] = kv[src];
+                sc[j] = score[src] + ape[(size_t)src_j * cd + half + e];
+            }
+            float m = -INFINITY;
+            for (int j = 0; j < ents; ++j) m = fmaxf(m, sc[j]);
+            if (!isfinite(m)) { row[e] = 0.0f; continue; }
+            float s = 0.0f;
+            for (int j = 0; j < ents; ++j) s += expf(sc[j] - m);
+            float acc = 0.0f;
+            for (int j = 0; j < ents; ++j) acc += kvv[j] * (expf(sc[j] - m) / s);
+            row[e] = acc;
+            (void)live;
+        }
+        comp_finish_row(row, norm, freqs, p, b * ratio);
+    }
+    return 0;
+}

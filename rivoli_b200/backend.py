@@ -483,6 +483,12 @@ def launch_kv_compress_deposit(kv, score, ape, kv_state, score_state, p: CompGeo
                                                    _stream(stream)), "kv_compress_deposit")
 
 
+def launch_kv_compress_prefill(kv, score, ape, norm, freqs, out, p: CompGeom, nblk: int, stream=None) -> None:
+    f = CompFinish(_ptr(norm), _ptr(freqs), _ptr(out))
+    ensure_status(lib().rivoli_kv_compress_prefill(_ptr(kv), _ptr(score), _ptr(ape), C.byref(f), C.byref(p), C.c_int(nblk),
+                                                   _stream(stream)), "kv_compress_prefill")
+
+
 def launch_kv_compress_decode(kv_state, score_state, norm, freqs, out, p: CompGeom, start_pos: int, stream=None) -> None:
     f = CompFinish(_ptr(norm), _ptr(freqs), _ptr(out))
     ensure_status(lib().rivoli_kv_compress_decode(_ptr(kv_state), _ptr(score_state), C.byref(f), C.byref(p),

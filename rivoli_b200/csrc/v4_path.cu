@@ -964,8 +964,28 @@ struct CpState {
     float* score;   // [ents][cd]
 };
 
+// bf16 row -> RMSNorm (bf16 store) -> rotation of the last rd dims at `pos` (bf16 store), in place, by one CTA.
+// red: CP_THREADS / 32 floats of shared memory.
+__device__ __forceinline__ void cp_finish_row(float* row, const float* __restrict__ norm, const float* __restrict__ freqs,
+                                              CompGeom p, int pos, float* red) {
+    const int tid = threadIdx.x, d = p.d;
+    float part = 0.0f;
+    for (int e = tid; e < d; e += CP_THREADS) part += row[e] * row[e];
+    const float rs = 1.0f / sqrtf(cp_block_sum(part, red) / (float)d + p.eps);
+    for (int e = tid; e < d; e += CP_THREADS) row[e] = v4_rbf16(norm[e] * (row[e] * rs));
+    __syncthreads();
+    float* seg = row + (d - p.rd);
+    for (int i = tid; i < p.rd / 2; i += CP_THREADS) {
+        const float c = freqs[(size_t)pos * p.rd + 2 * i], sn = freqs[(size_t)pos * p.rd + 2 * i + 1];
+        const float a = seg[2 * i], b = seg[2 * i + 1];
+        seg[2 * i] = v4_rbf16(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn)));
+        seg[2 * i + 1] = v4_rbf16(__fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c)));
+    }
+    __syncthreads();
+}
+
 // Pool + bf16 + RMSNorm + rotation of one sequence's state into row[d] (shared or global), by one CTA;
-// then the overlap half of the state moves down. red: CP_THREADS / 32 floats of shared memory.
+// then the overlap half of the state moves down.
 __device__ __forceinline__ void cp_pool_finish(CpState st, const float* __restrict__ norm,
                                                const float* __restrict__ freqs, float* row, CompGeom p,
                                                int start_pos, float* red) {
@@ -986,19 +1006,7 @@ __device__ __forceinline__ void cp_pool_finish(CpState st, const float* __restri
         row[e] = v4_rbf16(o);
     }
     __syncthreads();
-    float part = 0.0f;
-    for (int e = tid; e < d; e += CP_THREADS) part += row[e] * row[e];
-    const float rs = 1.0f / sqrtf(cp_block_sum(part, red) / (float)d + p.eps);
-    for (int e = tid; e < d; e += CP_THREADS) row[e] = v4_rbf16(norm[e] * (row[e] * rs));
-    __syncthreads();
-    const int pos = (start_pos / p.ratio) * p.ratio;
-    float* seg = row + (d - p.rd);
-    for (int i = tid; i < p.rd / 2; i += CP_THREADS) {
-        const float c = freqs[(size_t)pos * p.rd + 2 * i], sn = freqs[(size_t)pos * p.rd + 2 * i + 1];
-        const float a = seg[2 * i], b = seg[2 * i + 1];
-        seg[2 * i] = v4_rbf16(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn)));
-        seg[2 * i + 1] = v4_rbf16(__fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c)));
-    }
+    cp_finish_row(row, norm, freqs, p, (start_pos / p.ratio) * p.ratio, red);
     if (overlap) {   // every pooling read is done (barriers above): the overlap half moves down
         const size_t n = (size_t)p.ratio * cd;
         for (size_t i = tid; i < n; i += CP_THREADS) {
@@ -1007,6 +1015,39 @@ __device__ __forceinline__ void cp_pool_finish(CpState st, const float* __restri
         }
     }
     __syncthreads();
+}
+
+// Prefill arm: block b of a prompt that starts at position 0. Entry j of its window is row j - ratio of block b
+// (second half of the projected row) or, with overlap, row j of block b - 1 (first half; absent for block 0);
+// scores get the positional bias of the row's place in ITS block.
+__global__ void __launch_bounds__(CP_THREADS) cp_prefill_kernel(const float* __restrict__ kv,
+                                                                const float* __restrict__ score,
+                                                                const float* __restrict__ ape, CompFinish f, CompGeom p) {
+    __shared__ float red[CP_THREADS / 32];
+    const int b = blockIdx.x, tid = threadIdx.x, d = p.d, cd = p.cd, overlap = p.coff == 2;
+    float* row = f.out + (size_t)b * d;
+    for (int e = tid; e < d; e += CP_THREADS) {
+        float mx = -INFINITY;
+        float sum = 0.0f, o = 0.0f;
+        for (int pass = 0; pass < 3; ++pass) {   // 0: maximum, 1: sum of exponentials, 2: weighted values
+            for (int j = 0; j < p.ents; ++j) {
+                int sblk, src_j, half;
+                if (!overlap) { sblk = b; src_j = j; half = 0; }
+                else if (j >= p.ratio) { sblk = b; src_j = j - p.ratio; half = d; }
+                else if (b > 0) { sblk = b - 1; src_j = j; half = 0; }
+                else continue;
+                const size_t src = (size_t)(sblk * p.ratio + src_j) * cd + half + e;
+                const float sc = score[src] + ape[(size_t)src_j * cd + half + e];
+                if (pass == 0) mx = fmaxf(mx, sc);
+                else if (pass == 1) sum += expf(sc - mx);
+                else o += kv[src] * (expf(sc - mx) / sum);
+            }
+            if (pass == 0 && !isfinite(mx)) break;
+        }
+        row[e] = v4_rbf16(isfinite(mx) ? o : 0.0f);
+    }
+    __syncthreads();
+    cp_finish_row(row, f.norm, f.freqs, p, b * p.ratio, red);
 }
 
 __global__ void __launch_bounds__(CP_THREADS) cp_deposit_kernel(const float* __restrict__ kv,
@@ -1185,6 +1226,17 @@ RIVOLI_API int rivoli_kv_compress_deposit(const float* kv, const float* score, c
     rv_drain_error();
     cp_deposit_kernel<<<(unsigned)((n + CP_THREADS - 1) / CP_THREADS), CP_THREADS, 0, (cudaStream_t)stream>>>(
         kv, score, ape, kv_state, score_state, p, s, slot0);
+    return rv_launch_status();
+}
+
+RIVOLI_API int rivoli_kv_compress_prefill(const float* kv, const float* score, const float* ape, const CompFinish* ff,
+                                          const CompGeom* pp, int nblk, void* stream) {
+    if (!pp || !ff) return 1000;
+    const CompGeom p = *pp;
+    if (int g = cp_guard(p)) return g;
+    if (nblk <= 0) return 1006;
+    rv_drain_error();
+    cp_prefill_kernel<<<(unsigned)nblk, CP_THREADS, 0, (cudaStream_t)stream>>>(kv, score, ape, *ff, p);
     return rv_launch_status();
 }
 

@@ -368,3 +368,45 @@ def test_compressor_batched_step(rotate, d):
             if (b, r) not in written:
                 assert np.all(got_cache[b, r] == 0x1234)
     assert len(written) >= B
+
+
+@pytest.mark.parametrize("ratio,d,rd,s", [(4, 512, 64, 23), (4, 128, 64, 9), (128, 512, 64, 300)])
+def test_compressor_reference_layout_prefill(ratio, d, rd, s):
+    """A prompt through rivoli_kv_compress_deposit (s rows at once) and rivoli_kv_compress_prefill: the state it leaves
+    is bit-exact, every pooled block within rounding; then a decode token continues from that state."""
+    be = _be()
+    rng = np.random.default_rng(s)
+    op = orc.CompGeom.make(ratio=ratio, d=d, rd=rd)
+    bp = be.CompGeom(*[getattr(op, n) for n, _ in orc.CompGeom._fields_])
+    norm, freqs, ape = _comp_fixture(rng, op, s + ratio + 1)
+    kv = rng.standard_normal((s, op.cd)).astype(np.float32)
+    sc = rng.standard_normal((s, op.cd)).astype(np.float32)
+    kv_state = np.zeros((op.ents, op.cd), np.float32)
+    score_state = np.full((op.ents, op.cd), -np.inf, np.float32)
+    d_kv, d_sc = dev(kv_state), dev(score_state)
+    assert orc.v4_compress_deposit_prefill(kv, sc, ape, kv_state, score_state, op, s) == 0
+    be.launch_kv_compress_deposit(dev(kv), dev(sc), dev(ape), d_kv, d_sc, bp, s, 0)
+    assert np.array_equal(bits(d_kv.cpu().numpy()), bits(kv_state))
+    assert np.array_equal(bits(d_sc.cpu().numpy()), bits(score_state))
+    nblk = s // ratio
+    rc, want = orc.v4_compress_prefill(kv, sc, ape, norm, freqs, op, nblk)
+    out = torch.zeros((nblk, d), device="cuda")
+    be.launch_kv_compress_prefill(dev(kv), dev(sc), dev(ape), dev(norm), dev(freqs), out, bp, nblk)
+    got = out.cpu().numpy()
+    for b in range(nblk):
+        assert _row_close(got[b], want[b]), b
+    assert np.array_equal(bits(got), bits(orc.bf16_to_f32(orc.f32_to_bf16(got))))
+    # decode tokens continue from the prompt's state until the open block closes
+    row = torch.zeros(d, device="cuda")
+    for pos in range(s, (s // ratio + 1) * ratio):
+        k1, s1 = rng.standard_normal(op.cd).astype(np.float32), rng.standard_normal(op.cd).astype(np.float32)
+        orc.v4_compress_deposit_token(k1, s1, ape, kv_state, score_state, op, pos)
+        be.launch_kv_compress_deposit(dev(k1), dev(s1), dev(ape), d_kv, d_sc, bp, 1, pos % ratio)
+    pos = (s // ratio + 1) * ratio - 1
+    rc, want_row = orc.v4_compress_decode(kv_state, score_state, norm, freqs, op, pos)
+    be.launch_kv_compress_decode(d_kv, d_sc, dev(norm), dev(freqs), row, bp, pos)
+    assert rc == 0 and _row_close(row.cpu().numpy(), want_row)
+    assert np.array_equal(bits(d_kv.cpu().numpy()), bits(kv_state))
+    with pytest.raises(be.BackendError) as e:
+        be.launch_kv_compress_prefill(dev(kv), dev(sc), dev(ape), dev(norm), dev(freqs), out, bp, 0)
+    assert e.value.code == 1006

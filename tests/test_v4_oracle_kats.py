@@ -253,3 +253,41 @@ def test_compressor_decode_pools_by_entry_softmax_and_shifts_the_overlap():
     assert orc.v4_compress_decode(kv_state, score_state, norm, freqs, p, 0)[0] == 1007
     bad = orc.CompGeom(4, 2, 64, 128, 7, 16, 1e-6)
     assert orc.v4_compress_decode(kv_state, score_state, norm, freqs, bad, 3)[0] == 1003
+
+
+def test_compressor_prefill_and_decode_arms_agree():
+    """A prompt pooled by the prefill arm and the same tokens fed one at a time after a one-block prompt give the
+    same blocks and leave the same state: same entries, same fold order."""
+    rng = np.random.default_rng(23)
+    p = orc.CompGeom.make(ratio=4, d=64, rd=16)
+    norm, freqs, ape = _comp_fixture(rng, p, 16)
+    s = 11
+    kv = rng.standard_normal((s + 1, p.cd)).astype(np.float32)
+    sc = rng.standard_normal((s + 1, p.cd)).astype(np.float32)
+
+    def fresh():
+        return np.zeros((p.ents, p.cd), np.float32), np.full((p.ents, p.cd), -np.inf, np.float32)
+
+    # A: the whole prompt through the prefill arm, then one decode token closes block 2
+    ka, sa = fresh()
+    assert orc.v4_compress_deposit_prefill(kv[:s], sc[:s], ape, ka, sa, p, s) == 0
+    rc, blocks_a = orc.v4_compress_prefill(kv[:s], sc[:s], ape, norm, freqs, p, s // p.ratio)
+    assert rc == 0 and blocks_a.shape == (2, p.d)
+    orc.v4_compress_deposit_token(kv[s], sc[s], ape, ka, sa, p, s)
+    rc, b2_a = orc.v4_compress_decode(ka, sa, norm, freqs, p, s)
+    assert rc == 0
+    # B: one block of prompt, the rest token by token
+    kb, sb = fresh()
+    orc.v4_compress_deposit_prefill(kv[:4], sc[:4], ape, kb, sb, p, 4)
+    rc, blocks_b0 = orc.v4_compress_prefill(kv[:4], sc[:4], ape, norm, freqs, p, 1)
+    got = {}
+    for pos in range(4, s + 1):
+        orc.v4_compress_deposit_token(kv[pos], sc[pos], ape, kb, sb, p, pos)
+        if (pos + 1) % p.ratio == 0:
+            rc, got[pos // p.ratio] = orc.v4_compress_decode(kb, sb, norm, freqs, p, pos)
+    assert np.array_equal(blocks_a[0], blocks_b0[0])
+    assert np.array_equal(blocks_a[1], got[1])
+    assert np.array_equal(b2_a, got[2])
+    assert np.array_equal(ka, kb) and np.array_equal(sa, sb)
+    assert orc.v4_compress_prefill(kv, sc, ape, norm, freqs, p, 0)[0] == 1006
+    assert orc.v4_compress_deposit_prefill(kv, sc, ape, ka, sa, p, 0) == 1005
