@@ -410,3 +410,74 @@ def test_compressor_reference_layout_prefill(ratio, d, rd, s):
     with pytest.raises(be.BackendError) as e:
         be.launch_kv_compress_prefill(dev(kv), dev(sc), dev(ape), dev(norm), dev(freqs), out, bp, 0)
     assert e.value.code == 1006
+
+
+def test_bench_shape_properties():
+    """Batch 128 x context 8192 (the benchmark's shape), inputs made on the device: properties that need no oracle.
+    Selection: ring part is the rotation; the 512 ranked blocks are ascending, distinct, and no unselected block
+    outranks a selected one under (score descending, index ascending); packed and unpacked rows give the same rows.
+    Attention: a row whose only live slot is j returns kv[j] when the sink is far below; reordering the slots of a
+    row changes the output only by rounding; masked slots change nothing."""
+    be = _be()
+    from rivoli_b200.v4 import V4DecodeLayer
+    B, ctx = 128, 8192
+    g = be.V4Geom.make(max_comp=ctx // 4)
+    layer = V4DecodeLayer(g, B)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(77)
+    rnd = lambda *shape: torch.randn(shape, generator=gen, device="cuda")
+    layer.kv_cache.copy_(rnd(B, layer.kv_rows, g.head_dim).to(torch.bfloat16).view(torch.uint16))
+    rows = rnd(B * g.max_comp, g.index_dim).to(torch.bfloat16).float()
+    be.launch_act_quant_f4_rotated(rows, B * g.max_comp, g.index_dim)
+    layer.index_kv.copy_(rows.to(torch.bfloat16).view(torch.uint16).view(B, g.max_comp, g.index_dim))
+    iq = rnd(B * g.index_heads, g.index_dim).to(torch.bfloat16).float()
+    be.launch_act_quant_f4_rotated(iq, B * g.index_heads, g.index_dim)
+    iq = iq.to(torch.bfloat16).view(torch.uint16).view(B, g.index_heads, g.index_dim).contiguous()
+    iw = (rnd(B, g.index_heads) * 0.125).to(torch.bfloat16).float()
+    q = rnd(B, g.n_heads, g.head_dim).to(torch.bfloat16).view(torch.uint16)
+    layer.sink.copy_(rnd(g.n_heads))
+    pos = torch.randint(ctx - 512, ctx, (B,), generator=gen, device="cuda", dtype=torch.int32)
+    layer.select(pos, iq, iw)
+    sel_a = layer.sel.clone()
+    assert not layer.refolded.any().item()
+    scores = layer.scores.clone()
+    layer.pack_index_rows(None, (pos + 1) // 4, g.max_comp)
+    layer.select(pos, iq, iw)
+    assert torch.equal(layer.sel, sel_a) and torch.equal(layer.scores.view(torch.int32), scores.view(torch.int32))
+    sel, sc, p = sel_a.cpu().numpy(), scores.cpu().numpy(), pos.cpu().numpy()
+    W, K = g.window, g.index_topk
+    for b in range(0, B, 7):
+        assert sel[b, :W].tolist() == orc.v4_window_row(W, int(p[b])).tolist()
+        n_comp = (p[b] + 1) // 4
+        chosen = sel[b, W:] - W
+        assert np.all(np.diff(chosen) > 0) and chosen.min() >= 0 and chosen.max() < n_comp
+        key = sc[b, :n_comp].view(np.uint32).astype(np.int64)
+        key = np.where(key >> 31, (~key) & 0xffffffff, key | 0x80000000)      # total order on the bits
+        rest = np.setdiff1d(np.arange(n_comp), chosen)
+        worst_in, best_out = key[chosen].min(), key[rest].max()
+        assert worst_in >= best_out
+        if worst_in == best_out:   # ties go to the lower index
+            assert chosen[key[chosen] == worst_in].max() < rest[key[rest] == best_out].min()
+    # attention
+    out0 = layer.attend(q).clone()
+    assert not torch.isnan(out0.view(torch.bfloat16).float()).any()
+    perm = torch.randperm(layer.cols, generator=gen, device="cuda")
+    layer.sel.copy_(sel_a[:, perm])
+    out1 = layer.attend(q).clone()
+    ok, worst = wl.attend_close(out1.cpu().numpy(), out0.cpu().numpy())
+    assert ok, worst
+    masked = sel_a.clone()
+    masked[:, 1::2] = -1
+    wide = torch.cat([masked, torch.full_like(masked, -1)], dim=1).contiguous()     # twice as many columns, all masked
+    out_n = torch.zeros_like(layer.out)
+    be.launch_v4_sparse_attend_bf16(g, B, q, layer.kv_cache, layer.sink, masked, layer.cols, out_n)
+    out_w = torch.zeros_like(layer.out)
+    be.launch_v4_sparse_attend_bf16(g, B, q, layer.kv_cache, layer.sink, wide, 2 * layer.cols, out_w)
+    assert torch.equal(out_n, out_w)
+    one = torch.full_like(sel_a, -1)
+    one[:, 5] = sel_a[:, 300]
+    layer.sink.fill_(-1e30)
+    out_1 = torch.zeros_like(layer.out)
+    be.launch_v4_sparse_attend_bf16(g, B, q, layer.kv_cache, layer.sink, one, layer.cols, out_1)
+    want = layer.kv_cache.view(torch.int16)[torch.arange(B, device="cuda"), sel_a[:, 300].long()]
+    assert torch.equal(out_1.view(torch.int16), want[:, None, :].expand(-1, g.n_heads, -1))
