@@ -638,7 +638,10 @@ def run_v4(args):
                     "d2h_bytes_per_step": int(h_out.numel() * 2)},
             "gpu_launches": args.steps * 3, "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": ach / hbm_peak, "traffic": None,
+                         "frac": ach / hbm_peak,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this shape
+                         # (profiles/ncu_full_v4_kernels_batch128_ctx8192.md)
+                         "traffic": {"sparse_attend": 96.58e6, "select_blocks": 37.85e6}[dom],
                          "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
                          "stages": {"select_blocks": sel_bytes / (t_sel * 1e-3) / 1e9 / hbm_peak,
                                     "sparse_attend": att_bytes / (t_att * 1e-3) / 1e9 / hbm_peak}},
