@@ -424,11 +424,14 @@ int rivoli_kv_compress_decode(float* kv_state, float* score_state, const CompFin
  * (rotate != 0: the indexer's compressor, blockindex.hip:97-138) or the fp8 block-64 quantisation of the d - rd
  * un-rotated dims (the attention compressor, crates/oracles/src/v4oracle/compress.rs:235-247), and store the row as
  * bf16 at cache[(b * cache_rows + cache_row0 + pos[b] / ratio) * d]. prequant (optional) receives the row before
- * the finishing quantisation, [B][d] f32. */
+ * the finishing quantisation, [B][d] f32. packed / packed_exp (optional, both or neither; rotate != 0 and d == 128)
+ * receive the same row in the scorer's int8 + block-exponent form (see rivoli_v4_index_pack_bf16), at row
+ * b * cache_rows + cache_row0 + pos[b] / ratio of those arrays. */
 int rivoli_v4_compress_step_bf16(const CompGeom* p, int n_seqs, const int32_t* pos, const float* kv_proj,
                                  const float* score_proj, const float* ape, float* kv_state, float* score_state,
                                  const float* norm, const float* freqs, int rotate, uint16_t* cache, int cache_rows,
-                                 int cache_row0, float* prequant, void* stream);
+                                 int cache_row0, float* prequant, unsigned char* packed, uint32_t* packed_exp,
+                                 void* stream);
 
 /* Diagnostic, not on any product path (bench.py --profile gather): average milliseconds of a
  * launch in which each of n_ctas CTAs copies n_tiles tiles of 128 latent rows (576 bytes each,

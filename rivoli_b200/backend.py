@@ -497,11 +497,11 @@ def launch_kv_compress_decode(kv_state, score_state, norm, freqs, out, p: CompGe
 
 def launch_v4_compress_step_bf16(p: CompGeom, n_seqs: int, pos, kv_proj, score_proj, ape, kv_state, score_state, norm,
                                  freqs, rotate: bool, cache, cache_rows: int, cache_row0: int, prequant=None,
-                                 stream=None) -> None:
+                                 packed=None, packed_exp=None, stream=None) -> None:
     ensure_status(lib().rivoli_v4_compress_step_bf16(
         C.byref(p), C.c_int(n_seqs), _ptr(pos), _ptr(kv_proj), _ptr(score_proj), _ptr(ape), _ptr(kv_state),
         _ptr(score_state), _ptr(norm), _ptr(freqs), C.c_int(int(rotate)), _ptr(cache), C.c_int(cache_rows),
-        C.c_int(cache_row0), _ptr(prequant), _stream(stream)), "v4_compress_step_bf16")
+        C.c_int(cache_row0), _ptr(prequant), _ptr(packed), _ptr(packed_exp), _stream(stream)), "v4_compress_step_bf16")
 
 
 def probe_gather(method: int, depth: int, n_ctas: int, n_tiles: int, pool, n_pool_rows: int, scales, rows,

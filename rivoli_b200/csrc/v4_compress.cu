@@ -189,9 +189,12 @@ __global__ void __launch_bounds__(CP_THREADS) cp_step_kernel(CompGeom p, const i
                                                              float* score_state, const float* __restrict__ norm,
                                                              const float* __restrict__ freqs, int rotate,
                                                              uint16_t* __restrict__ cache, int cache_rows,
-                                                             int cache_row0, float* __restrict__ prequant) {
+                                                             int cache_row0, float* __restrict__ prequant,
+                                                             uint8_t* __restrict__ packed,
+                                                             uint32_t* __restrict__ packed_exp) {
     extern __shared__ __align__(16) float cp_row[];   // [d]
     __shared__ float red[CP_THREADS / 32];
+    __shared__ uint32_t exp_word;
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int sp = pos[b], slot = sp % p.ratio, d = p.d;
     const size_t st_n = (size_t)p.ents * p.cd;
@@ -231,9 +234,31 @@ __global__ void __launch_bounds__(CP_THREADS) cp_step_kernel(CompGeom p, const i
         // fp8 block-64 on the dims that were not rotated (crates/oracles/src/v4oracle/compress.rs:235-247)
         for (int blk = warp; blk < (d - p.rd) / 64; blk += CP_THREADS / 32) cp_act_quant_block(cp_row + blk * 64, cp_row + blk * 64, 64);
     }
+    if (tid == 0) exp_word = 0u;
     __syncthreads();
     uint16_t* out = cache + ((size_t)b * cache_rows + cache_row0 + sp / p.ratio) * d;
     for (int e = tid; e < d; e += CP_THREADS) out[e] = rv_f32_to_bf16(cp_row[e]);
+    if (packed) {
+        // the scorer's second form of the same row (d == 128, cache_rows rows per sequence): per block of 32, int8
+        // multiples of 2^(pb - 130), pb = biased exponent of the block's largest magnitude; 0xff = not of that form
+        const size_t prow = (size_t)b * cache_rows + cache_row0 + sp / p.ratio;
+        if (warp < 4) {
+            const float v = rv_bf16_to_f32(rv_f32_to_bf16(cp_row[warp * 32 + lane]));
+            const uint32_t bits = __float_as_uint(v);
+            int pb = (int)((bits >> 23) & 0xffu);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, o));
+            bool ok = pb >= 4 ? pb < 0xff : (pb == 0 && (bits & 0x7fffffffu) == 0);
+            const float x = pb >= 4 ? v * __int_as_float((257 - pb) << 23) : 0.0f;
+            const int m = __float2int_rn(x);
+            ok = ok && (float)m == x;
+            ok = __all_sync(0xffffffffu, ok);
+            packed[prow * 128 + warp * 32 + lane] = (uint8_t)(m & 0xff);
+            if (lane == 0) atomicOr(&exp_word, (uint32_t)(ok ? pb : 0xff) << (8 * warp));
+        }
+        __syncthreads();
+        if (tid == 0) packed_exp[prow] = exp_word;
+    }
 }
 
 static int cp_guard(const CompGeom& p) {
@@ -300,16 +325,19 @@ RIVOLI_API int rivoli_v4_compress_step_bf16(const CompGeom* pp, int n_seqs, cons
                                             const float* score_proj, const float* ape, float* kv_state,
                                             float* score_state, const float* norm, const float* freqs, int rotate,
                                             uint16_t* cache, int cache_rows, int cache_row0, float* prequant,
-                                            void* stream) {
+                                            unsigned char* packed, uint32_t* packed_exp, void* stream) {
     if (!pp) return 1000;
     const CompGeom p = *pp;
     if (int g = cp_guard(p)) return g;
     if (n_seqs <= 0 || cache_rows <= 0 || cache_row0 < 0) return 1001;
     if (rotate && (p.d > V4_ROT_MAX || (p.d & (p.d - 1)) || p.d % 32)) return 1002;
     if (!rotate && (p.d - p.rd) % 64) return 1004;
+    if ((packed != nullptr) != (packed_exp != nullptr)) return 1001;
+    if (packed && (!rotate || p.d != 128)) return 1002;   // the packed form is the indexer's: spread rows of width 128
     if ((size_t)p.d * 4 > 48 * 1024) return 1002;
     rv_drain_error();
     cp_step_kernel<<<(unsigned)n_seqs, CP_THREADS, (size_t)p.d * 4, (cudaStream_t)stream>>>(
-        p, pos, kv_proj, score_proj, ape, kv_state, score_state, norm, freqs, rotate, cache, cache_rows, cache_row0, prequant);
+        p, pos, kv_proj, score_proj, ape, kv_state, score_state, norm, freqs, rotate, cache, cache_rows, cache_row0, prequant,
+        packed, packed_exp);
     return rv_launch_status();
 }

@@ -339,13 +339,15 @@ def test_compressor_batched_step(rotate, d):
     d_kv, d_sc = dev(kv_state), dev(score_state)
     cache = torch.full((B, cache_rows, d), 0x1234, dtype=torch.uint16, device="cuda")
     preq = torch.zeros((B, d), device="cuda")
+    packed = torch.zeros((B, cache_rows, 128), dtype=torch.uint8, device="cuda") if rotate else None
+    pexp = torch.zeros((B, cache_rows), dtype=torch.int32, device="cuda") if rotate else None
     written = set()
     for t in range(steps):
         pos = pos0 + t
         kvp = rng.standard_normal((B, op.cd)).astype(np.float32)
         scp = rng.standard_normal((B, op.cd)).astype(np.float32)
         be.launch_v4_compress_step_bf16(bp, B, dev(pos), dev(kvp), dev(scp), dev(ape), d_kv, d_sc, dev(norm), dev(freqs),
-                                        rotate, cache, cache_rows, row0, preq)
+                                        rotate, cache, cache_rows, row0, preq, packed, pexp)
         got_pre, got_cache = preq.cpu().numpy(), cache.cpu().numpy()
         for b in range(B):
             orc.v4_compress_deposit_token(kvp[b], scp[b], ape, kv_state[b], score_state[b], op, int(pos[b]))
@@ -360,6 +362,17 @@ def test_compressor_batched_step(rotate, d):
             blk = int(pos[b]) // op.ratio
             assert np.array_equal(got_cache[b, row0 + blk], orc.f32_to_bf16(fin)), (t, b)
             written.add((b, row0 + blk))
+            if rotate:   # the int8 + exponent form of the same row: value = int8 * 2^(pb - 130) per block of 32
+                pk = packed[b, row0 + blk].cpu().numpy().view(np.int8).astype(np.float64)
+                ex = int(pexp[b, row0 + blk].item()) & 0xffffffff
+                for j in range(4):
+                    pb = (ex >> (8 * j)) & 0xff
+                    seg = fin[32 * j:32 * j + 32].astype(np.float64)
+                    if pb == 0:
+                        assert not seg.any() and not pk[32 * j:32 * j + 32].any()
+                    else:
+                        assert pb != 0xff and np.array_equal(pk[32 * j:32 * j + 32] * 2.0 ** (pb - 130), seg)
+                        assert np.abs(pk[32 * j:32 * j + 32]).max() in range(8, 16)
         assert np.array_equal(bits(d_kv.cpu().numpy()), bits(kv_state))
         assert np.array_equal(bits(d_sc.cpu().numpy()), bits(score_state))
     got_cache = cache.cpu().numpy()
