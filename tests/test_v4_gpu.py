@@ -494,3 +494,58 @@ def test_bench_shape_properties():
     be.launch_v4_sparse_attend_bf16(g, B, q, layer.kv_cache, layer.sink, one, layer.cols, out_1)
     want = layer.kv_cache.view(torch.int16)[torch.arange(B, device="cuda"), sel_a[:, 300].long()]
     assert torch.equal(out_1.view(torch.int16), want[:, None, :].expand(-1, g.n_heads, -1))
+
+
+def test_token_steps_wire_compressors_selection_and_attention():
+    """Twenty decode tokens through V4TokenStep for sequences at different phases. After every token the oracle
+    recomputes selection and attention FROM THE DEVICE'S OWN CACHES: rows must match exactly and outputs within the
+    attention bar; the caches must have grown by exactly the blocks that closed, at their positional rows."""
+    be = _be()
+    from rivoli_b200.v4 import V4Compressor, V4DecodeLayer, V4TokenStep
+    rng = np.random.default_rng(50)
+    g = wl.make_geom(n_heads=4, head_dim=128, window=8, index_heads=4, index_dim=128, index_topk=3, max_comp=32)
+    bg = be.V4Geom(*[getattr(g, n) for n, _ in orc.V4Geom._fields_])
+    B, steps = 3, 20
+    pos0 = np.array([3, 9, 30], np.int32)
+    layer = V4DecodeLayer(bg, B)
+    layer.sink.copy_(dev(rng.standard_normal(g.n_heads).astype(np.float32)))
+    pa, pi = be.CompGeom.make(ratio=4, d=128, rd=64), be.CompGeom.make(ratio=4, d=128, rd=64)
+    opa = orc.CompGeom.make(ratio=4, d=128, rd=64)
+    na, fa, aa = _comp_fixture(rng, opa, 128)
+    ni, fi, ai = _comp_fixture(rng, opa, 128)
+    comp_a = V4Compressor(pa, B, dev(aa), dev(na), dev(fa), rotate=False)
+    comp_i = V4Compressor(pi, B, dev(ai), dev(ni), dev(fi), rotate=True)
+    step = V4TokenStep(layer, comp_a, comp_i)
+    # history: earlier blocks already in the caches (random bf16 rows; indexer rows spread), packed form included
+    hist = (pos0 + 1) // 4
+    kvc = np.zeros((B, layer.kv_rows, 128), np.uint16)
+    ikv = np.zeros((B, g.max_comp, 128), np.uint16)
+    for b in range(B):
+        kvc[b, :8] = orc.f32_to_bf16(rng.standard_normal((8, 128)).astype(np.float32))
+        kvc[b, 8:8 + hist[b]] = orc.f32_to_bf16(rng.standard_normal((hist[b], 128)).astype(np.float32))
+        if hist[b]:
+            rows = orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((hist[b], 128)).astype(np.float32)))
+            ikv[b, :hist[b]] = orc.f32_to_bf16(orc.v4_spread(rows, 128)[1])
+    layer.kv_cache.copy_(dev(kvc)); layer.index_kv.copy_(dev(ikv))
+    layer.pack_index_rows(None, dev(hist.astype(np.int32)), int(hist.max()))
+    f32 = lambda *s: rng.standard_normal(s).astype(np.float32)
+    for t in range(steps):
+        pos = pos0 + 1 + t
+        q = orc.f32_to_bf16(f32(B, 4, 128))
+        iq = orc.f32_to_bf16(orc.v4_spread(orc.bf16_to_f32(orc.f32_to_bf16(f32(B * 4, 128))), 128)[1]).reshape(B, 4, 128)
+        iw = orc.bf16_to_f32(orc.f32_to_bf16(f32(B, 4)))
+        entry = orc.f32_to_bf16(f32(B, 128))
+        out = step(dev(pos), dev(entry), (dev(f32(B, 256)), dev(f32(B, 256))), (dev(f32(B, 256)), dev(f32(B, 256))),
+                   dev(q), dev(iq), dev(iw))
+        torch.cuda.synchronize()
+        kvc_now, ikv_now = layer.kv_cache.cpu().numpy(), layer.index_kv.cpu().numpy()
+        assert not layer.refolded.any().item()
+        for b in range(B):
+            assert np.array_equal(kvc_now[b, pos[b] % 8], entry[b])                       # the ring took the token
+            n_comp = (pos[b] + 1) // 4
+            assert ikv_now[b, :n_comp].any(axis=1).all() and not ikv_now[b, n_comp:].any()  # blocks by position
+            assert kvc_now[b, 8:8 + n_comp].any(axis=1).all() and not kvc_now[b, 8 + n_comp:].any()
+        want_sel, want_out = orc.v4_decode_step_bf16(g, pos, q, kvc_now, layer.sink.cpu().numpy(), iq, iw, ikv_now)
+        assert np.array_equal(layer.sel.cpu().numpy(), want_sel), t
+        ok, worst = wl.attend_close(out.cpu().numpy(), want_out)
+        assert ok, (t, worst)
