@@ -354,8 +354,9 @@ typedef struct V4Geom {
  * Scores are bit-exact. With index_dim == 128 they are computed on the integer tensor cores
  * (mma.m16n8k32.s8 per block of 32, exact) whenever the rows have the form the spread produces and the
  * block exponents of a (head, block) pair span at most 9 binades, which makes the host's ordered f32 fold
- * exact as well; any sequence with a row or pair outside that is re-scored by the ordered CUDA-core fold
- * (force_fold != 0 sends every sequence there). Indices are bit-exact. 1001 bad sizes / null scratch,
+ * exact as well; a cached row outside that has its column re-scored by the ordered CUDA-core fold, a query row
+ * outside it sends the whole sequence there (force_fold != 0 sends every sequence there; the flag word of a
+ * sequence reads 1 for "whole sequence", 2 for "some columns"). Indices are bit-exact. 1001 bad sizes / null scratch,
  * 1002 index_heads > 64 or index_dim > 128 or max_comp > 16384 or index_topk > 4096, 1004 index_dim % 32 != 0. */
 size_t rivoli_v4_select_scratch_bytes(const V4Geom* g, int n_seqs);
 int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const int32_t* pos, const uint16_t* index_q,

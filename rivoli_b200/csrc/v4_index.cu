@@ -64,12 +64,16 @@ constexpr int SC_MAX_HD = 128;
 template <class T>
 __device__ __forceinline__ void v4_score_blocks_warp(const float* __restrict__ qT, const float* __restrict__ wsh,
                                                      float* __restrict__ stage, const T* __restrict__ kv, int c0,
-                                                     int n_comp, int heads, int hd, float (&out)[SC_CB]) {
+                                                     int n_comp, int heads, int hd, float (&out)[SC_CB],
+                                                     const uint32_t* cols = nullptr) {
     const int lane = threadIdx.x & 31;
     __syncwarp();
     for (int i = lane; i < SC_CB * hd; i += 32) {
         const int cb = i / hd, e = i - cb * hd;
-        stage[i] = c0 + cb < n_comp ? v4_load_f32(kv, (size_t)(c0 + cb) * hd + e) : 0.0f;
+        // blocks c0 .. c0 + SC_CB - 1, or the listed ones (cols[c0 + cb], c0 + cb < n_comp = the list's length)
+        const bool live = c0 + cb < n_comp;
+        const size_t c = live ? (cols ? cols[c0 + cb] : (uint32_t)(c0 + cb)) : 0;
+        stage[i] = live ? v4_load_f32(kv, c * hd + e) : 0.0f;
     }
     __syncwarp();
     float dot[SC_CB][2];
@@ -182,6 +186,7 @@ __global__ void v4_score_blocks_serial_kernel(const float* __restrict__ q, const
 constexpr int SI_THREADS = 256;
 constexpr int SI_CHUNK = 256;       // blocks (columns) per CTA
 constexpr int SI_SPAN = 9;
+constexpr uint32_t SI_REFOLD = 0xffc0deadu;   // score word of a column left to the ordered fold (a NaN no fold produces)
 
 __device__ __forceinline__ void v4_mma_s8(int (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
@@ -287,6 +292,7 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
         uint32_t b0[4], b1[4];
         float ku[4];
         int k_lo = 1000, k_hi = -1000;
+        bool okk = true;                                    // this row (column of the score matrix)
         if (PACKED) {
             const uint8_t* prow = packed + ((size_t)b * g.max_comp + c) * 128;
             const uint32_t e4 = c < n_comp ? packed_exp[(size_t)b * g.max_comp + c] : 0u;
@@ -298,7 +304,7 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
                     b1[j] = *reinterpret_cast<const uint32_t*>(prow + j * 32 + 16 + quad * 4);
                 }
                 const int pb = (e4 >> (8 * j)) & 0xff;
-                if (pb == 0xff) ok = false;                 // the packer could not take this block
+                if (pb == 0xff) okk = false;                // the packer could not take this block
                 ku[j] = pb == 0xff ? 0.0f : v4_unit(pb);
                 if (pb >= 4 && pb != 0xff) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
             }
@@ -313,9 +319,9 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
                 int pb = max(v4_max_exp4(lo.x, lo.y), v4_max_exp4(hi.x, hi.y));
                 pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 1));
                 pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 2));
-                const float inv = v4_unit_inv(pb, ok);
-                b0[j] = v4_pack4(lo.x, lo.y, inv, ok);
-                b1[j] = v4_pack4(hi.x, hi.y, inv, ok);
+                const float inv = v4_unit_inv(pb, okk);
+                b0[j] = v4_pack4(lo.x, lo.y, inv, okk);
+                b1[j] = v4_pack4(hi.x, hi.y, inv, okk);
                 ku[j] = v4_unit(pb);
                 if (pb >= 4) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
             }
@@ -324,7 +330,9 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
         // inside [q_lo + k_lo, q_hi + k_hi] - 260. Inside the limits the ordered f32 fold is exact.
         if (k_hi >= k_lo && q_hi >= q_lo &&
             (q_span + (k_hi - k_lo) > SI_SPAN || q_lo + k_lo - 260 < -120 || q_hi + k_hi - 260 > 100))
-            ok = false;
+            okk = false;
+        // a row's verdict sits in the four lanes of its quad; lane j < 8 writes column j
+        const uint32_t bad_rows = __ballot_sync(0xffffffffu, !okk);
         // units of the two columns this thread's accumulators belong to
         float kuA[4], kuB[4];
 #pragma unroll
@@ -361,7 +369,8 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
             float acc = 0.0f;
 #pragma unroll 8
             for (int hh = 0; hh < heads; ++hh) acc = __fadd_rn(acc, terms[warp][hh][lane]);
-            scores[(size_t)b * g.max_comp + c0 + lane] = v4_rbf16_hw(acc);
+            const bool refold = ((bad_rows >> (4 * lane)) & 0xfu) != 0;
+            scores[(size_t)b * g.max_comp + c0 + lane] = refold ? __uint_as_float(SI_REFOLD) : v4_rbf16_hw(acc);
         }
         __syncwarp();
     }
@@ -420,6 +429,7 @@ __device__ __forceinline__ uint32_t v4_total_key(float v) {
 struct SelSmem {
     TkShared tk;
     float wsh[SC_MAX_HEADS];
+    uint32_t n_bad;      // columns the integer scorer left to the ordered fold
 };
 
 __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const int32_t* __restrict__ pos,
@@ -428,7 +438,7 @@ __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const i
                                                                const uint16_t* __restrict__ index_kv,
                                                                int32_t* __restrict__ sel,
                                                                float* __restrict__ scores,
-                                                               const int32_t* __restrict__ flags, int force_fold) {
+                                                               int32_t* __restrict__ flags, int force_fold) {
     extern __shared__ __align__(16) unsigned char sel_smem_raw[];
     SelSmem& sh = *reinterpret_cast<SelSmem*>(sel_smem_raw);
     float* qT = reinterpret_cast<float*>(sel_smem_raw + ((sizeof(SelSmem) + 15) & ~(size_t)15));
@@ -455,12 +465,12 @@ __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const i
     }
     float* srow = scores + (size_t)b * g.max_comp;
     rv_grid_dep_wait();      // the scorer's rows and flags
-    if (force_fold || flags[b]) {
-        // the ordered CUDA-core fold: rows the integer scorer could not take, or every row on request
+    const uint16_t* kv = index_kv + (size_t)b * g.max_comp * g.index_dim;
+    // the ordered CUDA-core fold over every block: on request, or when the integer scorer could not take the queries
+    auto fold_all = [&]() {
         v4_stage_q(index_q + (size_t)b * g.index_heads * g.index_dim, index_w + (size_t)b * g.index_heads, g.index_heads,
                    g.index_dim, qT, sh.wsh);
         __syncthreads();
-        const uint16_t* kv = index_kv + (size_t)b * g.max_comp * g.index_dim;
         for (int c0 = warp * SC_CB; c0 < n_comp; c0 += TK_WARPS * SC_CB) {
             float out[SC_CB];
             v4_score_blocks_warp(qT, sh.wsh, stage + warp * SC_CB * g.index_dim, kv, c0, n_comp, g.index_heads,
@@ -473,8 +483,44 @@ __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const i
                 srow[c0 + lane] = v;
             }
         }
+    };
+    if (force_fold || (flags[b] & 1)) {
+        fold_all();
     } else {
-        for (int c = tid; c < n_comp; c += TK_THREADS) sc[c] = srow[c];
+        // take the scorer's row; columns it marked are re-scored by the ordered fold, a few per warp
+        if (tid == 0) sh.n_bad = 0u;
+        __syncthreads();
+        for (int c = tid; c < n_comp; c += TK_THREADS) {
+            const float v = srow[c];
+            sc[c] = v;
+            if (__float_as_uint(v) == SI_REFOLD) {
+                const uint32_t i = atomicAdd(&sh.n_bad, 1u);
+                if (i < (uint32_t)K) picked[i] = (uint32_t)c;
+            }
+        }
+        __syncthreads();
+        const int n_bad = (int)sh.n_bad;
+        if (n_bad > K) {                 // more than the list holds: everything again
+            __syncthreads();
+            fold_all();
+        } else if (n_bad > 0) {
+            v4_stage_q(index_q + (size_t)b * g.index_heads * g.index_dim, index_w + (size_t)b * g.index_heads,
+                       g.index_heads, g.index_dim, qT, sh.wsh);
+            __syncthreads();
+            for (int i0 = warp * SC_CB; i0 < n_bad; i0 += TK_WARPS * SC_CB) {
+                float out[SC_CB];
+                v4_score_blocks_warp(qT, sh.wsh, stage + warp * SC_CB * g.index_dim, kv, i0, n_bad, g.index_heads,
+                                     g.index_dim, out, picked);
+                if (lane < SC_CB && i0 + lane < n_bad) {
+                    float v = out[0];
+#pragma unroll
+                    for (int cb = 1; cb < SC_CB; ++cb) v = lane == cb ? out[cb] : v;
+                    sc[picked[i0 + lane]] = v;
+                    srow[picked[i0 + lane]] = v;
+                }
+            }
+        }
+        if (n_bad > 0 && tid == 0) atomicOr(&flags[b], 2);
     }
     __syncthreads();
     auto key_at = [&](int i) { return v4_total_key(sc[i]); };
@@ -562,6 +608,6 @@ RIVOLI_API int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const i
     }
     cudaFuncSetAttribute(v4_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     rv_launch_dependent(v4_select_kernel, dim3((unsigned)n_seqs), dim3(TK_THREADS), smem, st, *g, pos, index_q, index_w,
-                        index_kv, sel, scores, (const int32_t*)flags, tensor ? 0 : 1);
+                        index_kv, sel, scores, flags, tensor ? 0 : 1);
     return rv_launch_status();
 }

@@ -34,7 +34,8 @@ class V4DecodeLayer:
 
     @property
     def refolded(self):
-        """Per sequence: 1 if the integer scorer handed it to the ordered CUDA-core fold in the last select()."""
+        """Per sequence after the last select(): bit 0 = the integer scorer handed the whole sequence to the ordered
+        CUDA-core fold (its queries were not of the integer form), bit 1 = some of its columns were re-scored."""
         return self.scratch[self.B * self.g.max_comp:].view(torch.int32)
 
     def pack_index_rows(self, row_begin, row_end, max_rows: int, stream=None):

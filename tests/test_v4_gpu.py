@@ -214,9 +214,10 @@ def test_fully_masked_row_is_nan_and_masked_slots_are_ignored():
 
 
 def test_rows_outside_the_integer_form_are_refolded_exactly():
-    """Arbitrary bf16 index rows (not spread): the integer scorer must notice and hand the sequence to the
-    ordered fold; scores and indices stay bit-exact. One sequence keeps spread rows and stays on the
-    tensor path; one has a single block pair whose exponents are far apart."""
+    """Arbitrary bf16 index rows (not spread): the integer scorer must notice and leave them to the ordered fold
+    (single columns when a cached row is the problem, the whole sequence when its queries are); scores and indices
+    stay bit-exact. One sequence keeps spread rows and stays on the tensor path; one has a single row with one
+    block 14 binades above its neighbours."""
     g = wl.make_geom(max_comp=640, index_topk=96)
     pos = np.array([2559, 2559, 2559, 2559], np.int32)
     inp = wl.make_inputs(g, 4, pos, seed=12)
@@ -230,7 +231,7 @@ def test_rows_outside_the_integer_form_are_refolded_exactly():
                                                           inp["iw"], inp["ikv"], want_scores=True)
     for pack in (False, True):
         sel, out, sc, flags = _run_step(g, inp, want_flags=True, pack=pack)
-        assert flags.tolist() == [0, 1, 1, 1]
+        assert flags.tolist() == [0, 2, 1, 2]      # bit 0: whole sequence re-folded (its queries); bit 1: some columns
         assert np.array_equal(bits(sc), bits(want_sc))
         assert np.array_equal(sel, want_sel)
 
