@@ -351,11 +351,11 @@ typedef struct V4Geom {
  * index_q bf16 [B][index_heads][index_dim] (already spread), index_w f32 [B][index_heads].
  * scratch = rivoli_v4_select_scratch_bytes(): the score rows f32 [B][max_comp] of the sequences that ranked
  * (readable after the call), then one flag per sequence.
- * Scores are bit-exact. With index_dim == 128 they are computed on the integer tensor cores
- * (mma.m16n8k32.s8 per block of 32, exact) whenever the rows have the form the spread produces and the
- * block exponents of a (head, block) pair span at most 9 binades, which makes the host's ordered f32 fold
- * exact as well; a cached row outside that has its column re-scored by the ordered CUDA-core fold, a query row
- * outside it sends the whole sequence there (force_fold != 0 sends every sequence there; the flag word of a
+ * Scores are bit-exact. With index_dim == 128 they are computed on the integer tensor cores (four chained
+ * mma.m16n8k32.s8 per dot product, exact) for rows of the form the spread produces (integer multiples of a row unit,
+ * block scales at most 3 binades apart), for which the host's ordered f32 fold is exact as well; a cached row
+ * outside that has its column re-scored by the ordered CUDA-core fold, a query row outside it sends the whole
+ * sequence there (force_fold != 0 sends every sequence there; the flag word of a
  * sequence reads 1 for "whole sequence", 2 for "some columns"). Indices are bit-exact. 1001 bad sizes / null scratch,
  * 1002 index_heads > 64 or index_dim > 128 or max_comp > 16384 or index_topk > 4096, 1004 index_dim % 32 != 0. */
 size_t rivoli_v4_select_scratch_bytes(const V4Geom* g, int n_seqs);
@@ -364,9 +364,10 @@ int rivoli_v4_select_blocks_bf16(const V4Geom* g, int n_seqs, const int32_t* pos
                                  const uint32_t* packed_exp, int32_t* sel, void* scratch, int force_fold, void* stream);
 
 /* Optional second form of the indexer's compressed rows, written ONCE when a row enters the cache, so that the
- * scorer does not convert every row from bf16 on every step: packed int8 [B][max_comp][128] (each block of 32 in
- * units of 2^(e - 130), e = biased exponent of the block's largest magnitude) and packed_exp u32 [B][max_comp]
- * (the four block exponents, one byte each; 0 = empty block, 0xff = block not of that form). Packs rows
+ * scorer does not convert every row from bf16 on every step: packed int8 [B][max_comp][128] (the row in units of
+ * 2^(e - 130), e = the smallest biased exponent any non-empty block's largest magnitude has) and packed_exp u32
+ * [B][max_comp] (e; 0 = the row is all zeros; 0xff = the row is not of that form: blocks more than 3 binades apart,
+ * a value that is not a multiple of the unit, magnitudes outside 2^-40 .. 2^40). Packs rows
  * [row_begin[b], row_end[b]) of every sequence (row_begin may be null = 0; max_rows = the largest count, sizes the
  * grid). Pass both arrays to rivoli_v4_select_blocks_bf16 (or two nulls); index_kv is still read by the ordered
  * fold. 1001 nulls / sizes, 1002 index_dim != 128. */

@@ -195,6 +195,7 @@ __global__ void __launch_bounds__(CP_THREADS) cp_step_kernel(CompGeom p, const i
     extern __shared__ __align__(16) float cp_row[];   // [d]
     __shared__ float red[CP_THREADS / 32];
     __shared__ uint32_t exp_word;
+    __shared__ int row_lo, row_hi;
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int sp = pos[b], slot = sp % p.ratio, d = p.d;
     const size_t st_n = (size_t)p.ents * p.cd;
@@ -234,30 +235,37 @@ __global__ void __launch_bounds__(CP_THREADS) cp_step_kernel(CompGeom p, const i
         // fp8 block-64 on the dims that were not rotated (crates/oracles/src/v4oracle/compress.rs:235-247)
         for (int blk = warp; blk < (d - p.rd) / 64; blk += CP_THREADS / 32) cp_act_quant_block(cp_row + blk * 64, cp_row + blk * 64, 64);
     }
-    if (tid == 0) exp_word = 0u;
+    if (tid == 0) { exp_word = 0u; row_lo = 1000; row_hi = -1000; }
     __syncthreads();
     uint16_t* out = cache + ((size_t)b * cache_rows + cache_row0 + sp / p.ratio) * d;
     for (int e = tid; e < d; e += CP_THREADS) out[e] = rv_f32_to_bf16(cp_row[e]);
     if (packed) {
-        // the scorer's second form of the same row (d == 128, cache_rows rows per sequence): per block of 32, int8
-        // multiples of 2^(pb - 130), pb = biased exponent of the block's largest magnitude; 0xff = not of that form
+        // the scorer's second form of the same row (d == 128, cache_rows rows per sequence): int8 multiples of the row's
+        // unit 2^(pmin - 130), pmin = the smallest biased exponent any non-empty block's largest magnitude has; the
+        // row's word holds pmin, 0 for an all-zero row, 0xff when the row is not of that form (blocks more than 3
+        // binades apart, magnitudes outside 2^-40 .. 2^40)
         const size_t prow = (size_t)b * cache_rows + cache_row0 + sp / p.ratio;
+        float v = 0.0f;
         if (warp < 4) {
-            const float v = rv_bf16_to_f32(rv_f32_to_bf16(cp_row[warp * 32 + lane]));
-            const uint32_t bits = __float_as_uint(v);
-            int pb = (int)((bits >> 23) & 0xffu);
+            v = rv_bf16_to_f32(rv_f32_to_bf16(cp_row[warp * 32 + lane]));
+            int pb = (int)((__float_as_uint(v) >> 23) & 0xffu);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, o));
-            bool ok = pb >= 4 ? pb < 0xff : (pb == 0 && (bits & 0x7fffffffu) == 0);
-            const float x = pb >= 4 ? v * __int_as_float((257 - pb) << 23) : 0.0f;
-            const int m = __float2int_rn(x);
-            ok = ok && (float)m == x;
-            ok = __all_sync(0xffffffffu, ok);
-            packed[prow * 128 + warp * 32 + lane] = (uint8_t)(m & 0xff);
-            if (lane == 0) atomicOr(&exp_word, (uint32_t)(ok ? pb : 0xff) << (8 * warp));
+            if (lane == 0 && pb > 0) { atomicMin(&row_lo, pb); atomicMax(&row_hi, pb); }
         }
         __syncthreads();
-        if (tid == 0) packed_exp[prow] = exp_word;
+        const int lo = row_lo, hi = row_hi;
+        const bool form = hi < lo || (lo >= 87 && hi <= 167 && hi - lo <= 3);
+        if (warp < 4) {
+            const float x = (form && hi >= lo) ? v * __int_as_float((257 - lo) << 23) : 0.0f;
+            const int m = __float2int_rn(x);
+            bool ok = form && (float)m == x && (hi >= lo || (__float_as_uint(v) & 0x7fffffffu) == 0);
+            ok = __all_sync(0xffffffffu, ok);
+            packed[prow * 128 + warp * 32 + lane] = (uint8_t)(m & 0xff);
+            if (lane == 0 && !ok) atomicOr(&exp_word, 1u);
+        }
+        __syncthreads();
+        if (tid == 0) packed_exp[prow] = exp_word ? 0xffu : (hi >= lo ? (uint32_t)lo : 0u);
     }
 }
 

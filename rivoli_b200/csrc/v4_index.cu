@@ -171,27 +171,31 @@ __global__ void v4_score_blocks_serial_kernel(const float* __restrict__ q, const
 // block scorer on the integer tensor cores, exact
 //
 // Rows that came through the spread are, block of 32 by block of 32, small integers times one power of
-// two: v = m * 2^e with |m| < 16 once e = (exponent of the block's largest magnitude) - 3. A block's share of
-// a dot product is then I_j * 2^(eq_j + ek_j) with I_j = sum of 32 integer products, which
-// mma.m16n8k32.s8 returns exactly (K = 32 is one block). The host's ascending f32 fold over the 128
-// products never rounds as long as every partial sum is representable: all of them are multiples of
-// 2^Emin and smaller than 2^(Emax + 15) (4 blocks x 32 terms x 15 x 15 < 2^15), so Emax - Emin <= 9
-// suffices, and then the fold equals the exact sum, which is what sum_j float(I_j) * 2^E_j gives here.
-// Everything after the dot (bf16 store, relu, head weight, bf16 store, ascending head sum) is evaluated
-// in the host's order on CUDA cores. A pair that misses the condition, or a row that is not of that form
-// (a value that is not an integer multiple of its block's unit, a subnormal, an exponent near the range
-// ends), raises the sequence's flag and the selection kernel re-scores that sequence with the ordered
-// CUDA-core fold: the result is exact either way.
+// two, and the block scales of one row lie within a few binades of each other (that is what the Hadamard
+// rotation is for). Take as a ROW's unit u = 2^(pmin - 130), pmin the smallest biased exponent any
+// non-empty block's largest magnitude has: every value of the row is an integer multiple of u, below
+// 16 * 2^span in magnitude (span = pmax - pmin). With span <= 3 on both sides the integers fit int8 and
+// the whole 128-term dot product is ONE integer,
+//     q_h . kv_c = I * u_q * u_k,   I = sum of 128 integer products,  |I| < 2^21,
+// which four chained mma.m16n8k32.s8 return exactly. The host's ascending f32 fold over the 128 products
+// never rounds here: every partial sum is a multiple of u_q u_k below 2^21 u_q u_k, inside f32's 24 bits,
+// so it ends on the same value, float(I) * u_q * u_k. Everything after the dot (bf16 store, relu, head
+// weight, bf16 store, ascending head sum) runs in the host's order on CUDA cores.
+// A CACHED row that is not of that form (a value that is not a multiple of the unit, block scales more
+// than 3 binades apart, a subnormal, magnitudes outside 2^-40 .. 2^40) gets a marker instead of a score
+// and the selection kernel re-scores that column with the ordered CUDA-core fold; a QUERY row outside the
+// form raises the sequence's flag and the whole sequence takes the ordered fold. Exact either way.
 // ---------------------------------------------------------------------------------------------------
 constexpr int SI_THREADS = 256;
 constexpr int SI_CHUNK = 256;       // blocks (columns) per CTA
-constexpr int SI_SPAN = 9;
+constexpr int SI_SPAN = 3;          // binades between the block scales of one row
+constexpr int SI_PMIN = 87, SI_PMAX = 167;     // biased exponents 2^-40 .. 2^40
 constexpr uint32_t SI_REFOLD = 0xffc0deadu;   // score word of a column left to the ordered fold (a NaN no fold produces)
 
 __device__ __forceinline__ void v4_mma_s8(int (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1), "r"(0));
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ float v4_rbf16_hw(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }  // finite inputs
 
@@ -201,29 +205,32 @@ __device__ __forceinline__ int v4_max_exp4(uint32_t w0, uint32_t w1) {
     return (int)(max(a, b) >> 23);
 }
 // Four bf16 values (two words) times `scale` (a power of two) -> four int8. ok is cleared when a product is
-// not an integer (the value is not a multiple of the block's unit).
+// not an integer (the value is not a multiple of the row's unit).
 __device__ __forceinline__ uint32_t v4_pack4(uint32_t w0, uint32_t w1, float scale, bool& ok) {
     const float x0 = __uint_as_float(w0 << 16) * scale, x1 = __uint_as_float(w0 & 0xffff0000u) * scale;
     const float x2 = __uint_as_float(w1 << 16) * scale, x3 = __uint_as_float(w1 & 0xffff0000u) * scale;
     const int m0 = __float2int_rn(x0), m1 = __float2int_rn(x1), m2 = __float2int_rn(x2), m3 = __float2int_rn(x3);
     ok = ok && (float)m0 == x0 && (float)m1 == x1 && (float)m2 == x2 && (float)m3 == x3;
-    if (scale == 0.0f) ok = ok && ((w0 | w1) & 0x7fff7fffu) == 0;   // an "empty" block must really be zeros
+    if (scale == 0.0f) ok = ok && ((w0 | w1) & 0x7fff7fffu) == 0;   // an "empty" row must really be zeros
     // cvt.pack d, a, b, c: d[7:0] = sat(b), d[15:8] = sat(a), d[31:16] = c[15:0]
     uint32_t hi, out;
     asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(m3), "r"(m2), "r"(0));
     asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(m1), "r"(m0), "r"(hi));
     return out;
 }
-// 2^(130 - pb): turns values of a block whose largest exponent is pb into integers below 16. Blocks whose
-// exponent sits at the very bottom of the range are left to the ordered fold.
-__device__ __forceinline__ float v4_unit_inv(int pb, bool& ok) {
-    if (pb < 4) { ok = ok && pb == 0; return 0.0f; }
-    return __int_as_float((257 - pb) << 23);
+// Row unit from the smallest / largest block exponent of a row (pmin > pmax when every block is empty):
+// inv = 2^(130 - pmin) turns the row into integers, unit = 2^(pmin - 130) turns them back; both 0 for an empty
+// row. Rows outside the limits clear ok.
+__device__ __forceinline__ void v4_row_unit(int pmin, int pmax, float& inv, float& unit, bool& ok) {
+    inv = 0.0f;
+    unit = 0.0f;
+    if (pmax < pmin) return;
+    if (pmin < SI_PMIN || pmax > SI_PMAX || pmax - pmin > SI_SPAN) { ok = false; return; }
+    inv = __int_as_float((257 - pmin) << 23);
+    unit = __int_as_float((pmin - 3) << 23);
 }
-// 2^(pb - 130), or 0 for an empty block.
-__device__ __forceinline__ float v4_unit(int pb) { return pb < 4 ? 0.0f : __int_as_float((pb - 3) << 23); }
 
-// PACKED: the rows come as int8 + block exponents (rivoli_v4_index_pack_bf16), written once when a row enters
+// PACKED: the rows come as int8 + row exponent (rivoli_v4_index_pack_bf16), written once when a row enters
 // the cache; otherwise every row is converted from bf16 on every step.
 template <bool PACKED>
 __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, const int32_t* __restrict__ pos,
@@ -235,9 +242,8 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
                                                                    float* __restrict__ scores,
                                                                    int32_t* __restrict__ flags) {
     __shared__ __align__(16) uint32_t qfrag[4 * 4 * 32 * 4];   // [m-tile][block][lane][4 regs]: A fragments, 8 KB
-    __shared__ __align__(16) float qunit[64][4];               // per head: 2^(e - 130) of its four blocks (0 = empty)
+    __shared__ float qunit[64];                                // per head: its row unit (0 = empty row)
     __shared__ float wsh[64];
-    __shared__ int qstat[3];                                   // over the heads: min / max block exponent, widest span
     __shared__ __align__(16) float terms[SI_THREADS / 32][64][8];   // written as float2: needs the alignment
     const int b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_comp = min((pos[b] + 1) / g.ratio, g.max_comp);
@@ -245,8 +251,6 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
     if (n_comp <= g.index_topk || c_begin >= n_comp) return;   // positional sequences are not scored
     const int heads = g.index_heads;
     bool ok = true;
-    if (tid == 0) { qstat[0] = 1000; qstat[1] = -1000; qstat[2] = 0; }
-    __syncthreads();
     // ---- q of this sequence: one thread per (head, block of 32)
     {
         const int hh = tid >> 2, j = tid & 3;
@@ -265,24 +269,23 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
 #pragma unroll
             for (int i = 0; i < 16; ++i) wv[i] = 0;
         }
-        const float inv = v4_unit_inv(pb, ok);
+        // exponent range of the head's non-empty blocks (its four threads are neighbours)
+        int lo = pb > 0 ? pb : 1000, hi = pb > 0 ? pb : -1000;
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, 1)); hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, 1));
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, 2)); hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, 2));
+        float inv, unit;
+        v4_row_unit(lo, hi, inv, unit, ok);
         const int mt = hh >> 4, r = hh & 15;
 #pragma unroll
         for (int k4 = 0; k4 < 8; ++k4) {                       // values 4 k4 .. 4 k4 + 3 of the block
-            const uint32_t packed = v4_pack4(wv[2 * k4], wv[2 * k4 + 1], inv, ok);
+            const uint32_t packed4 = v4_pack4(wv[2 * k4], wv[2 * k4 + 1], inv, ok);
             const int kk = 4 * k4, fl = (r & 7) * 4 + ((kk & 15) >> 2), reg = (r >> 3) + 2 * (kk >> 4);
-            qfrag[((mt * 4 + j) * 32 + fl) * 4 + reg] = packed;
+            qfrag[((mt * 4 + j) * 32 + fl) * 4 + reg] = packed4;
         }
-        qunit[hh][j] = v4_unit(pb);
-        // exponent range of the head's non-empty blocks (its four threads are neighbours)
-        int lo = pb >= 4 ? pb : 1000, hi = pb >= 4 ? pb : -1000;
-        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, 1)); hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, 1));
-        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, 2)); hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, 2));
-        if (j == 0 && hi >= lo) { atomicMin(&qstat[0], lo); atomicMax(&qstat[1], hi); atomicMax(&qstat[2], hi - lo); }
+        if (j == 0) qunit[hh] = unit;
         if (tid < 64) wsh[tid] = tid < heads ? index_w[(size_t)b * heads + tid] : 0.0f;
     }
     __syncthreads();
-    const int q_lo = qstat[0], q_hi = qstat[1], q_span = qstat[2];
     const uint16_t* kv = index_kv + (size_t)b * g.max_comp * 128;
     const int grp = lane >> 2, quad = lane & 3;
     const int c_end = min(n_comp, c_begin + SI_CHUNK);
@@ -290,12 +293,11 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
         // ---- B fragments: row c0 + grp, this thread's 8 values of each block
         const int c = c0 + grp;
         uint32_t b0[4], b1[4];
-        float ku[4];
-        int k_lo = 1000, k_hi = -1000;
+        float ku = 0.0f;
         bool okk = true;                                    // this row (column of the score matrix)
         if (PACKED) {
             const uint8_t* prow = packed + ((size_t)b * g.max_comp + c) * 128;
-            const uint32_t e4 = c < n_comp ? packed_exp[(size_t)b * g.max_comp + c] : 0u;
+            const uint32_t e = c < n_comp ? packed_exp[(size_t)b * g.max_comp + c] : 0u;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 b0[j] = b1[j] = 0u;
@@ -303,61 +305,50 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
                     b0[j] = *reinterpret_cast<const uint32_t*>(prow + j * 32 + quad * 4);
                     b1[j] = *reinterpret_cast<const uint32_t*>(prow + j * 32 + 16 + quad * 4);
                 }
-                const int pb = (e4 >> (8 * j)) & 0xff;
-                if (pb == 0xff) okk = false;                // the packer could not take this block
-                ku[j] = pb == 0xff ? 0.0f : v4_unit(pb);
-                if (pb >= 4 && pb != 0xff) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
             }
+            if (e == 0xffu) okk = false;                    // the packer could not take this row
+            else if (e != 0u) ku = __int_as_float(((int)e - 3) << 23);
         } else {
+            uint2 lo[4], hi[4];
+            int k_lo = 1000, k_hi = -1000;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                uint2 lo = make_uint2(0, 0), hi = make_uint2(0, 0);
+                lo[j] = hi[j] = make_uint2(0, 0);
                 if (c < n_comp) {
-                    lo = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + quad * 4);
-                    hi = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + 16 + quad * 4);
+                    lo[j] = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + quad * 4);
+                    hi[j] = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + 16 + quad * 4);
                 }
-                int pb = max(v4_max_exp4(lo.x, lo.y), v4_max_exp4(hi.x, hi.y));
+                // the block's largest exponent over the quad that holds the row, then the row's extremes
+                int pb = max(v4_max_exp4(lo[j].x, lo[j].y), v4_max_exp4(hi[j].x, hi[j].y));
                 pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 1));
                 pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 2));
-                const float inv = v4_unit_inv(pb, okk);
-                b0[j] = v4_pack4(lo.x, lo.y, inv, okk);
-                b1[j] = v4_pack4(hi.x, hi.y, inv, okk);
-                ku[j] = v4_unit(pb);
-                if (pb >= 4) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
+                if (pb > 0) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
+            }
+            float inv;
+            v4_row_unit(k_lo, k_hi, inv, ku, okk);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                b0[j] = v4_pack4(lo[j].x, lo[j].y, inv, okk);
+                b1[j] = v4_pack4(hi[j].x, hi[j].y, inv, okk);
             }
         }
-        // Every (head, this row) pair: block exponents E_j = eq_j + ek_j - 260 span at most span_q + span_k, and lie
-        // inside [q_lo + k_lo, q_hi + k_hi] - 260. Inside the limits the ordered f32 fold is exact.
-        if (k_hi >= k_lo && q_hi >= q_lo &&
-            (q_span + (k_hi - k_lo) > SI_SPAN || q_lo + k_lo - 260 < -120 || q_hi + k_hi - 260 > 100))
-            okk = false;
         // a row's verdict sits in the four lanes of its quad; lane j < 8 writes column j
         const uint32_t bad_rows = __ballot_sync(0xffffffffu, !okk);
         // units of the two columns this thread's accumulators belong to
-        float kuA[4], kuB[4];
+        const float kuA = __shfl_sync(0xffffffffu, ku, (quad * 2) * 4), kuB = __shfl_sync(0xffffffffu, ku, (quad * 2 + 1) * 4);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            kuA[j] = __shfl_sync(0xffffffffu, ku[j], (quad * 2) * 4);
-            kuB[j] = __shfl_sync(0xffffffffu, ku[j], (quad * 2 + 1) * 4);
-        }
-#pragma unroll 1
         for (int mt = 0; mt < 4; ++mt) {
-            int acc[4][4];
+            int acc[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint4 a = *reinterpret_cast<const uint4*>(&qfrag[((mt * 4 + j) * 32 + lane) * 4]);
-                v4_mma_s8(acc[j], a, b0[j], b1[j]);
+                v4_mma_s8(acc, a, b0[j], b1[j]);
             }
 #pragma unroll
             for (int rh = 0; rh < 2; ++rh) {                   // row half of the accumulator
                 const int hh = 16 * mt + grp + 8 * rh;
-                const float4 qu = *reinterpret_cast<const float4*>(qunit[hh]);
-                const float wv = wsh[hh];
-                float dA = 0.0f, dB = 0.0f;
-                dA = fmaf((float)acc[0][2 * rh], qu.x * kuA[0], dA); dB = fmaf((float)acc[0][2 * rh + 1], qu.x * kuB[0], dB);
-                dA = fmaf((float)acc[1][2 * rh], qu.y * kuA[1], dA); dB = fmaf((float)acc[1][2 * rh + 1], qu.y * kuB[1], dB);
-                dA = fmaf((float)acc[2][2 * rh], qu.z * kuA[2], dA); dB = fmaf((float)acc[2][2 * rh + 1], qu.z * kuB[2], dB);
-                dA = fmaf((float)acc[3][2 * rh], qu.w * kuA[3], dA); dB = fmaf((float)acc[3][2 * rh + 1], qu.w * kuB[3], dB);
+                const float qu = qunit[hh], wv = wsh[hh];
+                const float dA = (float)acc[2 * rh] * (qu * kuA), dB = (float)acc[2 * rh + 1] * (qu * kuB);
                 // bf16 store, relu, times the (signed) head weight, bf16 store
                 const float tA = v4_rbf16_hw(__fmul_rn(fmaxf(v4_rbf16_hw(dA), 0.0f), wv));
                 const float tB = v4_rbf16_hw(__fmul_rn(fmaxf(v4_rbf16_hw(dB), 0.0f), wv));
@@ -377,42 +368,51 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
     if (!ok) atomicOr(&flags[b], 1);
 }
 
-// One thread per (row, block of 32): the block's values as int8 multiples of 2^(pb - 130), pb = biased exponent of the
-// block's largest magnitude, stored in the row's exponent word (0 = empty block, 0xff = not of the integer form: the
-// scorer then hands the sequence to the ordered fold, which reads the bf16 rows).
+// One thread per (row, block of 32): the row's values as int8 multiples of its unit 2^(pmin - 130); the row's word
+// holds pmin (0 = the row is all zeros, 0xff = not of the integer form: the scorer then leaves the column to the
+// ordered fold, which reads the bf16 row).
 __global__ void v4_index_pack_kernel(V4Geom g, const int32_t* __restrict__ row_begin, const int32_t* __restrict__ row_end,
                                      const uint16_t* __restrict__ index_kv, uint8_t* __restrict__ packed,
                                      uint32_t* __restrict__ packed_exp) {
     const int b = blockIdx.y;
     const int r0 = row_begin ? row_begin[b] : 0, r1 = min(row_end[b], g.max_comp);
     const int id = blockIdx.x * blockDim.x + threadIdx.x, row = r0 + (id >> 2), j = id & 3;
-    uint32_t e = 0;
-    if (row < r1) {
-        const size_t off = ((size_t)b * g.max_comp + row) * 128 + j * 32;
+    const bool live = row < r1;
+    const size_t off = ((size_t)b * g.max_comp + (live ? row : 0)) * 128 + j * 32;
+    uint32_t wv[16];
+    int pb = 0;
+    if (live) {
         const uint4* src = reinterpret_cast<const uint4*>(index_kv + off);
-        uint32_t wv[16];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint4 v = src[i];
             wv[4 * i] = v.x; wv[4 * i + 1] = v.y; wv[4 * i + 2] = v.z; wv[4 * i + 3] = v.w;
         }
-        int pb = 0;
 #pragma unroll
         for (int i = 0; i < 16; i += 2) pb = max(pb, v4_max_exp4(wv[i], wv[i + 1]));
-        bool ok = pb < 0xff;
-        const float inv = v4_unit_inv(pb, ok);
-        uint32_t out[8];
+    } else {
 #pragma unroll
-        for (int k4 = 0; k4 < 8; ++k4) out[k4] = v4_pack4(wv[2 * k4], wv[2 * k4 + 1], inv, ok);
+        for (int i = 0; i < 16; ++i) wv[i] = 0;
+    }
+    // the four blocks of a row sit in four neighbouring threads
+    int lo = pb > 0 ? pb : 1000, hi = pb > 0 ? pb : -1000;
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, 1)); hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, 1));
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, 2)); hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, 2));
+    bool ok = true;
+    float inv, unit;
+    v4_row_unit(lo, hi, inv, unit, ok);
+    uint32_t out[8];
+#pragma unroll
+    for (int k4 = 0; k4 < 8; ++k4) out[k4] = v4_pack4(wv[2 * k4], wv[2 * k4 + 1], inv, ok);
+    uint32_t bad = ok ? 0u : 1u;
+    bad |= __shfl_xor_sync(0xffffffffu, bad, 1);
+    bad |= __shfl_xor_sync(0xffffffffu, bad, 2);
+    if (live) {
         uint4* dst = reinterpret_cast<uint4*>(packed + off);
         dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
         dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
-        e = (uint32_t)(ok ? pb : 0xff) << (8 * j);
+        if (j == 0) packed_exp[(size_t)b * g.max_comp + row] = bad ? 0xffu : (hi >= lo ? (uint32_t)lo : 0u);
     }
-    // the four blocks of a row sit in four neighbouring threads
-    e |= __shfl_xor_sync(0xffffffffu, e, 1);
-    e |= __shfl_xor_sync(0xffffffffu, e, 2);
-    if (row < r1 && j == 0) packed_exp[(size_t)b * g.max_comp + row] = e;
 }
 
 // ---------------------------------------------------------------------------------------------------
