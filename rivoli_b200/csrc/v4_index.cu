@@ -189,6 +189,7 @@ __global__ void v4_score_blocks_serial_kernel(const float* __restrict__ q, const
 constexpr int SI_THREADS = 256;
 constexpr int SI_CHUNK = 256;       // blocks (columns) per CTA
 constexpr int SI_SPAN = 3;          // binades between the block scales of one row
+constexpr int SI_NT = 2;            // column tiles of 8 a warp scores per iteration
 constexpr int SI_PMIN = 87, SI_PMAX = 167;     // biased exponents 2^-40 .. 2^40
 constexpr uint32_t SI_REFOLD = 0xffc0deadu;   // score word of a column left to the ordered fold (a NaN no fold produces)
 
@@ -244,7 +245,8 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
     __shared__ __align__(16) uint32_t qfrag[4 * 4 * 32 * 4];   // [m-tile][block][lane][4 regs]: A fragments, 8 KB
     __shared__ float qunit[64];                                // per head: its row unit (0 = empty row)
     __shared__ float wsh[64];
-    __shared__ __align__(16) float terms[SI_THREADS / 32][64][8];   // written as float2: needs the alignment
+    // written as float2 (needs the alignment); rows padded by two words so the eight heads of a store spread over banks
+    __shared__ __align__(16) float terms[SI_THREADS / 32][64][8 * SI_NT + 2];
     const int b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_comp = min((pos[b] + 1) / g.ratio, g.max_comp);
     const int c_begin = blockIdx.x * SI_CHUNK;
@@ -289,78 +291,99 @@ __global__ void __launch_bounds__(SI_THREADS) v4_score_int8_kernel(V4Geom g, con
     const uint16_t* kv = index_kv + (size_t)b * g.max_comp * 128;
     const int grp = lane >> 2, quad = lane & 3;
     const int c_end = min(n_comp, c_begin + SI_CHUNK);
-    for (int c0 = c_begin + warp * 8; c0 < c_end; c0 += (SI_THREADS / 32) * 8) {
-        // ---- B fragments: row c0 + grp, this thread's 8 values of each block
-        const int c = c0 + grp;
-        uint32_t b0[4], b1[4];
-        float ku = 0.0f;
-        bool okk = true;                                    // this row (column of the score matrix)
-        if (PACKED) {
-            const uint8_t* prow = packed + ((size_t)b * g.max_comp + c) * 128;
-            const uint32_t e = c < n_comp ? packed_exp[(size_t)b * g.max_comp + c] : 0u;
+    // units and weights of the eight heads this thread's accumulators belong to
+    float qu[8], qw[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                b0[j] = b1[j] = 0u;
-                if (c < n_comp) {
-                    b0[j] = *reinterpret_cast<const uint32_t*>(prow + j * 32 + quad * 4);
-                    b1[j] = *reinterpret_cast<const uint32_t*>(prow + j * 32 + 16 + quad * 4);
+    for (int i = 0; i < 8; ++i) {
+        const int hh = 16 * (i >> 1) + grp + 8 * (i & 1);
+        qu[i] = qunit[hh];
+        qw[i] = wsh[hh];
+    }
+    // SI_NT column tiles of 8 per iteration: every A fragment read from shared memory serves SI_NT MMAs
+    for (int c0 = c_begin + warp * (8 * SI_NT); c0 < c_end; c0 += (SI_THREADS / 32) * (8 * SI_NT)) {
+        uint32_t b0[SI_NT][4], b1[SI_NT][4];
+        float kuA[SI_NT], kuB[SI_NT];
+        uint32_t bad_rows[SI_NT];
+#pragma unroll
+        for (int t = 0; t < SI_NT; ++t) {
+            // ---- B fragments: row c0 + 8 t + grp, this thread's 8 values of each block
+            const int c = c0 + 8 * t + grp;
+            float ku = 0.0f;
+            bool okk = true;                                    // this row (column of the score matrix)
+            if (PACKED) {
+                const uint8_t* prow = packed + ((size_t)b * g.max_comp + c) * 128;
+                const uint32_t e = c < n_comp ? packed_exp[(size_t)b * g.max_comp + c] : 0u;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    b0[t][j] = b1[t][j] = 0u;
+                    if (c < n_comp) {
+                        b0[t][j] = *reinterpret_cast<const uint32_t*>(prow + j * 32 + quad * 4);
+                        b1[t][j] = *reinterpret_cast<const uint32_t*>(prow + j * 32 + 16 + quad * 4);
+                    }
+                }
+                if (e == 0xffu) okk = false;                    // the packer could not take this row
+                else if (e != 0u) ku = __int_as_float(((int)e - 3) << 23);
+            } else {
+                uint2 lo[4], hi[4];
+                int k_lo = 1000, k_hi = -1000;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    lo[j] = hi[j] = make_uint2(0, 0);
+                    if (c < n_comp) {
+                        lo[j] = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + quad * 4);
+                        hi[j] = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + 16 + quad * 4);
+                    }
+                    // the block's largest exponent over the quad that holds the row, then the row's extremes
+                    int pb = max(v4_max_exp4(lo[j].x, lo[j].y), v4_max_exp4(hi[j].x, hi[j].y));
+                    pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 1));
+                    pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 2));
+                    if (pb > 0) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
+                }
+                float inv;
+                v4_row_unit(k_lo, k_hi, inv, ku, okk);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    b0[t][j] = v4_pack4(lo[j].x, lo[j].y, inv, okk);
+                    b1[t][j] = v4_pack4(hi[j].x, hi[j].y, inv, okk);
                 }
             }
-            if (e == 0xffu) okk = false;                    // the packer could not take this row
-            else if (e != 0u) ku = __int_as_float(((int)e - 3) << 23);
-        } else {
-            uint2 lo[4], hi[4];
-            int k_lo = 1000, k_hi = -1000;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                lo[j] = hi[j] = make_uint2(0, 0);
-                if (c < n_comp) {
-                    lo[j] = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + quad * 4);
-                    hi[j] = *reinterpret_cast<const uint2*>(kv + (size_t)c * 128 + j * 32 + 16 + quad * 4);
-                }
-                // the block's largest exponent over the quad that holds the row, then the row's extremes
-                int pb = max(v4_max_exp4(lo[j].x, lo[j].y), v4_max_exp4(hi[j].x, hi[j].y));
-                pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 1));
-                pb = max(pb, __shfl_xor_sync(0xffffffffu, pb, 2));
-                if (pb > 0) { k_lo = min(k_lo, pb); k_hi = max(k_hi, pb); }
-            }
-            float inv;
-            v4_row_unit(k_lo, k_hi, inv, ku, okk);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                b0[j] = v4_pack4(lo[j].x, lo[j].y, inv, okk);
-                b1[j] = v4_pack4(hi[j].x, hi[j].y, inv, okk);
-            }
+            // a row's verdict sits in the four lanes of its quad
+            bad_rows[t] = __ballot_sync(0xffffffffu, !okk);
+            // units of the two columns this thread's accumulators belong to
+            kuA[t] = __shfl_sync(0xffffffffu, ku, (quad * 2) * 4);
+            kuB[t] = __shfl_sync(0xffffffffu, ku, (quad * 2 + 1) * 4);
         }
-        // a row's verdict sits in the four lanes of its quad; lane j < 8 writes column j
-        const uint32_t bad_rows = __ballot_sync(0xffffffffu, !okk);
-        // units of the two columns this thread's accumulators belong to
-        const float kuA = __shfl_sync(0xffffffffu, ku, (quad * 2) * 4), kuB = __shfl_sync(0xffffffffu, ku, (quad * 2 + 1) * 4);
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt) {
-            int acc[4] = {0, 0, 0, 0};
+            int acc[SI_NT][4];
+#pragma unroll
+            for (int t = 0; t < SI_NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint4 a = *reinterpret_cast<const uint4*>(&qfrag[((mt * 4 + j) * 32 + lane) * 4]);
-                v4_mma_s8(acc, a, b0[j], b1[j]);
+#pragma unroll
+                for (int t = 0; t < SI_NT; ++t) v4_mma_s8(acc[t], a, b0[t][j], b1[t][j]);
             }
 #pragma unroll
             for (int rh = 0; rh < 2; ++rh) {                   // row half of the accumulator
                 const int hh = 16 * mt + grp + 8 * rh;
-                const float qu = qunit[hh], wv = wsh[hh];
-                const float dA = (float)acc[2 * rh] * (qu * kuA), dB = (float)acc[2 * rh + 1] * (qu * kuB);
-                // bf16 store, relu, times the (signed) head weight, bf16 store
-                const float tA = v4_rbf16_hw(__fmul_rn(fmaxf(v4_rbf16_hw(dA), 0.0f), wv));
-                const float tB = v4_rbf16_hw(__fmul_rn(fmaxf(v4_rbf16_hw(dB), 0.0f), wv));
-                *reinterpret_cast<float2*>(&terms[warp][hh][quad * 2]) = make_float2(tA, tB);
+                const float u = qu[2 * mt + rh], wv = qw[2 * mt + rh];
+#pragma unroll
+                for (int t = 0; t < SI_NT; ++t) {
+                    const float dA = (float)acc[t][2 * rh] * (u * kuA[t]), dB = (float)acc[t][2 * rh + 1] * (u * kuB[t]);
+                    // bf16 store, relu, times the (signed) head weight, bf16 store
+                    const float tA = v4_rbf16_hw(__fmul_rn(fmaxf(v4_rbf16_hw(dA), 0.0f), wv));
+                    const float tB = v4_rbf16_hw(__fmul_rn(fmaxf(v4_rbf16_hw(dB), 0.0f), wv));
+                    *reinterpret_cast<float2*>(&terms[warp][hh][8 * t + quad * 2]) = make_float2(tA, tB);
+                }
             }
         }
         __syncwarp();
-        if (lane < 8 && c0 + lane < c_end) {
+        if (lane < 8 * SI_NT && c0 + lane < c_end) {           // lane j carries column j's ordered head sum
             float acc = 0.0f;
 #pragma unroll 8
             for (int hh = 0; hh < heads; ++hh) acc = __fadd_rn(acc, terms[warp][hh][lane]);
-            const bool refold = ((bad_rows >> (4 * lane)) & 0xfu) != 0;
+            const bool refold = ((bad_rows[lane >> 3] >> (4 * (lane & 7))) & 0xfu) != 0;
             scores[(size_t)b * g.max_comp + c0 + lane] = refold ? __uint_as_float(SI_REFOLD) : v4_rbf16_hw(acc);
         }
         __syncwarp();
