@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the decode-time MLA + DSA KV-cache path (one layer-step per "step").
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1|cfg5|v4]
 
 A layer-step = append one token per sequence -> indexer q quant + score + exact top-k ->
 gather/dequant + MLA attention -> bf16 out, over the whole per-GPU batch. Default workload
@@ -10,7 +10,9 @@ scattered over a pool 1.25x the live set). With N > 1 every rank runs the same p
 batch on its own sequences (weak scaling, no collective on the data path); the value is the
 aggregate over ranks, timed on the device and reduced with MAX over ranks.
 
-Prints ONE JSON line on rank 0.
+Prints ONE JSON line on rank 0. `--workload cfg5` (continuous batching with churn) and `--workload v4` (the V4
+cousin path: block scorer + selection rows + sparse MQA attention with sink) are one-GPU measurements of the CUDA
+arm that print the same kind of line; they are not the headline metric.
 """
 from __future__ import annotations
 
