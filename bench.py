@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the decode-time MLA + DSA KV-cache path (one layer-step per "step").
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1|cfg5|v4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1|cfg4|cfg5|v4]
 
 A layer-step = append one token per sequence -> indexer q quant + score + exact top-k ->
 gather/dequant + MLA attention -> bf16 out, over the whole per-GPU batch. Default workload
@@ -38,6 +38,9 @@ WORKLOADS = {
     # bound leaves a sequence 128 tokens to grow inside the 32,768-token limit of the tensor-core selection
     "cfg5": dict(B=32, ctx_lo=512, ctx_hi=32640, layers=78, n_heads=64, index_heads=32, index_dim=128, page_tokens=64,
                  top_k=2048, seed=4),
+    # long context, page-range sharded: every rank holds 1/N of every sequence's pages; candidates and partial
+    # attention outputs are exchanged (NCCL all-gather) and merged; needs --gpus >= 2 under torchrun
+    "cfg4": dict(B=4, ctx=131072, n_heads=64, index_heads=32, index_dim=128, page_tokens=64, top_k=2048, seed=3),
     # the V4 cousin path (a next-row measurement, not the headline): MQA over one shared 512-wide bf16 entry per
     # position, 128-slot ring + 512 scored compressed blocks of a ratio-4 compressor, 64-head block indexer
     "v4": dict(B=128, ctx=8192, n_heads=64, head_dim=512, window=128, index_heads=64, index_dim=128, index_topk=512,
@@ -652,6 +655,96 @@ def run_v4(args):
     print(json.dumps(line), flush=True)
 
 
+def run_cfg4(args):
+    """Long-context decode, page-range sharded over the ranks (strong scaling: batch 4 x context 131,072 in total).
+    A step = append the new token on the rank that owns the last page range, local exact scores and local top-k
+    candidates, one all-gather of (score) candidates that fixes the exact global cut, local partial attention, one
+    all-gather of (out, lse) partials and the merge. Timed on the device, MAX over ranks; rank 0 prints one line."""
+    import torch
+    import torch.distributed as dist
+    from rivoli_b200 import shard
+    w = dict(WORKLOADS["cfg4"])
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    assert world >= 2 and world == args.gpus, "cfg4 is the page-range sharded case: launch it under torchrun with --gpus >= 2"
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=device)
+    B, k = w["B"], w["top_k"]
+    ctx_local = w["ctx"] // world
+    g, layer, _ = build_layer(dict(w, ctx=ctx_local), device, w["seed"] * 100 + rank)   # ctx_local - 1 history tokens
+    gen = torch.Generator(device=device)
+    gen.manual_seed(w["seed"])                                                            # the step's inputs: same on every rank
+    x = step_inputs(w, device, gen)
+    last = rank == world - 1
+    local_len = torch.full((B,), ctx_local if last else ctx_local - 1, dtype=torch.int32, device=device)
+    offset = torch.full((B,), rank * (ctx_local - 1), dtype=torch.int32, device=device)
+    new_pos = torch.full((B,), ctx_local - 1, dtype=torch.int32, device=device)
+    ops = shard.gpu_shard_ops(layer)
+
+    def step():
+        if last:
+            layer.append(x["latent"], x["index_key"], new_pos)
+        return shard.page_range_step(ops, x["index_q"], x["index_w"], x["q"], local_len, offset, k)
+
+    out, rows_g, n_mine = step()
+    torch.cuda.synchronize(device)
+    layer.check_status()
+    # properties that need no oracle: the selected rows over all ranks number exactly k per sequence, each rank's are
+    # ascending and inside its own range, and every rank holds the same merged output
+    n_all = n_mine.clone()
+    dist.all_reduce(n_all)
+    assert (n_all == k).all().item(), n_all.tolist()
+    rg = rows_g.cpu().numpy()
+    for b in range(B):
+        r = rg[b, : int(n_mine[b])]
+        assert np.all(np.diff(r) > 0) and (r.size == 0 or (r[0] >= int(offset[b]) and r[-1] < int(offset[b]) + int(local_len[b])))
+    chk = out.view(torch.int16).to(torch.int64).sum().reshape(1)
+    lo, hi = chk.clone(), chk.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    assert lo.item() == hi.item(), "ranks disagree on the merged output"
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    dist.barrier()
+    torch.cuda.synchronize(device)
+    if sampler:
+        sampler.start()
+        sampler.mark()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize(device)
+    clocks = None
+    if sampler:
+        sampler.mark()
+        clocks = sampler.stop()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = float(ms.item())
+        per_seq = algorithmic_bytes(dict(w, ctx=w["ctx"]))
+        total = (per_seq["append"] + per_seq["index"] + per_seq["attend"]) * B
+        line = {"metric": METRIC, "value": 1e3 / ms, "unit": "layer-steps/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate", "data": "synthetic",
+                "config": {"workload": f"cfg4: batch {B} x context {w['ctx']}, page-range sharded {world}-way "
+                                       f"({ctx_local} tokens of every sequence per GPU), top-k {k}, seed {w['seed']}",
+                           "collectives": "per step: all-gather of top-k candidate scores and counts, all-gather of "
+                                          "partial outputs and log-sum-exps (NCCL), then the merge kernel",
+                           "l2": "per-GPU index pool %.0f MB" % (B * ctx_local * (w["index_dim"] + 4) / 1e6)},
+                "gpu_launches": args.steps * (8 + (1 if world else 0)), "clocks": clocks,
+                "roofline": {"bound": "hbm", "achieved": total / (ms * 1e-3) / 1e9 / world, "unit": "GB/s per GPU",
+                             "note": "algorithmic bytes of the whole step / time / GPUs; latency bound at batch 4"}}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def run_gather_probe(args):
     """Gather roofline of the attention access pattern: 1 of every 8 tokens of 64-token pages
     scattered in a 1.25x pool, 16 tiles of 128 rows per CTA (the cfg3 attention shape)."""
@@ -798,6 +891,12 @@ def main():
         ap.error("--batch is a --profile option; the bench always runs the workload's own batch")
     if args.profile:
         return run_profile(args)
+    if args.workload == "cfg4":
+        if args.impl == "reference":
+            ap.error("cfg4 is a multi-GPU measurement of the CUDA arm")
+        if args.steps == 400:
+            args.steps = 100
+        return run_cfg4(args)
     if args.workload == "v4":
         if args.impl == "reference" or args.gpus != 1:
             ap.error("the V4 workload is a one-GPU next-row measurement of the CUDA arm (its CPU arm is in the same line)")
