@@ -44,7 +44,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if r.returncode:
         raise RuntimeError("nvcc failed building librivolikernels.so")
     with open(os.path.join(HERE, "ptxas_info.txt"), "w") as f:
-        f.write(r.stdout + r.stderr)
+        # registers / spills / shared memory per kernel; the per-kernel compile times would only make the file churn
+        f.write("".join(l for l in (r.stdout + r.stderr).splitlines(True) if "Compile time" not in l))
     return OUT
 
 
