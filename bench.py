@@ -745,42 +745,8 @@ def run_cfg4(args):
     dist.destroy_process_group()
 
 
-def run_gather_probe(args):
-    """Gather roofline of the attention access pattern: 1 of every 8 tokens of 64-token pages
-    scattered in a 1.25x pool, 16 tiles of 128 rows per CTA (the cfg3 attention shape)."""
-    import torch
-    from rivoli_b200 import backend as be
-    w = WORKLOADS["cfg3"]
-    device = torch.device("cuda", 0)
-    torch.cuda.set_device(0)
-    P, n_tiles, max_ctas = w["page_tokens"], w["top_k"] // 128, 296
-    n_rows = (w["B"] * w["ctx"] * 5 // 4 // P) * P
-    pool = torch.ones(n_rows * (KV_LORA + ROPE), dtype=torch.uint8, device=device)
-    scales = torch.zeros(n_rows, dtype=torch.float32, device=device)
-    gen = torch.Generator(device=device)
-    gen.manual_seed(w["seed"])
-    k = torch.arange(n_tiles * 128, device=device).unsqueeze(0)
-    tok = k * 8 + torch.randint(0, 8, (max_ctas, n_tiles * 128), generator=gen, device=device)
-    page = (torch.arange(max_ctas, device=device).unsqueeze(1) * 2654435761 + (tok // P) * 40503) % (n_rows // P)
-    rows = (page * P + tok % P).to(torch.int32).contiguous()
-    names = {0: "cp.async 16 B, coalesced by row", 1: "cp.async.bulk 576 B per row", 2: "TMA tile::gather4 (swizzled)",
-             3: "cp.async 16 B + L2 prefetch 3 ahead"}
-    bytes_per_cta = n_tiles * 128 * (KV_LORA + ROPE + 4)
-    for n_ctas in (128, 148):
-        for method in (0, 1, 2, 3):
-            for depth in (1, 2, 3):
-                ms = be.probe_gather(method, depth, n_ctas, n_tiles, pool, n_rows, scales, rows)
-                print(f"{names[method]:34s} CTAs {n_ctas:3d} tiles in flight {depth}: {ms * 1e3:7.1f} us "
-                      f"{n_ctas * bytes_per_cta / (ms * 1e-3) / 1e9:7.1f} GB/s", flush=True)
-    ms = be.probe_gather(0, 1, 296, n_tiles, pool, n_rows, scales, rows)
-    print(f"{names[0]:34s} CTAs 296 tiles in flight 1: {ms * 1e3:7.1f} us {296 * bytes_per_cta / (ms * 1e-3) / 1e9:7.1f} GB/s")
-    print("profile run ok: gather")
-
-
 def run_profile(args):
     import torch
-    if args.profile == "gather":
-        return run_gather_probe(args)
     if args.profile == "proj":
         torch.cuda.set_device(0)
         print(time_projections(WORKLOADS[args.workload], torch.device("cuda", 0), steps=3))
@@ -880,7 +846,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile", default=None, choices=["select", "attend", "step", "gather", "proj"],
+    ap.add_argument("--profile", default=None, choices=["select", "attend", "step", "proj"],
                     help="build the workload, run 3 iterations of one stage (or the whole step) and exit: "
                          "the command line the profiles/ summaries were captured with")
     ap.add_argument("--layers", type=int, default=0, help="cfg5 only: number of layers (default 78)")

@@ -66,7 +66,9 @@ int rivoli_index_topk(const float* scores, int nt, int k, unsigned int* rows);
  * clat[h] = sum_t softmax_t((qabs_h.L_t + qrope_h.R_t)*scale) * L_t over the fp8 latent cache
  * (per-128 block scales) and bf16 roped keys; rows NULL = dense over 0..nr, else the nr
  * listed tokens. partial = scratch of rivoli_mla_attend_scratch_floats() floats, or NULL
- * (single split). Guards: 1001 sizes; 1002 16*(kvl+rope)*4 > 65536; 1004 kvl>512 or kvl%128. */
+ * (single split). Guards: 1001 sizes; 1002 16*(kvl+rope)*4 > 65536 or rope > 128; 1004 kvl>512 or kvl%128.
+ * Any H is accepted: one CTA takes as many heads as fit its shared memory (all 64 at the model's width) and
+ * larger head counts are tiled over the grid (the reference tiles them in blocks of 16). */
 int rivoli_mla_attend(const float* qabs, const float* qrope, const unsigned char* Lc8,
                       const float* Lscale, const unsigned short* Rc, const unsigned int* rows, int H,
                       int nr, int kvl, int rope, int n_blocks, float scale, float* clat,
@@ -179,8 +181,22 @@ int rivoli_dsa_append_select_paged(const DsaGeom* g, const uint16_t* latent, con
                                    float* latent_scale, uint8_t* index_pool, float* index_scale, int32_t* status,
                                    const uint16_t* index_q, const float* w, const int32_t* seq_len, int B,
                                    int score_stride, uint32_t* rows, int32_t* n_sel, void* scratch, void* stream);
-/* Synchronises `stream` and returns 1008 if a bounded device-side wait of the last
- * rivoli_index_select_paged call gave up (results are then undefined), else 0. */
+/* A whole decode layer-step in one call: rivoli_dsa_append_select_paged followed by
+ * rivoli_mla_attend_paged_bf16 over the selected rows (row_stride = top_k), same results. Because q is an
+ * input of the call it is known to be complete before the call's first kernel starts, so the attention kernel
+ * converts it while the selection kernel is still running (the separate attention entry point cannot assume
+ * that and reads q only after the kernel before it has finished). Replaces the per-layer launch sequence of
+ * crates/engine/src/glm/attn.rs:119-222 (append, indexer, attend) for a batch. */
+int rivoli_dsa_decode_step_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,
+                                 const int32_t* row_pos, const int32_t* block_table, uint8_t* latent_pool,
+                                 float* latent_scale, uint8_t* index_pool, float* index_scale, int32_t* status,
+                                 const uint16_t* index_q, const float* w, const int32_t* seq_len, int B,
+                                 int score_stride, uint32_t* rows, int32_t* n_sel, void* select_scratch,
+                                 const uint16_t* q, uint16_t* out, float* out_m, float* out_lse,
+                                 void* attend_scratch, void* stream);
+/* Synchronises `stream` and reports on the last rivoli_index_select_paged call (tensor-core path): 1008 if a
+ * bounded device-side wait gave up, 1005 if a block-table entry inside a sequence's length pointed outside
+ * the pool (that page was not read; results are undefined in both cases), else 0. */
 int rivoli_index_select_status(const DsaGeom* g, int B, int score_stride, void* scratch, void* stream);
 /* Diagnostics: per-sequence count of tokens the last call re-scored exactly, to HOST memory
  * host_band[B]. Synchronises `stream`. */
@@ -196,7 +212,10 @@ size_t rivoli_mla_attend_paged_scratch_bytes(const DsaGeom* g, int B);
  * q bf16 [B][n_heads][kv_lora+rope_dim] (absorbed q then roped q); rows u32 [B][row_stride]
  * or NULL (dense: row j = token j); n_rows i32 [B]. out bf16 [B][n_heads][kv_lora].
  * out_m / out_lse f32 [B][n_heads] (may be NULL): max score and log-sum-exp, the partial a
- * page-range shard hands to rivoli_attend_merge_partials. scratch = the bytes above. */
+ * page-range shard hands to rivoli_attend_merge_partials. scratch = the bytes above.
+ * With the model geometry and scratch the call runs the tensor-core kernel for sequences of 128 attended
+ * rows and more and the f32 CUDA-core kernel for shorter ones (two launches, disjoint sequences), so the
+ * output meets 2e-2 relative / 1e-3 absolute elementwise at every row count. */
 int rivoli_mla_attend_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
                                  const float* latent_scale, const int32_t* block_table,
                                  const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
@@ -435,16 +454,14 @@ int rivoli_v4_compress_step_bf16(const CompGeom* p, int n_seqs, const int32_t* p
                                  int cache_row0, float* prequant, unsigned char* packed, uint32_t* packed_exp,
                                  void* stream);
 
-/* Diagnostic, not on any product path (bench.py --profile gather): average milliseconds of a
- * launch in which each of n_ctas CTAs copies n_tiles tiles of 128 latent rows (576 bytes each,
- * rows[cta][tile][128] = pool row numbers) from the pool into shared memory with `depth` (1..3)
- * tiles in flight. method 0 = cp.async 16 B coalesced by row, 1 = cp.async.bulk per row,
- * 2 = TMA tile::gather4 into the swizzled operand layout, 3 = method 0 with the rows three tiles
- * on prefetched into L2. Allocates no device memory;
- * synchronises the stream. No counterpart in the reference. */
-int rivoli_probe_gather(int method, int depth, int n_ctas, int n_tiles, const uint8_t* pool,
-                        unsigned long long n_pool_rows, const float* scales, const uint32_t* rows, float* ms_out,
-                        void* stream);
+/* ---- test hooks (exercised by the GPU tests; not for production callers) ----------------------------------
+ * Overrides for the tensor-core attention's NEXT launches, host side only, no counterpart in the reference.
+ * min_rows >= 0 replaces the 128-row threshold below which a sequence goes to the CUDA-core kernel (0 = every
+ * sequence on the tensor cores; -1 restores the default). withhold != 0: the next launch leaves out one barrier
+ * arrival, so its bounded waits run out: the launch still returns, rivoli_mla_attend_paged_status reports 1008
+ * and later launches are unaffected (this is how the give-up path of the waits is tested; nothing faults).
+ * max_polls > 0 sets the poll limit of the bounded waits (<= 0 restores the default). */
+void rivoli_attend_mma_test_hook(int min_rows, int withhold, int max_polls);
 
 /* Library build tag, e.g. "sm_100a". */
 const char* rivoli_kernels_arch(void);

@@ -130,6 +130,15 @@ def index_score(q, w, kcache, heads, nt, nh, nact, hd, wscale, dscale) -> np.nda
     return out
 
 
+def index_score_f32(q, w, keys, nt, nh, hd, wscale, dscale) -> np.ndarray:
+    """The scoring core on f32 keys ``[nt, hd]`` (``orc_index_score`` is this after widening its bf16 keys)."""
+    scores = np.zeros(nt, dtype=np.float32)
+    lib().orc_index_score_f32(_p(_c(q, np.float32)), _p(_c(w, np.float32)), _p(_c(keys, np.float32)), None,
+                              C.c_int(nt), C.c_int(nh), C.c_int(nh), C.c_int(hd), C.c_float(wscale), C.c_float(dscale),
+                              _p(scores))
+    return scores
+
+
 def index_topk(scores, k) -> np.ndarray:
     s = _c(scores, np.float32)
     rows = np.zeros(max(min(k, s.size), 1), dtype=np.uint32)
@@ -156,6 +165,31 @@ def mla_attend(qabs, qrope, lc8, lscale, rc, rows, H, nr, kvl, rope, n_blocks, s
     lib().orc_mla_attend(_p(_c(qabs, np.float32)), _p(_c(qrope, np.float32)), _p(_c(lc8, np.uint8)),
                          _p(_c(lscale, np.float32)), _p(_c(rc, np.uint16)), _p(rp), H, nr, kvl, rope,
                          n_blocks, C.c_float(scale), _p(out))
+    return out
+
+
+def mla_attend_f32(qabs, qrope, lat, rk, H, nr, kvl, rope, scale) -> np.ndarray:
+    """The attention core on rows already dequantised to f32 (``lat [nr, kvl]``, ``rk [nr, rope]``)."""
+    clat = np.zeros((H, kvl), dtype=np.float32)
+    lib().orc_mla_attend_f32(_p(_c(qabs, np.float32)), _p(_c(qrope, np.float32)), _p(_c(lat, np.float32)),
+                             _p(_c(rk, np.float32)), C.c_int(H), C.c_int(nr), C.c_int(kvl), C.c_int(rope),
+                             C.c_float(scale), _p(clat))
+    return clat
+
+
+def mla_absorb_f32(q, wf, H, qh, nope, vh, kvl, nrow=1) -> np.ndarray:
+    """``mla_absorb_fp8`` on weights already dequantised to f32 ``[H*(nope+vh), kvl]``."""
+    out = np.zeros((nrow, H * kvl), dtype=np.float32)
+    lib().orc_mla_absorb_f32(_p(_c(q, np.float32)), _p(_c(wf, np.float32)), C.c_int(H), C.c_int(qh), C.c_int(nope),
+                             C.c_int(vh), C.c_int(kvl), C.c_int(nrow), _p(out))
+    return out
+
+
+def mla_value_f32(clat, wf, H, nope, vh, kvl, nrow=1) -> np.ndarray:
+    """``mla_value_fp8`` on weights already dequantised to f32."""
+    out = np.zeros((nrow, H * vh), dtype=np.float32)
+    lib().orc_mla_value_f32(_p(_c(clat, np.float32)), _p(_c(wf, np.float32)), C.c_int(H), C.c_int(nope), C.c_int(vh),
+                            C.c_int(kvl), C.c_int(nrow), _p(out))
     return out
 
 

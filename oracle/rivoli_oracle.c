@@ -16,13 +16,21 @@
  *     fixture are pinned by literal values recorded in the reference's tests
  *     (crates/core/src/routing.rs:207-212,259-284,338-362;
  *      crates/engine/tests/fwd_kernel.rs:140-160).
- *   - index_score, mla_attend and the split combine have NO literal expected values in
- *     the reference: its tests compute the expectation at run time from an inline host
- *     function.  Those inline functions are restated here statement for statement, but
- *     for them parity is "unpinned" beyond that structural restatement.
+ *   - index_score, mla_attend and the kv_b contractions have no literal expected values in
+ *     the reference's kernel tests (they compute the expectation at run time from an inline
+ *     host function, restated here statement for statement). They are pinned instead by the
+ *     reference's vendored captures of a real model run (crates/oracles/tests/glm-anchor-{1,2}.bin,
+ *     converted to tests/golden/ with the model weights regenerated from the capture driver's
+ *     name-seeded rule): the f32 cores orc_mla_absorb_f32 -> orc_mla_attend_f32 over the selected
+ *     rows -> orc_mla_value_f32 reproduce the captured attention outputs to 2e-6, and
+ *     orc_layernorm + orc_index_score_f32 + orc_index_topk reproduce the captured selections
+ *     (tests/test_glm_anchor_golden.py); the fp8 / bf16 / paged entry points are those cores on
+ *     their own dequantisation, bit for bit (same test file).
+ *   - the split combine (orc_attend_combine, orc_attend_merge_partials) is pinned only through
+ *     the identity "merged splits == dense result" against the pinned dense core.
  *   - everything paged / batched / per-token-scaled is a layout the reference does not
  *     have; it applies the reference's element codec and scale rule at a different
- *     granularity and is pinned only by this file.
+ *     granularity. Its arithmetic is the pinned cores'; its layout is defined by this file.
  *
  * Compile with -ffp-contract=off: the reference's host code never fuses a multiply
  * into an add, and several results below are compared bit for bit.
@@ -154,10 +162,12 @@ ORC_API void orc_index_append(const float* k, uint16_t* kcache, int pos, int hd)
 
 /* scores[t] = fold over active heads of acc + w[h]*wscale*max(dot*dscale, 0), dot a left
  * fold from 0.0 over hd. crates/engine/tests/indexer_kernel.rs:237-249. `heads` NULL =
- * all nh heads in ascending order (DSA); otherwise the nact listed heads (MISA). */
-ORC_API void orc_index_score(const float* q, const float* w, const uint16_t* kcache,
-                             const uint32_t* heads, int nt, int nh, int nact, int hd,
-                             float wscale, float dscale, float* scores) {
+ * all nh heads in ascending order (DSA); otherwise the nact listed heads (MISA).
+ * This is the arithmetic core on keys already widened to f32 ([nt][hd]); the bf16 entry point
+ * below widens (exactly) and calls it, so a pin on this function pins that one too. */
+ORC_API void orc_index_score_f32(const float* q, const float* w, const float* keys,
+                                 const uint32_t* heads, int nt, int nh, int nact, int hd,
+                                 float wscale, float dscale, float* scores) {
     (void)nh;
     for (int t = 0; t < nt; ++t) {
         float acc = 0.0f;
@@ -165,7 +175,7 @@ ORC_API void orc_index_score(const float* q, const float* w, const uint16_t* kca
             int h = heads ? (int)heads[a] : a;
             float dot = 0.0f;
             for (int i = 0; i < hd; ++i) {
-                float p = q[(size_t)h * hd + i] * orc_bf16_to_f32(kcache[(size_t)t * hd + i]);
+                float p = q[(size_t)h * hd + i] * keys[(size_t)t * hd + i];
                 dot = dot + p;
             }
             float r = dot * dscale;
@@ -176,6 +186,15 @@ ORC_API void orc_index_score(const float* q, const float* w, const uint16_t* kca
         }
         scores[t] = acc;
     }
+}
+
+ORC_API void orc_index_score(const float* q, const float* w, const uint16_t* kcache,
+                             const uint32_t* heads, int nt, int nh, int nact, int hd,
+                             float wscale, float dscale, float* scores) {
+    float* keys = (float*)malloc((size_t)(nt > 0 ? nt : 1) * hd * sizeof(float));
+    for (size_t i = 0; i < (size_t)nt * hd; ++i) keys[i] = orc_bf16_to_f32(kcache[i]);
+    orc_index_score_f32(q, w, keys, heads, nt, nh, nact, hd, wscale, dscale, scores);
+    free(keys);
 }
 
 /* Host comparator of topk_into: value descending (partial_cmp, so -0.0 == +0.0; an
@@ -230,28 +249,19 @@ ORC_API void orc_softmax(float* v, int n) {
     if (sum > 0.0f) for (int i = 0; i < n; ++i) v[i] /= sum;
 }
 
-/* Dense two-pass attention in latent space over `nr` rows; rows NULL = token t is row t,
- * otherwise row j is cached token rows[j] (the reference has no test for that arm; the
- * gathered subset is attended in the order given, which index_topk makes ascending).
- * crates/engine/tests/kernel_attend.rs:201-226 with the dequantisation of :243-245. */
-ORC_API void orc_mla_attend(const float* qabs, const float* qrope, const uint8_t* lc8,
-                            const float* lscale, const uint16_t* rc, const uint32_t* rows,
-                            int H, int nr, int kvl, int rope, int n_blocks, float scale,
-                            float* clat) {
-    int blk = kvl / n_blocks;
-    float* lat = (float*)malloc((size_t)nr * kvl * sizeof(float));
-    float* rk = (float*)malloc((size_t)nr * rope * sizeof(float));
-    for (int j = 0; j < nr; ++j) {
-        size_t t = rows ? rows[j] : (size_t)j;
-        for (int i = 0; i < kvl; ++i)
-            lat[(size_t)j * kvl + i] = orc_e4m3_to_f32(lc8[t * kvl + i]) * lscale[t * n_blocks + i / blk];
-        for (int d = 0; d < rope; ++d) rk[(size_t)j * rope + d] = orc_bf16_to_f32(rc[t * rope + d]);
-    }
+/* The arithmetic core of the attention on rows already dequantised to f32: lat [nr][kvl] (values
+ * that are both key and value), rk [nr][rope] (roped keys). Per head: score = one left fold over
+ * the latent terms then the rope terms, * scale; softmax (max-shift, exp, divide); out = sum of
+ * p_t * lat_t in ascending t. crates/engine/tests/kernel_attend.rs:201-226. Every attention entry
+ * point of this file is this function applied to its own dequantisation, so a pin on it (the
+ * vendored goldens of a real model run, tests/test_glm_anchor_golden.py) pins them all. */
+ORC_API void orc_mla_attend_f32(const float* qabs, const float* qrope, const float* lat, const float* rk,
+                                int H, int nr, int kvl, int rope, float scale, float* clat) {
 #pragma omp parallel for schedule(static)
     for (int head = 0; head < H; ++head) {
         const float* qa = qabs + (size_t)head * kvl;
         const float* qr = qrope + (size_t)head * rope;
-        float* sc = (float*)malloc((size_t)nr * sizeof(float));
+        float* sc = (float*)malloc((size_t)(nr > 0 ? nr : 1) * sizeof(float));
         for (int j = 0; j < nr; ++j) {
             float s = 0.0f;
             for (int i = 0; i < kvl; ++i) { float p = qa[i] * lat[(size_t)j * kvl + i]; s = s + p; }
@@ -265,6 +275,26 @@ ORC_API void orc_mla_attend(const float* qabs, const float* qrope, const uint8_t
             for (int i = 0; i < kvl; ++i) { float p = sc[j] * lat[(size_t)j * kvl + i]; out[i] = out[i] + p; }
         free(sc);
     }
+}
+
+/* Dense two-pass attention in latent space over `nr` rows; rows NULL = token t is row t,
+ * otherwise row j is cached token rows[j] (the reference has no test for that arm; the
+ * gathered subset is attended in the order given, which index_topk makes ascending).
+ * crates/engine/tests/kernel_attend.rs:201-226 with the dequantisation of :243-245. */
+ORC_API void orc_mla_attend(const float* qabs, const float* qrope, const uint8_t* lc8,
+                            const float* lscale, const uint16_t* rc, const uint32_t* rows,
+                            int H, int nr, int kvl, int rope, int n_blocks, float scale,
+                            float* clat) {
+    int blk = kvl / n_blocks;
+    float* lat = (float*)malloc((size_t)(nr > 0 ? nr : 1) * kvl * sizeof(float));
+    float* rk = (float*)malloc((size_t)(nr > 0 ? nr : 1) * rope * sizeof(float));
+    for (int j = 0; j < nr; ++j) {
+        size_t t = rows ? rows[j] : (size_t)j;
+        for (int i = 0; i < kvl; ++i)
+            lat[(size_t)j * kvl + i] = orc_e4m3_to_f32(lc8[t * kvl + i]) * lscale[t * n_blocks + i / blk];
+        for (int d = 0; d < rope; ++d) rk[(size_t)j * rope + d] = orc_bf16_to_f32(rc[t * rope + d]);
+    }
+    orc_mla_attend_f32(qabs, qrope, lat, rk, H, nr, kvl, rope, scale, clat);
     free(lat); free(rk);
 }
 
@@ -597,27 +627,23 @@ static float kvb_at(const uint8_t* kvb, const float* scale, int rows, int kvl, i
     return orc_e4m3_to_f32(kvb[r * (size_t)kvl + c]) * scale[rb * sc_cols + c / block];
 }
 
-/* qabs[row][head][i] = sum_d q[row][head*qh + d] * kvb[head*(nope+vh) + d][i]; nrow rows of q are
- * H*qh apart, of qabs H*kvl apart (mla.hip:27-31). */
-ORC_API void orc_mla_absorb_fp8(const float* q, const uint8_t* kvb, const float* scale, int H, int qh, int nope,
-                                int vh, int kvl, int block, int nrow, float* qabs) {
-    const int rows = H * (nope + vh);
+/* The two contractions on weights already dequantised to f32, wf [H*(nope+vh)][kvl]: the arithmetic cores
+ * (left folds in d resp. i, as above); the fp8 entry points dequantise (code * block scale, one rounding,
+ * the value the fold multiplies anyway) and call them. */
+ORC_API void orc_mla_absorb_f32(const float* q, const float* wf, int H, int qh, int nope, int vh, int kvl, int nrow,
+                                float* qabs) {
 #pragma omp parallel for collapse(2) schedule(static)
     for (int r = 0; r < nrow; ++r)
         for (int head = 0; head < H; ++head)
             for (int i = 0; i < kvl; ++i) {
                 float acc = 0.0f;
                 for (int d = 0; d < nope; ++d)
-                    acc += q[(size_t)r * H * qh + (size_t)head * qh + d] *
-                           kvb_at(kvb, scale, rows, kvl, block, (size_t)head * (nope + vh) + d, i);
+                    acc += q[(size_t)r * H * qh + (size_t)head * qh + d] * wf[((size_t)head * (nope + vh) + d) * kvl + i];
                 qabs[(size_t)r * H * kvl + (size_t)head * kvl + i] = acc;
             }
 }
-
-/* ctx[row][head][j] = sum_i clat[row][head*kvl + i] * kvb[head*(nope+vh) + nope + j][i] (mla.hip:138-175). */
-ORC_API void orc_mla_value_fp8(const float* clat, const uint8_t* kvb, const float* scale, int H, int nope, int vh,
-                               int kvl, int block, int nrow, float* ctx) {
-    const int rows = H * (nope + vh);
+ORC_API void orc_mla_value_f32(const float* clat, const float* wf, int H, int nope, int vh, int kvl, int nrow,
+                               float* ctx) {
 #pragma omp parallel for collapse(2) schedule(static)
     for (int r = 0; r < nrow; ++r)
         for (int head = 0; head < H; ++head)
@@ -625,9 +651,32 @@ ORC_API void orc_mla_value_fp8(const float* clat, const uint8_t* kvb, const floa
                 float acc = 0.0f;
                 for (int i = 0; i < kvl; ++i)
                     acc += clat[(size_t)r * H * kvl + (size_t)head * kvl + i] *
-                           kvb_at(kvb, scale, rows, kvl, block, (size_t)head * (nope + vh) + nope + j, i);
+                           wf[((size_t)head * (nope + vh) + nope + j) * kvl + i];
                 ctx[(size_t)r * H * vh + (size_t)head * vh + j] = acc;
             }
+}
+static float* kvb_dequant(const uint8_t* kvb, const float* scale, int rows, int kvl, int block) {
+    float* wf = (float*)malloc((size_t)rows * kvl * sizeof(float));
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < kvl; ++c) wf[(size_t)r * kvl + c] = kvb_at(kvb, scale, rows, kvl, block, (size_t)r, c);
+    return wf;
+}
+
+/* qabs[row][head][i] = sum_d q[row][head*qh + d] * kvb[head*(nope+vh) + d][i]; nrow rows of q are
+ * H*qh apart, of qabs H*kvl apart (mla.hip:27-31). */
+ORC_API void orc_mla_absorb_fp8(const float* q, const uint8_t* kvb, const float* scale, int H, int qh, int nope,
+                                int vh, int kvl, int block, int nrow, float* qabs) {
+    float* wf = kvb_dequant(kvb, scale, H * (nope + vh), kvl, block);
+    orc_mla_absorb_f32(q, wf, H, qh, nope, vh, kvl, nrow, qabs);
+    free(wf);
+}
+
+/* ctx[row][head][j] = sum_i clat[row][head*kvl + i] * kvb[head*(nope+vh) + nope + j][i] (mla.hip:138-175). */
+ORC_API void orc_mla_value_fp8(const float* clat, const uint8_t* kvb, const float* scale, int H, int nope, int vh,
+                               int kvl, int block, int nrow, float* ctx) {
+    float* wf = kvb_dequant(kvb, scale, H * (nope + vh), kvl, block);
+    orc_mla_value_f32(clat, wf, H, nope, vh, kvl, nrow, ctx);
+    free(wf);
 }
 
 /* Batched bf16 form (no reference counterpart): q bf16 [B][H][qh] with qh >= nope + rope; the

@@ -221,8 +221,21 @@ def launch_dsa_append_select_paged(g: DsaGeom, latent, index_key, row_pos, block
         "dsa_append_select_paged")
 
 
+def launch_dsa_decode_step_paged(g: DsaGeom, latent, index_key, row_pos, block_table, latent_pool, latent_scale,
+                                 index_pool, index_scale, status, index_q, w, seq_len, B: int, score_stride: int,
+                                 rows, n_sel, select_scratch, q, out, out_m, out_lse, attend_scratch,
+                                 stream=None) -> None:
+    """One decode layer-step in one call: append, select, attend (``rivoli_dsa_decode_step_paged``)."""
+    ensure_status(lib().rivoli_dsa_decode_step_paged(
+        C.byref(g), _ptr(latent), _ptr(index_key), _ptr(row_pos), _ptr(block_table), _ptr(latent_pool),
+        _ptr(latent_scale), _ptr(index_pool), _ptr(index_scale), _ptr(status), _ptr(index_q), _ptr(w), _ptr(seq_len),
+        C.c_int(B), C.c_int(score_stride), _ptr(rows), _ptr(n_sel), _ptr(select_scratch), _ptr(q), _ptr(out),
+        _ptr(out_m), _ptr(out_lse), _ptr(attend_scratch), _stream(stream)), "dsa_decode_step_paged")
+
+
 def index_select_status(g: DsaGeom, B: int, score_stride: int, scratch, stream=None) -> None:
-    """Synchronises; raises BackendError(1008) if a bounded device-side wait gave up."""
+    """Synchronises; raises BackendError(1008) if a bounded device-side wait gave up, (1005) if a block-table
+    entry inside a sequence pointed outside the pool."""
     ensure_status(lib().rivoli_index_select_status(C.byref(g), C.c_int(B), C.c_int(score_stride), _ptr(scratch),
                                                    _stream(stream)), "index_select_status")
 
@@ -248,6 +261,11 @@ def attend_paged_status(g: DsaGeom, scratch, stream=None) -> None:
     """Synchronises; raises BackendError(1008) if the tensor-core attention gave up on a wait."""
     ensure_status(lib().rivoli_mla_attend_paged_status(C.byref(g), _ptr(scratch), _stream(stream)),
                   "mla_attend_paged_status")
+
+
+def attend_mma_test_hook(min_rows: int = -1, withhold: int = 0, max_polls: int = 0) -> None:
+    """Test hook of the tensor-core attention (see include/rivoli_kernels.h); not for production callers."""
+    lib().rivoli_attend_mma_test_hook(C.c_int(min_rows), C.c_int(withhold), C.c_int(max_polls))
 
 
 def attend_simt_scratch_bytes(g: DsaGeom, B: int) -> int:
@@ -502,16 +520,6 @@ def launch_v4_compress_step_bf16(p: CompGeom, n_seqs: int, pos, kv_proj, score_p
         C.byref(p), C.c_int(n_seqs), _ptr(pos), _ptr(kv_proj), _ptr(score_proj), _ptr(ape), _ptr(kv_state),
         _ptr(score_state), _ptr(norm), _ptr(freqs), C.c_int(int(rotate)), _ptr(cache), C.c_int(cache_rows),
         C.c_int(cache_row0), _ptr(prequant), _ptr(packed), _ptr(packed_exp), _stream(stream)), "v4_compress_step_bf16")
-
-
-def probe_gather(method: int, depth: int, n_ctas: int, n_tiles: int, pool, n_pool_rows: int, scales, rows,
-                 stream=None) -> float:
-    """Diagnostic gather roofline: milliseconds per launch (see include/rivoli_kernels.h)."""
-    ms = C.c_float(0.0)
-    ensure_status(lib().rivoli_probe_gather(C.c_int(method), C.c_int(depth), C.c_int(n_ctas), C.c_int(n_tiles),
-                                            _ptr(pool), C.c_ulonglong(n_pool_rows), _ptr(scales), _ptr(rows),
-                                            C.byref(ms), _stream(stream)), "probe_gather")
-    return float(ms.value)
 
 
 def kernels_arch() -> str:

@@ -43,9 +43,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
         sys.stderr.write(r.stdout + r.stderr)
     if r.returncode:
         raise RuntimeError("nvcc failed building librivolikernels.so")
-    with open(os.path.join(HERE, "ptxas_info.txt"), "w") as f:
-        # registers / spills / shared memory per kernel; the per-kernel compile times would only make the file churn
-        f.write("".join(l for l in (r.stdout + r.stderr).splitlines(True) if "Compile time" not in l))
+    # registers / spills / shared memory per kernel: a build log, kept out of the source tree proper
+    log_dir = os.path.join(HERE, "..", "gpurun_out")
+    os.makedirs(log_dir, exist_ok=True)
+    with open(os.path.join(log_dir, "ptxas_info.txt"), "w") as f:
+        f.write(r.stdout + r.stderr)
     return OUT
 
 

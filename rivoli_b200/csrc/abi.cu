@@ -17,7 +17,7 @@ extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q,
                                             const float* latent_scale, const int32_t* block_table,
                                             const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
                                             uint16_t* out, float* out_m, float* out_lse, void* scratch,
-                                            void* stream);
+                                            int q_early, void* stream);
 extern "C" int rivoli_attend_mma_status(void* scratch, void* stream);
 
 RIVOLI_API size_t rivoli_mla_attend_paged_scratch_bytes(const DsaGeom* g, int B) {
@@ -40,21 +40,51 @@ RIVOLI_API int rivoli_mla_attend_paged_status(const DsaGeom* g, void* scratch, v
     return rivoli_attend_mma_status(scratch, stream);
 }
 
+static int attend_paged_dispatch(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
+                                 const float* latent_scale, const int32_t* block_table, const uint32_t* rows,
+                                 int row_stride, const int32_t* n_rows, int B, uint16_t* out, float* out_m,
+                                 float* out_lse, void* scratch, int q_early, void* stream) {
+    if (int e = rv_check_geom(g)) return e;
+    if (B <= 0 || !q || !latent_pool || !latent_scale || !block_table || !n_rows || !out) return 1001;
+    if (rows && row_stride <= 0) return 1001;
+    // Tensor-core kernel for the model geometry (64 heads, 512 + 64 dims), given scratch (error word and
+    // split partials); inside that call, sequences of fewer than 128 rows go to the CUDA-core kernel.
+    // Every other geometry runs on the CUDA-core kernel.
+    if (scratch && rivoli_attend_mma_supported(g))
+        return rivoli_attend_mma_paged_bf16(g, q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
+                                            B, out, out_m, out_lse, scratch, q_early, stream);
+    return rivoli_attend_simt_paged_bf16(g, q, latent_pool, latent_scale, block_table, rows, row_stride,
+                                         n_rows, B, out, out_m, out_lse, scratch, stream);
+}
+
 RIVOLI_API int rivoli_mla_attend_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
                                             const float* latent_scale, const int32_t* block_table,
                                             const uint32_t* rows, int row_stride, const int32_t* n_rows,
                                             int B, uint16_t* out, float* out_m, float* out_lse,
                                             void* scratch, void* stream) {
-    if (int e = rv_check_geom(g)) return e;
-    if (B <= 0 || !q || !latent_pool || !latent_scale || !block_table || !n_rows || !out) return 1001;
-    if (rows && row_stride <= 0) return 1001;
-    // Tensor-core kernel for the model geometry (64 heads, 512 + 64 dims); it needs the scratch
-    // for its fp8 q terms. Everything else runs on the CUDA-core kernel.
-    if (scratch && rivoli_attend_mma_supported(g))
-        return rivoli_attend_mma_paged_bf16(g, q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
-                                            B, out, out_m, out_lse, scratch, stream);
-    return rivoli_attend_simt_paged_bf16(g, q, latent_pool, latent_scale, block_table, rows, row_stride,
-                                         n_rows, B, out, out_m, out_lse, scratch, stream);
+    // q may have been written by the kernel launched just before this call: the attention kernel reads it
+    // only after its dependency wait.
+    return attend_paged_dispatch(g, q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows, B, out, out_m,
+                                 out_lse, scratch, 0, stream);
+}
+
+// One decode layer-step in one call: append the step's token of every sequence, select the attended rows,
+// attend over them. q is an input of the CALL, so it is complete before the first kernel of the call starts
+// and the attention kernel may convert it while the selection kernel is still running.
+RIVOLI_API int rivoli_dsa_decode_step_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,
+                                            const int32_t* row_pos, const int32_t* block_table, uint8_t* latent_pool,
+                                            float* latent_scale, uint8_t* index_pool, float* index_scale,
+                                            int32_t* status, const uint16_t* index_q, const float* w,
+                                            const int32_t* seq_len, int B, int score_stride, uint32_t* rows,
+                                            int32_t* n_sel, void* select_scratch, const uint16_t* q, uint16_t* out,
+                                            float* out_m, float* out_lse, void* attend_scratch, void* stream) {
+    if (!q || !out || !rows || !n_sel || !g) return 1001;
+    if (int e = rivoli_dsa_append_select_paged(g, latent, index_key, row_pos, block_table, latent_pool, latent_scale,
+                                               index_pool, index_scale, status, index_q, w, seq_len, B, score_stride,
+                                               rows, n_sel, select_scratch, stream))
+        return e;
+    return attend_paged_dispatch(g, q, latent_pool, latent_scale, block_table, rows, g->top_k, n_sel, B, out, out_m,
+                                 out_lse, attend_scratch, 1, stream);
 }
 
 // out[v] = sum_g w_g * part_out[g][v] / sum_g w_g,  w_g = exp(lse_g - max_g lse), ascending g.

@@ -46,7 +46,9 @@ constexpr int AM_SOFTMAX_THREADS = 256;
 constexpr int AM_MAX_SPLITS = 16;
 // P'' = 2^(s2' - m_ref + AM_POFF) with m_ref lagging the true maximum by at most AM_LAG, so
 // P'' <= 2^(AM_POFF + AM_LAG) = 256 < 448 while typical weights (a few binades below the maximum)
-// land where BOTH e4m3 terms are normal numbers.
+// land where BOTH e4m3 terms are normal numbers. In the code s2 carries the offset (s2 = s2' + AM_POFF)
+// and the reference is kept WITHOUT it (m_ref = max s2'), so that the difference s2 - m_ref is the
+// exponent of P'' directly.
 constexpr float AM_POFF = 5.0f, AM_LAG = 3.0f;
 
 // shared memory map (bytes); every operand tile is 1024-byte aligned
@@ -72,13 +74,6 @@ struct AmBars {
 static_assert(sizeof(AmBars) <= 128, "barrier block");
 static_assert(SM_TOTAL <= 232448, "shared memory budget");
 
-// Optional per-tile timeline of CTA (0, 0) for tuning builds (-DRIVOLI_DEBUG_TIMES); compiled out otherwise.
-#ifdef RIVOLI_DEBUG_TIMES
-__device__ long long g_am_times[64 * 16];
-#define AM_STAMP(tile, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) g_am_times[(tile) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define AM_STAMP(tile, slot) do { } while (0)
-#endif
 
 struct AttendMmaArgs {
     const uint16_t* q;       // [B][64][576] bf16: absorbed query, latent part then rope part
@@ -88,6 +83,10 @@ struct AttendMmaArgs {
     int page_tokens, max_pages, n_pool_pages, n_splits;
     uint16_t* out; float* out_m; float* out_lse; float* partial;
     int* err;
+    int min_rows;      // sequences with 0 < n_rows < min_rows are served by the CUDA-core kernel of the same call
+    int q_early;       // 1: q was complete before the preceding kernel was launched, so it may be read before the grid-dependency wait
+    int max_polls;     // poll limit of every bounded wait
+    int withhold;      // self-test: gather group 0 never signals its first tile (the waits on it must run out cleanly)
 };
 
 __device__ __forceinline__ uint32_t sw64_chunk(uint32_t row, uint32_t chunk) { return row * 64u + ((chunk ^ ((row >> 1) & 3u)) << 4); }
@@ -119,7 +118,6 @@ attend_mma_kernel(AttendMmaArgs A) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = blockIdx.y;
-    if (tid == 0) AM_STAMP(0, 12);
     const int P = A.page_tokens;
 
     if (tid == 0) {
@@ -147,7 +145,10 @@ attend_mma_kernel(AttendMmaArgs A) {
     //   hi = e4m3(q / s), s = absmax / 448;  lo = e4m3((q / s - hi) * 16)   =>  q ~ s * (hi + lo / 16)
     // Warps 0-7 take 8 heads each; a head's 576 values are 72 chunks of 8 (lane, lane+32, lane+64).
     // The gather warps do not wait for this: the MMA warp does (q_full) before its first QK.
-    if (tid == 0) AM_STAMP(0, 13);
+    // Under a programmatic dependent launch the kernel before this one may still be running. Unless the
+    // caller vouches that q was complete before that kernel was even launched (q_early: the fused decode
+    // step), q may be that kernel's output and is read only after the dependency wait.
+    if (!A.q_early) rv_grid_dep_wait();
     if (warp < 8) {
         const uint16_t* qb = A.q + (size_t)b * AM_H * AM_W;
 #pragma unroll 1
@@ -214,17 +215,19 @@ attend_mma_kernel(AttendMmaArgs A) {
         }
         tc::fence_proxy_async();
         tc::mbar_arrive(&bars.q_full);
-        if (tid == 0) AM_STAMP(0, 14);
     }
 
-    // Everything above reads only this kernel's own inputs, so under a programmatic dependent launch it
-    // overlaps the tail of the selection kernel; the selected rows and their counts are read below.
+    // With q_early everything above read only inputs that predate the preceding kernel, so it overlapped
+    // that kernel's tail; the selected rows and their counts are read below.
     rv_grid_dep_wait();
     int nr = A.n_rows[b];
     {
         const long long cap = A.rows ? A.row_stride : (long long)A.max_pages * P;
         nr = (int)max(0LL, min((long long)nr, cap));
     }
+    // Short contexts belong to the CUDA-core kernel launched by the same call: this CTA touches no output.
+    const bool skip = nr > 0 && nr < A.min_rows;
+    if (skip) nr = 0;
     const int ntiles_all = (nr + AM_TILE - 1) / AM_TILE;
     const int tps = (ntiles_all + A.n_splits - 1) / A.n_splits;
     const int r_begin = split * tps * AM_TILE;
@@ -280,9 +283,8 @@ attend_mma_kernel(AttendMmaArgs A) {
         const uint4 z = make_uint4(0, 0, 0, 0);
         for (int j = grp; j < ntiles && ok; j += 2) {
             uint8_t* kbuf = smem + SM_K0 + grp * SM_KBUF;
-            ok = tc::mbar_wait(&bars.kv_empty[grp], ((j >> 1) & 1) ^ 1, abort_flag, 41);
+            ok = tc::mbar_wait_warp(&bars.kv_empty[grp], ((j >> 1) & 1) ^ 1, abort_flag, 41, A.max_polls);
             if (!ok) break;
-            if (wi == 0 && lane == 0) AM_STAMP(j, 0);
 #pragma unroll
             for (int u = 0; u < 2; ++u) {              // latent part: row pw + it, chunk = lane
                 const int pw = u * 64 + wi * 32;
@@ -296,7 +298,7 @@ attend_mma_kernel(AttendMmaArgs A) {
                 }                                              // 0 x (stale NaN code) would poison O
             }
             // the single rope buffer is free as soon as the rope MMAs of the previous tile are done
-            ok = tc::mbar_wait(&bars.rope_free, (j & 1) ^ 1, abort_flag, 42);
+            ok = tc::mbar_wait_warp(&bars.rope_free, (j & 1) ^ 1, abort_flag, 42, A.max_polls);
             if (!ok) break;
 #pragma unroll
             for (int u = 0; u < 2; ++u) {              // rope part: 8 rows per instruction, 4 chunks each
@@ -321,8 +323,7 @@ attend_mma_kernel(AttendMmaArgs A) {
             }
             tc::cp_async_wait<0>();
             tc::fence_proxy_async();
-            if (wi == 0 && lane == 0) AM_STAMP(j, 1);
-            tc::mbar_arrive(&bars.k_full[grp]);
+            if (!(A.withhold && j == 0)) tc::mbar_arrive(&bars.k_full[grp]);
         }
     } else if (warp == 8 && ntiles > 0) {
         // ------------------------------ MMA issuer ------------------------------------------------
@@ -333,7 +334,7 @@ attend_mma_kernel(AttendMmaArgs A) {
         // Two in-order instruction streams, QK(0..n-1) and PV(0..n-1), issued in READY order: whichever
         // has its operands first goes first (PV preferred: it is what frees a K buffer for the gather).
         int qk_next = 0, pv_next = 0, idle = 0;
-        ok = tc::mbar_wait(&bars.q_full, 0, abort_flag, 51);
+        ok = tc::mbar_wait_warp(&bars.q_full, 0, abort_flag, 51, A.max_polls);
         tc::tc_fence_after();
         while (ok && pv_next < ntiles) {
             int can_pv = 0, can_qk = 0;
@@ -348,7 +349,6 @@ attend_mma_kernel(AttendMmaArgs A) {
             if (can_qk) {   // S^T(i) = K(i) . Qcat^T
                 const int i = qk_next, kb = i & 1;
                 tc::tc_fence_after();
-                if (lane == 0) AM_STAMP(i, 2);
                 if (lane == 0) {
                     const uint32_t a_k = tc::smem_u32(smem + SM_K0 + kb * SM_KBUF);
                     const uint32_t d = TM_S0 + kb * 128;
@@ -370,7 +370,6 @@ attend_mma_kernel(AttendMmaArgs A) {
             } else if (can_pv) {   // O^T += V(j)^T . P'(j)^T
                 const int j = pv_next, kb = j & 1;
                 tc::tc_fence_after();
-                if (lane == 0) AM_STAMP(j, 6);
                 if (lane == 0) {
                     const uint32_t a_k = tc::smem_u32(smem + SM_K0 + kb * SM_KBUF);
 #pragma unroll
@@ -391,7 +390,7 @@ attend_mma_kernel(AttendMmaArgs A) {
                 __syncwarp();
                 ++pv_next; idle = 0;
             } else {
-                if (++idle > 64 * tc::kMaxPolls) { *abort_flag = 54; ok = false; }   // bounded: nothing became ready
+                if (++idle > 64 * A.max_polls) { *abort_flag = 54; ok = false; }   // bounded: nothing became ready
                 else if ((idle & 255) == 0 && *abort_flag) ok = false;
                 else __nanosleep(100);
             }
@@ -411,11 +410,10 @@ attend_mma_kernel(AttendMmaArgs A) {
         bool ok = ntiles > 0;
         for (int i = 0; i < ntiles && ok; ++i) {
             const int kb = i & 1;
-            ok = tc::mbar_wait(&bars.k_full[kb], (i >> 1) & 1, abort_flag, 61) &&
-                 tc::mbar_wait(&bars.s_full[kb], (i >> 1) & 1, abort_flag, 62);
+            ok = tc::mbar_wait_warp(&bars.k_full[kb], (i >> 1) & 1, abort_flag, 61, A.max_polls) &&
+                 tc::mbar_wait_warp(&bars.s_full[kb], (i >> 1) & 1, abort_flag, 62, A.max_polls);
             if (!ok) break;
             tc::tc_fence_after();
-            if (tid == 0) AM_STAMP(i, 3);
             const float stok = s_tok[kb * 128 + row];
             const bool valid = r_begin + i * AM_TILE + row < r_end && stok > 0.0f;
             // rows past the end are exact zeros in shared memory, so their raw scores are 0 and an
@@ -445,18 +443,16 @@ attend_mma_kernel(AttendMmaArgs A) {
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&bars.s_empty[kb]);
-            if (tid == 0) AM_STAMP(i, 8);
 
             // Fast path: no score of the tile exceeds its head's reference by more than AM_LAG, so the
             // references stand and nothing has to be exchanged. One barrier-with-OR decides for the CTA.
             uint32_t slow;
             {
-                const uint32_t mine_slow = dmax > AM_LAG ? 1u : 0u;   // NaN-free: dmax is -inf or finite
+                const uint32_t mine_slow = dmax > AM_LAG + AM_POFF ? 1u : 0u;   // NaN-free: dmax is -inf or finite (s2 carries AM_POFF, the reference does not)
                 asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\t"
                              "bar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
                              : "=r"(slow) : "r"(mine_slow), "n"(AM_SOFTMAX_THREADS) : "memory");
             }
-            if (tid == 0) AM_STAMP(i, 10);
             if (slow) {
                 // exact per-head tile max: warp reduce, then fold the 4 lane groups; move the references
                 {
@@ -471,7 +467,7 @@ attend_mma_kernel(AttendMmaArgs A) {
                 }
                 tc::named_barrier(2, AM_SOFTMAX_THREADS);
                 if (tid < AM_H) {
-                    const float tm = fmaxf(fmaxf(s_wmax[tid], s_wmax[64 + tid]), fmaxf(s_wmax[128 + tid], s_wmax[192 + tid]));
+                    const float tm = fmaxf(fmaxf(s_wmax[tid], s_wmax[64 + tid]), fmaxf(s_wmax[128 + tid], s_wmax[192 + tid])) - AM_POFF;
                     float fac = 1.0f;
                     if (m_ref == -INFINITY) { if (tm > -INFINITY) m_ref = tm; }          // first live tile of this head
                     else if (tm > m_ref) { fac = exp2f(m_ref - tm); m_ref = tm; }          // any growth is taken now
@@ -480,7 +476,7 @@ attend_mma_kernel(AttendMmaArgs A) {
                 }
                 tc::named_barrier(2, AM_SOFTMAX_THREADS);
                 // bring O^T and l to the new references. PV(i-1) must have landed first.
-                if (i >= 1) { ok = tc::mbar_wait(&bars.pv_done, (i - 1) & 1, abort_flag, 63); if (!ok) break; }
+                if (i >= 1) { ok = tc::mbar_wait_warp(&bars.pv_done, (i - 1) & 1, abort_flag, 63, A.max_polls); if (!ok) break; }
                 tc::tc_fence_after();
                 if (i >= 1) {
                     uint32_t r[32];
@@ -498,7 +494,6 @@ attend_mma_kernel(AttendMmaArgs A) {
                 for (int h = 0; h < 32; ++h) l_part[h] *= s_fac[h0 + h];
                 tc::tc_fence_before();
             }
-            if (tid == 0) AM_STAMP(i, 11);
             // P'' = 2^(s2' - m) = weight * s_tok * 2^AM_POFF as two e4m3 terms (via f16: p <= 256 and the
             // residual p - hi are exact enough in half precision); l accumulates the plain weight
             uint32_t hi_w[8], lo_w[8];
@@ -527,8 +522,7 @@ attend_mma_kernel(AttendMmaArgs A) {
                 hi_w[h >> 2] = chs[0] | (chs[1] << 16);
                 lo_w[h >> 2] = cls[0] | (cls[1] << 16);
             }
-            if (tid == 0) AM_STAMP(i, 7);
-            ok = tc::mbar_wait(&bars.p_empty, (i & 1) ^ 1, abort_flag, 64);
+            ok = tc::mbar_wait_warp(&bars.p_empty, (i & 1) ^ 1, abort_flag, 64, A.max_polls);
             if (!ok) break;
             {
                 uint8_t* prow = smem + SM_P;
@@ -541,13 +535,11 @@ attend_mma_kernel(AttendMmaArgs A) {
                 }
             }
             tc::fence_proxy_async();
-            if (tid == 0) AM_STAMP(i, 5);
             tc::mbar_arrive(&bars.p_full);
         }
 
         // ---- epilogue ----
-        if (ok && ntiles > 0) ok = tc::mbar_wait(&bars.pv_done, (ntiles - 1) & 1, abort_flag, 65);
-        if (tid == 0) AM_STAMP(0, 15);
+        if (ok && ntiles > 0) ok = tc::mbar_wait_warp(&bars.pv_done, (ntiles - 1) & 1, abort_flag, 65, A.max_polls);
         tc::tc_fence_after();
         // l per head: butterfly over the 32 token lanes, then across the 4 lane groups through shared memory
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
@@ -561,12 +553,13 @@ attend_mma_kernel(AttendMmaArgs A) {
             s_wmax[q4 * 64 + h0 + lane] = mine;
         }
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
-        if (tid == 0) AM_STAMP(1, 13);
         if (tid < AM_H) {
             const int h = tid;
             const float l = s_wmax[h] + s_wmax[64 + h] + s_wmax[128 + h] + s_wmax[192 + h];
             const float m_nat = (m_ref - AM_POFF) * 0.6931471805599453f;   // natural-log units (l and O carry 2^AM_POFF)
-            if (A.n_splits > 1) {
+            if (skip) {
+                // nothing: the sequence's output and statistics are written by the CUDA-core kernel
+            } else if (A.n_splits > 1) {
                 float* ml = A.partial + (size_t)b * A.n_splits * AM_H * (AM_KVL + 2) +
                             (size_t)A.n_splits * AM_H * AM_KVL + ((size_t)split * AM_H + h) * 2;
                 ml[0] = (l > 0.0f && ok) ? m_nat : -INFINITY;
@@ -591,7 +584,7 @@ attend_mma_kernel(AttendMmaArgs A) {
         float* part = A.n_splits > 1 ? A.partial + (size_t)b * A.n_splits * AM_H * (AM_KVL + 2) +
                                            ((size_t)split * AM_H + h0) * AM_KVL : nullptr;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 4 && !skip; ++c) {
             const int dim = c * 128 + row;
             uint32_t r[32];
             if (ntiles > 0 && ok) {
@@ -601,7 +594,6 @@ attend_mma_kernel(AttendMmaArgs A) {
 #pragma unroll
                 for (int h = 0; h < 32; ++h) r[h] = 0u;
             }
-            if (tid == 0) AM_STAMP(2, 12 + c);
             if (part) {
 #pragma unroll
                 for (int hq = 0; hq < 32; ++hq) part[hq * AM_KVL + dim] = __uint_as_float(r[hq]);
@@ -611,10 +603,8 @@ attend_mma_kernel(AttendMmaArgs A) {
                 for (int hq = 0; hq < 32; ++hq) sp[hq * AM_KVL] = rv_f32_to_bf16(__uint_as_float(r[hq]) * inv_l[hq]);
             }
         }
-        if (tid == 0) AM_STAMP(3, 12);
-        if (A.n_splits == 1) {
+        if (A.n_splits == 1 && !skip) {
             tc::named_barrier(1, AM_SOFTMAX_THREADS);
-            if (tid == 0) AM_STAMP(3, 13);
             const uint4* sv = reinterpret_cast<const uint4*>(stage);
             uint4* gv = reinterpret_cast<uint4*>(A.out + (size_t)b * AM_H * AM_KVL);
 #pragma unroll 4
@@ -622,11 +612,9 @@ attend_mma_kernel(AttendMmaArgs A) {
         }
     }
 
-    if (tid == 0) AM_STAMP(1, 14);
     tc::tc_fence_before();
     __syncthreads();
     if (warp == 8) tc::tmem_dealloc<512>(tmem);
-    if (tid == 0) AM_STAMP(1, 12);
     if (tid == 0 && *abort_flag) atomicCAS(A.err, 0, *abort_flag);
 }
 
@@ -653,13 +641,40 @@ extern "C" size_t rivoli_attend_mma_scratch_bytes(const DsaGeom* g, int B) {
 }
 
 extern "C" void rivoli_attend_combine_paged(const float* partial, int H, int kvl, int n_splits, int B, uint16_t* out,
-                                            float* out_m, float* out_lse, cudaStream_t st);
+                                            float* out_m, float* out_lse, const int32_t* n_rows, long long cap,
+                                            int rows_lo, int rows_hi, int serve_empty, cudaStream_t st);
+extern "C" int rivoli_attend_simt_short_rows(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
+                                             const float* latent_scale, const int32_t* block_table,
+                                             const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
+                                             uint16_t* out, float* out_m, float* out_lse, int rows_hi,
+                                             cudaStream_t st);
 
+// Below this many attended rows a sequence is served by the f32 CUDA-core kernel instead: with one tile
+// or less the two-term fp8 operands of the tensor-core kernel (bf16-class, ~2^-9) no longer average out
+// against the 1e-3 absolute tolerance on near-zero outputs.
+constexpr int AM_MIN_ROWS = 128;
+
+// Self-test state (rivoli_attend_mma_test_hook): overrides of the next launches, host side only.
+static int g_am_min_rows_override = -1, g_am_withhold_once = 0, g_am_max_polls = tc::kMaxPolls;
+
+// Test hook, not for production callers. min_rows >= 0 replaces AM_MIN_ROWS until reset with -1 (0 sends every
+// sequence to the tensor-core kernel); withhold != 0 makes the NEXT launch leave out one barrier arrival so that
+// its bounded waits run out (the launch returns, the status call reports 1008 and later launches are unaffected);
+// max_polls > 0 sets the poll limit of the bounded waits (<= 0 restores the default).
+extern "C" __attribute__((visibility("default"))) void rivoli_attend_mma_test_hook(int min_rows, int withhold,
+                                                                                    int max_polls) {
+    g_am_min_rows_override = min_rows;
+    g_am_withhold_once = withhold;
+    g_am_max_polls = max_polls > 0 ? max_polls : tc::kMaxPolls;
+}
+
+// q_early != 0: the caller guarantees q was complete before the kernel preceding this call in the stream
+// was launched (the fused decode step), so the query conversion may overlap that kernel's tail.
 extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
                                             const float* latent_scale, const int32_t* block_table,
                                             const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
                                             uint16_t* out, float* out_m, float* out_lse, void* scratch,
-                                            void* stream) {
+                                            int q_early, void* stream) {
     if (!scratch) return 1001;
     if (((uintptr_t)latent_pool | (uintptr_t)scratch | (uintptr_t)q | (uintptr_t)out) & 15) return 1005;
     cudaStream_t st = (cudaStream_t)stream;
@@ -667,16 +682,27 @@ extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q,
     int* err = reinterpret_cast<int*>(sp);
     float* partial = reinterpret_cast<float*>(sp + 256);
     const int n_splits = mma_splits(B);
+    const int min_rows = g_am_min_rows_override >= 0 ? g_am_min_rows_override : AM_MIN_ROWS;
+    const int withhold = g_am_withhold_once;
+    g_am_withhold_once = 0;
 
+    // short contexts first (a programmatic dependent of whatever precedes this call; its CTAs leave at once
+    // for every other sequence), then the tensor-core kernel as a dependent of that launch
+    if (min_rows > 1)
+        if (int e = rivoli_attend_simt_short_rows(g, q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
+                                                  B, out, out_m, out_lse, min_rows, st))
+            return e;
     rv_drain_error();
     AttendMmaArgs a{q, g->softmax_scale, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
                     g->page_tokens, g->max_pages_per_seq, g->n_pool_pages, n_splits,
-                    out, out_m, out_lse, n_splits > 1 ? partial : nullptr, err};
+                    out, out_m, out_lse, n_splits > 1 ? partial : nullptr, err,
+                    min_rows, q_early ? 1 : 0, g_am_max_polls, withhold};
     cudaFuncSetAttribute(attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
     rv_launch_dependent(attend_mma_kernel, dim3(n_splits, B), dim3(AM_THREADS), (size_t)SM_TOTAL, st, a);
     if (int e = rv_launch_status()) return e;
     if (n_splits > 1) {
-        rivoli_attend_combine_paged(partial, AM_H, AM_KVL, n_splits, B, out, out_m, out_lse, st);
+        const long long cap = rows ? (long long)row_stride : (long long)g->max_pages_per_seq * g->page_tokens;
+        rivoli_attend_combine_paged(partial, AM_H, AM_KVL, n_splits, B, out, out_m, out_lse, n_rows, cap, min_rows, 0x7fffffff, 1, st);
         return rv_launch_status();
     }
     return 0;
@@ -692,8 +718,3 @@ extern "C" int rivoli_attend_mma_status(void* scratch, void* stream) {
     return h ? 1008 : 0;
 }
 
-#ifdef RIVOLI_DEBUG_TIMES
-extern "C" __attribute__((visibility("default"))) int rivoli_attend_mma_debug_times(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_am_times, sizeof(long long) * 64 * 16);
-}
-#endif

@@ -9,11 +9,12 @@
 //                                   f32 cross-check of the tensor-core kernel and the path
 //                                   used for geometries that kernel does not cover.
 //
-// One CTA of 32 warps attends ALL heads of one (sequence, split), so each cached row is
-// read from HBM once per split (the reference re-reads it ceil(H/16) times). q sits in
-// shared memory as f32 for the whole CTA; rows are dequantised 16 at a time into a shared
-// tile; warp w owns heads w, w+32, ... and its lanes own the columns i = lane (mod 32), so
-// the online accumulator is lane-private registers.
+// One CTA attends a GROUP of heads of one (sequence, split) - all of them whenever their q rows fit
+// shared memory, otherwise groups tiled over gridDim.z - so each cached row is read from HBM once per
+// (split, head group) (the reference re-reads it ceil(H/16) times). q sits in shared memory as f32
+// for the whole CTA; rows are dequantised 16 at a time into a shared tile; warp w owns heads
+// w, w + n_warps, ... of the group and its lanes own the columns i = lane (mod 32), so the online
+// accumulator is lane-private registers.
 #include "codec.cuh"
 #include "common.cuh"
 
@@ -30,16 +31,20 @@ struct AttPaged {
     const uint16_t* q; const uint8_t* pool; const float* pscale; const int32_t* block_table;
     const uint32_t* rows; long long row_stride; const int32_t* n_rows; int page_tokens; int max_pages;
     int n_pool_pages; uint16_t* out; float* out_m; float* out_lse;
+    int rows_lo, rows_hi;   // the launch serves sequences with rows_lo <= n_rows < rows_hi only (others are left untouched)
 };
 
 template <bool PAGED, int HPW>
 __global__ void __launch_bounds__(AT_THREADS, 1)
-attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int kvl, int rope, float scale, int nr_single,
+attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int hg, int kvl, int rope, float scale, int nr_single,
                    int n_splits, float* __restrict__ partial) {
     extern __shared__ __align__(16) float smem[];
     const int W = kvl + rope;
-    float* qs = smem;                      // [H][W]
-    float* tile = smem + (size_t)H * W;    // [AT_TT][W]
+    const int nthreads = blockDim.x, nwarps = nthreads >> 5;
+    const int head0 = blockIdx.z * hg;             // this CTA's head group: [head0, head0 + Hc)
+    const int Hc = min(hg, H - head0);
+    float* qs = smem;                      // [hg][W]
+    float* tile = smem + (size_t)hg * W;   // [AT_TT][W]
     __shared__ float tscale[AT_TT];
     __shared__ const uint8_t* trow[AT_TT];
 
@@ -47,21 +52,24 @@ attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int kvl, int rope, float scal
     const int split = blockIdx.x, b = blockIdx.y;
     int nr = nr_single;
     if (PAGED) {  // clamp device-side counts so a bad entry can never index past a table
+        rv_grid_dep_trigger();             // a dependent kernel may set itself up; it waits for this grid before reading
+        rv_grid_dep_wait();                // the counts (and rows) may come from the kernel before
         nr = pp.n_rows[b];
         const long long cap = pp.rows ? pp.row_stride : (long long)pp.max_pages * pp.page_tokens;
         nr = (int)max(0LL, min((long long)nr, cap));
+        if (nr < pp.rows_lo || nr >= pp.rows_hi) return;   // another kernel of the same call serves this sequence
     }
     const int nacc = kvl / 32;             // lane-owned latent columns (<= 16)
     const int nrp = (rope + 31) / 32;      // lane-owned rope columns (<= 4)
 
     // q -> shared f32
     if (PAGED) {
-        const uint16_t* q = pp.q + (size_t)b * H * W;
-        for (int i = tid; i < H * W; i += AT_THREADS) qs[i] = rv_bf16_to_f32(q[i]);
+        const uint16_t* q = pp.q + ((size_t)b * H + head0) * W;
+        for (int i = tid; i < Hc * W; i += nthreads) qs[i] = rv_bf16_to_f32(q[i]);
     } else {
-        for (int i = tid; i < H * W; i += AT_THREADS) {
+        for (int i = tid; i < Hc * W; i += nthreads) {
             const int h = i / W, c = i - h * W;
-            qs[i] = c < kvl ? sp.qabs[(size_t)h * kvl + c] : sp.qrope[(size_t)h * rope + (c - kvl)];
+            qs[i] = c < kvl ? sp.qabs[(size_t)(head0 + h) * kvl + c] : sp.qrope[(size_t)(head0 + h) * rope + (c - kvl)];
         }
     }
 
@@ -95,7 +103,7 @@ attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int kvl, int rope, float scal
             }
             __syncthreads();
             const int cpr = W / 16;  // 16-byte chunks per row
-            for (int c = tid; c < tcount * cpr; c += AT_THREADS) {
+            for (int c = tid; c < tcount * cpr; c += nthreads) {
                 const int row = c / cpr, ch = c - row * cpr;
                 const uint4 p = *reinterpret_cast<const uint4*>(trow[row] + ch * 16);
                 const float sc = tscale[row];
@@ -110,7 +118,7 @@ attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int kvl, int rope, float scal
                 }
             }
         } else {
-            for (int idx = tid; idx < tcount * W; idx += AT_THREADS) {
+            for (int idx = tid; idx < tcount * W; idx += nthreads) {
                 const int row = idx / W, c = idx - row * W;
                 const size_t t = sp.rows ? (size_t)sp.rows[t0 + row] : (size_t)(t0 + row);
                 tile[idx] = c < kvl
@@ -129,9 +137,9 @@ attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int kvl, int rope, float scal
             for (int k = 0; k < 4; ++k) rv[k] = (k < nrp && lane + 32 * k < rope) ? row[kvl + lane + 32 * k] : 0.0f;
 #pragma unroll
             for (int j = 0; j < HPW; ++j) {
-                const int head = warp + AT_WARPS * j;
-                if (head >= H) continue;                 // warp-uniform
-                const float* qh = qs + (size_t)head * W;
+                const int hl = warp + nwarps * j;        // head within the group
+                if (hl >= Hc) continue;                  // warp-uniform
+                const float* qh = qs + (size_t)hl * W;
                 float part = 0.0f;
 #pragma unroll
                 for (int k = 0; k < 16; ++k) if (k < nacc) part = fmaf(qh[lane + 32 * k], lv[k], part);
@@ -152,8 +160,8 @@ attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int kvl, int rope, float scal
 
 #pragma unroll
     for (int j = 0; j < HPW; ++j) {
-        const int head = warp + AT_WARPS * j;
-        if (head >= H) continue;
+        if (warp + nwarps * j >= Hc) continue;
+        const int head = head0 + warp + nwarps * j;
         if (n_splits > 1) {
             // unnormalised partial + (m, l); an empty split stores (-inf, 0, 0)
             float* base = partial + (size_t)b * n_splits * H * (kvl + 2);
@@ -185,10 +193,15 @@ attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int kvl, int rope, float scal
 template <bool PAGED>
 __global__ void __launch_bounds__(128)
 attend_combine_kernel(const float* __restrict__ partial, int H, int kvl, int n_splits, float* __restrict__ clat,
-                      uint16_t* __restrict__ out, float* __restrict__ out_m, float* __restrict__ out_lse) {
+                      uint16_t* __restrict__ out, float* __restrict__ out_m, float* __restrict__ out_lse,
+                      const int32_t* __restrict__ n_rows, long long cap, int rows_lo, int rows_hi, int serve_empty) {
     __shared__ float w[AT_MAX_SPLITS];
     __shared__ float inv_l;
     const int head = blockIdx.x, b = blockIdx.y;
+    if (PAGED && n_rows) {   // same clamp and range rule as the kernels that wrote the partials
+        const int nr = (int)max(0LL, min((long long)n_rows[b], cap));
+        if ((nr < rows_lo || nr >= rows_hi) && !(nr == 0 && serve_empty)) return;
+    }
     const float* base = partial + (size_t)b * n_splits * H * (kvl + 2);
     const float* ml = base + (size_t)n_splits * H * kvl;
     if (threadIdx.x == 0) {
@@ -215,20 +228,36 @@ attend_combine_kernel(const float* __restrict__ partial, int H, int kvl, int n_s
     }
 }
 
+// Launch plan: a CTA takes `hg` heads - all H when their q rows fit shared memory beside the row tile,
+// otherwise (or when `hg_req` asks for smaller groups) H is tiled over gridDim.z - with one warp per head up
+// to 32 warps, then 2 or 4 heads per warp. `dependent` launches the kernel as a programmatic dependent of the
+// kernel before it in the stream (paged form only: it waits for that kernel before reading the counts).
 template <bool PAGED>
 static int launch_attend_simt(const AttSlab& sp, const AttPaged& pp, int H, int kvl, int rope, float scale,
-                              int nr_single, int B, int n_splits, float* partial, cudaStream_t st) {
-    const size_t smem = ((size_t)H * (kvl + rope) + (size_t)AT_TT * (kvl + rope)) * sizeof(float);
-    if (smem > 227 * 1024 - 512) return 1006;
-    const int hpw = (H + AT_WARPS - 1) / AT_WARPS;
-    dim3 grid(n_splits, B);
+                              int nr_single, int B, int n_splits, float* partial, cudaStream_t st, int hg_req = 0,
+                              bool dependent = false) {
+    const int W = kvl + rope;
+    auto smem_of = [&](int h) { return ((size_t)h * W + (size_t)AT_TT * W) * sizeof(float); };
+    const size_t smem_max = 227 * 1024 - 512;
+    int hg = (hg_req > 0 && hg_req < H) ? hg_req : H;
+    while (hg > 1 && (hg > 4 * AT_WARPS || smem_of(hg) > smem_max)) hg = (hg + 1) / 2;
+    if (smem_of(hg) > smem_max) return 1006;
+    const size_t smem = smem_of(hg);
+    const int groups = (H + hg - 1) / hg;
+    const int warps = hg < AT_WARPS ? hg : AT_WARPS;
+    const int hpw = (hg + warps - 1) / warps;
+    dim3 grid(n_splits, B, groups);
     rv_drain_error();
-#define RV_ATT(HPW)                                                                                      \
-    do {                                                                                                 \
+#define RV_ATT(HPW)                                                                                       \
+    do {                                                                                                  \
         cudaFuncSetAttribute(attend_simt_kernel<PAGED, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                             (int)smem);                                                                 \
-        attend_simt_kernel<PAGED, HPW><<<grid, AT_THREADS, smem, st>>>(sp, pp, H, kvl, rope, scale,      \
-                                                                       nr_single, n_splits, partial);    \
+                             (int)smem);                                                                  \
+        if (dependent)                                                                                    \
+            rv_launch_dependent(attend_simt_kernel<PAGED, HPW>, grid, dim3(warps * 32), smem, st, sp, pp, H, hg, kvl,  \
+                                rope, scale, nr_single, n_splits, partial);                               \
+        else                                                                                              \
+            attend_simt_kernel<PAGED, HPW><<<grid, warps * 32, smem, st>>>(sp, pp, H, hg, kvl, rope, scale, \
+                                                                          nr_single, n_splits, partial);  \
     } while (0)
     if (hpw <= 1) RV_ATT(1);
     else if (hpw <= 2) RV_ATT(2);
@@ -236,15 +265,21 @@ static int launch_attend_simt(const AttSlab& sp, const AttPaged& pp, int H, int 
 #undef RV_ATT
     int e = rv_launch_status();
     if (e || n_splits <= 1) return e;
+    const long long cap = PAGED ? (pp.rows ? pp.row_stride : (long long)pp.max_pages * pp.page_tokens) : 0;
     attend_combine_kernel<PAGED><<<dim3(H, B), 128, 0, st>>>(partial, H, kvl, n_splits, sp.clat, pp.out,
-                                                              pp.out_m, pp.out_lse);
+                                                              pp.out_m, pp.out_lse, PAGED ? pp.n_rows : nullptr, cap,
+                                                              pp.rows_lo, pp.rows_hi, 0);
     return rv_launch_status();
 }
 
-// Combine launcher shared with the tensor-core kernel (same partial layout).
+// Combine launcher shared with the tensor-core kernel (same partial layout). Sequences whose row count
+// lies outside [rows_lo, rows_hi) are left untouched (another kernel of the same call wrote them), except
+// that an empty sequence is served when serve_empty is set.
 extern "C" void rivoli_attend_combine_paged(const float* partial, int H, int kvl, int n_splits, int B, uint16_t* out,
-                                            float* out_m, float* out_lse, cudaStream_t st) {
-    attend_combine_kernel<true><<<dim3(H, B), 128, 0, st>>>(partial, H, kvl, n_splits, nullptr, out, out_m, out_lse);
+                                            float* out_m, float* out_lse, const int32_t* n_rows, long long cap,
+                                            int rows_lo, int rows_hi, int serve_empty, cudaStream_t st) {
+    attend_combine_kernel<true><<<dim3(H, B), 128, 0, st>>>(partial, H, kvl, n_splits, nullptr, out, out_m, out_lse,
+                                                            n_rows, cap, rows_lo, rows_hi, serve_empty);
 }
 
 RIVOLI_API size_t rivoli_mla_attend_scratch_floats(int H, int kvl) {
@@ -261,8 +296,10 @@ RIVOLI_API int rivoli_mla_attend(const float* qabs, const float* qrope, const un
     // with the same codes (attn.hip:285-293).
     if (((size_t)16 * kvl + (size_t)16 * rope) * sizeof(float) > 65536) return 1002;
     if (kvl > 512 || (kvl % 128) != 0) return 1004;
-    if (H > 128 || rope > 128) return 1002;
-    // Split plan: a pure function of (H, nr, scratch present) -> same shape, same summation order.
+    if (rope > 128) return 1002;
+    // Any H: heads beyond what one CTA's shared memory holds are tiled over gridDim.z (the reference tiles
+    // them in blocks of 16, attn.hip:119-130). Split plan: a pure function of (H, nr, scratch present) ->
+    // same shape, same summation order.
     int n_splits = 1;
     if (partial) {
         n_splits = (nr + 255) / 256;
@@ -354,7 +391,22 @@ RIVOLI_API int rivoli_attend_simt_paged_bf16(const DsaGeom* g, const uint16_t* q
     int n_splits = scratch ? simt_paged_splits(B) : 1;
     AttSlab sp{};
     AttPaged pp{q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows, g->page_tokens,
-                g->max_pages_per_seq, g->n_pool_pages, out, out_m, out_lse};
+                g->max_pages_per_seq, g->n_pool_pages, out, out_m, out_lse, 0, 0x7fffffff};
     return launch_attend_simt<true>(sp, pp, g->n_heads, g->kv_lora, g->rope_dim, g->softmax_scale, 0, B,
                                     n_splits, (float*)scratch, (cudaStream_t)stream);
+}
+
+// The sequences of a batch with 0 < n_rows < rows_hi, on the CUDA-core kernel, eight heads per CTA and no
+// split (no scratch): the short-context arm of rivoli_mla_attend_paged_bf16, launched in front of the
+// tensor-core kernel as a programmatic dependent of whatever precedes it in the stream.
+extern "C" int rivoli_attend_simt_short_rows(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
+                                             const float* latent_scale, const int32_t* block_table,
+                                             const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
+                                             uint16_t* out, float* out_m, float* out_lse, int rows_hi,
+                                             cudaStream_t st) {
+    AttSlab sp{};
+    AttPaged pp{q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows, g->page_tokens,
+                g->max_pages_per_seq, g->n_pool_pages, out, out_m, out_lse, 1, rows_hi};
+    return launch_attend_simt<true>(sp, pp, g->n_heads, g->kv_lora, g->rope_dim, g->softmax_scale, 0, B, 1, nullptr,
+                                    st, 8, true);
 }

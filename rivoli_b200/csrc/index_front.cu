@@ -170,13 +170,6 @@ __device__ __forceinline__ void fm_mma(uint32_t d_tmem, uint64_t da, uint64_t db
                  ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ int g_front_err;
-#ifdef RIVOLI_DEBUG_TIMES
-__device__ long long g_fm_times[64];
-#define FM_STAMP(slot) do { if (blockIdx.x == FM_DBG_CTA && threadIdx.x == 0 && (slot) < 64) g_fm_times[slot] = clock64(); } while (0)
-constexpr int FM_DBG_CTA = 40;    // a CTA of the widest job
-#else
-#define FM_STAMP(slot) do { } while (0)
-#endif
 
 __global__ void __launch_bounds__(FM_THREADS)
 front_gemm_mma_kernel(FrontArgs A) {
@@ -197,14 +190,12 @@ front_gemm_mma_kernel(FrontArgs A) {
     const int nch = k1 > k0 ? (k1 - k0) / 64 : 0;
     const int sc_cols = J.K / 128;
     const float* srow = J.scale + (size_t)((tile * TN) >> 7) * sc_cols;
-    FM_STAMP(0);
     if (tid == 0) { tc::mbar_init(&bar[0], 1); tc::mbar_init(&bar[1], 1); tc::mbar_init_fence(); abort_word = 0; }
     if (warp == 0) tc::tmem_alloc<128>(&tmem_slot);
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    FM_STAMP(1);
     // instruction descriptor: bf16 x bf16 -> f32, both K-major, M = 128, N = TN
     const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
@@ -251,14 +242,11 @@ front_gemm_mma_kernel(FrontArgs A) {
         for (int c = 0; c < nch && ok; ++c) {
             const int wb = c & 1;
             // stage (c + 2) % 3 was read by the MMAs of chunk c - 1, weight buffer wb by those of chunk c - 2
-            if (c >= 1) ok = tc::mbar_wait(&bar[(c - 1) & 1], (done[(c - 1) & 1] - 1) & 1, abort_flag, 81);
+            if (c >= 1) ok = tc::mbar_wait_warp(&bar[(c - 1) & 1], (done[(c - 1) & 1] - 1) & 1, abort_flag, 81);
             if (!ok) break;
-            FM_STAMP(4 + c * 5);
             request(c + 2);
-            FM_STAMP(5 + c * 5);
             tc::cp_async_wait<2>();                          // chunk c has landed (two younger groups may be pending)
             __syncthreads();
-            FM_STAMP(6 + c * 5);
             const uint8_t* sA = fm_smem + (c % FM_NST) * FM_STAGE;
             const uint8_t* sW = sA + 16384;
             uint8_t* sB = fm_smem + FM_BOFF + wb * 16384;
@@ -278,7 +266,6 @@ front_gemm_mma_kernel(FrontArgs A) {
             }
             tc::fence_proxy_async();
             __syncthreads();
-            FM_STAMP(7 + c * 5);
             if (tid == 0) {
                 tc::tc_fence_after();
                 const uint64_t da0 = fm_desc(tc::smem_u32(sA)), db0 = fm_desc(tc::smem_u32(sB));
@@ -286,15 +273,13 @@ front_gemm_mma_kernel(FrontArgs A) {
                 for (int k = 0; k < 4; ++k) fm_mma(tmem, da0 + 2 * k, db0 + 2 * k, idesc, (c | k) ? 1u : 0u);   // +32 bytes = +2 in the address field
                 tc::mma_commit(&bar[wb]);
             }
-            FM_STAMP(8 + c * 5);
             ++done[wb];
         }
         tc::cp_async_wait<0>();
         // all MMAs of this batch tile: wait for the last commit of each weight buffer
         for (int st = 0; st < 2 && ok; ++st)
-            if (done[st] > 0) ok = tc::mbar_wait(&bar[st], (done[st] - 1) & 1, abort_flag, 83 + st);
+            if (done[st] > 0) ok = tc::mbar_wait_warp(&bar[st], (done[st] - 1) & 1, abort_flag, 83 + st);
         tc::tc_fence_after();
-        FM_STAMP(2);
         if (ok && nch > 0) {
             const int ncol_chunks = TN / 32;                 // 32-column chunks; warps 0-3 take the even ones, 4-7 the odd
             for (int c = chalf; c < ncol_chunks; c += 2) {
@@ -318,7 +303,6 @@ front_gemm_mma_kernel(FrontArgs A) {
         tc::tc_fence_before();
         __syncthreads();
     }
-    FM_STAMP(3);
     if (warp == 0) tc::tmem_dealloc<128>(tmem);
     if (tid == 0 && abort_word) atomicCAS(&g_front_err, 0, abort_word);
 }
@@ -573,8 +557,3 @@ RIVOLI_API int rivoli_index_frontend_status(void* stream) {
     return h ? 1008 : 0;
 }
 
-#ifdef RIVOLI_DEBUG_TIMES
-extern "C" __attribute__((visibility("default"))) int rivoli_front_debug_times(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_fm_times, sizeof(long long) * 64);
-}
-#endif

@@ -49,6 +49,7 @@ constexpr int IM_THREADS = 192;    // warps 0-3 epilogue, 4 producer, 5 MMA
 constexpr int IM_STAGE_BYTES = IM_TILE * IM_HD;   // 16 KiB
 constexpr int IM_Q_BYTES = IM_NPAD * IM_HD;       // 4 KiB
 constexpr float IM_EPS_REL = 1.52587890625e-05f;  // 2^-16
+constexpr int IM_ERR_BAD_PAGE = 1005;             // error word: a block-table entry inside seq_len lies outside the pool
 
 struct IndexMmaArgs {
     DsaGeom g;
@@ -213,18 +214,23 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
             for (int j = lane; j < IM_TPI * ppt; j += 32) {
                 const int lp = first_lp + j;
                 int pg = -1;
-                if (lp < g.max_pages_per_seq && lp * P < nt) pg = A.block_table[(size_t)b * g.max_pages_per_seq + lp];
-                s_pg[j] = (pg < 0 || pg >= g.n_pool_pages) ? -1 : pg;
+                const bool live = lp < g.max_pages_per_seq && lp * P < nt;
+                if (live) pg = A.block_table[(size_t)b * g.max_pages_per_seq + lp];
+                const bool bad = pg < 0 || pg >= g.n_pool_pages;
+                // A page inside the sequence that the table does not map into the pool is never loaded (its
+                // tokens get scores of whatever the stage held) and the call is flagged, as the append does.
+                if (live && bad) atomicCAS(A.err, 0, IM_ERR_BAD_PAGE);
+                s_pg[j] = bad ? -1 : pg;
             }
             __syncwarp();
             const int qb = items_done & 1;
             for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
                 const int s = it % IM_NS;
-                ok = tc::mbar_wait(&bars.empty[s], ((it / IM_NS) & 1) ^ 1, &abort_flag, 11);
+                ok = tc::mbar_wait_warp(&bars.empty[s], ((it / IM_NS) & 1) ^ 1, &abort_flag, 11);
                 if (!ok) break;
                 const bool first = tile == c * IM_TPI;
                 if (first) {
-                    ok = tc::mbar_wait(&bars.qfree[qb], ((items_done >> 1) & 1) ^ 1, &abort_flag, 12);
+                    ok = tc::mbar_wait_warp(&bars.qfree[qb], ((items_done >> 1) & 1) ^ 1, &abort_flag, 12);
                     if (!ok) break;
                 }
                 if (lane == 0) {
@@ -258,8 +264,8 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
             const int qb = items_done & 1;
             for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
                 const int s = it % IM_NS, a = it % IM_NACC;
-                ok = tc::mbar_wait(&bars.full[s], (it / IM_NS) & 1, &abort_flag, 21) &&
-                     tc::mbar_wait(&bars.tempty[a], ((it / IM_NACC) & 1) ^ 1, &abort_flag, 22);
+                ok = tc::mbar_wait_warp(&bars.full[s], (it / IM_NS) & 1, &abort_flag, 21) &&
+                     tc::mbar_wait_warp(&bars.tempty[a], ((it / IM_NACC) & 1) ^ 1, &abort_flag, 22);
                 if (!ok) break;
                 tc::tc_fence_after();
                 if (lane == 0) {
@@ -297,7 +303,7 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
             for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
                 const int a = it % IM_NACC;
                 const int t = tile * IM_TILE + tid;
-                ok = tc::mbar_wait(&bars.tfull[a], (it / IM_NACC) & 1, &abort_flag, 31);
+                ok = tc::mbar_wait_warp(&bars.tfull[a], (it / IM_NACC) & 1, &abort_flag, 31);
                 if (!ok) break;
                 tc::tc_fence_after();
                 uint32_t r[32];
@@ -328,16 +334,6 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
 // ---------------------------------------------------------------------------------------------
 constexpr int RF_LIST = 2048;      // band tokens re-scored per round
 
-// Optional phase timeline of CTA 0 for tuning builds (-DRIVOLI_DEBUG_TIMES); compiled out otherwise.
-#ifdef RIVOLI_DEBUG_TIMES
-__device__ long long g_rf_times[16];
-__device__ unsigned long long g_rf_span[1024][2];   // per CTA: globaltimer at entry and exit
-__device__ __forceinline__ unsigned long long rf_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define RF_STAMP(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_rf_times[slot] = clock64(); \
-                            if (threadIdx.x == 0 && blockIdx.x < 1024 && ((slot) == 0 || (slot) == 8)) g_rf_span[blockIdx.x][(slot) == 8] = rf_gtime(); } while (0)
-#else
-#define RF_STAMP(slot) do { } while (0)
-#endif
 
 // listed tokens a warp re-scores per pass: 4, or 2 where the key array leaves less shared memory
 __host__ __device__ constexpr int rf_tok(int ept) { return ept > 16 ? 2 : 4; }
@@ -370,7 +366,6 @@ index_select_refine_kernel(RefineArgs A) {
     const int nt = min(A.seq_len[b], A.score_stride);
     const int kk = min(A.k, nt);
     uint32_t* out = A.rows + (size_t)b * A.k;
-    RF_STAMP(0);
     if (tid == 0) A.n_sel[b] = kk > 0 ? kk : 0;
     if (kk <= 0) return;
     if (kk == nt) {
@@ -437,18 +432,15 @@ index_select_refine_kernel(RefineArgs A) {
         key[j] = j < nvalid ? topk_key(sc[j] * sk[j]) : 0u;
         skm = fmaxf(skm, sk[j]);
     }
-    RF_STAMP(2);
     int buf = 0;
     const float sk_max = __uint_as_float(tk_block_max(__float_as_uint(skm), sh, buf));   // also orders qf / list_n
     const float eps = sk_max * A.cb[b];
-    RF_STAMP(3);
 
     // k-th largest approximate score, located to 20 key bits: A_k lies in [T, T + 0xfff]
     const uint32_t T20 = tk_bisect<EPT>(key, (uint32_t)kk, 20, sh, buf);
     const float lo_f = topk_unkey(T20) - 2.0f * eps, hi_f = topk_unkey(T20 | 0xfffu) + 2.0f * eps;
     const uint32_t k_lo = lo_f == lo_f ? topk_key(lo_f) : 0u;
     const uint32_t k_hi = hi_f == hi_f ? topk_key(hi_f) : 0xffffffffu;
-    RF_STAMP(4);
 
     // classify from registers: surely selected / band (re-scored exactly) / surely not
     uint32_t m_in = 0u, m_band = 0u;
@@ -481,7 +473,6 @@ index_select_refine_kernel(RefineArgs A) {
     }
     __syncthreads();
     const uint32_t n_band = list_n;
-    RF_STAMP(5);
 
     // this lane's head constants for the exact re-score (nh <= 32)
     const float my_sq = lane < nh ? A.qscales[(size_t)b * nh + lane] : 0.0f;
@@ -567,7 +558,6 @@ index_select_refine_kernel(RefineArgs A) {
         // (exact key descending, index ascending); the selection takes the (kk - n_in) best.
         rescore(n_band, false);
         __syncthreads();
-        RF_STAMP(6);
         const uint32_t take = (uint32_t)kk - n_in;   // >= 1: at most kk - 1 tokens lie above the band
         for (uint32_t q2 = warp; q2 < n_band; q2 += TK_WARPS) {
             const uint32_t kq = bkey[q2], tq = list[q2];
@@ -580,7 +570,6 @@ index_select_refine_kernel(RefineArgs A) {
             if (lane == 0) dec[q2] = c < take ? 1u : 0u;
         }
         __syncthreads();
-        RF_STAMP(7);
         uint32_t pos = my_pos;
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
@@ -590,7 +579,6 @@ index_select_refine_kernel(RefineArgs A) {
         }
         tk_compact_contig<EPT>(key, nt, 0xfffffffeu, 0u, sh, out);
         if (tid == 0 && A.stats) { A.stats[b * 2] = n_band; A.stats[b * 2 + 1] = n_in; }
-        RF_STAMP(8);
         return;
     }
     // Rare case (tie-dominated scores): the band does not fit the list. The key array goes to
@@ -779,8 +767,9 @@ RIVOLI_API int rivoli_dsa_append_select_paged(const DsaGeom* g, const uint16_t* 
                        scratch, stream);
 }
 
-// Reads back the tensor-core scorer's error word (0 = no bounded wait ever gave up) and
-// clears it. Synchronises the stream.
+// Reads back the tensor-core scorer's error word and clears it: 1005 = a block-table entry inside a
+// sequence's length pointed outside the pool (rows undefined), 1008 = a bounded wait gave up.
+// Synchronises the stream.
 RIVOLI_API int rivoli_index_select_status(const DsaGeom* g, int B, int score_stride, void* scratch, void* stream) {
     if (!g || !scratch) return 1001;
     size_t total = 0;
@@ -790,7 +779,7 @@ RIVOLI_API int rivoli_index_select_status(const DsaGeom* g, int B, int score_str
     if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
     if (e != cudaSuccess) return -(int)e;
     if (h) cudaMemsetAsync(s.err, 0, sizeof(int), (cudaStream_t)stream);
-    return h ? 1008 : 0;
+    return h == IM_ERR_BAD_PAGE ? 1005 : (h ? 1008 : 0);
 }
 
 // Diagnostics: copies the per-sequence band sizes of the last call (tokens re-scored
@@ -805,11 +794,3 @@ RIVOLI_API int rivoli_index_select_band_stats(const DsaGeom* g, int B, int score
     return e == cudaSuccess ? 0 : -(int)e;
 }
 
-#ifdef RIVOLI_DEBUG_TIMES
-extern "C" __attribute__((visibility("default"))) int rivoli_refine_debug_times(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_rf_times, sizeof(long long) * 16);
-}
-extern "C" __attribute__((visibility("default"))) int rivoli_refine_debug_spans(unsigned long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_rf_span, sizeof(unsigned long long) * 2048);
-}
-#endif

@@ -23,17 +23,6 @@ namespace {
 constexpr int KP_THREADS = 256;   // 8 warps: loaders by (warp = row, lane = chunk); epilogue by (lane quadrant, column half)
 constexpr int KP_WARPS = KP_THREADS / 32;
 __device__ int g_kp_err;
-#ifdef RIVOLI_DEBUG_TIMES
-__device__ long long g_kp_times[2][8];
-__device__ unsigned long long g_kp_span[2][512][3];   // per CTA: globaltimer at entry / exit, SM id
-__device__ __forceinline__ unsigned long long kp_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ unsigned kp_smid() { unsigned v; asm volatile("mov.u32 %0, %smid;" : "=r"(v)); return v; }
-#define KP_STAMP(k, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_kp_times[k][slot] = clock64(); \
-    if (threadIdx.x == 0 && ((slot) == 0 || (slot) == 6)) { const int cta = blockIdx.y * gridDim.x + blockIdx.x; \
-        if (cta < 512) { g_kp_span[k][cta][(slot) == 6] = kp_gtime(); g_kp_span[k][cta][2] = kp_smid(); } } } while (0)
-#else
-#define KP_STAMP(k, slot) do { } while (0)
-#endif
 
 __device__ __forceinline__ uint64_t kp_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
@@ -104,10 +93,8 @@ kvb_absorb_mma_kernel(KpArgs A) {
     const bool two_runs = cut < nope;
     const float s1 = two_runs ? A.scale[((rbase + cut) >> 7) * sc_cols + iblk] : 0.0f;
 
-    KP_STAMP(0, 0);
     if (tid == 0) { tc::mbar_init(&bar, 1); tc::mbar_init_fence(); abort_word = 0; }
     if (warp == 0) tc::tmem_alloc<256>(&tmem_slot);
-    KP_STAMP(0, 1);
     // activations of a batch tile: 128 sequences x nope bf16, K-major swizzled; warp = row, lane = 16-byte chunk;
     // rows past B are zeros. Asynchronous: requested BEFORE the weights are fetched and converted.
     auto load_acts = [&](int b0) {
@@ -145,7 +132,6 @@ kvb_absorb_mma_kernel(KpArgs A) {
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    KP_STAMP(0, 2);
     const uint32_t idesc = kp_idesc(128, 128, 1);
     const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;   // TMEM lane quadrant of this warp
     const int erow = (warp & 3) * 32 + lane, chalf = warp >> 2;      // epilogue: sequence row, column half
@@ -165,7 +151,6 @@ kvb_absorb_mma_kernel(KpArgs A) {
         tc::cp_async_wait<0>();
         tc::fence_proxy_async();
         __syncthreads();
-        KP_STAMP(0, 3);
         if (tid == 0) {
             tc::tc_fence_after();
             const uint32_t a0 = tc::smem_u32(sA), b0a = tc::smem_u32(sB);
@@ -181,7 +166,6 @@ kvb_absorb_mma_kernel(KpArgs A) {
 #endif
             }
             tc::mma_commit(&bar);
-            KP_STAMP(0, 4);
         }
         if (rope_mine) {
             uint4* dst = reinterpret_cast<uint4*>(A.out + ((size_t)(b0 + tid) * A.H + h) * W + kvl);
@@ -189,8 +173,7 @@ kvb_absorb_mma_kernel(KpArgs A) {
             for (int e = 0; e < 8; ++e)
                 if (e < A.rope / 8) dst[e] = rope_v[e];
         }
-        ok = tc::mbar_wait(&bar, phase, abort_flag, 71);
-        KP_STAMP(0, 5);
+        ok = tc::mbar_wait_warp(&bar, phase, abort_flag, 71);
         tc::tc_fence_after();
         if (ok) {
 #pragma unroll 1
@@ -219,7 +202,6 @@ kvb_absorb_mma_kernel(KpArgs A) {
         }
         tc::tc_fence_before();
         __syncthreads();   // TMEM and the A tile are free for the next batch tile
-        KP_STAMP(0, 6);
     }
     if (warp == 0) tc::tmem_dealloc<256>(tmem);
     if (tid == 0 && abort_word) atomicCAS(&g_kp_err, 0, abort_word);
@@ -247,7 +229,6 @@ kvb_value_mma_kernel(KpArgs A) {
     uint8_t* sB = smem + hch * 16384;
     const size_t row0 = (size_t)h * (A.nope + vh) + A.nope + (size_t)jblk * 128;   // 128 value rows = 2 scale rows
     const int sc_cols = kvl / 128;
-    KP_STAMP(1, 0);
     if (tid < 2 * sc_cols) s_sc[tid / sc_cols][tid % sc_cols] = A.scale[((row0 + (tid / sc_cols) * 64) >> 7) * sc_cols + tid % sc_cols];
     if (tid == 0) { tc::mbar_init(&bar[0], 1); tc::mbar_init(&bar[1], 1); tc::mbar_init_fence(); abort_word = 0; }
     if (warp == 0) tc::tmem_alloc<512>(&tmem_slot);
@@ -293,7 +274,6 @@ kvb_value_mma_kernel(KpArgs A) {
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    KP_STAMP(1, 2);
     const uint32_t idesc = kp_idesc(128, 128, 0);
     const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;   // TMEM lane quadrant of this warp
     const int erow = (warp & 3) * 32 + lane, chalf = warp >> 2;      // epilogue: sequence row, 64-column half
@@ -305,7 +285,6 @@ kvb_value_mma_kernel(KpArgs A) {
             tc::cp_async_wait<0>();
             tc::fence_proxy_async();
             __syncthreads();
-            if (half == 0) KP_STAMP(1, 3);
             if (tid == 0) {
                 tc::tc_fence_after();
                 const uint32_t a0 = tc::smem_u32(sA), b0a = tc::smem_u32(sB);
@@ -316,12 +295,10 @@ kvb_value_mma_kernel(KpArgs A) {
                            kp_desc(b0a + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), idesc, (k & 7) ? 1u : 0u);
                 }
                 tc::mma_commit(&bar[half]);
-                if (half == 1) KP_STAMP(1, 4);
             }
             // the A half may be overwritten (and the accumulators read) only once these MMAs are done
-            ok = tc::mbar_wait(&bar[half], phase, abort_flag, 72 + half);
+            ok = tc::mbar_wait_warp(&bar[half], phase, abort_flag, 72 + half);
         }
-        KP_STAMP(1, 5);
         tc::tc_fence_after();
         if (ok) {
 #pragma unroll 1
@@ -350,7 +327,6 @@ kvb_value_mma_kernel(KpArgs A) {
         }
         tc::tc_fence_before();
         __syncthreads();
-        KP_STAMP(1, 6);
     }
     if (warp == 0) tc::tmem_dealloc<512>(tmem);
     if (tid == 0 && abort_word) atomicCAS(&g_kp_err, 0, abort_word);
@@ -405,11 +381,3 @@ RIVOLI_API int rivoli_kvb_proj_status(void* stream) {
     return h ? 1008 : 0;
 }
 
-#ifdef RIVOLI_DEBUG_TIMES
-extern "C" __attribute__((visibility("default"))) int rivoli_kvb_debug_times(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_kp_times, sizeof(long long) * 16);
-}
-extern "C" __attribute__((visibility("default"))) int rivoli_kvb_debug_spans(unsigned long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_kp_span, sizeof(unsigned long long) * 2 * 512 * 3);
-}
-#endif

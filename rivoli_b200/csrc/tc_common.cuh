@@ -33,9 +33,12 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 constexpr int kMaxPolls = 1000 * 1000;  // far beyond any legitimate wait (microseconds); bounds a protocol bug
 
 // Returns false (and raises *abort_flag) if the phase never completes or another wait gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+// Each lane polls on its own, so the lanes of a warp can disagree (one sees the phase complete while
+// another sees the abort word first): warp-collective code uses mbar_wait_warp below.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          int max_polls = kMaxPolls) {
     const uint32_t a = smem_u32(bar);
-    for (int it = 0; it < kMaxPolls; ++it) {
+    for (int it = 0; it < max_polls; ++it) {
         uint32_t ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(a), "r"(parity) : "memory");
@@ -44,6 +47,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
     *abort_flag = code;
     return false;
+}
+// The same wait with a warp-uniform answer: true only if every lane saw the phase complete. To be called
+// by all 32 lanes of a converged warp (code that goes on to shuffles, ballots, named barriers or
+// .sync.aligned tcgen05 instructions must not let lanes part ways on the outcome of a wait).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
+                                               int max_polls = kMaxPolls) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, code, max_polls));
 }
 
 // ---- proxies / fences ---------------------------------------------------------------------------

@@ -115,13 +115,6 @@ constexpr int SA_SEL = SA_IDX + 2 * SA_TILE * 4;            // i32 [SA_SEL_MAX] 
 constexpr int SA_SEL_MAX = 2048;
 constexpr int SA_TOTAL = SA_SEL + SA_SEL_MAX * 4;
 
-// Optional per-tile timeline of CTA 0, thread 0 for tuning builds (-DRIVOLI_DEBUG_TIMES); compiled out otherwise.
-#ifdef RIVOLI_DEBUG_TIMES
-__device__ long long g_v4_times[32 * 8];
-#define V4_STAMP(tile, slot) do { if (blockIdx.x == 0 && threadIdx.x == 0 && (tile) < 32) g_v4_times[(tile) * 8 + (slot)] = clock64(); } while (0)
-#else
-#define V4_STAMP(tile, slot) do { } while (0)
-#endif
 
 __device__ __forceinline__ uint32_t v4_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void v4_cp_async16(uint32_t dst, const void* src) {
@@ -162,7 +155,6 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
                                                                              uint16_t* __restrict__ out) {
     extern __shared__ __align__(1024) unsigned char sa_smem[];
     const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    V4_STAMP(30, 0);
     const uint32_t sbase = v4_smem_u32(sa_smem);
     float* sS = reinterpret_cast<float*>(sa_smem + SA_SS);
     float* sFac = reinterpret_cast<float*>(sa_smem + SA_FAC);
@@ -185,14 +177,15 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
         else *reinterpret_cast<uint4*>(sa_smem + off) = make_uint4(0, 0, 0, 0);   // masked slot: a row of zeros
     };
 
-    // q of this sequence (not produced by the kernel before this one), then that kernel's selection row, then
-    // the first tile
+    // Under a programmatic dependent launch the kernel before this one may still be running, and the caller
+    // may have produced q with it: nothing is read before the dependency wait. Then q of this sequence, the
+    // selection row and the first tile.
+    rv_grid_dep_wait();
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
         const int ch = tid + it * SA_THREADS, row = ch >> 6, c = ch & 63;
         v4_cp_async16(sbase + SA_SQ + swz(row, c), q + ((size_t)b * SA_H + row) * SA_D + c * 8);
     }
-    rv_grid_dep_wait();
     if (cols <= SA_SEL_MAX) {   // read the row once; the per-tile gathers then take their slots from shared memory
         int32_t* sSel = reinterpret_cast<int32_t*>(sa_smem + SA_SEL);
         for (int i = tid; i < cols; i += SA_THREADS) sSel[i] = ix[i];
@@ -219,7 +212,6 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
 
     for (int t = 0; t < n_tiles; ++t) {
         const int buf = t & 1;
-        V4_STAMP(t, 0);
         if (t + 1 < n_tiles) {
 #pragma unroll
             for (int it = 0; it < 8; ++it) gather_piece(t + 1, buf ^ 1, it);
@@ -228,9 +220,7 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        V4_STAMP(t, 1);
         __syncthreads();
-        V4_STAMP(t, 2);
         const uint32_t sK = sbase + SA_SK + buf * SA_TILE * SA_ROW_BYTES;
 
         // ---- scores: S[32 heads][16 tokens] over this warp's half of the dims
@@ -279,9 +269,7 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
                 }
             if (kh == 0) __syncthreads();
         }
-        V4_STAMP(t, 3);
         __syncthreads();
-        V4_STAMP(t, 4);
 
         // ---- softmax over the tile: head = tid / 8, tokens 8 * (tid % 8) .. +7
         {
@@ -318,7 +306,6 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
             if (part == 0) sFac[head] = fac;
         }
         __syncthreads();
-        V4_STAMP(t, 5);
 
         // ---- values: O[32 heads][64 dims] += P[32 heads][64 tokens] V[64 tokens][64 dims]
         {
@@ -348,12 +335,9 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
                 }
             }
         }
-        V4_STAMP(t, 6);
         __syncthreads();
-        V4_STAMP(t, 7);
     }
 
-    V4_STAMP(30, 1);
     // the sink joins the denominator only, shifted by the same running max
     {
         const int head = tid >> 3;
@@ -387,16 +371,10 @@ __global__ void __launch_bounds__(SA_THREADS, 1) v4_sparse_attend_mma_kernel(con
         *reinterpret_cast<uint4*>(out + ((size_t)b * SA_H + row) * SA_D + c * 8) =
             *reinterpret_cast<const uint4*>(sa_smem + SA_SQ + swz(row, c));
     }
-    V4_STAMP(30, 2);
 }
 
 }  // namespace
 
-#ifdef RIVOLI_DEBUG_TIMES
-RIVOLI_API int rivoli_v4_debug_times(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_v4_times, sizeof(long long) * 32 * 8);
-}
-#endif
 
 RIVOLI_API int rivoli_gather_attn_shared_kv(const float* q, const float* kv, const float* sink, const int* idxs, int m,
                                             int h, int d, int topk, float scale, float* o, void* stream) {

@@ -470,7 +470,11 @@ __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const i
     uint32_t* picked = reinterpret_cast<uint32_t*>(sc + g.max_comp);
 
     const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    rv_grid_dep_trigger();   // the attention kernel may start staging its queries
+    rv_grid_dep_trigger();   // the attention kernel may be scheduled; it waits for this grid before it reads anything
+    // Every CTA waits for the scorer first, including those that return early below: the kernel launched after
+    // this one relies on "this grid is complete" implying "everything before it is complete", and `sel` may
+    // still be read by a kernel of the previous step that the scorer's own wait orders.
+    rv_grid_dep_wait();
     const int W = g.window, K = g.index_topk, p = pos[b];
     int32_t* row = sel + (size_t)b * (W + K);
     // the ring: oldest first once full, live slots then -1 before that
@@ -486,8 +490,7 @@ __global__ void __launch_bounds__(TK_THREADS) v4_select_kernel(V4Geom g, const i
         for (int c = tid; c < K; c += TK_THREADS) row[W + c] = c < n_comp ? W + c : -1;
         return;
     }
-    float* srow = scores + (size_t)b * g.max_comp;
-    rv_grid_dep_wait();      // the scorer's rows and flags
+    float* srow = scores + (size_t)b * g.max_comp;   // the scorer's rows and flags (ordered by the wait above)
     const uint16_t* kv = index_kv + (size_t)b * g.max_comp * g.index_dim;
     // the ordered CUDA-core fold over every block: on request, or when the integer scorer could not take the queries
     auto fold_all = [&]() {

@@ -127,13 +127,16 @@ class DsaDecodeLayer:
 
     def step(self, latent, index_key, index_q, index_w, q, row_pos, seq_len, stream=None,
              out: torch.Tensor | None = None) -> torch.Tensor:
-        """One layer-step: append one token per sequence, select, attend (the append rides in the
-        launch that prepares the indexer query)."""
-        be.launch_dsa_append_select_paged(self.g, latent, index_key, row_pos, self.block_table, self.latent_pool,
-                                          self.latent_scale, self.index_pool, self.index_scale, self.status,
-                                          index_q, index_w, seq_len, self.B, self.score_stride, self.rows,
-                                          self.n_sel, self.select_scratch, stream)
-        return self.attend(q, stream, out=out)
+        """One layer-step in one library call: append one token per sequence, select, attend (the append
+        rides in the launch that prepares the indexer query; the attention kernel converts ``q`` while the
+        selection is still running, which the one-call form makes safe)."""
+        out = self.out if out is None else out
+        be.launch_dsa_decode_step_paged(self.g, latent, index_key, row_pos, self.block_table, self.latent_pool,
+                                        self.latent_scale, self.index_pool, self.index_scale, self.status,
+                                        index_q, index_w, seq_len, self.B, self.score_stride, self.rows,
+                                        self.n_sel, self.select_scratch, q, out, self.out_m, self.out_lse,
+                                        self.scratch, stream)
+        return out
 
     def check_status(self) -> None:
         """Raise if a kernel flagged a bad block-table entry since the last check (syncs)."""

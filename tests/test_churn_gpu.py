@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from oracle import oracle as orc
-from tests.helpers import attend_close_ref, bf16_normal, make_geom
+from tests.helpers import attend_close, attend_close_ref, bf16_normal, make_geom
 
 pytestmark = pytest.mark.gpu
 
@@ -78,7 +78,9 @@ def test_churn_three_layers_match_oracle():
             for b in range(n_slots):
                 np.testing.assert_array_equal(got_rows[b, :n_sel[b]], rows[b, :n_sel[b]], err_msg=f"step {step} layer {li} slot {b}")
             ok, worst, rms = attend_close_ref(out.cpu().view(torch.int16).numpy().view(np.uint16), want)
-            assert ok and rms <= 1e-2, (step, li, worst, rms)
+            assert ok and rms <= 5e-3, (step, li, worst, rms)
+            ok, worst = attend_close(out.cpu().view(torch.int16).numpy().view(np.uint16), want)   # elementwise 2e-2 / 1e-3
+            assert ok, (step, li, worst)
             # the pools themselves: bit-identical everywhere a live sequence has a token
             np.testing.assert_array_equal(L.latent_scale.cpu().numpy().view(np.uint32), M["ls"].view(np.uint32))
             np.testing.assert_array_equal(L.index_pool.cpu().numpy(), M["ip"])
@@ -127,4 +129,6 @@ def test_shared_layers_attend_over_the_full_layers_selection():
         assert orc.kv_append_paged(st0.og, st.new_latent, st.new_key, None, st0.row_pos, st0.block_table, lp, ls, ip, isc) == 0
         _, want, _, _ = orc.mla_attend_paged(st0.og, st.q, lp, ls, st0.block_table, rows, n_sel, want_f32=True)
         ok, worst, rms = attend_close_ref(outs[i].cpu().view(torch.int16).numpy().view(np.uint16), want)
-        assert ok and rms <= 1e-2, (i, worst, rms)
+        assert ok and rms <= 5e-3, (i, worst, rms)
+        ok, worst = attend_close(outs[i].cpu().view(torch.int16).numpy().view(np.uint16), want)       # elementwise 2e-2 / 1e-3
+        assert ok, (i, worst)

@@ -164,3 +164,37 @@ def test_absorb_step_value_chain_matches_oracle(be):
     got_c = orc.bf16_to_f32(ctx.cpu().view(torch.int16).numpy().view(np.uint16)).astype(np.float64)
     err = np.abs(got_c - want_c32)
     assert (err <= 2.0 ** -8 * np.abs(want_c32) + 1e-3 * np.abs(want_c32).max()).all(), float(err.max())
+
+
+def test_absorb_then_dense_attend_back_to_back_on_one_stream(be):
+    """q produced by the kernel launched immediately before the attention call (no other launch in between):
+    the attention kernel is a programmatic dependent of the absorb kernel and must not read q before that kernel
+    has completed. Repeated with fresh q so that a stale read would show."""
+    from rivoli_b200.layer import DsaDecodeLayer, KvbProjection
+    from tests.helpers import State, attend_close, make_geom
+    g0 = GLM
+    st = State(33, 3, [1500, 400, 129], top_k=256)
+    g = make_geom(be.DsaGeom, **st.geom_kw)
+    packed, scale, rng = _glm_weights(6)
+    B = st.B
+    want0 = st.oracle_step()                       # caches after the append
+    layer = DsaDecodeLayer(g, B, max_ctx=int(g.max_pages_per_seq * g.page_tokens))
+    layer.latent_pool.copy_(dev(want0["latent_pool"])); layer.latent_scale.copy_(dev(want0["latent_scale"]))
+    layer.upload_block_table(st.block_table)
+    proj = KvbProjection(g, B, dev(packed), dev(scale), g0["nope"], g0["vh"])
+    d_len = dev(st.seq_len)
+    stream = torch.cuda.Stream()
+    for rep in range(3):
+        q_heads = bf16_normal(rng, (B, g0["H"], g0["qh"]))
+        dq = dev(q_heads)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            q_abs = proj.absorb(dq, stream=stream)
+            out = layer.attend(q_abs, stream=stream, dense_len=d_len)
+        stream.synchronize()
+        layer.check_status(); be.kvb_proj_status()
+        got_q = q_abs.cpu().view(torch.int16).numpy().view(np.uint16)
+        _, o_f32, _, _ = orc.mla_attend_paged(st.og, got_q, want0["latent_pool"], want0["latent_scale"], st.block_table,
+                                              None, st.seq_len, want_f32=True)
+        ok, worst = attend_close(out.cpu().view(torch.int16).numpy().view(np.uint16), o_f32)
+        assert ok, (rep, worst)

@@ -209,3 +209,10 @@ def test_mla_attend_rejects_unsupported_kvl(be):
     guard(be, lambda: be.launch_attend(b, b, b, b, b, None, 0, 16, 512, 64, 4, 1.0, b, sc), 1001)
     be.device_sync()
     assert be.attend_scratch_floats(64, 512) == 16 * 64 * 514
+
+
+def test_mla_attend_takes_more_heads_than_one_block_holds(be):
+    """Any head count: 160 heads of width 512 + 64 do not fit one block's shared memory and are tiled over the
+    grid (the reference tiles heads in blocks of 16, crates/backend/kernels/attn.hip:119-130)."""
+    _attend_case(be, 0x0A5E1102, 160, 300, 512, 64)
+    _attend_case(be, 0x5F117BAD, 200, 90, 128, 16)
