@@ -38,34 +38,45 @@ class ContinuousBatcher:
         if r not in (None, 0):                                  # the oracle's pool returns codes
             raise be.BackendError("pagepool_reserve", int(r))
 
-    def admit(self, slot: int, context_len: int) -> int:
-        """Place a new request with ``context_len`` prefilled tokens in ``slot``; returns its id."""
+    def _evict(self, slot: int) -> None:
+        """Return the slot's pages and mark it empty (its bookkeeping never describes pages it no longer owns)."""
         if self.seq_id[slot] >= 0:
             self.pool.release(slot)
-        self._reserve(slot, context_len)
+        self.seq_id[slot] = -1
+        self.seq_len[slot] = 0
+
+    def _place(self, slot: int, context_len: int) -> int:
+        self._reserve(slot, context_len)                        # raises with the slot still marked empty
         self.seq_len[slot] = context_len
         self.seq_id[slot] = self._next_id
         self._next_id += 1
         return int(self.seq_id[slot])
 
+    def admit(self, slot: int, context_len: int) -> int:
+        """Place a new request with ``context_len`` prefilled tokens in ``slot``; returns its id. If the pool
+        cannot hold it the slot is left empty (1007 is raised)."""
+        self._evict(slot)
+        return self._place(slot, context_len)
+
     def begin_step(self):
         """Grow every live sequence by the token this step appends. Returns ``(row_pos, seq_len)``:
-        the position each slot writes (its old length) and the length after the append."""
-        live = self.seq_id >= 0
+        the position each slot writes (its old length) and the length after the append. A slot counts as
+        grown as soon as its page is reserved, so a failure part-way leaves lengths and pages in step."""
         row_pos = self.seq_len.copy()
-        for slot in np.nonzero(live)[0]:
+        for slot in np.nonzero(self.seq_id >= 0)[0]:
             self._reserve(int(slot), int(self.seq_len[slot]) + 1)
-        self.seq_len[live] += 1
+            self.seq_len[slot] += 1
         return row_pos, self.seq_len.copy()
 
     def finish(self, slots, new_context_lens) -> list[int]:
-        """Sequences in ``slots`` end: their pages go back to the free list and replacements with
-        the given prefilled context lengths take the slots (slot order). Returns the new ids."""
+        """Sequences in ``slots`` end and replacements with the given prefilled context lengths take their
+        slots. Every finishing slot returns its pages FIRST (slot order), then the replacements reserve (slot
+        order): near a full pool a replacement can use the pages of a slot that finishes later in the list,
+        and the order stays a pure function of the call. Returns the new ids."""
         order = np.argsort(np.asarray(slots), kind="stable")
-        ids = []
         for i in order:
-            ids.append(self.admit(int(slots[i]), int(new_context_lens[i])))
-        return ids
+            self._evict(int(slots[i]))
+        return [self._place(int(slots[i]), int(new_context_lens[i])) for i in order]
 
     def block_table(self) -> np.ndarray:
         return self.pool.block_table()

@@ -56,3 +56,25 @@ def test_pool_exhaustion_is_reported_not_hidden():
     with pytest.raises(be.BackendError) as e:
         a.admit(1, 128)                                                    # needs 2 pages, 1 left
     assert e.value.code == 1007
+
+
+def test_replacements_fit_at_pool_capacity_and_a_failed_admit_leaves_the_slot_empty():
+    """Three slots of two pages fill a six-page pool. Two finish and are replaced by a one-page and a three-page
+    request: that fits only because both finishing slots return their pages before either replacement reserves.
+    A request that cannot fit raises 1007 and leaves its slot empty rather than describing pages it gave back."""
+    build.build()
+    a = ContinuousBatcher(3, 6, 64 * 4, 64)
+    for s_ in range(3):
+        a.admit(s_, 128)
+    assert a.n_free == 0
+    a.finish([0, 2], [64 * 3, 64])                 # slot 0 needs 3 pages: its own 2 and one of slot 2's
+    assert a.n_free == 0 and a.seq_len.tolist() == [192, 128, 64]
+    bt = a.block_table()
+    live = bt[bt >= 0]
+    assert live.size == 6 and len(set(live.tolist())) == 6
+    with pytest.raises(be.BackendError) as e:
+        a.admit(1, 64 * 4)                         # 4 pages wanted, 2 come back
+    assert e.value.code == 1007
+    assert a.seq_id[1] == -1 and a.seq_len[1] == 0
+    row_pos, seq_len = a.begin_step()              # the empty slot does not grow
+    assert seq_len.tolist() == [193, 0, 65] and row_pos.tolist() == [192, 0, 64]
