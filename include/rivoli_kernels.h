@@ -156,7 +156,7 @@ int rivoli_index_topk_batched(const float* scores, int score_stride, const int32
 
 /* Fused indexer: q quantisation + scores + exact top-k in one call, on the tensor cores
  * where the geometry allows (index_dim 128, index_heads <= 32, 16 <= page_tokens <= 128,
- * score_stride <= 32768), otherwise through the three operators above. Replaces the chain
+ * score_stride <= 131072), otherwise through the three operators above. Replaces the chain
  * launch_index_score -> launch_index_topk (crates/backend/src/hip_attn.rs:457-495) for a
  * batch. The tensor-core scores are approximate; every token within a proven error band
  * of the k-th score is re-scored in the exact order of rivoli_index_score_paged before the

@@ -14,9 +14,9 @@
 //                               shared memory and consumed by tcgen05.mma kind::f8f6f4
 //                               (tokens = M 128, heads = N 32, dims = K 128), accumulators
 //                               in TMEM, scale/ReLU/head-weight epilogue from TMEM.
-//   3. index_select_refine_kernel  per sequence: locate the k-th approximate score A_k by bisection
-//                               over register-resident keys; every token with |a_t - A_k| <= 2*eps
-//                               (plus the bisection's residual width) is re-scored in
+//   3. index_select_cluster_kernel (index_select.cu)  per sequence, one thread-block cluster: locate
+//                               the bin of the k-th approximate score A_k with one histogram pass;
+//                               every token within 2*eps of that bin is re-scored in
 //                               the exact order (sequential f32 fold, identical to
 //                               rivoli_index_score_paged); tokens above the band are in,
 //                               below are out; the final exact top-k (ties -> lower index)
@@ -33,9 +33,8 @@
 #include "common.cuh"
 #include "quant.cuh"
 #include "tc_common.cuh"
+#include "index_select.hpp"
 #include "tmap.hpp"
-#include "topk_core.cuh"
-#include <type_traits>
 
 namespace {
 
@@ -329,287 +328,6 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
     if (tid == 0 && abort_flag) atomicCAS(A.err, 0, abort_flag);
 }
 
-// ---------------------------------------------------------------------------------------------
-// 3. per-sequence exact selection with band refinement
-// ---------------------------------------------------------------------------------------------
-constexpr int RF_LIST = 2048;      // band tokens re-scored per round
-
-
-// listed tokens a warp re-scores per pass: 4, or 2 where the key array leaves less shared memory
-__host__ __device__ constexpr int rf_tok(int ept) { return ept > 16 ? 2 : 4; }
-
-struct RefineArgs {
-    DsaGeom g;
-    const float* scores; int score_stride; const int32_t* seq_len;
-    const uint8_t* qcodes; const float* qscales; const float* w; const float* cb;
-    const uint8_t* index_pool; const float* index_scale; const int32_t* block_table;
-    uint32_t* rows; int32_t* n_sel; int k;
-    unsigned int* stats;   // [B][2]: band size, sure-in count (may be NULL)
-    int vec_ok;            // score rows and key scales allow 16-byte loads
-};
-
-template <int EPT>
-__global__ void __launch_bounds__(TK_THREADS)
-index_select_refine_kernel(RefineArgs A) {
-    // Thread t owns the EPT consecutive tokens t*EPT .. t*EPT+EPT-1 (keys in registers), so the
-    // score/scale loads are 16-byte vectors and the ascending write-out is one block-wide scan.
-    extern __shared__ __align__(16) uint32_t rf_smem[];
-    __shared__ TkSharedLite sh;
-    __shared__ uint32_t list_n, n_band_total;
-    const DsaGeom& g = A.g;
-    constexpr int hd = IM_HD;                      // mma_geometry_ok: index_dim == IM_HD (one code word per lane)
-    constexpr int TOK = rf_tok(EPT);               // listed tokens a warp re-scores per pass
-    const int nh = g.index_heads, P = g.page_tokens;
-    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    rv_grid_dep_trigger();   // the attention kernel may start converting its queries; it waits before reading rows
-    rv_grid_dep_wait();      // scores come from the kernel before
-    const int nt = min(A.seq_len[b], A.score_stride);
-    const int kk = min(A.k, nt);
-    uint32_t* out = A.rows + (size_t)b * A.k;
-    if (tid == 0) A.n_sel[b] = kk > 0 ? kk : 0;
-    if (kk <= 0) return;
-    if (kk == nt) {
-        for (int i = tid; i < nt; i += TK_THREADS) out[i] = (uint32_t)i;
-        if (tid == 0 && A.stats) { A.stats[b * 2] = 0; A.stats[b * 2 + 1] = (unsigned)nt; }
-        return;
-    }
-    // dynamic shared memory: qf[hd][32] | kf[32 warps][TOK tokens][hd] f32 | list | bkey | dec | keys[EPT*1024]
-    float* qf = reinterpret_cast<float*>(rf_smem);
-    float* kfw = qf + hd * 32;
-    uint32_t* list = reinterpret_cast<uint32_t*>(kfw + TK_WARPS * TOK * hd);
-    uint32_t* bkey = list + RF_LIST;               // exact keys of the listed tokens
-    uint32_t* dec = bkey + RF_LIST;                // 1 = the listed token is selected
-    uint32_t* keys = dec + RF_LIST;                // whole key array: tie-dominated (overflow) path only
-
-    // ---- approximate keys: (unscaled tensor-core score) * key scale of the token -------------------
-    const float* s = A.scores + (size_t)b * A.score_stride;
-    const int32_t* bt = A.block_table + (size_t)b * g.max_pages_per_seq;
-    const int i0 = tid * EPT;
-    const int nvalid = max(0, min(EPT, nt - i0));
-    float sc[EPT], sk[EPT];
-    if (A.vec_ok && nvalid == EPT) {
-        size_t r[EPT / 4];
-#pragma unroll
-        for (int j4 = 0; j4 < EPT / 4; ++j4) {
-            const int i = i0 + j4 * 4;
-            int pg = bt[i / P];
-            pg = (pg < 0 || pg >= g.n_pool_pages) ? 0 : pg;
-            r[j4] = (size_t)pg * P + (i & (P - 1));
-        }
-#pragma unroll
-        for (int j4 = 0; j4 < EPT / 4; ++j4) {
-            const float4 a = *reinterpret_cast<const float4*>(s + i0 + j4 * 4);
-            const float4 c = *reinterpret_cast<const float4*>(A.index_scale + r[j4]);
-            sc[j4 * 4] = a.x; sc[j4 * 4 + 1] = a.y; sc[j4 * 4 + 2] = a.z; sc[j4 * 4 + 3] = a.w;
-            sk[j4 * 4] = c.x; sk[j4 * 4 + 1] = c.y; sk[j4 * 4 + 2] = c.z; sk[j4 * 4 + 3] = c.w;
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-            const int i = i0 + j;
-            sc[j] = 0.0f; sk[j] = 0.0f;
-            if (j < nvalid) {
-                int pg = bt[i / P];
-                pg = (pg < 0 || pg >= g.n_pool_pages) ? 0 : pg;
-                sc[j] = s[i];
-                sk[j] = A.index_scale[(size_t)pg * P + (i & (P - 1))];
-            }
-        }
-    }
-    // q codes as f32, transposed to [dim][head] (lane = head on both sides: no bank conflicts)
-    for (int e = tid; e < 32 * (hd / 4); e += TK_THREADS) {
-        const int h = e & 31, d4 = e >> 5;
-        const uint32_t cw = h < nh ? *reinterpret_cast<const uint32_t*>(A.qcodes + ((size_t)b * nh + h) * hd + d4 * 4) : 0u;
-        const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw >> 16));
-        qf[(d4 * 4 + 0) * 32 + h] = x.x; qf[(d4 * 4 + 1) * 32 + h] = x.y;
-        qf[(d4 * 4 + 2) * 32 + h] = y.x; qf[(d4 * 4 + 3) * 32 + h] = y.y;
-    }
-    if (tid == 0) { list_n = 0; n_band_total = 0; }
-    uint32_t key[EPT];
-    float skm = 0.0f;
-#pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-        key[j] = j < nvalid ? topk_key(sc[j] * sk[j]) : 0u;
-        skm = fmaxf(skm, sk[j]);
-    }
-    int buf = 0;
-    const float sk_max = __uint_as_float(tk_block_max(__float_as_uint(skm), sh, buf));   // also orders qf / list_n
-    const float eps = sk_max * A.cb[b];
-
-    // k-th largest approximate score, located to 20 key bits: A_k lies in [T, T + 0xfff]
-    const uint32_t T20 = tk_bisect<EPT>(key, (uint32_t)kk, 20, sh, buf);
-    const float lo_f = topk_unkey(T20) - 2.0f * eps, hi_f = topk_unkey(T20 | 0xfffu) + 2.0f * eps;
-    const uint32_t k_lo = lo_f == lo_f ? topk_key(lo_f) : 0u;
-    const uint32_t k_hi = hi_f == hi_f ? topk_key(hi_f) : 0xffffffffu;
-
-    // classify from registers: surely selected / band (re-scored exactly) / surely not
-    uint32_t m_in = 0u, m_band = 0u;
-#pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-        if (j < nvalid) {
-            if (key[j] > k_hi) m_in |= 1u << j;
-            else if (key[j] >= k_lo) m_band |= 1u << j;
-        }
-    }
-    const uint32_t n_in = tk_block_sum((uint32_t)__popc(m_in), sh, buf);
-    // list positions: one shared-memory atomic per warp, order inside the list is irrelevant
-    uint32_t my_pos;
-    {
-        const uint32_t cnt = (uint32_t)__popc(m_band);
-        uint32_t incl = cnt;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += t;
-        }
-        uint32_t wbase = 0u;
-        if (lane == 31 && incl) wbase = atomicAdd(&list_n, incl);
-        wbase = __shfl_sync(0xffffffffu, wbase, 31);
-        my_pos = wbase + incl - cnt;
-        uint32_t pos = my_pos;
-#pragma unroll
-        for (int j = 0; j < EPT; ++j)
-            if (m_band & (1u << j)) { if (pos < RF_LIST) list[pos] = (uint32_t)(i0 + j); ++pos; }
-    }
-    __syncthreads();
-    const uint32_t n_band = list_n;
-
-    // this lane's head constants for the exact re-score (nh <= 32)
-    const float my_sq = lane < nh ? A.qscales[(size_t)b * nh + lane] : 0.0f;
-    const float my_wh = lane < nh ? __fmul_rn(A.w[(size_t)b * nh + lane], g.index_wscale) : 0.0f;
-
-    // exact score of listed tokens: a pass covers 32*TOK of them, warp w taking positions
-    // base + w, base + 32 + w, ... (an even split; their loads are in flight together and they
-    // share the q reads): lane = head; the code dot is the sequential f32 fold of
-    // rivoli_index_score_paged, heads fold ascending. Writes the exact key by list position
-    // (and into keys[] when asked).
-    auto rescore = [&](uint32_t ln, bool to_keys) {
-        float* kf = kfw + warp * (TOK * hd);
-        for (uint32_t base = 0; base < ln; base += TK_WARPS * TOK) {
-            if (base + warp >= ln) break;
-            const int n_here = min(TOK, (int)((ln - base - warp + TK_WARPS - 1) / TK_WARPS));   // warp-uniform, >= 1
-            uint32_t cw[TOK];
-            float skv[TOK];
-#pragma unroll
-            for (int e = 0; e < TOK; ++e) {
-                cw[e] = 0u; skv[e] = 0.0f;
-                if (e < n_here) {
-                    const int t = (int)list[base + e * TK_WARPS + warp];
-                    int pg = bt[t / P];
-                    pg = (pg < 0 || pg >= g.n_pool_pages) ? 0 : pg;
-                    const size_t r = (size_t)pg * P + (t & (P - 1));
-                    cw[e] = *reinterpret_cast<const uint32_t*>(A.index_pool + r * hd + lane * 4);
-                    skv[e] = A.index_scale[r];
-                }
-            }
-#pragma unroll
-            for (int e = 0; e < TOK; ++e) {
-                const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw[e] & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw[e] >> 16));
-                *reinterpret_cast<float4*>(kf + e * hd + lane * 4) = make_float4(x.x, x.y, y.x, y.y);
-            }
-            __syncwarp();
-            float cd[TOK];
-#pragma unroll
-            for (int e = 0; e < TOK; ++e) cd[e] = 0.0f;
-            auto fold = [&](auto ntok) {
-                constexpr int NT = decltype(ntok)::value < TOK ? decltype(ntok)::value : TOK;
-#pragma unroll 4
-                for (int d = 0; d < hd; d += 4) {
-                    const float q0f = qf[(d + 0) * 32 + lane], q1f = qf[(d + 1) * 32 + lane];
-                    const float q2f = qf[(d + 2) * 32 + lane], q3f = qf[(d + 3) * 32 + lane];
-#pragma unroll
-                    for (int e = 0; e < NT; ++e) {
-                        const float4 k4 = *reinterpret_cast<const float4*>(kf + e * hd + d);   // broadcast read
-                        cd[e] = fmaf(q0f, k4.x, cd[e]);
-                        cd[e] = fmaf(q1f, k4.y, cd[e]);
-                        cd[e] = fmaf(q2f, k4.z, cd[e]);
-                        cd[e] = fmaf(q3f, k4.w, cd[e]);
-                    }
-                }
-            };
-            if (n_here >= TOK) fold(std::integral_constant<int, TOK>{});
-            else if (n_here == 1) fold(std::integral_constant<int, 1>{});
-            else if (n_here == 2) fold(std::integral_constant<int, 2>{});
-            else fold(std::integral_constant<int, 3>{});
-            __syncwarp();
-#pragma unroll
-            for (int e = 0; e < TOK; ++e) {
-                const float dot = __fmul_rn(__fmul_rn(cd[e], my_sq), skv[e]);
-                float rr = __fmul_rn(dot, g.index_dscale);
-                rr = rr > 0.0f ? rr : 0.0f;
-                kf[e * hd + lane] = __fmul_rn(my_wh, rr);
-            }
-            __syncwarp();
-            if (lane < n_here) {
-                float acc = 0.0f;
-                for (int h = 0; h < nh; ++h) acc = __fadd_rn(acc, kf[lane * hd + h]);
-                uint32_t ku = topk_key(acc);
-                ku = ku == 0xffffffffu ? 0xfffffffeu : (ku == 0u ? 1u : ku);
-                const uint32_t q2 = base + lane * TK_WARPS + warp;
-                bkey[q2] = ku;
-                if (to_keys) keys[list[q2]] = ku;
-            }
-            __syncwarp();
-        }
-    };
-
-    if (n_band <= RF_LIST) {
-        // Common case: the whole band sits in list/bkey. Rank each band token among the band by
-        // (exact key descending, index ascending); the selection takes the (kk - n_in) best.
-        rescore(n_band, false);
-        __syncthreads();
-        const uint32_t take = (uint32_t)kk - n_in;   // >= 1: at most kk - 1 tokens lie above the band
-        for (uint32_t q2 = warp; q2 < n_band; q2 += TK_WARPS) {
-            const uint32_t kq = bkey[q2], tq = list[q2];
-            uint32_t c = 0;
-            for (uint32_t j2 = lane; j2 < n_band; j2 += 32) {
-                const uint32_t kj = bkey[j2];
-                c += (kj > kq || (kj == kq && list[j2] < tq)) ? 1u : 0u;
-            }
-            c = __reduce_add_sync(0xffffffffu, c);
-            if (lane == 0) dec[q2] = c < take ? 1u : 0u;
-        }
-        __syncthreads();
-        uint32_t pos = my_pos;
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-            uint32_t u = (m_in >> j) & 1u;
-            if (m_band & (1u << j)) { u = dec[pos]; ++pos; }
-            key[j] = u ? 0xffffffffu : 0u;
-        }
-        tk_compact_contig<EPT>(key, nt, 0xfffffffeu, 0u, sh, out);
-        if (tid == 0 && A.stats) { A.stats[b * 2] = n_band; A.stats[b * 2 + 1] = n_in; }
-        return;
-    }
-    // Rare case (tie-dominated scores): the band does not fit the list. The key array goes to
-    // shared memory (sure-in = max key, sure-out = 0), the band is re-scored in token chunks of
-    // RF_LIST (so a chunk's band always fits), then an exact selection runs over the whole array.
-#pragma unroll
-    for (int j = 0; j < EPT; ++j)
-        if (j < nvalid) keys[i0 + j] = ((m_in >> j) & 1u) ? 0xffffffffu : 0u;
-    for (int c0 = 0; c0 < nt; c0 += RF_LIST) {
-        __syncthreads();
-        if (tid == 0) list_n = 0;
-        __syncthreads();
-        if (i0 >= c0 && i0 < c0 + RF_LIST) {
-#pragma unroll
-            for (int j = 0; j < EPT; ++j)
-                if (m_band & (1u << j)) list[atomicAdd(&list_n, 1u)] = (uint32_t)(i0 + j);
-        }
-        __syncthreads();
-        const uint32_t ln = list_n;
-        rescore(ln, true);
-        if (tid == 0) n_band_total += ln;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < EPT; ++j) key[j] = j < nvalid ? keys[i0 + j] : 0u;
-    const uint32_t pivot = tk_bisect<EPT>(key, (uint32_t)kk, 32, sh, buf);
-    const uint32_t need = (uint32_t)kk - tk_count_gt<EPT>(key, pivot, sh, buf);
-    tk_compact_contig<EPT>(key, nt, pivot, need, sh, out);
-    if (tid == 0 && A.stats) { A.stats[b * 2] = n_band_total; A.stats[b * 2 + 1] = 0; }
-}
-
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct SelectScratch {
@@ -631,11 +349,11 @@ SelectScratch carve(const DsaGeom* g, int B, int score_stride, void* scratch, si
     return s;
 }
 
-constexpr int RF_MAX_NT = 32 * 1024;   // keys 128 KiB + q 16 + key rows 32 + lists 24 = 200 KiB < 227 KiB
+constexpr int SEL_MAX_NT = 8 * 512 * 32;   // what one cluster of the selection kernel covers
 
 bool mma_geometry_ok(const DsaGeom* g, int score_stride) {
     return g->index_dim == IM_HD && g->index_heads <= IM_NPAD && g->page_tokens >= 16 && g->page_tokens <= IM_TILE &&
-           score_stride <= RF_MAX_NT;
+           score_stride <= SEL_MAX_NT;
 }
 
 }  // namespace
@@ -717,22 +435,10 @@ static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* i
     rv_launch_dependent(index_score_mma_kernel, dim3(grid), dim3(IM_THREADS), smem1, st, ma, tm_keys, tm_q);
     if (int e = rv_launch_status()) return e;
 
-    RefineArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb,
-                  index_pool, index_scale, block_table, rows, n_sel, g->top_k, s.stats,
-                  (score_stride % 4 == 0 && ((uintptr_t)index_scale & 15) == 0 && g->page_tokens % 4 == 0) ? 1 : 0};
-#define RV_REFINE(EPT)                                                                                            \
-    do {                                                                                                          \
-        const size_t smem2 = ((size_t)(EPT) * TK_THREADS + (size_t)hd * 32 + (size_t)TK_WARPS * rf_tok(EPT) * hd +\
-                              3 * RF_LIST) * 4;                                                                   \
-        cudaFuncSetAttribute(index_select_refine_kernel<EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
-                             (int)smem2);                                                                         \
-        rv_launch_dependent(index_select_refine_kernel<EPT>, dim3(B), dim3(TK_THREADS), smem2, st, ra);           \
-    } while (0)
-    if (score_stride <= 8 * TK_THREADS) RV_REFINE(8);
-    else if (score_stride <= 16 * TK_THREADS) RV_REFINE(16);
-    else RV_REFINE(32);
-#undef RV_REFINE
-    return rv_launch_status();
+    const SelArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb,
+                     index_pool, index_scale, block_table, rows, n_sel, g->top_k, s.stats,
+                     (score_stride % 4 == 0 && ((uintptr_t)index_scale & 15) == 0 && g->page_tokens % 4 == 0) ? 1 : 0};
+    return rivoli::launch_index_select_cluster(ra, B, st);
 }
 
 RIVOLI_API int rivoli_index_select_paged(const DsaGeom* g, const uint16_t* index_q, const float* w,
