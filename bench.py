@@ -4,15 +4,19 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1|cfg4|cfg5|v4]
 
 A layer-step = append one token per sequence -> indexer q quant + score + exact top-k ->
-gather/dequant + MLA attention -> bf16 out, over the whole per-GPU batch. Default workload
-is the sparse DSA decode layer (batch 128 x context 16384, top-k 2048, 64-token pages
-scattered over a pool 1.25x the live set). With N > 1 every rank runs the same per-GPU
-batch on its own sequences (weak scaling, no collective on the data path); the value is the
-aggregate over ranks, timed on the device and reduced with MAX over ranks.
+gather/dequant + MLA attention -> bf16 out, over the whole batch. Default workload is the sparse DSA decode
+layer the metric is quoted on (batch 128 x context 16384, top-k 2048, 64-token pages scattered over a pool 1.25x
+the live set). With N > 1 (one process per GPU under torchrun) the batch of 128 is sharded by sequence over the
+ranks - 128 / N sequences each, no collective on the data path: STRONG scaling - and the value is whole-batch
+layer-steps/s, timed on the device and reduced with MAX over ranks. The same line then also carries, under
+`weak_scaling`, the figure with 128 sequences on every rank, and, under `cfg4`, the long-context case (batch 4 x
+context 131,072 sharded by page range, two NCCL all-gathers per step inside the library).
 
-Prints ONE JSON line on rank 0. `--workload cfg5` (continuous batching with churn) and `--workload v4` (the V4
-cousin path: block scorer + selection rows + sparse MQA attention with sink) are one-GPU measurements of the CUDA
-arm that print the same kind of line; they are not the headline metric.
+The timed region is R back-to-back repetitions of the K-step loop inside one CUDA-event pair (R sized for at least
+0.25 s), so the clock sampler has samples inside it. Before timing, one step at the benchmark's own size is checked
+against the oracle on two sampled sequences. Prints ONE JSON line on rank 0. `--workload cfg5` (continuous batching
+with churn, one 32-sequence slice per rank) and `--workload v4` (the V4 cousin path) print the same kind of line;
+they are not the headline metric.
 """
 from __future__ import annotations
 
@@ -34,9 +38,9 @@ WORKLOADS = {
     "cfg1": dict(B=1, ctx=257, n_heads=16, index_heads=8, index_dim=64, page_tokens=16, top_k=64, seed=0),
     "cfg2": dict(B=32, ctx=2048, n_heads=64, index_heads=32, index_dim=128, page_tokens=64, top_k=2048, seed=1),
     "cfg3": dict(B=128, ctx=16384, n_heads=64, index_heads=32, index_dim=128, page_tokens=64, top_k=2048, seed=2),
-    # continuous batching with churn: 78 layers, 32 sequences per GPU (256 over 8 GPUs), ragged contexts; the upper
-    # bound leaves a sequence 128 tokens to grow inside the 32,768-token limit of the tensor-core selection
-    "cfg5": dict(B=32, ctx_lo=512, ctx_hi=32640, layers=78, n_heads=64, index_heads=32, index_dim=128, page_tokens=64,
+    # continuous batching with churn: 78 layers, 32 sequences per GPU (256 over 8 GPUs), ragged contexts U[512, 32768]
+    # (pools and tables leave every sequence 64 tokens to grow)
+    "cfg5": dict(B=32, ctx_lo=512, ctx_hi=32768, layers=78, n_heads=64, index_heads=32, index_dim=128, page_tokens=64,
                  top_k=2048, seed=4),
     # long context, page-range sharded: every rank holds 1/N of every sequence's pages; candidates and partial
     # attention outputs are exchanged (NCCL all-gather) and merged; needs --gpus >= 2 under torchrun
@@ -47,20 +51,26 @@ WORKLOADS = {
                ratio=4, seed=5),
 }
 KV_LORA, ROPE = 512, 64
-# dram__bytes_read.sum + dram__bytes_write.sum per sequence of the cfg3 shape, from the ncu capture
-# summarised in profiles/dram_traffic_hot_kernels_cfg3.md (stage totals / 128 sequences)
-TRAFFIC_PER_SEQ = {"index_select": (1.32 + 269.16 + 5.3 + 19.12) * 1e6 / 128, "attend": (184.81 + 0.7) * 1e6 / 128}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch and per sequence of the cfg3 shape, from ncu captures of
+# these kernels at batch 32 (traffic grows in proportion to the sequences a launch processes; a full launch is the
+# per-sequence figure x the batch): profiles/ncu_hot_kernels_cfg3_batch32.md
+TRAFFIC_PER_SEQ = {"index_score_mma_kernel": 269.16e6 / 128, "attend_mma_kernel": 185.51e6 / 128,
+                   "index_select_cluster_kernel": 19.12e6 / 128, "step_prologue_kernel": 1.32e6 / 128}
+TRAFFIC_SOURCE = "ncu dram read+write of one launch at batch 32 of the cfg3 shape, per sequence x batch (profiles/ncu_hot_kernels_cfg3_batch32.md)"
 METRIC = "DSA decode layer-steps/s (batch×ctx)"
 
 
-def config_of(name, w, world):
+def config_of(name, w, world, B_rank, scaling):
     """The `config` object of the JSON line; both arms print the same one."""
-    B, ctx = w["B"], w["ctx"]
-    return {"workload": f"{name}: batch {B}/GPU x ctx {ctx}, top-k {w['top_k']}, "
+    ctx = w["ctx"]
+    total = B_rank * world
+    how = (f"batch {total} in total, {B_rank} per GPU (sharded by sequence, no collective)" if scaling == "strong" and world > 1
+           else f"batch {B_rank}/GPU")
+    return {"workload": f"{name}: {how} x ctx {ctx}, top-k {w['top_k']}, "
                         f"{w['page_tokens']}-token pages scattered in a 1.25x pool, seed {w['seed']}",
-            "l2": "inputs larger than L2 (index keys + latents >> 126 MB)" if B * ctx * 132 > 2e8
+            "l2": "inputs larger than L2 (index keys + latents >> 126 MB)" if B_rank * ctx * 132 > 2e8
                   else "working set fits L2: latency-bound config",
-            "sequences_per_step": B * world}
+            "sequences_per_step": total}
 
 
 def algorithmic_bytes(w):
@@ -74,10 +84,24 @@ def algorithmic_bytes(w):
     return dict(append=append, index=index, attend=attend)
 
 
+def kernel_bytes(w):
+    """Per-sequence algorithmic bytes of each KERNEL of the fused step (what it must read and write once)."""
+    nt, k, H, nh, hd = w["ctx"], w["top_k"], w["n_heads"], w["index_heads"], w["index_dim"]
+    n_sel = min(k, nt)
+    W = KV_LORA + ROPE
+    return {"step_prologue_kernel": W * 2 + hd * 2 + 4 + W + 4 + hd + 4 + nh * hd * 2 + nh * 4,
+            "index_score_mma_kernel": nt * hd + nh * hd,                 # key codes + query codes (scores are not counted)
+            "index_select_cluster_kernel": nt * 4 + n_sel * 4,           # key scales + rows out
+            "attend_mma_kernel": n_sel * (W + 4) + H * W * 2 + n_sel * 4 + H * KV_LORA * 2}
+
+
 def algorithmic_flops(w):
     nt, k, H, nh, hd = w["ctx"], w["top_k"], w["n_heads"], w["index_heads"], w["index_dim"]
     n_sel = min(k, nt)
     return dict(index=2 * nh * hd * nt, attend=2 * H * n_sel * (KV_LORA + ROPE + KV_LORA))
+
+
+KERNELS = ["step_prologue_kernel", "index_score_mma_kernel", "index_select_cluster_kernel", "attend_mma_kernel"]
 
 
 class ClockSampler:
@@ -90,7 +114,7 @@ class ClockSampler:
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, gpu_index: int):
-        self.idx, self.proc, self.samples, self.marks = gpu_index, None, [], []
+        self.idx, self.proc, self.samples, self.marks, self.extra = gpu_index, None, [], [], []
         self.stop_flag, self.h, self.nv, self.t, self.max_mhz = False, None, None, None, None
 
     def _physical_index(self):
@@ -131,6 +155,12 @@ class ClockSampler:
         while not self.stop_flag:
             try:
                 mhz = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                if i % 16 == 0:
+                    try:
+                        self.extra.append((time.perf_counter(), float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_MEM)),
+                                           nv.nvmlDeviceGetPowerUsage(h) / 1000.0))
+                    except Exception:
+                        pass
                 if i % 4 == 0:          # the reasons query is the slower of the two
                     try:
                         mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
@@ -178,10 +208,15 @@ class ClockSampler:
         mask = 0
         for s in use:
             mask |= s[2]
-        return {"sm_mhz": float(np.median([s[1] for s in use])), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(n for b, n in self.REASONS.items() if mask & b),
-                "samples": len(use), "samples_in_timed_region": len(inside),
-                "source": "nvml" if self.nv else "nvidia-smi"}
+        out = {"sm_mhz": float(np.median([s[1] for s in use])), "sm_max_mhz": self.max_mhz,
+               "reasons": sorted(n for b, n in self.REASONS.items() if mask & b),
+               "samples": len(use), "samples_in_timed_region": len(inside),
+               "source": "nvml" if self.nv else "nvidia-smi"}
+        ex = [e for e in self.extra if lo is not None and hi is not None and lo <= e[0] <= hi]
+        if ex:
+            out["mem_mhz"] = float(np.median([e[1] for e in ex]))
+            out["power_w_max"] = float(max(e[2] for e in ex))
+        return out
 
 
 def build_layer(w, device, seed):
@@ -233,6 +268,164 @@ def step_inputs(w, device, gen, pinned=False):
     return d
 
 
+def self_check(layer, g, w, x, row_pos, seq_len, seqs):
+    """Parity of ONE step at the benchmark's own size, outside any timed region: for the sampled sequences the
+    oracle runs the same step on a copy of their pages (append, scores, exact top-k, attention) and the GPU's
+    appended codes and scales, selected rows (bit for bit) and attention output (2e-2 relative / 1e-3 absolute,
+    elementwise) must agree. The pages are copied BEFORE the step; the step itself is the timed call."""
+    import torch
+    from oracle import oracle as orc
+    from oracle.workload import attend_close, make_geom
+    P, W, hd = g.page_tokens, KV_LORA + ROPE, g.index_dim
+    n_pages = (int(seq_len.max().item()) + P - 1) // P
+    seqs = list(seqs)
+    pages = layer.block_table[seqs, :n_pages].long().reshape(-1)                   # device
+    take = lambda pool, width: pool.view(g.n_pool_pages, P * width)[pages].cpu().numpy().reshape(-1)
+    lp, ls = take(layer.latent_pool, W), layer.latent_scale.view(g.n_pool_pages, P)[pages].cpu().numpy().reshape(-1)
+    ip, isc = take(layer.index_pool, hd), layer.index_scale.view(g.n_pool_pages, P)[pages].cpu().numpy().reshape(-1)
+    n = len(seqs)
+    bt = np.arange(n * n_pages, dtype=np.int32).reshape(n, n_pages)
+    og = make_geom(orc.Geom, n_heads=g.n_heads, index_heads=g.index_heads, index_dim=hd, page_tokens=P, top_k=g.top_k,
+                   max_pages_per_seq=n_pages, n_pool_pages=n * n_pages)
+    u16 = lambda t: t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+    rp, sl = row_pos[seqs].cpu().numpy(), seq_len[seqs].cpu().numpy()
+    assert orc.kv_append_paged(og, u16(x["latent"][seqs]), u16(x["index_key"][seqs]), None, rp, bt, lp, ls, ip, isc) == 0
+    qc, qs = orc.index_q_quant(u16(x["index_q"][seqs]), hd)
+    sc = orc.index_score_paged(og, qc, qs, x["index_w"][seqs].cpu().numpy(), ip, isc, bt, sl, int(sl.max()))
+    rows, n_sel = orc.index_topk_batched(sc, sl, g.top_k)
+    _, want, _, _ = orc.mla_attend_paged(og, u16(x["q"][seqs]), lp, ls, bt, rows, n_sel, want_f32=True)
+    out = layer.step(x["latent"], x["index_key"], x["index_q"], x["index_w"], x["q"], row_pos, seq_len)
+    torch.cuda.synchronize(layer.dev)
+    layer.check_status()
+    assert np.array_equal(take(layer.latent_pool, W), lp), "appended latent codes differ from the oracle"
+    assert np.array_equal(layer.latent_scale.view(g.n_pool_pages, P)[pages].cpu().numpy().reshape(-1).view(np.uint32), ls.view(np.uint32))
+    assert np.array_equal(take(layer.index_pool, hd), ip), "appended index codes differ from the oracle"
+    got_rows = layer.rows[seqs].cpu().numpy().view(np.uint32)
+    for i in range(n):
+        assert int(layer.n_sel[seqs[i]].item()) == int(n_sel[i])
+        assert np.array_equal(got_rows[i, :n_sel[i]], rows[i, :n_sel[i]]), "selected rows differ from the oracle"
+    ok, worst = attend_close(u16(out[seqs]), want)
+    assert ok, f"attention outside 2e-2 rel / 1e-3 abs (worst err/tol {worst:.2f})"
+    return {"sequences": seqs, "codes_scales_rows": "bit-exact", "attention_worst_err_over_tol": round(worst, 3)}
+
+
+def timed_steps(step, K, R, barrier, device):
+    """R back-to-back repetitions of the K-step loop inside ONE event pair (the timed region is then long enough
+    for the clock sampler to see it); returns milliseconds per step over all R * K steps."""
+    import torch
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(R):
+        for _ in range(K):
+            step()
+    t1.record()
+    barrier()
+    return t0.elapsed_time(t1) / (R * K)
+
+
+def kernel_times(layer, step, n, device):
+    """Average duration of each kernel of the fused step over n steps, from CUDA events the library records between
+    its launches (rivoli_dsa_step_set_timing_events) on the launching stream. Outside the `value` region: the records
+    serialise the kernels, which `value` keeps overlapped."""
+    import torch
+    from rivoli_b200 import backend as be
+    sets = []
+    for _ in range(n):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        for e in ev:
+            e.record()                     # creates the handles
+        sets.append(ev)
+    torch.cuda.synchronize(device)
+    for ev in sets:
+        be.step_set_timing_events(ev)
+        step()
+    be.step_set_timing_events(None)
+    torch.cuda.synchronize(device)
+    return {k: float(np.mean([ev[i].elapsed_time(ev[i + 1]) for ev in sets])) for i, k in enumerate(KERNELS)}
+
+
+def measure_layer(w, B, device, seed, args, barrier, sampler=None, check=False, e2e=True):
+    """Builds the workload with B sequences on this GPU and measures: device-resident ms/step (fused call), per-kernel
+    times, end-to-end ms/step through the host-buffer pipeline."""
+    import torch
+    from rivoli_b200.layer import HostStepPipeline
+    wB = dict(w, B=B)
+    g, layer, gen = build_layer(wB, device, seed)
+    ctx = w["ctx"]
+    x = step_inputs(wB, device, gen)
+    row_pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=device)
+    seq_len = torch.full((B,), ctx, dtype=torch.int32, device=device)
+    res = {"B": B}
+    if check:
+        res["self_check"] = self_check(layer, g, wB, x, row_pos, seq_len, sorted({0, B - 1}))
+
+    def step():
+        # the call a device-resident caller makes: ONE library call, 4 launches (append + query prologue, scorer,
+        # selection, tensor-core attention; the short-context attention arm is not launched: the scheduler's
+        # lower bound on the context says no sequence needs it)
+        layer.step(x["latent"], x["index_key"], x["index_q"], x["index_w"], x["q"], row_pos, seq_len, min_rows_hint=hint)
+
+    hint = min(w["top_k"], ctx)            # what a scheduler knows: every sequence of this batch attends that many rows
+    W_ = max(args.warmup, 3)
+    for _ in range(W_):
+        step()
+    barrier()
+    layer.check_status()
+    # size the repetitions so that the timed region is at least 0.25 s
+    t_est = timed_steps(step, 10, 1, barrier, device)
+    R = args.reps or max(1, int(np.ceil(250.0 / max(t_est * args.steps, 1e-3))))
+    if sampler:
+        sampler.start()
+        time.sleep(0.05)
+        sampler.mark()
+    res["ms"] = timed_steps(step, args.steps, R, barrier, device)
+    if sampler:
+        sampler.mark()
+    res["reps"] = R
+    res["kernel_ms"] = kernel_times(layer, step, min(args.steps, 50), device)
+    barrier()
+    layer.check_status()
+    if e2e:
+        # end to end through the host-facing call: one packed pinned input buffer up, the bf16 output down, every step
+        xh = step_inputs(wB, device, gen, pinned=True)
+        pipe = HostStepPipeline(layer, depth=2, min_rows_hint=hint)
+        packed = [pipe.pack(xh), pipe.pack(xh)]
+        outs_h = [pipe.new_output_buffer() for _ in range(2)]
+        torch.cuda.synchronize(device)
+        i_ = [0]
+
+        def e2e_step():
+            pipe.submit(packed[i_[0] & 1], outs_h[i_[0] & 1], row_pos, seq_len)
+            i_[0] += 1
+
+        for _ in range(4):
+            e2e_step()
+        pipe.drain()
+        barrier()
+        n_e2e = args.steps * max(1, R // 4)
+        t0 = time.perf_counter()          # host clock around a fully drained pipeline: submit never blocks, drain does
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        s_up = torch.cuda.ExternalStream(pipe.pipe.stream(0), device=device)
+        s_down = torch.cuda.ExternalStream(pipe.pipe.stream(2), device=device)
+        e0.record(s_up)
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record(s_down)                 # after the last download: every earlier leg precedes it
+        pipe.drain()
+        res["e2e_wall_ms"] = (time.perf_counter() - t0) * 1e3 / n_e2e
+        res["e2e_ms"] = e0.elapsed_time(e1) / n_e2e
+        res["e2e_legs_ms"] = pipe.leg_ms()
+        res["h2d"] = pipe.pipe.input_bytes
+        res["d2h"] = pipe.pipe.output_bytes
+        barrier()
+        layer.check_status()
+        del pipe
+    del layer
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -247,141 +440,94 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     be.lib()
     w = WORKLOADS[args.workload]
-    g, layer, gen = build_layer(w, device, w["seed"] + 1000 * rank)
-    B, ctx = w["B"], w["ctx"]
-    x = step_inputs(w, device, gen)
-    row_pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=device)
-    seq_len = torch.full((B,), ctx, dtype=torch.int32, device=device)
-
-    def step(inp):
-        # the call a device-resident caller makes: 4 launches (append + query prologue, scorer,
-        # selection, attention)
-        layer.step(inp["latent"], inp["index_key"], inp["index_q"], inp["index_w"], inp["q"], row_pos, seq_len)
-
-    def step_staged(inp, ev):
-        # the same work through the three separate operators, with an event between stages
-        ev[0].record()
-        layer.append(inp["latent"], inp["index_key"], row_pos)
-        ev[1].record()
-        layer.select(inp["index_q"], inp["index_w"], seq_len)
-        ev[2].record()
-        layer.attend(inp["q"])
-        ev[3].record()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    for _ in range(max(args.warmup, 3)):
-        step(x)
-    barrier()
-    layer.check_status()
-
-    # ---- device-resident timing --------------------------------------------------------------------
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    sampler.mark()
-    t0.record()
-    for i in range(args.steps):
-        step(x)
-    t1.record()
-    barrier()
-    sampler.mark()
-    ms_total = t0.elapsed_time(t1)
-    # per-stage durations (for the roofline objects): separate operator calls, outside the timed region
-    n_st = min(args.steps, 100)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_st)]
-    for i in range(n_st):
-        step_staged(x, evs[i])
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    stage_ms = [float(np.mean([e[i].elapsed_time(e[i + 1]) for e in evs])) for i in range(3)]
-
-    # ---- end to end through the host-facing call: pinned host inputs, device->host result ------------
-    # HostStepPipeline.submit is the call a host-resident caller makes: per step it uploads the step's
-    # inputs, runs the three operators and downloads the attention output (three streams, two slots).
-    from rivoli_b200.layer import HostStepPipeline
-    xh = step_inputs(w, device, gen, pinned=True)
-    pipe = HostStepPipeline(layer, depth=2)
-    outs_h = [torch.empty((B, w["n_heads"], KV_LORA), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-
-    def e2e_step(i):
-        pipe.submit(xh, outs_h[i & 1], row_pos, seq_len)
-
-    for i in range(4):
-        e2e_step(i)
-    pipe.drain()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(pipe.s_up)
-    for i in range(args.steps):
-        e2e_step(i)
-    e1.record(pipe.s_down)               # after the last download: every earlier leg precedes it
-    pipe.drain()
-    barrier()
-    layer.check_status()
-    ms_e2e = e0.elapsed_time(e1)
-    h2d = int(sum(v.numel() * v.element_size() for v in xh.values()))
-    d2h = int(outs_h[0].numel() * outs_h[0].element_size())
-
-    if world > 1:
-        t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
+    def max_over_ranks(vals):
+        if world == 1:
+            return [float(v) for v in vals]
+        t = torch.tensor(vals, device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, ms_e2e = float(t[0]), float(t[1])
+        return [float(v) for v in t]
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    # The configuration the metric is quoted on: the workload's batch IN TOTAL, sharded by sequence over the ranks
+    # (strong scaling; at N = 1 that is the whole batch on one GPU). Sequences that do not divide evenly go to the
+    # lower ranks.
+    base, rem = divmod(w["B"], world)
+    B_rank = base + (1 if rank < rem else 0)
+    strong = measure_layer(w, max(B_rank, 1), device, w["seed"] + 1000 * rank, args, barrier, sampler, check=(rank == 0))
+    clocks = sampler.stop() if sampler else None
+    ms, ms_e2e, ms_e2e_wall = max_over_ranks([strong["ms"], strong["e2e_ms"], strong["e2e_wall_ms"]])
+    weak = None
+    if world > 1:
+        # secondary figure: the same per-GPU batch on every rank (weak scaling, N independent replicas)
+        wk = measure_layer(w, w["B"], device, w["seed"] + 1000 * rank, args, barrier, None, check=False, e2e=False)
+        weak_ms, = max_over_ranks([wk["ms"]])
+        weak = {"scaling": "weak", "value": world * 1e3 / weak_ms, "unit": "layer-steps/s", "ms_per_step": weak_ms,
+                "sequences_per_step": w["B"] * world,
+                "what": f"every rank runs the whole batch of {w['B']} on its own sequences (independent replicas)"}
+    cfg4 = None
+    if world > 1 and args.workload == "cfg3":
+        cfg4 = measure_cfg4(args, rank, world, device, steps=min(args.steps, 100), warmup=max(args.warmup, 3))
 
     if rank == 0:
-        ab, af = algorithmic_bytes(w), algorithmic_flops(w)
+        ab, af, kb = algorithmic_bytes(w), algorithmic_flops(w), kernel_bytes(w)
         peaks = {}
         pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
         if os.path.exists(pk):
             peaks = json.load(open(pk))
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
-        # per-stage roofline; the headline object is the stage that takes longest (all are HBM bound:
-        # append / indexer by arithmetic intensity, attention sits at the tensor/HBM ridge)
-        names = ["append", "index_select", "attend"]
-        stage_bytes = {"append": ab["append"] * B, "index_select": ab["index"] * B, "attend": ab["attend"] * B}
-        stage_kernels = {"append": "kv_append_paged_kernel",
-                         "index_select": "index query prepare + index_score_mma (tcgen05) + index_select_refine",
-                         "attend": "attend_mma (tcgen05; q split, gather, QK, softmax, PV in one kernel)"}
-        per_stage = {n: {"ms": stage_ms[i], "bytes": stage_bytes[n],
-                         "gbs": stage_bytes[n] / (stage_ms[i] * 1e-3) / 1e9,
-                         "frac": stage_bytes[n] / (stage_ms[i] * 1e-3) / 1e9 / hbm_peak}
-                     for i, n in enumerate(names)}
-        dom = max(names, key=lambda n: per_stage[n]["ms"])
-        achieved = per_stage[dom]["gbs"]
-        value = world * args.steps / (ms_total * 1e-3)
+        B0 = strong["B"]
+        km = strong["kernel_ms"]
+        per_kernel = {k: {"us": km[k] * 1e3, "bytes": kb[k] * B0, "gbs": kb[k] * B0 / (km[k] * 1e-3) / 1e9,
+                          "frac": kb[k] * B0 / (km[k] * 1e-3) / 1e9 / hbm_peak} for k in KERNELS}
+        dom = max(KERNELS, key=lambda k: km[k])                    # the single longest kernel of the step
+        value = 1e3 / ms                                           # whole-job layer-steps/s (a layer-step = the whole batch)
+        step_bytes = sum(ab.values()) * B0
         line = {
             "metric": METRIC, "value": value, "unit": "layer-steps/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate",
-            "data": "synthetic",
-            "config": config_of(args.workload, w, world),
-            "e2e": {"value": world * args.steps / (ms_e2e * 1e-3), "unit": "layer-steps/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * 4,   # append + query prologue, scorer, selection, attention (1 split: no combine)
-            "stage_ms": {"append": stage_ms[0], "index_select": stage_ms[1], "attend": stage_ms[2]},
-            "roofline": {"bound": "hbm", "kernel": f"{dom} stage: {stage_kernels[dom]}",
-                         "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "peak_source": f"of {peak_src}", "traffic": TRAFFIC_PER_SEQ.get(dom, 0) * B or None,
-                         "traffic_source": "ncu dram read+write at cfg3 shape, per sequence x batch (profiles/)",
-                         "stages": per_stage,
-                         "layer_step_bytes": sum(ab.values()) * B,
-                         "layer_step_gbs": sum(ab.values()) * B / (ms_total / args.steps * 1e-3) / 1e9,
-                         "attend_tflops": af["attend"] * B / (stage_ms[2] * 1e-3) / 1e12},
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate", "data": "synthetic",
+            "config": dict(config_of(args.workload, w, world, base if world > 1 else w["B"], "strong"),
+                           timed_region=f"{strong['reps']} back-to-back repetitions of the {args.steps}-step loop inside one "
+                                        f"CUDA-event pair; ms_per_step is over all of them"),
+            "timed_repetitions": strong["reps"],
+            "e2e": {"value": 1e3 / ms_e2e, "unit": "layer-steps/s", "h2d_bytes_per_step": strong["h2d"] * (1 if world == 1 else 1),
+                    "d2h_bytes_per_step": strong["d2h"], "bytes_are": "per GPU", "ms_per_step": ms_e2e,
+                    "ms_per_step_host_clock": ms_e2e_wall, "legs_ms_rank0": strong["e2e_legs_ms"],
+                    "call": "rivoli_dsa_step_host: one packed pinned buffer up, fused step, bf16 output down, 3 streams x 2 slots"},
+            "gpu_launches": args.steps * strong["reps"] * (4 if min(w["top_k"], w["ctx"]) >= 128 else 5),   # prologue, scorer, selection, (short-context attention arm,) tensor-core attention
+            "kernel_us": {k: km[k] * 1e3 for k in KERNELS},
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": per_kernel[dom]["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                         "frac": per_kernel[dom]["frac"], "peak_source": f"of {peak_src}",
+                         "traffic": TRAFFIC_PER_SEQ.get(dom, 0) * B0 or None,
+                         "traffic_source": TRAFFIC_SOURCE,
+                         "kernels": per_kernel,
+                         "layer_step_bytes": step_bytes,
+                         "layer_step_gbs_per_gpu": step_bytes / (ms * 1e-3) / 1e9,
+                         "layer_step_frac": step_bytes / (ms * 1e-3) / 1e9 / hbm_peak,
+                         "attend_tflops": af["attend"] * B0 / (km["attend_mma_kernel"] * 1e-3) / 1e12},
+            "self_check": strong.get("self_check"),
             "clocks": clocks,
         }
-        proj = time_projections(w, device)
-        if proj:
-            line["next_rows"] = {"what": "q absorption, value up-projection (kv_b) and the indexer front end (two launches), tcgen05 kind::f16, per call "
-                                         "at this batch, L2 flushed between launches; not part of the layer-step metric",
-                                 **proj}
-        if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = cpu_baseline(w, seconds=12.0)
+        if weak:
+            line["weak_scaling"] = weak
+        if cfg4:
+            line["cfg4"] = cfg4
+        if world == 1:
+            proj = time_projections(w, device)
+            if proj:
+                line["next_rows"] = {"what": "q absorption, value up-projection (kv_b) and the indexer front end (two launches), tcgen05 kind::f16, per call "
+                                             "at this batch, L2 flushed between launches; not part of the layer-step metric",
+                                     **proj}
+            if not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_baseline(w, seconds=12.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -454,32 +600,128 @@ def time_projections(w, device, steps=50):
     return out
 
 
+def churn_parity_check(device):
+    """Continuous batching at reduced scale against the oracle, outside any timed region: 2 layers, 8 slots, contexts
+    U[300, 1500], three token-steps with 25 % of the slots replaced after each. Page tables and free list must equal
+    the oracle allocator's bit for bit, the selected rows of every layer the oracle's, the attention output within
+    2e-2 relative / 1e-3 absolute."""
+    import torch
+    from oracle import oracle as orc
+    from oracle.workload import attend_close, bf16_normal, make_geom
+    from rivoli_b200 import backend as be
+    from rivoli_b200.engine import DsaDecodeStack
+    from rivoli_b200.scheduler import ContinuousBatcher, churn_plan
+    n_slots, n_layers, P, top_k, steps, lo, hi = 8, 2, 64, 256, 3, 300, 1500
+    max_ctx = hi + steps + 1
+    max_pages = (max_ctx + P - 1) // P
+    n_pool = int(1.25 * n_slots * max_pages)
+    kw = dict(n_heads=64, index_heads=32, index_dim=128, page_tokens=P, top_k=top_k, max_pages_per_seq=max_pages, n_pool_pages=n_pool)
+    g, og = make_geom(be.DsaGeom, **kw), make_geom(orc.Geom, **kw)
+    stack = DsaDecodeStack(g, n_slots, [True] * n_layers, device=device, max_ctx=max_pages * P, shuffle_seed=4)
+    sched = ContinuousBatcher(n_slots, n_pool, max_ctx, P, pool=stack.pool)
+    opool = orc.Pool(n_pool, n_slots, max_pages, P)
+    opool.shuffle(4)
+
+    class _O:                               # the oracle's allocator behind the scheduler's pool interface
+        def reserve(self, s_, n): return opool.reserve(s_, n)
+        def release(self, s_): return opool.release(s_)
+        def block_table(self): return opool.block_table()
+        n_free = property(lambda self: opool.n_free)
+    osched = ContinuousBatcher(n_slots, n_pool, max_ctx, P, pool=_O())
+    rng = np.random.RandomState(4)
+    W, hd = KV_LORA + ROPE, 128
+    rows_n = n_pool * P
+    mirror = [dict(lp=np.zeros(rows_n * W, np.uint8), ls=np.zeros(rows_n, np.float32), ip=np.zeros(rows_n * hd, np.uint8),
+                   isc=np.zeros(rows_n, np.float32)) for _ in range(n_layers)]
+
+    def dev(a):
+        a = np.ascontiguousarray(a)
+        return torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).to(device)
+
+    def prefill(slots, lens):
+        stack.upload_block_table()
+        bt = sched.block_table()
+        for s_, n in zip(slots, lens):
+            pos, seq = np.arange(int(n), dtype=np.int32), np.full(int(n), int(s_), np.int32)
+            for L, M in zip(stack.layers, mirror):
+                lat, key = bf16_normal(rng, (int(n), W)), bf16_normal(rng, (int(n), hd))
+                L.append(dev(lat), dev(key), dev(pos), dev(seq))
+                assert orc.kv_append_paged(og, lat, key, seq, pos, bt, M["lp"], M["ls"], M["ip"], M["isc"]) == 0
+
+    first = rng.randint(lo, hi + 1, n_slots)
+    for s_, n in enumerate(first):
+        sched.admit(s_, int(n)); osched.admit(s_, int(n))
+    prefill(range(n_slots), first)
+    worst_all = 0.0
+    for step in range(steps):
+        row_pos, seq_len = sched.begin_step()
+        osched.begin_step()
+        bt = sched.block_table()
+        assert np.array_equal(bt, osched.block_table()), "page tables differ from the oracle allocator"
+        assert np.array_equal(stack.pool.free_list(), opool.free_list()), "free lists differ from the oracle allocator"
+        stack.upload_block_table()
+        for li, (L, M) in enumerate(zip(stack.layers, mirror)):
+            lat, key = bf16_normal(rng, (n_slots, W)), bf16_normal(rng, (n_slots, hd))
+            iq, iw = bf16_normal(rng, (n_slots, 32, hd)), orc.bf16_to_f32(bf16_normal(rng, (n_slots, 32)))
+            q = bf16_normal(rng, (n_slots, 64, W))
+            out = stack.step_layer(li, dev(lat), dev(key), dev(iq), dev(iw), dev(q), dev(row_pos), dev(seq_len))
+            torch.cuda.synchronize(device)
+            L.check_status()
+            assert orc.kv_append_paged(og, lat, key, None, row_pos, bt, M["lp"], M["ls"], M["ip"], M["isc"]) == 0
+            qc, qs = orc.index_q_quant(iq, hd)
+            sc = orc.index_score_paged(og, qc, qs, iw, M["ip"], M["isc"], bt, seq_len, int(seq_len.max()))
+            rows, n_sel = orc.index_topk_batched(sc, seq_len, top_k)
+            _, want, _, _ = orc.mla_attend_paged(og, q, M["lp"], M["ls"], bt, rows, n_sel, want_f32=True)
+            got = L.rows.cpu().numpy().view(np.uint32)
+            for b in range(n_slots):
+                assert np.array_equal(got[b, :n_sel[b]], rows[b, :n_sel[b]]), "selected rows differ from the oracle"
+            ok, worst = attend_close(out.cpu().view(torch.int16).numpy().view(np.uint16), want)
+            assert ok, worst
+            worst_all = max(worst_all, worst)
+        slots, lens = churn_plan(rng, n_slots, 0.25, lo, hi)
+        sched.finish(slots, lens); osched.finish(slots, lens)
+        prefill(slots, lens)
+    del stack
+    torch.cuda.empty_cache()
+    return {"what": f"{n_layers} layers x {n_slots} slots x {steps} token-steps with 25 % replacement: page tables, free list and "
+                    "selected rows bit-exact against the oracle, attention within 2e-2 / 1e-3",
+            "attention_worst_err_over_tol": round(worst_all, 3)}
+
+
 def run_churn(args):
     """Continuous batching with eviction churn: `layers` decode layers behind one page allocator, a ragged
     batch (contexts U[512, 32768]), every token-step appends one token per sequence per layer, selects and
     attends; after each token-step 10 % of the sequences finish, their pages return to the free list and
-    replacements with fresh contexts are admitted (their prefill is NOT timed). Prints one JSON line."""
+    replacements with fresh contexts are admitted (their prefill is NOT timed). Under torchrun every rank runs its own
+    32-sequence slice of the batch of 256 with its own allocator (sharded by sequence, no collective); the time is the
+    MAX over ranks. Prints one JSON line on rank 0."""
     import torch
+    import torch.distributed as dist
     from rivoli_b200 import backend as be
     from rivoli_b200.engine import DsaDecodeStack
     from rivoli_b200.scheduler import ContinuousBatcher, churn_plan
     w = WORKLOADS["cfg5"]
     n_layers = args.layers or w["layers"]
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    parity = churn_parity_check(device) if rank == 0 else None
     B, P, lo, hi = w["B"], w["page_tokens"], w["ctx_lo"], w["ctx_hi"]
-    max_ctx = 32768
+    max_ctx = 32768 + 64
     assert hi + args.steps + args.warmup < max_ctx, "too many token-steps for the context bound"
     max_pages = (max_ctx + P - 1) // P
     n_pool = int(1.25 * B * max_pages)
     g = be.DsaGeom.make(n_heads=w["n_heads"], kv_lora=KV_LORA, rope_dim=ROPE, index_heads=w["index_heads"],
                         index_dim=w["index_dim"], page_tokens=P, top_k=w["top_k"], max_pages_per_seq=max_pages,
                         n_pool_pages=n_pool)
-    stack = DsaDecodeStack(g, B, [True] * n_layers, device=device, max_ctx=max_pages * P, shuffle_seed=w["seed"])
+    seed = w["seed"] + 1000 * rank                 # every rank: its own requests
+    stack = DsaDecodeStack(g, B, [True] * n_layers, device=device, max_ctx=max_pages * P, shuffle_seed=seed)
     sched = ContinuousBatcher(B, n_pool, max_ctx, P, pool=stack.pool)
-    rng = np.random.RandomState(w["seed"])
+    rng = np.random.RandomState(seed)
     gen = torch.Generator(device=device)
-    gen.manual_seed(w["seed"])
+    gen.manual_seed(seed)
     W = KV_LORA + ROPE
     blk = 1 << 15                                  # one block of random rows serves every prefill (contents are irrelevant here)
     lat_blk = torch.randn((blk, W), generator=gen, device=device).to(torch.bfloat16)
@@ -505,11 +747,15 @@ def run_churn(args):
     for it in range(args.warmup + args.steps):
         row_pos, seq_len = sched.begin_step()          # host: one page-table update for all layers
         rp, sl = torch.from_numpy(row_pos).to(device), torch.from_numpy(seq_len).to(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         stack.upload_block_table()
         for i in range(n_layers):
-            stack.step_layer(i, x["latent"], x["index_key"], x["index_q"], x["index_w"], x["q"], rp, sl)
+            stack.step_layer(i, x["latent"], x["index_key"], x["index_q"], x["index_w"], x["q"], rp, sl,
+                             min_rows_hint=min(w["top_k"], lo))     # the scheduler's bound: no context below `lo`
         e1.record()
         torch.cuda.synchronize(device)
         if it >= args.warmup:
@@ -522,15 +768,27 @@ def run_churn(args):
     for L in stack.layers[:2]:
         L.check_status()
     ms = float(np.mean(times))
-    line = {"metric": METRIC, "value": n_layers / (ms * 1e-3), "unit": "layer-steps/s", "n_gpus": 1, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / n_layers, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate", "data": "synthetic",
-            "config": {"workload": f"cfg5 slice: {n_layers} layers x batch {B}/GPU, contexts U[{lo},{hi}], top-k {w['top_k']}, "
-                                   f"{P}-token pages from one shared free list, 10 % of sequences replaced per token-step "
-                                   f"(prefill untimed), seed {w['seed']}",
-                       "token_step_ms": ms, "mean_context": float(sched.seq_len.mean())},
-            "gpu_launches": args.steps * n_layers * 4}
-    print(json.dumps(line), flush=True)
+    mean_ctx = float(sched.seq_len.mean())
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        line = {"metric": METRIC, "value": n_layers / (ms * 1e-3), "unit": "layer-steps/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / n_layers, "higher_is_better": True,
+                "scaling": "strong" if world > 1 else "weak",
+                "vs_baseline": None, "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate", "data": "synthetic",
+                "config": {"workload": f"cfg5: {n_layers} layers x batch {B * world} ({B}/GPU, sharded by sequence), contexts "
+                                       f"U[{lo},{hi}], top-k {w['top_k']}, {P}-token pages from one shared free list per GPU, "
+                                       f"10 % of sequences replaced per token-step (prefill untimed), seed {w['seed']}",
+                           "token_step_ms": ms, "token_steps_per_s": 1e3 / ms, "tokens_per_s": B * world * 1e3 / ms,
+                           "mean_context_rank0": mean_ctx,
+                           "a_layer_step_is": f"one layer over the whole batch of {B * world} sequences"},
+                "parity": parity,
+                "gpu_launches": args.steps * n_layers * 5}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_v4(args):
@@ -655,22 +913,15 @@ def run_v4(args):
     print(json.dumps(line), flush=True)
 
 
-def run_cfg4(args):
-    """Long-context decode, page-range sharded over the ranks (strong scaling: batch 4 x context 131,072 in total).
-    A step = append the new token on the rank that owns the last page range, local exact scores and local top-k
-    candidates, one all-gather of (score) candidates that fixes the exact global cut, local partial attention, one
-    all-gather of (out, lse) partials and the merge. Timed on the device, MAX over ranks; rank 0 prints one line."""
+def measure_cfg4(args, rank, world, device, steps, warmup):
+    """Long-context decode, page-range sharded over the ranks (strong scaling: batch 4 x context 131,072 in total):
+    a step = append the new token on the rank that owns the last page range, then rivoli_shard_step_paged - local
+    selection, ncclAllGather of the candidates, exact global cut + local partial attention, ncclAllGather of the
+    partials, merge. Timed on the device, MAX over ranks. Returns the result object (every rank) for rank 0 to print."""
     import torch
     import torch.distributed as dist
     from rivoli_b200 import shard
     w = dict(WORKLOADS["cfg4"])
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    assert world >= 2 and world == args.gpus, "cfg4 is the page-range sharded case: launch it under torchrun with --gpus >= 2"
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    dist.init_process_group("nccl", device_id=device)
     B, k = w["B"], w["top_k"]
     ctx_local = w["ctx"] // world
     g, layer, _ = build_layer(dict(w, ctx=ctx_local), device, w["seed"] * 100 + rank)   # ctx_local - 1 history tokens
@@ -679,69 +930,110 @@ def run_cfg4(args):
     x = step_inputs(w, device, gen)
     last = rank == world - 1
     local_len = torch.full((B,), ctx_local if last else ctx_local - 1, dtype=torch.int32, device=device)
-    offset = torch.full((B,), rank * (ctx_local - 1), dtype=torch.int32, device=device)
+    offset = rank * (ctx_local - 1)
     new_pos = torch.full((B,), ctx_local - 1, dtype=torch.int32, device=device)
-    ops = shard.gpu_shard_ops(layer)
+    comm = shard.ShardedDecodeStep.nccl_comm(rank, world)
+    sh = shard.ShardedDecodeStep(layer, rank, world, comm)
 
     def step():
         if last:
             layer.append(x["latent"], x["index_key"], new_pos)
-        return shard.page_range_step(ops, x["index_q"], x["index_w"], x["q"], local_len, offset, k)
+        return sh.step(x["index_q"], x["index_w"], x["q"], local_len)
 
-    out, rows_g, n_mine = step()
+    out = step()
     torch.cuda.synchronize(device)
     layer.check_status()
     # properties that need no oracle: the selected rows over all ranks number exactly k per sequence, each rank's are
     # ascending and inside its own range, and every rank holds the same merged output
-    n_all = n_mine.clone()
+    n_all = sh.n_mine.clone()
     dist.all_reduce(n_all)
     assert (n_all == k).all().item(), n_all.tolist()
-    rg = rows_g.cpu().numpy()
+    ra, nm = sh.rows_att.cpu().numpy().view(np.uint32).astype(np.int64), sh.n_mine.cpu().numpy()
     for b in range(B):
-        r = rg[b, : int(n_mine[b])]
-        assert np.all(np.diff(r) > 0) and (r.size == 0 or (r[0] >= int(offset[b]) and r[-1] < int(offset[b]) + int(local_len[b])))
+        r = ra[b, : nm[b]]
+        assert np.all(np.diff(r) > 0) and (r.size == 0 or (r[0] >= 0 and r[-1] < int(local_len[b])))
     chk = out.view(torch.int16).to(torch.int64).sum().reshape(1)
     lo, hi = chk.clone(), chk.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     assert lo.item() == hi.item(), "ranks disagree on the merged output"
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+
+    def timed(fn, n):
+        dist.barrier()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize(device)
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms = timed(step, steps)
+    # the same kernels without the two collectives (buffers gathered once with torch.distributed): what is left of
+    # the step is NCCL launch latency + transfer + the wait for the slowest rank
+    cand = sh.candidates(x["index_q"], x["index_w"], local_len)
+    all_cand = torch.empty(world * cand.numel(), dtype=torch.uint8, device=device)
+    dist.all_gather_into_tensor(all_cand, cand)
+    part = sh.cut_attend(all_cand, x["q"])
+    all_part = torch.empty(world * part.numel(), dtype=torch.uint8, device=device)
+    dist.all_gather_into_tensor(all_part, part)
+
+    def local_only():
+        if last:
+            layer.append(x["latent"], x["index_key"], new_pos)
+        sh.candidates(x["index_q"], x["index_w"], local_len)
+        sh.cut_attend(all_cand, x["q"])
+        sh.merge(all_part)
+
+    for _ in range(3):
+        local_only()
+    ms_local = timed(local_only, steps)
+    layer.check_status()
     dist.barrier()
-    torch.cuda.synchronize(device)
-    if sampler:
-        sampler.start()
-        sampler.mark()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    dist.barrier()
-    torch.cuda.synchronize(device)
-    clocks = None
-    if sampler:
-        sampler.mark()
-        clocks = sampler.stop()
-    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    from rivoli_b200 import backend as be
+    be.shard_nccl_comm_destroy(comm)
+    per_seq = algorithmic_bytes(w)
+    total = (per_seq["append"] + per_seq["index"] + per_seq["attend"]) * B
+    res = {"metric": METRIC, "value": 1e3 / ms, "unit": "layer-steps/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+           "ms_per_step": ms, "scaling": "strong",
+           "config": {"workload": f"cfg4: batch {B} x context {w['ctx']}, page-range sharded {world}-way "
+                                  f"({ctx_local} tokens of every sequence per GPU), top-k {k}, seed {w['seed']}",
+                      "call": "rivoli_shard_step_paged: tensor-core scorer + cluster selection + exact candidate scores, "
+                              "ncclAllGather (candidates), global cut + partial attention, ncclAllGather (partials), merge",
+                      "collectives_per_step": 2,
+                      "bytes_per_rank_per_collective": [int(cand.numel()), int(part.numel())]},
+           "ms_kernels_only": ms_local, "ms_collectives": ms - ms_local,
+           "limiter": "two NCCL all-gathers of 33 KB / 265 KB per rank: launch latency and rank skew, not bandwidth; "
+                      "the kernels run at batch 4 and are latency bound themselves",
+           "gbs_per_gpu": total / (ms * 1e-3) / 1e9 / world,
+           "self_check": "k rows in total per sequence, ascending inside every rank's range, identical merged output on every rank"}
+    del sh, layer
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_cfg4(args):
+    """`--workload cfg4` under torchrun with --gpus >= 2: the page-range sharded step alone; rank 0 prints one line."""
+    import torch
+    import torch.distributed as dist
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    assert world >= 2 and world == args.gpus, "cfg4 is the page-range sharded case: launch it under torchrun with --gpus >= 2"
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=device)
+    res = measure_cfg4(args, rank, world, device, steps=args.steps, warmup=max(args.warmup, 3))
     if rank == 0:
-        ms = float(ms.item())
-        per_seq = algorithmic_bytes(dict(w, ctx=w["ctx"]))
-        total = (per_seq["append"] + per_seq["index"] + per_seq["attend"]) * B
-        line = {"metric": METRIC, "value": 1e3 / ms, "unit": "layer-steps/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate", "data": "synthetic",
-                "config": {"workload": f"cfg4: batch {B} x context {w['ctx']}, page-range sharded {world}-way "
-                                       f"({ctx_local} tokens of every sequence per GPU), top-k {k}, seed {w['seed']}",
-                           "collectives": "per step: all-gather of top-k candidate scores and counts, all-gather of "
-                                          "partial outputs and log-sum-exps (NCCL), then the merge kernel",
-                           "l2": "per-GPU index pool %.0f MB" % (B * ctx_local * (w["index_dim"] + 4) / 1e6)},
-                "gpu_launches": args.steps * (8 + (1 if world else 0)), "clocks": clocks,
-                "roofline": {"bound": "hbm", "achieved": total / (ms * 1e-3) / 1e9 / world, "unit": "GB/s per GPU",
-                             "note": "algorithmic bytes of the whole step / time / GPUs; latency bound at batch 4"}}
-        print(json.dumps(line), flush=True)
+        res.update({"higher_is_better": True, "vs_baseline": None, "data": "synthetic",
+                    "dtype": "fp8-e4m3 cache, bf16 activations, f32 accumulate", "gpu_launches": args.steps * 12})
+        print(json.dumps(res), flush=True)
     dist.destroy_process_group()
 
 
@@ -805,7 +1097,10 @@ def cpu_baseline(w, seconds=12.0, n_seq=None):
 
 def run_reference(args):
     """The reference's own CPU arithmetic for this path (the oracle port: the reference is a
-    Rust + HIP tree that cannot be compiled on this image), all host threads."""
+    Rust + HIP tree that cannot be compiled on this image), all host threads. A step = the layer-step on a bounded
+    SAMPLE of the batch (8 of its sequences); `ms_per_step` is that sample step as measured, `sample_scale` the
+    factor to the whole batch, `value` the whole-batch rate. The workload is the batch in total, whatever N is:
+    the CPU arm is one host."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -815,22 +1110,26 @@ def run_reference(args):
     orc.set_num_threads(len(os.sched_getaffinity(0)))      # torchrun exports OMP_NUM_THREADS=1; rank 0 runs alone
     # bounded sample: about 11 ms of CPU work per cfg3 sequence; keep the whole run near two minutes
     per_seq_s = 0.011 * w["ctx"] / 16384
-    n_seq = max(1, min(w["B"], 8, int(120.0 / max(1, args.steps + 1) / per_seq_s)))
+    warm = max(args.warmup, 3)
+    n_seq = max(1, min(w["B"], 8, int(120.0 / max(1, args.steps + warm) / per_seq_s)))
     st = cpu_sample_state(w, n_seq, w["seed"])
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(warm):
         st.oracle_step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         st.oracle_step()
     dt = (time.perf_counter() - t0) / args.steps
-    value = 1.0 / (dt / n_seq * w["B"])
+    scale = w["B"] / n_seq
+    value = 1.0 / (dt * scale)
     sample = (f"each step = {n_seq} of {w['B']} sequences of the same shape (ctx {w['ctx']}); value scaled by "
               f"{w['B']}/{n_seq}; one host, all threads")
+    base = w["B"] // world
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "layer-steps/s", "n_gpus": world,
-            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / n_seq * w["B"] * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU)",
+            "steps": args.steps, "warmup": warm, "ms_per_step": dt * 1e3, "sample_scale": scale,
+            "ms_per_whole_batch_step": dt * scale * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (CPU)",
             "data": "synthetic",
-            "config": config_of(args.workload, w, world),
+            "config": config_of(args.workload, w, world, base if world > 1 else w["B"], "strong"),
             "cpu_baseline": {"value": value, "unit": "layer-steps/s", "cores": orc.num_threads(), "kind": "port",
                              "sample": sample},
             "e2e": {"value": value, "unit": "layer-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -839,6 +1138,9 @@ def run_reference(args):
 
 
 def main():
+    # rank 0 prints ONE JSON line on stdout: keep NCCL's version banner (NCCL_DEBUG=VERSION prints it there) out of it
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
@@ -850,6 +1152,8 @@ def main():
                     help="build the workload, run 3 iterations of one stage (or the whole step) and exit: "
                          "the command line the profiles/ summaries were captured with")
     ap.add_argument("--layers", type=int, default=0, help="cfg5 only: number of layers (default 78)")
+    ap.add_argument("--reps", type=int, default=0,
+                    help="repetitions of the --steps loop inside the timed region (default: as many as make it 0.25 s long)")
     ap.add_argument("--batch", type=int, default=0,
                     help="with --profile only: sequences per GPU instead of the workload's own batch")
     args = ap.parse_args()
@@ -870,9 +1174,8 @@ def main():
             args.steps = 2000            # 0.14 ms each: long enough for the clock sampler to see the timed region
         return run_v4(args)
     if args.workload == "cfg5":
-        if args.impl == "reference" or args.gpus != 1:
-            ap.error("the churn workload runs on one GPU with the CUDA arm only (it is a parity / capacity case, "
-                     "not the headline line)")
+        if args.impl == "reference":
+            ap.error("the churn workload is a measurement of the CUDA arm (its parity check against the oracle is part of it)")
         if args.steps == 400:
             args.steps = 8               # token-steps of 78 layer-steps each
         return run_churn(args)

@@ -185,15 +185,51 @@ int rivoli_dsa_append_select_paged(const DsaGeom* g, const uint16_t* latent, con
  * rivoli_mla_attend_paged_bf16 over the selected rows (row_stride = top_k), same results. Because q is an
  * input of the call it is known to be complete before the call's first kernel starts, so the attention kernel
  * converts it while the selection kernel is still running (the separate attention entry point cannot assume
- * that and reads q only after the kernel before it has finished). Replaces the per-layer launch sequence of
- * crates/engine/src/glm/attn.rs:119-222 (append, indexer, attend) for a batch. */
+ * that and reads q only after the kernel before it has finished). min_rows_hint: a lower bound the caller's
+ * scheduler knows for min(top_k, seq_len[b]) over the batch, 0 if it knows none; from 128 on no sequence can need
+ * the short-context attention arm and its (otherwise empty) launch is left out. Replaces the per-layer launch
+ * sequence of crates/engine/src/glm/attn.rs:119-222 (append, indexer, attend) for a batch. */
 int rivoli_dsa_decode_step_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,
                                  const int32_t* row_pos, const int32_t* block_table, uint8_t* latent_pool,
                                  float* latent_scale, uint8_t* index_pool, float* index_scale, int32_t* status,
                                  const uint16_t* index_q, const float* w, const int32_t* seq_len, int B,
                                  int score_stride, uint32_t* rows, int32_t* n_sel, void* select_scratch,
                                  const uint16_t* q, uint16_t* out, float* out_m, float* out_lse,
-                                 void* attend_scratch, void* stream);
+                                 void* attend_scratch, int min_rows_hint, void* stream);
+/* ---- the same step for a caller whose activations live in HOST memory ---------------------------------------
+ * No counterpart in the reference, whose engine keeps activations on the device; the stream / event wrappers it
+ * would build this from are crates/backend/src/gpustream.rs:16-32. A pipe owns `depth` device-side slots, three
+ * non-blocking streams (upload | kernels | download) and the events that order them, all allocated in
+ * rivoli_step_pipe_create; a step allocates nothing and never blocks the host. One step = ONE host-to-device copy
+ * of the packed inputs, rivoli_dsa_decode_step_paged, ONE device-to-host copy of the bf16 output; the upload of
+ * step i+1 and the download of step i-1 overlap the kernels of step i.
+ * Packed input (pinned host memory, rivoli_step_pipe_input_bytes): latent bf16 [B][kv_lora+rope_dim], index_key
+ * bf16 [B][index_dim], index_q bf16 [B][index_heads][index_dim], index_w f32 [B][index_heads], q bf16
+ * [B][n_heads][kv_lora+rope_dim], each section starting on a 256-byte boundary (rivoli_step_pipe_input_offsets).
+ * host_out: pinned, bf16 [B][n_heads][kv_lora]; it may be reused once rivoli_step_pipe_wait(ticket) returned.
+ * row_pos / seq_len are DEVICE arrays (the caller's scheduler state), read when the step runs. */
+typedef struct DsaStepState {          /* device pointers of one layer: pools, selection and scratch */
+    const int32_t* block_table; uint8_t* latent_pool; float* latent_scale; uint8_t* index_pool; float* index_scale;
+    int32_t* status; uint32_t* rows; int32_t* n_sel; void* select_scratch; void* attend_scratch;
+    float* out_m; float* out_lse;      /* may be NULL */
+    int32_t score_stride;
+    int32_t min_rows_hint;             /* see rivoli_dsa_decode_step_paged; 0 = unknown */
+} DsaStepState;
+size_t rivoli_step_pipe_input_bytes(const DsaGeom* g, int B);
+size_t rivoli_step_pipe_output_bytes(const DsaGeom* g, int B);
+int rivoli_step_pipe_input_offsets(const DsaGeom* g, int B, size_t off[5]);
+void* rivoli_step_pipe_create(const DsaGeom* g, int B, int depth);       /* NULL on failure; depth 1..8 */
+void rivoli_step_pipe_destroy(void* pipe);
+/* Returns a ticket >= 0, or -(guard code) / -(cudaError_t). */
+long long rivoli_dsa_step_host(void* pipe, const DsaStepState* st, const void* host_in, void* host_out,
+                               const int32_t* row_pos, const int32_t* seq_len);
+int rivoli_step_pipe_wait(void* pipe, long long ticket);
+int rivoli_step_pipe_drain(void* pipe);
+/* ms[0] upload, ms[1] upload end -> kernels end, ms[2] kernels end -> download end, of the last use of every slot
+ * (average over the slots). Synchronises the pipe. */
+int rivoli_step_pipe_leg_ms(void* pipe, float ms[3]);
+void* rivoli_step_pipe_stream(void* pipe, int which);                    /* 0 upload, 1 kernels, 2 download */
+
 /* Synchronises `stream` and reports on the last rivoli_index_select_paged call (tensor-core path): 1008 if a
  * bounded device-side wait gave up, 1005 if a block-table entry inside a sequence's length pointed outside
  * the pool (that page was not read; results are undefined in both cases), else 0. */
@@ -213,6 +249,8 @@ size_t rivoli_mla_attend_paged_scratch_bytes(const DsaGeom* g, int B);
  * or NULL (dense: row j = token j); n_rows i32 [B]. out bf16 [B][n_heads][kv_lora].
  * out_m / out_lse f32 [B][n_heads] (may be NULL): max score and log-sum-exp, the partial a
  * page-range shard hands to rivoli_attend_merge_partials. scratch = the bytes above.
+ * A sequence whose first row entry is the dense marker 0xFFFFFFFF is attended as if rows were NULL for it
+ * (row j = token j over its first n_rows[b] tokens); this lets one call mix listed and dense sequences.
  * With the model geometry and scratch the call runs the tensor-core kernel for sequences of 128 attended
  * rows and more and the f32 CUDA-core kernel for shorter ones (two launches, disjoint sequences), so the
  * output meets 2e-2 relative / 1e-3 absolute elementwise at every row count. */
@@ -226,6 +264,13 @@ int rivoli_mla_attend_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint
  * (n_heads 64, kv_lora 512, rope_dim 64, scratch given); it then returns in out_m a softmax
  * reference point m <= lse rather than the exact maximum (merging needs only out and lse). */
 int rivoli_mla_attend_paged_uses_mma(const DsaGeom* g);
+/* The rows a layer serves under the one-step-stale selection (crates/engine/src/indexer.rs:14-63: what token t
+ * serves is what token t-1 stored; nothing stored = dense over the whole prefix), batched: per sequence mode 0 =
+ * the previous token's rows verbatim, 1 = this token's fresh rows, 2 = dense (out_rows[b][0] = the dense marker,
+ * out_n[b] = seq_len[b]). All arrays on the device; rows u32 [B][k]. */
+int rivoli_stale_compose_rows(const uint32_t* prev_rows, const int32_t* prev_n, const uint32_t* cur_rows,
+                              const int32_t* cur_n, const int32_t* mode, const int32_t* seq_len, int B, int k,
+                              uint32_t* out_rows, int32_t* out_n, void* stream);
 /* Synchronises `stream`; 1008 if a bounded device-side wait of the last tensor-core
  * attention call on `scratch` gave up (output undefined), else 0. */
 int rivoli_mla_attend_paged_status(const DsaGeom* g, void* scratch, void* stream);
@@ -235,6 +280,50 @@ int rivoli_mla_attend_paged_status(const DsaGeom* g, void* scratch, void* stream
  * part_lse f32 [G][n_vec], out bf16 [n_vec][kvl]. */
 int rivoli_attend_merge_partials(const uint16_t* part_out, const float* part_lse, int G, int n_vec,
                                  int kvl, uint16_t* out, void* stream);
+
+/* ---- page-range sharded decode step (one long context split over the GPUs of a box) ----------------------
+ * No counterpart in the reference (single GPU); the merge is its split combine (attn.hip:241-273) across GPUs.
+ * Every rank holds a page range of every sequence in its OWN pools at local positions 0..n-1 (local_len[b]
+ * tokens of sequence b; rank order = ascending token order). The step's new token is appended by the rank that
+ * owns the last range (rivoli_kv_append_paged) before the step. Three phases around two exchanges:
+ *   A  rivoli_shard_candidates: local selection -> rows_l u32 [B][top_k] (ascending local indices) and the
+ *      candidate buffer (rivoli_shard_candidate_bytes): [B][top_k] f32 EXACT scores of rows_l (-inf past n_l[b]),
+ *      then n_l i32 [B];
+ *   -- all-gather of the candidate buffers, rank-major --
+ *   B  rivoli_shard_cut_attend: the exact global top-k over the world * top_k candidates (ties -> lower rank, then
+ *      lower local index = lower global index), this rank's surviving rows -> rows_att / n_mine, local partial
+ *      attention -> the partial buffer (rivoli_shard_partial_bytes): out bf16 [B][n_heads][kv_lora] normalised
+ *      within the shard, then lse f32 [B][n_heads];
+ *   -- all-gather of the partial buffers, rank-major --
+ *   C  rivoli_shard_merge: weight_g = exp(lse_g - max lse), ascending g -> out bf16 [B][n_heads][kv_lora], the same
+ *      on every rank.
+ * rivoli_shard_step_paged runs A, ncclAllGather, B, ncclAllGather, C on the caller's communicator (an ncclComm_t
+ * passed as void*; NULL allowed when world == 1) and stream: two collectives per step. NCCL is loaded at run time;
+ * 1008 if it cannot be, 1100 + ncclResult_t if a collective fails. Needs index_dim 128 and index_heads <= 32
+ * (1004 otherwise). shard_scratch = rivoli_shard_scratch_bytes(); select_scratch / attend_scratch as for the
+ * single-GPU operators. Remote data reaches a GPU only through NCCL into that scratch. */
+size_t rivoli_shard_candidate_bytes(const DsaGeom* g, int B);
+size_t rivoli_shard_partial_bytes(const DsaGeom* g, int B);
+size_t rivoli_shard_scratch_bytes(const DsaGeom* g, int B, int world);
+int rivoli_shard_candidates(const DsaGeom* g, const uint16_t* index_q, const float* w, const uint8_t* index_pool,
+                            const float* index_scale, const int32_t* block_table, const int32_t* local_len, int B,
+                            int score_stride, uint32_t* rows_l, void* select_scratch, void* cand, void* stream);
+int rivoli_shard_cut_attend(const DsaGeom* g, const void* all_cand, int rank, int world, const uint32_t* rows_l,
+                            const uint16_t* q, const uint8_t* latent_pool, const float* latent_scale,
+                            const int32_t* block_table, int B, uint32_t* rows_att, int32_t* n_mine, void* part,
+                            void* shard_scratch, void* attend_scratch, void* stream);
+int rivoli_shard_merge(const DsaGeom* g, const void* all_part, int world, int B, uint16_t* out, void* stream);
+int rivoli_shard_step_paged(const DsaGeom* g, void* comm, int rank, int world, const uint16_t* index_q,
+                            const float* w, const uint16_t* q, const uint8_t* latent_pool, const float* latent_scale,
+                            const uint8_t* index_pool, const float* index_scale, const int32_t* block_table,
+                            const int32_t* local_len, int B, int score_stride, uint32_t* rows_l, uint32_t* rows_att,
+                            int32_t* n_mine, uint16_t* out, void* select_scratch, void* attend_scratch,
+                            void* shard_scratch, void* stream);
+/* Communicator helpers for a host that holds no ncclComm_t yet: rank 0 makes the 128-byte id, passes it to the
+ * other ranks by its own means, and every rank calls comm_create (a collective call). */
+int rivoli_shard_nccl_unique_id(void* id128);
+int rivoli_shard_nccl_comm_create(const void* id128, int rank, int world, void** comm);
+int rivoli_shard_nccl_comm_destroy(void* comm);
 
 /* CUDA-core (f32 accumulate) implementation of rivoli_mla_attend_paged_bf16, same contract.
  * No reference counterpart beyond attn.hip:119-232 itself: it is the cross-check of the
@@ -454,6 +543,14 @@ int rivoli_v4_compress_step_bf16(const CompGeom* p, int n_seqs, const int32_t* p
                                  int cache_row0, float* prequant, unsigned char* packed, uint32_t* packed_exp,
                                  void* stream);
 
+/* ---- measurement hook ------------------------------------------------------------------------------------------
+ * events[0..5): cudaEvent_t handles that the following rivoli_dsa_decode_step_paged / rivoli_dsa_append_select_paged
+ * calls record on their stream: 0 before the prologue kernel (append + query preparation), 1 before the scorer,
+ * 2 before the selection, 3 before the attention, 4 after it; a benchmark reads each kernel's own duration from
+ * them. The records take away the programmatic overlap between the kernels. NULL switches the hook off (the
+ * default). No counterpart in the reference. */
+void rivoli_dsa_step_set_timing_events(void* const* events);
+
 /* ---- test hooks (exercised by the GPU tests; not for production callers) ----------------------------------
  * Overrides for the tensor-core attention's NEXT launches, host side only, no counterpart in the reference.
  * min_rows >= 0 replaces the 128-row threshold below which a sequence goes to the CUDA-core kernel (0 = every
@@ -462,6 +559,9 @@ int rivoli_v4_compress_step_bf16(const CompGeom* p, int n_seqs, const int32_t* p
  * and later launches are unaffected (this is how the give-up path of the waits is tested; nothing faults).
  * max_polls > 0 sets the poll limit of the bounded waits (<= 0 restores the default). */
 void rivoli_attend_mma_test_hook(int min_rows, int withhold, int max_polls);
+/* Forces the thread-block cluster size of the following selection launches (1, 2, 4 or 8; anything else restores
+ * the library's own plan), so that a test can run every cluster size at any batch size. */
+void rivoli_index_select_test_cluster(int cluster);
 
 /* Library build tag, e.g. "sm_100a". */
 const char* rivoli_kernels_arch(void);

@@ -224,13 +224,72 @@ def launch_dsa_append_select_paged(g: DsaGeom, latent, index_key, row_pos, block
 def launch_dsa_decode_step_paged(g: DsaGeom, latent, index_key, row_pos, block_table, latent_pool, latent_scale,
                                  index_pool, index_scale, status, index_q, w, seq_len, B: int, score_stride: int,
                                  rows, n_sel, select_scratch, q, out, out_m, out_lse, attend_scratch,
-                                 stream=None) -> None:
+                                 min_rows_hint: int = 0, stream=None) -> None:
     """One decode layer-step in one call: append, select, attend (``rivoli_dsa_decode_step_paged``)."""
     ensure_status(lib().rivoli_dsa_decode_step_paged(
         C.byref(g), _ptr(latent), _ptr(index_key), _ptr(row_pos), _ptr(block_table), _ptr(latent_pool),
         _ptr(latent_scale), _ptr(index_pool), _ptr(index_scale), _ptr(status), _ptr(index_q), _ptr(w), _ptr(seq_len),
         C.c_int(B), C.c_int(score_stride), _ptr(rows), _ptr(n_sel), _ptr(select_scratch), _ptr(q), _ptr(out),
-        _ptr(out_m), _ptr(out_lse), _ptr(attend_scratch), _stream(stream)), "dsa_decode_step_paged")
+        _ptr(out_m), _ptr(out_lse), _ptr(attend_scratch), C.c_int(min_rows_hint), _stream(stream)),
+        "dsa_decode_step_paged")
+
+
+class DsaStepState(C.Structure):
+    """``DsaStepState`` of include/rivoli_kernels.h: the device pointers of one layer."""
+    _fields_ = [(n, C.c_void_p) for n in (
+        "block_table", "latent_pool", "latent_scale", "index_pool", "index_scale", "status", "rows", "n_sel",
+        "select_scratch", "attend_scratch", "out_m", "out_lse")] + [("score_stride", C.c_int32),
+                                                                      ("min_rows_hint", C.c_int32)]
+
+
+class StepPipe:
+    """Handle of the library's host-buffer step pipeline (``rivoli_step_pipe_*`` / ``rivoli_dsa_step_host``)."""
+
+    def __init__(self, g: DsaGeom, B: int, depth: int = 2):
+        L = lib()
+        L.rivoli_step_pipe_create.restype = C.c_void_p
+        L.rivoli_step_pipe_stream.restype = C.c_void_p
+        L.rivoli_step_pipe_input_bytes.restype = C.c_size_t
+        L.rivoli_step_pipe_output_bytes.restype = C.c_size_t
+        L.rivoli_dsa_step_host.restype = C.c_longlong
+        self._h = C.c_void_p(L.rivoli_step_pipe_create(C.byref(g), C.c_int(B), C.c_int(depth)))
+        if not self._h:
+            raise BackendError("step_pipe_create", 1008)
+        self.g, self.B, self.depth = g, B, depth
+        self.input_bytes = int(L.rivoli_step_pipe_input_bytes(C.byref(g), C.c_int(B)))
+        self.output_bytes = int(L.rivoli_step_pipe_output_bytes(C.byref(g), C.c_int(B)))
+        off = (C.c_size_t * 5)()
+        ensure_status(L.rivoli_step_pipe_input_offsets(C.byref(g), C.c_int(B), off), "step_pipe_input_offsets")
+        self.offsets = dict(zip(("latent", "index_key", "index_q", "index_w", "q"), (int(o) for o in off)))
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                lib().rivoli_step_pipe_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    def submit(self, state: DsaStepState, host_in, host_out, row_pos, seq_len) -> int:
+        t = int(lib().rivoli_dsa_step_host(self._h, C.byref(state), _ptr(host_in), _ptr(host_out), _ptr(row_pos),
+                                           _ptr(seq_len)))
+        if t < 0:
+            raise BackendError("dsa_step_host", -t if -t >= 1000 else t)
+        return t
+
+    def wait(self, ticket: int) -> None:
+        ensure_status(lib().rivoli_step_pipe_wait(self._h, C.c_longlong(ticket)), "step_pipe_wait")
+
+    def drain(self) -> None:
+        ensure_status(lib().rivoli_step_pipe_drain(self._h), "step_pipe_drain")
+
+    def leg_ms(self):
+        ms = (C.c_float * 3)()
+        ensure_status(lib().rivoli_step_pipe_leg_ms(self._h, ms), "step_pipe_leg_ms")
+        return {"upload": float(ms[0]), "kernels_after_upload": float(ms[1]), "download_after_kernels": float(ms[2])}
+
+    def stream(self, which: int) -> int:
+        return int(lib().rivoli_step_pipe_stream(self._h, C.c_int(which)) or 0)
 
 
 def index_select_status(g: DsaGeom, B: int, score_stride: int, scratch, stream=None) -> None:
@@ -249,6 +308,13 @@ def index_select_band_stats(g: DsaGeom, B: int, score_stride: int, scratch, stre
     return out
 
 
+def launch_stale_compose_rows(prev_rows, prev_n, cur_rows, cur_n, mode, seq_len, B: int, k: int, out_rows, out_n,
+                              stream=None) -> None:
+    ensure_status(lib().rivoli_stale_compose_rows(_ptr(prev_rows), _ptr(prev_n), _ptr(cur_rows), _ptr(cur_n), _ptr(mode),
+                                                  _ptr(seq_len), C.c_int(B), C.c_int(k), _ptr(out_rows), _ptr(out_n),
+                                                  _stream(stream)), "stale_compose_rows")
+
+
 def attend_paged_scratch_bytes(g: DsaGeom, B: int) -> int:
     return int(lib().rivoli_mla_attend_paged_scratch_bytes(C.byref(g), C.c_int(B)))
 
@@ -263,9 +329,24 @@ def attend_paged_status(g: DsaGeom, scratch, stream=None) -> None:
                   "mla_attend_paged_status")
 
 
+def step_set_timing_events(events) -> None:
+    """``events``: five ``torch.cuda.Event(enable_timing=True)`` objects (already recorded once, so that their
+    handles exist) or ``None`` to switch the hook off. See ``rivoli_dsa_step_set_timing_events``."""
+    if events is None:
+        lib().rivoli_dsa_step_set_timing_events(None)
+        return
+    arr = (C.c_void_p * 5)(*[C.c_void_p(e.cuda_event) for e in events])
+    lib().rivoli_dsa_step_set_timing_events(arr)
+
+
 def attend_mma_test_hook(min_rows: int = -1, withhold: int = 0, max_polls: int = 0) -> None:
     """Test hook of the tensor-core attention (see include/rivoli_kernels.h); not for production callers."""
     lib().rivoli_attend_mma_test_hook(C.c_int(min_rows), C.c_int(withhold), C.c_int(max_polls))
+
+
+def index_select_test_cluster(cluster: int = 0) -> None:
+    """Test hook: force the selection kernel's cluster size (1, 2, 4, 8; 0 = the library's plan)."""
+    lib().rivoli_index_select_test_cluster(C.c_int(cluster))
 
 
 def attend_simt_scratch_bytes(g: DsaGeom, B: int) -> int:
@@ -296,6 +377,74 @@ def launch_attend_merge_partials(part_out, part_lse, G: int, n_vec: int, kvl: in
     ensure_status(lib().rivoli_attend_merge_partials(_ptr(part_out), _ptr(part_lse), C.c_int(G),
                                                      C.c_int(n_vec), C.c_int(kvl), _ptr(out),
                                                      _stream(stream)), "attend_merge_partials")
+
+
+# --- page-range sharded step --------------------------------------------------------------------------------
+def shard_candidate_bytes(g: DsaGeom, B: int) -> int:
+    f = lib().rivoli_shard_candidate_bytes
+    f.restype = C.c_size_t
+    return int(f(C.byref(g), C.c_int(B)))
+
+
+def shard_partial_bytes(g: DsaGeom, B: int) -> int:
+    f = lib().rivoli_shard_partial_bytes
+    f.restype = C.c_size_t
+    return int(f(C.byref(g), C.c_int(B)))
+
+
+def shard_scratch_bytes(g: DsaGeom, B: int, world: int) -> int:
+    f = lib().rivoli_shard_scratch_bytes
+    f.restype = C.c_size_t
+    return int(f(C.byref(g), C.c_int(B), C.c_int(world)))
+
+
+def launch_shard_candidates(g: DsaGeom, index_q, w, index_pool, index_scale, block_table, local_len, B: int,
+                            score_stride: int, rows_l, select_scratch, cand, stream=None) -> None:
+    ensure_status(lib().rivoli_shard_candidates(C.byref(g), _ptr(index_q), _ptr(w), _ptr(index_pool), _ptr(index_scale),
+                                                _ptr(block_table), _ptr(local_len), C.c_int(B), C.c_int(score_stride),
+                                                _ptr(rows_l), _ptr(select_scratch), _ptr(cand), _stream(stream)),
+                  "shard_candidates")
+
+
+def launch_shard_cut_attend(g: DsaGeom, all_cand, rank: int, world: int, rows_l, q, latent_pool, latent_scale,
+                            block_table, B: int, rows_att, n_mine, part, shard_scratch, attend_scratch,
+                            stream=None) -> None:
+    ensure_status(lib().rivoli_shard_cut_attend(C.byref(g), _ptr(all_cand), C.c_int(rank), C.c_int(world), _ptr(rows_l),
+                                                _ptr(q), _ptr(latent_pool), _ptr(latent_scale), _ptr(block_table),
+                                                C.c_int(B), _ptr(rows_att), _ptr(n_mine), _ptr(part), _ptr(shard_scratch),
+                                                _ptr(attend_scratch), _stream(stream)), "shard_cut_attend")
+
+
+def launch_shard_merge(g: DsaGeom, all_part, world: int, B: int, out, stream=None) -> None:
+    ensure_status(lib().rivoli_shard_merge(C.byref(g), _ptr(all_part), C.c_int(world), C.c_int(B), _ptr(out),
+                                           _stream(stream)), "shard_merge")
+
+
+def launch_shard_step_paged(g: DsaGeom, comm: int, rank: int, world: int, index_q, w, q, latent_pool, latent_scale,
+                            index_pool, index_scale, block_table, local_len, B: int, score_stride: int, rows_l,
+                            rows_att, n_mine, out, select_scratch, attend_scratch, shard_scratch, stream=None) -> None:
+    ensure_status(lib().rivoli_shard_step_paged(
+        C.byref(g), C.c_void_p(comm or 0), C.c_int(rank), C.c_int(world), _ptr(index_q), _ptr(w), _ptr(q),
+        _ptr(latent_pool), _ptr(latent_scale), _ptr(index_pool), _ptr(index_scale), _ptr(block_table), _ptr(local_len),
+        C.c_int(B), C.c_int(score_stride), _ptr(rows_l), _ptr(rows_att), _ptr(n_mine), _ptr(out), _ptr(select_scratch),
+        _ptr(attend_scratch), _ptr(shard_scratch), _stream(stream)), "shard_step_paged")
+
+
+def shard_nccl_unique_id() -> bytes:
+    buf = C.create_string_buffer(128)
+    ensure_status(lib().rivoli_shard_nccl_unique_id(buf), "shard_nccl_unique_id")
+    return buf.raw
+
+
+def shard_nccl_comm_create(unique_id: bytes, rank: int, world: int) -> int:
+    comm = C.c_void_p(0)
+    ensure_status(lib().rivoli_shard_nccl_comm_create(C.c_char_p(unique_id), C.c_int(rank), C.c_int(world),
+                                                      C.byref(comm)), "shard_nccl_comm_create")
+    return int(comm.value or 0)
+
+
+def shard_nccl_comm_destroy(comm: int) -> None:
+    ensure_status(lib().rivoli_shard_nccl_comm_destroy(C.c_void_p(comm)), "shard_nccl_comm_destroy")
 
 
 # --- Part 3: host page allocator ----------------------------------------------------------------------

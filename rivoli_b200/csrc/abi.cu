@@ -17,7 +17,7 @@ extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q,
                                             const float* latent_scale, const int32_t* block_table,
                                             const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
                                             uint16_t* out, float* out_m, float* out_lse, void* scratch,
-                                            int q_early, void* stream);
+                                            int q_early, int min_rows_hint, void* stream);
 extern "C" int rivoli_attend_mma_status(void* scratch, void* stream);
 
 RIVOLI_API size_t rivoli_mla_attend_paged_scratch_bytes(const DsaGeom* g, int B) {
@@ -40,10 +40,23 @@ RIVOLI_API int rivoli_mla_attend_paged_status(const DsaGeom* g, void* scratch, v
     return rivoli_attend_mma_status(scratch, stream);
 }
 
+static cudaEvent_t g_timing_events[5];
+static bool g_timing_on = false;
+extern "C" cudaEvent_t* rivoli_step_timing_events() { return g_timing_on ? g_timing_events : nullptr; }
+
+// events[0..5): CUDA events (cudaEvent_t) the following decode-step calls record around their kernels: 0 before the
+// prologue (append + query preparation), 1 before the scorer, 2 before the selection, 3 before the attention, 4 after
+// it. NULL switches the hook off. The records serialise the kernels (no programmatic overlap between them).
+RIVOLI_API void rivoli_dsa_step_set_timing_events(void* const* events) {
+    g_timing_on = events != nullptr;
+    if (events)
+        for (int i = 0; i < 5; ++i) g_timing_events[i] = (cudaEvent_t)events[i];
+}
+
 static int attend_paged_dispatch(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
                                  const float* latent_scale, const int32_t* block_table, const uint32_t* rows,
                                  int row_stride, const int32_t* n_rows, int B, uint16_t* out, float* out_m,
-                                 float* out_lse, void* scratch, int q_early, void* stream) {
+                                 float* out_lse, void* scratch, int q_early, int min_rows_hint, void* stream) {
     if (int e = rv_check_geom(g)) return e;
     if (B <= 0 || !q || !latent_pool || !latent_scale || !block_table || !n_rows || !out) return 1001;
     if (rows && row_stride <= 0) return 1001;
@@ -52,7 +65,7 @@ static int attend_paged_dispatch(const DsaGeom* g, const uint16_t* q, const uint
     // Every other geometry runs on the CUDA-core kernel.
     if (scratch && rivoli_attend_mma_supported(g))
         return rivoli_attend_mma_paged_bf16(g, q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
-                                            B, out, out_m, out_lse, scratch, q_early, stream);
+                                            B, out, out_m, out_lse, scratch, q_early, min_rows_hint, stream);
     return rivoli_attend_simt_paged_bf16(g, q, latent_pool, latent_scale, block_table, rows, row_stride,
                                          n_rows, B, out, out_m, out_lse, scratch, stream);
 }
@@ -65,26 +78,32 @@ RIVOLI_API int rivoli_mla_attend_paged_bf16(const DsaGeom* g, const uint16_t* q,
     // q may have been written by the kernel launched just before this call: the attention kernel reads it
     // only after its dependency wait.
     return attend_paged_dispatch(g, q, latent_pool, latent_scale, block_table, rows, row_stride, n_rows, B, out, out_m,
-                                 out_lse, scratch, 0, stream);
+                                 out_lse, scratch, 0, 0, stream);
 }
 
 // One decode layer-step in one call: append the step's token of every sequence, select the attended rows,
 // attend over them. q is an input of the CALL, so it is complete before the first kernel of the call starts
-// and the attention kernel may convert it while the selection kernel is still running.
+// and the attention kernel may convert it while the selection kernel is still running. min_rows_hint: a lower
+// bound the caller's scheduler knows for min(top_k, seq_len[b]) over the batch (0 = unknown); from 128 on, the
+// launch of the short-context attention arm is left out.
 RIVOLI_API int rivoli_dsa_decode_step_paged(const DsaGeom* g, const uint16_t* latent, const uint16_t* index_key,
                                             const int32_t* row_pos, const int32_t* block_table, uint8_t* latent_pool,
                                             float* latent_scale, uint8_t* index_pool, float* index_scale,
                                             int32_t* status, const uint16_t* index_q, const float* w,
                                             const int32_t* seq_len, int B, int score_stride, uint32_t* rows,
                                             int32_t* n_sel, void* select_scratch, const uint16_t* q, uint16_t* out,
-                                            float* out_m, float* out_lse, void* attend_scratch, void* stream) {
+                                            float* out_m, float* out_lse, void* attend_scratch, int min_rows_hint,
+                                            void* stream) {
     if (!q || !out || !rows || !n_sel || !g) return 1001;
     if (int e = rivoli_dsa_append_select_paged(g, latent, index_key, row_pos, block_table, latent_pool, latent_scale,
                                                index_pool, index_scale, status, index_q, w, seq_len, B, score_stride,
                                                rows, n_sel, select_scratch, stream))
         return e;
-    return attend_paged_dispatch(g, q, latent_pool, latent_scale, block_table, rows, g->top_k, n_sel, B, out, out_m,
-                                 out_lse, attend_scratch, 1, stream);
+    rv_stage_event(3, (cudaStream_t)stream);
+    const int e = attend_paged_dispatch(g, q, latent_pool, latent_scale, block_table, rows, g->top_k, n_sel, B, out, out_m,
+                                        out_lse, attend_scratch, 1, min_rows_hint, stream);
+    rv_stage_event(4, (cudaStream_t)stream);
+    return e;
 }
 
 // out[v] = sum_g w_g * part_out[g][v] / sum_g w_g,  w_g = exp(lse_g - max_g lse), ascending g.
@@ -116,6 +135,30 @@ RIVOLI_API int rivoli_attend_merge_partials(const uint16_t* part_out, const floa
     if (G > 64) return 1002;
     rv_drain_error();
     merge_partials_kernel<<<(n_vec + 7) / 8, 256, 0, (cudaStream_t)stream>>>(part_out, part_lse, G, n_vec, kvl, out);
+    return rv_launch_status();
+}
+
+// Rows a layer serves under the one-step-stale selection (crates/engine/src/indexer.rs:14-63, batched): per sequence
+// mode 0 = the rows stored at the previous token, verbatim; 1 = this token's fresh rows; 2 = dense over the whole
+// prefix (first entry = the dense marker 0xFFFFFFFF, which the attention kernels read as "row j = token j").
+__global__ void stale_compose_kernel(const uint32_t* __restrict__ prev_rows, const int32_t* __restrict__ prev_n,
+                                     const uint32_t* __restrict__ cur_rows, const int32_t* __restrict__ cur_n,
+                                     const int32_t* __restrict__ mode, const int32_t* __restrict__ seq_len, int k,
+                                     uint32_t* __restrict__ out_rows, int32_t* __restrict__ out_n) {
+    const int b = blockIdx.x, m = mode[b];
+    const uint32_t* src = m == 0 ? prev_rows + (size_t)b * k : cur_rows + (size_t)b * k;
+    const int n = m == 0 ? prev_n[b] : (m == 1 ? cur_n[b] : seq_len[b]);
+    for (int j = threadIdx.x; j < k; j += blockDim.x) out_rows[(size_t)b * k + j] = (m == 2 && j == 0) ? 0xffffffffu : src[j];
+    if (threadIdx.x == 0) out_n[b] = n;
+}
+
+RIVOLI_API int rivoli_stale_compose_rows(const uint32_t* prev_rows, const int32_t* prev_n, const uint32_t* cur_rows,
+                                         const int32_t* cur_n, const int32_t* mode, const int32_t* seq_len, int B, int k,
+                                         uint32_t* out_rows, int32_t* out_n, void* stream) {
+    if (B <= 0 || k <= 0 || !prev_rows || !prev_n || !cur_rows || !cur_n || !mode || !seq_len || !out_rows || !out_n)
+        return 1001;
+    rv_drain_error();
+    stale_compose_kernel<<<B, 256, 0, (cudaStream_t)stream>>>(prev_rows, prev_n, cur_rows, cur_n, mode, seq_len, k, out_rows, out_n);
     return rv_launch_status();
 }
 

@@ -221,8 +221,10 @@ attend_mma_kernel(AttendMmaArgs A) {
     // that kernel's tail; the selected rows and their counts are read below.
     rv_grid_dep_wait();
     int nr = A.n_rows[b];
+    // a row list whose first entry is the dense marker stands for "row j = token j" over the first n_rows tokens
+    const bool listed = A.rows && A.rows[(size_t)b * A.row_stride] != 0xffffffffu;
     {
-        const long long cap = A.rows ? A.row_stride : (long long)A.max_pages * P;
+        const long long cap = listed ? A.row_stride : (long long)A.max_pages * P;
         nr = (int)max(0LL, min((long long)nr, cap));
     }
     // Short contexts belong to the CUDA-core kernel launched by the same call: this CTA touches no output.
@@ -249,7 +251,7 @@ attend_mma_kernel(AttendMmaArgs A) {
         // iteration, so no copy waits on it: t_n = token two tiles on, r_n = pool row one tile on,
         // (src, scale) = the current tile ("tile" = the group's own sequence j, j+2, j+4, ...).
         constexpr uint32_t NONE = 0xffffffffu;
-        const uint32_t* rowp = A.rows ? A.rows + (size_t)b * A.row_stride : nullptr;
+        const uint32_t* rowp = listed ? A.rows + (size_t)b * A.row_stride : nullptr;
         const int32_t* btp = A.block_table + (size_t)b * A.max_pages;
         auto load_t = [&](int j, int p) -> uint32_t {
             const int ri = r_begin + j * AM_TILE + p;
@@ -642,7 +644,8 @@ extern "C" size_t rivoli_attend_mma_scratch_bytes(const DsaGeom* g, int B) {
 
 extern "C" void rivoli_attend_combine_paged(const float* partial, int H, int kvl, int n_splits, int B, uint16_t* out,
                                             float* out_m, float* out_lse, const int32_t* n_rows, long long cap,
-                                            int rows_lo, int rows_hi, int serve_empty, cudaStream_t st);
+                                            int rows_lo, int rows_hi, int serve_empty, const uint32_t* rows,
+                                            long long row_stride, long long dense_cap, cudaStream_t st);
 extern "C" int rivoli_attend_simt_short_rows(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
                                              const float* latent_scale, const int32_t* block_table,
                                              const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
@@ -670,11 +673,13 @@ extern "C" __attribute__((visibility("default"))) void rivoli_attend_mma_test_ho
 
 // q_early != 0: the caller guarantees q was complete before the kernel preceding this call in the stream
 // was launched (the fused decode step), so the query conversion may overlap that kernel's tail.
+// min_rows_hint: a lower bound the caller knows for n_rows over the batch (0 = unknown). With a bound of
+// AM_MIN_ROWS or more no sequence needs the CUDA-core arm and its launch is left out.
 extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
                                             const float* latent_scale, const int32_t* block_table,
                                             const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
                                             uint16_t* out, float* out_m, float* out_lse, void* scratch,
-                                            int q_early, void* stream) {
+                                            int q_early, int min_rows_hint, void* stream) {
     if (!scratch) return 1001;
     if (((uintptr_t)latent_pool | (uintptr_t)scratch | (uintptr_t)q | (uintptr_t)out) & 15) return 1005;
     cudaStream_t st = (cudaStream_t)stream;
@@ -682,7 +687,8 @@ extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q,
     int* err = reinterpret_cast<int*>(sp);
     float* partial = reinterpret_cast<float*>(sp + 256);
     const int n_splits = mma_splits(B);
-    const int min_rows = g_am_min_rows_override >= 0 ? g_am_min_rows_override : AM_MIN_ROWS;
+    int min_rows = g_am_min_rows_override >= 0 ? g_am_min_rows_override : AM_MIN_ROWS;
+    if (min_rows_hint >= min_rows) min_rows = 0;          // the caller vouches that no sequence is that short
     const int withhold = g_am_withhold_once;
     g_am_withhold_once = 0;
 
@@ -702,7 +708,8 @@ extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q,
     if (int e = rv_launch_status()) return e;
     if (n_splits > 1) {
         const long long cap = rows ? (long long)row_stride : (long long)g->max_pages_per_seq * g->page_tokens;
-        rivoli_attend_combine_paged(partial, AM_H, AM_KVL, n_splits, B, out, out_m, out_lse, n_rows, cap, min_rows, 0x7fffffff, 1, st);
+        rivoli_attend_combine_paged(partial, AM_H, AM_KVL, n_splits, B, out, out_m, out_lse, n_rows, cap, min_rows, 0x7fffffff, 1,
+                                    rows, row_stride, (long long)g->max_pages_per_seq * g->page_tokens, st);
         return rv_launch_status();
     }
     return 0;

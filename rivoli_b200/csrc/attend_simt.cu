@@ -55,6 +55,8 @@ attend_simt_kernel(AttSlab sp, AttPaged pp, int H, int hg, int kvl, int rope, fl
         rv_grid_dep_trigger();             // a dependent kernel may set itself up; it waits for this grid before reading
         rv_grid_dep_wait();                // the counts (and rows) may come from the kernel before
         nr = pp.n_rows[b];
+        // a row list whose first entry is the dense marker stands for "row j = token j" over the first n_rows tokens
+        if (pp.rows && pp.rows[(size_t)b * pp.row_stride] == 0xffffffffu) pp.rows = nullptr;
         const long long cap = pp.rows ? pp.row_stride : (long long)pp.max_pages * pp.page_tokens;
         nr = (int)max(0LL, min((long long)nr, cap));
         if (nr < pp.rows_lo || nr >= pp.rows_hi) return;   // another kernel of the same call serves this sequence
@@ -194,11 +196,13 @@ template <bool PAGED>
 __global__ void __launch_bounds__(128)
 attend_combine_kernel(const float* __restrict__ partial, int H, int kvl, int n_splits, float* __restrict__ clat,
                       uint16_t* __restrict__ out, float* __restrict__ out_m, float* __restrict__ out_lse,
-                      const int32_t* __restrict__ n_rows, long long cap, int rows_lo, int rows_hi, int serve_empty) {
+                      const int32_t* __restrict__ n_rows, long long cap, int rows_lo, int rows_hi, int serve_empty,
+                      const uint32_t* __restrict__ rows, long long row_stride, long long dense_cap) {
     __shared__ float w[AT_MAX_SPLITS];
     __shared__ float inv_l;
     const int head = blockIdx.x, b = blockIdx.y;
     if (PAGED && n_rows) {   // same clamp and range rule as the kernels that wrote the partials
+        if (rows && rows[(size_t)b * row_stride] == 0xffffffffu) cap = dense_cap;   // dense marker: see the attention kernels
         const int nr = (int)max(0LL, min((long long)n_rows[b], cap));
         if ((nr < rows_lo || nr >= rows_hi) && !(nr == 0 && serve_empty)) return;
     }
@@ -268,7 +272,8 @@ static int launch_attend_simt(const AttSlab& sp, const AttPaged& pp, int H, int 
     const long long cap = PAGED ? (pp.rows ? pp.row_stride : (long long)pp.max_pages * pp.page_tokens) : 0;
     attend_combine_kernel<PAGED><<<dim3(H, B), 128, 0, st>>>(partial, H, kvl, n_splits, sp.clat, pp.out,
                                                               pp.out_m, pp.out_lse, PAGED ? pp.n_rows : nullptr, cap,
-                                                              pp.rows_lo, pp.rows_hi, 0);
+                                                              pp.rows_lo, pp.rows_hi, 0, pp.rows, pp.row_stride,
+                                                              (long long)pp.max_pages * pp.page_tokens);
     return rv_launch_status();
 }
 
@@ -277,9 +282,11 @@ static int launch_attend_simt(const AttSlab& sp, const AttPaged& pp, int H, int 
 // that an empty sequence is served when serve_empty is set.
 extern "C" void rivoli_attend_combine_paged(const float* partial, int H, int kvl, int n_splits, int B, uint16_t* out,
                                             float* out_m, float* out_lse, const int32_t* n_rows, long long cap,
-                                            int rows_lo, int rows_hi, int serve_empty, cudaStream_t st) {
+                                            int rows_lo, int rows_hi, int serve_empty, const uint32_t* rows,
+                                            long long row_stride, long long dense_cap, cudaStream_t st) {
     attend_combine_kernel<true><<<dim3(H, B), 128, 0, st>>>(partial, H, kvl, n_splits, nullptr, out, out_m, out_lse,
-                                                            n_rows, cap, rows_lo, rows_hi, serve_empty);
+                                                            n_rows, cap, rows_lo, rows_hi, serve_empty, rows, row_stride,
+                                                            dense_cap);
 }
 
 RIVOLI_API size_t rivoli_mla_attend_scratch_floats(int H, int kvl) {

@@ -36,6 +36,16 @@ static inline void rv_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3
 }
 #endif
 
+// Measurement hook (rivoli_dsa_step_set_timing_events): when set, the decode-step entry points record event k
+// on their stream before kernel k of the step (and the last one after it), so that a benchmark can read each
+// kernel's own duration. An event record between two launches also takes away their programmatic overlap,
+// which is what a per-kernel time wants; it is off (NULL) in every other use.
+extern "C" cudaEvent_t* rivoli_step_timing_events();
+static inline void rv_stage_event(int k, cudaStream_t st) {
+    cudaEvent_t* ev = rivoli_step_timing_events();
+    if (ev) (void)cudaEventRecord(ev[k], st);
+}
+
 static inline bool rv_is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
 
 // Geometry guard shared by every paged entry point. Decided on the host; nothing is

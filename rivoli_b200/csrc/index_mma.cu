@@ -409,6 +409,7 @@ static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* i
     }
 
     rv_drain_error();
+    rv_stage_event(0, st);
     if (ap)
         step_prologue_kernel<<<B + (B + 31) / 32, 1024, 0, st>>>(*g, *ap, B, index_q, w, s.qcodes, s.qscales, s.cb,
                                                                  s.err);
@@ -432,8 +433,10 @@ static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* i
                                              (uint32_t)g->page_tokens))
         return e;
     if (int e = rivoli::make_tmap_rows_sw128(&tm_q, s.qcodes, (uint64_t)B * nh, IM_HD, (uint32_t)nh)) return e;
+    rv_stage_event(1, st);
     rv_launch_dependent(index_score_mma_kernel, dim3(grid), dim3(IM_THREADS), smem1, st, ma, tm_keys, tm_q);
     if (int e = rv_launch_status()) return e;
+    rv_stage_event(2, st);
 
     const SelArgs ra{*g, s.scores, score_stride, seq_len, s.qcodes, s.qscales, w, s.cb,
                      index_pool, index_scale, block_table, rows, n_sel, g->top_k, s.stats,
@@ -471,6 +474,16 @@ RIVOLI_API int rivoli_dsa_append_select_paged(const DsaGeom* g, const uint16_t* 
     const AppendArgs ap{latent, index_key, row_pos, block_table, latent_pool, latent_scale, index_pool, index_scale, status};
     return select_impl(g, &ap, index_q, w, index_pool, index_scale, block_table, seq_len, B, score_stride, rows, n_sel,
                        scratch, stream);
+}
+
+// Where the last rivoli_index_select_paged call on `scratch` left the query codes and their scales (both paths
+// of that call fill them): read by the page-range shard step, which re-scores its candidates exactly.
+extern "C" void rivoli_index_select_query_codes(const DsaGeom* g, int B, int score_stride, void* scratch,
+                                                const uint8_t** qcodes, const float** qscales) {
+    size_t total = 0;
+    SelectScratch s = carve(g, B, score_stride, scratch, &total);
+    *qcodes = s.qcodes;
+    *qscales = s.qscales;
 }
 
 // Reads back the tensor-core scorer's error word and clears it: 1005 = a block-table entry inside a

@@ -31,9 +31,9 @@
 
 #include "codec.cuh"
 #include "common.cuh"
+#include "index_rescore.cuh"
 #include "index_select.hpp"
 #include "topk_core.cuh"
-#include <type_traits>
 
 namespace cg = cooperative_groups;
 
@@ -43,7 +43,7 @@ constexpr int SEL_THREADS = 512, SEL_WARPS = SEL_THREADS / 32;
 constexpr int SEL_BINS = 4096;
 constexpr int SEL_LIST = 2048;     // band tokens per SEQUENCE the fast path holds (and per chunk on the slow path)
 constexpr int SEL_TOK = 4;         // band tokens a warp re-scores per pass
-constexpr int SEL_HD = 128;        // index dim (one code word per lane)
+constexpr int SEL_HD = RS_HD;      // index dim (one code word per lane)
 
 struct SelXc {                     // per-CTA exchange block; slot q of an array is written by rank q (its own copy in phase 1)
     uint32_t kmin[SEL_MAX_CLUSTER], kmax[SEL_MAX_CLUSTER], skmax[SEL_MAX_CLUSTER];
@@ -180,14 +180,7 @@ index_select_cluster_kernel(SelArgs A) {
             skm = fmaxf(skm, sk[j]);
         }
     }
-    // q codes as f32, transposed to [dim][head] (lane = head on both sides: no bank conflicts)
-    for (int e = tid; e < 32 * (hd / 4); e += SEL_THREADS) {
-        const int h = e & 31, d4 = e >> 5;
-        const uint32_t cw = h < nh ? *reinterpret_cast<const uint32_t*>(A.qcodes + ((size_t)b * nh + h) * hd + d4 * 4) : 0u;
-        const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw >> 16));
-        qf[(d4 * 4 + 0) * 32 + h] = x.x; qf[(d4 * 4 + 1) * 32 + h] = x.y;
-        qf[(d4 * 4 + 2) * 32 + h] = y.x; qf[(d4 * 4 + 3) * 32 + h] = y.y;
-    }
+    rv_rescore_stage_q(A.qcodes + (size_t)b * nh * hd, nh, qf);
     for (int i = tid; i < SEL_BINS; i += SEL_THREADS) hist[i] = 0u;
     if (tid == 0) xc.list_n = 0;
     int buf = 0;
@@ -350,75 +343,13 @@ index_select_cluster_kernel(SelArgs A) {
     // this lane's head constants for the exact re-score (nh <= 32)
     const float my_sq = lane < nh ? A.qscales[(size_t)b * nh + lane] : 0.0f;
     const float my_wh = lane < nh ? __fmul_rn(A.w[(size_t)b * nh + lane], g.index_wscale) : 0.0f;
-    // Exact score of the first `ln` listed tokens: a pass covers 16 * SEL_TOK of them, warp w taking positions
-    // base + w, base + 16 + w, ... (their loads are in flight together and they share the q reads); lane =
-    // head; the code dot is the sequential f32 fold of rivoli_index_score_paged, heads fold ascending.
+    // Exact key of the first `ln` listed tokens -> l_key[position] (0 and ~0 are reserved for "surely out" / "surely in").
     auto rescore = [&](uint32_t ln) {
-        float* kf = kfw + warp * (SEL_TOK * hd);
-        for (uint32_t base = 0; base < ln; base += SEL_WARPS * SEL_TOK) {
-            if (base + warp >= ln) break;
-            const int n_here = min(SEL_TOK, (int)((ln - base - warp + SEL_WARPS - 1) / SEL_WARPS));   // warp-uniform, >= 1
-            uint32_t cw[SEL_TOK];
-            float skv[SEL_TOK];
-#pragma unroll
-            for (int e = 0; e < SEL_TOK; ++e) {
-                cw[e] = 0u; skv[e] = 0.0f;
-                if (e < n_here) {
-                    const int t = (int)l_tok[base + e * SEL_WARPS + warp];
-                    int pg = bt[t / P];
-                    pg = (pg < 0 || pg >= g.n_pool_pages) ? 0 : pg;
-                    const size_t rr = (size_t)pg * P + (t & (P - 1));
-                    cw[e] = *reinterpret_cast<const uint32_t*>(A.index_pool + rr * hd + lane * 4);
-                    skv[e] = A.index_scale[rr];
-                }
-            }
-#pragma unroll
-            for (int e = 0; e < SEL_TOK; ++e) {
-                const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw[e] & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw[e] >> 16));
-                *reinterpret_cast<float4*>(kf + e * hd + lane * 4) = make_float4(x.x, x.y, y.x, y.y);
-            }
-            __syncwarp();
-            float cd[SEL_TOK];
-#pragma unroll
-            for (int e = 0; e < SEL_TOK; ++e) cd[e] = 0.0f;
-            auto fold = [&](auto ntok) {
-                constexpr int NT = decltype(ntok)::value;
-#pragma unroll 4
-                for (int d = 0; d < hd; d += 4) {
-                    const float q0f = qf[(d + 0) * 32 + lane], q1f = qf[(d + 1) * 32 + lane];
-                    const float q2f = qf[(d + 2) * 32 + lane], q3f = qf[(d + 3) * 32 + lane];
-#pragma unroll
-                    for (int e = 0; e < NT; ++e) {
-                        const float4 k4 = *reinterpret_cast<const float4*>(kf + e * hd + d);   // broadcast read
-                        cd[e] = fmaf(q0f, k4.x, cd[e]);
-                        cd[e] = fmaf(q1f, k4.y, cd[e]);
-                        cd[e] = fmaf(q2f, k4.z, cd[e]);
-                        cd[e] = fmaf(q3f, k4.w, cd[e]);
-                    }
-                }
-            };
-            if (n_here >= 4) fold(std::integral_constant<int, 4>{});
-            else if (n_here == 1) fold(std::integral_constant<int, 1>{});
-            else if (n_here == 2) fold(std::integral_constant<int, 2>{});
-            else fold(std::integral_constant<int, 3>{});
-            __syncwarp();
-#pragma unroll
-            for (int e = 0; e < SEL_TOK; ++e) {
-                const float dot = __fmul_rn(__fmul_rn(cd[e], my_sq), skv[e]);
-                float rr = __fmul_rn(dot, g.index_dscale);
-                rr = rr > 0.0f ? rr : 0.0f;
-                kf[e * hd + lane] = __fmul_rn(my_wh, rr);
-            }
-            __syncwarp();
-            if (lane < n_here) {
-                float acc = 0.0f;
-                for (int h = 0; h < nh; ++h) acc = __fadd_rn(acc, kf[lane * hd + h]);
-                uint32_t ku = topk_key(acc);
-                ku = ku == 0xffffffffu ? 0xfffffffeu : (ku == 0u ? 1u : ku);   // 0 and ~0 mean "surely out" / "surely in"
-                l_key[base + lane * SEL_WARPS + warp] = ku;
-            }
-            __syncwarp();
-        }
+        rv_rescore_listed<SEL_WARPS, SEL_TOK>(l_tok, ln, qf, kfw + warp * (SEL_TOK * hd), bt, g, A.index_pool, A.index_scale,
+                                              my_sq, my_wh, [&](uint32_t pos, float score) {
+            uint32_t ku = topk_key(score);
+            l_key[pos] = ku == 0xffffffffu ? 0xfffffffeu : (ku == 0u ? 1u : ku);
+        });
     };
     // ascending write-out of this CTA's tokens whose bit is set in `sel`, from slot `base` on (one barrier)
     auto write_out = [&](uint32_t sel, uint32_t base) {
@@ -596,9 +527,12 @@ index_select_cluster_kernel(SelArgs A) {
 
 namespace rivoli {
 
+static int g_sel_cluster_override = 0;
+
 bool select_cluster_plan(int B, int score_stride, int* cluster, int* ept) {
     int C = 1;
     while (C < SEL_MAX_CLUSTER && (long long)B * C * 2 <= 2 * 148) C *= 2;     // about two CTAs per SM at most
+    if (g_sel_cluster_override > 0) C = g_sel_cluster_override;
     for (;;) {
         for (int e = 4; e <= 32; e *= 2)
             if ((long long)C * SEL_THREADS * e >= score_stride) { *cluster = C; *ept = e; return true; }
@@ -606,6 +540,16 @@ bool select_cluster_plan(int B, int score_stride, int* cluster, int* ept) {
         C *= 2;
     }
 }
+
+}  // namespace rivoli
+
+// Test hook: force the cluster size of the following selection launches (1, 2, 4 or 8; 0 = the plan's own choice),
+// so that every cluster size can be exercised at any batch size.
+extern "C" __attribute__((visibility("default"))) void rivoli_index_select_test_cluster(int cluster) {
+    rivoli::g_sel_cluster_override = (cluster == 1 || cluster == 2 || cluster == 4 || cluster == 8) ? cluster : 0;
+}
+
+namespace rivoli {
 
 int launch_index_select_cluster(const SelArgs& a, int B, cudaStream_t st) {
     int C = 1, ept = 4;

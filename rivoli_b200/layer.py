@@ -126,16 +126,17 @@ class DsaDecodeLayer:
         return out
 
     def step(self, latent, index_key, index_q, index_w, q, row_pos, seq_len, stream=None,
-             out: torch.Tensor | None = None) -> torch.Tensor:
+             out: torch.Tensor | None = None, min_rows_hint: int = 0) -> torch.Tensor:
         """One layer-step in one library call: append one token per sequence, select, attend (the append
         rides in the launch that prepares the indexer query; the attention kernel converts ``q`` while the
-        selection is still running, which the one-call form makes safe)."""
+        selection is still running, which the one-call form makes safe). ``min_rows_hint``: a lower bound the
+        caller's scheduler knows for ``min(top_k, seq_len)`` over the batch (0 = unknown)."""
         out = self.out if out is None else out
         be.launch_dsa_decode_step_paged(self.g, latent, index_key, row_pos, self.block_table, self.latent_pool,
                                         self.latent_scale, self.index_pool, self.index_scale, self.status,
                                         index_q, index_w, seq_len, self.B, self.score_stride, self.rows,
                                         self.n_sel, self.select_scratch, q, out, self.out_m, self.out_lse,
-                                        self.scratch, stream)
+                                        self.scratch, min_rows_hint, stream)
         return out
 
     def check_status(self) -> None:
@@ -199,64 +200,56 @@ class IndexerFrontEnd:
 
 
 class HostStepPipeline:
-    """Layer-steps for a caller whose activations live in HOST memory (pinned): every step
-    copies its inputs host->device, runs append -> select -> attend, and copies the attention
-    output device->host. The three legs run on three streams with two device-side slots, so the
-    upload of step ``i+1`` and the download of step ``i-1`` overlap the kernels of step ``i``;
-    within a stream everything stays in program order, so results equal the serial order.
+    """Layer-steps for a caller whose activations live in HOST memory (pinned): a thin caller of the library's
+    ``rivoli_dsa_step_host``. Every step copies ONE packed input buffer host->device, runs the fused decode step
+    and copies the attention output device->host; the three legs run on three streams with ``depth`` device-side
+    slots inside the library, so the upload of step ``i+1`` and the download of step ``i-1`` overlap the kernels
+    of step ``i`` and results equal the serial order.
 
-    The caller owns the pinned host buffers and must not reuse an output buffer before
-    ``wait(ticket)`` (or ``drain()``) has returned for the step that fills it.
-    """
+    ``pack`` lays the five inputs out in one pinned buffer (the layout ``rivoli_step_pipe_input_offsets``
+    gives). The caller owns the pinned buffers and must not reuse an output buffer before ``wait(ticket)`` (or
+    ``drain()``) has returned for the step that fills it. The layer's pools and the ``row_pos`` / ``seq_len``
+    device arrays must be complete before the first ``submit`` (the pipe's streams do not synchronise with
+    other streams)."""
     KEYS = ("latent", "index_key", "index_q", "index_w", "q")
 
-    def __init__(self, layer: DsaDecodeLayer, depth: int = 2):
+    def __init__(self, layer: DsaDecodeLayer, depth: int = 2, min_rows_hint: int = 0):
         self.layer, self.depth = layer, depth
-        g, B, d = layer.g, layer.B, layer.dev
-        W = g.kv_lora + g.rope_dim
-        bf, f32 = torch.bfloat16, torch.float32
-        shapes = dict(latent=((B, W), bf), index_key=((B, g.index_dim), bf),
-                      index_q=((B, g.index_heads, g.index_dim), bf), index_w=((B, g.index_heads), f32),
-                      q=((B, g.n_heads, W), bf))
-        self.slots = [{k: torch.empty(s, dtype=t, device=d) for k, (s, t) in shapes.items()} for _ in range(depth)]
-        self.outs = [torch.empty((B, g.n_heads, g.kv_lora), dtype=bf, device=d) for _ in range(depth)]
-        with torch.cuda.device(d):
-            self.s_up, self.s_run, self.s_down = (torch.cuda.Stream(d) for _ in range(3))
-            mk = lambda: [torch.cuda.Event() for _ in range(depth)]
-            self.ev_up, self.ev_run, self.ev_down = mk(), mk(), mk()
-        self.n = 0
+        self.pipe = be.StepPipe(layer.g, layer.B, depth)
+        L = layer
+        p = lambda t: t.data_ptr()
+        self.state = be.DsaStepState(p(L.block_table), p(L.latent_pool), p(L.latent_scale), p(L.index_pool),
+                                     p(L.index_scale), p(L.status), p(L.rows), p(L.n_sel), p(L.select_scratch),
+                                     p(L.scratch), p(L.out_m), p(L.out_lse), L.score_stride, min_rows_hint)
 
-    def submit(self, host_in: dict, host_out: torch.Tensor, row_pos: torch.Tensor, seq_len: torch.Tensor) -> int:
+    def new_input_buffer(self) -> torch.Tensor:
+        return torch.zeros(self.pipe.input_bytes, dtype=torch.uint8).pin_memory()
+
+    def new_output_buffer(self) -> torch.Tensor:
+        g = self.layer.g
+        return torch.zeros((self.layer.B, g.n_heads, g.kv_lora), dtype=torch.bfloat16).pin_memory()
+
+    def pack(self, host_in: dict, buf: torch.Tensor | None = None) -> torch.Tensor:
+        """Copy the five host tensors into one packed pinned buffer (host-side memcpy)."""
+        buf = self.new_input_buffer() if buf is None else buf
+        for k in self.KEYS:
+            src = host_in[k].contiguous().view(torch.uint8).reshape(-1)
+            o = self.pipe.offsets[k]
+            buf[o:o + src.numel()].copy_(src)
+        return buf
+
+    def submit(self, packed_in: torch.Tensor, host_out: torch.Tensor, row_pos: torch.Tensor, seq_len: torch.Tensor) -> int:
         """Enqueue one layer-step; returns a ticket for ``wait``. Never blocks the host."""
-        L, s = self.layer, self.n % self.depth
-        first = self.n < self.depth
-        if not first:
-            self.s_up.wait_event(self.ev_run[s])        # the step that last read this input slot is done
-        with torch.cuda.stream(self.s_up):
-            for k in self.KEYS:
-                self.slots[s][k].copy_(host_in[k], non_blocking=True)
-            self.ev_up[s].record(self.s_up)
-        self.s_run.wait_event(self.ev_up[s])
-        if not first:
-            self.s_run.wait_event(self.ev_down[s])      # this output slot has been downloaded
-        x = self.slots[s]
-        L.step(x["latent"], x["index_key"], x["index_q"], x["index_w"], x["q"], row_pos, seq_len,
-               stream=self.s_run, out=self.outs[s])
-        self.ev_run[s].record(self.s_run)
-        self.s_down.wait_event(self.ev_run[s])
-        with torch.cuda.stream(self.s_down):
-            host_out.copy_(self.outs[s], non_blocking=True)
-            self.ev_down[s].record(self.s_down)
-        self.n += 1
-        return self.n - 1
+        return self.pipe.submit(self.state, packed_in, host_out, row_pos, seq_len)
 
     def wait(self, ticket: int) -> None:
-        """Block until the output of step ``ticket`` is in its host buffer (the slot's event belongs to
-        that step or to a later one on the same in-order stream, which implies it)."""
-        self.ev_down[ticket % self.depth].synchronize()
+        self.pipe.wait(ticket)
 
     def drain(self) -> None:
-        self.s_down.synchronize()
+        self.pipe.drain()
+
+    def leg_ms(self):
+        return self.pipe.leg_ms()
 
 
 def bf16_bits(t: torch.Tensor) -> np.ndarray:

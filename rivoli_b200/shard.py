@@ -125,36 +125,55 @@ def page_range_step(ops: ShardOps, index_q, index_w, q, local_len: torch.Tensor,
     return out, rows_global, n_mine
 
 
-def gpu_shard_ops(layer) -> ShardOps:
-    """The CUDA library as the arithmetic of a page-range shard. ``layer`` is this rank's
-    ``DsaDecodeLayer`` holding the rank's slice of every sequence at local positions 0..n-1."""
-    from . import backend as be
-    g, B, dev = layer.g, layer.B, layer.dev
+class ShardedDecodeStep:
+    """A page-range shard's layer-step through the CUDA library (``rivoli_shard_*``): this rank's ``DsaDecodeLayer``
+    holds its slice of every sequence at local positions ``0 .. n-1``. ``step`` runs the three phases around two
+    NCCL all-gathers inside the library (``rivoli_shard_step_paged``) on the communicator created by
+    ``nccl_comm``; ``candidates`` / ``cut_attend`` / ``merge`` are the phases on their own, for a host that
+    exchanges the two small buffers itself."""
 
-    def score(index_q, index_w, local_len):
-        be.launch_index_q_quant(index_q, B * g.index_heads, g.index_dim, layer.qcodes, layer.qscales)
-        be.launch_index_score_paged(g, layer.qcodes, layer.qscales, index_w, layer.index_pool, layer.index_scale,
-                                    layer.block_table, local_len, B, layer.scores, layer.score_stride)
-        return layer.scores
+    def __init__(self, layer, rank: int, world: int, comm: int = 0):
+        from . import backend as be
+        self.be, self.layer, self.rank, self.world, self.comm = be, layer, rank, world, comm
+        g, B, d = layer.g, layer.B, layer.dev
+        u8 = torch.uint8
+        self.shard_scratch = torch.zeros(be.shard_scratch_bytes(g, B, world), dtype=u8, device=d)
+        self.cand = torch.zeros(be.shard_candidate_bytes(g, B), dtype=u8, device=d)
+        self.part = torch.zeros(be.shard_partial_bytes(g, B), dtype=u8, device=d)
+        self.rows_l = torch.zeros((B, g.top_k), dtype=torch.int32, device=d)
+        self.rows_att = torch.zeros((B, g.top_k), dtype=torch.int32, device=d)
+        self.n_mine = torch.zeros(B, dtype=torch.int32, device=d)
+        self.out = torch.zeros((B, g.n_heads, g.kv_lora), dtype=torch.bfloat16, device=d)
 
-    def topk(scores, lens, k):
-        rows = torch.zeros((B, k), dtype=torch.int32, device=dev)
-        n = torch.zeros(B, dtype=torch.int32, device=dev)
-        scores = scores.contiguous()
-        be.launch_index_topk_batched(scores, scores.shape[1], lens.contiguous(), B, k, rows, n)
-        return rows, n
+    @staticmethod
+    def nccl_comm(rank: int, world: int, group=None) -> int:
+        """An NCCL communicator for the library: rank 0 makes the id, ``torch.distributed`` carries it."""
+        from . import backend as be
+        box = [be.shard_nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0, group=group)
+        return be.shard_nccl_comm_create(box[0], rank, world)
 
-    def attend(q, rows, n_rows):
-        rows = rows.contiguous()
-        be.launch_attend_paged_bf16(g, q, layer.latent_pool, layer.latent_scale, layer.block_table, rows,
-                                    rows.shape[1], n_rows.contiguous(), B, layer.out, layer.out_m, layer.out_lse,
-                                    layer.scratch)
-        return layer.out, layer.out_lse
+    def step(self, index_q, index_w, q, local_len, stream=None) -> torch.Tensor:
+        L, g = self.layer, self.layer.g
+        self.be.launch_shard_step_paged(g, self.comm, self.rank, self.world, index_q, index_w, q, L.latent_pool,
+                                        L.latent_scale, L.index_pool, L.index_scale, L.block_table, local_len, L.B,
+                                        L.score_stride, self.rows_l, self.rows_att, self.n_mine, self.out,
+                                        L.select_scratch, L.scratch, self.shard_scratch, stream)
+        return self.out
 
-    def merge(part_out, part_lse):
-        G, n_vec, kvl = part_out.shape
-        out = torch.empty((n_vec, kvl), dtype=torch.bfloat16, device=dev)
-        be.launch_attend_merge_partials(part_out.contiguous(), part_lse.contiguous(), G, n_vec, kvl, out)
-        return out
+    def candidates(self, index_q, index_w, local_len, stream=None) -> torch.Tensor:
+        L = self.layer
+        self.be.launch_shard_candidates(L.g, index_q, index_w, L.index_pool, L.index_scale, L.block_table, local_len, L.B,
+                                        L.score_stride, self.rows_l, L.select_scratch, self.cand, stream)
+        return self.cand
 
-    return ShardOps(score, topk, attend, merge)
+    def cut_attend(self, all_cand, q, stream=None) -> torch.Tensor:
+        L = self.layer
+        self.be.launch_shard_cut_attend(L.g, all_cand, self.rank, self.world, self.rows_l, q, L.latent_pool,
+                                        L.latent_scale, L.block_table, L.B, self.rows_att, self.n_mine, self.part,
+                                        self.shard_scratch, L.scratch, stream)
+        return self.part
+
+    def merge(self, all_part, stream=None) -> torch.Tensor:
+        self.be.launch_shard_merge(self.layer.g, all_part, self.world, self.layer.B, self.out, stream)
+        return self.out

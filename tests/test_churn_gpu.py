@@ -132,3 +132,83 @@ def test_shared_layers_attend_over_the_full_layers_selection():
         assert ok and rms <= 5e-3, (i, worst, rms)
         ok, worst = attend_close(outs[i].cpu().view(torch.int16).numpy().view(np.uint16), want)       # elementwise 2e-2 / 1e-3
         assert ok, (i, worst)
+
+
+def test_stale_selection_serves_the_previous_tokens_rows():
+    """The one-step-stale selection (crates/engine/src/indexer.rs:14-63), batched and on the device: a full layer
+    followed by a shared layer, three token-steps. Token t attends over the rows token t-1 selected (verbatim, the
+    new token's own row absent); a sequence at or below top_k (nothing stored) attends densely; a request that has
+    just taken its slot with a long context serves its fresh selection once. Checked against the oracle step by
+    step, for the full layer and for the shared layer that inherits the served rows."""
+    from rivoli_b200 import backend as be
+    from rivoli_b200.engine import DsaDecodeStack
+    from tests.helpers import State
+    be.lib()
+    k = 256
+    states = [State(70 + i, 3, [200, 257, 700], top_k=k) for i in range(2)]          # one cache content per layer
+    st0 = states[0]
+    og = st0.og
+    P = og.page_tokens
+    steps = 3
+    # room to grow: a pool and table sized for `steps` more tokens
+    max_pages = int((st0.seq_len.max() + steps + P - 1) // P)
+    g = make_geom(be.DsaGeom, **{**st0.geom_kw, "max_pages_per_seq": max_pages, "n_pool_pages": 3 * max_pages})
+    ogs = make_geom(orc.Geom, **{**st0.geom_kw, "max_pages_per_seq": max_pages, "n_pool_pages": 3 * max_pages})
+    stack = DsaDecodeStack(g, 3, [True, False], max_ctx=max_pages * P, stale=True)
+    W, hd = 576, 128
+    rows_n = 3 * max_pages * P
+    mirror = []
+    seq_len = st0.seq_len.astype(np.int32) - 1                                        # cached tokens before step 0
+    for b in range(3):
+        stack.pool.reserve(b, int(seq_len[b]))
+    bt = stack.pool.block_table()
+    for L, st in zip(stack.layers, states):
+        lp, ls = np.zeros(rows_n * W, np.uint8), np.zeros(rows_n, np.float32)
+        ip, isc = np.zeros(rows_n * hd, np.uint8), np.zeros(rows_n, np.float32)
+        assert orc.kv_append_paged(ogs, st.hist_latent, st.hist_key, st.hist_seq, st.hist_pos, bt, lp, ls, ip, isc) == 0
+        L.latent_pool.copy_(dev(lp)); L.latent_scale.copy_(dev(ls)); L.index_pool.copy_(dev(ip)); L.index_scale.copy_(dev(isc))
+        mirror.append(dict(lp=lp, ls=ls, ip=ip, isc=isc))
+    rng = np.random.RandomState(7)
+    prev_rows = [None] * 3
+    u16 = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16)
+    for step in range(steps):
+        for b in range(3):
+            stack.pool.reserve(b, int(seq_len[b]) + 1)
+        row_pos = seq_len.copy()
+        seq_len = seq_len + 1
+        bt = stack.pool.block_table()
+        stack.upload_block_table()
+        stack.begin_token(seq_len)
+        lat = [bf16_normal(rng, (3, W)) for _ in range(2)]
+        key, iq = bf16_normal(rng, (3, hd)), bf16_normal(rng, (3, 32, hd))
+        iw = orc.bf16_to_f32(bf16_normal(rng, (3, 32)))
+        q = [bf16_normal(rng, (3, 64, W)) for _ in range(2)]
+        outs = [stack.step_layer(0, dev(lat[0]), dev(key), dev(iq), dev(iw), dev(q[0]), dev(row_pos), dev(seq_len)).clone(),
+                stack.step_layer(1, dev(lat[1]), None, None, None, dev(q[1]), dev(row_pos), dev(seq_len)).clone()]
+        be.device_sync()
+        for L in stack.layers:
+            L.check_status()
+        # oracle: append, fresh selection of the full layer, the rows each sequence is SERVED
+        M0, M1 = mirror
+        assert orc.kv_append_paged(ogs, lat[0], key, None, row_pos, bt, M0["lp"], M0["ls"], M0["ip"], M0["isc"]) == 0
+        assert orc.kv_append_paged(ogs, lat[1], np.zeros_like(key), None, row_pos, bt, M1["lp"], M1["ls"], M1["ip"], M1["isc"]) == 0
+        qc, qs = orc.index_q_quant(iq, hd)
+        sc = orc.index_score_paged(ogs, qc, qs, iw, M0["ip"], M0["isc"], bt, seq_len, int(seq_len.max()))
+        fresh, n_fresh = orc.index_topk_batched(sc, seq_len, k)
+        stride = int(seq_len.max())
+        served = np.zeros((3, stride), np.uint32); n_served = np.zeros(3, np.int32)
+        for b in range(3):
+            if prev_rows[b] is not None:                      # stored at the previous token
+                r = prev_rows[b]
+            elif seq_len[b] <= k + 1:                         # nothing stored: dense over the whole prefix
+                r = np.arange(seq_len[b], dtype=np.uint32)
+            else:                                             # a fresh slot with a long context: its own selection, once
+                r = fresh[b, :n_fresh[b]]
+            served[b, :r.size] = r; n_served[b] = r.size
+            prev_rows[b] = fresh[b, :n_fresh[b]].copy() if seq_len[b] > k else None
+        for li, M in enumerate(mirror):
+            _, want, _, _ = orc.mla_attend_paged(ogs, q[li], M["lp"], M["ls"], bt, served, n_served, want_f32=True)
+            ok, worst = attend_close(u16(outs[li]), want)
+            assert ok, (step, li, worst)
+    # what was served really was the stale set: sequence 2 attended 256 rows that do NOT contain its newest token
+    assert n_served[2] == k and served[2, :k].max() < seq_len[2] - 1

@@ -515,3 +515,56 @@ def test_fused_step_call_equals_the_separate_operators(be):
         assert np.array_equal(a, b2)
     want = st.oracle_step()
     check_mma_attention(outs[0][0], want["out_f32"])
+
+
+def test_host_buffer_pipeline_equals_the_device_resident_step(be):
+    """rivoli_dsa_step_host: one packed pinned buffer up, fused step, bf16 output down, slots reused across steps.
+    Every step's output equals the device-resident call on the same state, bit for bit, and the cache advances
+    identically."""
+    from rivoli_b200.layer import DsaDecodeLayer, HostStepPipeline
+    st = State(50, 3, [900, 300, 2100], top_k=256)
+    P = st.og.page_tokens
+    steps = 5
+    max_pages = int((st.seq_len.max() + steps + P - 1) // P)
+    g = make_geom(be.DsaGeom, **{**st.geom_kw, "max_pages_per_seq": max_pages, "n_pool_pages": 3 * max_pages})
+    layers = []
+    for _ in range(2):
+        L = DsaDecodeLayer(g, st.B, max_ctx=max_pages * P, shuffle_seed=3)
+        for b in range(st.B):
+            L.reserve(b, int(st.seq_len[b]) + steps)
+        L.upload_block_table()
+        L.append(dev(st.hist_latent), dev(st.hist_key), dev(st.hist_pos), dev(st.hist_seq))
+        layers.append(L)
+    be.device_sync()
+    ref_layer, pipe_layer = layers
+    pipe = HostStepPipeline(pipe_layer, depth=2)
+    rng = np.random.RandomState(1)
+    W = 576
+    bufs = [pipe.new_input_buffer() for _ in range(steps)]
+    outs = [pipe.new_output_buffer() for _ in range(steps)]
+    pos_dev = [dev((st.seq_len - 1 + i).astype(np.int32)) for i in range(steps)]
+    len_dev = [dev((st.seq_len + i).astype(np.int32)) for i in range(steps)]
+    torch.cuda.synchronize()
+    want, tickets = [], []
+    for i in range(steps):
+        x = dict(latent=bf16_n(rng, (st.B, W)), index_key=bf16_n(rng, (st.B, 128)), index_q=bf16_n(rng, (st.B, 32, 128)),
+                 index_w=torch.from_numpy(orc.bf16_to_f32(orc.f32_to_bf16(rng.standard_normal((st.B, 32)).astype(np.float32)))),
+                 q=bf16_n(rng, (st.B, 64, W)))
+        pipe.pack(x, bufs[i])
+        tickets.append(pipe.submit(bufs[i], outs[i], pos_dev[i], len_dev[i]))        # never blocks
+        xd = {k: v.cuda() for k, v in x.items()}
+        want.append(u16(ref_layer.step(xd["latent"], xd["index_key"], xd["index_q"], xd["index_w"], xd["q"], pos_dev[i],
+                                       len_dev[i])).copy())
+    pipe.wait(tickets[1])
+    assert np.array_equal(u16(outs[1]), want[1])
+    pipe.drain()
+    ref_layer.check_status(); pipe_layer.check_status()
+    for i in range(steps):
+        assert np.array_equal(u16(outs[i]), want[i]), i
+    assert torch.equal(ref_layer.latent_pool, pipe_layer.latent_pool) and torch.equal(ref_layer.index_pool, pipe_layer.index_pool)
+    legs = pipe.leg_ms()
+    assert all(v >= 0.0 for v in legs.values())
+
+
+def bf16_n(rng, shape):
+    return torch.from_numpy(orc.f32_to_bf16(rng.standard_normal(shape).astype(np.float32)).view(np.int16)).view(torch.bfloat16)
