@@ -21,13 +21,13 @@
 // TMEM (512 columns): S double buffered (2 x 128) + O^T (4 x 64).
 //
 // One CTA per (sequence, split), 13 warps: 0-7 softmax + epilogue (TMEM lane group = warp % 4 =
-// tokens / dims, warps 0-3 own heads 0-31 and warps 4-7 heads 32-63), 8 MMA issue, 9-12 gather:
-// two independent groups of two warps, one per K buffer (even / odd tiles), so two tiles are in
-// flight whenever both buffers are free; a lane locates rows, copies go row by row with 32 lanes
+// tokens / dims, head group = warp / 4: warps 0-3 own heads 0-31 and warps 4-7 heads 32-63), 8 MMA issue,
+// 9-12 gather: two independent groups of two warps, one per K buffer (even / odd tiles), so two tiles
+// are in flight whenever both buffers are free; a lane locates rows, copies go row by row with 32 lanes
 // on 32 consecutive 16-byte chunks (cp.async into the swizzled tile); the row address chain
 // (token -> page -> pool row -> scale) is software-pipelined three tiles deep.
-// q arrives as bf16 and is split into its two e4m3 terms by warps 0-7 inside the kernel while the
-// first tiles are gathered; the output is staged in the idle K buffer and written as one block.
+// q arrives as bf16 and is split into its two e4m3 terms by the softmax warps inside the kernel while the
+// first tiles are gathered; the output leaves straight from the accumulator registers (64 contiguous bytes per warp store).
 // Online softmax with a LAGGING reference max: as long as no score of a tile exceeds its head's
 // reference by more than 3 (log2) the references stand (one barrier-with-OR per tile, no exchange);
 // otherwise the exact per-head maxima are taken and O is rescaled through TMEM. P' carries 2^5, so
@@ -41,8 +41,13 @@ namespace {
 
 constexpr int AM_TILE = 128;
 constexpr int AM_H = 64, AM_KVL = 512, AM_ROPE = 64, AM_W = AM_KVL + AM_ROPE;
-constexpr int AM_THREADS = 416;   // warps 0-7 softmax + epilogue, 8 MMA issue, 9-12 gather
-constexpr int AM_SOFTMAX_THREADS = 256;
+// softmax + epilogue warps: TMEM lane group = warp % 4, head group = warp / 4. 8 or 16: sixteen (16 heads per thread)
+// halve a tile's softmax work per warp but measured no faster (94.9 against 92.0 us at batch 128 x 2048 rows): the
+// chain is bound by latency between its stages, not by the softmax warps' issue rate.
+constexpr int AM_SW = 8;
+constexpr int AM_HPT = AM_H / (AM_SW / 4);          // heads per softmax thread (32)
+constexpr int AM_SOFTMAX_THREADS = AM_SW * 32;
+constexpr int AM_THREADS = AM_SOFTMAX_THREADS + 160;   // + warp AM_SW: MMA issue, + 4 gather warps
 constexpr int AM_MAX_SPLITS = 16;
 // P'' = 2^(s2' - m_ref + AM_POFF) with m_ref lagging the true maximum by at most AM_LAG, so
 // P'' <= 2^(AM_POFF + AM_LAG) = 256 < 448 while typical weights (a few binades below the maximum)
@@ -124,14 +129,14 @@ attend_mma_kernel(AttendMmaArgs A) {
         tc::mbar_init(&bars.k_full[0], 64); tc::mbar_init(&bars.k_full[1], 64);
         tc::mbar_init(&bars.kv_empty[0], 1); tc::mbar_init(&bars.kv_empty[1], 1);
         tc::mbar_init(&bars.s_full[0], 1); tc::mbar_init(&bars.s_full[1], 1);
-        tc::mbar_init(&bars.s_empty[0], 8); tc::mbar_init(&bars.s_empty[1], 8);
+        tc::mbar_init(&bars.s_empty[0], AM_SW); tc::mbar_init(&bars.s_empty[1], AM_SW);
         tc::mbar_init(&bars.rope_free, 1); tc::mbar_init(&bars.p_full, AM_SOFTMAX_THREADS);
         tc::mbar_init(&bars.p_empty, 1); tc::mbar_init(&bars.pv_done, 1);
         tc::mbar_init(&bars.q_full, AM_SOFTMAX_THREADS);
         tc::mbar_init_fence();
         *abort_flag = 0;
     }
-    if (warp == 8) tc::tmem_alloc<512>(tmem_base_s);
+    if (warp == AM_SW) tc::tmem_alloc<512>(tmem_base_s);
 
     if (tid < AM_H) { s_muse[tid] = -INFINITY; s_fac[tid] = 1.0f; }   // no reference yet: the first tile takes the exact path
     tc::fence_proxy_async();
@@ -143,20 +148,21 @@ attend_mma_kernel(AttendMmaArgs A) {
 
     // q -> two e4m3 terms per head, written straight into the swizzled operand tiles (once per CTA):
     //   hi = e4m3(q / s), s = absmax / 448;  lo = e4m3((q / s - hi) * 16)   =>  q ~ s * (hi + lo / 16)
-    // Warps 0-7 take 8 heads each; a head's 576 values are 72 chunks of 8 (lane, lane+32, lane+64).
+    // Every softmax warp takes 64 / AM_SW heads; a head's 576 values are 72 chunks of 8 (lane, lane+32, lane+64).
     // The gather warps do not wait for this: the MMA warp does (q_full) before its first QK.
     // Under a programmatic dependent launch the kernel before this one may still be running. Unless the
     // caller vouches that q was complete before that kernel was even launched (q_early: the fused decode
     // step), q may be that kernel's output and is read only after the dependency wait.
     if (!A.q_early) rv_grid_dep_wait();
-    if (warp < 8) {
+    if (warp < AM_SW) {
         const uint16_t* qb = A.q + (size_t)b * AM_H * AM_W;
+        constexpr int HPW = AM_H / AM_SW;          // heads a warp converts (a multiple of 4)
 #pragma unroll 1
-        for (int h4 = 0; h4 < 8; h4 += 4) {
+        for (int h4 = 0; h4 < HPW; h4 += 4) {
             uint4 v[4][3];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const uint16_t* src = qb + (size_t)(warp * 8 + h4 + u) * AM_W;
+                const uint16_t* src = qb + (size_t)(warp * HPW + h4 + u) * AM_W;
 #pragma unroll
                 for (int c = 0; c < 3; ++c) {
                     const int chunk = lane + 32 * c;
@@ -165,7 +171,7 @@ attend_mma_kernel(AttendMmaArgs A) {
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int h = warp * 8 + h4 + u;
+                const int h = warp * HPW + h4 + u;
                 float f[3][8];
                 float amax = 0.0f;
 #pragma unroll
@@ -237,13 +243,13 @@ attend_mma_kernel(AttendMmaArgs A) {
     const int ntiles = r_end > r_begin ? (r_end - r_begin + AM_TILE - 1) / AM_TILE : 0;
 
 
-    if (warp >= 9 && ntiles > 0) {
+    if (warp > AM_SW && ntiles > 0) {
         // ------------------------------ gather producers ------------------------------------------
         // Two independent groups of two warps: group 0 fills the even tiles (buffer 0), group 1 the odd
         // ones (buffer 1), each in plain program order (wait for its buffer, copy, signal). With one
         // group per buffer neither ever waits on the other's buffer, so two tiles are in flight
         // whenever both buffers are free. A thread owns two rows of its group's tile.
-        const int grp = (warp - 9) >> 1, wi = (warp - 9) & 1;
+        const int grp = (warp - AM_SW - 1) >> 1, wi = (warp - AM_SW - 1) & 1;
         const int pr[2] = {wi * 32 + lane, 64 + wi * 32 + lane};
         bool ok = true;
         // The address chain of a row (selected token -> page -> pool row -> scale) is three dependent
@@ -327,7 +333,7 @@ attend_mma_kernel(AttendMmaArgs A) {
             tc::fence_proxy_async();
             if (!(A.withhold && j == 0)) tc::mbar_arrive(&bars.k_full[grp]);
         }
-    } else if (warp == 8 && ntiles > 0) {
+    } else if (warp == AM_SW && ntiles > 0) {
         // ------------------------------ MMA issuer ------------------------------------------------
         bool ok = true;
         const uint32_t id_qk = tc::idesc_e4m3(128, 128, 0, 0), id_pv = tc::idesc_e4m3(128, 64, 1, 1);
@@ -397,17 +403,17 @@ attend_mma_kernel(AttendMmaArgs A) {
                 else __nanosleep(100);
             }
         }
-    } else if (warp < 8) {
+    } else if (warp < AM_SW) {
         // ------------------------------ softmax + epilogue ---------------------------------------
         // thread = (TMEM lane, head half): lane group q = warp % 4 -> token (or latent dim) 32 q + lane,
-        // hh = warp / 4 -> heads 32 hh .. 32 hh + 31.
-        const int q4 = warp & 3, hh = warp >> 2;
+        // hg = warp / 4 -> heads AM_HPT hg .. AM_HPT hg + AM_HPT - 1.
+        const int q4 = warp & 3, hg = warp >> 2;
         const int row = q4 * 32 + lane;                  // token of the tile / dim of a 128-dim block
         const uint32_t lane_base = ((uint32_t)(q4 * 32)) << 16;
-        const int h0 = hh * 32;
-        float l_part[32];
+        const int h0 = hg * AM_HPT;
+        float l_part[AM_HPT];
 #pragma unroll
-        for (int h = 0; h < 32; ++h) l_part[h] = 0.0f;
+        for (int h = 0; h < AM_HPT; ++h) l_part[h] = 0.0f;
         float m_ref = -INFINITY;                          // threads tid < 64: reference max of head tid
         bool ok = ntiles > 0;
         for (int i = 0; i < ntiles && ok; ++i) {
@@ -422,15 +428,15 @@ attend_mma_kernel(AttendMmaArgs A) {
             // additive -inf makes every weight of theirs exactly 0 without a select per element
             const float c2 = valid ? log2f(stok) + AM_POFF : -INFINITY;   // P'' = weight * s_tok * 2^AM_POFF
             const float inv_tok = valid ? 1.0f / stok : 0.0f;
-            float s2[32];
+            float s2[AM_HPT];
             float dmax = -INFINITY;               // max over this thread's heads of s2' - reference
             {
-                uint32_t rh[32], rl[32];
-                tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + h0, rh);
-                tc::tmem_ld32(TM_S0 + kb * 128 + lane_base + 64 + h0, rl);
+                uint32_t rh[AM_HPT], rl[AM_HPT];
+                tc::tmem_ldn<AM_HPT>(TM_S0 + kb * 128 + lane_base + h0, rh);
+                tc::tmem_ldn<AM_HPT>(TM_S0 + kb * 128 + lane_base + 64 + h0, rl);
                 tc::tmem_ld_wait();
 #pragma unroll
-                for (int h = 0; h < 32; h += 4) {
+                for (int h = 0; h < AM_HPT; h += 4) {
                     const float4 a4 = *reinterpret_cast<const float4*>(s_ahi + h0 + h);
                     const float4 m4 = *reinterpret_cast<const float4*>(s_muse + h0 + h);
                     const float av[4] = {a4.x, a4.y, a4.z, a4.w}, mv[4] = {m4.x, m4.y, m4.z, m4.w};
@@ -460,12 +466,12 @@ attend_mma_kernel(AttendMmaArgs A) {
                 {
                     float mine = -INFINITY;
 #pragma unroll
-                    for (int h = 0; h < 32; ++h) {
+                    for (int h = 0; h < AM_HPT; ++h) {
                         float mx;
                         asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(mx) : "f"(s2[h]));
                         if (h == lane) mine = mx;
                     }
-                    s_wmax[q4 * 64 + h0 + lane] = mine;
+                    if (lane < AM_HPT) s_wmax[q4 * 64 + h0 + lane] = mine;
                 }
                 tc::named_barrier(2, AM_SOFTMAX_THREADS);
                 if (tid < AM_H) {
@@ -481,26 +487,26 @@ attend_mma_kernel(AttendMmaArgs A) {
                 if (i >= 1) { ok = tc::mbar_wait_warp(&bars.pv_done, (i - 1) & 1, abort_flag, 63, A.max_polls); if (!ok) break; }
                 tc::tc_fence_after();
                 if (i >= 1) {
-                    uint32_t r[32];
+                    uint32_t r[AM_HPT];
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {   // this thread's dim lane, its 32 head columns of each block
-                        tc::tmem_ld32(TM_O + lane_base + c * 64 + h0, r);
+                    for (int c = 0; c < 4; ++c) {   // this thread's dim lane, its head columns of each block
+                        tc::tmem_ldn<AM_HPT>(TM_O + lane_base + c * 64 + h0, r);
                         tc::tmem_ld_wait();
 #pragma unroll
-                        for (int h = 0; h < 32; ++h) r[h] = __float_as_uint(__uint_as_float(r[h]) * s_fac[h0 + h]);
-                        tc::tmem_st32(TM_O + lane_base + c * 64 + h0, r);
+                        for (int h = 0; h < AM_HPT; ++h) r[h] = __float_as_uint(__uint_as_float(r[h]) * s_fac[h0 + h]);
+                        tc::tmem_stn<AM_HPT>(TM_O + lane_base + c * 64 + h0, r);
                     }
                     tc::tmem_st_wait();
                 }
 #pragma unroll
-                for (int h = 0; h < 32; ++h) l_part[h] *= s_fac[h0 + h];
+                for (int h = 0; h < AM_HPT; ++h) l_part[h] *= s_fac[h0 + h];
                 tc::tc_fence_before();
             }
             // P'' = 2^(s2' - m) = weight * s_tok * 2^AM_POFF as two e4m3 terms (via f16: p <= 256 and the
             // residual p - hi are exact enough in half precision); l accumulates the plain weight
-            uint32_t hi_w[8], lo_w[8];
+            uint32_t hi_w[AM_HPT / 4], lo_w[AM_HPT / 4];
 #pragma unroll
-            for (int h = 0; h < 32; h += 4) {
+            for (int h = 0; h < AM_HPT; h += 4) {
                 const float4 m4 = *reinterpret_cast<const float4*>(s_muse + h0 + h);
                 const float mv[4] = {m4.x, m4.y, m4.z, m4.w};
                 uint32_t chs[2], cls[2];
@@ -529,10 +535,10 @@ attend_mma_kernel(AttendMmaArgs A) {
             {
                 uint8_t* prow = smem + SM_P;
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(row, hh * 2 + c)) =
+                for (int c = 0; c < AM_HPT / 16; ++c) {   // a 16-byte chunk = 16 heads of one term
+                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(row, hg * (AM_HPT / 16) + c)) =
                         make_uint4(hi_w[4 * c], hi_w[4 * c + 1], hi_w[4 * c + 2], hi_w[4 * c + 3]);
-                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(row, 4 + hh * 2 + c)) =
+                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(row, 4 + hg * (AM_HPT / 16) + c)) =
                         make_uint4(lo_w[4 * c], lo_w[4 * c + 1], lo_w[4 * c + 2], lo_w[4 * c + 3]);
                 }
             }
@@ -543,16 +549,30 @@ attend_mma_kernel(AttendMmaArgs A) {
         // ---- epilogue ----
         if (ok && ntiles > 0) ok = tc::mbar_wait_warp(&bars.pv_done, (ntiles - 1) & 1, abort_flag, 65, A.max_polls);
         tc::tc_fence_after();
-        // l per head: butterfly over the 32 token lanes, then across the 4 lane groups through shared memory
+        // l per head: the warp's 32 token lanes each hold AM_HPT partial sums; a recursive-halving exchange (a lane
+        // keeps the half of the heads whose index bit matches its own lane bit and sends the other half) leaves the
+        // sum of head j in lane j after AM_HPT - 1 shuffles, instead of a five-step butterfly per head. Then the 4
+        // lane groups meet through shared memory.
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
         {
-            float mine = 0.0f;
+            int n = AM_HPT;
 #pragma unroll
-            for (int h = 0; h < 32; ++h) {
-                const float v = rv_warp_sum(l_part[h]);
-                if (h == lane) mine = v;
+            for (int off = AM_HPT / 2; off >= 1; off >>= 1) {
+                n >>= 1;
+                const bool up = (lane & off) != 0;
+#pragma unroll
+                for (int i = 0; i < AM_HPT / 2; ++i) {
+                    if (i < n) {
+                        const float send = up ? l_part[i] : l_part[i + n];
+                        const float recv = __shfl_xor_sync(0xffffffffu, send, off);
+                        l_part[i] = (up ? l_part[i + n] : l_part[i]) + recv;
+                    }
+                }
             }
-            s_wmax[q4 * 64 + h0 + lane] = mine;
+            // with fewer heads than lanes (AM_HPT == 16) lanes l and l ^ 16 hold two halves of head (l & 15)
+            float mine = l_part[0];
+            if (AM_HPT < 32) mine += __shfl_xor_sync(0xffffffffu, mine, 16);
+            if (lane < AM_HPT) s_wmax[q4 * 64 + h0 + lane] = mine;
         }
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
         if (tid < AM_H) {
@@ -573,13 +593,13 @@ attend_mma_kernel(AttendMmaArgs A) {
             s_muse[h] = l > 0.0f ? 1.0f / l : 0.0f;
         }
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
-        // O^T: this thread's TMEM lane is one latent dim of each 128-dim block; its 32 head columns.
-        // Single split: the sequence's [64][512] bf16 output is staged in the (now idle) K buffer 0 and
-        // written out as one contiguous 64 KiB block with 16-byte stores. Splits write f32 partials.
-        uint16_t* stage = reinterpret_cast<uint16_t*>(smem + SM_K0);
-        float inv_l[32];   // 1 / l of this thread's 32 heads (registers: the stores below must not wait on loads)
+        // O^T: this thread's TMEM lane is one latent dim of each 128-dim block; its head columns. For a given head
+        // the 32 lanes of a warp hold 32 consecutive dims, so a warp's store covers 64 contiguous bytes of the bf16
+        // output row (two full sectors) and the output goes to global memory straight from the registers; splits
+        // write their f32 partials the same way (128 contiguous bytes per warp store).
+        float inv_l[AM_HPT];   // 1 / l of this thread's heads (registers: the stores below must not wait on loads)
 #pragma unroll
-        for (int h = 0; h < 32; h += 4) {
+        for (int h = 0; h < AM_HPT; h += 4) {
             const float4 m4 = *reinterpret_cast<const float4*>(s_muse + h0 + h);
             inv_l[h] = m4.x; inv_l[h + 1] = m4.y; inv_l[h + 2] = m4.z; inv_l[h + 3] = m4.w;
         }
@@ -588,35 +608,28 @@ attend_mma_kernel(AttendMmaArgs A) {
 #pragma unroll 1
         for (int c = 0; c < 4 && !skip; ++c) {
             const int dim = c * 128 + row;
-            uint32_t r[32];
+            uint32_t r[AM_HPT];
             if (ntiles > 0 && ok) {
-                tc::tmem_ld32(TM_O + lane_base + c * 64 + h0, r);
+                tc::tmem_ldn<AM_HPT>(TM_O + lane_base + c * 64 + h0, r);
                 tc::tmem_ld_wait();
             } else {
 #pragma unroll
-                for (int h = 0; h < 32; ++h) r[h] = 0u;
+                for (int h = 0; h < AM_HPT; ++h) r[h] = 0u;
             }
             if (part) {
 #pragma unroll
-                for (int hq = 0; hq < 32; ++hq) part[hq * AM_KVL + dim] = __uint_as_float(r[hq]);
+                for (int hq = 0; hq < AM_HPT; ++hq) part[hq * AM_KVL + dim] = __uint_as_float(r[hq]);
             } else {
-                uint16_t* sp = stage + h0 * AM_KVL + dim;
+                uint16_t* gp = A.out + ((size_t)b * AM_H + h0) * AM_KVL + dim;
 #pragma unroll
-                for (int hq = 0; hq < 32; ++hq) sp[hq * AM_KVL] = rv_f32_to_bf16(__uint_as_float(r[hq]) * inv_l[hq]);
+                for (int hq = 0; hq < AM_HPT; ++hq) gp[hq * AM_KVL] = rv_f32_to_bf16(__uint_as_float(r[hq]) * inv_l[hq]);
             }
-        }
-        if (A.n_splits == 1 && !skip) {
-            tc::named_barrier(1, AM_SOFTMAX_THREADS);
-            const uint4* sv = reinterpret_cast<const uint4*>(stage);
-            uint4* gv = reinterpret_cast<uint4*>(A.out + (size_t)b * AM_H * AM_KVL);
-#pragma unroll 4
-            for (int i = tid; i < AM_H * AM_KVL * 2 / 16; i += AM_SOFTMAX_THREADS) gv[i] = sv[i];
         }
     }
 
     tc::tc_fence_before();
     __syncthreads();
-    if (warp == 8) tc::tmem_dealloc<512>(tmem);
+    if (warp == AM_SW) tc::tmem_dealloc<512>(tmem);
     if (tid == 0 && *abort_flag) atomicCAS(A.err, 0, *abort_flag);
 }
 
