@@ -39,7 +39,7 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int SEL_THREADS = 512, SEL_WARPS = SEL_THREADS / 32;
+constexpr int SEL_MAX_WARPS = 32;   // CTAs of 512 threads (clusters of 2 to 8) or of 1024 threads (one CTA per sequence)
 constexpr int SEL_BINS = 4096;
 constexpr int SEL_LIST = 2048;     // band tokens per SEQUENCE the fast path holds (and per chunk on the slow path)
 constexpr int SEL_TOK = 4;         // band tokens a warp re-scores per pass
@@ -52,37 +52,41 @@ struct SelXc {                     // per-CTA exchange block; slot q of an array
     uint32_t n_in[SEL_MAX_CLUSTER], n_band[SEL_MAX_CLUSTER];
     uint32_t n_out[SEL_MAX_CLUSTER];
     uint32_t cnt_gt[SEL_MAX_CLUSTER], cnt_eq[SEL_MAX_CLUSTER];
-    uint32_t red[2][SEL_WARPS];
-    uint32_t wcnt[SEL_WARPS];
+    uint32_t red[2][SEL_MAX_WARPS];
+    uint32_t wcnt[SEL_MAX_WARPS];
     uint32_t list_n;
     uint32_t bstar, n_above;
     uint32_t pivot, need;
 };
 
-// Block-wide reductions over 512 threads, one barrier per call (double-buffered partials as in topk_core.cuh).
+// Block-wide reductions over NW warps, one barrier per call (double-buffered partials as in topk_core.cuh).
+template <int NW>
 __device__ __forceinline__ uint32_t sel_block_sum(uint32_t v, SelXc& xc, int& buf) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     v = __reduce_add_sync(0xffffffffu, v);
     if (lane == 0) xc.red[buf][warp] = v;
     __syncthreads();
-    const uint32_t t = __reduce_add_sync(0xffffffffu, lane < SEL_WARPS ? xc.red[buf][lane] : 0u);
+    const uint32_t t = __reduce_add_sync(0xffffffffu, lane < NW ? xc.red[buf][lane] : 0u);
     buf ^= 1;
     return t;
 }
+template <int NW>
 __device__ __forceinline__ uint32_t sel_block_max(uint32_t v, SelXc& xc, int& buf) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     v = __reduce_max_sync(0xffffffffu, v);
     if (lane == 0) xc.red[buf][warp] = v;
     __syncthreads();
-    const uint32_t t = __reduce_max_sync(0xffffffffu, lane < SEL_WARPS ? xc.red[buf][lane] : 0u);
+    const uint32_t t = __reduce_max_sync(0xffffffffu, lane < NW ? xc.red[buf][lane] : 0u);
     buf ^= 1;
     return t;
 }
+template <int NW>
 __device__ __forceinline__ uint32_t sel_block_min(uint32_t v, SelXc& xc, int& buf) {
-    return ~sel_block_max(~v, xc, buf);
+    return ~sel_block_max<NW>(~v, xc, buf);
 }
 
 // Exclusive prefix of `v` over the block in thread order (one barrier).
+template <int NW>
 __device__ __forceinline__ uint32_t sel_block_excl(uint32_t v, SelXc& xc) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t incl = v;
@@ -93,22 +97,23 @@ __device__ __forceinline__ uint32_t sel_block_excl(uint32_t v, SelXc& xc) {
     }
     if (lane == 31) xc.wcnt[warp] = incl;
     __syncthreads();
-    const uint32_t cw = lane < SEL_WARPS ? xc.wcnt[lane] : 0u;
+    const uint32_t cw = lane < NW ? xc.wcnt[lane] : 0u;
     const uint32_t pre = __reduce_add_sync(0xffffffffu, lane < warp ? cw : 0u);
     __syncthreads();                                   // wcnt may be rewritten by the next call
     return pre + incl - v;
 }
 
-template <int EPT>
-__global__ void __launch_bounds__(SEL_THREADS, EPT <= 16 ? 2 : 1)
+template <int EPT, int NT>
+__global__ void __launch_bounds__(NT, (NT == 512 && EPT <= 16) ? 2 : 1)
 index_select_cluster_kernel(SelArgs A) {
+    constexpr int NW = NT / 32;
     cg::cluster_group cluster = cg::this_cluster();
     const int C = (int)cluster.dim_blocks().x, r = (int)cluster.block_rank();
     extern __shared__ __align__(16) uint32_t sel_smem[];
     __shared__ SelXc xc;
     float* qf = reinterpret_cast<float*>(sel_smem);                       // [SEL_HD][32] q codes as f32, [dim][head]
-    float* kfw = qf + SEL_HD * 32;                                        // [SEL_WARPS][SEL_TOK][SEL_HD] key rows as f32
-    uint32_t* hist = reinterpret_cast<uint32_t*>(kfw + SEL_WARPS * SEL_TOK * SEL_HD);   // [SEL_BINS]; later `dec`
+    float* kfw = qf + SEL_HD * 32;                                        // [NW][SEL_TOK][SEL_HD] key rows as f32
+    uint32_t* hist = reinterpret_cast<uint32_t*>(kfw + NW * SEL_TOK * SEL_HD);   // [SEL_BINS]; later `dec`
     uint32_t* l_tok = hist + SEL_BINS;                                    // [SEL_LIST] this CTA's band tokens
     uint32_t* l_key = l_tok + SEL_LIST;                                   // [SEL_LIST] their exact keys
     uint32_t* a_tok = l_key + SEL_LIST;                                   // [SEL_LIST] the cluster's band, gathered
@@ -127,7 +132,7 @@ index_select_cluster_kernel(SelArgs A) {
     uint32_t* out = A.rows + (size_t)b * A.k;
     if (r == 0 && tid == 0) A.n_sel[b] = kk > 0 ? kk : 0;
     if (kk <= 0) return;                                                  // uniform over the cluster
-    constexpr int CH = EPT * SEL_THREADS;
+    constexpr int CH = EPT * NT;
     const int i0 = r * CH + tid * EPT;
     const int nvalid = max(0, min(EPT, nt - i0));
     if (kk == nt) {                                                       // everything is selected: the identity
@@ -181,7 +186,7 @@ index_select_cluster_kernel(SelArgs A) {
         }
     }
     rv_rescore_stage_q(A.qcodes + (size_t)b * nh * hd, nh, qf);
-    for (int i = tid; i < SEL_BINS; i += SEL_THREADS) hist[i] = 0u;
+    for (int i = tid; i < SEL_BINS; i += NT) hist[i] = 0u;
     if (tid == 0) xc.list_n = 0;
     int buf = 0;
     {
@@ -189,9 +194,9 @@ index_select_cluster_kernel(SelArgs A) {
 #pragma unroll
         for (int j = 0; j < EPT; ++j)
             if (j < nvalid) { mn = min(mn, key[j]); mx = max(mx, key[j]); }
-        mn = sel_block_min(mn, xc, buf);
-        mx = sel_block_max(mx, xc, buf);
-        const uint32_t sm = sel_block_max(__float_as_uint(skm), xc, buf);     // scales are >= 0: bit order = value order
+        mn = sel_block_min<NW>(mn, xc, buf);
+        mx = sel_block_max<NW>(mx, xc, buf);
+        const uint32_t sm = sel_block_max<NW>(__float_as_uint(skm), xc, buf);     // scales are >= 0: bit order = value order
         if (tid == 0) { xc.kmin[r] = mn; xc.kmax[r] = mx; xc.skmax[r] = sm; }
     }
     // [1] The first exchange is a PULL: a CTA may touch another CTA's shared memory only once that CTA is known
@@ -236,13 +241,13 @@ index_select_cluster_kernel(SelArgs A) {
     const int SL = SEL_BINS / C;                                              // rank r reduces bins [r * SL, (r + 1) * SL)
     {
         uint32_t tot = 0u;
-        for (int i = tid; i < SL; i += SEL_THREADS) {
+        for (int i = tid; i < SL; i += NT) {
             uint32_t v = 0u;
             for (int q = 0; q < C; ++q) v += cluster.map_shared_rank(hist, q)[r * SL + i];
             red_hist[i] = v;
             tot += v;
         }
-        tot = sel_block_sum(tot, xc, buf);
+        tot = sel_block_sum<NW>(tot, xc, buf);
         if (tid < C) cluster.map_shared_rank(&xc, tid)->slice_tot[r] = tot;
     }
     __syncthreads();
@@ -255,15 +260,15 @@ index_select_cluster_kernel(SelArgs A) {
     }
     {
         const uint32_t* src = cluster.map_shared_rank(red_hist, s_star);
-        for (int i = tid; i < SL; i += SEL_THREADS) slice[i] = src[i];
+        for (int i = tid; i < SL; i += NT) slice[i] = src[i];
     }
     __syncthreads();
     {
         // suffix scan over the slice: thread t owns bins [t * per, (t + 1) * per), per = ceil(SL / 512)
-        const int per = (SL + SEL_THREADS - 1) / SEL_THREADS;
+        const int per = (SL + NT - 1) / NT;
         uint32_t mine = 0u;
         for (int j = 0; j < per; ++j) { const int i = tid * per + j; if (i < SL) mine += slice[i]; }
-        const uint32_t before = sel_block_excl(mine, xc);                     // bins below this thread's
+        const uint32_t before = sel_block_excl<NW>(mine, xc);                     // bins below this thread's
         const uint32_t total = xc.slice_tot[s_star];
         uint32_t acc = above + (total - before - mine);                       // tokens in bins above this thread's
         for (int j = per - 1; j >= 0; --j) {
@@ -287,8 +292,8 @@ index_select_cluster_kernel(SelArgs A) {
 #pragma unroll
         for (int j = 0; j < EPT; ++j)
             if (j < nvalid && bin_of(key[j]) == bstar) { mn = min(mn, key[j]); mx = max(mx, key[j]); }
-        mn = sel_block_min(mn, xc, buf);
-        mx = sel_block_max(mx, xc, buf);
+        mn = sel_block_min<NW>(mn, xc, buf);
+        mx = sel_block_max<NW>(mx, xc, buf);
         if (tid < C) {
             SelXc* dst = cluster.map_shared_rank(&xc, tid);
             dst->bmin[r] = mn; dst->bmax[r] = mx;
@@ -308,7 +313,7 @@ index_select_cluster_kernel(SelArgs A) {
             else if (key[j] >= k_lo) m_band |= 1u << j;
         }
     }
-    const uint32_t n_in_mine = sel_block_sum((uint32_t)__popc(m_in), xc, buf);
+    const uint32_t n_in_mine = sel_block_sum<NW>((uint32_t)__popc(m_in), xc, buf);
     uint32_t my_pos;                                                          // list position of this thread's first band token
     {
         const uint32_t cnt = (uint32_t)__popc(m_band);
@@ -345,7 +350,7 @@ index_select_cluster_kernel(SelArgs A) {
     const float my_wh = lane < nh ? __fmul_rn(A.w[(size_t)b * nh + lane], g.index_wscale) : 0.0f;
     // Exact key of the first `ln` listed tokens -> l_key[position] (0 and ~0 are reserved for "surely out" / "surely in").
     auto rescore = [&](uint32_t ln) {
-        rv_rescore_listed<SEL_WARPS, SEL_TOK>(l_tok, ln, qf, kfw + warp * (SEL_TOK * hd), bt, g, A.index_pool, A.index_scale,
+        rv_rescore_listed<NW, SEL_TOK>(l_tok, ln, qf, kfw + warp * (SEL_TOK * hd), bt, g, A.index_pool, A.index_scale,
                                               my_sq, my_wh, [&](uint32_t pos, float score) {
             uint32_t ku = topk_key(score);
             l_key[pos] = ku == 0xffffffffu ? 0xfffffffeu : (ku == 0u ? 1u : ku);
@@ -353,7 +358,7 @@ index_select_cluster_kernel(SelArgs A) {
     };
     // ascending write-out of this CTA's tokens whose bit is set in `sel`, from slot `base` on (one barrier)
     auto write_out = [&](uint32_t sel, uint32_t base) {
-        uint32_t pos = base + sel_block_excl((uint32_t)__popc(sel), xc);
+        uint32_t pos = base + sel_block_excl<NW>((uint32_t)__popc(sel), xc);
 #pragma unroll
         for (int j = 0; j < EPT; ++j)
             if (sel & (1u << j)) out[pos++] = (uint32_t)(i0 + j);
@@ -370,7 +375,7 @@ index_select_cluster_kernel(SelArgs A) {
                 const uint32_t nq = xc.n_band[q];
                 const uint32_t* st = cluster.map_shared_rank(l_tok, q);
                 const uint32_t* sk2 = cluster.map_shared_rank(l_key, q);
-                for (uint32_t i = tid; i < nq; i += SEL_THREADS) { a_tok[off + i] = st[i]; a_key[off + i] = sk2[i]; }
+                for (uint32_t i = tid; i < nq; i += NT) { a_tok[off + i] = st[i]; a_key[off + i] = sk2[i]; }
                 off += nq;
             }
         }
@@ -378,7 +383,7 @@ index_select_cluster_kernel(SelArgs A) {
         // rank each of this CTA's band tokens among ALL band tokens by (exact key descending, index ascending)
         uint32_t* dec = hist;
         const uint32_t take = (uint32_t)kk - n_in;   // >= 1: fewer than kk tokens lie above the band
-        for (uint32_t q2 = warp; q2 < n_band_mine; q2 += SEL_WARPS) {
+        for (uint32_t q2 = warp; q2 < n_band_mine; q2 += NW) {
             const uint32_t kq = l_key[q2], tq = l_tok[q2];
             uint32_t c = 0;
             for (uint32_t j2 = lane; j2 < n_band; j2 += 32) {
@@ -396,7 +401,7 @@ index_select_cluster_kernel(SelArgs A) {
             for (int j = 0; j < EPT; ++j)
                 if (m_band & (1u << j)) { if (dec[pos]) sel |= 1u << j; ++pos; }
         }
-        const uint32_t n_out_mine = sel_block_sum((uint32_t)__popc(sel), xc, buf);
+        const uint32_t n_out_mine = sel_block_sum<NW>((uint32_t)__popc(sel), xc, buf);
         if (tid < C) cluster.map_shared_rank(&xc, tid)->n_out[r] = n_out_mine;
         cluster.sync();                                                       // [6] counts; nobody reads our lists any more
         uint32_t base = 0u;
@@ -438,10 +443,10 @@ index_select_cluster_kernel(SelArgs A) {
     // exact cluster-wide radix selection, four 8-bit digits, MSB first; per-warp histograms so that ties never
     // serialise a CTA on one bin; whist aliases `hist`, the CTA's digit histogram goes to a_tok[0..256)
     uint32_t pivot = 0u, mask = 0u, need = (uint32_t)kk;
-    uint32_t* whist = hist;                                                   // [SEL_WARPS][256]
+    uint32_t* whist = hist;                                                   // [NW][256]
     for (int sh2 = 24; sh2 >= 0; sh2 -= 8) {
         __syncthreads();
-        for (int i = tid; i < SEL_WARPS * 256; i += SEL_THREADS) whist[i] = 0u;
+        for (int i = tid; i < NW * 256; i += NT) whist[i] = 0u;
         __syncthreads();
 #pragma unroll
         for (int j = 0; j < EPT; ++j)
@@ -450,7 +455,7 @@ index_select_cluster_kernel(SelArgs A) {
         if (tid < 256) {
             uint32_t t = 0;
 #pragma unroll
-            for (int w2 = 0; w2 < SEL_WARPS; ++w2) t += whist[w2 * 256 + tid];
+            for (int w2 = 0; w2 < NW; ++w2) t += whist[w2 * 256 + tid];
             a_tok[tid] = t;
         }
         __syncthreads();
@@ -497,8 +502,8 @@ index_select_cluster_kernel(SelArgs A) {
             else if (key[j] == pivot) sel_eq |= 1u << j;
         }
     }
-    const uint32_t gt_mine = sel_block_sum((uint32_t)__popc(sel_gt), xc, buf);
-    const uint32_t eq_mine = sel_block_sum((uint32_t)__popc(sel_eq), xc, buf);
+    const uint32_t gt_mine = sel_block_sum<NW>((uint32_t)__popc(sel_gt), xc, buf);
+    const uint32_t eq_mine = sel_block_sum<NW>((uint32_t)__popc(sel_eq), xc, buf);
     if (tid < C) {
         SelXc* dst = cluster.map_shared_rank(&xc, tid);
         dst->cnt_gt[r] = gt_mine; dst->cnt_eq[r] = eq_mine;
@@ -511,7 +516,7 @@ index_select_cluster_kernel(SelArgs A) {
         eq_before += xc.cnt_eq[q];
     }
     const uint32_t need_mine = need > eq_before ? need - eq_before : 0u;        // ties this CTA may still take
-    const uint32_t eq_excl = sel_block_excl((uint32_t)__popc(sel_eq), xc);      // ties in this CTA before this thread's
+    const uint32_t eq_excl = sel_block_excl<NW>((uint32_t)__popc(sel_eq), xc);      // ties in this CTA before this thread's
     uint32_t sel = sel_gt;
     {
         uint32_t e = eq_excl;
@@ -529,15 +534,20 @@ namespace rivoli {
 
 static int g_sel_cluster_override = 0;
 
-bool select_cluster_plan(int B, int score_stride, int* cluster, int* ept) {
-    int C = 1;
-    while (C < SEL_MAX_CLUSTER && (long long)B * C * 2 <= 2 * 148) C *= 2;     // about two CTAs per SM at most
+bool select_cluster_plan(int B, int score_stride, int* cluster, int* ept, int* threads) {
+    // A batch that fills the chip by itself (one CTA per SM) takes ONE CTA of 1024 threads per sequence: no exchange
+    // between CTAs at all. Smaller batches spread a sequence over a cluster of 2 to 8 CTAs of 512 threads, about two
+    // CTAs per SM at most.
+    int C = 1, NT = 512;
+    while (C < SEL_MAX_CLUSTER && (long long)B * C * 2 <= 2 * 148) C *= 2;
     if (g_sel_cluster_override > 0) C = g_sel_cluster_override;
+    if (C == 1 && (long long)1024 * 16 >= score_stride) NT = 1024;   // 16 keys per thread fit the 64 registers of a 1024-thread CTA
     for (;;) {
         for (int e = 4; e <= 32; e *= 2)
-            if ((long long)C * SEL_THREADS * e >= score_stride) { *cluster = C; *ept = e; return true; }
+            if ((long long)C * NT * e >= score_stride) { *cluster = C; *ept = e; *threads = NT; return true; }
         if (C >= SEL_MAX_CLUSTER) return false;
         C *= 2;
+        NT = 512;
     }
 }
 
@@ -552,11 +562,11 @@ extern "C" __attribute__((visibility("default"))) void rivoli_index_select_test_
 namespace rivoli {
 
 int launch_index_select_cluster(const SelArgs& a, int B, cudaStream_t st) {
-    int C = 1, ept = 4;
-    if (!select_cluster_plan(B, a.score_stride, &C, &ept)) return 1002;
-    const size_t smem = ((size_t)SEL_HD * 32 + (size_t)SEL_WARPS * SEL_TOK * SEL_HD + SEL_BINS + 4 * SEL_LIST) * 4;
+    int C = 1, ept = 4, nt = 512;
+    if (!select_cluster_plan(B, a.score_stride, &C, &ept, &nt)) return 1002;
+    const size_t smem = ((size_t)SEL_HD * 32 + (size_t)(nt / 32) * SEL_TOK * SEL_HD + SEL_BINS + 4 * SEL_LIST) * 4;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(B * C)); cfg.blockDim = dim3(SEL_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.gridDim = dim3((unsigned)(B * C)); cfg.blockDim = dim3((unsigned)nt); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = (unsigned)C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
@@ -564,15 +574,22 @@ int launch_index_select_cluster(const SelArgs& a, int B, cudaStream_t st) {
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 2;
     rv_drain_error();
-#define RV_SEL(EPT)                                                                                                   \
-    do {                                                                                                              \
-        cudaFuncSetAttribute(index_select_cluster_kernel<EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        (void)cudaLaunchKernelEx(&cfg, index_select_cluster_kernel<EPT>, a);                                          \
+#define RV_SEL(EPT, NT)                                                                                                   \
+    do {                                                                                                                  \
+        cudaFuncSetAttribute(index_select_cluster_kernel<EPT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        (void)cudaLaunchKernelEx(&cfg, index_select_cluster_kernel<EPT, NT>, a);                                          \
     } while (0)
-    if (ept == 4) RV_SEL(4);
-    else if (ept == 8) RV_SEL(8);
-    else if (ept == 16) RV_SEL(16);
-    else RV_SEL(32);
+    if (nt == 1024) {
+        if (ept == 4) RV_SEL(4, 1024);
+        else if (ept == 8) RV_SEL(8, 1024);
+        else if (ept == 16) RV_SEL(16, 1024);
+        else RV_SEL(32, 1024);
+    } else {
+        if (ept == 4) RV_SEL(4, 512);
+        else if (ept == 8) RV_SEL(8, 512);
+        else if (ept == 16) RV_SEL(16, 512);
+        else RV_SEL(32, 512);
+    }
 #undef RV_SEL
     return rv_launch_status();
 }

@@ -20,10 +20,9 @@ struct SelArgs {
 };
 
 namespace rivoli {
-// Cluster size and tokens per thread for a batch of B sequences of up to score_stride tokens:
-// cluster * 512 * ept >= score_stride, about two CTAs per SM at most. False if score_stride exceeds
-// 8 * 512 * 32 = 131,072 tokens.
-bool select_cluster_plan(int B, int score_stride, int* cluster, int* ept);
+// Cluster size, tokens per thread and threads per CTA for a batch of B sequences of up to score_stride tokens:
+// cluster * threads * ept >= score_stride. False if score_stride exceeds 8 * 512 * 32 = 131,072 tokens.
+bool select_cluster_plan(int B, int score_stride, int* cluster, int* ept, int* threads);
 // Launches the selection as a programmatic dependent of the kernel before it in the stream. 0, a guard code or
 // -(cudaError_t).
 int launch_index_select_cluster(const SelArgs& a, int B, cudaStream_t st);
