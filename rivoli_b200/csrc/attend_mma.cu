@@ -7,25 +7,31 @@
 // dequantisation pass and half the shared memory of a 16-bit staging. The two operands that
 // are not fp8 by nature are split into two e4m3 terms each (x ~ hi + lo, relative error
 // ~2^-8, bf16-like):
-//   * q (bf16 in)  -> q_hi | q_lo stacked along N (128 "virtual heads"), per-head scales;
+//   * q (bf16 in)  -> q_hi and q_lo as 128 "virtual heads" along M, per-head scales;
 //   * P (softmax)  -> p_hi, p_lo issued as two MMAs accumulating into the same columns.
 // The per-token scale folds into the softmax: with s2 = log2(e) * scale * (q.k) and
 // s2' = s2 + log2(s_tok), P' = 2^(s2' - m) = weight * s_tok, so P' x (raw V codes) is already
 // the dequantised product and P' is bounded by 2^8 whatever the scales are.
 //
-// Orientation: tokens are the MMA M dimension (128 per tile), so every instruction is a full
-// M = 128 shape:
-//   S^T[128 tok x 128 (hi|lo heads)] = K_tile[128 x 576] . Qcat^T          18 MMAs (K = 32)
-//   O^T[512 dims x 64 heads]        += V^T (the SAME shared tile, read MN-major) . P'^T
-//                                      4 blocks x 4 K-steps x {hi, lo} = 32 MMAs (N = 64)
-// TMEM (512 columns): S double buffered (2 x 128) + O^T (4 x 64).
+// What bounds this kernel is how many gathered rows an SM keeps in flight, so the tile is SMALL and the
+// ring is DEEP: 64 tokens per tile, four tiles (4 x 36 KiB) in flight next to the 72 KiB of q. Tokens are the
+// MMA N dimension, which may be 64 while every instruction keeps the full M = 128:
+//   S[128 (hi|lo heads) x 64 tok] = Qcat . K_tile^T                         18 MMAs (K = 32)
+//   O^T[512 dims x 64 heads]     += V^T (the SAME shared tile, read MN-major) . P'
+//                                   4 blocks x 2 K-steps x {hi, lo} = 16 MMAs (N = 64)
+// TMEM (512 columns): S four deep (4 x 64) + O^T (4 x 64).
 //
-// One CTA per (sequence, split), 13 warps: 0-7 softmax + epilogue (TMEM lane group = warp % 4 =
-// tokens / dims, head group = warp / 4: warps 0-3 own heads 0-31 and warps 4-7 heads 32-63), 8 MMA issue,
-// 9-12 gather: two independent groups of two warps, one per K buffer (even / odd tiles), so two tiles
-// are in flight whenever both buffers are free; a lane locates rows, copies go row by row with 32 lanes
-// on 32 consecutive 16-byte chunks (cp.async into the swizzled tile); the row address chain
-// (token -> page -> pool row -> scale) is software-pipelined three tiles deep.
+// One CTA per (sequence, split), 14 warps: 0-7 softmax + epilogue, 8 QK issue, 9 PV issue, 10-13 gather (warp g owns ring
+// stage g: tiles g, g + 4, ... in plain program order, so four tiles are in flight whenever four stages are
+// free; a lane locates rows, copies go row by row with 32 lanes on 32 consecutive 16-byte chunks (cp.async into
+// the swizzled tile); the row address chain (token -> page -> pool row -> scale) is software-pipelined three
+// tiles deep).
+// A softmax thread is one TMEM lane = one virtual head, and the q rows are ordered so that the hi and lo terms of a
+// head sit 16 lanes apart in the SAME warp: lanes 0-15 of warp s hold the hi rows of heads 16 s .. 16 s + 15, lanes
+// 16-31 their lo rows. One shuffle per score adds the two terms and leaves each lane with HALF the tokens of its
+// head: thread = (head, 16 tokens of the tile), two warps per lane quarter take the two 32-token halves. A head's
+// reference maximum, its running sum and its q scale are registers, and P' leaves as one 16-byte store per term
+// (heads are the rows of the K-major P' operand, tokens its bytes).
 // q arrives as bf16 and is split into its two e4m3 terms by the softmax warps inside the kernel while the
 // first tiles are gathered; the output leaves straight from the accumulator registers (64 contiguous bytes per warp store).
 // Online softmax with a LAGGING reference max: as long as no score of a tile exceeds its head's
@@ -39,15 +45,15 @@
 
 namespace {
 
-constexpr int AM_TILE = 128;
+constexpr int AM_TILE = 64;
+constexpr int AM_STAGES = 4;             // K ring depth (one gather warp and one S buffer per stage)
+constexpr int AM_ROPES = 3;              // rope tiles: released right after the two rope MMAs of a tile, so fewer than stages
 constexpr int AM_H = 64, AM_KVL = 512, AM_ROPE = 64, AM_W = AM_KVL + AM_ROPE;
-// softmax + epilogue warps: TMEM lane group = warp % 4, head group = warp / 4. 8 or 16: sixteen (16 heads per thread)
-// halve a tile's softmax work per warp but measured no faster (94.9 against 92.0 us at batch 128 x 2048 rows): the
-// chain is bound by latency between its stages, not by the softmax warps' issue rate.
-constexpr int AM_SW = 8;
-constexpr int AM_HPT = AM_H / (AM_SW / 4);          // heads per softmax thread (32)
+constexpr int AM_SW = 8;                 // softmax + epilogue warps: TMEM lane quarter = warp % 4, token / head half = warp / 4
+constexpr int AM_HPT = 32;               // head columns of O^T a thread owns in the rescale and the epilogue
 constexpr int AM_SOFTMAX_THREADS = AM_SW * 32;
-constexpr int AM_THREADS = AM_SOFTMAX_THREADS + 160;   // + warp AM_SW: MMA issue, + 4 gather warps
+constexpr int AM_QKW = AM_SW, AM_PVW = AM_SW + 1, AM_GW0 = AM_SW + 2;   // warp roles: QK issue, PV issue, first gather warp
+constexpr int AM_THREADS = (AM_GW0 + AM_STAGES) * 32;
 constexpr int AM_MAX_SPLITS = 16;
 // P'' = 2^(s2' - m_ref + AM_POFF) with m_ref lagging the true maximum by at most AM_LAG, so
 // P'' <= 2^(AM_POFF + AM_LAG) = 256 < 448 while typical weights (a few binades below the maximum)
@@ -57,27 +63,29 @@ constexpr int AM_MAX_SPLITS = 16;
 constexpr float AM_POFF = 5.0f, AM_LAG = 3.0f;
 
 // shared memory map (bytes); every operand tile is 1024-byte aligned
-constexpr int SM_K0 = 0;                 // 2 x (4 latent chunks x [128 rows][128 B]), 128-byte swizzle
-constexpr int SM_KBUF = 65536;
-constexpr int SM_ROPE = 131072;          // [128 rows][64 B], 64-byte swizzle (single buffer)
-constexpr int SM_QL = 139264;            // 4 chunks x [128 rows: hi heads 0-63, lo heads 64-127][128 B]
-constexpr int SM_QR = 204800;            // [128 rows][64 B], 64-byte swizzle
-constexpr int SM_P = 212992;             // [128 tokens][128 B = hi 64 heads | lo 64 heads], 128-byte swizzle
-constexpr int SM_SMALL = 229376;
-constexpr int SM_TOK = SM_SMALL;         // f32 [2][128] token scales
-constexpr int SM_AHI = SM_TOK + 1024;    // f32 [64] per-head q scale * softmax scale * log2(e)
-constexpr int SM_WMAX = SM_AHI + 256;    // f32 [4][64] cross-warp exchange
-constexpr int SM_MUSE = SM_WMAX + 1024;  // f32 [64] reference max every thread uses for the current tile
-constexpr int SM_FAC = SM_MUSE + 256;    // f32 [64] rescale factor of the current tile (1 = unchanged)
+constexpr int SM_K0 = 0;                 // 4 stages x (4 latent chunks x [64 rows][128 B]), 128-byte swizzle
+constexpr int SM_KSTAGE = 32768, SM_KCHUNK = 8192;
+constexpr int SM_ROPE = SM_K0 + AM_STAGES * SM_KSTAGE;       // 3 x [64 rows][64 B], 64-byte swizzle
+constexpr int SM_ROPEBUF = 4096;
+constexpr int SM_QL = SM_ROPE + AM_ROPES * SM_ROPEBUF;       // 4 chunks x [128 virtual heads][128 B]
+constexpr int SM_QR = SM_QL + 65536;     // [128 virtual heads][64 B], 64-byte swizzle
+constexpr int SM_P = SM_QR + 8192;       // hi [64 heads][64 tokens], lo the same: K-major, 64-byte swizzle
+constexpr int SM_PTERM = 4096;
+constexpr int SM_TOK = SM_P + 2 * SM_PTERM;   // float4 [4 stages][64 tokens]: scale, log2(scale) + AM_POFF, 1 / scale, -
+constexpr int SM_AHI = SM_TOK + AM_STAGES * AM_TILE * 16;   // f32 [64] per-head q scale * softmax scale * log2(e)
+constexpr int SM_WMAX = SM_AHI + 256;    // f32 [2][64] exchange between the two token halves
+constexpr int SM_FAC = SM_WMAX + 512;    // f32 [64] rescale factor of the current tile; 1 / l in the epilogue
 constexpr int SM_BARS = SM_FAC + 256;    // mbarriers
-constexpr int SM_MISC = SM_BARS + 128;
-constexpr int SM_TOTAL = SM_MISC + 64;   // 232,384 <= 232,448
+constexpr int SM_MISC = SM_BARS + 256;
+constexpr int SM_TOTAL = SM_MISC + 64;
 
 struct AmBars {
-    uint64_t k_full[2], kv_empty[2], s_full[2], s_empty[2], rope_free, p_full, p_empty, pv_done, q_full;
+    uint64_t k_full[AM_STAGES], k_empty[AM_STAGES], s_full[AM_STAGES], s_empty[AM_STAGES], rope_free[AM_ROPES],
+        p_full, pv_done, q_full;
 };
-static_assert(sizeof(AmBars) <= 128, "barrier block");
+static_assert(sizeof(AmBars) <= 256, "barrier block");
 static_assert(SM_TOTAL <= 232448, "shared memory budget");
+static_assert(SM_QL % 1024 == 0 && SM_P % 1024 == 0 && SM_ROPE % 1024 == 0, "operand tiles are 1024-byte aligned");
 
 
 struct AttendMmaArgs {
@@ -91,7 +99,7 @@ struct AttendMmaArgs {
     int min_rows;      // sequences with 0 < n_rows < min_rows are served by the CUDA-core kernel of the same call
     int q_early;       // 1: q was complete before the preceding kernel was launched, so it may be read before the grid-dependency wait
     int max_polls;     // poll limit of every bounded wait
-    int withhold;      // self-test: gather group 0 never signals its first tile (the waits on it must run out cleanly)
+    int withhold;      // self-test: the gather warp of stage 0 never signals its first tile (the waits on it must run out cleanly)
 };
 
 __device__ __forceinline__ uint32_t sw64_chunk(uint32_t row, uint32_t chunk) { return row * 64u + ((chunk ^ ((row >> 1) & 3u)) << 4); }
@@ -106,6 +114,10 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
     return d;
 }
 
+// Row of the stacked q operand (= TMEM lane of S) that holds term `t` (0 = hi, 1 = lo) of head h: the two terms of a
+// head lie 16 lanes apart inside one warp's lane quarter.
+__device__ __forceinline__ int q_row(int h, int t) { return 32 * (h >> 4) + 16 * t + (h & 15); }
+
 // ---------------------------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------------------------
@@ -113,10 +125,9 @@ __global__ void __launch_bounds__(AM_THREADS, 1)
 attend_mma_kernel(AttendMmaArgs A) {
     extern __shared__ __align__(1024) uint8_t smem[];
     AmBars& bars = *reinterpret_cast<AmBars*>(smem + SM_BARS);
-    float* s_tok = reinterpret_cast<float*>(smem + SM_TOK);
+    float4* s_tok = reinterpret_cast<float4*>(smem + SM_TOK);
     float* s_ahi = reinterpret_cast<float*>(smem + SM_AHI);
     float* s_wmax = reinterpret_cast<float*>(smem + SM_WMAX);
-    float* s_muse = reinterpret_cast<float*>(smem + SM_MUSE);
     float* s_fac = reinterpret_cast<float*>(smem + SM_FAC);
     uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + SM_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_MISC + 4);
@@ -126,19 +137,21 @@ attend_mma_kernel(AttendMmaArgs A) {
     const int P = A.page_tokens;
 
     if (tid == 0) {
-        tc::mbar_init(&bars.k_full[0], 64); tc::mbar_init(&bars.k_full[1], 64);
-        tc::mbar_init(&bars.kv_empty[0], 1); tc::mbar_init(&bars.kv_empty[1], 1);
-        tc::mbar_init(&bars.s_full[0], 1); tc::mbar_init(&bars.s_full[1], 1);
-        tc::mbar_init(&bars.s_empty[0], AM_SW); tc::mbar_init(&bars.s_empty[1], AM_SW);
-        tc::mbar_init(&bars.rope_free, 1); tc::mbar_init(&bars.p_full, AM_SOFTMAX_THREADS);
-        tc::mbar_init(&bars.p_empty, 1); tc::mbar_init(&bars.pv_done, 1);
+#pragma unroll
+        for (int s = 0; s < AM_STAGES; ++s) {
+            tc::mbar_init(&bars.k_full[s], 32); tc::mbar_init(&bars.k_empty[s], 1);
+            tc::mbar_init(&bars.s_full[s], 1); tc::mbar_init(&bars.s_empty[s], AM_SW);
+        }
+#pragma unroll
+        for (int s = 0; s < AM_ROPES; ++s) tc::mbar_init(&bars.rope_free[s], 1);
+        tc::mbar_init(&bars.p_full, AM_SOFTMAX_THREADS);
+        tc::mbar_init(&bars.pv_done, 1);
         tc::mbar_init(&bars.q_full, AM_SOFTMAX_THREADS);
         tc::mbar_init_fence();
         *abort_flag = 0;
     }
-    if (warp == AM_SW) tc::tmem_alloc<512>(tmem_base_s);
+    if (warp == AM_QKW) tc::tmem_alloc<512>(tmem_base_s);
 
-    if (tid < AM_H) { s_muse[tid] = -INFINITY; s_fac[tid] = 1.0f; }   // no reference yet: the first tile takes the exact path
     tc::fence_proxy_async();
     tc::tc_fence_before();
     __syncthreads();
@@ -147,7 +160,9 @@ attend_mma_kernel(AttendMmaArgs A) {
     const uint32_t TM_S0 = tmem, TM_O = tmem + 256;
 
     // q -> two e4m3 terms per head, written straight into the swizzled operand tiles (once per CTA):
-    //   hi = e4m3(q / s), s = absmax / 448;  lo = e4m3((q / s - hi) * 16)   =>  q ~ s * (hi + lo / 16)
+    //   hi = e4m3(q / s), s = absmax / 448;  lo = e4m3(q / s - hi)   =>  q ~ s * (hi + lo)
+    // (the residual of a value of typical size is a normal e4m3 number; below 2^-6 it is kept to 2^-10 absolute,
+    // 2^-19 of the head's largest value).
     // Every softmax warp takes 64 / AM_SW heads; a head's 576 values are 72 chunks of 8 (lane, lane+32, lane+64).
     // The gather warps do not wait for this: the MMA warp does (q_full) before its first QK.
     // Under a programmatic dependent launch the kernel before this one may still be running. Unless the
@@ -172,6 +187,7 @@ attend_mma_kernel(AttendMmaArgs A) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int h = warp * HPW + h4 + u;
+                const int row_hi = q_row(h, 0), row_lo = q_row(h, 1);
                 float f[3][8];
                 float amax = 0.0f;
 #pragma unroll
@@ -201,17 +217,17 @@ attend_mma_kernel(AttendMmaArgs A) {
                                 uint16_t ch, cl;
                                 asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(ch) : "f"(x1), "f"(x0));
                                 const float2 xh = rv_e4m3x2_to_f32x2(ch);
-                                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(cl) : "f"((x1 - xh.y) * 16.0f), "f"((x0 - xh.x) * 16.0f));
+                                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(cl) : "f"(x1 - xh.y), "f"(x0 - xh.x));
                                 hw |= (uint32_t)ch << (8 * e);
                                 lw |= (uint32_t)cl << (8 * e);
                             }
                             hi_w[i] = hw; lo_w[i] = lw;
                         }
                         const int j16 = chunk >> 1, half = (chunk & 1) * 8;
-                        uint8_t* dh = j16 < 32 ? smem + SM_QL + (j16 >> 3) * 16384 + tc::sw128_chunk(h, j16 & 7)
-                                               : smem + SM_QR + sw64_chunk(h, j16 - 32);
-                        uint8_t* dl = j16 < 32 ? smem + SM_QL + (j16 >> 3) * 16384 + tc::sw128_chunk(64 + h, j16 & 7)
-                                               : smem + SM_QR + sw64_chunk(64 + h, j16 - 32);
+                        uint8_t* dh = j16 < 32 ? smem + SM_QL + (j16 >> 3) * 16384 + tc::sw128_chunk(row_hi, j16 & 7)
+                                               : smem + SM_QR + sw64_chunk(row_hi, j16 - 32);
+                        uint8_t* dl = j16 < 32 ? smem + SM_QL + (j16 >> 3) * 16384 + tc::sw128_chunk(row_lo, j16 & 7)
+                                               : smem + SM_QR + sw64_chunk(row_lo, j16 - 32);
                         *reinterpret_cast<uint2*>(dh + half) = make_uint2(hi_w[0], hi_w[1]);
                         *reinterpret_cast<uint2*>(dl + half) = make_uint2(lo_w[0], lo_w[1]);
                     }
@@ -221,6 +237,7 @@ attend_mma_kernel(AttendMmaArgs A) {
         }
         tc::fence_proxy_async();
         tc::mbar_arrive(&bars.q_full);
+        tc::named_barrier(3, AM_SOFTMAX_THREADS);   // the head scales are read by other warps than the ones that wrote them
     }
 
     // With q_early everything above read only inputs that predate the preceding kernel, so it overlapped
@@ -243,19 +260,18 @@ attend_mma_kernel(AttendMmaArgs A) {
     const int ntiles = r_end > r_begin ? (r_end - r_begin + AM_TILE - 1) / AM_TILE : 0;
 
 
-    if (warp > AM_SW && ntiles > 0) {
+    if (warp >= AM_GW0 && ntiles > 0) {
         // ------------------------------ gather producers ------------------------------------------
-        // Two independent groups of two warps: group 0 fills the even tiles (buffer 0), group 1 the odd
-        // ones (buffer 1), each in plain program order (wait for its buffer, copy, signal). With one
-        // group per buffer neither ever waits on the other's buffer, so two tiles are in flight
-        // whenever both buffers are free. A thread owns two rows of its group's tile.
-        const int grp = (warp - AM_SW - 1) >> 1, wi = (warp - AM_SW - 1) & 1;
-        const int pr[2] = {wi * 32 + lane, 64 + wi * 32 + lane};
+        // Warp g fills ring stage g with the tiles g, g + 4, g + 8, ... in plain program order (wait for the stage,
+        // copy, signal), so no warp ever waits on another's stage and four tiles are in flight whenever four stages
+        // are free. A lane owns two rows of its warp's tile.
+        const int g = warp - AM_GW0;
+        const int pr[2] = {lane, 32 + lane};
         bool ok = true;
         // The address chain of a row (selected token -> page -> pool row -> scale) is three dependent
         // global loads; it runs as a software pipeline three tiles deep, one load per stage and
         // iteration, so no copy waits on it: t_n = token two tiles on, r_n = pool row one tile on,
-        // (src, scale) = the current tile ("tile" = the group's own sequence j, j+2, j+4, ...).
+        // (src, scale) = the current tile ("tile" = the warp's own sequence j, j+4, j+8, ...).
         constexpr uint32_t NONE = 0xffffffffu;
         const uint32_t* rowp = listed ? A.rows + (size_t)b * A.row_stride : nullptr;
         const int32_t* btp = A.block_table + (size_t)b * A.max_pages;
@@ -279,8 +295,8 @@ attend_mma_kernel(AttendMmaArgs A) {
         };
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            const uint32_t t0 = load_t(grp, pr[u]), t1 = load_t(grp + 2, pr[u]);
-            t_n[u] = load_t(grp + 4, pr[u]);
+            const uint32_t t0 = load_t(g, pr[u]), t1 = load_t(g + AM_STAGES, pr[u]);
+            t_n[u] = load_t(g + 2 * AM_STAGES, pr[u]);
             const uint32_t r0 = load_r(t0);
             r_n[u] = load_r(t1);
             set_cur(u, r0);
@@ -289,198 +305,180 @@ attend_mma_kernel(AttendMmaArgs A) {
         // the warp on 32 consecutive 16-byte chunks (the row pointer travels by shuffle): one warp
         // instruction then reads 512 contiguous bytes instead of 32 scattered 16-byte pieces.
         const uint4 z = make_uint4(0, 0, 0, 0);
-        for (int j = grp; j < ntiles && ok; j += 2) {
-            uint8_t* kbuf = smem + SM_K0 + grp * SM_KBUF;
-            ok = tc::mbar_wait_warp(&bars.kv_empty[grp], ((j >> 1) & 1) ^ 1, abort_flag, 41, A.max_polls);
+        uint8_t* kbuf = smem + SM_K0 + g * SM_KSTAGE;
+        for (int j = g; j < ntiles && ok; j += AM_STAGES) {
+            const int use = j / AM_STAGES;
+            ok = tc::mbar_wait_warp(&bars.k_empty[g], (use & 1) ^ 1, abort_flag, 41, A.max_polls);
             if (!ok) break;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {              // latent part: row pw + it, chunk = lane
-                const int pw = u * 64 + wi * 32;
+            for (int u = 0; u < 2; ++u) {              // latent part: row 32 u + it, chunk = lane
                 const unsigned long long sp = reinterpret_cast<unsigned long long>(src[u]);
 #pragma unroll 8
                 for (int it = 0; it < 32; ++it) {
                     const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, it));
-                    uint8_t* dst = kbuf + (lane >> 3) * 16384 + tc::sw128_chunk(pw + it, lane & 7);
+                    uint8_t* dst = kbuf + (lane >> 3) * SM_KCHUNK + tc::sw128_chunk(u * 32 + it, lane & 7);
                     if (rs) tc::cp_async16(tc::smem_u32(dst), rs + lane * 16);
                     else *reinterpret_cast<uint4*>(dst) = z;   // rows past the end must be exact zeros:
                 }                                              // 0 x (stale NaN code) would poison O
             }
-            // the single rope buffer is free as soon as the rope MMAs of the previous tile are done
-            ok = tc::mbar_wait_warp(&bars.rope_free, (j & 1) ^ 1, abort_flag, 42, A.max_polls);
+            // a rope tile is free as soon as the two rope MMAs of the tile that used it last are done
+            const int rb = j % AM_ROPES;
+            ok = tc::mbar_wait_warp(&bars.rope_free[rb], ((j / AM_ROPES) & 1) ^ 1, abort_flag, 42, A.max_polls);
             if (!ok) break;
+            uint8_t* rope = smem + SM_ROPE + rb * SM_ROPEBUF;
 #pragma unroll
             for (int u = 0; u < 2; ++u) {              // rope part: 8 rows per instruction, 4 chunks each
-                const int pw = u * 64 + wi * 32;
                 const unsigned long long sp = reinterpret_cast<unsigned long long>(src[u]);
 #pragma unroll
                 for (int it = 0; it < 4; ++it) {
                     const int rl = it * 8 + (lane >> 2);
                     const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, rl));
-                    uint8_t* dst = smem + SM_ROPE + sw64_chunk(pw + rl, lane & 3);
+                    uint8_t* dst = rope + sw64_chunk(u * 32 + rl, lane & 3);
                     if (rs) tc::cp_async16(tc::smem_u32(dst), rs + 512 + (lane & 3) * 16);
                     else *reinterpret_cast<uint4*>(dst) = z;
                 }
-                s_tok[grp * 128 + pr[u]] = scale[u];
+                const bool live = src[u] != nullptr && scale[u] > 0.0f;
+                s_tok[g * AM_TILE + pr[u]] = live ? make_float4(scale[u], log2f(scale[u]) + AM_POFF, 1.0f / scale[u], 0.0f)
+                                                  : make_float4(0.0f, -INFINITY, 0.0f, 0.0f);
             }
             tc::cp_async_commit();
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {              // the group's next tile becomes current
+            for (int u = 0; u < 2; ++u) {              // the warp's next tile becomes current
                 set_cur(u, r_n[u]);
                 r_n[u] = load_r(t_n[u]);
-                t_n[u] = load_t(j + 6, pr[u]);
+                t_n[u] = load_t(j + 3 * AM_STAGES, pr[u]);
             }
             tc::cp_async_wait<0>();
             tc::fence_proxy_async();
-            if (!(A.withhold && j == 0)) tc::mbar_arrive(&bars.k_full[grp]);
+            if (!(A.withhold && j == 0)) tc::mbar_arrive(&bars.k_full[g]);
         }
-    } else if (warp == AM_SW && ntiles > 0) {
-        // ------------------------------ MMA issuer ------------------------------------------------
-        bool ok = true;
-        const uint32_t id_qk = tc::idesc_e4m3(128, 128, 0, 0), id_pv = tc::idesc_e4m3(128, 64, 1, 1);
-        const uint32_t a_ql = tc::smem_u32(smem + SM_QL), a_qr = tc::smem_u32(smem + SM_QR);
-        const uint32_t a_rope = tc::smem_u32(smem + SM_ROPE), a_p = tc::smem_u32(smem + SM_P);
-        // Two in-order instruction streams, QK(0..n-1) and PV(0..n-1), issued in READY order: whichever
-        // has its operands first goes first (PV preferred: it is what frees a K buffer for the gather).
-        int qk_next = 0, pv_next = 0, idle = 0;
-        ok = tc::mbar_wait_warp(&bars.q_full, 0, abort_flag, 51, A.max_polls);
-        tc::tc_fence_after();
-        while (ok && pv_next < ntiles) {
-            int can_pv = 0, can_qk = 0;
-            if (lane == 0) {
-                can_pv = pv_next < qk_next && tc::mbar_test(&bars.p_full, pv_next & 1);
-                if (!can_pv && qk_next < ntiles)
-                    can_qk = tc::mbar_test(&bars.k_full[qk_next & 1], (qk_next >> 1) & 1) &&
-                             tc::mbar_test(&bars.s_empty[qk_next & 1], ((qk_next >> 1) & 1) ^ 1);
+    } else if (warp == AM_QKW) {
+        // ------------------------------ QK issuer -------------------------------------------------
+        // The two MMA streams, QK(0..n-1) and PV(0..n-1), are each in order and are issued by ONE thread each, from two
+        // warps: a thread blocks on the barriers of its own next instruction group only, so neither stream's control
+        // latency (barrier observed -> fence -> issue -> commit) sits in the other's way and the tensor pipe takes
+        // whichever group arrives first. QK runs ahead of the softmax by up to the four S buffers / ring stages.
+        if (lane == 0 && ntiles > 0) {
+            const uint32_t id_qk = tc::idesc_e4m3(128, AM_TILE, 0, 0);
+            const uint64_t d_ql = smem_desc(tc::smem_u32(smem + SM_QL), 16, 1024, 2);
+            const uint64_t d_qr = smem_desc(tc::smem_u32(smem + SM_QR), 16, 512, 4);
+            bool ok = tc::mbar_wait(&bars.q_full, 0, abort_flag, 51, A.max_polls);
+            for (int i = 0; i < ntiles && ok; ++i) {   // S(i) = Qcat . K(i)^T
+                const int s = i % AM_STAGES, use = i / AM_STAGES, rb = i % AM_ROPES;
+                ok = tc::mbar_wait(&bars.k_full[s], use & 1, abort_flag, 52, A.max_polls) &&
+                     tc::mbar_wait(&bars.s_empty[s], (use & 1) ^ 1, abort_flag, 53, A.max_polls);
+                if (!ok) break;
+                tc::tc_fence_after();
+                const uint64_t d_k = smem_desc(tc::smem_u32(smem + SM_K0 + s * SM_KSTAGE), 16, 1024, 2);
+                const uint64_t d_rope = smem_desc(tc::smem_u32(smem + SM_ROPE + rb * SM_ROPEBUF), 16, 512, 4);
+                const uint32_t d = TM_S0 + s * AM_TILE;
+                // rope columns first: their tile is released as soon as these two are done
+#pragma unroll
+                for (int k = 0; k < 2; ++k) tc::mma_f8(d, d_qr + (uint64_t)(k * 2), d_rope + (uint64_t)(k * 2), id_qk, k != 0);
+                tc::mma_commit(&bars.rope_free[rb]);
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)   // descriptor address fields count 16-byte units
+                        tc::mma_f8(d, d_ql + (uint64_t)((c * 16384 + k * 32) >> 4), d_k + (uint64_t)((c * SM_KCHUNK + k * 32) >> 4), id_qk, 1);
+                tc::mma_commit(&bars.s_full[s]);
             }
-            can_pv = __shfl_sync(0xffffffffu, can_pv, 0);
-            can_qk = __shfl_sync(0xffffffffu, can_qk, 0);
-            if (can_qk) {   // S^T(i) = K(i) . Qcat^T
-                const int i = qk_next, kb = i & 1;
+        }
+    } else if (warp == AM_PVW) {
+        // ------------------------------ PV issuer -------------------------------------------------
+        if (lane == 0 && ntiles > 0) {
+            const uint32_t id_pv = tc::idesc_e4m3(128, AM_H, 1, 0);
+            const uint64_t d_phi = smem_desc(tc::smem_u32(smem + SM_P), 16, 512, 4);
+            const uint64_t d_plo = smem_desc(tc::smem_u32(smem + SM_P + SM_PTERM), 16, 512, 4);
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {   // O^T += V(j)^T . P'(j)
+                const int s = j % AM_STAGES;
+                ok = tc::mbar_wait(&bars.p_full, j & 1, abort_flag, 54, A.max_polls);
+                if (!ok) break;
                 tc::tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t a_k = tc::smem_u32(smem + SM_K0 + kb * SM_KBUF);
-                    const uint32_t d = TM_S0 + kb * 128;
-                    // rope columns first: their (single) buffer is released as soon as these two are done
+                const uint64_t d_v = smem_desc(tc::smem_u32(smem + SM_K0 + s * SM_KSTAGE), SM_KCHUNK, 1024, 2);
 #pragma unroll
-                    for (int k = 0; k < 2; ++k)
-                        tc::mma_f8(d, smem_desc(a_rope + k * 32, 16, 512, 4), smem_desc(a_qr + k * 32, 16, 512, 4), id_qk, k != 0);
-                    tc::mma_commit(&bars.rope_free);
+                for (int c = 0; c < 4; ++c) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
+                    for (int k = 0; k < 2; ++k)   // p_hi
+                        tc::mma_f8(TM_O + c * 64, d_v + (uint64_t)((c * SM_KCHUNK + k * 4096) >> 4), d_phi + (uint64_t)(k * 2), id_pv, (j | k) != 0);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            tc::mma_f8(d, smem_desc(a_k + c * 16384 + k * 32, 16, 1024, 2),
-                                       smem_desc(a_ql + c * 16384 + k * 32, 16, 1024, 2), id_qk, 1);
-                    tc::mma_commit(&bars.s_full[kb]);
+                    for (int k = 0; k < 2; ++k)   // p_lo, same accumulator
+                        tc::mma_f8(TM_O + c * 64, d_v + (uint64_t)((c * SM_KCHUNK + k * 4096) >> 4), d_plo + (uint64_t)(k * 2), id_pv, 1);
                 }
-                __syncwarp();
-                ++qk_next; idle = 0;
-            } else if (can_pv) {   // O^T += V(j)^T . P'(j)^T
-                const int j = pv_next, kb = j & 1;
-                tc::tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t a_k = tc::smem_u32(smem + SM_K0 + kb * SM_KBUF);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)   // p_hi
-                            tc::mma_f8(TM_O + c * 64, smem_desc(a_k + c * 16384 + k * 4096, 16384, 1024, 2),
-                                       smem_desc(a_p + k * 4096, 16384, 1024, 2), id_pv, (j | k) != 0);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)   // p_lo, same accumulator
-                            tc::mma_f8(TM_O + c * 64, smem_desc(a_k + c * 16384 + k * 4096, 16384, 1024, 2),
-                                       smem_desc(a_p + 64 + k * 4096, 16384, 1024, 2), id_pv, 1);
-                    }
-                    tc::mma_commit(&bars.kv_empty[kb]);
-                    tc::mma_commit(&bars.p_empty);
-                    tc::mma_commit(&bars.pv_done);
-                }
-                __syncwarp();
-                ++pv_next; idle = 0;
-            } else {
-                if (++idle > 64 * A.max_polls) { *abort_flag = 54; ok = false; }   // bounded: nothing became ready
-                else if ((idle & 255) == 0 && *abort_flag) ok = false;
-                else __nanosleep(100);
+                tc::mma_commit(&bars.k_empty[s]);
+                tc::mma_commit(&bars.pv_done);
             }
         }
     } else if (warp < AM_SW) {
         // ------------------------------ softmax + epilogue ---------------------------------------
-        // thread = (TMEM lane, head half): lane group q = warp % 4 -> token (or latent dim) 32 q + lane,
-        // hg = warp / 4 -> heads AM_HPT hg .. AM_HPT hg + AM_HPT - 1.
-        const int q4 = warp & 3, hg = warp >> 2;
-        const int row = q4 * 32 + lane;                  // token of the tile / dim of a 128-dim block
-        const uint32_t lane_base = ((uint32_t)(q4 * 32)) << 16;
-        const int h0 = hg * AM_HPT;
-        float l_part[AM_HPT];
-#pragma unroll
-        for (int h = 0; h < AM_HPT; ++h) l_part[h] = 0.0f;
-        float m_ref = -INFINITY;                          // threads tid < 64: reference max of head tid
+        // S: TMEM lane = virtual head. Warp (sq, th): lane quarter sq = warp % 4 (heads 16 sq .. 16 sq + 15, hi terms in
+        // lanes 0-15 and lo terms in lanes 16-31), token half th = warp / 4 (columns 32 th .. 32 th + 31 of the tile).
+        // After the hi + lo exchange lane l keeps the 16 tokens 32 th + 16 (l / 16) .. + 15 of head 16 sq + l % 16.
+        // O^T: TMEM lane = latent dim 32 sq + lane of each 128-dim block, head columns 32 th .. 32 th + 31.
+        const int sq = warp & 3, th = warp >> 2, tb = lane >> 4;
+        const int hd = 16 * sq + (lane & 15);
+        const int row = sq * 32 + lane;
+        const uint32_t lane_base = ((uint32_t)(sq * 32)) << 16;
+        const int h0 = th * AM_HPT;
+        const float a_h = s_ahi[hd];
+        float l_acc = 0.0f;                                // sum of this thread's weights of head hd
+        float m_ref = -INFINITY;                           // reference max of head hd (the same in its four threads)
         bool ok = ntiles > 0;
         for (int i = 0; i < ntiles && ok; ++i) {
-            const int kb = i & 1;
-            ok = tc::mbar_wait_warp(&bars.k_full[kb], (i >> 1) & 1, abort_flag, 61, A.max_polls) &&
-                 tc::mbar_wait_warp(&bars.s_full[kb], (i >> 1) & 1, abort_flag, 62, A.max_polls);
+            const int s = i % AM_STAGES, use = i / AM_STAGES;
+            ok = tc::mbar_wait_warp(&bars.k_full[s], use & 1, abort_flag, 61, A.max_polls) &&
+                 tc::mbar_wait_warp(&bars.s_full[s], use & 1, abort_flag, 62, A.max_polls);
             if (!ok) break;
             tc::tc_fence_after();
-            const float stok = s_tok[kb * 128 + row];
-            const bool valid = r_begin + i * AM_TILE + row < r_end && stok > 0.0f;
-            // rows past the end are exact zeros in shared memory, so their raw scores are 0 and an
-            // additive -inf makes every weight of theirs exactly 0 without a select per element
-            const float c2 = valid ? log2f(stok) + AM_POFF : -INFINITY;   // P'' = weight * s_tok * 2^AM_POFF
-            const float inv_tok = valid ? 1.0f / stok : 0.0f;
-            float s2[AM_HPT];
-            float dmax = -INFINITY;               // max over this thread's heads of s2' - reference
+            const float4* ti = s_tok + s * AM_TILE + 32 * th + 16 * tb;   // this thread's 16 tokens
+            float s2[16];
+            float dmax = -INFINITY;               // max over this thread's tokens of s2' - reference
             {
-                uint32_t rh[AM_HPT], rl[AM_HPT];
-                tc::tmem_ldn<AM_HPT>(TM_S0 + kb * 128 + lane_base + h0, rh);
-                tc::tmem_ldn<AM_HPT>(TM_S0 + kb * 128 + lane_base + 64 + h0, rl);
+                uint32_t r[32];
+                tc::tmem_ld32(TM_S0 + s * AM_TILE + lane_base + 32 * th, r);
                 tc::tmem_ld_wait();
+                tc::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&bars.s_empty[s]);
 #pragma unroll
-                for (int h = 0; h < AM_HPT; h += 4) {
-                    const float4 a4 = *reinterpret_cast<const float4*>(s_ahi + h0 + h);
-                    const float4 m4 = *reinterpret_cast<const float4*>(s_muse + h0 + h);
-                    const float av[4] = {a4.x, a4.y, a4.z, a4.w}, mv[4] = {m4.x, m4.y, m4.z, m4.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float raw = fmaf(__uint_as_float(rl[h + e]), 0.0625f, __uint_as_float(rh[h + e]));
-                        s2[h + e] = fmaf(raw, av[e] * stok, c2);
-                        dmax = fmaxf(dmax, s2[h + e] - mv[e]);   // reference is -inf before the first tile
-                    }
+                for (int j = 0; j < 16; ++j) {
+                    const float mine = __uint_as_float(tb ? r[16 + j] : r[j]);
+                    const float give = __uint_as_float(tb ? r[j] : r[16 + j]);
+                    const float raw = mine + __shfl_xor_sync(0xffffffffu, give, 16);
+                    const float4 t = ti[j];
+                    // rows past the end are exact zeros in shared memory, so their raw scores are 0 and an
+                    // additive -inf makes every weight of theirs exactly 0 without a select per element
+                    s2[j] = fmaf(raw, a_h * t.x, t.y);
+                    dmax = fmaxf(dmax, s2[j] - m_ref);   // reference is -inf before the first tile
                 }
             }
-            tc::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&bars.s_empty[kb]);
 
             // Fast path: no score of the tile exceeds its head's reference by more than AM_LAG, so the
             // references stand and nothing has to be exchanged. One barrier-with-OR decides for the CTA.
             uint32_t slow;
             {
-                const uint32_t mine_slow = dmax > AM_LAG + AM_POFF ? 1u : 0u;   // NaN-free: dmax is -inf or finite (s2 carries AM_POFF, the reference does not)
+                const uint32_t mine_slow = dmax > AM_LAG + AM_POFF ? 1u : 0u;   // NaN-free: dmax is -inf or finite or +inf (s2 carries AM_POFF, the reference does not)
                 asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\t"
                              "bar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
                              : "=r"(slow) : "r"(mine_slow), "n"(AM_SOFTMAX_THREADS) : "memory");
             }
             if (slow) {
-                // exact per-head tile max: warp reduce, then fold the 4 lane groups; move the references
+                // exact per-head tile max: this thread's 16 tokens, its partner lane's, the other token half's warp
                 {
-                    float mine = -INFINITY;
+                    float mx = s2[0];
 #pragma unroll
-                    for (int h = 0; h < AM_HPT; ++h) {
-                        float mx;
-                        asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(mx) : "f"(s2[h]));
-                        if (h == lane) mine = mx;
-                    }
-                    if (lane < AM_HPT) s_wmax[q4 * 64 + h0 + lane] = mine;
+                    for (int j = 1; j < 16; ++j) mx = fmaxf(mx, s2[j]);
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    if (lane < 16) s_wmax[th * 64 + hd] = mx;
                 }
                 tc::named_barrier(2, AM_SOFTMAX_THREADS);
-                if (tid < AM_H) {
-                    const float tm = fmaxf(fmaxf(s_wmax[tid], s_wmax[64 + tid]), fmaxf(s_wmax[128 + tid], s_wmax[192 + tid])) - AM_POFF;
-                    float fac = 1.0f;
+                float fac = 1.0f;
+                {
+                    const float tm = fmaxf(s_wmax[hd], s_wmax[64 + hd]) - AM_POFF;
                     if (m_ref == -INFINITY) { if (tm > -INFINITY) m_ref = tm; }          // first live tile of this head
                     else if (tm > m_ref) { fac = exp2f(m_ref - tm); m_ref = tm; }          // any growth is taken now
-                    s_muse[tid] = m_ref;
-                    s_fac[tid] = fac;
+                    if (th == 0 && lane < 16) s_fac[hd] = fac;
                 }
                 tc::named_barrier(2, AM_SOFTMAX_THREADS);
                 // bring O^T and l to the new references. PV(i-1) must have landed first.
@@ -490,33 +488,32 @@ attend_mma_kernel(AttendMmaArgs A) {
                     uint32_t r[AM_HPT];
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {   // this thread's dim lane, its head columns of each block
-                        tc::tmem_ldn<AM_HPT>(TM_O + lane_base + c * 64 + h0, r);
+                        tc::tmem_ld32(TM_O + lane_base + c * 64 + h0, r);
                         tc::tmem_ld_wait();
 #pragma unroll
                         for (int h = 0; h < AM_HPT; ++h) r[h] = __float_as_uint(__uint_as_float(r[h]) * s_fac[h0 + h]);
-                        tc::tmem_stn<AM_HPT>(TM_O + lane_base + c * 64 + h0, r);
+                        tc::tmem_st32(TM_O + lane_base + c * 64 + h0, r);
                     }
                     tc::tmem_st_wait();
                 }
-#pragma unroll
-                for (int h = 0; h < AM_HPT; ++h) l_part[h] *= s_fac[h0 + h];
+                l_acc *= fac;
                 tc::tc_fence_before();
             }
             // P'' = 2^(s2' - m) = weight * s_tok * 2^AM_POFF as two e4m3 terms (via f16: p <= 256 and the
-            // residual p - hi are exact enough in half precision); l accumulates the plain weight
-            uint32_t hi_w[AM_HPT / 4], lo_w[AM_HPT / 4];
+            // residual p - hi are exact enough in half precision); l accumulates the plain weight.
+            // A head that has seen no live token yet has no reference: its scores are all -inf and weigh 0.
+            const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+            uint32_t hi_w[4], lo_w[4];
 #pragma unroll
-            for (int h = 0; h < AM_HPT; h += 4) {
-                const float4 m4 = *reinterpret_cast<const float4*>(s_muse + h0 + h);
-                const float mv[4] = {m4.x, m4.y, m4.z, m4.w};
+            for (int j = 0; j < 16; j += 4) {
                 uint32_t chs[2], cls[2];
 #pragma unroll
                 for (int e = 0; e < 4; e += 2) {
                     float p0, p1;
-                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(s2[h + e] - mv[e]));
-                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(s2[h + e + 1] - mv[e + 1]));
-                    l_part[h + e] = fmaf(p0, inv_tok, l_part[h + e]);
-                    l_part[h + e + 1] = fmaf(p1, inv_tok, l_part[h + e + 1]);
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(s2[j + e] - m_use));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(s2[j + e + 1] - m_use));
+                    l_acc = fmaf(p0, ti[j + e].z, l_acc);
+                    l_acc = fmaf(p1, ti[j + e + 1].z, l_acc);
                     const __half2 ph = __floats2half2_rn(p0, p1);
                     const uint32_t phb = *reinterpret_cast<const uint32_t*>(&ph);
                     uint16_t ch, cl;
@@ -527,20 +524,16 @@ attend_mma_kernel(AttendMmaArgs A) {
                     asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(cl) : "r"(*reinterpret_cast<const uint32_t*>(&res)));
                     chs[e >> 1] = ch; cls[e >> 1] = cl;
                 }
-                hi_w[h >> 2] = chs[0] | (chs[1] << 16);
-                lo_w[h >> 2] = cls[0] | (cls[1] << 16);
+                hi_w[j >> 2] = chs[0] | (chs[1] << 16);
+                lo_w[j >> 2] = cls[0] | (cls[1] << 16);
             }
-            ok = tc::mbar_wait_warp(&bars.p_empty, (i & 1) ^ 1, abort_flag, 64, A.max_polls);
+            ok = tc::mbar_wait_warp(&bars.pv_done, (i & 1) ^ 1, abort_flag, 64, A.max_polls);   // PV(i - 1) has read the P' tile
             if (!ok) break;
             {
-                uint8_t* prow = smem + SM_P;
-#pragma unroll
-                for (int c = 0; c < AM_HPT / 16; ++c) {   // a 16-byte chunk = 16 heads of one term
-                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(row, hg * (AM_HPT / 16) + c)) =
-                        make_uint4(hi_w[4 * c], hi_w[4 * c + 1], hi_w[4 * c + 2], hi_w[4 * c + 3]);
-                    *reinterpret_cast<uint4*>(prow + tc::sw128_chunk(row, 4 + hg * (AM_HPT / 16) + c)) =
-                        make_uint4(lo_w[4 * c], lo_w[4 * c + 1], lo_w[4 * c + 2], lo_w[4 * c + 3]);
-                }
+                // row = head, bytes = tokens: this thread's 16 tokens are the 16-byte chunk 2 th + tb of its head's row
+                uint8_t* prow = smem + SM_P + sw64_chunk(hd, 2 * th + tb);
+                *reinterpret_cast<uint4*>(prow) = make_uint4(hi_w[0], hi_w[1], hi_w[2], hi_w[3]);
+                *reinterpret_cast<uint4*>(prow + SM_PTERM) = make_uint4(lo_w[0], lo_w[1], lo_w[2], lo_w[3]);
             }
             tc::fence_proxy_async();
             tc::mbar_arrive(&bars.p_full);
@@ -549,35 +542,17 @@ attend_mma_kernel(AttendMmaArgs A) {
         // ---- epilogue ----
         if (ok && ntiles > 0) ok = tc::mbar_wait_warp(&bars.pv_done, (ntiles - 1) & 1, abort_flag, 65, A.max_polls);
         tc::tc_fence_after();
-        // l per head: the warp's 32 token lanes each hold AM_HPT partial sums; a recursive-halving exchange (a lane
-        // keeps the half of the heads whose index bit matches its own lane bit and sends the other half) leaves the
-        // sum of head j in lane j after AM_HPT - 1 shuffles, instead of a five-step butterfly per head. Then the 4
-        // lane groups meet through shared memory.
+        // l per head: its four threads (two lanes 16 apart in each of the two token-half warps) meet by one shuffle
+        // and one exchange through shared memory.
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
         {
-            int n = AM_HPT;
-#pragma unroll
-            for (int off = AM_HPT / 2; off >= 1; off >>= 1) {
-                n >>= 1;
-                const bool up = (lane & off) != 0;
-#pragma unroll
-                for (int i = 0; i < AM_HPT / 2; ++i) {
-                    if (i < n) {
-                        const float send = up ? l_part[i] : l_part[i + n];
-                        const float recv = __shfl_xor_sync(0xffffffffu, send, off);
-                        l_part[i] = (up ? l_part[i + n] : l_part[i]) + recv;
-                    }
-                }
-            }
-            // with fewer heads than lanes (AM_HPT == 16) lanes l and l ^ 16 hold two halves of head (l & 15)
-            float mine = l_part[0];
-            if (AM_HPT < 32) mine += __shfl_xor_sync(0xffffffffu, mine, 16);
-            if (lane < AM_HPT) s_wmax[q4 * 64 + h0 + lane] = mine;
+            const float mine = l_acc + __shfl_xor_sync(0xffffffffu, l_acc, 16);
+            if (lane < 16) s_wmax[th * 64 + hd] = mine;
         }
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
-        if (tid < AM_H) {
-            const int h = tid;
-            const float l = s_wmax[h] + s_wmax[64 + h] + s_wmax[128 + h] + s_wmax[192 + h];
+        if (th == 0 && lane < 16) {
+            const int h = hd;
+            const float l = s_wmax[h] + s_wmax[64 + h];
             const float m_nat = (m_ref - AM_POFF) * 0.6931471805599453f;   // natural-log units (l and O carry 2^AM_POFF)
             if (skip) {
                 // nothing: the sequence's output and statistics are written by the CUDA-core kernel
@@ -590,7 +565,7 @@ attend_mma_kernel(AttendMmaArgs A) {
                 if (A.out_m) A.out_m[(size_t)b * AM_H + h] = l > 0.0f ? m_nat : -INFINITY;
                 if (A.out_lse) A.out_lse[(size_t)b * AM_H + h] = l > 0.0f ? m_nat + logf(l) : -INFINITY;
             }
-            s_muse[h] = l > 0.0f ? 1.0f / l : 0.0f;
+            s_fac[h] = l > 0.0f ? 1.0f / l : 0.0f;
         }
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
         // O^T: this thread's TMEM lane is one latent dim of each 128-dim block; its head columns. For a given head
@@ -600,7 +575,7 @@ attend_mma_kernel(AttendMmaArgs A) {
         float inv_l[AM_HPT];   // 1 / l of this thread's heads (registers: the stores below must not wait on loads)
 #pragma unroll
         for (int h = 0; h < AM_HPT; h += 4) {
-            const float4 m4 = *reinterpret_cast<const float4*>(s_muse + h0 + h);
+            const float4 m4 = *reinterpret_cast<const float4*>(s_fac + h0 + h);
             inv_l[h] = m4.x; inv_l[h + 1] = m4.y; inv_l[h + 2] = m4.z; inv_l[h + 3] = m4.w;
         }
         float* part = A.n_splits > 1 ? A.partial + (size_t)b * A.n_splits * AM_H * (AM_KVL + 2) +
@@ -610,7 +585,7 @@ attend_mma_kernel(AttendMmaArgs A) {
             const int dim = c * 128 + row;
             uint32_t r[AM_HPT];
             if (ntiles > 0 && ok) {
-                tc::tmem_ldn<AM_HPT>(TM_O + lane_base + c * 64 + h0, r);
+                tc::tmem_ld32(TM_O + lane_base + c * 64 + h0, r);
                 tc::tmem_ld_wait();
             } else {
 #pragma unroll
@@ -629,7 +604,7 @@ attend_mma_kernel(AttendMmaArgs A) {
 
     tc::tc_fence_before();
     __syncthreads();
-    if (warp == AM_SW) tc::tmem_dealloc<512>(tmem);
+    if (warp == AM_QKW) tc::tmem_dealloc<512>(tmem);
     if (tid == 0 && *abort_flag) atomicCAS(A.err, 0, *abort_flag);
 }
 
