@@ -21,11 +21,11 @@
 //                                   4 blocks x 2 K-steps x {hi, lo} = 16 MMAs (N = 64)
 // TMEM (512 columns): S four deep (4 x 64) + O^T (4 x 64).
 //
-// One CTA per (sequence, split), 14 warps: 0-7 softmax + epilogue, 8 QK issue, 9 PV issue, 10-13 gather (warp g owns ring
-// stage g: tiles g, g + 4, ... in plain program order, so four tiles are in flight whenever four stages are
-// free; a lane locates rows, copies go row by row with 32 lanes on 32 consecutive 16-byte chunks (cp.async into
-// the swizzled tile); the row address chain (token -> page -> pool row -> scale) is software-pipelined three
-// tiles deep).
+// One CTA per (sequence, split), 14 warps: 0-7 softmax + epilogue, 8 QK issue, 9 PV issue, 10-13 gather (the four
+// warps fill the ring tile by tile, 16 rows each, and do not wait for their copies: the copies signal the stage's
+// barrier themselves, so up to four tiles are in flight and land one after the other; a lane locates rows, copies go
+// row by row with 32 lanes on 32 consecutive 16-byte chunks (cp.async into the swizzled tile); the row address chain
+// (token -> page -> pool row -> scale) is software-pipelined three tiles deep).
 // A softmax thread is one TMEM lane = one virtual head, and the q rows are ordered so that the hi and lo terms of a
 // head sit 16 lanes apart in the SAME warp: lanes 0-15 of warp s hold the hi rows of heads 16 s .. 16 s + 15, lanes
 // 16-31 their lo rows. One shuffle per score adds the two terms and leaves each lane with HALF the tokens of its
@@ -99,7 +99,7 @@ struct AttendMmaArgs {
     int min_rows;      // sequences with 0 < n_rows < min_rows are served by the CUDA-core kernel of the same call
     int q_early;       // 1: q was complete before the preceding kernel was launched, so it may be read before the grid-dependency wait
     int max_polls;     // poll limit of every bounded wait
-    int withhold;      // self-test: the gather warp of stage 0 never signals its first tile (the waits on it must run out cleanly)
+    int withhold;      // self-test: one gather warp never signals its part of the first tile (the waits on it must run out cleanly)
 };
 
 __device__ __forceinline__ uint32_t sw64_chunk(uint32_t row, uint32_t chunk) { return row * 64u + ((chunk ^ ((row >> 1) & 3u)) << 4); }
@@ -139,7 +139,7 @@ attend_mma_kernel(AttendMmaArgs A) {
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < AM_STAGES; ++s) {
-            tc::mbar_init(&bars.k_full[s], 32); tc::mbar_init(&bars.k_empty[s], 1);
+            tc::mbar_init(&bars.k_full[s], AM_STAGES * 32 + AM_STAGES); tc::mbar_init(&bars.k_empty[s], 1);
             tc::mbar_init(&bars.s_full[s], 1); tc::mbar_init(&bars.s_empty[s], AM_SW);
         }
 #pragma unroll
@@ -262,21 +262,23 @@ attend_mma_kernel(AttendMmaArgs A) {
 
     if (warp >= AM_GW0 && ntiles > 0) {
         // ------------------------------ gather producers ------------------------------------------
-        // Warp g fills ring stage g with the tiles g, g + 4, g + 8, ... in plain program order (wait for the stage,
-        // copy, signal), so no warp ever waits on another's stage and four tiles are in flight whenever four stages
-        // are free. A lane owns two rows of its warp's tile.
+        // The four warps fill the ring TILE BY TILE, each copying 16 rows of every tile, and never wait for a copy to
+        // land: a thread's copies signal the stage's barrier themselves when they are complete
+        // (cp.async.mbarrier.arrive), so a warp goes straight on to the next free stage. Tiles therefore land one after
+        // the other, each with the whole ingest bandwidth of the SM, instead of four at a time at a quarter of it:
+        // the first can be multiplied while the next ones are still in flight.
         const int g = warp - AM_GW0;
-        const int pr[2] = {lane, 32 + lane};
+        const int myrow = 16 * g + (lane & 15);            // the tile row whose address this lane resolves (both half-warps alike)
         bool ok = true;
         // The address chain of a row (selected token -> page -> pool row -> scale) is three dependent
         // global loads; it runs as a software pipeline three tiles deep, one load per stage and
         // iteration, so no copy waits on it: t_n = token two tiles on, r_n = pool row one tile on,
-        // (src, scale) = the current tile ("tile" = the warp's own sequence j, j+4, j+8, ...).
+        // (src, scale) = the current tile.
         constexpr uint32_t NONE = 0xffffffffu;
         const uint32_t* rowp = listed ? A.rows + (size_t)b * A.row_stride : nullptr;
         const int32_t* btp = A.block_table + (size_t)b * A.max_pages;
-        auto load_t = [&](int j, int p) -> uint32_t {
-            const int ri = r_begin + j * AM_TILE + p;
+        auto load_t = [&](int j) -> uint32_t {
+            const int ri = r_begin + j * AM_TILE + myrow;
             if (j >= ntiles || ri >= r_end) return NONE;
             return rowp ? rowp[ri] : (uint32_t)ri;
         };
@@ -286,40 +288,36 @@ attend_mma_kernel(AttendMmaArgs A) {
             const int pg = lp < A.max_pages ? btp[lp] : -1;
             return (pg >= 0 && pg < A.n_pool_pages) ? (uint32_t)pg * (uint32_t)P + (t & (uint32_t)(P - 1)) : NONE;
         };
-        const uint8_t* src[2];
-        float scale[2];
-        uint32_t t_n[2], r_n[2];
-        auto set_cur = [&](int u, uint32_t r) {
-            src[u] = nullptr; scale[u] = 0.0f;
-            if (r != NONE) { src[u] = A.pool + (size_t)r * AM_W; scale[u] = A.pscale[r]; }
+        const uint8_t* src = nullptr;
+        float scale = 0.0f;
+        auto set_cur = [&](uint32_t r) {
+            src = nullptr; scale = 0.0f;
+            if (r != NONE) { src = A.pool + (size_t)r * AM_W; scale = A.pscale[r]; }
         };
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const uint32_t t0 = load_t(g, pr[u]), t1 = load_t(g + AM_STAGES, pr[u]);
-            t_n[u] = load_t(g + 2 * AM_STAGES, pr[u]);
+        uint32_t t_n, r_n;
+        {
+            const uint32_t t0 = load_t(0), t1 = load_t(1);
+            t_n = load_t(2);
             const uint32_t r0 = load_r(t0);
-            r_n[u] = load_r(t1);
-            set_cur(u, r0);
+            r_n = load_r(t1);
+            set_cur(r0);
         }
         // Each lane owns the address of a row, but the COPIES are issued row by row with the 32 lanes of
         // the warp on 32 consecutive 16-byte chunks (the row pointer travels by shuffle): one warp
-        // instruction then reads 512 contiguous bytes instead of 32 scattered 16-byte pieces.
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        uint8_t* kbuf = smem + SM_K0 + g * SM_KSTAGE;
-        for (int j = g; j < ntiles && ok; j += AM_STAGES) {
-            const int use = j / AM_STAGES;
-            ok = tc::mbar_wait_warp(&bars.k_empty[g], (use & 1) ^ 1, abort_flag, 41, A.max_polls);
+        // instruction then reads 512 contiguous bytes instead of 32 scattered 16-byte pieces. A row past the end
+        // (or on an unmapped page) is written as exact zeros by the same instruction with a source size of 0:
+        // 0 x (stale NaN code) would poison O.
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int s = j % AM_STAGES, use = j / AM_STAGES;
+            ok = tc::mbar_wait_warp(&bars.k_empty[s], (use & 1) ^ 1, abort_flag, 41, A.max_polls);
             if (!ok) break;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {              // latent part: row 32 u + it, chunk = lane
-                const unsigned long long sp = reinterpret_cast<unsigned long long>(src[u]);
+            uint8_t* kbuf = smem + SM_K0 + s * SM_KSTAGE;
+            const unsigned long long sp = reinterpret_cast<unsigned long long>(src);
 #pragma unroll 8
-                for (int it = 0; it < 32; ++it) {
-                    const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, it));
-                    uint8_t* dst = kbuf + (lane >> 3) * SM_KCHUNK + tc::sw128_chunk(u * 32 + it, lane & 7);
-                    if (rs) tc::cp_async16(tc::smem_u32(dst), rs + lane * 16);
-                    else *reinterpret_cast<uint4*>(dst) = z;   // rows past the end must be exact zeros:
-                }                                              // 0 x (stale NaN code) would poison O
+            for (int it = 0; it < 16; ++it) {          // latent part: row 16 g + it, chunk = lane
+                const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, it));
+                uint8_t* dst = kbuf + (lane >> 3) * SM_KCHUNK + tc::sw128_chunk(16 * g + it, lane & 7);
+                tc::cp_async16_zfill(tc::smem_u32(dst), rs ? rs + lane * 16 : A.pool, rs ? 16u : 0u);
             }
             // a rope tile is free as soon as the two rope MMAs of the tile that used it last are done
             const int rb = j % AM_ROPES;
@@ -327,30 +325,25 @@ attend_mma_kernel(AttendMmaArgs A) {
             if (!ok) break;
             uint8_t* rope = smem + SM_ROPE + rb * SM_ROPEBUF;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {              // rope part: 8 rows per instruction, 4 chunks each
-                const unsigned long long sp = reinterpret_cast<unsigned long long>(src[u]);
-#pragma unroll
-                for (int it = 0; it < 4; ++it) {
-                    const int rl = it * 8 + (lane >> 2);
-                    const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, rl));
-                    uint8_t* dst = rope + sw64_chunk(u * 32 + rl, lane & 3);
-                    if (rs) tc::cp_async16(tc::smem_u32(dst), rs + 512 + (lane & 3) * 16);
-                    else *reinterpret_cast<uint4*>(dst) = z;
-                }
-                const bool live = src[u] != nullptr && scale[u] > 0.0f;
-                s_tok[g * AM_TILE + pr[u]] = live ? make_float4(scale[u], log2f(scale[u]) + AM_POFF, 1.0f / scale[u], 0.0f)
+            for (int it = 0; it < 2; ++it) {           // rope part: 8 rows per instruction, 4 chunks each
+                const int rl = it * 8 + (lane >> 2);
+                const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, rl));
+                uint8_t* dst = rope + sw64_chunk(16 * g + rl, lane & 3);
+                tc::cp_async16_zfill(tc::smem_u32(dst), rs ? rs + 512 + (lane & 3) * 16 : A.pool, rs ? 16u : 0u);
+            }
+            if (lane < 16) {
+                const bool live = src != nullptr && scale > 0.0f;
+                s_tok[s * AM_TILE + myrow] = live ? make_float4(scale, log2f(scale) + AM_POFF, 1.0f / scale, 0.0f)
                                                   : make_float4(0.0f, -INFINITY, 0.0f, 0.0f);
             }
-            tc::cp_async_commit();
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {              // the warp's next tile becomes current
-                set_cur(u, r_n[u]);
-                r_n[u] = load_r(t_n[u]);
-                t_n[u] = load_t(j + 3 * AM_STAGES, pr[u]);
-            }
-            tc::cp_async_wait<0>();
-            tc::fence_proxy_async();
-            if (!(A.withhold && j == 0)) tc::mbar_arrive(&bars.k_full[g]);
+            // the stage is full when every thread's copies have landed (128 arrivals by the copies themselves) and every
+            // warp's token scales are written (4 plain arrivals, which also publish those stores)
+            tc::cp_async_mbar_arrive_noinc(&bars.k_full[s]);
+            __syncwarp();
+            if (lane == 0 && !(A.withhold && j == 0 && g == 0)) tc::mbar_arrive(&bars.k_full[s]);
+            set_cur(r_n);                              // the next tile becomes current
+            r_n = load_r(t_n);
+            t_n = load_t(j + 3);
         }
     } else if (warp == AM_QKW) {
         // ------------------------------ QK issuer -------------------------------------------------
@@ -368,6 +361,7 @@ attend_mma_kernel(AttendMmaArgs A) {
                 ok = tc::mbar_wait(&bars.k_full[s], use & 1, abort_flag, 52, A.max_polls) &&
                      tc::mbar_wait(&bars.s_empty[s], (use & 1) ^ 1, abort_flag, 53, A.max_polls);
                 if (!ok) break;
+                tc::fence_proxy_async();   // the copies wrote through the generic proxy, the MMAs read through the async one
                 tc::tc_fence_after();
                 const uint64_t d_k = smem_desc(tc::smem_u32(smem + SM_K0 + s * SM_KSTAGE), 16, 1024, 2);
                 const uint64_t d_rope = smem_desc(tc::smem_u32(smem + SM_ROPE + rb * SM_ROPEBUF), 16, 512, 4);
@@ -395,6 +389,7 @@ attend_mma_kernel(AttendMmaArgs A) {
                 const int s = j % AM_STAGES;
                 ok = tc::mbar_wait(&bars.p_full, j & 1, abort_flag, 54, A.max_polls);
                 if (!ok) break;
+                tc::fence_proxy_async();
                 tc::tc_fence_after();
                 const uint64_t d_v = smem_desc(tc::smem_u32(smem + SM_K0 + s * SM_KSTAGE), SM_KCHUNK, 1024, 2);
 #pragma unroll
