@@ -270,40 +270,48 @@ attend_mma_kernel(AttendMmaArgs A) {
         const int g = warp - AM_GW0;
         const int myrow = 16 * g + (lane & 15);            // the tile row whose address this lane resolves (both half-warps alike)
         bool ok = true;
-        // The address chain of a row (selected token -> page -> pool row -> scale) is three dependent
-        // global loads; it runs as a software pipeline three tiles deep, one load per stage and
-        // iteration, so no copy waits on it: t_n = token two tiles on, r_n = pool row one tile on,
-        // (src, scale) = the current tile.
+        // The address chain of a row (selected token -> page -> pool row -> scale) is three dependent global loads, and
+        // under load each of them comes back only after the tens of kilobytes of copies queued in front of it: several
+        // tiles later. It therefore runs as a software pipeline AM_LOOK tiles deep PER LEVEL that keeps the raw loaded
+        // words in register queues and touches a word only AM_LOOK iterations after it was requested (the warp issues
+        // in order: a use right behind its load would stall every copy after it):
+        //   tk[k]            token of tile j + 2 AM_LOOK + k, being loaded
+        //   tok[k], pg[k]    token of tile j + AM_LOOK + k and its page-table entry, being loaded
+        //   row[k], scl[k]   pool row of tile j + k (NONE: write zeros) and its scale, being loaded; k = 0 is the current tile
         constexpr uint32_t NONE = 0xffffffffu;
+        constexpr int AM_LOOK = 3;
         const uint32_t* rowp = listed ? A.rows + (size_t)b * A.row_stride : nullptr;
         const int32_t* btp = A.block_table + (size_t)b * A.max_pages;
-        auto load_t = [&](int j) -> uint32_t {
+        const int pshift = 31 - __clz(P);                  // page sizes are powers of two (checked by the host entry)
+        auto load_tok = [&](int j) -> uint32_t {
             const int ri = r_begin + j * AM_TILE + myrow;
             if (j >= ntiles || ri >= r_end) return NONE;
             return rowp ? rowp[ri] : (uint32_t)ri;
         };
-        auto load_r = [&](uint32_t t) -> uint32_t {
-            if (t == NONE) return NONE;
-            const int lp = (int)(t / (uint32_t)P);
-            const int pg = lp < A.max_pages ? btp[lp] : -1;
-            return (pg >= 0 && pg < A.n_pool_pages) ? (uint32_t)pg * (uint32_t)P + (t & (uint32_t)(P - 1)) : NONE;
+        auto load_pg = [&](uint32_t t) -> int32_t {
+            if (t == NONE) return -1;
+            const uint32_t lp = t >> pshift;
+            return lp < (uint32_t)A.max_pages ? btp[lp] : -1;
         };
-        const uint8_t* src = nullptr;
-        float scale = 0.0f;
-        auto set_cur = [&](uint32_t r) {
-            src = nullptr; scale = 0.0f;
-            if (r != NONE) { src = A.pool + (size_t)r * AM_W; scale = A.pscale[r]; }
+        auto pool_row = [&](uint32_t t, int32_t pg) -> uint32_t {
+            return (t != NONE && pg >= 0 && pg < A.n_pool_pages) ? (uint32_t)pg * (uint32_t)P + (t & (uint32_t)(P - 1)) : NONE;
         };
-        uint32_t t_n, r_n;
-        {
-            const uint32_t t0 = load_t(0), t1 = load_t(1);
-            t_n = load_t(2);
-            const uint32_t r0 = load_r(t0);
-            r_n = load_r(t1);
-            set_cur(r0);
+        auto load_scl = [&](uint32_t r) -> float { return r != NONE ? A.pscale[r] : 0.0f; };
+        uint32_t tk[AM_LOOK], tok[AM_LOOK], row[AM_LOOK];
+        int32_t pg[AM_LOOK];
+        float scl[AM_LOOK];
+        {   // prologue: all token loads at once, then the page entries, then the scales of the first tiles
+            uint32_t t0[AM_LOOK];
+            int32_t p0[AM_LOOK];
+#pragma unroll
+            for (int k = 0; k < AM_LOOK; ++k) { t0[k] = load_tok(k); tok[k] = load_tok(AM_LOOK + k); tk[k] = load_tok(2 * AM_LOOK + k); }
+#pragma unroll
+            for (int k = 0; k < AM_LOOK; ++k) { p0[k] = load_pg(t0[k]); pg[k] = load_pg(tok[k]); }
+#pragma unroll
+            for (int k = 0; k < AM_LOOK; ++k) { row[k] = pool_row(t0[k], p0[k]); scl[k] = load_scl(row[k]); }
         }
         // Each lane owns the address of a row, but the COPIES are issued row by row with the 32 lanes of
-        // the warp on 32 consecutive 16-byte chunks (the row pointer travels by shuffle): one warp
+        // the warp on 32 consecutive 16-byte chunks (the pool row travels by shuffle): one warp
         // instruction then reads 512 contiguous bytes instead of 32 scattered 16-byte pieces. A row past the end
         // (or on an unmapped page) is written as exact zeros by the same instruction with a source size of 0:
         // 0 x (stale NaN code) would poison O.
@@ -312,12 +320,11 @@ attend_mma_kernel(AttendMmaArgs A) {
             ok = tc::mbar_wait_warp(&bars.k_empty[s], (use & 1) ^ 1, abort_flag, 41, A.max_polls);
             if (!ok) break;
             uint8_t* kbuf = smem + SM_K0 + s * SM_KSTAGE;
-            const unsigned long long sp = reinterpret_cast<unsigned long long>(src);
 #pragma unroll 8
             for (int it = 0; it < 16; ++it) {          // latent part: row 16 g + it, chunk = lane
-                const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, it));
+                const uint32_t r = __shfl_sync(0xffffffffu, row[0], it);
                 uint8_t* dst = kbuf + (lane >> 3) * SM_KCHUNK + tc::sw128_chunk(16 * g + it, lane & 7);
-                tc::cp_async16_zfill(tc::smem_u32(dst), rs ? rs + lane * 16 : A.pool, rs ? 16u : 0u);
+                tc::cp_async16_zfill(tc::smem_u32(dst), A.pool + (r != NONE ? (size_t)r * AM_W + lane * 16 : 0), r != NONE ? 16u : 0u);
             }
             // a rope tile is free as soon as the two rope MMAs of the tile that used it last are done
             const int rb = j % AM_ROPES;
@@ -327,23 +334,31 @@ attend_mma_kernel(AttendMmaArgs A) {
 #pragma unroll
             for (int it = 0; it < 2; ++it) {           // rope part: 8 rows per instruction, 4 chunks each
                 const int rl = it * 8 + (lane >> 2);
-                const uint8_t* rs = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, sp, rl));
+                const uint32_t r = __shfl_sync(0xffffffffu, row[0], rl);
                 uint8_t* dst = rope + sw64_chunk(16 * g + rl, lane & 3);
-                tc::cp_async16_zfill(tc::smem_u32(dst), rs ? rs + 512 + (lane & 3) * 16 : A.pool, rs ? 16u : 0u);
-            }
-            if (lane < 16) {
-                const bool live = src != nullptr && scale > 0.0f;
-                s_tok[s * AM_TILE + myrow] = live ? make_float4(scale, log2f(scale) + AM_POFF, 1.0f / scale, 0.0f)
-                                                  : make_float4(0.0f, -INFINITY, 0.0f, 0.0f);
+                tc::cp_async16_zfill(tc::smem_u32(dst), A.pool + (r != NONE ? (size_t)r * AM_W + 512 + (lane & 3) * 16 : 0), r != NONE ? 16u : 0u);
             }
             // the stage is full when every thread's copies have landed (128 arrivals by the copies themselves) and every
             // warp's token scales are written (4 plain arrivals, which also publish those stores)
             tc::cp_async_mbar_arrive_noinc(&bars.k_full[s]);
+            if (lane < 16) {
+                const float sc = scl[0];
+                const bool live = row[0] != NONE && sc > 0.0f;
+                s_tok[s * AM_TILE + myrow] = live ? make_float4(sc, __log2f(sc) + AM_POFF, __frcp_rn(sc), 0.0f)
+                                                  : make_float4(0.0f, -INFINITY, 0.0f, 0.0f);
+            }
             __syncwarp();
             if (lane == 0 && !(A.withhold && j == 0 && g == 0)) tc::mbar_arrive(&bars.k_full[s]);
-            set_cur(r_n);                              // the next tile becomes current
-            r_n = load_r(t_n);
-            t_n = load_t(j + 3);
+            // advance the chain: every value consumed here was requested AM_LOOK iterations ago
+            {
+                const uint32_t row_new = pool_row(tok[0], pg[0]);
+                const uint32_t tok_new = tk[0];
+#pragma unroll
+                for (int k = 0; k + 1 < AM_LOOK; ++k) { row[k] = row[k + 1]; scl[k] = scl[k + 1]; tok[k] = tok[k + 1]; pg[k] = pg[k + 1]; tk[k] = tk[k + 1]; }
+                row[AM_LOOK - 1] = row_new; scl[AM_LOOK - 1] = load_scl(row_new);
+                tok[AM_LOOK - 1] = tok_new; pg[AM_LOOK - 1] = load_pg(tok_new);
+                tk[AM_LOOK - 1] = load_tok(j + 3 * AM_LOOK);
+            }
         }
     } else if (warp == AM_QKW) {
         // ------------------------------ QK issuer -------------------------------------------------
