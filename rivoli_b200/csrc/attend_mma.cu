@@ -71,8 +71,9 @@ constexpr int SM_QL = SM_ROPE + AM_ROPES * SM_ROPEBUF;       // 4 chunks x [128 
 constexpr int SM_QR = SM_QL + 65536;     // [128 virtual heads][64 B], 64-byte swizzle
 constexpr int SM_P = SM_QR + 8192;       // hi [64 heads][64 tokens], lo the same: K-major, 64-byte swizzle
 constexpr int SM_PTERM = 4096;
-constexpr int SM_TOK = SM_P + 2 * SM_PTERM;   // float4 [4 stages][64 tokens]: scale, log2(scale) + AM_POFF, 1 / scale, -
-constexpr int SM_AHI = SM_TOK + AM_STAGES * AM_TILE * 16;   // f32 [64] per-head q scale * softmax scale * log2(e)
+constexpr int SM_TOK = SM_P + 2 * SM_PTERM;   // f32 [3][4 stages][64 tokens]: scale | log2(scale) + AM_POFF | 1 / scale
+constexpr int SM_TOKPLANE = AM_STAGES * AM_TILE * 4;
+constexpr int SM_AHI = SM_TOK + 3 * SM_TOKPLANE;   // f32 [64] per-head q scale * softmax scale * log2(e)
 constexpr int SM_WMAX = SM_AHI + 256;    // f32 [2][64] exchange between the two token halves
 constexpr int SM_FAC = SM_WMAX + 512;    // f32 [64] rescale factor of the current tile; 1 / l in the epilogue
 constexpr int SM_BARS = SM_FAC + 256;    // mbarriers
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(AM_THREADS, 1)
 attend_mma_kernel(AttendMmaArgs A) {
     extern __shared__ __align__(1024) uint8_t smem[];
     AmBars& bars = *reinterpret_cast<AmBars*>(smem + SM_BARS);
-    float4* s_tok = reinterpret_cast<float4*>(smem + SM_TOK);
+    float* s_tok = reinterpret_cast<float*>(smem + SM_TOK);   // three planes of SM_TOKPLANE bytes
     float* s_ahi = reinterpret_cast<float*>(smem + SM_AHI);
     float* s_wmax = reinterpret_cast<float*>(smem + SM_WMAX);
     float* s_fac = reinterpret_cast<float*>(smem + SM_FAC);
@@ -344,8 +345,10 @@ attend_mma_kernel(AttendMmaArgs A) {
             if (lane < 16) {
                 const float sc = scl[0];
                 const bool live = row[0] != NONE && sc > 0.0f;
-                s_tok[s * AM_TILE + myrow] = live ? make_float4(sc, __log2f(sc) + AM_POFF, __frcp_rn(sc), 0.0f)
-                                                  : make_float4(0.0f, -INFINITY, 0.0f, 0.0f);
+                float* tp = s_tok + s * AM_TILE + myrow;
+                tp[0] = live ? sc : 0.0f;
+                tp[SM_TOKPLANE / 4] = live ? __log2f(sc) + AM_POFF : -INFINITY;
+                tp[2 * (SM_TOKPLANE / 4)] = live ? __frcp_rn(sc) : 0.0f;
             }
             __syncwarp();
             if (lane == 0 && !(A.withhold && j == 0 && g == 0)) tc::mbar_arrive(&bars.k_full[s]);
@@ -441,7 +444,8 @@ attend_mma_kernel(AttendMmaArgs A) {
                  tc::mbar_wait_warp(&bars.s_full[s], use & 1, abort_flag, 62, A.max_polls);
             if (!ok) break;
             tc::tc_fence_after();
-            const float4* ti = s_tok + s * AM_TILE + 32 * th + 16 * tb;   // this thread's 16 tokens
+            // this thread's 16 tokens: four 16-byte loads per plane (the two half-warps read 64 bytes apart: no bank conflict)
+            const float4* ti = reinterpret_cast<const float4*>(s_tok + s * AM_TILE + 32 * th + 16 * tb);
             float s2[16];
             float dmax = -INFINITY;               // max over this thread's tokens of s2' - reference
             {
@@ -452,15 +456,20 @@ attend_mma_kernel(AttendMmaArgs A) {
                 __syncwarp();
                 if (lane == 0) tc::mbar_arrive(&bars.s_empty[s]);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float mine = __uint_as_float(tb ? r[16 + j] : r[j]);
-                    const float give = __uint_as_float(tb ? r[j] : r[16 + j]);
-                    const float raw = mine + __shfl_xor_sync(0xffffffffu, give, 16);
-                    const float4 t = ti[j];
-                    // rows past the end are exact zeros in shared memory, so their raw scores are 0 and an
-                    // additive -inf makes every weight of theirs exactly 0 without a select per element
-                    s2[j] = fmaf(raw, a_h * t.x, t.y);
-                    dmax = fmaxf(dmax, s2[j] - m_ref);   // reference is -inf before the first tile
+                for (int j4 = 0; j4 < 4; ++j4) {
+                    const float4 ts = ti[j4], tc2 = ti[SM_TOKPLANE / 16 + j4];
+                    const float sc4[4] = {ts.x, ts.y, ts.z, ts.w}, c24[4] = {tc2.x, tc2.y, tc2.z, tc2.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = 4 * j4 + e;
+                        const float mine = __uint_as_float(tb ? r[16 + j] : r[j]);
+                        const float give = __uint_as_float(tb ? r[j] : r[16 + j]);
+                        const float raw = mine + __shfl_xor_sync(0xffffffffu, give, 16);
+                        // rows past the end are exact zeros in shared memory, so their raw scores are 0 and an
+                        // additive -inf makes every weight of theirs exactly 0 without a select per element
+                        s2[j] = fmaf(raw, a_h * sc4[e], c24[e]);
+                        dmax = fmaxf(dmax, s2[j] - m_ref);   // reference is -inf before the first tile
+                    }
                 }
             }
 
@@ -516,14 +525,16 @@ attend_mma_kernel(AttendMmaArgs A) {
             uint32_t hi_w[4], lo_w[4];
 #pragma unroll
             for (int j = 0; j < 16; j += 4) {
+                const float4 ti4 = ti[2 * (SM_TOKPLANE / 16) + (j >> 2)];
+                const float inv4[4] = {ti4.x, ti4.y, ti4.z, ti4.w};
                 uint32_t chs[2], cls[2];
 #pragma unroll
                 for (int e = 0; e < 4; e += 2) {
                     float p0, p1;
                     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(s2[j + e] - m_use));
                     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(s2[j + e + 1] - m_use));
-                    l_acc = fmaf(p0, ti[j + e].z, l_acc);
-                    l_acc = fmaf(p1, ti[j + e + 1].z, l_acc);
+                    l_acc = fmaf(p0, inv4[e], l_acc);
+                    l_acc = fmaf(p1, inv4[e + 1], l_acc);
                     const __half2 ph = __floats2half2_rn(p0, p1);
                     const uint32_t phb = *reinterpret_cast<const uint32_t*>(&ph);
                     uint16_t ch, cl;
