@@ -13,19 +13,22 @@
 // s2' = s2 + log2(s_tok), P' = 2^(s2' - m) = weight * s_tok, so P' x (raw V codes) is already
 // the dequantised product and P' is bounded by 2^8 whatever the scales are.
 //
-// What bounds this kernel is how many gathered rows an SM keeps in flight, so the tile is SMALL and the
-// ring is DEEP: 64 tokens per tile, four tiles (4 x 36 KiB) in flight next to the 72 KiB of q. Tokens are the
-// MMA N dimension, which may be 64 while every instruction keeps the full M = 128:
-//   S[128 (hi|lo heads) x 64 tok] = Qcat . K_tile^T                         18 MMAs (K = 32)
+// What bounds this kernel is how many gathered rows an SM keeps in flight, so the tile is SMALL and the ring is
+// DEEP: 64 tokens per tile, SIX tiles (6 x 36 KiB) in flight. The room comes from keeping q out of shared memory: its
+// 512 latent columns live in TENSOR MEMORY as the A operand of the QK MMAs (128 lanes = hi|lo heads, 128 columns of
+// four e4m3 codes), which also spares the shared-memory pipe 64 KiB of operand reads per tile; only the 64 rope
+// columns of q stay in shared memory. Tokens are the MMA N dimension, which may be 64 while every instruction keeps
+// the full M = 128:
+//   S[128 (hi|lo heads) x 64 tok] = Qcat . K_tile^T                         2 (rope, A in smem) + 16 (A in TMEM) MMAs, K = 32
 //   O^T[512 dims x 64 heads]     += V^T (the SAME shared tile, read MN-major) . P'
 //                                   4 blocks x 2 K-steps x {hi, lo} = 16 MMAs (N = 64)
-// TMEM (512 columns): S four deep (4 x 64) + O^T (4 x 64).
+// TMEM (512 columns): S double buffered (2 x 64) + q (128) + O^T (4 x 64).
 //
-// One CTA per (sequence, split), 14 warps: 0-7 softmax + epilogue, 8 QK issue, 9 PV issue, 10-13 gather (the four
-// warps fill the ring tile by tile, 16 rows each, and do not wait for their copies: the copies signal the stage's
-// barrier themselves, so up to four tiles are in flight and land one after the other; a lane locates rows, copies go
-// row by row with 32 lanes on 32 consecutive 16-byte chunks (cp.async into the swizzled tile); the row address chain
-// (token -> page -> pool row -> scale) is software-pipelined three tiles deep).
+// One CTA per (sequence, split), 14 warps: 0-7 softmax + epilogue, 8 QK issue, 9 PV issue, 10-13 gather (warp g
+// fills the tiles g, g + 4, ... in plain program order and does not wait for its copies: the copies signal the
+// stage's barrier themselves, so a warp goes straight on to its next tile as soon as that tile's stage is free; a lane
+// locates two rows, copies go row by row with 32 lanes on 32 consecutive 16-byte chunks (cp.async into the swizzled
+// tile); the row address chain (token -> page -> pool row -> scale) is software-pipelined in register queues).
 // A softmax thread is one TMEM lane = one virtual head, and the q rows are ordered so that the hi and lo terms of a
 // head sit 16 lanes apart in the SAME warp: lanes 0-15 of warp s hold the hi rows of heads 16 s .. 16 s + 15, lanes
 // 16-31 their lo rows. One shuffle per score adds the two terms and leaves each lane with HALF the tokens of its
@@ -33,7 +36,8 @@
 // reference maximum, its running sum and its q scale are registers, and P' leaves as one 16-byte store per term
 // (heads are the rows of the K-major P' operand, tokens its bytes).
 // q arrives as bf16 and is split into its two e4m3 terms by the softmax warps inside the kernel while the
-// first tiles are gathered; the output leaves straight from the accumulator registers (64 contiguous bytes per warp store).
+// first tiles are gathered (a thread converts the row of its own TMEM lane and stores it with tcgen05.st); the output
+// leaves straight from the accumulator registers (64 contiguous bytes per warp store).
 // Online softmax with a LAGGING reference max: as long as no score of a tile exceeds its head's
 // reference by more than 3 (log2) the references stand (one barrier-with-OR per tile, no exchange);
 // otherwise the exact per-head maxima are taken and O is rescaled through TMEM. P' carries 2^5, so
@@ -46,14 +50,16 @@
 namespace {
 
 constexpr int AM_TILE = 64;
-constexpr int AM_STAGES = 4;             // K ring depth (one gather warp and one S buffer per stage)
+constexpr int AM_STAGES = 6;             // K ring depth
 constexpr int AM_ROPES = 3;              // rope tiles: released right after the two rope MMAs of a tile, so fewer than stages
+constexpr int AM_SBUF = 2;               // S accumulators
+constexpr int AM_GW = 4;                 // gather warps
 constexpr int AM_H = 64, AM_KVL = 512, AM_ROPE = 64, AM_W = AM_KVL + AM_ROPE;
 constexpr int AM_SW = 8;                 // softmax + epilogue warps: TMEM lane quarter = warp % 4, token / head half = warp / 4
 constexpr int AM_HPT = 32;               // head columns of O^T a thread owns in the rescale and the epilogue
 constexpr int AM_SOFTMAX_THREADS = AM_SW * 32;
 constexpr int AM_QKW = AM_SW, AM_PVW = AM_SW + 1, AM_GW0 = AM_SW + 2;   // warp roles: QK issue, PV issue, first gather warp
-constexpr int AM_THREADS = (AM_GW0 + AM_STAGES) * 32;
+constexpr int AM_THREADS = (AM_GW0 + AM_GW) * 32;
 constexpr int AM_MAX_SPLITS = 16;
 // P'' = 2^(s2' - m_ref + AM_POFF) with m_ref lagging the true maximum by at most AM_LAG, so
 // P'' <= 2^(AM_POFF + AM_LAG) = 256 < 448 while typical weights (a few binades below the maximum)
@@ -62,16 +68,19 @@ constexpr int AM_MAX_SPLITS = 16;
 // exponent of P'' directly.
 constexpr float AM_POFF = 5.0f, AM_LAG = 3.0f;
 
+// tensor memory map (columns)
+constexpr int TMC_S = 0, TMC_Q = AM_SBUF * AM_TILE, TMC_O = TMC_Q + AM_KVL / 4;
+static_assert(TMC_O + 4 * AM_H == 512, "tensor memory budget");
+
 // shared memory map (bytes); every operand tile is 1024-byte aligned
-constexpr int SM_K0 = 0;                 // 4 stages x (4 latent chunks x [64 rows][128 B]), 128-byte swizzle
+constexpr int SM_K0 = 0;                 // 6 stages x (4 latent chunks x [64 rows][128 B]), 128-byte swizzle
 constexpr int SM_KSTAGE = 32768, SM_KCHUNK = 8192;
 constexpr int SM_ROPE = SM_K0 + AM_STAGES * SM_KSTAGE;       // 3 x [64 rows][64 B], 64-byte swizzle
 constexpr int SM_ROPEBUF = 4096;
-constexpr int SM_QL = SM_ROPE + AM_ROPES * SM_ROPEBUF;       // 4 chunks x [128 virtual heads][128 B]
-constexpr int SM_QR = SM_QL + 65536;     // [128 virtual heads][64 B], 64-byte swizzle
+constexpr int SM_QR = SM_ROPE + AM_ROPES * SM_ROPEBUF;       // rope columns of q: [128 virtual heads][64 B], 64-byte swizzle
 constexpr int SM_P = SM_QR + 8192;       // hi [64 heads][64 tokens], lo the same: K-major, 64-byte swizzle
 constexpr int SM_PTERM = 4096;
-constexpr int SM_TOK = SM_P + 2 * SM_PTERM;   // f32 [3][4 stages][64 tokens]: scale | log2(scale) + AM_POFF | 1 / scale
+constexpr int SM_TOK = SM_P + 2 * SM_PTERM;   // f32 [3][6 stages][64 tokens]: scale | log2(scale) + AM_POFF | 1 / scale
 constexpr int SM_TOKPLANE = AM_STAGES * AM_TILE * 4;
 constexpr int SM_AHI = SM_TOK + 3 * SM_TOKPLANE;   // f32 [64] per-head q scale * softmax scale * log2(e)
 constexpr int SM_WMAX = SM_AHI + 256;    // f32 [2][64] exchange between the two token halves
@@ -81,12 +90,12 @@ constexpr int SM_MISC = SM_BARS + 256;
 constexpr int SM_TOTAL = SM_MISC + 64;
 
 struct AmBars {
-    uint64_t k_full[AM_STAGES], k_empty[AM_STAGES], s_full[AM_STAGES], s_empty[AM_STAGES], rope_free[AM_ROPES],
+    uint64_t k_full[AM_STAGES], k_empty[AM_STAGES], s_full[AM_SBUF], s_empty[AM_SBUF], rope_free[AM_ROPES],
         p_full, pv_done, q_full;
 };
 static_assert(sizeof(AmBars) <= 256, "barrier block");
 static_assert(SM_TOTAL <= 232448, "shared memory budget");
-static_assert(SM_QL % 1024 == 0 && SM_P % 1024 == 0 && SM_ROPE % 1024 == 0, "operand tiles are 1024-byte aligned");
+static_assert(SM_QR % 1024 == 0 && SM_P % 1024 == 0 && SM_ROPE % 1024 == 0, "operand tiles are 1024-byte aligned");
 
 
 struct AttendMmaArgs {
@@ -139,10 +148,9 @@ attend_mma_kernel(AttendMmaArgs A) {
 
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < AM_STAGES; ++s) {
-            tc::mbar_init(&bars.k_full[s], AM_STAGES * 32 + AM_STAGES); tc::mbar_init(&bars.k_empty[s], 1);
-            tc::mbar_init(&bars.s_full[s], 1); tc::mbar_init(&bars.s_empty[s], AM_SW);
-        }
+        for (int s = 0; s < AM_STAGES; ++s) { tc::mbar_init(&bars.k_full[s], 32 + 1); tc::mbar_init(&bars.k_empty[s], 1); }
+#pragma unroll
+        for (int s = 0; s < AM_SBUF; ++s) { tc::mbar_init(&bars.s_full[s], 1); tc::mbar_init(&bars.s_empty[s], AM_SW); }
 #pragma unroll
         for (int s = 0; s < AM_ROPES; ++s) tc::mbar_init(&bars.rope_free[s], 1);
         tc::mbar_init(&bars.p_full, AM_SOFTMAX_THREADS);
@@ -158,85 +166,85 @@ attend_mma_kernel(AttendMmaArgs A) {
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = *tmem_base_s;
-    const uint32_t TM_S0 = tmem, TM_O = tmem + 256;
+    const uint32_t TM_S0 = tmem + TMC_S, TM_Q = tmem + TMC_Q, TM_O = tmem + TMC_O;
 
-    // q -> two e4m3 terms per head, written straight into the swizzled operand tiles (once per CTA):
+    // q -> two e4m3 terms per head (once per CTA):
     //   hi = e4m3(q / s), s = absmax / 448;  lo = e4m3(q / s - hi)   =>  q ~ s * (hi + lo)
     // (the residual of a value of typical size is a normal e4m3 number; below 2^-6 it is kept to 2^-10 absolute,
     // 2^-19 of the head's largest value).
-    // Every softmax warp takes 64 / AM_SW heads; a head's 576 values are 72 chunks of 8 (lane, lane+32, lane+64).
-    // The gather warps do not wait for this: the MMA warp does (q_full) before its first QK.
+    // A thread converts the row of its OWN tensor-memory lane: lane l of warp w is the virtual head
+    // (16 (w % 4) + l % 16, term l / 16), and w / 4 picks the half of the 512 latent columns (the rope columns go with
+    // half 0). Two passes over the row: the absolute maximum, then the codes - 128 at a time into 32 registers and
+    // from there into 32 tensor-memory columns (column c = codes 4c .. 4c + 3, lowest byte first, which is the layout
+    // the MMA expects of an 8-bit A operand); the rope codes go to the shared operand tile.
+    // The gather warps do not wait for this: the QK issuer does (q_full) before its first MMA.
     // Under a programmatic dependent launch the kernel before this one may still be running. Unless the
     // caller vouches that q was complete before that kernel was even launched (q_early: the fused decode
     // step), q may be that kernel's output and is read only after the dependency wait.
     if (!A.q_early) rv_grid_dep_wait();
     if (warp < AM_SW) {
-        const uint16_t* qb = A.q + (size_t)b * AM_H * AM_W;
-        constexpr int HPW = AM_H / AM_SW;          // heads a warp converts (a multiple of 4)
-#pragma unroll 1
-        for (int h4 = 0; h4 < HPW; h4 += 4) {
-            uint4 v[4][3];
+        const int sq = warp & 3, half = warp >> 2, term = lane >> 4;
+        const int h = 16 * sq + (lane & 15);
+        const uint16_t* qrow = A.q + ((size_t)b * AM_H + h) * AM_W;
+        const uint4* qn = reinterpret_cast<const uint4*>(qrow + half * 256);   // 32 chunks of 8 latent values
+        const uint4* qr = reinterpret_cast<const uint4*>(qrow + AM_KVL);        // 8 chunks of 8 rope values (half 0)
+        float amax = 0.0f;
+        auto absmax8 = [&](const uint4 v) {
+            const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint16_t* src = qb + (size_t)(warp * HPW + h4 + u) * AM_W;
+            for (int i = 0; i < 4; ++i)
+                amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(ww[i] << 16)), fabsf(__uint_as_float(ww[i] & 0xffff0000u))));
+        };
+#pragma unroll 8
+        for (int c = 0; c < 32; ++c) absmax8(qn[c]);
+        if (half == 0) {
 #pragma unroll
-                for (int c = 0; c < 3; ++c) {
-                    const int chunk = lane + 32 * c;
-                    v[u][c] = chunk < 72 ? *reinterpret_cast<const uint4*>(src + chunk * 8) : make_uint4(0, 0, 0, 0);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int h = warp * HPW + h4 + u;
-                const int row_hi = q_row(h, 0), row_lo = q_row(h, 1);
-                float f[3][8];
-                float amax = 0.0f;
-#pragma unroll
-                for (int c = 0; c < 3; ++c) {
-                    const uint32_t ww[4] = {v[u][c].x, v[u][c].y, v[u][c].z, v[u][c].w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        f[c][2 * i] = __uint_as_float(ww[i] << 16);
-                        f[c][2 * i + 1] = __uint_as_float(ww[i] & 0xffff0000u);
-                        amax = fmaxf(amax, fmaxf(fabsf(f[c][2 * i]), fabsf(f[c][2 * i + 1])));
-                    }
-                }
-                amax = rv_warp_max(amax);
-                const float sq = amax > 0.0f ? amax / 448.0f : 1.0f;
-                const float inv = 1.0f / sq;
-#pragma unroll
-                for (int c = 0; c < 3; ++c) {
-                    const int chunk = lane + 32 * c;
-                    if (chunk < 72) {
-                        uint32_t hi_w[2], lo_w[2];
-#pragma unroll
-                        for (int i = 0; i < 2; ++i) {
-                            uint32_t hw = 0u, lw = 0u;
-#pragma unroll
-                            for (int e = 0; e < 4; e += 2) {
-                                const float x0 = f[c][4 * i + e] * inv, x1 = f[c][4 * i + e + 1] * inv;
-                                uint16_t ch, cl;
-                                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(ch) : "f"(x1), "f"(x0));
-                                const float2 xh = rv_e4m3x2_to_f32x2(ch);
-                                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(cl) : "f"(x1 - xh.y), "f"(x0 - xh.x));
-                                hw |= (uint32_t)ch << (8 * e);
-                                lw |= (uint32_t)cl << (8 * e);
-                            }
-                            hi_w[i] = hw; lo_w[i] = lw;
-                        }
-                        const int j16 = chunk >> 1, half = (chunk & 1) * 8;
-                        uint8_t* dh = j16 < 32 ? smem + SM_QL + (j16 >> 3) * 16384 + tc::sw128_chunk(row_hi, j16 & 7)
-                                               : smem + SM_QR + sw64_chunk(row_hi, j16 - 32);
-                        uint8_t* dl = j16 < 32 ? smem + SM_QL + (j16 >> 3) * 16384 + tc::sw128_chunk(row_lo, j16 & 7)
-                                               : smem + SM_QR + sw64_chunk(row_lo, j16 - 32);
-                        *reinterpret_cast<uint2*>(dh + half) = make_uint2(hi_w[0], hi_w[1]);
-                        *reinterpret_cast<uint2*>(dl + half) = make_uint2(lo_w[0], lo_w[1]);
-                    }
-                }
-                if (lane == 0) s_ahi[h] = sq * A.softmax_scale * 1.4426950408889634f;
-            }
+            for (int c = 0; c < 8; ++c) absmax8(qr[c]);
         }
+        if (lane < 16) s_wmax[half * 64 + h] = amax;
+        tc::named_barrier(3, AM_SOFTMAX_THREADS);
+        amax = fmaxf(s_wmax[h], s_wmax[64 + h]);
+        const float sc = amax > 0.0f ? amax / 448.0f : 1.0f;
+        const float inv = 1.0f / sc;
+        // 8 values -> 8 codes of this thread's term (two 32-bit words)
+        auto codes8 = [&](const uint4 v, uint32_t& w0, uint32_t& w1) {
+            const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+            uint32_t out[2] = {0u, 0u};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float x0 = __uint_as_float(ww[i] << 16) * inv, x1 = __uint_as_float(ww[i] & 0xffff0000u) * inv;
+                uint16_t c;
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(x1), "f"(x0));
+                if (term) {
+                    const float2 xh = rv_e4m3x2_to_f32x2(c);
+                    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(x1 - xh.y), "f"(x0 - xh.x));
+                }
+                out[i >> 1] |= (uint32_t)c << (16 * (i & 1));
+            }
+            w0 = out[0]; w1 = out[1];
+        };
+        const uint32_t lane_addr = ((uint32_t)(sq * 32)) << 16;
+#pragma unroll 1
+        for (int grp = 0; grp < 2; ++grp) {       // 128 values = 32 columns per store
+            uint32_t r[32];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) codes8(qn[grp * 16 + c], r[2 * c], r[2 * c + 1]);
+            tc::tmem_st32(TM_Q + lane_addr + half * 64 + grp * 32, r);
+        }
+        if (half == 0) {
+            const int rowq = q_row(h, term);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {          // 16 rope values = one 16-byte chunk of the shared operand row
+                uint32_t w[4];
+                codes8(qr[2 * c], w[0], w[1]);
+                codes8(qr[2 * c + 1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(smem + SM_QR + sw64_chunk(rowq, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            if (term == 0) s_ahi[h] = sc * A.softmax_scale * 1.4426950408889634f;
+        }
+        tc::tmem_st_wait();
         tc::fence_proxy_async();
+        tc::tc_fence_before();
         tc::mbar_arrive(&bars.q_full);
         tc::named_barrier(3, AM_SOFTMAX_THREADS);   // the head scales are read by other warps than the ones that wrote them
     }
@@ -263,29 +271,27 @@ attend_mma_kernel(AttendMmaArgs A) {
 
     if (warp >= AM_GW0 && ntiles > 0) {
         // ------------------------------ gather producers ------------------------------------------
-        // The four warps fill the ring TILE BY TILE, each copying 16 rows of every tile, and never wait for a copy to
-        // land: a thread's copies signal the stage's barrier themselves when they are complete
-        // (cp.async.mbarrier.arrive), so a warp goes straight on to the next free stage. Tiles therefore land one after
-        // the other, each with the whole ingest bandwidth of the SM, instead of four at a time at a quarter of it:
-        // the first can be multiplied while the next ones are still in flight.
+        // Warp g fills the tiles g, g + 4, g + 8, ... (ring stage = tile % 6) in plain program order and never waits for
+        // a copy to land: a thread's copies signal the stage's barrier themselves when they are complete
+        // (cp.async.mbarrier.arrive), so the warp goes straight on to its next tile as soon as that tile's stage is
+        // free. A lane resolves the addresses of two rows of its warp's tile.
         const int g = warp - AM_GW0;
-        const int myrow = 16 * g + (lane & 15);            // the tile row whose address this lane resolves (both half-warps alike)
         bool ok = true;
         // The address chain of a row (selected token -> page -> pool row -> scale) is three dependent global loads, and
-        // under load each of them comes back only after the tens of kilobytes of copies queued in front of it: several
-        // tiles later. It therefore runs as a software pipeline AM_LOOK tiles deep PER LEVEL that keeps the raw loaded
+        // under load each of them comes back only after the tens of kilobytes of copies queued in front of it. It
+        // therefore runs as a software pipeline AM_LOOK of the warp's tiles deep PER LEVEL that keeps the raw loaded
         // words in register queues and touches a word only AM_LOOK iterations after it was requested (the warp issues
-        // in order: a use right behind its load would stall every copy after it):
-        //   tk[k]            token of tile j + 2 AM_LOOK + k, being loaded
-        //   tok[k], pg[k]    token of tile j + AM_LOOK + k and its page-table entry, being loaded
-        //   row[k], scl[k]   pool row of tile j + k (NONE: write zeros) and its scale, being loaded; k = 0 is the current tile
+        // in order: a use right behind its load would stall every copy after it). For row u of the lane:
+        //   tk[u][k]               token of the warp's tile i + 2 AM_LOOK + k, being loaded
+        //   tok[u][k], pg[u][k]    token of its tile i + AM_LOOK + k and its page-table entry, being loaded
+        //   row[u][k], scl[u][k]   pool row of its tile i + k (NONE: write zeros) and its scale; k = 0 is the current tile
         constexpr uint32_t NONE = 0xffffffffu;
-        constexpr int AM_LOOK = 3;
+        constexpr int AM_LOOK = 2;
         const uint32_t* rowp = listed ? A.rows + (size_t)b * A.row_stride : nullptr;
         const int32_t* btp = A.block_table + (size_t)b * A.max_pages;
         const int pshift = 31 - __clz(P);                  // page sizes are powers of two (checked by the host entry)
-        auto load_tok = [&](int j) -> uint32_t {
-            const int ri = r_begin + j * AM_TILE + myrow;
+        auto load_tok = [&](int j, int u) -> uint32_t {     // j = tile of the split
+            const int ri = r_begin + j * AM_TILE + u * 32 + lane;
             if (j >= ntiles || ri >= r_end) return NONE;
             return rowp ? rowp[ri] : (uint32_t)ri;
         };
@@ -298,34 +304,41 @@ attend_mma_kernel(AttendMmaArgs A) {
             return (t != NONE && pg >= 0 && pg < A.n_pool_pages) ? (uint32_t)pg * (uint32_t)P + (t & (uint32_t)(P - 1)) : NONE;
         };
         auto load_scl = [&](uint32_t r) -> float { return r != NONE ? A.pscale[r] : 0.0f; };
-        uint32_t tk[AM_LOOK], tok[AM_LOOK], row[AM_LOOK];
-        int32_t pg[AM_LOOK];
-        float scl[AM_LOOK];
-        {   // prologue: all token loads at once, then the page entries, then the scales of the first tiles
+        uint32_t tk[2][AM_LOOK], tok[2][AM_LOOK], row[2][AM_LOOK];
+        int32_t pg[2][AM_LOOK];
+        float scl[2][AM_LOOK];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {   // prologue: all token loads at once, then the page entries, then the scales of the first tiles
             uint32_t t0[AM_LOOK];
             int32_t p0[AM_LOOK];
 #pragma unroll
-            for (int k = 0; k < AM_LOOK; ++k) { t0[k] = load_tok(k); tok[k] = load_tok(AM_LOOK + k); tk[k] = load_tok(2 * AM_LOOK + k); }
+            for (int k = 0; k < AM_LOOK; ++k) {
+                t0[k] = load_tok(g + AM_GW * k, u); tok[u][k] = load_tok(g + AM_GW * (AM_LOOK + k), u);
+                tk[u][k] = load_tok(g + AM_GW * (2 * AM_LOOK + k), u);
+            }
 #pragma unroll
-            for (int k = 0; k < AM_LOOK; ++k) { p0[k] = load_pg(t0[k]); pg[k] = load_pg(tok[k]); }
+            for (int k = 0; k < AM_LOOK; ++k) { p0[k] = load_pg(t0[k]); pg[u][k] = load_pg(tok[u][k]); }
 #pragma unroll
-            for (int k = 0; k < AM_LOOK; ++k) { row[k] = pool_row(t0[k], p0[k]); scl[k] = load_scl(row[k]); }
+            for (int k = 0; k < AM_LOOK; ++k) { row[u][k] = pool_row(t0[k], p0[k]); scl[u][k] = load_scl(row[u][k]); }
         }
-        // Each lane owns the address of a row, but the COPIES are issued row by row with the 32 lanes of
+        // Each lane owns the addresses of two rows, but the COPIES are issued row by row with the 32 lanes of
         // the warp on 32 consecutive 16-byte chunks (the pool row travels by shuffle): one warp
         // instruction then reads 512 contiguous bytes instead of 32 scattered 16-byte pieces. A row past the end
         // (or on an unmapped page) is written as exact zeros by the same instruction with a source size of 0:
         // 0 x (stale NaN code) would poison O.
-        for (int j = 0; j < ntiles && ok; ++j) {
+        for (int j = g; j < ntiles && ok; j += AM_GW) {
             const int s = j % AM_STAGES, use = j / AM_STAGES;
             ok = tc::mbar_wait_warp(&bars.k_empty[s], (use & 1) ^ 1, abort_flag, 41, A.max_polls);
             if (!ok) break;
             uint8_t* kbuf = smem + SM_K0 + s * SM_KSTAGE;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
 #pragma unroll 8
-            for (int it = 0; it < 16; ++it) {          // latent part: row 16 g + it, chunk = lane
-                const uint32_t r = __shfl_sync(0xffffffffu, row[0], it);
-                uint8_t* dst = kbuf + (lane >> 3) * SM_KCHUNK + tc::sw128_chunk(16 * g + it, lane & 7);
-                tc::cp_async16_zfill(tc::smem_u32(dst), A.pool + (r != NONE ? (size_t)r * AM_W + lane * 16 : 0), r != NONE ? 16u : 0u);
+                for (int it = 0; it < 32; ++it) {      // latent part: row 32 u + it, chunk = lane
+                    const uint32_t r = __shfl_sync(0xffffffffu, row[u][0], it);
+                    uint8_t* dst = kbuf + (lane >> 3) * SM_KCHUNK + tc::sw128_chunk(u * 32 + it, lane & 7);
+                    tc::cp_async16_zfill(tc::smem_u32(dst), A.pool + (r != NONE ? (size_t)r * AM_W + lane * 16 : 0), r != NONE ? 16u : 0u);
+                }
             }
             // a rope tile is free as soon as the two rope MMAs of the tile that used it last are done
             const int rb = j % AM_ROPES;
@@ -333,34 +346,41 @@ attend_mma_kernel(AttendMmaArgs A) {
             if (!ok) break;
             uint8_t* rope = smem + SM_ROPE + rb * SM_ROPEBUF;
 #pragma unroll
-            for (int it = 0; it < 2; ++it) {           // rope part: 8 rows per instruction, 4 chunks each
-                const int rl = it * 8 + (lane >> 2);
-                const uint32_t r = __shfl_sync(0xffffffffu, row[0], rl);
-                uint8_t* dst = rope + sw64_chunk(16 * g + rl, lane & 3);
-                tc::cp_async16_zfill(tc::smem_u32(dst), A.pool + (r != NONE ? (size_t)r * AM_W + 512 + (lane & 3) * 16 : 0), r != NONE ? 16u : 0u);
+            for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {       // rope part: 8 rows per instruction, 4 chunks each
+                    const int rl = it * 8 + (lane >> 2);
+                    const uint32_t r = __shfl_sync(0xffffffffu, row[u][0], rl);
+                    uint8_t* dst = rope + sw64_chunk(u * 32 + rl, lane & 3);
+                    tc::cp_async16_zfill(tc::smem_u32(dst), A.pool + (r != NONE ? (size_t)r * AM_W + 512 + (lane & 3) * 16 : 0), r != NONE ? 16u : 0u);
+                }
             }
-            // the stage is full when every thread's copies have landed (128 arrivals by the copies themselves) and every
-            // warp's token scales are written (4 plain arrivals, which also publish those stores)
+            // the stage is full when every lane's copies have landed (32 arrivals by the copies themselves) and the token
+            // scales are written (one plain arrival, which also publishes those stores)
             tc::cp_async_mbar_arrive_noinc(&bars.k_full[s]);
-            if (lane < 16) {
-                const float sc = scl[0];
-                const bool live = row[0] != NONE && sc > 0.0f;
-                float* tp = s_tok + s * AM_TILE + myrow;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const float sc = scl[u][0];
+                const bool live = row[u][0] != NONE && sc > 0.0f;
+                float* tp = s_tok + s * AM_TILE + u * 32 + lane;
                 tp[0] = live ? sc : 0.0f;
                 tp[SM_TOKPLANE / 4] = live ? __log2f(sc) + AM_POFF : -INFINITY;
                 tp[2 * (SM_TOKPLANE / 4)] = live ? __frcp_rn(sc) : 0.0f;
             }
             __syncwarp();
-            if (lane == 0 && !(A.withhold && j == 0 && g == 0)) tc::mbar_arrive(&bars.k_full[s]);
+            if (lane == 0 && !(A.withhold && j == 0)) tc::mbar_arrive(&bars.k_full[s]);
             // advance the chain: every value consumed here was requested AM_LOOK iterations ago
-            {
-                const uint32_t row_new = pool_row(tok[0], pg[0]);
-                const uint32_t tok_new = tk[0];
 #pragma unroll
-                for (int k = 0; k + 1 < AM_LOOK; ++k) { row[k] = row[k + 1]; scl[k] = scl[k + 1]; tok[k] = tok[k + 1]; pg[k] = pg[k + 1]; tk[k] = tk[k + 1]; }
-                row[AM_LOOK - 1] = row_new; scl[AM_LOOK - 1] = load_scl(row_new);
-                tok[AM_LOOK - 1] = tok_new; pg[AM_LOOK - 1] = load_pg(tok_new);
-                tk[AM_LOOK - 1] = load_tok(j + 3 * AM_LOOK);
+            for (int u = 0; u < 2; ++u) {
+                const uint32_t row_new = pool_row(tok[u][0], pg[u][0]);
+                const uint32_t tok_new = tk[u][0];
+#pragma unroll
+                for (int k = 0; k + 1 < AM_LOOK; ++k) {
+                    row[u][k] = row[u][k + 1]; scl[u][k] = scl[u][k + 1]; tok[u][k] = tok[u][k + 1]; pg[u][k] = pg[u][k + 1]; tk[u][k] = tk[u][k + 1];
+                }
+                row[u][AM_LOOK - 1] = row_new; scl[u][AM_LOOK - 1] = load_scl(row_new);
+                tok[u][AM_LOOK - 1] = tok_new; pg[u][AM_LOOK - 1] = load_pg(tok_new);
+                tk[u][AM_LOOK - 1] = load_tok(j + AM_GW * 3 * AM_LOOK, u);
             }
         }
     } else if (warp == AM_QKW) {
@@ -371,29 +391,28 @@ attend_mma_kernel(AttendMmaArgs A) {
         // whichever group arrives first. QK runs ahead of the softmax by up to the four S buffers / ring stages.
         if (lane == 0 && ntiles > 0) {
             const uint32_t id_qk = tc::idesc_e4m3(128, AM_TILE, 0, 0);
-            const uint64_t d_ql = smem_desc(tc::smem_u32(smem + SM_QL), 16, 1024, 2);
             const uint64_t d_qr = smem_desc(tc::smem_u32(smem + SM_QR), 16, 512, 4);
             bool ok = tc::mbar_wait(&bars.q_full, 0, abort_flag, 51, A.max_polls);
             for (int i = 0; i < ntiles && ok; ++i) {   // S(i) = Qcat . K(i)^T
-                const int s = i % AM_STAGES, use = i / AM_STAGES, rb = i % AM_ROPES;
+                const int s = i % AM_STAGES, use = i / AM_STAGES, rb = i % AM_ROPES, sb = i % AM_SBUF, suse = i / AM_SBUF;
                 ok = tc::mbar_wait(&bars.k_full[s], use & 1, abort_flag, 52, A.max_polls) &&
-                     tc::mbar_wait(&bars.s_empty[s], (use & 1) ^ 1, abort_flag, 53, A.max_polls);
+                     tc::mbar_wait(&bars.s_empty[sb], (suse & 1) ^ 1, abort_flag, 53, A.max_polls);
                 if (!ok) break;
                 tc::fence_proxy_async();   // the copies wrote through the generic proxy, the MMAs read through the async one
                 tc::tc_fence_after();
                 const uint64_t d_k = smem_desc(tc::smem_u32(smem + SM_K0 + s * SM_KSTAGE), 16, 1024, 2);
                 const uint64_t d_rope = smem_desc(tc::smem_u32(smem + SM_ROPE + rb * SM_ROPEBUF), 16, 512, 4);
-                const uint32_t d = TM_S0 + s * AM_TILE;
-                // rope columns first: their tile is released as soon as these two are done
+                const uint32_t d = TM_S0 + sb * AM_TILE;
+                // rope columns first (A from shared memory): their tile is released as soon as these two are done
 #pragma unroll
                 for (int k = 0; k < 2; ++k) tc::mma_f8(d, d_qr + (uint64_t)(k * 2), d_rope + (uint64_t)(k * 2), id_qk, k != 0);
                 tc::mma_commit(&bars.rope_free[rb]);
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)   // descriptor address fields count 16-byte units
-                        tc::mma_f8(d, d_ql + (uint64_t)((c * 16384 + k * 32) >> 4), d_k + (uint64_t)((c * SM_KCHUNK + k * 32) >> 4), id_qk, 1);
-                tc::mma_commit(&bars.s_full[s]);
+                    for (int k = 0; k < 4; ++k)   // A from tensor memory: 32 codes = 8 columns per step; descriptor address fields count 16-byte units
+                        tc::mma_f8_ta(d, TM_Q + (uint32_t)(c * 32 + k * 8), d_k + (uint64_t)((c * SM_KCHUNK + k * 32) >> 4), id_qk, 1);
+                tc::mma_commit(&bars.s_full[sb]);
             }
         }
     } else if (warp == AM_PVW) {
@@ -439,9 +458,9 @@ attend_mma_kernel(AttendMmaArgs A) {
         float m_ref = -INFINITY;                           // reference max of head hd (the same in its four threads)
         bool ok = ntiles > 0;
         for (int i = 0; i < ntiles && ok; ++i) {
-            const int s = i % AM_STAGES, use = i / AM_STAGES;
+            const int s = i % AM_STAGES, use = i / AM_STAGES, sb = i % AM_SBUF, suse = i / AM_SBUF;
             ok = tc::mbar_wait_warp(&bars.k_full[s], use & 1, abort_flag, 61, A.max_polls) &&
-                 tc::mbar_wait_warp(&bars.s_full[s], use & 1, abort_flag, 62, A.max_polls);
+                 tc::mbar_wait_warp(&bars.s_full[sb], suse & 1, abort_flag, 62, A.max_polls);
             if (!ok) break;
             tc::tc_fence_after();
             // this thread's 16 tokens: four 16-byte loads per plane (the two half-warps read 64 bytes apart: no bank conflict)
@@ -450,11 +469,11 @@ attend_mma_kernel(AttendMmaArgs A) {
             float dmax = -INFINITY;               // max over this thread's tokens of s2' - reference
             {
                 uint32_t r[32];
-                tc::tmem_ld32(TM_S0 + s * AM_TILE + lane_base + 32 * th, r);
+                tc::tmem_ld32(TM_S0 + sb * AM_TILE + lane_base + 32 * th, r);
                 tc::tmem_ld_wait();
                 tc::tc_fence_before();
                 __syncwarp();
-                if (lane == 0) tc::mbar_arrive(&bars.s_empty[s]);
+                if (lane == 0) tc::mbar_arrive(&bars.s_empty[sb]);
 #pragma unroll
                 for (int j4 = 0; j4 < 4; ++j4) {
                     const float4 ts = ti[j4], tc2 = ti[SM_TOKPLANE / 16 + j4];

@@ -126,6 +126,13 @@ __device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t da, uint64_t db
                  "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the A operand in tensor memory: 128 lanes = rows, a 32-bit column holds four consecutive 8-bit K
+// elements (lowest byte first), so one instruction (K = 32) reads 8 columns from `a_tmem` on.
+__device__ __forceinline__ void mma_f8_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
 // All MMAs issued so far by this thread arrive on `bar` when they have completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
