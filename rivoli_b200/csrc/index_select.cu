@@ -24,6 +24,9 @@
 //      gathered cluster-wide, every band token is ranked against all of them.
 //   5. ascending write-out: counts are exchanged, each CTA compacts its own contiguous token range.
 //
+// A batch that fills the chip by itself runs this kernel as ONE CTA of 1024 threads per sequence (a cluster of one):
+// for that shape the exchanges, the cluster barriers and the list copies are compiled out (SOLO below).
+//
 // If the band does not fit the list (tie-dominated scores: thousands of tokens at the cut) the cluster takes
 // the slow path instead: every band token is re-scored chunk by chunk, the exact keys replace the approximate
 // ones in the registers, and an exact 4 x 8-bit radix selection runs over the whole cluster.
@@ -53,6 +56,7 @@ struct SelXc {                     // per-CTA exchange block; slot q of an array
     uint32_t n_out[SEL_MAX_CLUSTER];
     uint32_t cnt_gt[SEL_MAX_CLUSTER], cnt_eq[SEL_MAX_CLUSTER];
     uint32_t red[2][SEL_MAX_WARPS];
+    uint32_t red3[2][3][SEL_MAX_WARPS];
     uint32_t wcnt[SEL_MAX_WARPS];
     uint32_t list_n;
     uint32_t bstar, n_above;
@@ -85,6 +89,21 @@ __device__ __forceinline__ uint32_t sel_block_min(uint32_t v, SelXc& xc, int& bu
     return ~sel_block_max<NW>(~v, xc, buf);
 }
 
+// min, max and a second max over the block in ONE barrier.
+template <int NW>
+__device__ __forceinline__ void sel_block_minmaxmax(uint32_t& mn, uint32_t& mx, uint32_t& mx2, SelXc& xc, int& buf) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    mn = __reduce_min_sync(0xffffffffu, mn);
+    mx = __reduce_max_sync(0xffffffffu, mx);
+    mx2 = __reduce_max_sync(0xffffffffu, mx2);
+    if (lane == 0) { xc.red3[buf][0][warp] = mn; xc.red3[buf][1][warp] = mx; xc.red3[buf][2][warp] = mx2; }
+    __syncthreads();
+    mn = __reduce_min_sync(0xffffffffu, lane < NW ? xc.red3[buf][0][lane] : 0xffffffffu);
+    mx = __reduce_max_sync(0xffffffffu, lane < NW ? xc.red3[buf][1][lane] : 0u);
+    mx2 = __reduce_max_sync(0xffffffffu, lane < NW ? xc.red3[buf][2][lane] : 0u);
+    buf ^= 1;
+}
+
 // Exclusive prefix of `v` over the block in thread order (one barrier).
 template <int NW>
 __device__ __forceinline__ uint32_t sel_block_excl(uint32_t v, SelXc& xc) {
@@ -107,8 +126,12 @@ template <int EPT, int NT>
 __global__ void __launch_bounds__(NT, (NT == 512 && EPT <= 16) ? 2 : 1)
 index_select_cluster_kernel(SelArgs A) {
     constexpr int NW = NT / 32;
+    // A CTA of 1024 threads is launched only as a cluster of ONE (a batch that fills the chip by itself): every
+    // exchange between CTAs and every cluster barrier falls away at compile time, and with them most of the block
+    // barriers, which is what this latency-bound kernel is made of.
+    constexpr bool SOLO = NT == 1024;
     cg::cluster_group cluster = cg::this_cluster();
-    const int C = (int)cluster.dim_blocks().x, r = (int)cluster.block_rank();
+    const int C = SOLO ? 1 : (int)cluster.dim_blocks().x, r = SOLO ? 0 : (int)cluster.block_rank();
     extern __shared__ __align__(16) uint32_t sel_smem[];
     __shared__ SelXc xc;
     float* qf = reinterpret_cast<float*>(sel_smem);                       // [SEL_HD][32] q codes as f32, [dim][head]
@@ -189,25 +212,28 @@ index_select_cluster_kernel(SelArgs A) {
     for (int i = tid; i < SEL_BINS; i += NT) hist[i] = 0u;
     if (tid == 0) xc.list_n = 0;
     int buf = 0;
+    uint32_t kmin = 0xffffffffu, kmax = 0u;
+    float sk_max = 0.0f;
     {
         uint32_t mn = 0xffffffffu, mx = 0u;
 #pragma unroll
         for (int j = 0; j < EPT; ++j)
             if (j < nvalid) { mn = min(mn, key[j]); mx = max(mx, key[j]); }
-        mn = sel_block_min<NW>(mn, xc, buf);
-        mx = sel_block_max<NW>(mx, xc, buf);
-        const uint32_t sm = sel_block_max<NW>(__float_as_uint(skm), xc, buf);     // scales are >= 0: bit order = value order
-        if (tid == 0) { xc.kmin[r] = mn; xc.kmax[r] = mx; xc.skmax[r] = sm; }
-    }
-    // [1] The first exchange is a PULL: a CTA may touch another CTA's shared memory only once that CTA is known
-    // to be running, which its arrival at this barrier proves. Every later exchange pushes.
-    cluster.sync();
-    uint32_t kmin = 0xffffffffu, kmax = 0u;
-    float sk_max = 0.0f;
-    for (int q = 0; q < C; ++q) {
-        const SelXc* src = cluster.map_shared_rank(&xc, q);
-        kmin = min(kmin, src->kmin[q]); kmax = max(kmax, src->kmax[q]);
-        sk_max = fmaxf(sk_max, __uint_as_float(src->skmax[q]));
+        uint32_t sm = __float_as_uint(skm);                                      // scales are >= 0: bit order = value order
+        sel_block_minmaxmax<NW>(mn, mx, sm, xc, buf);                            // (also orders the zeroing above before the histogram)
+        if constexpr (SOLO) {
+            kmin = mn; kmax = mx; sk_max = __uint_as_float(sm);
+        } else {
+            if (tid == 0) { xc.kmin[r] = mn; xc.kmax[r] = mx; xc.skmax[r] = sm; }
+            // [1] The first exchange is a PULL: a CTA may touch another CTA's shared memory only once that CTA is known
+            // to be running, which its arrival at this barrier proves. Every later exchange pushes.
+            cluster.sync();
+            for (int q = 0; q < C; ++q) {
+                const SelXc* src = cluster.map_shared_rank(&xc, q);
+                kmin = min(kmin, src->kmin[q]); kmax = max(kmax, src->kmax[q]);
+                sk_max = fmaxf(sk_max, __uint_as_float(src->skmax[q]));
+            }
+        }
     }
     const float eps = sk_max * A.cb[b];
 
@@ -237,44 +263,51 @@ index_select_cluster_kernel(SelArgs A) {
         if (run) atomicAdd(&hist[cur], run);
     }
     __syncthreads();
-    cluster.sync();                                                           // [2] every CTA's histogram is complete
-    const int SL = SEL_BINS / C;                                              // rank r reduces bins [r * SL, (r + 1) * SL)
-    {
-        uint32_t tot = 0u;
-        for (int i = tid; i < SL; i += NT) {
-            uint32_t v = 0u;
-            for (int q = 0; q < C; ++q) v += cluster.map_shared_rank(hist, q)[r * SL + i];
-            red_hist[i] = v;
-            tot += v;
-        }
-        tot = sel_block_sum<NW>(tot, xc, buf);
-        if (tid < C) cluster.map_shared_rank(&xc, tid)->slice_tot[r] = tot;
-    }
-    __syncthreads();
-    cluster.sync();                                                           // [3] reduced slices and their totals
+    int SL = SEL_BINS;                                                        // bins of the slice that holds the k-th value
     int s_star = 0;
     uint32_t above = 0u;                                                      // tokens in slices above the k-th value's
-    for (int q = C - 1; q >= 0; --q) {
-        if (above + xc.slice_tot[q] >= (uint32_t)kk) { s_star = q; break; }
-        above += xc.slice_tot[q];
+    uint32_t slice_total = (uint32_t)nt;                                      // tokens in that slice
+    const uint32_t* slice_c = hist;
+    if constexpr (!SOLO) {
+        cluster.sync();                                                       // [2] every CTA's histogram is complete
+        SL = SEL_BINS / C;                                                    // rank r reduces bins [r * SL, (r + 1) * SL)
+        {
+            uint32_t tot = 0u;
+            for (int i = tid; i < SL; i += NT) {
+                uint32_t v = 0u;
+                for (int q = 0; q < C; ++q) v += cluster.map_shared_rank(hist, q)[r * SL + i];
+                red_hist[i] = v;
+                tot += v;
+            }
+            tot = sel_block_sum<NW>(tot, xc, buf);
+            if (tid < C) cluster.map_shared_rank(&xc, tid)->slice_tot[r] = tot;
+        }
+        __syncthreads();
+        cluster.sync();                                                       // [3] reduced slices and their totals
+        for (int q = C - 1; q >= 0; --q) {
+            if (above + xc.slice_tot[q] >= (uint32_t)kk) { s_star = q; break; }
+            above += xc.slice_tot[q];
+        }
+        {
+            const uint32_t* src = cluster.map_shared_rank(red_hist, s_star);
+            for (int i = tid; i < SL; i += NT) slice[i] = src[i];
+        }
+        __syncthreads();
+        slice_total = xc.slice_tot[s_star];
+        slice_c = slice;
     }
-    {
-        const uint32_t* src = cluster.map_shared_rank(red_hist, s_star);
-        for (int i = tid; i < SL; i += NT) slice[i] = src[i];
-    }
-    __syncthreads();
     {
         // suffix scan over the slice: thread t owns bins [t * per, (t + 1) * per), per = ceil(SL / 512)
         const int per = (SL + NT - 1) / NT;
         uint32_t mine = 0u;
-        for (int j = 0; j < per; ++j) { const int i = tid * per + j; if (i < SL) mine += slice[i]; }
+        for (int j = 0; j < per; ++j) { const int i = tid * per + j; if (i < SL) mine += slice_c[i]; }
         const uint32_t before = sel_block_excl<NW>(mine, xc);                     // bins below this thread's
-        const uint32_t total = xc.slice_tot[s_star];
+        const uint32_t total = slice_total;
         uint32_t acc = above + (total - before - mine);                       // tokens in bins above this thread's
         for (int j = per - 1; j >= 0; --j) {
             const int i = tid * per + j;
             if (i < SL) {
-                const uint32_t h = slice[i];
+                const uint32_t h = slice_c[i];
                 if (acc < (uint32_t)kk && (uint32_t)kk <= acc + h) { xc.bstar = (uint32_t)(s_star * SL + i); xc.n_above = acc; }
                 acc += h;
             }
@@ -292,15 +325,17 @@ index_select_cluster_kernel(SelArgs A) {
 #pragma unroll
         for (int j = 0; j < EPT; ++j)
             if (j < nvalid && bin_of(key[j]) == bstar) { mn = min(mn, key[j]); mx = max(mx, key[j]); }
-        mn = sel_block_min<NW>(mn, xc, buf);
-        mx = sel_block_max<NW>(mx, xc, buf);
-        if (tid < C) {
-            SelXc* dst = cluster.map_shared_rank(&xc, tid);
-            dst->bmin[r] = mn; dst->bmax[r] = mx;
+        uint32_t unused = 0u;
+        sel_block_minmaxmax<NW>(mn, mx, unused, xc, buf);
+        if constexpr (!SOLO) {
+            if (tid < C) {
+                SelXc* dst = cluster.map_shared_rank(&xc, tid);
+                dst->bmin[r] = mn; dst->bmax[r] = mx;
+            }
+            cluster.sync();                                                   // [3b]
+            mn = 0xffffffffu; mx = 0u;
+            for (int q = 0; q < C; ++q) { mn = min(mn, xc.bmin[q]); mx = max(mx, xc.bmax[q]); }
         }
-        cluster.sync();                                                       // [3b]
-        mn = 0xffffffffu; mx = 0u;
-        for (int q = 0; q < C; ++q) { mn = min(mn, xc.bmin[q]); mx = max(mx, xc.bmax[q]); }
         const float lo_f = topk_unkey(mn) - 2.0f * eps, hi_f = topk_unkey(mx) + 2.0f * eps;
         k_lo = lo_f == lo_f ? topk_key(lo_f) : 0u;
         k_hi = hi_f == hi_f ? topk_key(hi_f) : 0xffffffffu;
@@ -313,7 +348,10 @@ index_select_cluster_kernel(SelArgs A) {
             else if (key[j] >= k_lo) m_band |= 1u << j;
         }
     }
-    const uint32_t n_in_mine = sel_block_sum<NW>((uint32_t)__popc(m_in), xc, buf);
+    {   // this CTA's count of surely selected tokens: the warp sums meet at the barrier that closes the list
+        const uint32_t v = __reduce_add_sync(0xffffffffu, (uint32_t)__popc(m_in));
+        if (lane == 0) xc.red[buf][warp] = v;
+    }
     uint32_t my_pos;                                                          // list position of this thread's first band token
     {
         const uint32_t cnt = (uint32_t)__popc(m_band);
@@ -333,16 +371,18 @@ index_select_cluster_kernel(SelArgs A) {
             if (m_band & (1u << j)) { if (pos < SEL_LIST) l_tok[pos] = (uint32_t)(i0 + j); ++pos; }
     }
     __syncthreads();
+    const uint32_t n_in_mine = __reduce_add_sync(0xffffffffu, lane < NW ? xc.red[buf][lane] : 0u);
+    buf ^= 1;
     const uint32_t n_band_mine = xc.list_n;
-    if (tid < C) {
-        SelXc* dst = cluster.map_shared_rank(&xc, tid);
-        dst->n_in[r] = n_in_mine; dst->n_band[r] = n_band_mine;
-    }
-    cluster.sync();                                                           // [4] (also: nobody reads red_hist any more)
-    uint32_t n_in = 0u, n_band = 0u, band_off = 0u;
-    for (int q = 0; q < C; ++q) {
-        if (q < r) band_off += xc.n_band[q];
-        n_in += xc.n_in[q]; n_band += xc.n_band[q];
+    uint32_t n_in = n_in_mine, n_band = n_band_mine;
+    if constexpr (!SOLO) {
+        if (tid < C) {
+            SelXc* dst = cluster.map_shared_rank(&xc, tid);
+            dst->n_in[r] = n_in_mine; dst->n_band[r] = n_band_mine;
+        }
+        cluster.sync();                                                       // [4] (also: nobody reads red_hist any more)
+        n_in = 0u; n_band = 0u;
+        for (int q = 0; q < C; ++q) { n_in += xc.n_in[q]; n_band += xc.n_band[q]; }
     }
 
     // this lane's head constants for the exact re-score (nh <= 32)
@@ -368,8 +408,10 @@ index_select_cluster_kernel(SelArgs A) {
         // ---- 4. common case: the whole band fits the list --------------------------------------------------
         rescore(n_band_mine);
         __syncthreads();
-        cluster.sync();                                                       // [5] every CTA's exact band keys
-        {
+        const uint32_t* all_tok = l_tok;                                      // the cluster's band: a lone CTA's own lists
+        const uint32_t* all_key = l_key;
+        if constexpr (!SOLO) {
+            cluster.sync();                                                   // [5] every CTA's exact band keys
             uint32_t off = 0u;
             for (int q = 0; q < C; ++q) {
                 const uint32_t nq = xc.n_band[q];
@@ -378,8 +420,9 @@ index_select_cluster_kernel(SelArgs A) {
                 for (uint32_t i = tid; i < nq; i += NT) { a_tok[off + i] = st[i]; a_key[off + i] = sk2[i]; }
                 off += nq;
             }
+            __syncthreads();
+            all_tok = a_tok; all_key = a_key;
         }
-        __syncthreads();
         // rank each of this CTA's band tokens among ALL band tokens by (exact key descending, index ascending)
         uint32_t* dec = hist;
         const uint32_t take = (uint32_t)kk - n_in;   // >= 1: fewer than kk tokens lie above the band
@@ -387,8 +430,8 @@ index_select_cluster_kernel(SelArgs A) {
             const uint32_t kq = l_key[q2], tq = l_tok[q2];
             uint32_t c = 0;
             for (uint32_t j2 = lane; j2 < n_band; j2 += 32) {
-                const uint32_t kj = a_key[j2];
-                c += (kj > kq || (kj == kq && a_tok[j2] < tq)) ? 1u : 0u;
+                const uint32_t kj = all_key[j2];
+                c += (kj > kq || (kj == kq && all_tok[j2] < tq)) ? 1u : 0u;
             }
             c = __reduce_add_sync(0xffffffffu, c);
             if (lane == 0) dec[q2] = c < take ? 1u : 0u;
@@ -401,11 +444,13 @@ index_select_cluster_kernel(SelArgs A) {
             for (int j = 0; j < EPT; ++j)
                 if (m_band & (1u << j)) { if (dec[pos]) sel |= 1u << j; ++pos; }
         }
-        const uint32_t n_out_mine = sel_block_sum<NW>((uint32_t)__popc(sel), xc, buf);
-        if (tid < C) cluster.map_shared_rank(&xc, tid)->n_out[r] = n_out_mine;
-        cluster.sync();                                                       // [6] counts; nobody reads our lists any more
         uint32_t base = 0u;
-        for (int q = 0; q < r; ++q) base += xc.n_out[q];
+        if constexpr (!SOLO) {
+            const uint32_t n_out_mine = sel_block_sum<NW>((uint32_t)__popc(sel), xc, buf);
+            if (tid < C) cluster.map_shared_rank(&xc, tid)->n_out[r] = n_out_mine;
+            cluster.sync();                                                   // [6] counts; nobody reads our lists any more
+            for (int q = 0; q < r; ++q) base += xc.n_out[q];
+        }
         write_out(sel, base);
         if (r == 0 && tid == 0 && A.stats) { A.stats[b * 2] = n_band; A.stats[b * 2 + 1] = n_in; }
         return;
