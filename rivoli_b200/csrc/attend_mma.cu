@@ -43,9 +43,13 @@
 // otherwise the exact per-head maxima are taken and O is rescaled through TMEM. P' carries 2^5, so
 // it stays <= 256 < 448 and typical weights keep both e4m3 terms in the normal range.
 // All waits are bounded (tc_common.cuh).
+#include <cooperative_groups.h>
+
 #include "codec.cuh"
 #include "common.cuh"
 #include "tc_common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -60,7 +64,7 @@ constexpr int AM_HPT = 32;               // head columns of O^T a thread owns in
 constexpr int AM_SOFTMAX_THREADS = AM_SW * 32;
 constexpr int AM_QKW = AM_SW, AM_PVW = AM_SW + 1, AM_GW0 = AM_SW + 2;   // warp roles: QK issue, PV issue, first gather warp
 constexpr int AM_THREADS = (AM_GW0 + AM_GW) * 32;
-constexpr int AM_MAX_SPLITS = 16;
+constexpr int AM_MAX_SPLITS = 8;     // CTAs per sequence = thread-block cluster size
 // P'' = 2^(s2' - m_ref + AM_POFF) with m_ref lagging the true maximum by at most AM_LAG, so
 // P'' <= 2^(AM_POFF + AM_LAG) = 256 < 448 while typical weights (a few binades below the maximum)
 // land where BOTH e4m3 terms are normal numbers. In the code s2 carries the offset (s2 = s2' + AM_POFF)
@@ -87,7 +91,10 @@ constexpr int SM_WMAX = SM_AHI + 256;    // f32 [2][64] exchange between the two
 constexpr int SM_FAC = SM_WMAX + 512;    // f32 [64] rescale factor of the current tile; 1 / l in the epilogue
 constexpr int SM_BARS = SM_FAC + 256;    // mbarriers
 constexpr int SM_MISC = SM_BARS + 256;
-constexpr int SM_TOTAL = SM_MISC + 64;
+constexpr int SM_XS = SM_MISC + 64;      // f32 [2][64]: this CTA's reference maximum and weight sum per head, read by its cluster
+constexpr int SM_TOTAL = SM_XS + 512;
+constexpr int SM_STAGE = SM_K0;          // f32 [64 heads][512 dims]: this CTA's scaled O, read by its cluster (the ring is idle by then)
+static_assert(AM_H * AM_KVL * 4 <= AM_STAGES * SM_KSTAGE, "the O staging fits the ring");
 
 struct AmBars {
     uint64_t k_full[AM_STAGES], k_empty[AM_STAGES], s_full[AM_SBUF], s_empty[AM_SBUF], rope_free[AM_ROPES],
@@ -104,7 +111,7 @@ struct AttendMmaArgs {
     const uint8_t* pool; const float* pscale; const int32_t* block_table;
     const uint32_t* rows; long long row_stride; const int32_t* n_rows;
     int page_tokens, max_pages, n_pool_pages, n_splits;
-    uint16_t* out; float* out_m; float* out_lse; float* partial;
+    uint16_t* out; float* out_m; float* out_lse;
     int* err;
     int min_rows;      // sequences with 0 < n_rows < min_rows are served by the CUDA-core kernel of the same call
     int q_early;       // 1: q was complete before the preceding kernel was launched, so it may be read before the grid-dependency wait
@@ -172,11 +179,14 @@ attend_mma_kernel(AttendMmaArgs A) {
     //   hi = e4m3(q / s), s = absmax / 448;  lo = e4m3(q / s - hi)   =>  q ~ s * (hi + lo)
     // (the residual of a value of typical size is a normal e4m3 number; below 2^-6 it is kept to 2^-10 absolute,
     // 2^-19 of the head's largest value).
-    // A thread converts the row of its OWN tensor-memory lane: lane l of warp w is the virtual head
+    // A thread fills the row of its OWN tensor-memory lane: lane l of warp w is the virtual head
     // (16 (w % 4) + l % 16, term l / 16), and w / 4 picks the half of the 512 latent columns (the rope columns go with
-    // half 0). Two passes over the row: the absolute maximum, then the codes - 128 at a time into 32 registers and
-    // from there into 32 tensor-memory columns (column c = codes 4c .. 4c + 3, lowest byte first, which is the layout
-    // the MMA expects of an 8-bit A operand); the rope codes go to the shared operand tile.
+    // half 0). The two lanes of a head (16 apart) share the work: the hi lane reads the even 8-value chunks of the
+    // half-row and the lo lane the odd ones, each derives BOTH terms of its chunks and hands the other lane the codes
+    // that belong in that lane's row (one shuffle per word). Two passes over the chunks: the absolute maximum, then
+    // the codes - 64 values of the row at a time into 16 registers and from there into 16 tensor-memory columns
+    // (column c = codes 4c .. 4c + 3, lowest byte first, which is the layout the MMA expects of an 8-bit A
+    // operand); the rope codes go to the shared operand tile.
     // The gather warps do not wait for this: the QK issuer does (q_full) before its first MMA.
     // Under a programmatic dependent launch the kernel before this one may still be running. Unless the
     // caller vouches that q was complete before that kernel was even launched (q_early: the fused decode
@@ -186,8 +196,8 @@ attend_mma_kernel(AttendMmaArgs A) {
         const int sq = warp & 3, half = warp >> 2, term = lane >> 4;
         const int h = 16 * sq + (lane & 15);
         const uint16_t* qrow = A.q + ((size_t)b * AM_H + h) * AM_W;
-        const uint4* qn = reinterpret_cast<const uint4*>(qrow + half * 256);   // 32 chunks of 8 latent values
-        const uint4* qr = reinterpret_cast<const uint4*>(qrow + AM_KVL);        // 8 chunks of 8 rope values (half 0)
+        const uint4* qn = reinterpret_cast<const uint4*>(qrow + half * 256) + term;   // this lane's chunks: qn[2 m], m = 0..15
+        const uint4* qr = reinterpret_cast<const uint4*>(qrow + AM_KVL) + term;        // rope (half 0): qr[2 m], m = 0..3
         float amax = 0.0f;
         auto absmax8 = [&](const uint4 v) {
             const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
@@ -195,50 +205,68 @@ attend_mma_kernel(AttendMmaArgs A) {
             for (int i = 0; i < 4; ++i)
                 amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(ww[i] << 16)), fabsf(__uint_as_float(ww[i] & 0xffff0000u))));
         };
-#pragma unroll 8
-        for (int c = 0; c < 32; ++c) absmax8(qn[c]);
+        {
+            uint4 v[16];
+#pragma unroll
+            for (int m = 0; m < 16; ++m) v[m] = qn[2 * m];
+#pragma unroll
+            for (int m = 0; m < 16; ++m) absmax8(v[m]);
+        }
         if (half == 0) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) absmax8(qr[c]);
+            for (int m = 0; m < 4; ++m) absmax8(qr[2 * m]);
         }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
         if (lane < 16) s_wmax[half * 64 + h] = amax;
         tc::named_barrier(3, AM_SOFTMAX_THREADS);
         amax = fmaxf(s_wmax[h], s_wmax[64 + h]);
         const float sc = amax > 0.0f ? amax / 448.0f : 1.0f;
         const float inv = 1.0f / sc;
-        // 8 values -> 8 codes of this thread's term (two 32-bit words)
-        auto codes8 = [&](const uint4 v, uint32_t& w0, uint32_t& w1) {
+        // 8 values -> their 8 hi codes and 8 lo codes (two 32-bit words each)
+        auto codes8 = [&](const uint4 v, uint32_t* hi, uint32_t* lo) {
             const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
-            uint32_t out[2] = {0u, 0u};
+            hi[0] = hi[1] = lo[0] = lo[1] = 0u;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float x0 = __uint_as_float(ww[i] << 16) * inv, x1 = __uint_as_float(ww[i] & 0xffff0000u) * inv;
-                uint16_t c;
-                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(x1), "f"(x0));
-                if (term) {
-                    const float2 xh = rv_e4m3x2_to_f32x2(c);
-                    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c) : "f"(x1 - xh.y), "f"(x0 - xh.x));
-                }
-                out[i >> 1] |= (uint32_t)c << (16 * (i & 1));
+                uint16_t ch, cl;
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(ch) : "f"(x1), "f"(x0));
+                const float2 xh = rv_e4m3x2_to_f32x2(ch);
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(cl) : "f"(x1 - xh.y), "f"(x0 - xh.x));
+                hi[i >> 1] |= (uint32_t)ch << (16 * (i & 1));
+                lo[i >> 1] |= (uint32_t)cl << (16 * (i & 1));
             }
-            w0 = out[0]; w1 = out[1];
         };
         const uint32_t lane_addr = ((uint32_t)(sq * 32)) << 16;
 #pragma unroll 1
-        for (int grp = 0; grp < 2; ++grp) {       // 128 values = 32 columns per store
-            uint32_t r[32];
+        for (int grp = 0; grp < 4; ++grp) {       // 8 chunks of the half-row = 64 values = 16 columns per store
+            uint4 v[4];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) codes8(qn[grp * 16 + c], r[2 * c], r[2 * c + 1]);
-            tc::tmem_st32(TM_Q + lane_addr + half * 64 + grp * 32, r);
+            for (int m = 0; m < 4; ++m) v[m] = qn[2 * (grp * 4 + m)];
+            uint32_t r[16];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                uint32_t hi[2], lo[2];
+                codes8(v[m], hi, lo);
+                // this lane's own chunk is 2 m + term of the group; the partner made the codes of chunk 2 m + (1 - term)
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const uint32_t own = term ? lo[w] : hi[w];
+                    const uint32_t got = __shfl_xor_sync(0xffffffffu, term ? hi[w] : lo[w], 16);
+                    r[4 * m + w] = term ? got : own;          // even chunk: made by the hi lane
+                    r[4 * m + 2 + w] = term ? own : got;      // odd chunk: made by the lo lane
+                }
+            }
+            tc::tmem_st16(TM_Q + lane_addr + half * 64 + grp * 16, r);
         }
         if (half == 0) {
-            const int rowq = q_row(h, term);
+            const int row_hi = q_row(h, 0), row_lo = q_row(h, 1);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {          // 16 rope values = one 16-byte chunk of the shared operand row
-                uint32_t w[4];
-                codes8(qr[2 * c], w[0], w[1]);
-                codes8(qr[2 * c + 1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(smem + SM_QR + sw64_chunk(rowq, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int m = 0; m < 4; ++m) {          // rope chunk 2 m + term: 8 bytes of the 16-byte chunk m of both rows
+                uint32_t hi[2], lo[2];
+                codes8(qr[2 * m], hi, lo);
+                *reinterpret_cast<uint2*>(smem + SM_QR + sw64_chunk(row_hi, m) + 8 * term) = make_uint2(hi[0], hi[1]);
+                *reinterpret_cast<uint2*>(smem + SM_QR + sw64_chunk(row_lo, m) + 8 * term) = make_uint2(lo[0], lo[1]);
             }
             if (term == 0) s_ahi[h] = sc * A.softmax_scale * 1.4426950408889634f;
         }
@@ -263,6 +291,7 @@ attend_mma_kernel(AttendMmaArgs A) {
     const bool skip = nr > 0 && nr < A.min_rows;
     if (skip) nr = 0;
     const int ntiles_all = (nr + AM_TILE - 1) / AM_TILE;
+    const bool clustered = A.n_splits > 1;   // the CTAs of a sequence form one thread-block cluster and merge through its shared memory
     const int tps = (ntiles_all + A.n_splits - 1) / A.n_splits;
     const int r_begin = split * tps * AM_TILE;
     const int r_end = min(nr, r_begin + tps * AM_TILE);
@@ -594,13 +623,12 @@ attend_mma_kernel(AttendMmaArgs A) {
             const int h = hd;
             const float l = s_wmax[h] + s_wmax[64 + h];
             const float m_nat = (m_ref - AM_POFF) * 0.6931471805599453f;   // natural-log units (l and O carry 2^AM_POFF)
-            if (skip) {
+            if (clustered) {
+                float* xs = reinterpret_cast<float*>(smem + SM_XS);
+                xs[h] = (l > 0.0f && ok) ? m_ref : -INFINITY;
+                xs[64 + h] = (l > 0.0f && ok) ? l : 0.0f;
+            } else if (skip) {
                 // nothing: the sequence's output and statistics are written by the CUDA-core kernel
-            } else if (A.n_splits > 1) {
-                float* ml = A.partial + (size_t)b * A.n_splits * AM_H * (AM_KVL + 2) +
-                            (size_t)A.n_splits * AM_H * AM_KVL + ((size_t)split * AM_H + h) * 2;
-                ml[0] = (l > 0.0f && ok) ? m_nat : -INFINITY;
-                ml[1] = (l > 0.0f && ok) ? l : 0.0f;
             } else {
                 if (A.out_m) A.out_m[(size_t)b * AM_H + h] = l > 0.0f ? m_nat : -INFINITY;
                 if (A.out_lse) A.out_lse[(size_t)b * AM_H + h] = l > 0.0f ? m_nat + logf(l) : -INFINITY;
@@ -610,18 +638,16 @@ attend_mma_kernel(AttendMmaArgs A) {
         tc::named_barrier(1, AM_SOFTMAX_THREADS);
         // O^T: this thread's TMEM lane is one latent dim of each 128-dim block; its head columns. For a given head
         // the 32 lanes of a warp hold 32 consecutive dims, so a warp's store covers 64 contiguous bytes of the bf16
-        // output row (two full sectors) and the output goes to global memory straight from the registers; splits
-        // write their f32 partials the same way (128 contiguous bytes per warp store).
+        // output row (two full sectors) and the output goes to global memory straight from the registers (a split
+        // sequence is merged inside its cluster instead, below).
         float inv_l[AM_HPT];   // 1 / l of this thread's heads (registers: the stores below must not wait on loads)
 #pragma unroll
         for (int h = 0; h < AM_HPT; h += 4) {
             const float4 m4 = *reinterpret_cast<const float4*>(s_fac + h0 + h);
             inv_l[h] = m4.x; inv_l[h + 1] = m4.y; inv_l[h + 2] = m4.z; inv_l[h + 3] = m4.w;
         }
-        float* part = A.n_splits > 1 ? A.partial + (size_t)b * A.n_splits * AM_H * (AM_KVL + 2) +
-                                           ((size_t)split * AM_H + h0) * AM_KVL : nullptr;
 #pragma unroll 1
-        for (int c = 0; c < 4 && !skip; ++c) {
+        for (int c = 0; c < 4 && !skip && !clustered; ++c) {
             const int dim = c * 128 + row;
             uint32_t r[AM_HPT];
             if (ntiles > 0 && ok) {
@@ -631,15 +657,82 @@ attend_mma_kernel(AttendMmaArgs A) {
 #pragma unroll
                 for (int h = 0; h < AM_HPT; ++h) r[h] = 0u;
             }
-            if (part) {
+            uint16_t* gp = A.out + ((size_t)b * AM_H + h0) * AM_KVL + dim;
 #pragma unroll
-                for (int hq = 0; hq < AM_HPT; ++hq) part[hq * AM_KVL + dim] = __uint_as_float(r[hq]);
-            } else {
-                uint16_t* gp = A.out + ((size_t)b * AM_H + h0) * AM_KVL + dim;
+            for (int hq = 0; hq < AM_HPT; ++hq) gp[hq * AM_KVL] = rv_f32_to_bf16(__uint_as_float(r[hq]) * inv_l[hq]);
+        }
+    }
+
+    if (clustered) {
+        // ---- merge of a sequence's splits inside its thread-block cluster ----
+        // Every CTA has published its reference maximum and weight sum per head; each scales its own O^T to the
+        // common reference and the total sum and lays it out as f32 [head][dim] in its (now idle) ring; then CTA r adds up
+        // the heads [64 r / n, 64 (r + 1) / n) over all CTAs through distributed shared memory (plain loads of mapped
+        // addresses) and writes them. All threads of all CTAs take part in the three cluster barriers, whatever a
+        // bounded wait did before: a CTA that gave up publishes weight sums of zero.
+        cg::cluster_group cluster = cg::this_cluster();
+        const int n = A.n_splits;
+        float* xs = reinterpret_cast<float*>(smem + SM_XS);
+        float* stage = reinterpret_cast<float*>(smem + SM_STAGE);
+        __syncthreads();
+        const bool live = ntiles > 0 && *abort_flag == 0;
+        cluster.sync();                                                       // [1] every CTA's (m, l)
+        if (warp < AM_SW) {
+            const int sq = warp & 3, th = warp >> 2;
+            const uint32_t lane_base = ((uint32_t)(sq * 32)) << 16;
+            const int h0 = th * AM_HPT;
+            if (tid < AM_H) {
+                const int h = tid;
+                float mg = -INFINITY;
+                for (int q = 0; q < n; ++q) mg = fmaxf(mg, cluster.map_shared_rank(xs, q)[h]);
+                float L = 0.0f;
+                for (int q = 0; q < n; ++q) {
+                    const float* px = cluster.map_shared_rank(xs, q);
+                    const float lq = px[64 + h];
+                    if (lq > 0.0f) L += lq * exp2f(px[h] - mg);
+                }
+                const float lm = xs[64 + h];
+                s_fac[h] = (L > 0.0f && lm > 0.0f) ? exp2f(xs[h] - mg) / L : 0.0f;
+                if (split == 0 && !skip) {
+                    const float m_nat = (mg - AM_POFF) * 0.6931471805599453f;
+                    if (A.out_m) A.out_m[(size_t)b * AM_H + h] = L > 0.0f ? m_nat : -INFINITY;
+                    if (A.out_lse) A.out_lse[(size_t)b * AM_H + h] = L > 0.0f ? m_nat + logf(L) : -INFINITY;
+                }
+            }
+            tc::named_barrier(1, AM_SOFTMAX_THREADS);
+            tc::tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                const int dim = c * 128 + sq * 32 + lane;
+                uint32_t r[AM_HPT];
+                if (live) {
+                    tc::tmem_ld32(TM_O + lane_base + c * 64 + h0, r);
+                    tc::tmem_ld_wait();
+                } else {
 #pragma unroll
-                for (int hq = 0; hq < AM_HPT; ++hq) gp[hq * AM_KVL] = rv_f32_to_bf16(__uint_as_float(r[hq]) * inv_l[hq]);
+                    for (int h = 0; h < AM_HPT; ++h) r[h] = 0u;
+                }
+#pragma unroll
+                for (int hq = 0; hq < AM_HPT; ++hq)   // lanes = consecutive dims: conflict-free stores
+                    stage[(h0 + hq) * AM_KVL + dim] = live ? __uint_as_float(r[hq]) * s_fac[h0 + hq] : 0.0f;
             }
         }
+        cluster.sync();                                                       // [2] every CTA's scaled O
+        if (warp < AM_SW && !skip) {
+            const int hb = split * AM_H / n, he = (split + 1) * AM_H / n;
+            for (int e = tid; e < (he - hb) * (AM_KVL / 4); e += AM_SOFTMAX_THREADS) {
+                const int h = hb + e / (AM_KVL / 4), d4 = e % (AM_KVL / 4);
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int q = 0; q < n; ++q) {
+                    const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(stage, q) + h * AM_KVL + d4 * 4);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+                const uint32_t w0 = (uint32_t)rv_f32_to_bf16(acc.x) | ((uint32_t)rv_f32_to_bf16(acc.y) << 16);
+                const uint32_t w1 = (uint32_t)rv_f32_to_bf16(acc.z) | ((uint32_t)rv_f32_to_bf16(acc.w) << 16);
+                *reinterpret_cast<uint2*>(A.out + ((size_t)b * AM_H + h) * AM_KVL + d4 * 4) = make_uint2(w0, w1);
+            }
+        }
+        cluster.sync();                                                       // [3] nobody reads this CTA's memory any more
     }
 
     tc::tc_fence_before();
@@ -648,14 +741,30 @@ attend_mma_kernel(AttendMmaArgs A) {
     if (tid == 0 && *abort_flag) atomicCAS(A.err, 0, *abort_flag);
 }
 
+// A CTA takes a whole SM (shared memory), and the CTAs of a sequence form one thread-block cluster (co-scheduled
+// inside a GPC). A batch is split only as far as all its clusters are resident at once: the largest cluster size
+// (<= 8) for which the device reports room for B clusters; anything more would run as a second wave.
 int mma_splits(int B) {
-    if (B >= 100) return 1;
-    int n = (148 + B / 2) / B;
+    static int cache[149];   // 0 = not asked yet
+    if (B <= 0 || B > 74) return 1;
+    if (cache[B]) return cache[B];
+    cudaFuncSetAttribute(attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
+    int n = 148 / B;
     if (n > AM_MAX_SPLITS) n = AM_MAX_SPLITS;
-    return n < 1 ? 1 : n;
+    for (; n > 1; --n) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)n, (unsigned)B); cfg.blockDim = dim3(AM_THREADS); cfg.dynamicSmemBytes = SM_TOTAL;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = (unsigned)n; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        int active = 0;
+        if (cudaOccupancyMaxActiveClusters(&active, attend_mma_kernel, &cfg) == cudaSuccess && active >= B) break;
+        (void)cudaGetLastError();
+    }
+    cache[B] = n < 1 ? 1 : n;
+    return cache[B];
 }
-
-size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 }  // namespace
 
@@ -663,17 +772,13 @@ extern "C" bool rivoli_attend_mma_supported(const DsaGeom* g) {
     return g->n_heads == AM_H && g->kv_lora == AM_KVL && g->rope_dim == AM_ROPE;
 }
 
-// scratch layout: [err 256 B][partials]. The error word is sticky: it keeps the first failure
+// scratch layout: [err 256 B]. The error word is sticky: it keeps the first failure
 // until rivoli_attend_mma_status reads and clears it, so it must be zero before the first call.
 extern "C" size_t rivoli_attend_mma_scratch_bytes(const DsaGeom* g, int B) {
-    const size_t part = mma_splits(B) > 1 ? (size_t)B * mma_splits(B) * AM_H * (AM_KVL + 2) * sizeof(float) : 0;
-    return 256 + align256(part);
+    (void)g; (void)B;
+    return 256;
 }
 
-extern "C" void rivoli_attend_combine_paged(const float* partial, int H, int kvl, int n_splits, int B, uint16_t* out,
-                                            float* out_m, float* out_lse, const int32_t* n_rows, long long cap,
-                                            int rows_lo, int rows_hi, int serve_empty, const uint32_t* rows,
-                                            long long row_stride, long long dense_cap, cudaStream_t st);
 extern "C" int rivoli_attend_simt_short_rows(const DsaGeom* g, const uint16_t* q, const uint8_t* latent_pool,
                                              const float* latent_scale, const int32_t* block_table,
                                              const uint32_t* rows, int row_stride, const int32_t* n_rows, int B,
@@ -711,9 +816,7 @@ extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q,
     if (!scratch) return 1001;
     if (((uintptr_t)latent_pool | (uintptr_t)scratch | (uintptr_t)q | (uintptr_t)out) & 15) return 1005;
     cudaStream_t st = (cudaStream_t)stream;
-    uint8_t* sp = static_cast<uint8_t*>(scratch);
-    int* err = reinterpret_cast<int*>(sp);
-    float* partial = reinterpret_cast<float*>(sp + 256);
+    int* err = reinterpret_cast<int*>(scratch);
     const int n_splits = mma_splits(B);
     int min_rows = g_am_min_rows_override >= 0 ? g_am_min_rows_override : AM_MIN_ROWS;
     if (min_rows_hint >= min_rows) min_rows = 0;          // the caller vouches that no sequence is that short
@@ -729,18 +832,21 @@ extern "C" int rivoli_attend_mma_paged_bf16(const DsaGeom* g, const uint16_t* q,
     rv_drain_error();
     AttendMmaArgs a{q, g->softmax_scale, latent_pool, latent_scale, block_table, rows, row_stride, n_rows,
                     g->page_tokens, g->max_pages_per_seq, g->n_pool_pages, n_splits,
-                    out, out_m, out_lse, n_splits > 1 ? partial : nullptr, err,
+                    out, out_m, out_lse, err,
                     min_rows, q_early ? 1 : 0, g_am_max_polls, withhold};
     cudaFuncSetAttribute(attend_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
-    rv_launch_dependent(attend_mma_kernel, dim3(n_splits, B), dim3(AM_THREADS), (size_t)SM_TOTAL, st, a);
-    if (int e = rv_launch_status()) return e;
-    if (n_splits > 1) {
-        const long long cap = rows ? (long long)row_stride : (long long)g->max_pages_per_seq * g->page_tokens;
-        rivoli_attend_combine_paged(partial, AM_H, AM_KVL, n_splits, B, out, out_m, out_lse, n_rows, cap, min_rows, 0x7fffffff, 1,
-                                    rows, row_stride, (long long)g->max_pages_per_seq * g->page_tokens, st);
-        return rv_launch_status();
-    }
-    return 0;
+    // one CTA per (sequence, split); the splits of a sequence are one thread-block cluster and merge inside the kernel
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)n_splits, (unsigned)B); cfg.blockDim = dim3(AM_THREADS);
+    cfg.dynamicSmemBytes = (size_t)SM_TOTAL; cfg.stream = st;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    at[1].id = cudaLaunchAttributeClusterDimension;
+    at[1].val.clusterDim.x = (unsigned)n_splits; at[1].val.clusterDim.y = 1; at[1].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = n_splits > 1 ? 2 : 1;
+    (void)cudaLaunchKernelEx(&cfg, attend_mma_kernel, a);
+    return rv_launch_status();
 }
 
 // Synchronises `stream`; 1008 if a bounded device-side wait of the last call gave up.
