@@ -43,7 +43,7 @@ constexpr int IM_HD = 128;         // index dim = one 128-byte swizzle row
 constexpr int IM_NPAD = 32;        // heads padded to N = 32
 constexpr int IM_NS = 6;           // key-tile stages in flight
 constexpr int IM_NACC = 4;         // TMEM accumulators (32 columns each)
-constexpr int IM_TPI = 16;         // tiles per work item
+constexpr int IM_TPI = 16;         // most tiles per work item (a launch picks fewer when the batch is small: IndexMmaArgs::tpi)
 constexpr int IM_THREADS = 192;    // warps 0-3 epilogue, 4 producer, 5 MMA
 constexpr int IM_STAGE_BYTES = IM_TILE * IM_HD;   // 16 KiB
 constexpr int IM_Q_BYTES = IM_NPAD * IM_HD;       // 4 KiB
@@ -56,6 +56,7 @@ struct IndexMmaArgs {
     const uint8_t* index_pool; const float* index_scale; const int32_t* block_table; const int32_t* seq_len;
     float* scores; int score_stride; int B;
     int* err;              // device error word (0 = ok)
+    int tpi;               // tiles per work item, 1 .. IM_TPI: small enough that every persistent CTA gets work
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -191,8 +192,9 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
     rv_grid_dep_trigger();   // the selection kernel may be scheduled; it waits for this grid before reading scores
     rv_grid_dep_wait();      // query codes, head scales and this step's appended keys come from the kernel before
 
+    const int tpi = A.tpi;
     const int max_tiles = (A.score_stride + IM_TILE - 1) / IM_TILE;
-    const int chunks = (max_tiles + IM_TPI - 1) / IM_TPI;
+    const int chunks = (max_tiles + tpi - 1) / tpi;
     const int n_items = A.B * chunks;
 
     if (warp == 4) {
@@ -206,11 +208,11 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int b = item / chunks, c = item - b * chunks;
             const int nt = min(A.seq_len[b], A.score_stride);
-            const int tile_end = min((c + 1) * IM_TPI, (nt + IM_TILE - 1) / IM_TILE);
-            if (c * IM_TPI >= tile_end) continue;
-            const int first_lp = c * IM_TPI * ppt;
+            const int tile_end = min((c + 1) * tpi, (nt + IM_TILE - 1) / IM_TILE);
+            if (c * tpi >= tile_end) continue;
+            const int first_lp = c * tpi * ppt;
             __syncwarp();
-            for (int j = lane; j < IM_TPI * ppt; j += 32) {
+            for (int j = lane; j < tpi * ppt; j += 32) {
                 const int lp = first_lp + j;
                 int pg = -1;
                 const bool live = lp < g.max_pages_per_seq && lp * P < nt;
@@ -223,17 +225,17 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
             }
             __syncwarp();
             const int qb = items_done & 1;
-            for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
+            for (int tile = c * tpi; tile < tile_end && ok; ++tile) {
                 const int s = it % IM_NS;
                 ok = tc::mbar_wait_warp(&bars.empty[s], ((it / IM_NS) & 1) ^ 1, &abort_flag, 11);
                 if (!ok) break;
-                const bool first = tile == c * IM_TPI;
+                const bool first = tile == c * tpi;
                 if (first) {
                     ok = tc::mbar_wait_warp(&bars.qfree[qb], ((items_done >> 1) & 1) ^ 1, &abort_flag, 12);
                     if (!ok) break;
                 }
                 if (lane == 0) {
-                    const int pbase = (tile - c * IM_TPI) * ppt;
+                    const int pbase = (tile - c * tpi) * ppt;
                     uint32_t bytes = first ? (uint32_t)nh * IM_HD : 0u;
                     for (int p2 = 0; p2 < ppt; ++p2) bytes += s_pg[pbase + p2] >= 0 ? (uint32_t)P * IM_HD : 0u;
                     tc::mbar_arrive_expect_tx(&bars.full[s], bytes);
@@ -259,9 +261,9 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int b = item / chunks, c = item - b * chunks;
             const int nt = min(A.seq_len[b], A.score_stride);
-            const int tile_end = min((c + 1) * IM_TPI, (nt + IM_TILE - 1) / IM_TILE);
+            const int tile_end = min((c + 1) * tpi, (nt + IM_TILE - 1) / IM_TILE);
             const int qb = items_done & 1;
-            for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
+            for (int tile = c * tpi; tile < tile_end && ok; ++tile) {
                 const int s = it % IM_NS, a = it % IM_NACC;
                 ok = tc::mbar_wait_warp(&bars.full[s], (it / IM_NS) & 1, &abort_flag, 21) &&
                      tc::mbar_wait_warp(&bars.tempty[a], ((it / IM_NACC) & 1) ^ 1, &abort_flag, 22);
@@ -280,7 +282,7 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
                 __syncwarp();
                 ++it;
             }
-            if (c * IM_TPI < tile_end) ++items_done;      // items without tiles never touched a q buffer
+            if (c * tpi < tile_end) ++items_done;      // items without tiles never touched a q buffer
         }
     } else {
         // ------------------------------ epilogue: TMEM -> scores --------------------------------
@@ -289,8 +291,8 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int b = item / chunks, c = item - b * chunks;
             const int nt = min(A.seq_len[b], A.score_stride);
-            const int tile_end = min((c + 1) * IM_TPI, (nt + IM_TILE - 1) / IM_TILE);
-            if (c * IM_TPI >= tile_end) continue;
+            const int tile_end = min((c + 1) * tpi, (nt + IM_TILE - 1) / IM_TILE);
+            if (c * tpi >= tile_end) continue;
             tc::named_barrier(1, 128);  // previous item's constants are no longer read
             if (tid < IM_NPAD) {
                 // a_t / s_k = sum_h (w_h ws s_q[h] ds) * max(cd_h, 0): the exact formula up to a few
@@ -299,7 +301,7 @@ index_score_mma_kernel(IndexMmaArgs A, const __grid_constant__ CUtensorMap tm_ke
                                            g.index_dscale : 0.0f;
             }
             tc::named_barrier(1, 128);
-            for (int tile = c * IM_TPI; tile < tile_end && ok; ++tile) {
+            for (int tile = c * tpi; tile < tile_end && ok; ++tile) {
                 const int a = it % IM_NACC;
                 const int t = tile * IM_TILE + tid;
                 ok = tc::mbar_wait_warp(&bars.tfull[a], (it / IM_NACC) & 1, &abort_flag, 31);
@@ -419,14 +421,21 @@ static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* i
     if (int e = rv_launch_status()) return e;
 
     IndexMmaArgs ma{*g, s.qcodes, s.qscales, w, index_pool, index_scale, block_table, seq_len,
-                    s.scores, score_stride, B, s.err};
+                    s.scores, score_stride, B, s.err, IM_TPI};
     const size_t smem1 = (size_t)IM_NS * IM_STAGE_BYTES + 2 * IM_Q_BYTES + 1024;
     cudaFuncSetAttribute(index_score_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int max_tiles = (score_stride + IM_TILE - 1) / IM_TILE;
-    const int n_items = B * ((max_tiles + IM_TPI - 1) / IM_TPI);
+    // work items of 16 tiles; when that leaves SMs without any item (a small batch), smaller items: about four per SM
+    // (measured: 17.9 -> 15.2 us at batch 16 x 16,384 tokens, while batches that already fill the chip lose 10 % to the
+    // per-item set-up with smaller items)
+    if ((long long)B * ((max_tiles + IM_TPI - 1) / IM_TPI) < sms) {
+        long long tpi = (long long)B * max_tiles / (4LL * sms);
+        ma.tpi = (int)(tpi < 2 ? 2 : (tpi > IM_TPI ? IM_TPI : tpi));
+    }
+    const int n_items = B * ((max_tiles + ma.tpi - 1) / ma.tpi);
     const int grid = n_items < 2 * sms ? n_items : 2 * sms;
     CUtensorMap tm_keys, tm_q;
     if (int e = rivoli::make_tmap_rows_sw128(&tm_keys, index_pool, (uint64_t)g->n_pool_pages * g->page_tokens, IM_HD,
