@@ -584,7 +584,8 @@ bool select_cluster_plan(int B, int score_stride, int* cluster, int* ept, int* t
     // between CTAs at all. Smaller batches spread a sequence over a cluster of 2 to 8 CTAs of 512 threads, about two
     // CTAs per SM at most.
     int C = 1, NT = 512;
-    while (C < SEL_MAX_CLUSTER && (long long)B * C * 2 <= 2 * 148) C *= 2;
+    if ((long long)B * 4 < 3 * 148)   // from three quarters of the SMs on, one CTA per sequence (measured at batch 128: 161 against 166 us per step with clusters of 2)
+        while (C < SEL_MAX_CLUSTER && (long long)B * C * 2 <= 2 * 148) C *= 2;
     if (g_sel_cluster_override > 0) C = g_sel_cluster_override;
     if (C == 1 && (long long)1024 * 16 >= score_stride) NT = 1024;   // 16 keys per thread fit the 64 registers of a 1024-thread CTA
     for (;;) {
