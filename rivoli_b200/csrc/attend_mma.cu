@@ -42,6 +42,8 @@
 // reference by more than 3 (log2) the references stand (one barrier-with-OR per tile, no exchange);
 // otherwise the exact per-head maxima are taken and O is rescaled through TMEM. P' carries 2^5, so
 // it stays <= 256 < 448 and typical weights keep both e4m3 terms in the normal range.
+// A batch too small to fill the chip is split: the CTAs of a sequence form one thread-block cluster (up to 8), each takes
+// a contiguous range of tiles, and they merge their (maximum, sum, O) through distributed shared memory inside the kernel.
 // All waits are bounded (tc_common.cuh).
 #include <cooperative_groups.h>
 
