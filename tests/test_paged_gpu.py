@@ -271,6 +271,12 @@ ATTEND_CASES = {
     "every-tile-count": dict(seed=45, B=12, ctx=[128, 200, 256, 257, 384, 511, 640, 768, 1024, 1300, 1700, 2047],
                              top_k=2048),
     "big-batch-one-split": dict(seed=43, B=100, ctx=[200] * 100, top_k=128),
+    # batches that split every sequence over a thread-block cluster of 7, 6, 5 and 3 CTAs (148 SMs / B), with sequences
+    # of fewer tiles than CTAs and some on the f32 kernel inside the same launch
+    "cluster-of-7": dict(seed=46, B=20, ctx=[700, 64, 130, 2] + [300 + 37 * i for i in range(16)], top_k=512),
+    "cluster-of-6": dict(seed=47, B=24, ctx=[513, 129] + [200 + 29 * i for i in range(22)], top_k=512),
+    "cluster-of-5": dict(seed=48, B=29, ctx=[640] + [150 + 17 * i for i in range(28)], top_k=512),
+    "cluster-of-3": dict(seed=49, B=40, ctx=[384, 128, 1] + [140 + 11 * i for i in range(37)], top_k=256),
 }
 
 
