@@ -431,7 +431,9 @@ static int select_impl(const DsaGeom* g, const AppendArgs* ap, const uint16_t* i
     // work items of 16 tiles; when that leaves SMs without any item (a small batch), smaller items: about four per SM
     // (measured: 17.9 -> 15.2 us at batch 16 x 16,384 tokens, while batches that already fill the chip lose 10 % to the
     // per-item set-up with smaller items)
-    if ((long long)B * ((max_tiles + IM_TPI - 1) / IM_TPI) < sms) {
+    if ((long long)B * ((max_tiles + IM_TPI - 1) / IM_TPI) >= 6LL * sms) {
+        ma.tpi = IM_TPI / 2;   // plenty of items: halves of them even out the last round (measured: 160.6 -> 158.6 us per step at batch 128 x 16,384)
+    } else if ((long long)B * ((max_tiles + IM_TPI - 1) / IM_TPI) < sms) {
         long long tpi = (long long)B * max_tiles / (4LL * sms);
         ma.tpi = (int)(tpi < 2 ? 2 : (tpi > IM_TPI ? IM_TPI : tpi));
     }
