@@ -2,7 +2,7 @@
 //   cd = left fold over d of qcode[h][d] * kcode[t][d]   (each product of two e4m3 values is exact in f32, so the fused
 //        multiply-add IS the reference's acc + q * k: crates/engine/tests/indexer_kernel.rs:237-249)
 //   dot = (cd * s_q[h]) * s_k[t];  term_h = (w[h] * wscale) * max(dot * dscale, 0);  score = fold over h ascending.
-// A warp takes TOK tokens per pass (their loads are in flight together and they share the q reads), lane = head
+// A warp takes TOK tokens per pass (their loads are in flight together and they share the decoded q values), lane = head
 // (index_heads <= 32), index_dim = 128 (one 4-code word per lane).
 #pragma once
 
@@ -13,15 +13,14 @@
 
 constexpr int RS_HD = 128;
 
-// q codes of one sequence as f32, transposed to [dim][head] in shared memory (lane = head on both sides: no bank
-// conflicts). qf holds RS_HD * 32 floats. All threads of the CTA call it; the caller synchronises afterwards.
-__device__ __forceinline__ void rv_rescore_stage_q(const uint8_t* __restrict__ qcodes_seq, int nh, float* qf) {
+// q codes of one sequence, PACKED as they lie in memory (word w of head h = its dims 4w .. 4w+3), transposed to
+// [word][head] in shared memory (lane = head on both sides: no bank conflicts). qf holds (RS_HD / 4) * 32 words. The fold
+// decodes a word into its four f32 values on the fly (exactly: every e4m3 value is an f32): one shared-memory load per
+// four dims instead of four. All threads of the CTA call it; the caller synchronises afterwards.
+__device__ __forceinline__ void rv_rescore_stage_q(const uint8_t* __restrict__ qcodes_seq, int nh, uint32_t* qf) {
     for (int e = threadIdx.x; e < 32 * (RS_HD / 4); e += blockDim.x) {
         const int h = e & 31, d4 = e >> 5;
-        const uint32_t cw = h < nh ? *reinterpret_cast<const uint32_t*>(qcodes_seq + (size_t)h * RS_HD + d4 * 4) : 0u;
-        const float2 x = rv_e4m3x2_to_f32x2((uint16_t)(cw & 0xffff)), y = rv_e4m3x2_to_f32x2((uint16_t)(cw >> 16));
-        qf[(d4 * 4 + 0) * 32 + h] = x.x; qf[(d4 * 4 + 1) * 32 + h] = x.y;
-        qf[(d4 * 4 + 2) * 32 + h] = y.x; qf[(d4 * 4 + 3) * 32 + h] = y.y;
+        qf[d4 * 32 + h] = h < nh ? *reinterpret_cast<const uint32_t*>(qcodes_seq + (size_t)h * RS_HD + d4 * 4) : 0u;
     }
 }
 
@@ -29,7 +28,7 @@ __device__ __forceinline__ void rv_rescore_stage_q(const uint8_t* __restrict__ q
 // kf = this WARP's staging of TOK key rows as f32 (TOK * RS_HD floats). my_sq / my_wh = this lane's head scale and
 // weight * wscale (0 for lanes >= nh). emit(position, score) is called by one lane per token.
 template <int WARPS, int TOK, class Emit>
-__device__ __forceinline__ void rv_rescore_listed(const uint32_t* toks, uint32_t ln, const float* qf, float* kf,
+__device__ __forceinline__ void rv_rescore_listed(const uint32_t* toks, uint32_t ln, const uint32_t* qf, float* kf,
                                                   const int32_t* __restrict__ bt, const DsaGeom& g,
                                                   const uint8_t* __restrict__ index_pool,
                                                   const float* __restrict__ index_scale, float my_sq, float my_wh,
@@ -68,8 +67,9 @@ __device__ __forceinline__ void rv_rescore_listed(const uint32_t* toks, uint32_t
             constexpr int NT = decltype(ntok)::value < TOK ? decltype(ntok)::value : TOK;
 #pragma unroll 4
             for (int d = 0; d < hd; d += 4) {
-                const float q0f = qf[(d + 0) * 32 + lane], q1f = qf[(d + 1) * 32 + lane];
-                const float q2f = qf[(d + 2) * 32 + lane], q3f = qf[(d + 3) * 32 + lane];
+                const uint32_t qc = qf[(d >> 2) * 32 + lane];
+                const float2 qlo = rv_e4m3x2_to_f32x2((uint16_t)(qc & 0xffff)), qhi = rv_e4m3x2_to_f32x2((uint16_t)(qc >> 16));
+                const float q0f = qlo.x, q1f = qlo.y, q2f = qhi.x, q3f = qhi.y;
 #pragma unroll
                 for (int e = 0; e < NT; ++e) {
                     const float4 k4 = *reinterpret_cast<const float4*>(kf + e * hd + d);   // broadcast read

@@ -134,8 +134,8 @@ index_select_cluster_kernel(SelArgs A) {
     const int C = SOLO ? 1 : (int)cluster.dim_blocks().x, r = SOLO ? 0 : (int)cluster.block_rank();
     extern __shared__ __align__(16) uint32_t sel_smem[];
     __shared__ SelXc xc;
-    float* qf = reinterpret_cast<float*>(sel_smem);                       // [SEL_HD][32] q codes as f32, [dim][head]
-    float* kfw = qf + SEL_HD * 32;                                        // [NW][SEL_TOK][SEL_HD] key rows as f32
+    uint32_t* qf = sel_smem;                                              // [SEL_HD / 4][32] packed q codes, [word][head]
+    float* kfw = reinterpret_cast<float*>(qf + (SEL_HD / 4) * 32);        // [NW][SEL_TOK][SEL_HD] key rows as f32
     uint32_t* hist = reinterpret_cast<uint32_t*>(kfw + NW * SEL_TOK * SEL_HD);   // [SEL_BINS]; later `dec`
     uint32_t* l_tok = hist + SEL_BINS;                                    // [SEL_LIST] this CTA's band tokens
     uint32_t* l_key = l_tok + SEL_LIST;                                   // [SEL_LIST] their exact keys
@@ -610,7 +610,7 @@ namespace rivoli {
 int launch_index_select_cluster(const SelArgs& a, int B, cudaStream_t st) {
     int C = 1, ept = 4, nt = 512;
     if (!select_cluster_plan(B, a.score_stride, &C, &ept, &nt)) return 1002;
-    const size_t smem = ((size_t)SEL_HD * 32 + (size_t)(nt / 32) * SEL_TOK * SEL_HD + SEL_BINS + 4 * SEL_LIST) * 4;
+    const size_t smem = ((size_t)(SEL_HD / 4) * 32 + (size_t)(nt / 32) * SEL_TOK * SEL_HD + SEL_BINS + 4 * SEL_LIST) * 4;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(B * C)); cfg.blockDim = dim3((unsigned)nt); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute at[2];

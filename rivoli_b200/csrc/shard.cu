@@ -46,8 +46,8 @@ shard_rescore_kernel(DsaGeom g, const uint8_t* __restrict__ qcodes, const float*
                      const float* __restrict__ index_scale, const int32_t* __restrict__ block_table,
                      const uint32_t* __restrict__ rows, const int32_t* __restrict__ n_sel, float* __restrict__ cand) {
     extern __shared__ __align__(16) float sr_smem[];
-    float* qf = sr_smem;                                   // [RS_HD][32]
-    float* kfw = qf + RS_HD * 32;                          // [SH_WARPS][SH_TOK][RS_HD]
+    uint32_t* qf = reinterpret_cast<uint32_t*>(sr_smem);   // [RS_HD / 4][32] packed q codes
+    float* kfw = sr_smem + (RS_HD / 4) * 32;               // [SH_WARPS][SH_TOK][RS_HD]
     const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nh = g.index_heads, k = g.top_k;
     const int per_cta = SH_WARPS * SH_TOK * 4;             // candidate slots of one CTA
@@ -199,7 +199,7 @@ RIVOLI_API int rivoli_shard_candidates(const DsaGeom* g, const uint16_t* index_q
         return e;
     const uint8_t* qcodes; const float* qscales;
     rivoli_index_select_query_codes(g, B, score_stride, select_scratch, &qcodes, &qscales);
-    const size_t smem = ((size_t)RS_HD * 32 + (size_t)SH_WARPS * SH_TOK * RS_HD) * 4;
+    const size_t smem = ((size_t)(RS_HD / 4) * 32 + (size_t)SH_WARPS * SH_TOK * RS_HD) * 4;
     const int per_cta = SH_WARPS * SH_TOK * 4;
     rv_drain_error();
     cudaFuncSetAttribute(shard_rescore_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
