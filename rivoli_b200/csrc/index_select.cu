@@ -629,7 +629,7 @@ int launch_index_select_cluster(const SelArgs& a, int B, cudaStream_t st) {
         if (ept == 4) RV_SEL(4, 1024);
         else if (ept == 8) RV_SEL(8, 1024);
         else if (ept == 16) RV_SEL(16, 1024);
-        else RV_SEL(32, 1024);
+        else return 1002;   // the plan takes 1024-thread CTAs only up to 16 keys per thread
     } else {
         if (ept == 4) RV_SEL(4, 512);
         else if (ept == 8) RV_SEL(8, 512);
