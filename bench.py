@@ -54,7 +54,7 @@ KV_LORA, ROPE = 512, 64
 # dram__bytes_read.sum + dram__bytes_write.sum per launch and per sequence of the cfg3 shape, from ncu captures of
 # these kernels at batch 32 (traffic grows in proportion to the sequences a launch processes; a full launch is the
 # per-sequence figure x the batch): profiles/ncu_hot_kernels_cfg3_batch32.md
-TRAFFIC_PER_SEQ = {"index_score_mma_kernel": (67.31e6 + 0.77e6) / 32, "attend_mma_kernel": (46.23e6 + 0.12e6) / 32,
+TRAFFIC_PER_SEQ = {"index_score_mma_kernel": (67.31e6 + 0.91e6) / 32, "attend_mma_kernel": (46.23e6 + 0.12e6) / 32,
                    "index_select_cluster_kernel": 4.86e6 / 32}
 TRAFFIC_SOURCE = "ncu dram read+write of one launch at batch 32 of the cfg3 shape, per sequence x batch (profiles/ncu_hot_kernels_cfg3_batch32.md)"
 METRIC = "DSA decode layer-steps/s (batch×ctx)"
